@@ -1,0 +1,632 @@
+"""CPU oracle for the LaCT large-chunk fast-weight TTT step.
+
+TEST INFRASTRUCTURE ONLY.  Nothing in the product package may import this module; it is
+used by the tests, by the smoke check and by the CPU-baseline leg of the benchmark as the
+checker / timed CPU baseline, never as the thing shipped.
+
+It restates, with plain PyTorch CPU tensor ops, the algorithm of the reference repository
+a1600012888/LaCT for this path.  Every public function names the reference file:line it
+follows.  Two numerics policies exist:
+
+* ``policy="ref"``  - the arithmetic of the reference's *unfused* PyTorch functions, dtype for
+  dtype (fp32 inputs run in fp32; ``autocast=True`` emulates ``torch.autocast(bfloat16)`` by
+  casting both bmm operands to bf16).  With fp32 inputs it is bit-identical on CPU to the
+  reference functions; the committed fixtures under ``tests/golden`` (made by importing the
+  reference, see ``tests/golden/make_golden.py``) pin that.
+* ``policy="fused"`` - the rounding model of the reference's fused (Triton) path, which is
+  also the rounding model of the CUDA kernels: bf16 operands, fp32 accumulators, fp32
+  epilogue math, one rounding to bf16 when a tile is stored, bf16 batched-GEMM outputs,
+  fp32 momentum / renormalisation, Newton-Schulz in bf16.
+
+Parity status: PINNED against outputs of the reference itself (fixtures generated in the build
+container by running the reference functions on CPU in eager mode).  The reference ships no
+golden vectors or tests of its own for this path.
+"""
+from __future__ import annotations
+
+import dataclasses
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+import torch.nn.functional as F
+
+BF16 = torch.bfloat16
+
+# Newton-Schulz coefficient triples.
+# Tuned five-step table: lact_llm/lact_model/ttt_operation.py:49-55 (same in
+# ttt_operation_fused_kernel.py:46-52, minimal_implementations/bidirectional_lact_layer.py:53-59).
+NS_TUNED5 = (
+    (4.0848, -6.8946, 2.9270),
+    (3.9505, -6.3029, 2.6377),
+    (3.7418, -5.5913, 2.3037),
+    (2.8769, -3.1427, 1.2046),
+    (2.8366, -3.0525, 1.2012),
+)
+# Constant triple: lact_nvs/lact_ttt.py:50, lact_ar_video/minVid/models/blocks/functions.py:56.
+NS_CONST = (3.4445, -4.7750, 2.0315)
+
+
+# ----------------------------------------------------------------------------------------------
+# small helpers
+# ----------------------------------------------------------------------------------------------
+def silu_backprop(dy: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    """d/dx of silu applied to dy.  lact_llm/lact_model/ttt_operation.py:5-17."""
+    sigma = torch.sigmoid(x)
+    return dy * sigma * (1 + x * (1 - sigma))
+
+
+def newton_schulz(G: torch.Tensor, steps: Optional[int] = None) -> torch.Tensor:
+    """Batched Newton-Schulz orthogonalisation in bf16 with the reference's eager rounding points.
+
+    ``steps=None``: tuned 5-triple table, lact_llm/lact_model/ttt_operation.py:30-66.
+    ``steps=int`` : constant triple repeated ``steps`` times, lact_nvs/lact_ttt.py:32-67.
+    """
+    assert G.dim() == 3
+    coeffs = NS_TUNED5 if steps is None else (NS_CONST,) * steps
+    X = G.bfloat16()
+    flip = G.size(1) > G.size(2)
+    if flip:
+        X = X.transpose(1, 2)
+    X = X / (X.norm(dim=(1, 2), keepdim=True) + 1e-7)
+    for a, b, c in coeffs:
+        A = X @ X.transpose(1, 2)
+        B = b * A + c * A @ A
+        X = a * X + B @ X
+    if flip:
+        X = X.transpose(1, 2)
+    return X
+
+
+def newton_schulz_f64(G: torch.Tensor, steps: Optional[int] = None) -> torch.Tensor:
+    """The same iteration carried out in float64 on the bf16-rounded input (accuracy yardstick)."""
+    coeffs = NS_TUNED5 if steps is None else (NS_CONST,) * steps
+    X = G.bfloat16().double()
+    flip = G.size(1) > G.size(2)
+    if flip:
+        X = X.transpose(1, 2)
+    X = X / (X.norm(dim=(1, 2), keepdim=True) + 1e-7)
+    for a, b, c in coeffs:
+        A = X @ X.transpose(1, 2)
+        B = b * A + (c * A) @ A
+        X = a * X + B @ X
+    if flip:
+        X = X.transpose(1, 2)
+    return X
+
+
+@dataclasses.dataclass
+class Numerics:
+    """Numerics policy (see module docstring)."""
+
+    policy: str = "ref"  # "ref" | "fused"
+    autocast: bool = False  # ref policy: emulate torch.autocast(bfloat16) around bmm
+
+
+def _bmm(a: torch.Tensor, b: torch.Tensor, nm: Numerics) -> torch.Tensor:
+    if nm.autocast:
+        return torch.bmm(a.to(BF16), b.to(BF16))
+    return torch.bmm(a, b)
+
+
+def _f32mm_round(a: torch.Tensor, b: torch.Tensor, out_dtype) -> torch.Tensor:
+    """GEMM with fp32 accumulation of (bf16-valued) operands, one rounding at the store."""
+    return torch.bmm(a.float(), b.float()).to(out_dtype)
+
+
+# ----------------------------------------------------------------------------------------------
+# apply / fast-weight gradient, LLM layout (w0,w2: [B,H,D], w1: [B,D,H])
+# ----------------------------------------------------------------------------------------------
+def apply_ref(w0, w1, w2, q, nm: Numerics) -> torch.Tensor:
+    """o = w1 (silu(w0 q^T) * (w2 q^T)), returned as [B, l, D].
+
+    lact_llm/lact_model/ttt_operation.py:139-144 (also :203-212).
+    """
+    qt = q.transpose(1, 2)
+    h = _bmm(w2, qt, nm)
+    gate = F.silu(_bmm(w0, qt, nm))
+    return _bmm(w1, gate * h, nm).transpose(1, 2)
+
+
+def grads_ref(w0, w1, w2, k, v, lr0, lr1, lr2, nm: Numerics, style: str = "llm", w_scale: float = 1.0):
+    """Per-token-lr weighted gradient of -<f(k), v> w.r.t. w0, w1, w2 (to be ADDED to the weights).
+
+    style "llm": lact_llm/lact_model/ttt_operation.py:146-168 (lr-scaled operand cast back with
+    type_as);  style "ar": lact_ar_video/minVid/models/blocks/ar_lact_swa_repeat.py:110-138
+    (lr * w_scale, no cast).
+    """
+    kt = k.transpose(1, 2)
+    vt = v.transpose(1, 2)
+    g = _bmm(w0, kt, nm)
+    h = _bmm(w2, kt, nm)
+    silu_g = F.silu(g)
+    hidden = silu_g * h
+    dhidden = _bmm(w1.transpose(1, 2), vt, nm)
+    dh2 = dhidden * silu_g
+    dg = silu_backprop(dhidden * h, g)
+    if style == "llm":
+        dw1 = _bmm(vt, (hidden.transpose(1, 2) * lr1).type_as(vt), nm)
+        dw0 = _bmm(dg, (k * lr0).type_as(dg), nm)
+        dw2 = _bmm(dh2, (k * lr2).type_as(dh2), nm)
+    else:
+        dw1 = _bmm(vt, hidden.transpose(1, 2) * lr1 * w_scale, nm)
+        dw0 = _bmm(dg, k * lr0 * w_scale, nm)
+        dw2 = _bmm(dh2, k * lr2 * w_scale, nm)
+    return dw0, dw1, dw2
+
+
+def apply_fused(w0w2_b, w1_b, q) -> torch.Tensor:
+    """Fused-path apply: bf16 operands, fp32 SwiGLU epilogue, hidden rounded to bf16, bf16 out.
+
+    lact_llm/lact_model/lact_triton_kernels/lact_swiglu_ffn.py:19-44 with the kernel epilogue of
+    triton_swiglu_kernels.py:111-120; formula = reference_swiglu_ffn_fwd (lact_swiglu_ffn.py:104-116).
+    """
+    H = w0w2_b.shape[1] // 2
+    x = q.float().transpose(1, 2)
+    y0 = torch.bmm(w0w2_b[:, :H].float(), x)
+    y2 = torch.bmm(w0w2_b[:, H:].float(), x)
+    hidden = (y2 * (y0 * torch.sigmoid(y0))).to(q.dtype)  # [B,H,l]
+    return _f32mm_round(hidden.transpose(1, 2), w1_b.transpose(1, 2), q.dtype)
+
+
+def grads_fused(w0w2_b, w1_b, k, v, lr0, lr1, lr2, w_scale: float = 1.0):
+    """Fused-path gradient (DW0|DW2 [B,2H,D], DW1 [B,D,H]); lr are [B,l].
+
+    lact_llm/lact_model/lact_triton_kernels/lact_fw_grad.py:21-58; epilogue
+    triton_swiglu_bwd_with_lr.py:134-194; formula = reference_lact_swiglu_ffn_fast_weight_grads
+    (lact_fw_grad.py:268-306).
+    """
+    H = w0w2_b.shape[1] // 2
+    dt = k.dtype
+    kt = k.float().transpose(1, 2)
+    y0 = torch.bmm(w0w2_b[:, :H].float(), kt)
+    y2 = torch.bmm(w0w2_b[:, H:].float(), kt)
+    dh = torch.bmm(w1_b.float().transpose(1, 2), v.float().transpose(1, 2))
+    sigma = torch.sigmoid(y0)
+    swish = sigma * y0
+    l0 = (lr0.float() * w_scale).unsqueeze(1)
+    l1 = (lr1.float() * w_scale).unsqueeze(1)
+    l2 = (lr2.float() * w_scale).unsqueeze(1)
+    hidden = (swish * y2 * l1).to(dt)
+    dy0 = (sigma * y2 * dh * (1.0 + y0 * (1.0 - sigma)) * l0).to(dt)
+    dy2 = (swish * dh * l2).to(dt)
+    dy = torch.cat([dy0, dy2], dim=1)
+    dw0w2 = _f32mm_round(dy, k, dt)
+    dw1 = _f32mm_round(v.transpose(1, 2), hidden.transpose(1, 2), dt)
+    return dw0w2, dw1
+
+
+def l2_norm_add(x, x_add, tgt_scale, eps: float = 1e-5):
+    """(x + x_add) * rsqrt(sum((x + x_add)^2) + eps) * scale, eps INSIDE the square root.
+
+    lact_llm/lact_model/lact_triton_kernels/l2norm_triton_kernels.py:430-440 (kernel :60-94).
+    """
+    y = x.to(torch.float32) + x_add.to(torch.float32)
+    rstd = 1 / torch.sqrt(torch.sum(y * y, dim=2, keepdim=True) + eps)
+    return y * rstd * tgt_scale.unsqueeze(-1)
+
+
+def prenorm_update_with_momentum(x, dx, dx_momentum, momentum_mu, tgt_scale, eps: float = 1e-5):
+    """m = dx + mu*m; x += m; y = x / sqrt(sum x^2 + eps) * scale (bf16).
+
+    lact_llm/lact_model/lact_triton_kernels/triton_prenorm_update_with_momentum.py:10-38.
+    """
+    m = dx + dx_momentum * momentum_mu.unsqueeze(-1).unsqueeze(-1)
+    x_new = x + m
+    denom = torch.sqrt(torch.sum(x_new ** 2, dim=-1, keepdim=True) + eps)
+    return x_new, m, (x_new / denom * tgt_scale.unsqueeze(-1)).to(BF16)
+
+
+def _renorm_outer(w, n0):
+    """w / (||w|| + 1e-5) * n0 along dim 2.  lact_llm/lact_model/ttt_operation.py:198-200."""
+    return w / (w.norm(dim=2, keepdim=True) + 1e-5) * n0
+
+
+# ----------------------------------------------------------------------------------------------
+# chunk drivers.  Every driver can record the (kind, start, end) steps it executes in `trace`.
+# ----------------------------------------------------------------------------------------------
+def _rec(trace, kind, s, e, out=None):
+    if trace is not None:
+        trace.append((kind, int(s), int(e), int(s if out is None else out)))
+
+
+def block_causal_lact_swiglu(
+    w0, w1, w2, q, k, v, lr0, lr1, lr2, chunk_size=2048, use_muon=False, momentum=None,
+    *, prenorm=False, nm: Numerics = Numerics(), trace: Optional[list] = None, states: Optional[list] = None,
+):
+    """Causal apply-then-update chunk recurrence, unfused arithmetic.
+
+    Post-norm: lact_llm/lact_model/ttt_operation.py:69-214 (identical to
+    minimal_implementations/causal_lact_with_sliding_window_attn.py:83-211).
+    Pre-norm (``prenorm=True``): lact_llm/lact_model/ttt_operation.py:217-364.
+    ``states`` (optional list) receives (w0, w1, w2) after every update, for teacher-forced checks.
+    """
+    n0, n1, n2 = (w.norm(dim=2, keepdim=True) for w in (w0, w1, w2))
+    m0 = m1 = m2 = None
+    if momentum is not None:
+        m0, m1, m2 = torch.zeros_like(w0), torch.zeros_like(w1), torch.zeros_like(w2)
+    w0m, w1m, w2m = w0, w1, w2  # pre-norm master copies
+    L = k.shape[1]
+    out = torch.zeros_like(v)
+    e = 0
+    for s in range(0, L - chunk_size, chunk_size):
+        e = s + chunk_size
+        _rec(trace, "apply", s, e)
+        out[:, s:e] = apply_ref(w0, w1, w2, q[:, s:e], nm)
+        _rec(trace, "update", s, e)
+        dw0, dw1, dw2 = grads_ref(w0, w1, w2, k[:, s:e], v[:, s:e], lr0[:, s:e], lr1[:, s:e], lr2[:, s:e], nm)
+        if momentum is not None:
+            beta = momentum[:, s:e].mean(dim=1, keepdim=True)
+            dw0 = dw0 + m0 * beta
+            dw1 = dw1 + m1 * beta
+            dw2 = dw2 + m2 * beta
+            m0, m1, m2 = dw0, dw1, dw2
+        if use_muon:
+            dw1 = newton_schulz(dw1)
+            dw0 = newton_schulz(dw0)
+            dw2 = newton_schulz(dw2)
+        if prenorm:
+            w1m, w0m, w2m = w1m + dw1, w0m + dw0, w2m + dw2
+            w0, w1, w2 = _renorm_outer(w0m, n0), _renorm_outer(w1m, n1), _renorm_outer(w2m, n2)
+        else:
+            w1, w0, w2 = w1 + dw1, w0 + dw0, w2 + dw2
+            w0, w1, w2 = _renorm_outer(w0, n0), _renorm_outer(w1, n1), _renorm_outer(w2, n2)
+        if states is not None:
+            states.append((w0, w1, w2))
+    _rec(trace, "apply", e, L)
+    out[:, e:L] = apply_ref(w0, w1, w2, q[:, e:L], nm)
+    return out
+
+
+def block_causal_lact_swiglu_fused(
+    w0, w1, w2, q, k, v, lr0, lr1, lr2, chunk_size=2048, use_muon=False, momentum=None,
+    *, prenorm=False, trace: Optional[list] = None, states: Optional[list] = None,
+    teacher: Optional[Sequence[Tuple[torch.Tensor, torch.Tensor]]] = None,
+):
+    """Causal apply-then-update recurrence with the fused path's semantics and rounding.
+
+    Post-norm: lact_llm/lact_model/ttt_operation_fused_kernel.py:66-186; pre-norm: :189-316.
+    Differences from the unfused functions that are reproduced here: zero padding to a chunk
+    multiple (:112-122), Newton-Schulz on the concatenated [2H, D] matrix (:169-171), renorm
+    with eps inside the square root (post-norm, :173-174), bf16 weight shadows (:151-152).
+    ``teacher``: optional list of (w0w2, w1) master states to substitute after update i.
+    """
+    w0w2 = torch.cat([w0, w2], dim=1).contiguous()
+    n02 = w0w2.norm(dim=2, keepdim=prenorm)
+    n1 = w1.norm(dim=2, keepdim=prenorm)
+    w0w2_main, w1_main = w0w2, w1
+    if prenorm:
+        w0w2, w1 = w0w2.to(BF16), w1.to(BF16)
+    m02 = m1 = None
+    if momentum is not None:
+        m02, m1 = torch.zeros_like(w0w2_main), torch.zeros_like(w1_main)
+    L = q.shape[1]
+    C = chunk_size
+    pad = -L % C
+    padf = lambda t: F.pad(t, (0, 0, 0, pad))
+    qp, kp, vp = padf(q), padf(k), padf(v)
+    l0, l1, l2 = (padf(t)[..., 0] for t in (lr0, lr1, lr2))
+    mp = padf(momentum) if momentum is not None else None
+    n_chunks = (L + pad + C - 1) // C
+    out = torch.zeros_like(qp)
+    for ci in range(n_chunks - 1):
+        s, e = ci * C, (ci + 1) * C
+        w02b, w1b = w0w2.to(BF16), w1.to(BF16)
+        _rec(trace, "apply", s, e)
+        out[:, s:e] = apply_fused(w02b, w1b, qp[:, s:e])
+        _rec(trace, "update", s, e)
+        dw02, dw1 = grads_fused(w02b, w1b, kp[:, s:e], vp[:, s:e], l0[:, s:e], l1[:, s:e], l2[:, s:e])
+        if momentum is not None:
+            beta = mp[:, s:e].mean(dim=1, keepdim=True)
+            dw02 = dw02 + m02 * beta
+            dw1 = dw1 + m1 * beta
+            m02, m1 = dw02, dw1
+        if use_muon:
+            dw1 = newton_schulz(dw1)
+            dw02 = newton_schulz(dw02)
+        if prenorm:
+            w0w2_main = w0w2_main + dw02
+            w1_main = w1_main + dw1
+            w0w2 = (w0w2_main / (w0w2_main.norm(dim=2, keepdim=True) + 1e-5) * n02).to(BF16)
+            w1 = (w1_main / (w1_main.norm(dim=2, keepdim=True) + 1e-5) * n1).to(BF16)
+        else:
+            w0w2 = l2_norm_add(w0w2, dw02, n02, eps=1e-5)
+            w1 = l2_norm_add(w1, dw1, n1, eps=1e-5)
+        if teacher is not None:
+            if prenorm:
+                w0w2_main, w1_main = teacher[ci]
+                w0w2 = (w0w2_main / (w0w2_main.norm(dim=2, keepdim=True) + 1e-5) * n02).to(BF16)
+                w1 = (w1_main / (w1_main.norm(dim=2, keepdim=True) + 1e-5) * n1).to(BF16)
+            else:
+                w0w2, w1 = teacher[ci]
+        if states is not None:
+            states.append((w0w2_main, w1_main) if prenorm else (w0w2, w1))
+    s = (n_chunks - 1) * C
+    _rec(trace, "apply", s, L)
+    out[:, s:] = apply_fused(w0w2.to(BF16), w1.to(BF16), qp[:, s:])
+    return out[:, :L]
+
+
+def bidirectional_lact_swiglu(w0, w1, w2, q, k, v, lr0, lr1, lr2, use_muon=True,
+                              *, nm: Numerics = Numerics(), trace: Optional[list] = None):
+    """One update on all tokens, then apply to all tokens.
+
+    minimal_implementations/bidirectional_lact_layer.py:73-160, INCLUDING its quirk (:139-146):
+    with Muon the weights are first overwritten by NS(dw) and the raw dw is then added, i.e.
+    w <- renorm(NS(dw) + dw).
+    """
+    n0, n1, n2 = (w.norm(dim=2, keepdim=True) for w in (w0, w1, w2))
+    L = k.shape[1]
+    _rec(trace, "update", 0, L)
+    dw0, dw1, dw2 = grads_ref(w0, w1, w2, k, v, lr0, lr1, lr2, nm)
+    if use_muon:
+        w0 = newton_schulz(dw0)
+        w1 = newton_schulz(dw1)
+        w2 = newton_schulz(dw2)
+    w1, w0, w2 = w1 + dw1, w0 + dw0, w2 + dw2
+    w0, w1, w2 = _renorm_outer(w0, n0), _renorm_outer(w1, n1), _renorm_outer(w2, n2)
+    _rec(trace, "apply", 0, L)
+    return apply_ref(w0, w1, w2, q, nm)
+
+
+def nvs_mini_batch_apply(w0, w1, w2, q, k, v, lr0, lr1, lr2, ttt_ua_order, muon_update_steps=0,
+                         *, nm: Numerics = Numerics(), trace: Optional[list] = None):
+    """Operator-list driver in the NVS (transposed) layout: w0,w2 [B,D,H], w1 [B,H,D].
+
+    lact_nvs/lact_ttt.py:70-147.  Every update runs Newton-Schulz with the constant triple for
+    ``muon_update_steps`` iterations (0 iterations still normalises by the Frobenius norm);
+    norms are taken along dim 1; outputs of apply operators are concatenated in list order.
+    """
+    mm = (lambda a, b: a.to(BF16) @ b.to(BF16)) if nm.autocast else (lambda a, b: a @ b)
+    n0, n1, n2 = (w.detach().norm(dim=1, keepdim=True) for w in (w0, w1, w2))
+    outs = []
+    out_pos = 0
+    for start, end, update, apply in ttt_ua_order:
+        if update:
+            _rec(trace, "update", start, end)
+            ki, vi = k[:, start:end], v[:, start:end]
+            g = mm(ki, w0)
+            h = mm(ki, w2)
+            hidden = F.silu(g) * h
+            dhidden = mm(vi, w1.transpose(-1, -2))
+            dh2 = dhidden * F.silu(g)
+            dg = silu_backprop(dhidden * h, g)
+            g1 = newton_schulz(mm((hidden * lr1[:, start:end]).transpose(-1, -2), vi), muon_update_steps)
+            g0 = newton_schulz(mm((ki * lr0[:, start:end]).transpose(-1, -2), dg), muon_update_steps)
+            g2 = newton_schulz(mm((ki * lr2[:, start:end]).transpose(-1, -2), dh2), muon_update_steps)
+            w1, w0, w2 = w1 + g1, w0 + g0, w2 + g2
+            w0 = w0 / (w0.norm(dim=1, keepdim=True) + 1e-5) * n0
+            w1 = w1 / (w1.norm(dim=1, keepdim=True) + 1e-5) * n1
+            w2 = w2 / (w2.norm(dim=1, keepdim=True) + 1e-5) * n2
+        if apply:
+            if trace is not None:
+                trace.append(("apply", int(start), int(min(end, q.shape[1])), out_pos))
+            qi = q[:, start:end]
+            outs.append(mm(F.silu(mm(qi, w0)) * mm(qi, w2), w1))
+            out_pos += qi.shape[1]
+    return torch.cat(outs, dim=1), w0, w1, w2
+
+
+def ar_mini_batch(
+    w0, w1, w2, q, k, v, lr0, lr1, lr2, w_scale, num_repeat=1, mini_batch_size=-1, update_length=-1,
+    update_every=-1, use_moun=False, num_moun_iters=3, weight_norm=True, fw_momentum=None, use_momentum=False,
+    *, nm: Numerics = Numerics(), trace: Optional[list] = None,
+):
+    """Autoregressive-video training driver (update-then-apply with an `update_every` stride).
+
+    Without momentum: lact_ar_video/minVid/models/blocks/ar_lact_swa_repeat.py:22-168 (the
+    `num_repeat` loop wraps the chunk loop).  With momentum:
+    ar_lact_swa_repeat_sp.py:27-193 (which has no `num_repeat` loop: one pass).
+    """
+    L = k.shape[1]
+    if update_length == -1:
+        update_length = L
+    if mini_batch_size == -1:
+        mini_batch_size = update_length
+    if update_every == -1:
+        update_every = mini_batch_size * 2
+    n0, n1, n2 = (w.norm(dim=2, keepdim=True) for w in (w0, w1, w2))
+    out = torch.zeros_like(q)
+    first = update_every - mini_batch_size
+    _rec(trace, "apply", 0, min(first, L))
+    out[:, :first] = apply_ref(w0, w1, w2, q[:, :first], nm)
+    if use_momentum:
+        m0, m1, m2 = torch.zeros_like(w0), torch.zeros_like(w1), torch.zeros_like(w2)
+    for _ in range(1 if use_momentum else num_repeat):
+        for s in range(first, update_length, update_every):
+            e = s + mini_batch_size
+            _rec(trace, "update", s, min(e, L))
+            dw0, dw1, dw2 = grads_ref(w0, w1, w2, k[:, s:e], v[:, s:e], lr0[:, s:e], lr1[:, s:e], lr2[:, s:e],
+                                      nm, style="ar", w_scale=w_scale)
+            if use_momentum:
+                beta = fw_momentum[:, s:e].mean(dim=1, keepdim=True)
+                dw0, dw1, dw2 = dw0 + m0 * beta, dw1 + m1 * beta, dw2 + m2 * beta
+                m0, m1, m2 = dw0, dw1, dw2
+            if use_moun:
+                dw1 = newton_schulz(dw1, num_moun_iters)
+                dw0 = newton_schulz(dw0, num_moun_iters)
+                dw2 = newton_schulz(dw2, num_moun_iters)
+            w1, w0, w2 = w1 + dw1, w0 + dw0, w2 + dw2
+            if weight_norm:
+                w0, w1, w2 = _renorm_outer(w0, n0), _renorm_outer(w1, n1), _renorm_outer(w2, n2)
+            e = s + update_every
+            _rec(trace, "apply", s, min(e, L))
+            out[:, s:e] = apply_ref(w0, w1, w2, q[:, s:e], nm)
+    return out, w0, w1, w2
+
+
+def ar_mini_batch_inference(
+    w0, w1, w2, q, k, v, lr0, lr1, lr2, w_scale, num_repeat=1, mini_batch_size=-1, do_update=False,
+    use_moun=False, num_moun_iters=3, weight_norm=True, fw_momentum=None, dw0_momentum=None,
+    dw1_momentum=None, dw2_momentum=None, use_momentum=False, with_momentum_api=False,
+    *, nm: Numerics = Numerics(), trace: Optional[list] = None,
+):
+    """Autoregressive-video inference driver: at most `num_repeat` updates on the first
+    mini-batch, then apply to every query token.
+
+    lact_ar_video/minVid/models/blocks/ar_lact_swa_repeat.py:171-296 (4-tuple return) and
+    ar_lact_swa_repeat_sp.py:196-339 (momentum state in and out, 7-tuple return).
+    """
+    L = k.shape[1]
+    if mini_batch_size == -1:
+        mini_batch_size = L
+    n0, n1, n2 = (w.norm(dim=2, keepdim=True) for w in (w0, w1, w2))
+    if dw0_momentum is None and use_momentum:
+        dw0_momentum, dw1_momentum, dw2_momentum = torch.zeros_like(w0), torch.zeros_like(w1), torch.zeros_like(w2)
+    if do_update:
+        for _ in range(num_repeat):
+            e = mini_batch_size
+            _rec(trace, "update", 0, min(e, L))
+            dw0, dw1, dw2 = grads_ref(w0, w1, w2, k[:, :e], v[:, :e], lr0[:, :e], lr1[:, :e], lr2[:, :e],
+                                      nm, style="ar", w_scale=w_scale)
+            if use_momentum:
+                beta = fw_momentum[:, :e].mean(dim=1, keepdim=True)
+                dw0 = dw0 + dw0_momentum * beta
+                dw1 = dw1 + dw1_momentum * beta
+                dw2 = dw2 + dw2_momentum * beta
+                dw0_momentum, dw1_momentum, dw2_momentum = dw0, dw1, dw2
+            if use_moun:
+                dw1 = newton_schulz(dw1, num_moun_iters)
+                dw0 = newton_schulz(dw0, num_moun_iters)
+                dw2 = newton_schulz(dw2, num_moun_iters)
+            w1, w0, w2 = w1 + dw1, w0 + dw0, w2 + dw2
+            if weight_norm:
+                w0, w1, w2 = _renorm_outer(w0, n0), _renorm_outer(w1, n1), _renorm_outer(w2, n2)
+    _rec(trace, "apply", 0, L)
+    out = apply_ref(w0, w1, w2, q, nm)
+    if with_momentum_api:
+        return out, w0, w1, w2, dw0_momentum, dw1_momentum, dw2_momentum
+    return out, w0, w1, w2
+
+
+# ----------------------------------------------------------------------------------------------
+# kernel-rounding model of the general scan (what the CUDA path computes), LLM layout.
+# ----------------------------------------------------------------------------------------------
+@dataclasses.dataclass
+class ScanConfig:
+    """Semantic switches of the general scan; mirrors the C-ABI configuration struct."""
+
+    use_muon: bool = False
+    ns_steps: int = 5
+    ns_const_coeffs: bool = False  # False: tuned 5-triple table (ns_steps must be 5)
+    ns_concat: bool = False  # Newton-Schulz on cat([dw0, dw2], dim=1)
+    ns_gram_right: bool = False  # square matrices: iterate on the transpose (NVS layout)
+    renorm: str = "outer"  # "none" | "outer" (eps outside) | "inner" (eps inside sqrt)
+    prenorm: bool = False
+    prenorm_bf16: bool = False  # fused pre-norm: normalised weights are stored as bf16
+    overwrite_quirk: bool = False  # bidirectional: w <- renorm(NS(dw) + dw)
+    w_scale: float = 1.0
+    fp32_mode: bool = False  # activations / operands in fp32 (no bf16 rounding outside NS)
+
+
+def _ns_model(G, cfg: ScanConfig):
+    steps = cfg.ns_steps if cfg.ns_const_coeffs else None
+    if cfg.ns_gram_right and G.size(1) == G.size(2):
+        return newton_schulz(G.transpose(1, 2), steps).transpose(1, 2)
+    return newton_schulz(G, steps)
+
+
+def scan_model(w0, w1, w2, q, k, v, lr0, lr1, lr2, steps: Sequence[Tuple[str, int, int, int]], cfg: ScanConfig,
+               momentum=None, m_init=None, out_len: Optional[int] = None):
+    """Kernel-rounding model of the general scan.  `steps` = (kind, start, end, out_start).
+
+    Returns (o, w0, w1, w2, (m0, m1, m2) or None).  In bf16 mode the arithmetic is that of
+    `apply_fused` / `grads_fused`; in fp32 mode plain fp32.  Momentum, Newton-Schulz and the
+    renormalisation follow the reference lines cited on the drivers above.
+    """
+    act = torch.float32 if cfg.fp32_mode else BF16
+    H = w0.shape[1]
+    w0, w1, w2 = w0.float(), w1.float(), w2.float()
+    n0, n1, n2 = (w.norm(dim=2, keepdim=True) for w in (w0, w1, w2))
+    w0m, w1m, w2m = w0, w1, w2
+    wdt = torch.float32 if cfg.fp32_mode else BF16
+    ms = None
+    if momentum is not None:
+        ms = [torch.zeros_like(w0), torch.zeros_like(w1), torch.zeros_like(w2)] if m_init is None else [t.float() for t in m_init]
+    out_len = q.shape[1] if out_len is None else out_len
+    out = torch.zeros(q.shape[0], out_len, w1.shape[1], dtype=act)
+    l0, l1, l2 = lr0[..., 0], lr1[..., 0], lr2[..., 0]
+
+    def norm_w(w, n):
+        if cfg.renorm == "none":
+            return w
+        if cfg.renorm == "inner":
+            return w * (1 / torch.sqrt(torch.sum(w * w, dim=2, keepdim=True) + 1e-5)) * n
+        return w / (w.norm(dim=2, keepdim=True) + 1e-5) * n
+
+    for kind, s, e, o in steps:
+        w02b = torch.cat([w0, w2], dim=1).to(wdt)
+        w1b = w1.to(wdt)
+        if kind == "apply":
+            out[:, o:o + (e - s)] = apply_fused(w02b, w1b, q[:, s:e].to(act))
+            continue
+        dw02, dw1 = grads_fused(w02b, w1b, k[:, s:e].to(act), v[:, s:e].to(act), l0[:, s:e], l1[:, s:e], l2[:, s:e],
+                                cfg.w_scale)
+        dw0, dw2 = dw02[:, :H], dw02[:, H:]
+        if ms is not None:
+            beta = momentum[:, s:e].float().mean(dim=1, keepdim=True)
+            dw0, dw1, dw2 = dw0.float() + ms[0] * beta, dw1.float() + ms[1] * beta, dw2.float() + ms[2] * beta
+            ms = [dw0, dw1, dw2]
+        g0, g1, g2 = dw0, dw1, dw2
+        if cfg.use_muon:
+            g1 = _ns_model(dw1, cfg)
+            if cfg.ns_concat:
+                g02 = _ns_model(torch.cat([dw0, dw2], dim=1), cfg)
+                g0, g2 = g02[:, :H], g02[:, H:]
+            else:
+                g0, g2 = _ns_model(dw0, cfg), _ns_model(dw2, cfg)
+        if cfg.overwrite_quirk and cfg.use_muon:
+            w0m, w1m, w2m = g0.float() + dw0.float(), g1.float() + dw1.float(), g2.float() + dw2.float()
+        else:
+            w0m, w1m, w2m = w0m + g0.float(), w1m + g1.float(), w2m + g2.float()
+        w0, w1, w2 = norm_w(w0m, n0), norm_w(w1m, n1), norm_w(w2m, n2)
+        if cfg.prenorm:
+            if cfg.prenorm_bf16:
+                w0, w1, w2 = w0.to(BF16).float(), w1.to(BF16).float(), w2.to(BF16).float()
+        else:
+            w0m, w1m, w2m = w0, w1, w2
+    return out, w0, w1, w2, ms
+
+
+# ----------------------------------------------------------------------------------------------
+# metrics (fp64)
+# ----------------------------------------------------------------------------------------------
+def rel_max(a: torch.Tensor, ref: torch.Tensor) -> float:
+    """max|a - ref| / max|ref| in float64."""
+    a, ref = a.double(), ref.double()
+    return float((a - ref).abs().max() / ref.abs().max().clamp_min(1e-30))
+
+
+def rel_fro(a: torch.Tensor, ref: torch.Tensor) -> float:
+    """||a - ref||_F / ||ref||_F in float64."""
+    a, ref = a.double(), ref.double()
+    return float((a - ref).norm() / ref.norm().clamp_min(1e-30))
+
+
+def cosine(a: torch.Tensor, ref: torch.Tensor) -> float:
+    a, ref = a.double().flatten(), ref.double().flatten()
+    return float(torch.dot(a, ref) / (a.norm() * ref.norm()).clamp_min(1e-30))
+
+
+# ----------------------------------------------------------------------------------------------
+# seeded synthetic inputs
+# ----------------------------------------------------------------------------------------------
+def make_inputs(B: int, L: int, D: int, H: int, seed: int = 0, act_dtype=torch.float32, lr_dtype=torch.float32):
+    """q,k,v ~ N(0,1), q and k L2-normalised per token; W0,W2 = randn/sqrt(D), W1 = randn/sqrt(H);
+    lr = softplus(N(-2,1)) x3; beta = sigmoid(N(0,1)).  Initialisation follows
+    minimal_implementations/bidirectional_lact_layer.py:206-210 and
+    lact_llm/lact_model/layer_lact_swiglu.py:214-222.
+    """
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(B, L, D, generator=g)
+    k = torch.randn(B, L, D, generator=g)
+    v = torch.randn(B, L, D, generator=g)
+    q = q / q.norm(dim=-1, keepdim=True)
+    k = k / k.norm(dim=-1, keepdim=True)
+    w0 = torch.randn(B, H, D, generator=g) / D ** 0.5
+    w1 = torch.randn(B, D, H, generator=g) / H ** 0.5
+    w2 = torch.randn(B, H, D, generator=g) / D ** 0.5
+    lr = F.softplus(torch.randn(B, L, 3, generator=g) - 2.0)
+    lr0, lr1, lr2 = (t.contiguous().to(lr_dtype) for t in lr.chunk(3, dim=-1))
+    beta = torch.sigmoid(torch.randn(B, L, 1, generator=g))
+    return dict(w0=w0, w1=w1, w2=w2, q=q.to(act_dtype), k=k.to(act_dtype), v=v.to(act_dtype),
+                lr0=lr0, lr1=lr1, lr2=lr2, momentum=beta)

@@ -1,0 +1,171 @@
+"""Generates tests/golden/ref_outputs.pt by RUNNING THE REFERENCE's own functions on CPU.
+
+Run in a container that holds the reference tree (default /root/reference, or
+LACT_REFERENCE_ROOT):
+
+    python tests/golden/make_golden.py
+
+The reference ships no golden vectors for this path, so these fixtures are outputs of the
+reference itself (eager mode, CPU) on seeded inputs produced by `oracle.lact_oracle.make_inputs`.
+Inputs are not stored; their float64 checksums are, so generator drift is detected.
+"""
+from __future__ import annotations
+
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+
+from oracle import ref_loader  # noqa: E402  (sets TORCHDYNAMO_DISABLE before torch is used)
+import torch  # noqa: E402
+from oracle import lact_oracle as orc  # noqa: E402
+
+OUT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "ref_outputs.pt")
+BF16 = torch.bfloat16
+
+
+def checksum(inp: dict) -> float:
+    return float(sum(t.double().sum() for t in inp.values()))
+
+
+def cases():
+    """(name, kind, input spec, kwargs).  Shapes are small; D and H are multiples of 64."""
+    out = []
+    for muon in (False, True):
+        for mom in (False, True):
+            out.append((f"llm_post_fp32_muon{int(muon)}_mom{int(mom)}", "llm_post",
+                        dict(B=1, L=209, D=64, H=64, seed=1), dict(chunk_size=64, use_muon=muon, mom=mom)))
+    out.append(("llm_pre_fp32_muon0_mom1", "llm_pre", dict(B=1, L=209, D=64, H=64, seed=2),
+                dict(chunk_size=64, use_muon=False, mom=True)))
+    out.append(("llm_pre_fp32_muon1_mom1", "llm_pre", dict(B=1, L=192, D=64, H=128, seed=3),
+                dict(chunk_size=64, use_muon=True, mom=True)))
+    out.append(("llm_post_fp32_short", "llm_post", dict(B=2, L=50, D=64, H=64, seed=4),
+                dict(chunk_size=64, use_muon=True, mom=True)))
+    out.append(("llm_post_fp32_rect", "llm_post", dict(B=1, L=150, D=128, H=64, seed=5),
+                dict(chunk_size=50, use_muon=True, mom=False)))
+    for muon in (False, True):
+        out.append((f"llm_post_bf16_muon{int(muon)}_mom1", "llm_post_autocast",
+                    dict(B=2, L=320, D=64, H=64, seed=6), dict(chunk_size=64, use_muon=muon, mom=True)))
+        out.append((f"bidi_fp32_muon{int(muon)}", "bidi", dict(B=2, L=128, D=64, H=64, seed=7),
+                    dict(use_muon=muon)))
+    for steps in (0, 5):
+        out.append((f"nvs_fp32_steps{steps}", "nvs", dict(B=1, L=320, D=64, H=128, seed=8),
+                    dict(order=[(0, 192, True, False), (0, 320, False, True)], steps=steps)))
+    out.append(("nvs_fp32_multi", "nvs", dict(B=1, L=320, D=64, H=64, seed=9),
+                dict(order=[(0, 128, True, True), (128, 256, True, False), (200, 320, False, True)], steps=3)))
+    out.append(("ar_train_plain", "ar", dict(B=1, L=448, D=64, H=128, seed=10),
+                dict(w_scale=1.0, mini_batch_size=64, update_every=128, use_moun=False)))
+    out.append(("ar_train_muon5", "ar", dict(B=1, L=448, D=64, H=128, seed=10),
+                dict(w_scale=0.5, mini_batch_size=64, update_every=128, use_moun=True, num_moun_iters=5)))
+    out.append(("ar_train_repeat2", "ar", dict(B=1, L=320, D=64, H=64, seed=11),
+                dict(w_scale=1.0, num_repeat=2, mini_batch_size=80, update_every=80, use_moun=True,
+                     num_moun_iters=3, weight_norm=True)))
+    out.append(("ar_train_nonorm", "ar", dict(B=1, L=256, D=64, H=64, seed=12),
+                dict(w_scale=1.0, mini_batch_size=64, update_every=64, use_moun=False, weight_norm=False)))
+    out.append(("ar_train_momentum", "ar_mom", dict(B=1, L=390, D=64, H=128, seed=13),
+                dict(w_scale=1.0, mini_batch_size=78, update_every=78, use_moun=True, num_moun_iters=5,
+                     use_momentum=True)))
+    out.append(("ar_infer_update", "ar_inf", dict(B=1, L=200, D=64, H=128, seed=14),
+                dict(w_scale=1.0, mini_batch_size=120, do_update=True, use_moun=True, num_moun_iters=5)))
+    out.append(("ar_infer_noupdate", "ar_inf", dict(B=1, L=200, D=64, H=128, seed=14),
+                dict(w_scale=1.0, do_update=False)))
+    out.append(("ar_infer_momentum", "ar_inf_mom", dict(B=1, L=200, D=64, H=128, seed=15),
+                dict(w_scale=1.0, mini_batch_size=120, do_update=True, use_moun=True, num_moun_iters=5,
+                     use_momentum=True)))
+    return out
+
+
+def run_reference(kind: str, inp: dict, kw: dict):
+    w0, w1, w2, q, k, v = (inp[n] for n in ("w0", "w1", "w2", "q", "k", "v"))
+    lr0, lr1, lr2, beta = inp["lr0"], inp["lr1"], inp["lr2"], inp["momentum"]
+    if kind in ("llm_post", "llm_pre", "llm_post_autocast"):
+        mod = ref_loader.llm_unfused()
+        fn = mod.prenorm_block_causal_lact_swiglu if kind == "llm_pre" else mod.block_causal_lact_swiglu
+        mom = beta if kw["mom"] else None
+        if kind == "llm_post_autocast":
+            with torch.autocast("cpu", dtype=BF16):
+                o = fn(w0, w1, w2, q.to(BF16), k.to(BF16), v.to(BF16), lr0, lr1, lr2,
+                       chunk_size=kw["chunk_size"], use_muon=kw["use_muon"], momentum=mom)
+        else:
+            o = fn(w0, w1, w2, q, k, v, lr0, lr1, lr2, chunk_size=kw["chunk_size"], use_muon=kw["use_muon"],
+                   momentum=mom)
+        return dict(o=o)
+    if kind == "bidi":
+        return dict(o=ref_loader.bidirectional().bidirectional_lact_swiglu(
+            w0, w1, w2, q, k, v, lr0, lr1, lr2, use_muon=kw["use_muon"]))
+    if kind == "nvs":
+        mod = ref_loader.nvs()
+        order = [mod.TTTOperator(*t) for t in kw["order"]]
+        t = lambda w: w.transpose(1, 2).contiguous()
+        o, a, b, c = mod.fast_weight_swish_glu_weight_norm_mini_batch_apply(
+            t(w0), t(w1), t(w2), q, k, v, lr0, lr1, lr2, order, muon_update_steps=kw["steps"])
+        return dict(o=o, w0=a, w1=b, w2=c)
+    ar = ref_loader.ar_ops()
+    if kind == "ar":
+        o, a, b, c = ar["ar_fast_weight_swish_glu_weight_norm_mini_batch"](w0, w1, w2, q, k, v, lr0, lr1, lr2, **kw)
+        return dict(o=o, w0=a, w1=b, w2=c)
+    if kind == "ar_mom":
+        o, a, b, c = ar["ar_fast_weight_swish_glu_weight_norm_mini_batch_with_momentum"](
+            w0, w1, w2, q, k, v, lr0, lr1, lr2, fw_momentum=beta, **kw)
+        return dict(o=o, w0=a, w1=b, w2=c)
+    if kind == "ar_inf":
+        o, a, b, c = ar["ar_fast_weight_swish_glu_weight_norm_mini_batch_inference"](
+            w0, w1, w2, q, k, v, lr0, lr1, lr2, **kw)
+        return dict(o=o, w0=a, w1=b, w2=c)
+    if kind == "ar_inf_mom":
+        r = ar["ar_fast_weight_swish_glu_weight_norm_mini_batch_inference_with_momentum"](
+            w0, w1, w2, q, k, v, lr0, lr1, lr2, fw_momentum=beta, **kw)
+        return dict(zip(("o", "w0", "w1", "w2", "m0", "m1", "m2"), r))
+    raise KeyError(kind)
+
+
+def subop_cases():
+    """Outputs of the reference's in-file PyTorch reference functions for the fused sub-ops."""
+    fh = ref_loader.fused_helpers()
+    g = torch.Generator().manual_seed(100)
+    B, H, D, L = 2, 128, 64, 200
+    W02 = torch.randn(B, 2 * H, D, generator=g) / D ** 0.5
+    W1 = torch.randn(B, D, H, generator=g) / H ** 0.5
+    X = torch.randn(B, L, D, generator=g)
+    V = torch.randn(B, L, D, generator=g)
+    l0, l1, l2 = torch.rand(3, B, L, generator=g).unbind(0)
+    res = {}
+    res["swiglu_ffn_fwd"] = dict(o=fh["reference_swiglu_ffn_fwd"](W02, W1, X))
+    a, b = fh["reference_lact_swiglu_ffn_fast_weight_grads"](W02, W1, X, V, l0, l1, l2)
+    res["fw_grads"] = dict(dw0w2=a, dw1=b)
+    xa = torch.randn(B, 2 * H, D, generator=g) * 0.1
+    sc = torch.rand(B, 2 * H, generator=g) + 0.5
+    res["l2_norm_add"] = dict(y=fh["reference_l2_norm_add_fused"](W02, xa, sc))
+    m = torch.randn(B, 2 * H, D, generator=g) * 0.1
+    mu = torch.rand(B, generator=g)
+    x_new, m_new, y = fh["reference_l2_norm_add_fused_with_momentum"](W02, xa, m, mu, sc)
+    res["prenorm_momentum"] = dict(x=x_new, m=m_new, y=y)
+    # Newton-Schulz, both coefficient schedules, square / wide / tall
+    llm = ref_loader.llm_unfused()
+    nvs = ref_loader.nvs()
+    for name, shape in (("sq", (2, 64, 64)), ("wide", (2, 64, 128)), ("tall", (2, 128, 64))):
+        G = torch.randn(*shape, generator=g)
+        res[f"ns_tuned_{name}"] = dict(x=llm.zeropower_via_newtonschulz5(G))
+        for steps in (0, 3, 5):
+            res[f"ns_const{steps}_{name}"] = dict(x=nvs.zeropower_via_newtonschulz5(G, steps))
+    res["_subop_seed"] = 100
+    return res
+
+
+def main():
+    assert ref_loader.available(), "reference tree not found"
+    torch.set_num_threads(1)  # fixtures must not depend on the thread count
+    blob = {"cases": {}, "subops": subop_cases(), "torch": torch.__version__}
+    for name, kind, spec, kw in cases():
+        inp = orc.make_inputs(**spec)
+        res = run_reference(kind, inp, kw)
+        blob["cases"][name] = dict(kind=kind, spec=spec, kw=kw, checksum=checksum(inp),
+                                   out={k: v.detach().clone() for k, v in res.items() if v is not None})
+        print(f"{name:32s} " + " ".join(f"{k}:{tuple(v.shape)}:{str(v.dtype)[6:]}" for k, v in res.items() if v is not None))
+    torch.save(blob, OUT)
+    print("wrote", OUT, os.path.getsize(OUT) // 1024, "KiB")
+
+
+if __name__ == "__main__":
+    main()
