@@ -1,0 +1,160 @@
+/* C ABI of liblact_b200: B200 (sm_100a) kernels for the LaCT large-chunk fast-weight TTT step.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (passed as void*),
+ * enqueues its kernels on that stream without synchronising, and returns an int:
+ *     0   success (work enqueued)
+ *   < 0   argument / configuration error detected on the host (nothing was enqueued)
+ * Device-side status (a bounded wait that ran out) is recorded in the first word of the
+ * caller-provided workspace and read with lact_read_status().
+ * The library never allocates or frees device memory: all scratch comes from `workspace`,
+ * sized by the matching *_workspace_bytes call.
+ *
+ * The reference (a1600012888/LaCT) has no FFI: its interface for this path is a set of Python
+ * functions on tensors.  Each declaration cites the reference function whose arithmetic the
+ * entry point replaces; the Python package `lact_b200` re-exports those functions under the
+ * reference's names and signatures and binds to this ABI with ctypes.
+ *
+ * Layouts ("LLM layout"): w0, w2: [B, H, D]; w1: [B, D, H]; q, k, v, o: [B, L, D];
+ * lr0/1/2, momentum: [B, L]; B = batch * heads (merged), D = head dim, H = fast-weight hidden dim.
+ */
+#ifndef LACT_B200_H_
+#define LACT_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* dtype codes */
+#define LACT_F32 0
+#define LACT_BF16 1
+
+/* error codes (negative: host-side argument errors) */
+#define LACT_OK 0
+#define LACT_ERR_NULL -1        /* a required pointer is NULL */
+#define LACT_ERR_SHAPE -2       /* unsupported or inconsistent sizes / strides / alignment */
+#define LACT_ERR_DTYPE -3       /* unsupported dtype combination */
+#define LACT_ERR_WORKSPACE -4   /* workspace missing or too small */
+#define LACT_ERR_CONFIG -5      /* inconsistent configuration flags */
+#define LACT_ERR_STEPS -6       /* malformed step list (empty update range, range outside [0, L]) */
+#define LACT_ERR_CUDA -7        /* a CUDA runtime / driver call failed */
+#define LACT_ERR_DEVICE -8      /* device is not sm_100 */
+
+/* step kinds of the scan program */
+#define LACT_STEP_APPLY 0
+#define LACT_STEP_UPDATE 1
+
+/* renormalisation modes */
+#define LACT_RENORM_NONE 0
+#define LACT_RENORM_EPS_OUTSIDE 1 /* w / (||w|| + 1e-5) * n0   : ttt_operation.py:198-200 */
+#define LACT_RENORM_EPS_INSIDE 2  /* w * rsqrt(sum w^2 + 1e-5) * n0 : l2norm_triton_kernels.py:80 */
+
+typedef struct lact_scan_config {
+  int64_t B, L, D, H; /* merged batch*heads, tokens, head dim, fast-weight hidden dim */
+  int64_t out_len;    /* tokens in o (== L except for operator lists that concatenate applies) */
+  int32_t act_dtype;  /* dtype of q, k, v, o (LACT_BF16; LACT_F32 = split-precision fp32 mode) */
+  int32_t lr_dtype;   /* dtype of lr0, lr1, lr2 */
+  int32_t mom_dtype;  /* dtype of momentum */
+  int32_t w_dtype;    /* dtype of w0, w1, w2 (inputs); outputs and state are always fp32 */
+  int32_t use_momentum;
+  int32_t use_muon;
+  int32_t ns_steps;        /* Newton-Schulz iterations */
+  int32_t ns_const_coeffs; /* 0: tuned 5-step table (ns_steps must be 5); 1: constant triple */
+  int32_t ns_concat;       /* 1: orthogonalise cat([dw0, dw2], dim=1) as one [2H, D] matrix */
+  int32_t ns_gram_right;   /* 1: square matrices iterate on the transpose (NVS weight layout) */
+  int32_t renorm;          /* LACT_RENORM_* */
+  int32_t prenorm;         /* 1: keep an un-normalised master, compute with the normalised copy */
+  int32_t prenorm_bf16;    /* 1: the normalised copy is rounded to bf16 (fused pre-norm path) */
+  int32_t overwrite_quirk; /* 1: w <- renorm(NS(dw) + dw) (bidirectional_lact_layer.py:139-146) */
+  float w_scale;           /* scalar multiplied into the three learning rates */
+  /* strides in elements; innermost (feature) stride is 1 */
+  int64_t q_bs, q_ts, k_bs, k_ts, v_bs, v_ts, o_bs, o_ts;
+} lact_scan_config;
+
+typedef struct lact_scan_io {
+  const void *w0, *w1, *w2;          /* initial fast weights */
+  const void *q, *k, *v;             /* activations */
+  const void *lr0, *lr1, *lr2;       /* per-token learning rates, [B, L] contiguous */
+  const void *momentum;              /* per-token momentum, [B, L] contiguous, or NULL */
+  const void *m0_in, *m1_in, *m2_in; /* initial momentum state (fp32, weight shapes) or NULL = zeros */
+  void *o;                           /* [B, out_len, D], act_dtype */
+  void *w0_out, *w1_out, *w2_out;    /* final fast weights, fp32, or NULL */
+  void *m0_out, *m1_out, *m2_out;    /* final momentum state, fp32, or NULL */
+} lact_scan_io;
+
+/* Library version (major * 1000 + minor).  No counterpart in the reference. */
+int lact_version(void);
+
+/* Human-readable text for a return code.  No counterpart in the reference. */
+const char *lact_error_string(int code);
+
+/* Reads the device status word of a workspace after synchronising `stream`.
+ * Returns 0 (ok), a positive device status (101 = a bounded wait timed out) or LACT_ERR_CUDA. */
+int lact_read_status(const void *workspace, void *stream);
+
+/* Scratch bytes needed by lact_scan_fwd for this configuration and step list. */
+int lact_scan_workspace_bytes(const lact_scan_config *cfg, int32_t n_steps, const int32_t *kind,
+                              const int64_t *start, const int64_t *end, size_t *bytes_out);
+
+/* The chunk recurrence: executes `n_steps` steps in order; APPLY writes
+ * o[:, out_start : out_start + (end - start)] = f_W(q[:, start:end]); UPDATE updates the fast
+ * weights from k, v, lr on [start, end) (gradient, momentum, Newton-Schulz, add, renorm).
+ * Replaces the loops of: block_causal_lact_swiglu / prenorm_block_causal_lact_swiglu
+ * (lact_llm/lact_model/ttt_operation.py:69-214, :217-364), the fused pair
+ * (lact_llm/lact_model/ttt_operation_fused_kernel.py:66-186, :189-316),
+ * bidirectional_lact_swiglu (minimal_implementations/bidirectional_lact_layer.py:73-160),
+ * fast_weight_swish_glu_weight_norm_mini_batch_apply (lact_nvs/lact_ttt.py:70-147) and the four
+ * autoregressive-video functions (lact_ar_video/minVid/models/blocks/ar_lact_swa_repeat.py:22-296,
+ * ar_lact_swa_repeat_sp.py:27-339). */
+int lact_scan_fwd(const lact_scan_config *cfg, const lact_scan_io *io, int32_t n_steps, const int32_t *kind,
+                  const int64_t *start, const int64_t *end, const int64_t *out_start, void *workspace,
+                  size_t workspace_bytes, void *stream);
+
+/* out[B, N, D] = (silu(x w0^T) * (x w2^T)) w1^T with w0w2 = [B, 2H, D] (w0 rows first), all bf16.
+ * Replaces fused_swiglu_ffn_fwd (lact_llm/lact_model/lact_triton_kernels/lact_swiglu_ffn.py:79-96).
+ * Workspace: lact_swiglu_ffn_workspace_bytes. */
+int lact_swiglu_ffn_workspace_bytes(int64_t B, int64_t N, int64_t D, int64_t H, size_t *bytes_out);
+int lact_swiglu_ffn_fwd(const void *w0w2, const void *w1, const void *x, void *out, int64_t B, int64_t N,
+                        int64_t D, int64_t H, void *workspace, size_t workspace_bytes, void *stream);
+
+/* dw0w2[B, 2H, D], dw1[B, D, H] (bf16) = per-token-lr weighted fast-weight gradient.
+ * Replaces fused_lact_swiglu_ffn_fast_weight_grads
+ * (lact_llm/lact_model/lact_triton_kernels/lact_fw_grad.py:159-175).  lr: [B, N], lr_dtype. */
+int lact_fw_grad_workspace_bytes(int64_t B, int64_t N, int64_t D, int64_t H, size_t *bytes_out);
+int lact_fw_grad(const void *w0w2, const void *w1, const void *k, const void *v, const void *lr0, const void *lr1,
+                 const void *lr2, int32_t lr_dtype, void *dw0w2, void *dw1, int64_t B, int64_t N, int64_t D,
+                 int64_t H, void *workspace, size_t workspace_bytes, void *stream);
+
+/* x[B, R, C] (bf16) = Newton-Schulz orthogonalisation of g[B, R, C] (g_dtype), bf16 arithmetic.
+ * const_coeffs = 0: zeropower_via_newtonschulz5(G) (lact_llm/lact_model/ttt_operation.py:30-66),
+ * steps must be 5; const_coeffs = 1: zeropower_via_newtonschulz5(G, steps)
+ * (lact_nvs/lact_ttt.py:32-67). */
+int lact_newton_schulz_workspace_bytes(int64_t B, int64_t R, int64_t C, size_t *bytes_out);
+int lact_newton_schulz(const void *g, int32_t g_dtype, void *x, int64_t B, int64_t R, int64_t C, int32_t steps,
+                       int32_t const_coeffs, void *workspace, size_t workspace_bytes, void *stream);
+
+/* y = (x + x_add) * rsqrt(sum_row (x + x_add)^2 + eps) * scale[row]; x: [B, T, D].
+ * Replaces l2_norm_add_fused (lact_llm/lact_model/lact_triton_kernels/l2norm_triton_kernels.py:419-427). */
+int lact_l2_norm_add(const void *x, int32_t x_dtype, const void *x_add, int32_t add_dtype, const void *scale,
+                     void *y, int32_t y_dtype, int64_t B, int64_t T, int64_t D, float eps, void *stream);
+
+/* m' = dx + mu[b] * m; x' = x + m'; y = bf16(x' / sqrt(sum_row x'^2 + eps) * scale[row]).
+ * Replaces fused_prenorm_update_with_momentum_and_l2_norm
+ * (lact_llm/lact_model/lact_triton_kernels/triton_prenorm_update_with_momentum.py:379-401).
+ * x, m: fp32 [B, T, D]; dx: bf16; mu: fp32 [B]; scale: fp32 [B, T]. */
+int lact_prenorm_momentum_l2norm(const void *x, const void *dx, const void *m, const void *mu, const void *scale,
+                                 void *x_out, void *m_out, void *y_out, int64_t B, int64_t T, int64_t D, float eps,
+                                 void *stream);
+
+/* c[batch, M, N] = a * b^T with bf16 operands and fp32 accumulation (c_dtype output).
+ * a is [batch, M, K] (a_mn_major = 0) or [batch, K, M] (a_mn_major = 1); b likewise with N.
+ * Test hook for the tcgen05 GEMM engine; no counterpart in the reference (it calls torch.bmm). */
+int lact_bmm_bf16(const void *a, int32_t a_mn_major, const void *b, int32_t b_mn_major, void *c, int32_t c_dtype,
+                  int64_t batch, int64_t M, int64_t N, int64_t K, int32_t *status_word, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LACT_B200_H_ */

@@ -1,0 +1,143 @@
+"""ctypes binding of liblact_b200.so (the C ABI in include/lact_b200.h).
+
+There is no fallback: if the shared library is missing, loading raises and every op fails.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Dict, Optional
+
+import torch
+
+PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG_DIR, "liblact_b200.so")
+
+LACT_F32, LACT_BF16 = 0, 1
+RENORM_NONE, RENORM_EPS_OUTSIDE, RENORM_EPS_INSIDE = 0, 1, 2
+
+
+class ScanConfig(C.Structure):
+    _fields_ = [(n, C.c_int64) for n in ("B", "L", "D", "H", "out_len")] + [
+        (n, C.c_int32) for n in ("act_dtype", "lr_dtype", "mom_dtype", "w_dtype", "use_momentum", "use_muon",
+                                 "ns_steps", "ns_const_coeffs", "ns_concat", "ns_gram_right", "renorm", "prenorm",
+                                 "prenorm_bf16", "overwrite_quirk")] + [("w_scale", C.c_float)] + [
+        (n, C.c_int64) for n in ("q_bs", "q_ts", "k_bs", "k_ts", "v_bs", "v_ts", "o_bs", "o_ts")]
+
+
+class ScanIO(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("w0", "w1", "w2", "q", "k", "v", "lr0", "lr1", "lr2", "momentum", "m0_in",
+                                          "m1_in", "m2_in", "o", "w0_out", "w1_out", "w2_out", "m0_out", "m1_out",
+                                          "m2_out")]
+
+
+_lib: Optional[C.CDLL] = None
+
+
+def _declare(lib: C.CDLL) -> None:
+    vp, i32, i64, f32 = C.c_void_p, C.c_int32, C.c_int64, C.c_float
+    szp = C.POINTER(C.c_size_t)
+    lib.lact_version.restype = C.c_int
+    lib.lact_error_string.restype = C.c_char_p
+    lib.lact_error_string.argtypes = [C.c_int]
+    lib.lact_read_status.argtypes = [vp, vp]
+    lib.lact_scan_workspace_bytes.argtypes = [C.POINTER(ScanConfig), i32, C.POINTER(i32), C.POINTER(i64),
+                                              C.POINTER(i64), szp]
+    lib.lact_scan_fwd.argtypes = [C.POINTER(ScanConfig), C.POINTER(ScanIO), i32, C.POINTER(i32), C.POINTER(i64),
+                                  C.POINTER(i64), C.POINTER(i64), vp, C.c_size_t, vp]
+    lib.lact_swiglu_ffn_workspace_bytes.argtypes = [i64, i64, i64, i64, szp]
+    lib.lact_swiglu_ffn_fwd.argtypes = [vp, vp, vp, vp, i64, i64, i64, i64, vp, C.c_size_t, vp]
+    lib.lact_fw_grad_workspace_bytes.argtypes = [i64, i64, i64, i64, szp]
+    lib.lact_fw_grad.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, vp, vp, i64, i64, i64, i64, vp, C.c_size_t, vp]
+    lib.lact_newton_schulz_workspace_bytes.argtypes = [i64, i64, i64, szp]
+    lib.lact_newton_schulz.argtypes = [vp, i32, vp, i64, i64, i64, i32, i32, vp, C.c_size_t, vp]
+    lib.lact_l2_norm_add.argtypes = [vp, i32, vp, i32, vp, vp, i32, i64, i64, i64, f32, vp]
+    lib.lact_prenorm_momentum_l2norm.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, f32, vp]
+    lib.lact_bmm_bf16.argtypes = [vp, i32, vp, i32, vp, i32, i64, i64, i64, i64, vp, vp]
+    for name in ("lact_read_status", "lact_scan_workspace_bytes", "lact_scan_fwd", "lact_swiglu_ffn_workspace_bytes",
+                 "lact_swiglu_ffn_fwd", "lact_fw_grad_workspace_bytes", "lact_fw_grad",
+                 "lact_newton_schulz_workspace_bytes", "lact_newton_schulz", "lact_l2_norm_add",
+                 "lact_prenorm_momentum_l2norm", "lact_bmm_bf16"):
+        getattr(lib, name).restype = C.c_int
+
+
+def lib() -> C.CDLL:
+    """Loads the shared library (once).  Raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(f"{LIB_PATH} is missing: build it with `python -m lact_b200.build` "
+                              "(there is no fallback implementation)")
+        handle = C.CDLL(LIB_PATH)
+        _declare(handle)
+        _lib = handle
+    return _lib
+
+
+class LactError(RuntimeError):
+    pass
+
+
+def check(rc: int, what: str) -> None:
+    if rc == 0:
+        return
+    msg = lib().lact_error_string(rc).decode()
+    if rc in (-1, -2, -3, -5, -6):
+        raise ValueError(f"{what}: {msg} (code {rc})")
+    raise LactError(f"{what}: {msg} (code {rc})")
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return LACT_F32
+    if t.dtype == torch.bfloat16:
+        return LACT_BF16
+    raise TypeError(f"unsupported dtype {t.dtype}: expected float32 or bfloat16")
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+# One growing scratch buffer per (device, stream), taken from PyTorch's caching allocator.  Kernels
+# of consecutive calls on one stream are ordered, so reuse is safe.
+_workspaces: Dict[tuple, torch.Tensor] = {}
+_pending: Dict[tuple, bool] = {}
+SYNC_CHECK = os.environ.get("LACT_B200_SYNC_CHECK", "0") == "1"
+
+
+def workspace(nbytes: int, device: torch.device) -> torch.Tensor:
+    key = (device.index if device.index is not None else torch.cuda.current_device(), stream_ptr())
+    if _pending.get(key):
+        # the previous call on this stream left a status word behind: read it before reuse
+        read_status(_workspaces[key])
+        _pending[key] = False
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+def mark_pending(ws: torch.Tensor) -> None:
+    """Remembers that `ws` holds a device status word to be examined (lazily, or now if
+    LACT_B200_SYNC_CHECK=1)."""
+    if SYNC_CHECK:
+        read_status(ws)
+        return
+    key = (ws.device.index, stream_ptr())
+    _pending[key] = True
+
+
+def read_status(ws: torch.Tensor) -> None:
+    rc = lib().lact_read_status(ws.data_ptr(), stream_ptr())
+    if rc != 0:
+        raise LactError("device status: " + lib().lact_error_string(rc).decode() + f" (code {rc})")
+
+
+def synchronize_and_check() -> None:
+    """Synchronises and raises if any earlier call recorded a device-side error."""
+    for key, buf in list(_workspaces.items()):
+        if _pending.get(key):
+            read_status(buf)
+            _pending[key] = False

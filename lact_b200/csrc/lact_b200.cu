@@ -1,0 +1,750 @@
+// Host side of liblact_b200: argument validation, TMA tensor-map construction, workspace
+// planning, the chunk-recurrence driver and the extern "C" entry points declared in
+// include/lact_b200.h.  No device memory is allocated here: all scratch is carved out of the
+// caller's workspace.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+#include "../../include/lact_b200.h"
+#include "ops.cuh"
+
+namespace lact {
+namespace {
+
+// ------------------------------------------------------------------------------------------
+// tensor maps
+// ------------------------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn get_encode_fn() {
+  static EncodeFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) p = nullptr;
+    return reinterpret_cast<EncodeFn>(p);
+  }();
+  return fn;
+}
+
+// A batched row-major bf16 matrix in global memory: [batch][rows][cols], cols contiguous.
+struct Mat {
+  const void* ptr;
+  int64_t rows, cols, ld, batch, bs;  // ld / bs: row / batch stride in elements
+};
+
+// Encodes a 3-D map (cols, rows, batch) with a {64, box_rows, 1} box and 128-byte swizzle.
+int encode_map(CUtensorMap* map, const Mat& m, uint32_t box_rows) {
+  EncodeFn fn = get_encode_fn();
+  if (fn == nullptr) return LACT_ERR_CUDA;
+  if ((reinterpret_cast<uintptr_t>(m.ptr) & 15) != 0 || (m.ld % 8) != 0 || (m.batch > 1 && (m.bs % 8) != 0))
+    return LACT_ERR_SHAPE;
+  if (m.rows < 1 || m.cols < 1 || m.batch < 1 || box_rows > 256) return LACT_ERR_SHAPE;
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(m.cols), static_cast<cuuint64_t>(m.rows),
+                        static_cast<cuuint64_t>(m.batch)};
+  const int64_t bs = m.batch > 1 ? m.bs : m.ld * m.rows;
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(m.ld) * 2, static_cast<cuuint64_t>(bs) * 2};
+  cuuint32_t box[3] = {64, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(m.ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? LACT_OK : LACT_ERR_CUDA;
+}
+
+// Operand of a GEMM: `m` used K-major (mn = rows, k = cols) or MN-major (k = rows, mn = cols).
+int make_operand(CUtensorMap* map, OperandInfo* info, const Mat& m, int mn_major, int tile_rows, int mn_off, int k_off,
+                 int batch_off = 0) {
+  info->mn_major = mn_major;
+  info->mn_off = mn_off;
+  info->k_off = k_off;
+  info->batch_off = batch_off;
+  if (((mn_major ? mn_off : k_off) % 8) != 0) return LACT_ERR_SHAPE;  // innermost TMA coordinate: 16-byte rule
+  return encode_map(map, m, mn_major ? 64 : static_cast<uint32_t>(tile_rows));
+}
+
+// ------------------------------------------------------------------------------------------
+// launch helpers
+// ------------------------------------------------------------------------------------------
+#define LACT_TRY(expr)                   \
+  do {                                   \
+    int _rc = (expr);                    \
+    if (_rc != LACT_OK) return _rc;      \
+  } while (0)
+
+#define LACT_CUDA(expr)                               \
+  do {                                                \
+    if ((expr) != cudaSuccess) return LACT_ERR_CUDA;  \
+  } while (0)
+
+int check_device() {
+  static std::mutex mu;
+  static int ok_dev[64] = {0};
+  int dev = 0;
+  LACT_CUDA(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(mu);
+  if (dev < 64 && ok_dev[dev] == 1) return LACT_OK;
+  int major = 0;
+  LACT_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+  if (major != 10) return LACT_ERR_DEVICE;
+  if (dev < 64) ok_dev[dev] = 1;
+  return LACT_OK;
+}
+
+// Launches the first `nprob` problems of `args` (grid.z = nprob).
+template <class Op, int NPROB>
+int launch_gemm(const GemmArgs<Op, NPROB>& args, cudaStream_t stream, int nprob = NPROB) {
+  auto kernel = umma_gemm_kernel<Op, NPROB>;
+  constexpr uint32_t smem = gemm_smem_bytes<Op>();
+  static std::mutex mu;
+  static bool configured[64] = {false};
+  int dev = 0;
+  LACT_CUDA(cudaGetDevice(&dev));
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev >= 64 || !configured[dev]) {
+      LACT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      if (dev < 64) configured[dev] = true;
+    }
+  }
+  int tiles = 0, batch = 0;
+  for (int p = 0; p < nprob; ++p) {
+    const auto& P = args.prob[p];
+    if (P.M < 1 || P.N < 1 || P.batch < 1 || P.K < 0) return LACT_ERR_SHAPE;
+    tiles = std::max(tiles, ((P.M + kBM - 1) / kBM) * ((P.N + Op::BN - 1) / Op::BN));
+    batch = std::max(batch, P.batch);
+  }
+  if (batch > 65535) return LACT_ERR_SHAPE;
+  dim3 grid(tiles, batch, nprob);
+  kernel<<<grid, kGemmThreads, smem, stream>>>(args);
+  LACT_CUDA(cudaGetLastError());
+  return LACT_OK;
+}
+
+inline int ceil_div(int64_t a, int64_t b) { return static_cast<int>((a + b - 1) / b); }
+
+using OpStore = OpBmm<EpiStore, 128, 3>;
+using OpDW = OpBmm<EpiDW, 128, 4>;
+using OpNs = OpBmm<EpiNs, 128, 3>;
+
+// ------------------------------------------------------------------------------------------
+// building blocks (device pointers in, kernels enqueued)
+// ------------------------------------------------------------------------------------------
+struct ApplyArgs {
+  const bf16* w02b;  // [B][2H][D]
+  const bf16* w1b;   // [B][D][H]
+  const void* x;     // activations [B][*][D], bf16
+  int64_t x_bs, x_ts;
+  int64_t start, end;  // token range
+  void* out;           // [B][*][D] bf16
+  int64_t o_bs, o_ts;
+  int64_t out_start;
+  bf16* hidden;  // scratch [B][end-start][H]
+  int64_t B, D, H;
+};
+
+int run_apply(const ApplyArgs& a, int32_t* status, cudaStream_t stream) {
+  const int64_t len = a.end - a.start;
+  if (len <= 0) return LACT_OK;
+  const Mat w02{a.w02b, 2 * a.H, a.D, a.D, a.B, 2 * a.H * a.D};
+  const Mat w1{a.w1b, a.D, a.H, a.H, a.B, a.D * a.H};
+  const Mat x{a.x, a.end, a.D, a.x_ts, a.B, a.x_bs};
+  const Mat hid{a.hidden, len, a.H, a.H, a.B, len * a.H};
+  {
+    GemmArgs<OpSwigluGate, 1> g;
+    std::memset(&g, 0, sizeof(g));
+    auto& P = g.prob[0];
+    LACT_TRY(make_operand(&P.a[0], &P.ai[0], x, 0, kBM, static_cast<int>(a.start), 0));
+    LACT_TRY(make_operand(&P.b[0], &P.bi[0], w02, 0, OpSwigluGate::BN, 0, 0));
+    LACT_TRY(make_operand(&P.b[1], &P.bi[1], w02, 0, OpSwigluGate::BN, static_cast<int>(a.H), 0));
+    P.M = static_cast<int>(len); P.N = static_cast<int>(a.H); P.K = static_cast<int>(a.D);
+    P.batch = static_cast<int>(a.B);
+    P.ep = EpiSwiglu{a.hidden, len * a.H, a.H};
+    g.status = status;
+    LACT_TRY(launch_gemm(g, stream));
+  }
+  {
+    GemmArgs<OpStore, 1> g;
+    std::memset(&g, 0, sizeof(g));
+    auto& P = g.prob[0];
+    LACT_TRY(make_operand(&P.a[0], &P.ai[0], hid, 0, kBM, 0, 0));
+    LACT_TRY(make_operand(&P.b[0], &P.bi[0], w1, 0, OpStore::BN, 0, 0));
+    P.M = static_cast<int>(len); P.N = static_cast<int>(a.D); P.K = static_cast<int>(a.H);
+    P.batch = static_cast<int>(a.B);
+    P.ep = EpiStore{a.out, a.o_bs, a.o_ts, static_cast<int32_t>(a.out_start), 0};
+    g.status = status;
+    LACT_TRY(launch_gemm(g, stream));
+  }
+  return LACT_OK;
+}
+
+struct GradArgs {
+  const bf16* w02b;
+  const bf16* w1b;
+  const void *k, *v;
+  int64_t k_bs, k_ts, v_bs, v_ts;
+  int64_t start, end;
+  const void *lr0, *lr1, *lr2;
+  int32_t lr_f32;
+  int64_t lr_bs;
+  float w_scale;
+  bf16* dy02;  // scratch [B][len][2H]
+  bf16* hid;   // scratch [B][len][H]
+  void* g02;   // [B][2H][D] fp32 (state) or bf16
+  void* g1;    // [B][D][H]
+  int32_t g_f32;
+  const float* beta;  // [B] or nullptr
+  int64_t B, D, H;
+};
+
+int run_grad(const GradArgs& a, int32_t* status, cudaStream_t stream) {
+  const int64_t len = a.end - a.start;
+  if (len <= 0) return LACT_ERR_STEPS;
+  const Mat w02{a.w02b, 2 * a.H, a.D, a.D, a.B, 2 * a.H * a.D};
+  const Mat w1{a.w1b, a.D, a.H, a.H, a.B, a.D * a.H};
+  const Mat km{a.k, a.end, a.D, a.k_ts, a.B, a.k_bs};
+  const Mat vm{a.v, a.end, a.D, a.v_ts, a.B, a.v_bs};
+  const Mat dy{a.dy02, len, 2 * a.H, 2 * a.H, a.B, len * 2 * a.H};
+  const Mat hid{a.hid, len, a.H, a.H, a.B, len * a.H};
+  {
+    GemmArgs<OpFwGradPointwise, 1> g;
+    std::memset(&g, 0, sizeof(g));
+    auto& P = g.prob[0];
+    LACT_TRY(make_operand(&P.a[0], &P.ai[0], km, 0, kBM, static_cast<int>(a.start), 0));
+    LACT_TRY(make_operand(&P.a[1], &P.ai[1], vm, 0, kBM, static_cast<int>(a.start), 0));
+    LACT_TRY(make_operand(&P.b[0], &P.bi[0], w02, 0, OpFwGradPointwise::BN, 0, 0));
+    LACT_TRY(make_operand(&P.b[1], &P.bi[1], w02, 0, OpFwGradPointwise::BN, static_cast<int>(a.H), 0));
+    // dh = v w1: w1 is [D][H], i.e. k (= D) rows with the n (= H) axis contiguous
+    LACT_TRY(make_operand(&P.b[2], &P.bi[2], w1, 1, OpFwGradPointwise::BN, 0, 0));
+    P.M = static_cast<int>(len); P.N = static_cast<int>(a.H); P.K = static_cast<int>(a.D);
+    P.batch = static_cast<int>(a.B);
+    P.ep = EpiFwGrad{a.lr0, a.lr1, a.lr2, a.lr_f32, static_cast<int32_t>(a.start), a.lr_bs, a.w_scale,
+                     a.dy02, len * 2 * a.H, 2 * a.H, static_cast<int32_t>(a.H), a.hid, len * a.H, a.H};
+    g.status = status;
+    LACT_TRY(launch_gemm(g, stream));
+  }
+  {
+    // token contraction: [dw0; dw2] = dy02^T k  and  dw1 = v^T hidden
+    GemmArgs<OpDW, 2> g;
+    std::memset(&g, 0, sizeof(g));
+    auto& P0 = g.prob[0];
+    LACT_TRY(make_operand(&P0.a[0], &P0.ai[0], dy, 1, kBM, 0, 0));
+    LACT_TRY(make_operand(&P0.b[0], &P0.bi[0], km, 1, OpDW::BN, 0, static_cast<int>(a.start)));
+    P0.M = static_cast<int>(2 * a.H); P0.N = static_cast<int>(a.D); P0.K = static_cast<int>(len);
+    P0.batch = static_cast<int>(a.B);
+    P0.ep = EpiDW{a.g02, 2 * a.H * a.D, a.D, a.beta, 1, a.g_f32};
+    auto& P1 = g.prob[1];
+    LACT_TRY(make_operand(&P1.a[0], &P1.ai[0], vm, 1, kBM, 0, static_cast<int>(a.start)));
+    LACT_TRY(make_operand(&P1.b[0], &P1.bi[0], hid, 1, OpDW::BN, 0, 0));
+    P1.M = static_cast<int>(a.D); P1.N = static_cast<int>(a.H); P1.K = static_cast<int>(len);
+    P1.batch = static_cast<int>(a.B);
+    P1.ep = EpiDW{a.g1, a.D * a.H, a.H, a.beta, 1, a.g_f32};
+    g.status = status;
+    LACT_TRY(launch_gemm(g, stream));
+  }
+  return LACT_OK;
+}
+
+// Newton-Schulz coefficient schedules.
+const float kNsTuned[5][3] = {{4.0848f, -6.8946f, 2.9270f},
+                              {3.9505f, -6.3029f, 2.6377f},
+                              {3.7418f, -5.5913f, 2.3037f},
+                              {2.8769f, -3.1427f, 1.2046f},
+                              {2.8366f, -3.0525f, 1.2012f}};
+const float kNsConst[3] = {3.4445f, -4.7750f, 2.0315f};
+
+// One group of equally shaped matrices under iteration: X is [nmat][m][n] with m <= n.
+struct NsGroup {
+  int32_t nmat, m, n;
+  bf16 *xa, *xb;         // ping-pong iterates [nmat][m][n]
+  bf16 *gram, *cgram, *poly;  // [nmat][m][m]
+};
+
+inline size_t ns_group_bytes(int64_t nmat, int64_t m, int64_t n) {
+  return static_cast<size_t>(nmat) * (2 * m * n + 3 * m * m) * 2;
+}
+
+// Runs `steps` iterations on up to two groups (one launch per GEMM covers both).
+// Returns in result[g] the buffer that holds the final iterate.
+int run_ns_iterations(NsGroup* grp, int ngroups, int steps, int const_coeffs, const bf16** result, int32_t* status,
+                      cudaStream_t stream) {
+  if (ngroups < 1 || ngroups > 2) return LACT_ERR_CONFIG;
+  if (!const_coeffs && steps != 5) return LACT_ERR_CONFIG;
+  bf16* cur[2];
+  bf16* nxt[2];
+  for (int g = 0; g < ngroups; ++g) { cur[g] = grp[g].xa; nxt[g] = grp[g].xb; }
+  for (int it = 0; it < steps; ++it) {
+    const float* co = const_coeffs ? kNsConst : kNsTuned[it];
+    GemmArgs<OpNs, 2> ga, gb, gc;
+    std::memset(&ga, 0, sizeof(ga));
+    std::memset(&gb, 0, sizeof(gb));
+    std::memset(&gc, 0, sizeof(gc));
+    for (int g = 0; g < ngroups; ++g) {
+      const NsGroup& G = grp[g];
+      const int gi = g;
+      const Mat X{cur[gi], G.m, G.n, G.n, G.nmat, static_cast<int64_t>(G.m) * G.n};
+      const Mat A{G.gram, G.m, G.m, G.m, G.nmat, static_cast<int64_t>(G.m) * G.m};
+      const Mat CA{G.cgram, G.m, G.m, G.m, G.nmat, static_cast<int64_t>(G.m) * G.m};
+      const Mat PB{G.poly, G.m, G.m, G.m, G.nmat, static_cast<int64_t>(G.m) * G.m};
+      const int nb = G.nmat;
+      // gram = X X^T ; cgram = c * gram
+      auto& PA = ga.prob[g];
+      LACT_TRY(make_operand(&PA.a[0], &PA.ai[0], X, 0, kBM, 0, 0));
+      LACT_TRY(make_operand(&PA.b[0], &PA.bi[0], X, 0, OpNs::BN, 0, 0));
+      PA.M = G.m; PA.N = G.m; PA.K = G.n; PA.batch = nb;
+      PA.ep = EpiNs{G.gram, G.cgram, nullptr, 0.f, co[2], static_cast<int64_t>(G.m) * G.m, G.m};
+      // poly = b * gram + cgram gram   (gram is symmetric: its rows serve as the K-major B operand)
+      auto& PBm = gb.prob[g];
+      LACT_TRY(make_operand(&PBm.a[0], &PBm.ai[0], CA, 0, kBM, 0, 0));
+      LACT_TRY(make_operand(&PBm.b[0], &PBm.bi[0], A, 0, OpNs::BN, 0, 0));
+      PBm.M = G.m; PBm.N = G.m; PBm.K = G.m; PBm.batch = nb;
+      PBm.ep = EpiNs{G.poly, nullptr, G.gram, co[1], 0.f, static_cast<int64_t>(G.m) * G.m, G.m};
+      // X' = a * X + poly X   (X is [m][n]: k rows, n contiguous -> MN-major B operand)
+      auto& PC = gc.prob[g];
+      LACT_TRY(make_operand(&PC.a[0], &PC.ai[0], PB, 0, kBM, 0, 0));
+      LACT_TRY(make_operand(&PC.b[0], &PC.bi[0], X, 1, OpNs::BN, 0, 0));
+      PC.M = G.m; PC.N = G.n; PC.K = G.m; PC.batch = nb;
+      PC.ep = EpiNs{nxt[gi], nullptr, cur[gi], co[0], 0.f, static_cast<int64_t>(G.m) * G.n, G.n};
+    }
+    ga.status = gb.status = gc.status = status;
+    LACT_TRY(launch_gemm(ga, stream, ngroups));
+    LACT_TRY(launch_gemm(gb, stream, ngroups));
+    LACT_TRY(launch_gemm(gc, stream, ngroups));
+    for (int g = 0; g < ngroups; ++g) std::swap(cur[g], nxt[g]);
+  }
+  for (int g = 0; g < ngroups; ++g) result[g] = cur[g];
+  return LACT_OK;
+}
+
+
+// ------------------------------------------------------------------------------------------
+// workspace planning
+// ------------------------------------------------------------------------------------------
+struct Carver {
+  uint8_t* base;
+  size_t off = 0;
+  explicit Carver(void* b) : base(static_cast<uint8_t*>(b)) {}
+  template <class T>
+  T* take(size_t count) {
+    off = (off + 255) & ~static_cast<size_t>(255);
+    T* p = base ? reinterpret_cast<T*>(base + off) : nullptr;
+    off += count * sizeof(T);
+    return p;
+  }
+};
+
+struct NsPlan {
+  int ngroups;
+  NsGroup grp[2];
+};
+
+// Carves Newton-Schulz buffers.  separate: one group of 3B matrices [m][n] (w0 and w2 of batch b
+// at 2b, 2b+1; w1 of batch b at 2B + b).  concat: group 0 = [w0; w2] as B matrices, group 1 = w1.
+void plan_ns(Carver& c, int64_t B, int64_t D, int64_t H, int concat, NsPlan* plan) {
+  auto fill = [&](NsGroup& g, int64_t nmat, int64_t r, int64_t cc) {
+    g.nmat = static_cast<int32_t>(nmat);
+    g.m = static_cast<int32_t>(std::min(r, cc));
+    g.n = static_cast<int32_t>(std::max(r, cc));
+    const size_t mn = static_cast<size_t>(nmat) * g.m * g.n, mm = static_cast<size_t>(nmat) * g.m * g.m;
+    g.xa = c.take<bf16>(mn);
+    g.xb = c.take<bf16>(mn);
+    g.gram = c.take<bf16>(mm);
+    g.cgram = c.take<bf16>(mm);
+    g.poly = c.take<bf16>(mm);
+  };
+  if (concat) {
+    plan->ngroups = 2;
+    fill(plan->grp[0], B, 2 * H, D);
+    fill(plan->grp[1], B, D, H);
+  } else {
+    plan->ngroups = 1;
+    fill(plan->grp[0], 3 * B, H, D);
+  }
+}
+
+struct ScanPlan {
+  int32_t* status;
+  float *W02, *W1, *W02c, *W1c, *n02, *n1, *G02, *G1, *beta;
+  bf16 *W02b, *W1b, *hidden, *dy02, *hid;
+  NsPlan ns;
+  size_t bytes;
+};
+
+int plan_scan(const lact_scan_config& c, int32_t n_steps, const int32_t* kind, const int64_t* start,
+              const int64_t* end, void* base, ScanPlan* p) {
+  int64_t max_apply = 0, max_update = 0;
+  for (int i = 0; i < n_steps; ++i) {
+    if (start[i] < 0 || end[i] > c.L || end[i] < start[i]) return LACT_ERR_STEPS;
+    const int64_t len = end[i] - start[i];
+    if (kind[i] == LACT_STEP_APPLY) max_apply = std::max(max_apply, len);
+    else if (kind[i] == LACT_STEP_UPDATE) {
+      if (len <= 0) return LACT_ERR_STEPS;
+      max_update = std::max(max_update, len);
+    } else return LACT_ERR_STEPS;
+  }
+  Carver cv(base);
+  const size_t B = c.B, D = c.D, H = c.H;
+  p->status = cv.take<int32_t>(64);
+  p->W02 = cv.take<float>(B * 2 * H * D);
+  p->W1 = cv.take<float>(B * D * H);
+  p->W02c = cv.take<float>(B * 2 * H * D);
+  p->W1c = cv.take<float>(B * D * H);
+  p->n02 = cv.take<float>(B * 2 * H);
+  p->n1 = cv.take<float>(B * D);
+  p->G02 = cv.take<float>(B * 2 * H * D);
+  p->G1 = cv.take<float>(B * D * H);
+  p->beta = cv.take<float>(B);
+  p->W02b = cv.take<bf16>(B * 2 * H * D);
+  p->W1b = cv.take<bf16>(B * D * H);
+  p->hidden = cv.take<bf16>(B * static_cast<size_t>(max_apply) * H);
+  p->dy02 = cv.take<bf16>(B * static_cast<size_t>(max_update) * 2 * H);
+  p->hid = cv.take<bf16>(B * static_cast<size_t>(max_update) * H);
+  p->ns.ngroups = 0;
+  if (c.use_muon && max_update > 0) plan_ns(cv, c.B, c.D, c.H, c.ns_concat, &p->ns);
+  p->bytes = cv.off + 256;
+  return LACT_OK;
+}
+
+int validate_scan_config(const lact_scan_config& c) {
+  if (c.B < 1 || c.L < 1 || c.D < 16 || c.H < 16 || c.out_len < 0) return LACT_ERR_SHAPE;
+  if ((c.D % 16) != 0 || (c.H % 16) != 0) return LACT_ERR_SHAPE;
+  if (c.B > 65535 / 3 || c.L > (1ll << 30)) return LACT_ERR_SHAPE;
+  if (c.act_dtype != LACT_BF16) return LACT_ERR_DTYPE;
+  if (c.use_muon) {
+    if (c.ns_steps < 0 || c.ns_steps > 64) return LACT_ERR_CONFIG;
+    if (!c.ns_const_coeffs && c.ns_steps != 5) return LACT_ERR_CONFIG;
+  }
+  if (c.renorm < 0 || c.renorm > 2) return LACT_ERR_CONFIG;
+  if (c.prenorm && c.overwrite_quirk) return LACT_ERR_CONFIG;
+  return LACT_OK;
+}
+
+// Normalises `nmat` gradient matrices and writes the wide-orientation iterate.
+int launch_ns_prepare(const void* src, int src_f32, int64_t src_ms, int ld, int R, int C, int gram_right, bf16* X,
+                      int nmat, cudaStream_t stream) {
+  const int transpose = (R > C) || (R == C && gram_right);
+  ns_prepare_kernel<<<nmat, 512, 0, stream>>>(src, src_f32, src_ms, ld, R, C, transpose, X,
+                                              static_cast<int64_t>(R) * C);
+  LACT_CUDA(cudaGetLastError());
+  return LACT_OK;
+}
+
+int scan_fwd(const lact_scan_config& c, const lact_scan_io& io, int32_t n_steps, const int32_t* kind,
+             const int64_t* start, const int64_t* end, const int64_t* out_start, void* workspace, size_t ws_bytes,
+             cudaStream_t stream) {
+  LACT_TRY(check_device());
+  LACT_TRY(validate_scan_config(c));
+  if (!io.w0 || !io.w1 || !io.w2 || !io.q || !io.k || !io.v || !io.lr0 || !io.lr1 || !io.lr2 || !io.o)
+    return LACT_ERR_NULL;
+  if (c.use_momentum && !io.momentum) return LACT_ERR_NULL;
+  if (!workspace) return LACT_ERR_WORKSPACE;
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0) return LACT_ERR_WORKSPACE;
+  ScanPlan p;
+  LACT_TRY(plan_scan(c, n_steps, kind, start, end, workspace, &p));
+  if (p.bytes > ws_bytes) return LACT_ERR_WORKSPACE;
+  for (int i = 0; i < n_steps; ++i)
+    if (kind[i] == LACT_STEP_APPLY && (out_start[i] < 0 || out_start[i] + (end[i] - start[i]) > c.out_len))
+      return LACT_ERR_STEPS;
+
+  const int64_t B = c.B, D = c.D, H = c.H;
+  LACT_CUDA(cudaMemsetAsync(p.status, 0, 256, stream));
+  {
+    const int64_t rows = B * (2 * H + D);
+    prepare_weights_kernel<<<ceil_div(rows, 8), 256, 0, stream>>>(io.w0, io.w1, io.w2, c.w_dtype == LACT_F32,
+                                                                  static_cast<int>(B), static_cast<int>(H),
+                                                                  static_cast<int>(D), p.W02, p.W1, p.W02c, p.W1c,
+                                                                  p.n02, p.n1, p.W02b, p.W1b);
+    LACT_CUDA(cudaGetLastError());
+  }
+  // gradient / momentum state
+  if (io.m0_in && io.m1_in && io.m2_in) {
+    LACT_CUDA(cudaMemcpy2DAsync(p.G02, 2 * H * D * 4, io.m0_in, H * D * 4, H * D * 4, B, cudaMemcpyDeviceToDevice,
+                                stream));
+    LACT_CUDA(cudaMemcpy2DAsync(p.G02 + H * D, 2 * H * D * 4, io.m2_in, H * D * 4, H * D * 4, B,
+                                cudaMemcpyDeviceToDevice, stream));
+    LACT_CUDA(cudaMemcpyAsync(p.G1, io.m1_in, B * D * H * 4, cudaMemcpyDeviceToDevice, stream));
+  } else {
+    LACT_CUDA(cudaMemsetAsync(p.G02, 0, B * 2 * H * D * 4, stream));
+    LACT_CUDA(cudaMemsetAsync(p.G1, 0, B * D * H * 4, stream));
+  }
+
+  for (int i = 0; i < n_steps; ++i) {
+    if (kind[i] == LACT_STEP_APPLY) {
+      ApplyArgs a{p.W02b, p.W1b, io.q, c.q_bs, c.q_ts, start[i], end[i], io.o, c.o_bs, c.o_ts, out_start[i],
+                  p.hidden, B, D, H};
+      LACT_TRY(run_apply(a, p.status, stream));
+      continue;
+    }
+    const float* beta = nullptr;
+    if (c.use_momentum) {
+      momentum_mean_kernel<<<static_cast<int>(B), 256, 0, stream>>>(io.momentum, c.mom_dtype == LACT_F32, c.L,
+                                                                    static_cast<int>(start[i]),
+                                                                    static_cast<int>(end[i]), p.beta);
+      LACT_CUDA(cudaGetLastError());
+      beta = p.beta;
+    }
+    GradArgs g{p.W02b, p.W1b, io.k, io.v, c.k_bs, c.k_ts, c.v_bs, c.v_ts, start[i], end[i], io.lr0, io.lr1, io.lr2,
+               c.lr_dtype == LACT_F32, c.L, c.w_scale, p.dy02, p.hid, p.G02, p.G1, 1, beta, B, D, H};
+    LACT_TRY(run_grad(g, p.status, stream));
+
+    const bf16* xres[2] = {nullptr, nullptr};
+    if (c.use_muon) {
+      NsPlan& ns = p.ns;
+      if (c.ns_concat) {
+        LACT_TRY(launch_ns_prepare(p.G02, 1, 2 * H * D, static_cast<int>(D), static_cast<int>(2 * H),
+                                   static_cast<int>(D), c.ns_gram_right, ns.grp[0].xa, static_cast<int>(B), stream));
+        LACT_TRY(launch_ns_prepare(p.G1, 1, D * H, static_cast<int>(H), static_cast<int>(D), static_cast<int>(H),
+                                   c.ns_gram_right, ns.grp[1].xa, static_cast<int>(B), stream));
+      } else {
+        LACT_TRY(launch_ns_prepare(p.G02, 1, H * D, static_cast<int>(D), static_cast<int>(H), static_cast<int>(D),
+                                   c.ns_gram_right, ns.grp[0].xa, static_cast<int>(2 * B), stream));
+        LACT_TRY(launch_ns_prepare(p.G1, 1, D * H, static_cast<int>(H), static_cast<int>(D), static_cast<int>(H),
+                                   c.ns_gram_right, ns.grp[0].xa + 2 * B * H * D, static_cast<int>(B), stream));
+      }
+      LACT_TRY(run_ns_iterations(ns.grp, ns.ngroups, c.ns_steps, c.ns_const_coeffs, xres, p.status, stream));
+    }
+    // add + renormalise, one launch per weight array
+    for (int w = 0; w < 2; ++w) {
+      RenormArgs r;
+      std::memset(&r, 0, sizeof(r));
+      const int R = static_cast<int>(w == 0 ? 2 * H : D), C = static_cast<int>(w == 0 ? D : H);
+      r.master = w == 0 ? p.W02 : p.W1;
+      r.compute = w == 0 ? p.W02c : p.W1c;
+      r.shadow = w == 0 ? p.W02b : p.W1b;
+      r.n0 = w == 0 ? p.n02 : p.n1;
+      r.g = w == 0 ? p.G02 : p.G1;
+      r.B = static_cast<int>(B); r.R = R; r.C = C;
+      r.mode = c.renorm; r.prenorm = c.prenorm; r.prenorm_bf16 = c.prenorm_bf16; r.quirk = c.overwrite_quirk;
+      if (c.use_muon) {
+        int mat_rows;  // rows of one orthogonalised matrix in the weight's own orientation
+        if (c.ns_concat) {
+          r.x = xres[w];
+          r.x_mats_per_b = 1; r.x_mat_off = 0;
+          mat_rows = R;
+        } else {
+          r.x = xres[0];
+          r.x_mats_per_b = w == 0 ? 2 : 1;
+          r.x_mat_off = w == 0 ? 0 : static_cast<int>(2 * B);
+          mat_rows = static_cast<int>(w == 0 ? H : D);
+        }
+        r.x_rows_per_mat = mat_rows;
+        r.x_ms = static_cast<int64_t>(mat_rows) * C;
+        r.x_transposed = (mat_rows > C) || (mat_rows == C && c.ns_gram_right);
+        r.x_ld = r.x_transposed ? mat_rows : C;
+      }
+      const int64_t rows = B * R;
+      add_renorm_kernel<<<ceil_div(rows, 8), 256, 0, stream>>>(r);
+      LACT_CUDA(cudaGetLastError());
+    }
+  }
+  // final state out
+  if (io.w0_out) LACT_CUDA(cudaMemcpy2DAsync(io.w0_out, H * D * 4, p.W02c, 2 * H * D * 4, H * D * 4, B,
+                                             cudaMemcpyDeviceToDevice, stream));
+  if (io.w2_out) LACT_CUDA(cudaMemcpy2DAsync(io.w2_out, H * D * 4, p.W02c + H * D, 2 * H * D * 4, H * D * 4, B,
+                                             cudaMemcpyDeviceToDevice, stream));
+  if (io.w1_out) LACT_CUDA(cudaMemcpyAsync(io.w1_out, p.W1c, B * D * H * 4, cudaMemcpyDeviceToDevice, stream));
+  if (io.m0_out) LACT_CUDA(cudaMemcpy2DAsync(io.m0_out, H * D * 4, p.G02, 2 * H * D * 4, H * D * 4, B,
+                                             cudaMemcpyDeviceToDevice, stream));
+  if (io.m2_out) LACT_CUDA(cudaMemcpy2DAsync(io.m2_out, H * D * 4, p.G02 + H * D, 2 * H * D * 4, H * D * 4, B,
+                                             cudaMemcpyDeviceToDevice, stream));
+  if (io.m1_out) LACT_CUDA(cudaMemcpyAsync(io.m1_out, p.G1, B * D * H * 4, cudaMemcpyDeviceToDevice, stream));
+  return LACT_OK;
+}
+
+}  // namespace
+}  // namespace lact
+
+// ==========================================================================================
+// extern "C" entry points
+// ==========================================================================================
+using namespace lact;
+
+extern "C" {
+
+int lact_version(void) { return 1000; }
+
+const char* lact_error_string(int code) {
+  switch (code) {
+    case LACT_OK: return "ok";
+    case LACT_ERR_NULL: return "a required pointer is NULL";
+    case LACT_ERR_SHAPE: return "unsupported or inconsistent sizes, strides or alignment";
+    case LACT_ERR_DTYPE: return "unsupported dtype combination";
+    case LACT_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
+    case LACT_ERR_CONFIG: return "inconsistent configuration flags";
+    case LACT_ERR_STEPS: return "malformed step list";
+    case LACT_ERR_CUDA: return "a CUDA runtime or driver call failed";
+    case LACT_ERR_DEVICE: return "device is not compute capability 10.x (B200)";
+    case kStatusWaitTimeout: return "device: a bounded barrier wait timed out";
+    default: return "unknown code";
+  }
+}
+
+int lact_read_status(const void* workspace, void* stream) {
+  if (!workspace) return LACT_ERR_NULL;
+  int32_t st = 0;
+  if (cudaMemcpyAsync(&st, workspace, 4, cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)) != cudaSuccess)
+    return LACT_ERR_CUDA;
+  if (cudaStreamSynchronize(static_cast<cudaStream_t>(stream)) != cudaSuccess) return LACT_ERR_CUDA;
+  return st;
+}
+
+int lact_scan_workspace_bytes(const lact_scan_config* cfg, int32_t n_steps, const int32_t* kind,
+                              const int64_t* start, const int64_t* end, size_t* bytes_out) {
+  if (!cfg || !bytes_out || (n_steps > 0 && (!kind || !start || !end))) return LACT_ERR_NULL;
+  LACT_TRY(validate_scan_config(*cfg));
+  ScanPlan p;
+  LACT_TRY(plan_scan(*cfg, n_steps, kind, start, end, nullptr, &p));
+  *bytes_out = p.bytes;
+  return LACT_OK;
+}
+
+int lact_scan_fwd(const lact_scan_config* cfg, const lact_scan_io* io, int32_t n_steps, const int32_t* kind,
+                  const int64_t* start, const int64_t* end, const int64_t* out_start, void* workspace,
+                  size_t workspace_bytes, void* stream) {
+  if (!cfg || !io || (n_steps > 0 && (!kind || !start || !end || !out_start))) return LACT_ERR_NULL;
+  return scan_fwd(*cfg, *io, n_steps, kind, start, end, out_start, workspace, workspace_bytes,
+                  static_cast<cudaStream_t>(stream));
+}
+
+// ---------------------------------------------------------------- sub-ops
+static int check_dims(int64_t B, int64_t N, int64_t D, int64_t H) {
+  if (B < 1 || N < 1 || D < 16 || H < 16 || (D % 16) || (H % 16) || B > 65535 || N > (1ll << 30))
+    return LACT_ERR_SHAPE;
+  return LACT_OK;
+}
+
+int lact_swiglu_ffn_workspace_bytes(int64_t B, int64_t N, int64_t D, int64_t H, size_t* bytes_out) {
+  if (!bytes_out) return LACT_ERR_NULL;
+  LACT_TRY(check_dims(B, N, D, H));
+  *bytes_out = 512 + static_cast<size_t>(B) * N * H * 2;
+  return LACT_OK;
+}
+
+int lact_swiglu_ffn_fwd(const void* w0w2, const void* w1, const void* x, void* out, int64_t B, int64_t N, int64_t D,
+                        int64_t H, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!w0w2 || !w1 || !x || !out) return LACT_ERR_NULL;
+  LACT_TRY(check_device());
+  size_t need = 0;
+  LACT_TRY(lact_swiglu_ffn_workspace_bytes(B, N, D, H, &need));
+  if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255)) return LACT_ERR_WORKSPACE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  LACT_CUDA(cudaMemsetAsync(workspace, 0, 256, s));
+  ApplyArgs a{static_cast<const bf16*>(w0w2), static_cast<const bf16*>(w1), x, N * D, D, 0, N, out, N * D, D, 0,
+              reinterpret_cast<bf16*>(static_cast<uint8_t*>(workspace) + 256), B, D, H};
+  return run_apply(a, static_cast<int32_t*>(workspace), s);
+}
+
+int lact_fw_grad_workspace_bytes(int64_t B, int64_t N, int64_t D, int64_t H, size_t* bytes_out) {
+  if (!bytes_out) return LACT_ERR_NULL;
+  LACT_TRY(check_dims(B, N, D, H));
+  *bytes_out = 1024 + static_cast<size_t>(B) * N * 3 * H * 2;
+  return LACT_OK;
+}
+
+int lact_fw_grad(const void* w0w2, const void* w1, const void* k, const void* v, const void* lr0, const void* lr1,
+                 const void* lr2, int32_t lr_dtype, void* dw0w2, void* dw1, int64_t B, int64_t N, int64_t D, int64_t H,
+                 void* workspace, size_t workspace_bytes, void* stream) {
+  if (!w0w2 || !w1 || !k || !v || !lr0 || !lr1 || !lr2 || !dw0w2 || !dw1) return LACT_ERR_NULL;
+  LACT_TRY(check_device());
+  size_t need = 0;
+  LACT_TRY(lact_fw_grad_workspace_bytes(B, N, D, H, &need));
+  if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255)) return LACT_ERR_WORKSPACE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  LACT_CUDA(cudaMemsetAsync(workspace, 0, 256, s));
+  Carver cv(workspace);
+  int32_t* status = cv.take<int32_t>(64);
+  bf16* dy02 = cv.take<bf16>(static_cast<size_t>(B) * N * 2 * H);
+  bf16* hid = cv.take<bf16>(static_cast<size_t>(B) * N * H);
+  GradArgs g{static_cast<const bf16*>(w0w2), static_cast<const bf16*>(w1), k, v, N * D, D, N * D, D, 0, N, lr0, lr1,
+             lr2, lr_dtype == LACT_F32, N, 1.0f, dy02, hid, dw0w2, dw1, 0, nullptr, B, D, H};
+  return run_grad(g, status, s);
+}
+
+int lact_newton_schulz_workspace_bytes(int64_t B, int64_t R, int64_t C, size_t* bytes_out) {
+  if (!bytes_out) return LACT_ERR_NULL;
+  if (B < 1 || B > 65535 || R < 8 || C < 8 || (R % 8) || (C % 8)) return LACT_ERR_SHAPE;
+  *bytes_out = 2048 + ns_group_bytes(B, std::min(R, C), std::max(R, C));
+  return LACT_OK;
+}
+
+int lact_newton_schulz(const void* g, int32_t g_dtype, void* x, int64_t B, int64_t R, int64_t C, int32_t steps,
+                       int32_t const_coeffs, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!g || !x) return LACT_ERR_NULL;
+  LACT_TRY(check_device());
+  size_t need = 0;
+  LACT_TRY(lact_newton_schulz_workspace_bytes(B, R, C, &need));
+  if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255)) return LACT_ERR_WORKSPACE;
+  if (steps < 0 || steps > 64 || (!const_coeffs && steps != 5)) return LACT_ERR_CONFIG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  LACT_CUDA(cudaMemsetAsync(workspace, 0, 256, s));
+  Carver cv(workspace);
+  int32_t* status = cv.take<int32_t>(64);
+  NsGroup grp;
+  const int64_t m = std::min(R, C), n = std::max(R, C);
+  grp.nmat = static_cast<int32_t>(B); grp.m = static_cast<int32_t>(m); grp.n = static_cast<int32_t>(n);
+  grp.xa = cv.take<bf16>(B * m * n);
+  grp.xb = cv.take<bf16>(B * m * n);
+  grp.gram = cv.take<bf16>(B * m * m);
+  grp.cgram = cv.take<bf16>(B * m * m);
+  grp.poly = cv.take<bf16>(B * m * m);
+  LACT_TRY(launch_ns_prepare(g, g_dtype == LACT_F32, R * C, static_cast<int>(C), static_cast<int>(R),
+                             static_cast<int>(C), 0, grp.xa, static_cast<int>(B), s));
+  const bf16* res = nullptr;
+  LACT_TRY(run_ns_iterations(&grp, 1, steps, const_coeffs, &res, status, s));
+  ns_export_kernel<<<static_cast<int>(B), 512, 0, s>>>(res, m * n, static_cast<int>(R), static_cast<int>(C), R > C,
+                                                       static_cast<bf16*>(x), R * C);
+  LACT_CUDA(cudaGetLastError());
+  return LACT_OK;
+}
+
+int lact_l2_norm_add(const void* x, int32_t x_dtype, const void* x_add, int32_t add_dtype, const void* scale, void* y,
+                     int32_t y_dtype, int64_t B, int64_t T, int64_t D, float eps, void* stream) {
+  if (!x || !x_add || !scale || !y) return LACT_ERR_NULL;
+  if (B < 1 || T < 1 || D < 1) return LACT_ERR_SHAPE;
+  const int64_t rows = B * T;
+  l2_norm_add_kernel<<<ceil_div(rows, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      x, x_dtype == LACT_F32, x_add, add_dtype == LACT_F32, static_cast<const float*>(scale), y, y_dtype == LACT_F32,
+      rows, static_cast<int>(D), eps);
+  LACT_CUDA(cudaGetLastError());
+  return LACT_OK;
+}
+
+int lact_prenorm_momentum_l2norm(const void* x, const void* dx, const void* m, const void* mu, const void* scale,
+                                 void* x_out, void* m_out, void* y_out, int64_t B, int64_t T, int64_t D, float eps,
+                                 void* stream) {
+  if (!x || !dx || !m || !mu || !scale || !x_out || !m_out || !y_out) return LACT_ERR_NULL;
+  if (B < 1 || T < 1 || D < 1) return LACT_ERR_SHAPE;
+  const int64_t rows = B * T;
+  prenorm_momentum_kernel<<<ceil_div(rows, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const float*>(x), static_cast<const bf16*>(dx), static_cast<const float*>(m),
+      static_cast<const float*>(mu), static_cast<const float*>(scale), static_cast<float*>(x_out),
+      static_cast<float*>(m_out), static_cast<bf16*>(y_out), rows, static_cast<int>(T), static_cast<int>(D), eps);
+  LACT_CUDA(cudaGetLastError());
+  return LACT_OK;
+}
+
+int lact_bmm_bf16(const void* a, int32_t a_mn_major, const void* b, int32_t b_mn_major, void* c, int32_t c_dtype,
+                  int64_t batch, int64_t M, int64_t N, int64_t K, int32_t* status_word, void* stream) {
+  if (!a || !b || !c || !status_word) return LACT_ERR_NULL;
+  LACT_TRY(check_device());
+  if (batch < 1 || batch > 65535 || M < 1 || N < 8 || K < 1 || (M % 8) || (N % 8) || (K % 8)) return LACT_ERR_SHAPE;
+  const Mat A = a_mn_major ? Mat{a, K, M, M, batch, K * M} : Mat{a, M, K, K, batch, M * K};
+  const Mat Bm = b_mn_major ? Mat{b, K, N, N, batch, K * N} : Mat{b, N, K, K, batch, N * K};
+  GemmArgs<OpStore, 1> g;
+  std::memset(&g, 0, sizeof(g));
+  auto& P = g.prob[0];
+  LACT_TRY(make_operand(&P.a[0], &P.ai[0], A, a_mn_major, kBM, 0, 0));
+  LACT_TRY(make_operand(&P.b[0], &P.bi[0], Bm, b_mn_major, OpStore::BN, 0, 0));
+  P.M = static_cast<int>(M); P.N = static_cast<int>(N); P.K = static_cast<int>(K); P.batch = static_cast<int>(batch);
+  P.ep = EpiStore{c, M * N, N, 0, c_dtype == LACT_F32};
+  g.status = status_word;
+  return launch_gemm(g, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

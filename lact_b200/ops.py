@@ -1,0 +1,406 @@
+"""Drop-in replacements for the reference's fused sub-ops and chunk drivers.
+
+Same names, positional order, keyword defaults and return types as the reference functions
+(cited per function); the arithmetic runs in the sm_100a kernels of liblact_b200.so through the
+C ABI.  Forward only: outputs do not carry autograd history.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from . import _lib as L
+from . import program as P
+
+BF16 = torch.bfloat16
+
+
+def _need_cuda(*ts: torch.Tensor) -> torch.device:
+    dev = None
+    for t in ts:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError("lact_b200 runs on CUDA tensors only (there is no CPU implementation)")
+        if dev is not None and t.device != dev:
+            raise ValueError("all tensors must be on the same device")
+        dev = t.device
+    return dev
+
+
+def _act(t: torch.Tensor, name: str) -> torch.Tensor:
+    if t.dtype != BF16:
+        raise TypeError(f"{name} must be bfloat16 (got {t.dtype}); cast the activations before the call")
+    if t.dim() != 3:
+        raise ValueError(f"{name} must be [b, l, d]")
+    if t.stride(2) != 1 or t.stride(1) % 8 or t.stride(0) % 8 or t.data_ptr() % 16:
+        t = t.contiguous()
+    return t
+
+
+def _vec(t: torch.Tensor, B: int, Ltok: int, name: str) -> torch.Tensor:
+    """[b, l, 1] or [b, l] per-token scalar -> contiguous [b, l] in fp32 or bf16."""
+    if t.dim() == 3:
+        if t.shape[2] != 1:
+            raise ValueError(f"{name} must be [b, l, 1]")
+        t = t[..., 0]
+    if tuple(t.shape) != (B, Ltok):
+        raise ValueError(f"{name} has shape {tuple(t.shape)}, expected {(B, Ltok)}")
+    if t.dtype not in (torch.float32, BF16):
+        t = t.float()
+    return t.contiguous()
+
+
+def _weight(t: torch.Tensor, shape: tuple, name: str) -> torch.Tensor:
+    if tuple(t.shape) != shape:
+        raise ValueError(f"{name} has shape {tuple(t.shape)}, expected {shape}")
+    if t.dtype not in (torch.float32, BF16):
+        t = t.float()
+    return t.contiguous()
+
+
+def scan(w0, w1, w2, q, k, v, lr0, lr1, lr2, steps: Sequence[P.Step], *, out_len: Optional[int] = None,
+         momentum=None, m_init=None, use_muon=False, ns_steps=5, ns_const_coeffs=False, ns_concat=False,
+         ns_gram_right=False, renorm=L.RENORM_EPS_OUTSIDE, prenorm=False, prenorm_bf16=False, overwrite_quirk=False,
+         w_scale=1.0, return_state=False, return_momentum=False):
+    """General chunk recurrence in the LLM layout (w0, w2: [B,H,D]; w1: [B,D,H]); see
+    `lact_scan_fwd` in include/lact_b200.h.  Returns o, and optionally the final fast weights
+    and momentum state (fp32)."""
+    dev = _need_cuda(w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum)
+    q, k, v = _act(q, "q"), _act(k, "k"), _act(v, "v")
+    B, Ltok, D = k.shape
+    H = w0.shape[1]
+    if q.shape[0] != B or q.shape[2] != D or v.shape != k.shape:
+        raise ValueError("q, k, v shapes disagree")
+    w0 = _weight(w0, (B, H, D), "w0")
+    w1 = _weight(w1, (B, D, H), "w1")
+    w2 = _weight(w2, (B, H, D), "w2")
+    if not (w0.dtype == w1.dtype == w2.dtype):
+        w0, w1, w2 = w0.float(), w1.float(), w2.float()
+    lr0, lr1, lr2 = (_vec(t, B, Ltok, n) for t, n in ((lr0, "lr0"), (lr1, "lr1"), (lr2, "lr2")))
+    if not (lr0.dtype == lr1.dtype == lr2.dtype):
+        lr0, lr1, lr2 = lr0.float(), lr1.float(), lr2.float()
+    if momentum is not None:
+        momentum = _vec(momentum, B, Ltok, "momentum")
+    if q.shape[1] != Ltok:
+        raise ValueError("q and k must have the same number of tokens")
+    out_len = Ltok if out_len is None else int(out_len)
+    o = torch.empty(B, out_len, D, dtype=BF16, device=dev)
+
+    cfg = L.ScanConfig()
+    cfg.B, cfg.L, cfg.D, cfg.H, cfg.out_len = B, Ltok, D, H, out_len
+    cfg.act_dtype = L.LACT_BF16
+    cfg.lr_dtype = L.dtype_code(lr0)
+    cfg.mom_dtype = L.dtype_code(momentum) if momentum is not None else L.LACT_F32
+    cfg.w_dtype = L.dtype_code(w0)
+    cfg.use_momentum = int(momentum is not None)
+    cfg.use_muon, cfg.ns_steps, cfg.ns_const_coeffs = int(use_muon), int(ns_steps), int(ns_const_coeffs)
+    cfg.ns_concat, cfg.ns_gram_right = int(ns_concat), int(ns_gram_right)
+    cfg.renorm, cfg.prenorm, cfg.prenorm_bf16 = int(renorm), int(prenorm), int(prenorm_bf16)
+    cfg.overwrite_quirk, cfg.w_scale = int(overwrite_quirk), float(w_scale)
+    cfg.q_bs, cfg.q_ts = q.stride(0), q.stride(1)
+    cfg.k_bs, cfg.k_ts = k.stride(0), k.stride(1)
+    cfg.v_bs, cfg.v_ts = v.stride(0), v.stride(1)
+    cfg.o_bs, cfg.o_ts = o.stride(0), o.stride(1)
+
+    n = len(steps)
+    kind = (C.c_int32 * n)(*[s[0] for s in steps])
+    start = (C.c_int64 * n)(*[s[1] for s in steps])
+    end = (C.c_int64 * n)(*[s[2] for s in steps])
+    outs = (C.c_int64 * n)(*[s[3] for s in steps])
+    lib = L.lib()
+    need = C.c_size_t(0)
+    L.check(lib.lact_scan_workspace_bytes(C.byref(cfg), n, kind, start, end, C.byref(need)), "lact_scan_workspace_bytes")
+    ws = L.workspace(need.value, dev)
+
+    io = L.ScanIO()
+    io.w0, io.w1, io.w2 = w0.data_ptr(), w1.data_ptr(), w2.data_ptr()
+    io.q, io.k, io.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
+    io.lr0, io.lr1, io.lr2 = lr0.data_ptr(), lr1.data_ptr(), lr2.data_ptr()
+    io.momentum = momentum.data_ptr() if momentum is not None else None
+    keep = []
+    if m_init is not None:
+        m_init = [t.float().contiguous() for t in m_init]
+        keep += m_init
+        io.m0_in, io.m1_in, io.m2_in = (t.data_ptr() for t in m_init)
+    io.o = o.data_ptr()
+    state = mom = None
+    if return_state:
+        state = (torch.empty(B, H, D, dtype=torch.float32, device=dev),
+                 torch.empty(B, D, H, dtype=torch.float32, device=dev),
+                 torch.empty(B, H, D, dtype=torch.float32, device=dev))
+        io.w0_out, io.w1_out, io.w2_out = (t.data_ptr() for t in state)
+    if return_momentum:
+        mom = (torch.empty(B, H, D, dtype=torch.float32, device=dev),
+               torch.empty(B, D, H, dtype=torch.float32, device=dev),
+               torch.empty(B, H, D, dtype=torch.float32, device=dev))
+        io.m0_out, io.m1_out, io.m2_out = (t.data_ptr() for t in mom)
+    with torch.cuda.device(dev):
+        L.check(lib.lact_scan_fwd(C.byref(cfg), C.byref(io), n, kind, start, end, outs, ws.data_ptr(), ws.numel(),
+                                  L.stream_ptr()), "lact_scan_fwd")
+    L.mark_pending(ws)
+    res = [o]
+    if return_state:
+        res.extend(state)
+    if return_momentum:
+        res.extend(mom)
+    return res[0] if len(res) == 1 else tuple(res)
+
+
+# ----------------------------------------------------------------------------------------------
+# chunk drivers, reference signatures
+# ----------------------------------------------------------------------------------------------
+def block_causal_lact_swiglu(w0, w1, w2, q, k, v, lr0, lr1, lr2, chunk_size: int = 2048, use_muon: bool = False,
+                             momentum: torch.Tensor = None):
+    """lact_llm/lact_model/ttt_operation.py:69-214: causal apply-then-update recurrence, post-norm,
+    Newton-Schulz per matrix, renorm with eps outside the norm.  Returns o [b, l, dv]."""
+    return scan(w0, w1, w2, q, k, v, lr0, lr1, lr2, P.causal_program(k.shape[1], chunk_size), momentum=momentum,
+                use_muon=use_muon, renorm=L.RENORM_EPS_OUTSIDE)
+
+
+def prenorm_block_causal_lact_swiglu(w0, w1, w2, q, k, v, lr0, lr1, lr2, chunk_size: int = 2048,
+                                     use_muon: bool = False, momentum: torch.Tensor = None):
+    """lact_llm/lact_model/ttt_operation.py:217-364: as above with an un-normalised master copy."""
+    return scan(w0, w1, w2, q, k, v, lr0, lr1, lr2, P.causal_program(k.shape[1], chunk_size), momentum=momentum,
+                use_muon=use_muon, renorm=L.RENORM_EPS_OUTSIDE, prenorm=True)
+
+
+def minimal_block_causal_lact_swiglu(w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum: torch.Tensor = None,
+                                     use_muon: bool = True, chunk_size: int = 2048):
+    """minimal_implementations/causal_lact_with_sliding_window_attn.py:83-211 (note the different
+    order and defaults of the last three arguments)."""
+    return block_causal_lact_swiglu(w0, w1, w2, q, k, v, lr0, lr1, lr2, chunk_size=chunk_size, use_muon=use_muon,
+                                    momentum=momentum)
+
+
+def postnorm_block_causal_lact_swiglu_fused_kernel_triton(w0, w1, w2, q, k, v, lr0, lr1, lr2, chunk_size: int = 2048,
+                                                          use_muon: bool = False, momentum: torch.Tensor = None):
+    """lact_llm/lact_model/ttt_operation_fused_kernel.py:66-186: Newton-Schulz on the concatenated
+    [2H, D] gradient, renorm with eps inside the square root."""
+    return scan(w0, w1, w2, q, k, v, lr0, lr1, lr2, P.causal_program(k.shape[1], chunk_size), momentum=momentum,
+                use_muon=use_muon, ns_concat=True, renorm=L.RENORM_EPS_INSIDE)
+
+
+def prenorm_block_causal_lact_swiglu_fused_kernel_triton(w0, w1, w2, q, k, v, lr0, lr1, lr2, chunk_size: int = 2048,
+                                                         use_muon: bool = False, momentum: torch.Tensor = None):
+    """lact_llm/lact_model/ttt_operation_fused_kernel.py:189-316: fp32 master, bf16 normalised copy."""
+    return scan(w0, w1, w2, q, k, v, lr0, lr1, lr2, P.causal_program(k.shape[1], chunk_size), momentum=momentum,
+                use_muon=use_muon, ns_concat=True, renorm=L.RENORM_EPS_OUTSIDE, prenorm=True, prenorm_bf16=True)
+
+
+def bidirectional_lact_swiglu(w0, w1, w2, q, k, v, lr0, lr1, lr2, use_muon: bool = True) -> torch.Tensor:
+    """minimal_implementations/bidirectional_lact_layer.py:73-160, including its behaviour with
+    Muon: w <- renorm(NS(dw) + dw)."""
+    return scan(w0, w1, w2, q, k, v, lr0, lr1, lr2, P.bidirectional_program(k.shape[1]), use_muon=use_muon,
+                renorm=L.RENORM_EPS_OUTSIDE, overwrite_quirk=True)
+
+
+def fast_weight_swish_glu_weight_norm_mini_batch_apply(w0, w1, w2, q, k, v, lr0, lr1, lr2, ttt_ua_order: list,
+                                                       muon_update_steps: int = 0):
+    """lact_nvs/lact_ttt.py:70-147.  NVS layout: w0, w2 [b, d, dh], w1 [b, dh, d].  Returns
+    (output, w0, w1, w2) with the weights in the same layout (fp32)."""
+    steps, out_len = P.operator_list_program([tuple(op) for op in ttt_ua_order], k.shape[1])
+    t = lambda w: w.transpose(1, 2)
+    o, a, b, c = scan(t(w0), t(w1), t(w2), q, k, v, lr0, lr1, lr2, steps, out_len=out_len, use_muon=True,
+                      ns_steps=int(muon_update_steps), ns_const_coeffs=True, ns_gram_right=True,
+                      renorm=L.RENORM_EPS_OUTSIDE, return_state=True)
+    return o, t(a).contiguous(), t(b).contiguous(), t(c).contiguous()
+
+
+def ar_fast_weight_swish_glu_weight_norm_mini_batch(w0, w1, w2, q, k, v, lr0, lr1, lr2, w_scale: float,
+                                                    num_repeat: int = 1, mini_batch_size: int = -1,
+                                                    update_length: int = -1, update_every: int = -1,
+                                                    use_moun: bool = False, num_moun_iters: int = 3,
+                                                    weight_norm: bool = True):
+    """lact_ar_video/minVid/models/blocks/ar_lact_swa_repeat.py:22-168.  Returns (o, w0, w1, w2)."""
+    steps = P.ar_train_program(k.shape[1], mini_batch_size, update_length, update_every, num_repeat)
+    return scan(w0, w1, w2, q, k, v, lr0, lr1, lr2, steps, use_muon=use_moun, ns_steps=num_moun_iters,
+                ns_const_coeffs=True, renorm=L.RENORM_EPS_OUTSIDE if weight_norm else L.RENORM_NONE,
+                w_scale=w_scale, return_state=True)
+
+
+def ar_fast_weight_swish_glu_weight_norm_mini_batch_with_momentum(
+        w0, w1, w2, q, k, v, lr0, lr1, lr2, w_scale: float, num_repeat: int = 1, mini_batch_size: int = -1,
+        update_length: int = -1, update_every: int = -1, use_moun: bool = False, num_moun_iters: int = 3,
+        weight_norm: bool = True, fw_momentum: torch.Tensor = None, use_momentum: bool = False):
+    """lact_ar_video/minVid/models/blocks/ar_lact_swa_repeat_sp.py:27-193 (one pass; `num_repeat`
+    is accepted and ignored, as in the reference)."""
+    steps = P.ar_train_program(k.shape[1], mini_batch_size, update_length, update_every, 1)
+    return scan(w0, w1, w2, q, k, v, lr0, lr1, lr2, steps, momentum=fw_momentum if use_momentum else None,
+                use_muon=use_moun, ns_steps=num_moun_iters, ns_const_coeffs=True,
+                renorm=L.RENORM_EPS_OUTSIDE if weight_norm else L.RENORM_NONE, w_scale=w_scale, return_state=True)
+
+
+def ar_fast_weight_swish_glu_weight_norm_mini_batch_inference(w0, w1, w2, q, k, v, lr0, lr1, lr2, w_scale: float,
+                                                              num_repeat: int = 1, mini_batch_size: int = -1,
+                                                              do_update: bool = False, use_moun: bool = False,
+                                                              num_moun_iters: int = 3, weight_norm: bool = True):
+    """lact_ar_video/minVid/models/blocks/ar_lact_swa_repeat.py:171-296.  Returns (o, w0, w1, w2)."""
+    steps = P.ar_inference_program(k.shape[1], mini_batch_size, do_update, num_repeat)
+    return scan(w0, w1, w2, q, k, v, lr0, lr1, lr2, steps, use_muon=use_moun, ns_steps=num_moun_iters,
+                ns_const_coeffs=True, renorm=L.RENORM_EPS_OUTSIDE if weight_norm else L.RENORM_NONE,
+                w_scale=w_scale, return_state=True)
+
+
+def ar_fast_weight_swish_glu_weight_norm_mini_batch_inference_with_momentum(
+        w0, w1, w2, q, k, v, lr0, lr1, lr2, w_scale: float, num_repeat: int = 1, mini_batch_size: int = -1,
+        do_update: bool = False, use_moun: bool = False, num_moun_iters: int = 3, weight_norm: bool = True,
+        fw_momentum: torch.Tensor = None, dw0_momentum: torch.Tensor = None, dw1_momentum: torch.Tensor = None,
+        dw2_momentum: torch.Tensor = None, use_momentum: bool = False):
+    """lact_ar_video/minVid/models/blocks/ar_lact_swa_repeat_sp.py:196-339.  Returns
+    (o, w0, w1, w2, dw0_momentum, dw1_momentum, dw2_momentum); the momentum entries are None
+    when momentum is off and none was passed in."""
+    steps = P.ar_inference_program(k.shape[1], mini_batch_size, do_update, num_repeat)
+    m_init = None
+    if use_momentum and dw0_momentum is not None:
+        m_init = (dw0_momentum, dw1_momentum, dw2_momentum)
+    res = scan(w0, w1, w2, q, k, v, lr0, lr1, lr2, steps, momentum=fw_momentum if use_momentum else None,
+               m_init=m_init, use_muon=use_moun, ns_steps=num_moun_iters, ns_const_coeffs=True,
+               renorm=L.RENORM_EPS_OUTSIDE if weight_norm else L.RENORM_NONE, w_scale=w_scale, return_state=True,
+               return_momentum=use_momentum and do_update)
+    if use_momentum and do_update:
+        return res
+    o, a, b, c = res
+    if use_momentum:  # no update ran: the state passes through (zeros if none was given)
+        if dw0_momentum is None:
+            dw0_momentum, dw1_momentum, dw2_momentum = (torch.zeros_like(t) for t in (a, b, c))
+        return o, a, b, c, dw0_momentum, dw1_momentum, dw2_momentum
+    return o, a, b, c, dw0_momentum, dw1_momentum, dw2_momentum
+
+
+# ----------------------------------------------------------------------------------------------
+# fused sub-ops, reference signatures
+# ----------------------------------------------------------------------------------------------
+def _bf16_contig(t: torch.Tensor, name: str) -> torch.Tensor:
+    if t.dtype != BF16:
+        raise AssertionError(f"{name} must be bfloat16")  # the reference launchers assert bf16 inputs
+    return t.contiguous()
+
+
+def fused_swiglu_ffn_fwd(W0_W2: torch.Tensor, W1: torch.Tensor, X: torch.Tensor) -> torch.Tensor:
+    """lact_llm/lact_model/lact_triton_kernels/lact_swiglu_ffn.py:79-96: W0_W2 [B, 2H, D],
+    W1 [B, D, H], X [B, N, D] (bf16) -> [B, N, D]."""
+    dev = _need_cuda(W0_W2, W1, X)
+    W0_W2, W1, X = _bf16_contig(W0_W2, "W0_W2"), _bf16_contig(W1, "W1"), _bf16_contig(X, "X")
+    B, N, D = X.shape
+    H = W0_W2.shape[1] // 2
+    assert W0_W2.shape == (B, 2 * H, D) and W1.shape == (B, D, H)
+    out = torch.empty(B, N, D, dtype=BF16, device=dev)
+    lib = L.lib()
+    need = C.c_size_t(0)
+    L.check(lib.lact_swiglu_ffn_workspace_bytes(B, N, D, H, C.byref(need)), "lact_swiglu_ffn_workspace_bytes")
+    ws = L.workspace(need.value, dev)
+    with torch.cuda.device(dev):
+        L.check(lib.lact_swiglu_ffn_fwd(W0_W2.data_ptr(), W1.data_ptr(), X.data_ptr(), out.data_ptr(), B, N, D, H,
+                                        ws.data_ptr(), ws.numel(), L.stream_ptr()), "lact_swiglu_ffn_fwd")
+    L.mark_pending(ws)
+    return out
+
+
+def fused_lact_swiglu_ffn_fast_weight_grads(W0_W2, W1, K, V, lr0, lr1, lr2):
+    """lact_llm/lact_model/lact_triton_kernels/lact_fw_grad.py:159-175: returns (DW0_DW2
+    [B, 2H, D], DW1 [B, D, H]) in bf16; lr0/1/2 are [B, N]."""
+    dev = _need_cuda(W0_W2, W1, K, V, lr0, lr1, lr2)
+    W0_W2, W1 = _bf16_contig(W0_W2, "W0_W2"), _bf16_contig(W1, "W1")
+    K, V = _bf16_contig(K, "K"), _bf16_contig(V, "V")
+    B, N, D = K.shape
+    H = W0_W2.shape[1] // 2
+    lr0, lr1, lr2 = (_vec(t, B, N, "lr") for t in (lr0, lr1, lr2))
+    if not (lr0.dtype == lr1.dtype == lr2.dtype):
+        lr0, lr1, lr2 = lr0.float(), lr1.float(), lr2.float()
+    dw02 = torch.empty(B, 2 * H, D, dtype=BF16, device=dev)
+    dw1 = torch.empty(B, D, H, dtype=BF16, device=dev)
+    lib = L.lib()
+    need = C.c_size_t(0)
+    L.check(lib.lact_fw_grad_workspace_bytes(B, N, D, H, C.byref(need)), "lact_fw_grad_workspace_bytes")
+    ws = L.workspace(need.value, dev)
+    with torch.cuda.device(dev):
+        L.check(lib.lact_fw_grad(W0_W2.data_ptr(), W1.data_ptr(), K.data_ptr(), V.data_ptr(), lr0.data_ptr(),
+                                 lr1.data_ptr(), lr2.data_ptr(), L.dtype_code(lr0), dw02.data_ptr(), dw1.data_ptr(),
+                                 B, N, D, H, ws.data_ptr(), ws.numel(), L.stream_ptr()), "lact_fw_grad")
+    L.mark_pending(ws)
+    return dw02, dw1
+
+
+def zeropower_via_newtonschulz5(G: torch.Tensor, steps: Optional[int] = None) -> torch.Tensor:
+    """Newton-Schulz orthogonalisation in bf16.  `steps=None`: the tuned 5-step schedule of
+    lact_llm/lact_model/ttt_operation.py:30-66; `steps=int`: the constant-coefficient variant of
+    lact_nvs/lact_ttt.py:32-67.  G: [b, r, c], any float dtype -> bf16 [b, r, c]."""
+    assert len(G.shape) == 3
+    dev = _need_cuda(G)
+    if G.dtype not in (torch.float32, BF16):
+        G = G.float()
+    G = G.contiguous()
+    B, R, Cc = G.shape
+    x = torch.empty(B, R, Cc, dtype=BF16, device=dev)
+    lib = L.lib()
+    need = C.c_size_t(0)
+    L.check(lib.lact_newton_schulz_workspace_bytes(B, R, Cc, C.byref(need)), "lact_newton_schulz_workspace_bytes")
+    ws = L.workspace(need.value, dev)
+    with torch.cuda.device(dev):
+        L.check(lib.lact_newton_schulz(G.data_ptr(), L.dtype_code(G), x.data_ptr(), B, R, Cc,
+                                       5 if steps is None else int(steps), int(steps is not None), ws.data_ptr(),
+                                       ws.numel(), L.stream_ptr()), "lact_newton_schulz")
+    L.mark_pending(ws)
+    return x
+
+
+def l2_norm_add_fused(x, x_add, tgt_scale, eps: float = 1e-5, tgt_dtype=None) -> torch.Tensor:
+    """lact_llm/lact_model/lact_triton_kernels/l2norm_triton_kernels.py:419-427."""
+    dev = _need_cuda(x, x_add, tgt_scale)
+    tgt_dtype = x.dtype if tgt_dtype is None else tgt_dtype
+    if tgt_dtype not in (torch.float32, BF16):
+        raise TypeError("tgt_dtype must be float32 or bfloat16")
+    x, x_add = x.contiguous(), x_add.contiguous()
+    B, T, D = x.shape
+    if tgt_scale.dim() == 3:
+        tgt_scale = tgt_scale.squeeze(-1)
+    sc = tgt_scale.float().contiguous()
+    y = torch.empty(B, T, D, dtype=tgt_dtype, device=dev)
+    with torch.cuda.device(dev):
+        L.check(L.lib().lact_l2_norm_add(x.data_ptr(), L.dtype_code(x), x_add.data_ptr(), L.dtype_code(x_add),
+                                         sc.data_ptr(), y.data_ptr(), L.dtype_code(y), B, T, D, float(eps),
+                                         L.stream_ptr()), "lact_l2_norm_add")
+    return y
+
+
+def fused_prenorm_update_with_momentum_and_l2_norm(x_main, dx, dx_momentum, momentum_mu, tgt_scale, eps: float = 1e-5):
+    """lact_llm/lact_model/lact_triton_kernels/triton_prenorm_update_with_momentum.py:379-401.
+    Returns (y_main fp32, updated_momentum fp32, y_normalized bf16)."""
+    dev = _need_cuda(x_main, dx, dx_momentum, momentum_mu, tgt_scale)
+    B, T, D = x_main.shape
+    x = x_main.float().contiguous()
+    m = dx_momentum.float().contiguous()
+    dxb = dx.to(BF16).contiguous()
+    mu = momentum_mu.float().contiguous()
+    sc = tgt_scale.float().contiguous()
+    xo, mo = torch.empty_like(x), torch.empty_like(m)
+    yo = torch.empty(B, T, D, dtype=BF16, device=dev)
+    with torch.cuda.device(dev):
+        L.check(L.lib().lact_prenorm_momentum_l2norm(x.data_ptr(), dxb.data_ptr(), m.data_ptr(), mu.data_ptr(),
+                                                     sc.data_ptr(), xo.data_ptr(), mo.data_ptr(), yo.data_ptr(), B, T,
+                                                     D, float(eps), L.stream_ptr()), "lact_prenorm_momentum_l2norm")
+    return xo, mo, yo
+
+
+def bmm_bf16(a: torch.Tensor, b: torch.Tensor, a_mn_major: bool = False, b_mn_major: bool = False,
+             out_dtype=torch.float32) -> torch.Tensor:
+    """c = A B^T on the tcgen05 engine (test hook).  a: [batch, M, K] or, MN-major, [batch, K, M];
+    b: [batch, N, K] or [batch, K, N]."""
+    dev = _need_cuda(a, b)
+    a, b = _bf16_contig(a, "a"), _bf16_contig(b, "b")
+    batch = a.shape[0]
+    M, K = (a.shape[2], a.shape[1]) if a_mn_major else (a.shape[1], a.shape[2])
+    N = b.shape[2] if b_mn_major else b.shape[1]
+    c = torch.empty(batch, M, N, dtype=out_dtype, device=dev)
+    status = torch.zeros(64, dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        L.check(L.lib().lact_bmm_bf16(a.data_ptr(), int(a_mn_major), b.data_ptr(), int(b_mn_major), c.data_ptr(),
+                                      L.dtype_code(c), batch, M, N, K, status.data_ptr(), L.stream_ptr()),
+                "lact_bmm_bf16")
+    st = int(status[0].item())
+    if st != 0:
+        raise L.LactError(f"device status {st}")
+    return c
