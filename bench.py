@@ -1,0 +1,348 @@
+"""Benchmark of the LaCT TTT-layer forward at the 760M-LLM shape on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+One "step" = one forward of the causal fused post-norm TTT op
+(`postnorm_block_causal_lact_swiglu_fused_kernel_triton` signature) over one batch:
+batch 8 x 4 heads (B = 32 merged), 32768 tokens, head dim = fast-weight hidden = 384, chunk 2048,
+bf16 q/k/v/lr, fp32 fast weights, per-chunk momentum, 5-step Newton-Schulz, L2 renorm.
+Synthetic seeded inputs (no dataset exists for this op).  Multi-GPU is weak scaling: every rank
+runs the same per-GPU workload on its own data, no collective on the data path.
+
+Prints ONE JSON line (rank 0).  `value` = tokens/s with inputs resident in HBM; `e2e` = the same
+through the public Python API with pinned host buffers (H2D of all inputs and D2H of the output
+inside the timed region); `roofline` = the dominant kernel class against the measured bf16 peak;
+`cpu_baseline` = the CPU oracle (a port of the reference arithmetic) on a bounded sample.
+`--impl reference` times that CPU port alone with all host threads.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+BF16 = torch.bfloat16
+CFG = dict(batch=8, heads=4, L=32768, D=384, H=384, chunk=2048, ns_steps=5)
+METRIC = "ttt_layer_fwd_tokens_per_s_760M_shape"
+
+
+# ------------------------------------------------------------------------------------------ helpers
+def algorithmic_flops(B, L, D, H, C, ns_steps):
+    """Algorithmic FLOPs of one forward (recomputation and elementwise work not counted):
+    apply 6DH per token, update 12DH per updated token, Newton-Schulz steps*(4 m^2 n + 2 m^3) per
+    matrix, on the concatenated [2H, D] gradient and on dw1, once per updated chunk."""
+    n_upd = len(range(0, L - C, C))
+    ns = lambda r, c: ns_steps * (4 * min(r, c) ** 2 * max(r, c) + 2 * min(r, c) ** 3)
+    per_head = 6 * D * H * L + 12 * D * H * n_upd * C + n_upd * (ns(2 * H, D) + ns(D, H))
+    return B * per_head
+
+
+def class_flops(name, B, D, H, C, ns_steps):
+    """Algorithmic FLOPs of ONE launch of a kernel class at the benchmark shape."""
+    m1, n1 = min(D, H), max(D, H)
+    m2, n2 = min(2 * H, D), max(2 * H, D)
+    return {
+        "gemm_swiglu_gate": 4 * D * H * C * B,
+        "gemm_down_proj": 2 * D * H * C * B,
+        "gemm_fwgrad_pointwise": 6 * D * H * C * B,
+        "gemm_fwgrad_contract": 6 * D * H * C * B,
+        "gemm_ns_gram": 2 * B * (m1 * m1 * n1 + m2 * m2 * n2),
+        "gemm_ns_poly": 2 * B * (m1 ** 3 + m2 ** 3),
+        "gemm_ns_update": 2 * B * (m1 * m1 * n1 + m2 * m2 * n2),
+    }.get(name)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            d = json.load(fh)
+        return dict(bf16_burst=d.get("bf16_tflops"), bf16_sustained=d.get("bf16_tflops_sustained"),
+                    hbm_gbs=d.get("hbm_gbs"), source="measured")
+    return dict(bf16_burst=1590.0, bf16_sustained=1400.0, hbm_gbs=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for nm, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        sm_sorted = sorted(sm)
+        return {"sm_mhz": sm_sorted[len(sm_sorted) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def make_inputs(device, seed, pinned_host=False):
+    """Seeded synthetic inputs of the benchmark shape, generated on `device` in slabs."""
+    B, L, D, H = CFG["batch"] * CFG["heads"], CFG["L"], CFG["D"], CFG["H"]
+    g = torch.Generator(device=device).manual_seed(seed)
+    rn = lambda *s: torch.randn(*s, device=device, generator=g)
+    out = {}
+    for name in ("q", "k", "v"):
+        t = torch.empty(B, L, D, dtype=BF16, device=device)
+        for b in range(B):
+            x = rn(L, D)
+            if name != "v":
+                x = x / x.norm(dim=-1, keepdim=True)
+            t[b] = x.to(BF16)
+        out[name] = t
+    out["w0"] = rn(B, H, D) / D ** 0.5
+    out["w1"] = rn(B, D, H) / H ** 0.5
+    out["w2"] = rn(B, H, D) / D ** 0.5
+    for name in ("lr0", "lr1", "lr2"):
+        out[name] = torch.nn.functional.softplus(rn(B, L, 1) - 2.0).to(BF16)
+    out["momentum"] = torch.sigmoid(rn(B, L, 1))
+    return out
+
+
+ARG_ORDER = ("w0", "w1", "w2", "q", "k", "v", "lr0", "lr1", "lr2")
+
+
+def run_step(lb, t):
+    return lb.postnorm_block_causal_lact_swiglu_fused_kernel_triton(
+        *[t[n] for n in ARG_ORDER], chunk_size=CFG["chunk"], use_muon=True, momentum=t["momentum"])
+
+
+# ------------------------------------------------------------------------------------------ CPU arm
+def cpu_reference_sample(steps: int, warmup: int, threads: int):
+    """Times the CPU port of the reference's fused arithmetic (oracle) on a bounded sample:
+    one batch element (4 heads) x 8192 tokens (4 chunks) of the benchmark workload per step."""
+    from oracle import lact_oracle as orc
+    torch.set_num_threads(threads)
+    Ls, heads = 8192, CFG["heads"]
+    i = orc.make_inputs(heads, Ls, CFG["D"], CFG["H"], seed=0, act_dtype=BF16, lr_dtype=BF16)
+    fn = lambda: orc.block_causal_lact_swiglu_fused(i["w0"], i["w1"], i["w2"], i["q"], i["k"], i["v"], i["lr0"],
+                                                    i["lr1"], i["lr2"], chunk_size=CFG["chunk"], use_muon=True,
+                                                    momentum=i["momentum"])
+    for _ in range(warmup):
+        fn()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        fn()
+    dt = (time.perf_counter() - t0) / steps
+    sample = f"1 batch element ({heads} heads) x {Ls} tokens ({Ls // CFG['chunk']} chunks) per step"
+    return Ls / dt, dt, sample
+
+
+def reference_arm(args, rank):
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    steps, warmup = max(1, min(args.steps, 5)), max(1, min(args.warmup, 1))
+    val, dt, sample = cpu_reference_sample(steps, warmup, threads)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": steps, "warmup": warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+        "note": "CPU port (oracle) of the reference's fused-path arithmetic; the reference tree is Python and is "
+                "not present on the GPU box",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n):
+    return {"workload": "causal LaCT TTT layer forward, 760M-LLM shape: batch 8 x seq 32768, 4 heads of dim 384, "
+                        "fast-weight hidden 384, chunk 2048, apply-then-update, momentum + Muon(5) + L2 renorm, "
+                        "bf16 q/k/v/lr, fp32 fast weights",
+            "signature": "postnorm_block_causal_lact_swiglu_fused_kernel_triton",
+            "batch_per_gpu": CFG["batch"], "global_batch": CFG["batch"] * n, "seq_len": CFG["L"],
+            "parallelism": f"(batch x head) partition, {n} rank(s), no collective",
+            "l2": "inputs (3.2 GB per step) exceed L2; no explicit flush"}
+
+
+# ------------------------------------------------------------------------------------------ main arm
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        reference_arm(args, rank)
+        return
+    warmup = max(3, args.warmup)
+    steps = max(1, args.steps)
+
+    import torch.distributed as dist
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    from lact_b200 import build
+    if rank == 0:
+        build.build()
+    if world > 1:
+        dist.barrier()
+    import lact_b200
+    from lact_b200 import _lib as LL
+
+    B, L, D, H, C = CFG["batch"] * CFG["heads"], CFG["L"], CFG["D"], CFG["H"], CFG["chunk"]
+    tokens_per_step = CFG["batch"] * L
+    t = make_inputs(dev, seed=rank)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(warmup):
+        run_step(lact_b200, t)
+    lact_b200.synchronize_and_check()
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = LL.launch_count()
+    with ClockSampler(local_rank) as clocks:
+        ev0.record()
+        for _ in range(steps):
+            run_step(lact_b200, t)
+        ev1.record()
+        barrier()
+    launches = LL.launch_count() - launches0
+    lact_b200.synchronize_and_check()
+    ms = torch.tensor([ev0.elapsed_time(ev1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_per_step = float(ms.item()) / steps
+    value = world * tokens_per_step / (ms_per_step * 1e-3)
+
+    # per-kernel-class durations (CUDA events around every launch, on the launching stream), second pass
+    peaks = measured_peaks()
+    LL.profile_enable(True)
+    prof_steps = min(steps, 3)
+    for _ in range(prof_steps):
+        run_step(lact_b200, t)
+    torch.cuda.synchronize()
+    prof = LL.profile_read()
+    LL.profile_enable(False)
+    total_prof = sum(v[0] for v in prof.values())
+    top = max((k for k in prof if class_flops(k, B, D, H, C, CFG["ns_steps"])), key=lambda k: prof[k][0])
+    top_ms = prof[top][0] / prof[top][1]
+    achieved = class_flops(top, B, D, H, C, CFG["ns_steps"]) / (top_ms * 1e-3) / 1e12
+    flops = algorithmic_flops(B, L, D, H, C, CFG["ns_steps"])
+    step_tflops = flops / (ms_per_step * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "kernel": top, "achieved": achieved, "peak": peaks["bf16_sustained"],
+                "unit": "TFLOP/s", "frac": achieved / peaks["bf16_sustained"], "traffic": None,
+                "peak_source": peaks["source"] + " (sustained cuBLAS bf16)",
+                "kernel_share_of_step": prof[top][0] / total_prof,
+                "classes": {k: {"ms_per_launch": v[0] / v[1], "launches_per_step": v[1] / prof_steps,
+                                "share": v[0] / total_prof} for k, v in sorted(prof.items())}}
+
+    # end to end through the public API with pinned host buffers
+    e2e = None
+    if not args.no_e2e:
+        host = {k: v.cpu().pin_memory() for k, v in t.items()}
+        h2d = sum(v.numel() * v.element_size() for v in host.values())
+        out_host = torch.empty(B, L, D, dtype=BF16).pin_memory()
+        d2h = out_host.numel() * out_host.element_size()
+        dev_bufs = {k: torch.empty_like(v, device=dev) for k, v in host.items()}
+        n_e2e = max(2, min(steps, 4))
+
+        def e2e_step():
+            for k_, v_ in host.items():
+                dev_bufs[k_].copy_(v_, non_blocking=True)
+            o = run_step(lact_b200, dev_bufs)
+            out_host.copy_(o, non_blocking=True)
+
+        e2e_step()
+        barrier()
+        ev0.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        ev1.record()
+        barrier()
+        ems = torch.tensor([ev0.elapsed_time(ev1)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(ems, op=dist.ReduceOp.MAX)
+        e2e = {"value": world * tokens_per_step / (float(ems.item()) / n_e2e * 1e-3), "unit": "tokens/s",
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": n_e2e}
+        del host, dev_bufs, out_host
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        threads = os.cpu_count() or 1
+        val, dt, sample = cpu_reference_sample(2, 1, threads)
+        cpu = {"value": val, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
+            "step_tflops_per_gpu": step_tflops, "frac_of_bf16_peak_burst": step_tflops / peaks["bf16_burst"],
+            "frac_of_bf16_peak_sustained": step_tflops / peaks["bf16_sustained"],
+            "algorithmic_flops_per_step_per_gpu": flops,
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches,
+            "clocks": clocks.summary(),
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

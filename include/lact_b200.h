@@ -90,6 +90,19 @@ int lact_version(void);
 /* Human-readable text for a return code.  No counterpart in the reference. */
 const char *lact_error_string(int code);
 
+/* Number of kernels this library has launched in the process so far.  No counterpart in the
+ * reference. */
+int64_t lact_launch_count(void);
+
+/* Per-kernel-class timing (a measurement aid; no counterpart in the reference).  While enabled,
+ * every kernel launch is bracketed by two CUDA events on its stream.  lact_profile_read waits
+ * for the recorded events, writes the summed milliseconds and launch counts of each class into
+ * arrays of lact_profile_num_classes() entries, and clears the records. */
+int lact_profile_enable(int enable);
+int lact_profile_num_classes(void);
+const char *lact_profile_class_name(int cls);
+int lact_profile_read(double *ms, int64_t *launches);
+
 /* Reads the device status word of a workspace after synchronising `stream`.
  * Returns 0 (ok), a positive device status (101 = a bounded wait timed out) or LACT_ERR_CUDA. */
 int lact_read_status(const void *workspace, void *stream);

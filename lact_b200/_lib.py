@@ -41,6 +41,14 @@ def _declare(lib: C.CDLL) -> None:
     lib.lact_error_string.restype = C.c_char_p
     lib.lact_error_string.argtypes = [C.c_int]
     lib.lact_read_status.argtypes = [vp, vp]
+    lib.lact_launch_count.restype = C.c_int64
+    lib.lact_profile_enable.argtypes = [C.c_int]
+    lib.lact_profile_enable.restype = C.c_int
+    lib.lact_profile_num_classes.restype = C.c_int
+    lib.lact_profile_class_name.argtypes = [C.c_int]
+    lib.lact_profile_class_name.restype = C.c_char_p
+    lib.lact_profile_read.argtypes = [C.POINTER(C.c_double), C.POINTER(C.c_int64)]
+    lib.lact_profile_read.restype = C.c_int
     lib.lact_scan_workspace_bytes.argtypes = [C.POINTER(ScanConfig), i32, C.POINTER(i32), C.POINTER(i64),
                                               C.POINTER(i64), szp]
     lib.lact_scan_fwd.argtypes = [C.POINTER(ScanConfig), C.POINTER(ScanIO), i32, C.POINTER(i32), C.POINTER(i64),
@@ -141,3 +149,21 @@ def synchronize_and_check() -> None:
         if _pending.get(key):
             read_status(buf)
             _pending[key] = False
+
+
+def launch_count() -> int:
+    """Kernels launched by the library in this process so far."""
+    return int(lib().lact_launch_count())
+
+
+def profile_enable(on: bool) -> None:
+    lib().lact_profile_enable(int(on))
+
+
+def profile_read() -> dict:
+    """{class name: (total ms, launches)} for launches recorded since the last read."""
+    n = lib().lact_profile_num_classes()
+    ms = (C.c_double * n)()
+    cnt = (C.c_int64 * n)()
+    check(lib().lact_profile_read(ms, cnt), "lact_profile_read")
+    return {lib().lact_profile_class_name(i).decode(): (ms[i], int(cnt[i])) for i in range(n) if cnt[i]}

@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
@@ -70,6 +71,56 @@ int make_operand(CUtensorMap* map, OperandInfo* info, const Mat& m, int mn_major
 }
 
 // ------------------------------------------------------------------------------------------
+// launch accounting and optional per-kernel-class timing
+// ------------------------------------------------------------------------------------------
+enum KernelClass : int {
+  kClsPrepare = 0, kClsGate, kClsDown, kClsGradPointwise, kClsGradContract, kClsMomentumMean, kClsNsPrepare,
+  kClsNsGram, kClsNsPoly, kClsNsUpdate, kClsRenorm, kClsOther, kNumClasses
+};
+const char* const kClassNames[kNumClasses] = {
+    "prepare_weights", "gemm_swiglu_gate", "gemm_down_proj", "gemm_fwgrad_pointwise", "gemm_fwgrad_contract",
+    "momentum_mean", "ns_prepare", "gemm_ns_gram", "gemm_ns_poly", "gemm_ns_update", "add_renorm", "other"};
+
+struct Profiler {
+  std::mutex mu;
+  std::atomic<bool> enabled{false};
+  std::atomic<int64_t> launches{0};
+  struct Rec { cudaEvent_t a, b; int cls; };
+  std::vector<Rec> recs;
+  std::vector<cudaEvent_t> pool;
+  cudaEvent_t get() {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!pool.empty()) { cudaEvent_t e = pool.back(); pool.pop_back(); return e; }
+    cudaEvent_t e = nullptr;
+    cudaEventCreate(&e);
+    return e;
+  }
+};
+Profiler g_prof;
+
+// Counts one kernel launch; when timing is enabled, brackets it with two events on its stream.
+struct KernelScope {
+  int cls;
+  cudaStream_t stream;
+  cudaEvent_t a = nullptr, b = nullptr;
+  KernelScope(int cls_, cudaStream_t s) : cls(cls_), stream(s) {
+    g_prof.launches.fetch_add(1, std::memory_order_relaxed);
+    if (g_prof.enabled.load(std::memory_order_relaxed)) {
+      a = g_prof.get();
+      b = g_prof.get();
+      if (a) cudaEventRecord(a, stream);
+    }
+  }
+  ~KernelScope() {
+    if (a && b) {
+      cudaEventRecord(b, stream);
+      std::lock_guard<std::mutex> lock(g_prof.mu);
+      g_prof.recs.push_back({a, b, cls});
+    }
+  }
+};
+
+// ------------------------------------------------------------------------------------------
 // launch helpers
 // ------------------------------------------------------------------------------------------
 #define LACT_TRY(expr)                   \
@@ -99,7 +150,7 @@ int check_device() {
 
 // Launches the first `nprob` problems of `args` (grid.z = nprob).
 template <class Op, int NPROB>
-int launch_gemm(const GemmArgs<Op, NPROB>& args, cudaStream_t stream, int nprob = NPROB) {
+int launch_gemm(const GemmArgs<Op, NPROB>& args, cudaStream_t stream, int cls, int nprob = NPROB) {
   auto kernel = umma_gemm_kernel<Op, NPROB>;
   constexpr uint32_t smem = gemm_smem_bytes<Op>();
   static std::mutex mu;
@@ -122,6 +173,7 @@ int launch_gemm(const GemmArgs<Op, NPROB>& args, cudaStream_t stream, int nprob 
   }
   if (batch > 65535) return LACT_ERR_SHAPE;
   dim3 grid(tiles, batch, nprob);
+  KernelScope scope(cls, stream);
   kernel<<<grid, kGemmThreads, smem, stream>>>(args);
   LACT_CUDA(cudaGetLastError());
   return LACT_OK;
@@ -167,7 +219,7 @@ int run_apply(const ApplyArgs& a, int32_t* status, cudaStream_t stream) {
     P.batch = static_cast<int>(a.B);
     P.ep = EpiSwiglu{a.hidden, len * a.H, a.H};
     g.status = status;
-    LACT_TRY(launch_gemm(g, stream));
+    LACT_TRY(launch_gemm(g, stream, kClsGate));
   }
   {
     GemmArgs<OpStore, 1> g;
@@ -179,7 +231,7 @@ int run_apply(const ApplyArgs& a, int32_t* status, cudaStream_t stream) {
     P.batch = static_cast<int>(a.B);
     P.ep = EpiStore{a.out, a.o_bs, a.o_ts, static_cast<int32_t>(a.out_start), 0};
     g.status = status;
-    LACT_TRY(launch_gemm(g, stream));
+    LACT_TRY(launch_gemm(g, stream, kClsDown));
   }
   return LACT_OK;
 }
@@ -227,7 +279,7 @@ int run_grad(const GradArgs& a, int32_t* status, cudaStream_t stream) {
     P.ep = EpiFwGrad{a.lr0, a.lr1, a.lr2, a.lr_f32, static_cast<int32_t>(a.start), a.lr_bs, a.w_scale,
                      a.dy02, len * 2 * a.H, 2 * a.H, static_cast<int32_t>(a.H), a.hid, len * a.H, a.H};
     g.status = status;
-    LACT_TRY(launch_gemm(g, stream));
+    LACT_TRY(launch_gemm(g, stream, kClsGradPointwise));
   }
   {
     // token contraction: [dw0; dw2] = dy02^T k  and  dw1 = v^T hidden
@@ -246,7 +298,7 @@ int run_grad(const GradArgs& a, int32_t* status, cudaStream_t stream) {
     P1.batch = static_cast<int>(a.B);
     P1.ep = EpiDW{a.g1, a.D * a.H, a.H, a.beta, 1, a.g_f32};
     g.status = status;
-    LACT_TRY(launch_gemm(g, stream));
+    LACT_TRY(launch_gemm(g, stream, kClsGradContract));
   }
   return LACT_OK;
 }
@@ -313,9 +365,9 @@ int run_ns_iterations(NsGroup* grp, int ngroups, int steps, int const_coeffs, co
       PC.ep = EpiNs{nxt[gi], nullptr, cur[gi], co[0], 0.f, static_cast<int64_t>(G.m) * G.n, G.n};
     }
     ga.status = gb.status = gc.status = status;
-    LACT_TRY(launch_gemm(ga, stream, ngroups));
-    LACT_TRY(launch_gemm(gb, stream, ngroups));
-    LACT_TRY(launch_gemm(gc, stream, ngroups));
+    LACT_TRY(launch_gemm(ga, stream, kClsNsGram, ngroups));
+    LACT_TRY(launch_gemm(gb, stream, kClsNsPoly, ngroups));
+    LACT_TRY(launch_gemm(gc, stream, kClsNsUpdate, ngroups));
     for (int g = 0; g < ngroups; ++g) std::swap(cur[g], nxt[g]);
   }
   for (int g = 0; g < ngroups; ++g) result[g] = cur[g];
@@ -429,6 +481,7 @@ int validate_scan_config(const lact_scan_config& c) {
 int launch_ns_prepare(const void* src, int src_f32, int64_t src_ms, int ld, int R, int C, int gram_right, bf16* X,
                       int nmat, cudaStream_t stream) {
   const int transpose = (R > C) || (R == C && gram_right);
+  KernelScope scope(kClsNsPrepare, stream);
   ns_prepare_kernel<<<nmat, 512, 0, stream>>>(src, src_f32, src_ms, ld, R, C, transpose, X,
                                               static_cast<int64_t>(R) * C);
   LACT_CUDA(cudaGetLastError());
@@ -456,6 +509,7 @@ int scan_fwd(const lact_scan_config& c, const lact_scan_io& io, int32_t n_steps,
   LACT_CUDA(cudaMemsetAsync(p.status, 0, 256, stream));
   {
     const int64_t rows = B * (2 * H + D);
+    KernelScope scope(kClsPrepare, stream);
     prepare_weights_kernel<<<ceil_div(rows, 8), 256, 0, stream>>>(io.w0, io.w1, io.w2, c.w_dtype == LACT_F32,
                                                                   static_cast<int>(B), static_cast<int>(H),
                                                                   static_cast<int>(D), p.W02, p.W1, p.W02c, p.W1c,
@@ -483,6 +537,7 @@ int scan_fwd(const lact_scan_config& c, const lact_scan_io& io, int32_t n_steps,
     }
     const float* beta = nullptr;
     if (c.use_momentum) {
+      KernelScope scope(kClsMomentumMean, stream);
       momentum_mean_kernel<<<static_cast<int>(B), 256, 0, stream>>>(io.momentum, c.mom_dtype == LACT_F32, c.L,
                                                                     static_cast<int>(start[i]),
                                                                     static_cast<int>(end[i]), p.beta);
@@ -539,6 +594,7 @@ int scan_fwd(const lact_scan_config& c, const lact_scan_io& io, int32_t n_steps,
         r.x_ld = r.x_transposed ? mat_rows : C;
       }
       const int64_t rows = B * R;
+      KernelScope scope(kClsRenorm, stream);
       add_renorm_kernel<<<ceil_div(rows, 8), 256, 0, stream>>>(r);
       LACT_CUDA(cudaGetLastError());
     }
@@ -583,6 +639,37 @@ const char* lact_error_string(int code) {
     case kStatusWaitTimeout: return "device: a bounded barrier wait timed out";
     default: return "unknown code";
   }
+}
+
+int64_t lact_launch_count(void) { return g_prof.launches.load(); }
+
+int lact_profile_enable(int enable) {
+  g_prof.enabled.store(enable != 0);
+  return LACT_OK;
+}
+
+int lact_profile_num_classes(void) { return kNumClasses; }
+
+const char* lact_profile_class_name(int cls) { return (cls >= 0 && cls < kNumClasses) ? kClassNames[cls] : "?"; }
+
+int lact_profile_read(double* ms, int64_t* launches) {
+  if (!ms || !launches) return LACT_ERR_NULL;
+  std::vector<Profiler::Rec> recs;
+  {
+    std::lock_guard<std::mutex> lock(g_prof.mu);
+    recs.swap(g_prof.recs);
+  }
+  for (int i = 0; i < kNumClasses; ++i) { ms[i] = 0.0; launches[i] = 0; }
+  int rc = LACT_OK;
+  for (auto& r : recs) {
+    float t = 0.f;
+    if (cudaEventSynchronize(r.b) != cudaSuccess || cudaEventElapsedTime(&t, r.a, r.b) != cudaSuccess) rc = LACT_ERR_CUDA;
+    ms[r.cls] += t;
+    launches[r.cls] += 1;
+  }
+  std::lock_guard<std::mutex> lock(g_prof.mu);
+  for (auto& r : recs) { g_prof.pool.push_back(r.a); g_prof.pool.push_back(r.b); }
+  return rc;
 }
 
 int lact_read_status(const void* workspace, void* stream) {
@@ -697,6 +784,7 @@ int lact_newton_schulz(const void* g, int32_t g_dtype, void* x, int64_t B, int64
                              static_cast<int>(C), 0, grp.xa, static_cast<int>(B), s));
   const bf16* res = nullptr;
   LACT_TRY(run_ns_iterations(&grp, 1, steps, const_coeffs, &res, status, s));
+  KernelScope scope(kClsOther, s);
   ns_export_kernel<<<static_cast<int>(B), 512, 0, s>>>(res, m * n, static_cast<int>(R), static_cast<int>(C), R > C,
                                                        static_cast<bf16*>(x), R * C);
   LACT_CUDA(cudaGetLastError());
@@ -708,6 +796,7 @@ int lact_l2_norm_add(const void* x, int32_t x_dtype, const void* x_add, int32_t 
   if (!x || !x_add || !scale || !y) return LACT_ERR_NULL;
   if (B < 1 || T < 1 || D < 1) return LACT_ERR_SHAPE;
   const int64_t rows = B * T;
+  KernelScope scope(kClsOther, static_cast<cudaStream_t>(stream));
   l2_norm_add_kernel<<<ceil_div(rows, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       x, x_dtype == LACT_F32, x_add, add_dtype == LACT_F32, static_cast<const float*>(scale), y, y_dtype == LACT_F32,
       rows, static_cast<int>(D), eps);
@@ -721,6 +810,7 @@ int lact_prenorm_momentum_l2norm(const void* x, const void* dx, const void* m, c
   if (!x || !dx || !m || !mu || !scale || !x_out || !m_out || !y_out) return LACT_ERR_NULL;
   if (B < 1 || T < 1 || D < 1) return LACT_ERR_SHAPE;
   const int64_t rows = B * T;
+  KernelScope scope(kClsOther, static_cast<cudaStream_t>(stream));
   prenorm_momentum_kernel<<<ceil_div(rows, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const float*>(x), static_cast<const bf16*>(dx), static_cast<const float*>(m),
       static_cast<const float*>(mu), static_cast<const float*>(scale), static_cast<float*>(x_out),
@@ -744,7 +834,7 @@ int lact_bmm_bf16(const void* a, int32_t a_mn_major, const void* b, int32_t b_mn
   P.M = static_cast<int>(M); P.N = static_cast<int>(N); P.K = static_cast<int>(K); P.batch = static_cast<int>(batch);
   P.ep = EpiStore{c, M * N, N, 0, c_dtype == LACT_F32};
   g.status = status_word;
-  return launch_gemm(g, static_cast<cudaStream_t>(stream));
+  return launch_gemm(g, static_cast<cudaStream_t>(stream), kClsOther);
 }
 
 }  // extern "C"
