@@ -216,14 +216,22 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--batch", type=int, default=None,
+                    help="override the batch size (profiler captures on a small case; not a headline number)")
+    ap.add_argument("--seq-len", type=int, default=None, help="override the sequence length (same caveat)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    reduced = args.batch is not None or args.seq_len is not None
+    if args.batch is not None:
+        CFG["batch"] = args.batch
+    if args.seq_len is not None:
+        CFG["L"] = args.seq_len
     if args.impl == "reference":
         reference_arm(args, rank)
         return
-    warmup = max(3, args.warmup)
+    warmup = args.warmup if reduced else max(3, args.warmup)
     steps = max(1, args.steps)
 
     import torch.distributed as dist
@@ -339,6 +347,8 @@ def main():
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches,
             "clocks": clocks.summary(),
         }
+        if reduced:
+            line["reduced_case"] = "batch/seq overridden for a profiler capture: not the benchmark workload"
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -41,6 +41,7 @@ extern "C" {
 #define LACT_ERR_STEPS -6       /* malformed step list (empty update range, range outside [0, L]) */
 #define LACT_ERR_CUDA -7        /* a CUDA runtime / driver call failed */
 #define LACT_ERR_DEVICE -8      /* device is not sm_100 */
+#define LACT_ERR_STATIC_LIMIT -9 /* lact_swiglu_ffn_fwd_static: scratch need exceeds the static buffer */
 
 /* step kinds of the scan program */
 #define LACT_STEP_APPLY 0
@@ -131,6 +132,31 @@ int lact_scan_fwd(const lact_scan_config *cfg, const lact_scan_io *io, int32_t n
 int lact_swiglu_ffn_workspace_bytes(int64_t B, int64_t N, int64_t D, int64_t H, size_t *bytes_out);
 int lact_swiglu_ffn_fwd(const void *w0w2, const void *w1, const void *x, void *out, int64_t B, int64_t N,
                         int64_t D, int64_t H, void *workspace, size_t workspace_bytes, void *stream);
+
+/* The same computation as lact_swiglu_ffn_fwd for callers that must not allocate and cannot hand
+ * over a workspace.  No counterpart in the reference.
+ *
+ * Who needs it: code that runs where device allocation is off limits -- an inference-server
+ * execution callback or plugin `enqueue` hook whose contract forbids cudaMalloc, a process whose
+ * framework has already reserved the whole device for its own pool, or a latency-critical loop
+ * that cannot afford the implicit device synchronisation of an allocator call.  Such a caller
+ * still passes the operands and the output buffer; the hidden activations [B, N, H] (bf16) go
+ * into a fixed array that is part of the library image.
+ *
+ * Limit: 256 + B * N * H * 2 bytes must fit in lact_static_scratch_bytes() (16 MiB; for example
+ * B = 4, N = 2048, H = 384).  Larger problems return LACT_ERR_STATIC_LIMIT and enqueue nothing.
+ * Every GPU that loads the library holds that array until the process exits.
+ *
+ * The first call on a device looks up the array's device address (once per device, with that
+ * device current); make that first call before starting any stream capture.  The call itself
+ * allocates and frees nothing, on the device or through any library.
+ *
+ * All calls share the one array and it keeps the previous call's contents (the entry point clears
+ * the status word it needs at zero, and overwrites the rest before reading it).  Two calls that
+ * overlap on the GPU -- different streams, or different threads -- race on it: serialise them. */
+size_t lact_static_scratch_bytes(void);
+int lact_swiglu_ffn_fwd_static(const void *w0w2, const void *w1, const void *x, void *out, int64_t B, int64_t N,
+                               int64_t D, int64_t H, void *stream);
 
 /* dw0w2[B, 2H, D], dw1[B, D, H] (bf16) = per-token-lr weighted fast-weight gradient.
  * Replaces fused_lact_swiglu_ffn_fast_weight_grads

@@ -55,6 +55,9 @@ def _declare(lib: C.CDLL) -> None:
                                   C.POINTER(i64), C.POINTER(i64), vp, C.c_size_t, vp]
     lib.lact_swiglu_ffn_workspace_bytes.argtypes = [i64, i64, i64, i64, szp]
     lib.lact_swiglu_ffn_fwd.argtypes = [vp, vp, vp, vp, i64, i64, i64, i64, vp, C.c_size_t, vp]
+    lib.lact_static_scratch_bytes.restype = C.c_size_t
+    lib.lact_swiglu_ffn_fwd_static.argtypes = [vp, vp, vp, vp, i64, i64, i64, i64, vp]
+    lib.lact_swiglu_ffn_fwd_static.restype = C.c_int
     lib.lact_fw_grad_workspace_bytes.argtypes = [i64, i64, i64, i64, szp]
     lib.lact_fw_grad.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, vp, vp, i64, i64, i64, i64, vp, C.c_size_t, vp]
     lib.lact_newton_schulz_workspace_bytes.argtypes = [i64, i64, i64, szp]

@@ -636,6 +636,9 @@ const char* lact_error_string(int code) {
     case LACT_ERR_STEPS: return "malformed step list";
     case LACT_ERR_CUDA: return "a CUDA runtime or driver call failed";
     case LACT_ERR_DEVICE: return "device is not compute capability 10.x (B200)";
+    case LACT_ERR_STATIC_LIMIT:
+      return "problem needs more scratch than the library's built-in static buffer holds (16 MiB): "
+             "use the workspace variant or a smaller B * N * H";
     case kStatusWaitTimeout: return "device: a bounded barrier wait timed out";
     default: return "unknown code";
   }
@@ -725,6 +728,52 @@ int lact_swiglu_ffn_fwd(const void* w0w2, const void* w1, const void* x, void* o
   ApplyArgs a{static_cast<const bf16*>(w0w2), static_cast<const bf16*>(w1), x, N * D, D, 0, N, out, N * D, D, 0,
               reinterpret_cast<bf16*>(static_cast<uint8_t*>(workspace) + 256), B, D, H};
   return run_apply(a, static_cast<int32_t*>(workspace), s);
+}
+
+// ---------------------------------------------------------------- allocation-free variant
+// Scratch for lact_swiglu_ffn_fwd_static.  It lives in the library image: every GPU that loads
+// the library holds these bytes until the process exits.
+#define LACT_STATIC_SCRATCH_BYTES (16u << 20)
+static __device__ __align__(256) unsigned char g_static_scratch[LACT_STATIC_SCRATCH_BYTES];
+
+// Device address of g_static_scratch on the current device, resolved once per device.  In host
+// code the array's name is only a handle for the runtime, never a pointer a kernel may use, so
+// the address is asked for with cudaGetSymbolAddress and that result is what kernels receive.
+static int static_scratch_address(void** out) {
+  static std::mutex mu;
+  static void* addr[64] = {nullptr};
+  int dev = 0;
+  LACT_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return LACT_ERR_DEVICE;
+  std::lock_guard<std::mutex> lock(mu);
+  if (addr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_scratch) != cudaSuccess || p == nullptr)
+      return LACT_ERR_CUDA;
+    addr[dev] = p;
+  }
+  *out = addr[dev];
+  return LACT_OK;
+}
+
+size_t lact_static_scratch_bytes(void) { return LACT_STATIC_SCRATCH_BYTES; }
+
+int lact_swiglu_ffn_fwd_static(const void* w0w2, const void* w1, const void* x, void* out, int64_t B, int64_t N,
+                               int64_t D, int64_t H, void* stream) {
+  if (!w0w2 || !w1 || !x || !out) return LACT_ERR_NULL;
+  LACT_TRY(check_device());
+  size_t need = 0;
+  LACT_TRY(lact_swiglu_ffn_workspace_bytes(B, N, D, H, &need));
+  if (need > LACT_STATIC_SCRATCH_BYTES) return LACT_ERR_STATIC_LIMIT;
+  void* scratch = nullptr;
+  LACT_TRY(static_scratch_address(&scratch));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // the array keeps whatever the previous call left: the status word must start at zero; the
+  // hidden activations behind it are fully overwritten before they are read
+  LACT_CUDA(cudaMemsetAsync(scratch, 0, 256, s));
+  ApplyArgs a{static_cast<const bf16*>(w0w2), static_cast<const bf16*>(w1), x, N * D, D, 0, N, out, N * D, D, 0,
+              reinterpret_cast<bf16*>(static_cast<uint8_t*>(scratch) + 256), B, D, H};
+  return run_apply(a, static_cast<int32_t*>(scratch), s);
 }
 
 int lact_fw_grad_workspace_bytes(int64_t B, int64_t N, int64_t D, int64_t H, size_t* bytes_out) {

