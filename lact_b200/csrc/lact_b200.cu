@@ -7,12 +7,13 @@
 #include <algorithm>
 #include <atomic>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <vector>
 
 #include "../../include/lact_b200.h"
-#include "ops.cuh"
+#include "ns_fused.cuh"
 
 namespace lact {
 namespace {
@@ -70,16 +71,26 @@ int make_operand(CUtensorMap* map, OperandInfo* info, const Mat& m, int mn_major
   return encode_map(map, m, mn_major ? 64 : static_cast<uint32_t>(tile_rows));
 }
 
+// Output of a staged epilogue: bf16 matrix `m` whose extents clip the stored tiles.
+int make_output(CUtensorMap* map, OutInfo* info, const Mat& m, int row_off, int col_off, int batch_off = 0) {
+  info->row_off = row_off;
+  info->col_off = col_off;
+  info->batch_off = batch_off;
+  info->enabled = 1;
+  if ((col_off % 8) != 0 || row_off < 0 || col_off < 0) return LACT_ERR_SHAPE;
+  return encode_map(map, m, kBM);
+}
+
 // ------------------------------------------------------------------------------------------
 // launch accounting and optional per-kernel-class timing
 // ------------------------------------------------------------------------------------------
 enum KernelClass : int {
   kClsPrepare = 0, kClsGate, kClsDown, kClsGradPointwise, kClsGradContract, kClsMomentumMean, kClsNsPrepare,
-  kClsNsGram, kClsNsPoly, kClsNsUpdate, kClsRenorm, kClsOther, kNumClasses
+  kClsNsGram, kClsNsPoly, kClsNsUpdate, kClsRenorm, kClsNsFused, kClsOther, kNumClasses
 };
 const char* const kClassNames[kNumClasses] = {
     "prepare_weights", "gemm_swiglu_gate", "gemm_down_proj", "gemm_fwgrad_pointwise", "gemm_fwgrad_contract",
-    "momentum_mean", "ns_prepare", "gemm_ns_gram", "gemm_ns_poly", "gemm_ns_update", "add_renorm", "other"};
+    "momentum_mean", "ns_prepare", "gemm_ns_gram", "gemm_ns_poly", "gemm_ns_update", "add_renorm", "ns_fused", "other"};
 
 struct Profiler {
   std::mutex mu;
@@ -148,11 +159,24 @@ int check_device() {
   return LACT_OK;
 }
 
-// Launches the first `nprob` problems of `args` (grid.z = nprob).
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+// Launches the first `nprob` problems of `args` as one persistent grid (one CTA per SM at most).
 template <class Op, int NPROB>
 int launch_gemm(const GemmArgs<Op, NPROB>& args, cudaStream_t stream, int cls, int nprob = NPROB) {
   auto kernel = umma_gemm_kernel<Op, NPROB>;
   constexpr uint32_t smem = gemm_smem_bytes<Op>();
+  static_assert(smem <= 232448, "shared memory budget exceeded");
   static std::mutex mu;
   static bool configured[64] = {false};
   int dev = 0;
@@ -164,26 +188,58 @@ int launch_gemm(const GemmArgs<Op, NPROB>& args, cudaStream_t stream, int cls, i
       if (dev < 64) configured[dev] = true;
     }
   }
-  int tiles = 0, batch = 0;
+  int64_t tiles = 0;
   for (int p = 0; p < nprob; ++p) {
     const auto& P = args.prob[p];
-    if (P.M < 1 || P.N < 1 || P.batch < 1 || P.K < 0) return LACT_ERR_SHAPE;
-    tiles = std::max(tiles, ((P.M + kBM - 1) / kBM) * ((P.N + Op::BN - 1) / Op::BN));
-    batch = std::max(batch, P.batch);
+    if (P.M < 1 || P.N < 1 || P.batch < 1 || P.K < 1) return LACT_ERR_SHAPE;
+    tiles += static_cast<int64_t>((P.M + kBM - 1) / kBM) * ((P.N + Op::BT - 1) / Op::BT) * P.batch;
   }
-  if (batch > 65535) return LACT_ERR_SHAPE;
-  dim3 grid(tiles, batch, nprob);
+  if (tiles > (1ll << 30)) return LACT_ERR_SHAPE;
+  const int grid = static_cast<int>(std::min<int64_t>(tiles, sm_count()));
   KernelScope scope(cls, stream);
-  kernel<<<grid, kGemmThreads, smem, stream>>>(args);
+  kernel<<<grid, kGemmThreadsV2, smem, stream>>>(args, nprob);
   LACT_CUDA(cudaGetLastError());
   return LACT_OK;
 }
 
 inline int ceil_div(int64_t a, int64_t b) { return static_cast<int>((a + b - 1) / b); }
 
-using OpStore = OpBmm<EpiStore, 128, 3>;
-using OpDW = OpBmm<EpiDW, 128, 4>;
-using OpNs = OpBmm<EpiNs, 128, 3>;
+// Output-tile width for a single-accumulator GEMM: the candidate with the least padded work over
+// the problems of the launch (ties go to the wider tile, whose MMA shape is more efficient).
+struct NW { int64_t n, weight; };
+int choose_bt(std::initializer_list<NW> probs) {
+  const int cands[4] = {256, 192, 128, 64};
+  int best = 128;
+  int64_t best_cost = -1;
+  for (int bt : cands) {
+    int64_t cost = 0;
+    for (const NW& q : probs) cost += ((q.n + bt - 1) / bt) * bt * q.weight;
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bt; }
+  }
+  return best;
+}
+
+// Instantiates OpT<BT> for the chosen tile width; `fill(args, bt)` populates the problems.
+template <template <int> class OpT, int NPROB, class Fill>
+int launch_op(int bt, Fill&& fill, cudaStream_t stream, int cls, int nprob) {
+#define LACT_OP_CASE(BTV)                                    \
+  case BTV: {                                                \
+    GemmArgs<OpT<BTV>, NPROB> g;                             \
+    std::memset(&g, 0, sizeof(g));                           \
+    LACT_TRY(fill(g, BTV));                                  \
+    return launch_gemm(g, stream, cls, nprob);               \
+  }
+  switch (bt) {
+    LACT_OP_CASE(64)
+    LACT_OP_CASE(128)
+    LACT_OP_CASE(192)
+    LACT_OP_CASE(256)
+    default: return LACT_ERR_CONFIG;
+  }
+#undef LACT_OP_CASE
+}
+template <int BT> using OpDWT = OpBmm<EpiDW, BT>;
+template <int BT> using OpStoreDirectT = OpBmm<EpiStore, BT>;
 
 // ------------------------------------------------------------------------------------------
 // building blocks (device pointers in, kernels enqueued)
@@ -201,6 +257,22 @@ struct ApplyArgs {
   int64_t B, D, H;
 };
 
+template <int BT>
+int launch_gate(const ApplyArgs& a, const Mat& x, const Mat& w02, int64_t len, int32_t* status, cudaStream_t stream) {
+  GemmArgs<OpSwigluGate<BT>, 1> g;
+  std::memset(&g, 0, sizeof(g));
+  auto& P = g.prob[0];
+  LACT_TRY(make_operand(&P.a[0], &P.ai[0], x, 0, kBM, static_cast<int>(a.start), 0));
+  LACT_TRY(make_operand(&P.b[0], &P.bi[0], w02, 0, BT, 0, 0));
+  LACT_TRY(make_operand(&P.b[1], &P.bi[1], w02, 0, BT, static_cast<int>(a.H), 0));
+  const Mat hid{a.hidden, len, a.H, a.H, a.B, len * a.H};
+  LACT_TRY(make_output(&P.out[0], &P.oi[0], hid, 0, 0));
+  P.M = static_cast<int>(len); P.N = static_cast<int>(a.H); P.K = static_cast<int>(a.D);
+  P.batch = static_cast<int>(a.B);
+  g.status = status;
+  return launch_gemm(g, stream, kClsGate);
+}
+
 int run_apply(const ApplyArgs& a, int32_t* status, cudaStream_t stream) {
   const int64_t len = a.end - a.start;
   if (len <= 0) return LACT_OK;
@@ -208,32 +280,22 @@ int run_apply(const ApplyArgs& a, int32_t* status, cudaStream_t stream) {
   const Mat w1{a.w1b, a.D, a.H, a.H, a.B, a.D * a.H};
   const Mat x{a.x, a.end, a.D, a.x_ts, a.B, a.x_bs};
   const Mat hid{a.hidden, len, a.H, a.H, a.B, len * a.H};
-  {
-    GemmArgs<OpSwigluGate, 1> g;
-    std::memset(&g, 0, sizeof(g));
-    auto& P = g.prob[0];
-    LACT_TRY(make_operand(&P.a[0], &P.ai[0], x, 0, kBM, static_cast<int>(a.start), 0));
-    LACT_TRY(make_operand(&P.b[0], &P.bi[0], w02, 0, OpSwigluGate::BN, 0, 0));
-    LACT_TRY(make_operand(&P.b[1], &P.bi[1], w02, 0, OpSwigluGate::BN, static_cast<int>(a.H), 0));
-    P.M = static_cast<int>(len); P.N = static_cast<int>(a.H); P.K = static_cast<int>(a.D);
-    P.batch = static_cast<int>(a.B);
-    P.ep = EpiSwiglu{a.hidden, len * a.H, a.H};
-    g.status = status;
-    LACT_TRY(launch_gemm(g, stream, kClsGate));
-  }
-  {
-    GemmArgs<OpStore, 1> g;
-    std::memset(&g, 0, sizeof(g));
+  if (a.H % 128 == 0) LACT_TRY(launch_gate<128>(a, x, w02, len, status, stream));
+  else LACT_TRY(launch_gate<64>(a, x, w02, len, status, stream));
+  const int bt = choose_bt({{a.D, 1}});
+  auto fill = [&](auto& g, int btv) -> int {
     auto& P = g.prob[0];
     LACT_TRY(make_operand(&P.a[0], &P.ai[0], hid, 0, kBM, 0, 0));
-    LACT_TRY(make_operand(&P.b[0], &P.bi[0], w1, 0, OpStore::BN, 0, 0));
+    LACT_TRY(make_operand(&P.b[0], &P.bi[0], w1, 0, btv, 0, 0));
+    // rows beyond the range's end must not be written: the map ends at out_start + len
+    const Mat om{a.out, a.out_start + len, a.D, a.o_ts, a.B, a.o_bs};
+    LACT_TRY(make_output(&P.out[0], &P.oi[0], om, static_cast<int>(a.out_start), 0));
     P.M = static_cast<int>(len); P.N = static_cast<int>(a.D); P.K = static_cast<int>(a.H);
     P.batch = static_cast<int>(a.B);
-    P.ep = EpiStore{a.out, a.o_bs, a.o_ts, static_cast<int32_t>(a.out_start), 0};
     g.status = status;
-    LACT_TRY(launch_gemm(g, stream, kClsDown));
-  }
-  return LACT_OK;
+    return LACT_OK;
+  };
+  return launch_op<OpBmmStore, 1>(bt, fill, stream, kClsDown, 1);
 }
 
 struct GradArgs {
@@ -268,39 +330,44 @@ int run_grad(const GradArgs& a, int32_t* status, cudaStream_t stream) {
     GemmArgs<OpFwGradPointwise, 1> g;
     std::memset(&g, 0, sizeof(g));
     auto& P = g.prob[0];
+    constexpr int BT = OpFwGradPointwise::BT;
     LACT_TRY(make_operand(&P.a[0], &P.ai[0], km, 0, kBM, static_cast<int>(a.start), 0));
     LACT_TRY(make_operand(&P.a[1], &P.ai[1], vm, 0, kBM, static_cast<int>(a.start), 0));
-    LACT_TRY(make_operand(&P.b[0], &P.bi[0], w02, 0, OpFwGradPointwise::BN, 0, 0));
-    LACT_TRY(make_operand(&P.b[1], &P.bi[1], w02, 0, OpFwGradPointwise::BN, static_cast<int>(a.H), 0));
+    LACT_TRY(make_operand(&P.b[0], &P.bi[0], w02, 0, BT, 0, 0));
+    LACT_TRY(make_operand(&P.b[1], &P.bi[1], w02, 0, BT, static_cast<int>(a.H), 0));
     // dh = v w1: w1 is [D][H], i.e. k (= D) rows with the n (= H) axis contiguous
-    LACT_TRY(make_operand(&P.b[2], &P.bi[2], w1, 1, OpFwGradPointwise::BN, 0, 0));
+    LACT_TRY(make_operand(&P.b[2], &P.bi[2], w1, 1, BT, 0, 0));
     P.M = static_cast<int>(len); P.N = static_cast<int>(a.H); P.K = static_cast<int>(a.D);
     P.batch = static_cast<int>(a.B);
-    P.ep = EpiFwGrad{a.lr0, a.lr1, a.lr2, a.lr_f32, static_cast<int32_t>(a.start), a.lr_bs, a.w_scale,
-                     a.dy02, len * 2 * a.H, 2 * a.H, static_cast<int32_t>(a.H), a.hid, len * a.H, a.H};
+    P.ep = EpiFwGrad{a.lr0, a.lr1, a.lr2, a.lr_f32, static_cast<int32_t>(a.start), a.lr_bs, a.w_scale};
+    // dy0 and dy2 share the [len][2H] plane: two maps of H columns each, so neither can spill
+    const Mat dy0m{a.dy02, len, a.H, 2 * a.H, a.B, len * 2 * a.H};
+    const Mat dy2m{a.dy02 + a.H, len, a.H, 2 * a.H, a.B, len * 2 * a.H};
+    LACT_TRY(make_output(&P.out[0], &P.oi[0], dy0m, 0, 0));
+    LACT_TRY(make_output(&P.out[1], &P.oi[1], dy2m, 0, 0));
+    LACT_TRY(make_output(&P.out[2], &P.oi[2], hid, 0, 0));
     g.status = status;
     LACT_TRY(launch_gemm(g, stream, kClsGradPointwise));
   }
-  {
-    // token contraction: [dw0; dw2] = dy02^T k  and  dw1 = v^T hidden
-    GemmArgs<OpDW, 2> g;
-    std::memset(&g, 0, sizeof(g));
+  // token contraction: [dw0; dw2] = dy02^T k  and  dw1 = v^T hidden
+  const int bt = choose_bt({{a.D, 2 * a.H}, {a.H, a.D}});
+  auto fill = [&](auto& g, int btv) -> int {
     auto& P0 = g.prob[0];
     LACT_TRY(make_operand(&P0.a[0], &P0.ai[0], dy, 1, kBM, 0, 0));
-    LACT_TRY(make_operand(&P0.b[0], &P0.bi[0], km, 1, OpDW::BN, 0, static_cast<int>(a.start)));
+    LACT_TRY(make_operand(&P0.b[0], &P0.bi[0], km, 1, btv, 0, static_cast<int>(a.start)));
     P0.M = static_cast<int>(2 * a.H); P0.N = static_cast<int>(a.D); P0.K = static_cast<int>(len);
     P0.batch = static_cast<int>(a.B);
     P0.ep = EpiDW{a.g02, 2 * a.H * a.D, a.D, a.beta, 1, a.g_f32};
     auto& P1 = g.prob[1];
     LACT_TRY(make_operand(&P1.a[0], &P1.ai[0], vm, 1, kBM, 0, static_cast<int>(a.start)));
-    LACT_TRY(make_operand(&P1.b[0], &P1.bi[0], hid, 1, OpDW::BN, 0, 0));
+    LACT_TRY(make_operand(&P1.b[0], &P1.bi[0], hid, 1, btv, 0, 0));
     P1.M = static_cast<int>(a.D); P1.N = static_cast<int>(a.H); P1.K = static_cast<int>(len);
     P1.batch = static_cast<int>(a.B);
     P1.ep = EpiDW{a.g1, a.D * a.H, a.H, a.beta, 1, a.g_f32};
     g.status = status;
-    LACT_TRY(launch_gemm(g, stream, kClsGradContract));
-  }
-  return LACT_OK;
+    return LACT_OK;
+  };
+  return launch_op<OpDWT, 2>(bt, fill, stream, kClsGradContract, 2);
 }
 
 // Newton-Schulz coefficient schedules.
@@ -311,69 +378,241 @@ const float kNsTuned[5][3] = {{4.0848f, -6.8946f, 2.9270f},
                               {2.8366f, -3.0525f, 1.2012f}};
 const float kNsConst[3] = {3.4445f, -4.7750f, 2.0315f};
 
-// One group of equally shaped matrices under iteration: X is [nmat][m][n] with m <= n.
+// One group of equally shaped gradient matrices [R][C] under iteration.  The iteration runs on
+// X = [m][n] with m <= n: X = G^T when `transposed`.  The result is always delivered in the
+// gradient's own [R][C] orientation.
 struct NsGroup {
-  int32_t nmat, m, n;
-  bf16 *xa, *xb;         // ping-pong iterates [nmat][m][n]
+  int32_t nmat, R, C, m, n, transposed;
+  bf16 *xa, *xb;              // ping-pong iterates, nmat * m * n each
   bf16 *gram, *cgram, *poly;  // [nmat][m][m]
+  float* partial;             // [nmat][kNsSlabs] partial sums of squares
 };
 
 inline size_t ns_group_bytes(int64_t nmat, int64_t m, int64_t n) {
-  return static_cast<size_t>(nmat) * (2 * m * n + 3 * m * m) * 2;
+  return static_cast<size_t>(nmat) * (2 * m * n + 3 * m * m) * 2 + static_cast<size_t>(nmat) * kNsSlabs * 4 + 6 * 256;
 }
 
-// Runs `steps` iterations on up to two groups (one launch per GEMM covers both).
-// Returns in result[g] the buffer that holds the final iterate.
-int run_ns_iterations(NsGroup* grp, int ngroups, int steps, int const_coeffs, const bf16** result, int32_t* status,
+void ns_group_init(NsGroup& g, int64_t nmat, int64_t R, int64_t C, int gram_right) {
+  g.nmat = static_cast<int32_t>(nmat);
+  g.R = static_cast<int32_t>(R);
+  g.C = static_cast<int32_t>(C);
+  g.m = static_cast<int32_t>(std::min(R, C));
+  g.n = static_cast<int32_t>(std::max(R, C));
+  g.transposed = (R > C) || (R == C && gram_right);
+}
+
+// Frobenius normalisation of the gradient matrices of one or two groups (src[g]: [nmat][R][C],
+// contiguous) into each group's first iterate.  With steps == 0 the normalised matrix is the
+// result and is written untransposed.
+int launch_ns_prepare(const NsGroup* grp, int ngroups, const void* const* src, int src_f32, int steps,
                       cudaStream_t stream) {
+  NsPrepArgs pa;
+  std::memset(&pa, 0, sizeof(pa));
+  pa.ngroups = ngroups;
+  int nmat = 0, tiles = 0;
+  for (int g = 0; g < ngroups; ++g) {
+    const NsGroup& G = grp[g];
+    pa.grp[g] = NsPrepGroup{src[g], src_f32, G.nmat, G.R, G.C, (G.transposed && steps > 0) ? 1 : 0, G.xa, G.partial};
+    nmat += G.nmat;
+    tiles = std::max(tiles, ceil_div(G.R, 64) * ceil_div(G.C, 64));
+  }
+  {
+    KernelScope scope(kClsNsPrepare, stream);
+    ns_sumsq_kernel<<<dim3(nmat, kNsSlabs), 256, 0, stream>>>(pa);
+    LACT_CUDA(cudaGetLastError());
+  }
+  KernelScope scope(kClsNsPrepare, stream);
+  ns_scale_kernel<<<dim3(nmat, tiles), 256, 0, stream>>>(pa);
+  LACT_CUDA(cudaGetLastError());
+  return LACT_OK;
+}
+
+// Runs `steps` iterations on one or two groups (every GEMM launch covers all groups).
+// result[g] = buffer holding the final iterate of group g, in [R][C] orientation.
+int run_ns_iterations(const NsGroup* grp, int ngroups, int steps, int const_coeffs, const bf16** result,
+                      int32_t* status, cudaStream_t stream) {
   if (ngroups < 1 || ngroups > 2) return LACT_ERR_CONFIG;
   if (!const_coeffs && steps != 5) return LACT_ERR_CONFIG;
   bf16* cur[2];
   bf16* nxt[2];
   for (int g = 0; g < ngroups; ++g) { cur[g] = grp[g].xa; nxt[g] = grp[g].xb; }
+  const NsGroup& G0 = grp[0];
+  const NsGroup& G1 = grp[ngroups - 1];
+  const int bt_mm = choose_bt({{G0.m, static_cast<int64_t>(G0.nmat) * G0.m}, {G1.m, static_cast<int64_t>(G1.nmat) * G1.m}});
+  const int bt_mn = choose_bt({{G0.n, static_cast<int64_t>(G0.nmat) * G0.m}, {G1.n, static_cast<int64_t>(G1.nmat) * G1.m}});
   for (int it = 0; it < steps; ++it) {
     const float* co = const_coeffs ? kNsConst : kNsTuned[it];
-    GemmArgs<OpNs, 2> ga, gb, gc;
-    std::memset(&ga, 0, sizeof(ga));
-    std::memset(&gb, 0, sizeof(gb));
-    std::memset(&gc, 0, sizeof(gc));
-    for (int g = 0; g < ngroups; ++g) {
-      const NsGroup& G = grp[g];
-      const int gi = g;
-      const Mat X{cur[gi], G.m, G.n, G.n, G.nmat, static_cast<int64_t>(G.m) * G.n};
-      const Mat A{G.gram, G.m, G.m, G.m, G.nmat, static_cast<int64_t>(G.m) * G.m};
-      const Mat CA{G.cgram, G.m, G.m, G.m, G.nmat, static_cast<int64_t>(G.m) * G.m};
-      const Mat PB{G.poly, G.m, G.m, G.m, G.nmat, static_cast<int64_t>(G.m) * G.m};
-      const int nb = G.nmat;
-      // gram = X X^T ; cgram = c * gram
-      auto& PA = ga.prob[g];
-      LACT_TRY(make_operand(&PA.a[0], &PA.ai[0], X, 0, kBM, 0, 0));
-      LACT_TRY(make_operand(&PA.b[0], &PA.bi[0], X, 0, OpNs::BN, 0, 0));
-      PA.M = G.m; PA.N = G.m; PA.K = G.n; PA.batch = nb;
-      PA.ep = EpiNs{G.gram, G.cgram, nullptr, 0.f, co[2], static_cast<int64_t>(G.m) * G.m, G.m};
-      // poly = b * gram + cgram gram   (gram is symmetric: its rows serve as the K-major B operand)
-      auto& PBm = gb.prob[g];
-      LACT_TRY(make_operand(&PBm.a[0], &PBm.ai[0], CA, 0, kBM, 0, 0));
-      LACT_TRY(make_operand(&PBm.b[0], &PBm.bi[0], A, 0, OpNs::BN, 0, 0));
-      PBm.M = G.m; PBm.N = G.m; PBm.K = G.m; PBm.batch = nb;
-      PBm.ep = EpiNs{G.poly, nullptr, G.gram, co[1], 0.f, static_cast<int64_t>(G.m) * G.m, G.m};
-      // X' = a * X + poly X   (X is [m][n]: k rows, n contiguous -> MN-major B operand)
-      auto& PC = gc.prob[g];
-      LACT_TRY(make_operand(&PC.a[0], &PC.ai[0], PB, 0, kBM, 0, 0));
-      LACT_TRY(make_operand(&PC.b[0], &PC.bi[0], X, 1, OpNs::BN, 0, 0));
-      PC.M = G.m; PC.N = G.n; PC.K = G.m; PC.batch = nb;
-      PC.ep = EpiNs{nxt[gi], nullptr, cur[gi], co[0], 0.f, static_cast<int64_t>(G.m) * G.n, G.n};
-    }
-    ga.status = gb.status = gc.status = status;
-    LACT_TRY(launch_gemm(ga, stream, kClsNsGram, ngroups));
-    LACT_TRY(launch_gemm(gb, stream, kClsNsPoly, ngroups));
-    LACT_TRY(launch_gemm(gc, stream, kClsNsUpdate, ngroups));
+    const bool last = (it == steps - 1);
+    // gram = X X^T ; cgram = c * gram
+    auto fill_gram = [&](auto& ga, int btv) -> int {
+      for (int g = 0; g < ngroups; ++g) {
+        const NsGroup& G = grp[g];
+        const Mat X{cur[g], G.m, G.n, G.n, G.nmat, static_cast<int64_t>(G.m) * G.n};
+        auto& P = ga.prob[g];
+        LACT_TRY(make_operand(&P.a[0], &P.ai[0], X, 0, kBM, 0, 0));
+        LACT_TRY(make_operand(&P.b[0], &P.bi[0], X, 0, btv, 0, 0));
+        P.M = G.m; P.N = G.m; P.K = G.n; P.batch = G.nmat;
+        const Mat A{G.gram, G.m, G.m, G.m, G.nmat, static_cast<int64_t>(G.m) * G.m};
+        const Mat CA{G.cgram, G.m, G.m, G.m, G.nmat, static_cast<int64_t>(G.m) * G.m};
+        LACT_TRY(make_output(&P.out[0], &P.oi[0], A, 0, 0));
+        LACT_TRY(make_output(&P.out[1], &P.oi[1], CA, 0, 0));
+        P.ep = EpiNs{nullptr, 0.f, co[2], static_cast<int64_t>(G.m) * G.m, G.m, 0, 0};
+      }
+      ga.status = status;
+      return LACT_OK;
+    };
+    // poly = b * gram + cgram gram   (gram is symmetric: its rows serve as the K-major B operand)
+    auto fill_poly = [&](auto& gb, int btv) -> int {
+      for (int g = 0; g < ngroups; ++g) {
+        const NsGroup& G = grp[g];
+        const Mat A{G.gram, G.m, G.m, G.m, G.nmat, static_cast<int64_t>(G.m) * G.m};
+        const Mat CA{G.cgram, G.m, G.m, G.m, G.nmat, static_cast<int64_t>(G.m) * G.m};
+        auto& P = gb.prob[g];
+        LACT_TRY(make_operand(&P.a[0], &P.ai[0], CA, 0, kBM, 0, 0));
+        LACT_TRY(make_operand(&P.b[0], &P.bi[0], A, 0, btv, 0, 0));
+        P.M = G.m; P.N = G.m; P.K = G.m; P.batch = G.nmat;
+        const Mat PBm{G.poly, G.m, G.m, G.m, G.nmat, static_cast<int64_t>(G.m) * G.m};
+        LACT_TRY(make_output(&P.out[0], &P.oi[0], PBm, 0, 0));
+        LACT_TRY(encode_map(&P.res, A, kBM));
+        P.res_enabled = 1;
+        P.ep = EpiNs{nullptr, co[1], 0.f, static_cast<int64_t>(G.m) * G.m, G.m, 0, 0};
+      }
+      gb.status = status;
+      return LACT_OK;
+    };
+    // X' = a * X + poly X   (X is [m][n]: k rows, n contiguous -> MN-major B operand); the last
+    // iterate of a transposed group is written back in the gradient's orientation
+    auto fill_upd = [&](auto& gc, int btv) -> int {
+      for (int g = 0; g < ngroups; ++g) {
+        const NsGroup& G = grp[g];
+        const Mat X{cur[g], G.m, G.n, G.n, G.nmat, static_cast<int64_t>(G.m) * G.n};
+        const Mat PB{G.poly, G.m, G.m, G.m, G.nmat, static_cast<int64_t>(G.m) * G.m};
+        auto& P = gc.prob[g];
+        LACT_TRY(make_operand(&P.a[0], &P.ai[0], PB, 0, kBM, 0, 0));
+        LACT_TRY(make_operand(&P.b[0], &P.bi[0], X, 1, btv, 0, 0));
+        P.M = G.m; P.N = G.n; P.K = G.m; P.batch = G.nmat;
+        const Mat XN{nxt[g], G.m, G.n, G.n, G.nmat, static_cast<int64_t>(G.m) * G.n};
+        LACT_TRY(make_output(&P.out[0], &P.oi[0], XN, 0, 0));
+        LACT_TRY(encode_map(&P.res, X, kBM));
+        P.res_enabled = 1;
+        P.ep = EpiNs{nxt[g], co[0], 0.f, static_cast<int64_t>(G.m) * G.n, G.n, (last && G.transposed) ? 1 : 0, G.m};
+      }
+      gc.status = status;
+      return LACT_OK;
+    };
+    LACT_TRY((launch_op<OpNs, 2>(bt_mm, fill_gram, stream, kClsNsGram, ngroups)));
+    LACT_TRY((launch_op<OpNs, 2>(bt_mm, fill_poly, stream, kClsNsPoly, ngroups)));
+    LACT_TRY((launch_op<OpNs, 2>(bt_mn, fill_upd, stream, kClsNsUpdate, ngroups)));
     for (int g = 0; g < ngroups; ++g) std::swap(cur[g], nxt[g]);
   }
   for (int g = 0; g < ngroups; ++g) result[g] = cur[g];
   return LACT_OK;
 }
 
+// Fused path: all iterations in one cooperative launch (the first iterates must be in grp[g].xa).
+template <int BT_MM, int BT_MN>
+int launch_ns_fused(const NsGroup* grp, int ngroups, int steps, int const_coeffs, uint32_t* barrier, int32_t* status,
+                    cudaStream_t stream, uint64_t* trace) {
+  using Args = NsFusedArgs<BT_MM, BT_MN>;
+  auto kernel = ns_fused_kernel<BT_MM, BT_MN>;
+  constexpr uint32_t smem = ns_fused_smem_bytes<BT_MM, BT_MN>();
+  static_assert(smem <= 232448, "shared memory budget exceeded");
+  static_assert(ns_fused_ring<BT_MM, BT_MN>() >= 3, "ring too shallow");
+  static std::mutex mu;
+  static bool configured[64] = {false};
+  int dev = 0;
+  LACT_CUDA(cudaGetDevice(&dev));
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev >= 64 || !configured[dev]) {
+      LACT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      if (dev < 64) configured[dev] = true;
+    }
+  }
+  Args args;
+  std::memset(&args, 0, sizeof(args));
+  int64_t max_tiles = 1;
+  for (int g = 0; g < ngroups; ++g) {
+    const NsGroup& G = grp[g];
+    const int64_t mm = static_cast<int64_t>(G.m) * G.m, mn = static_cast<int64_t>(G.m) * G.n;
+    const Mat A{G.gram, G.m, G.m, G.m, G.nmat, mm};
+    const Mat CA{G.cgram, G.m, G.m, G.m, G.nmat, mm};
+    const Mat PB{G.poly, G.m, G.m, G.m, G.nmat, mm};
+    for (int par = 0; par < 2; ++par) {
+      bf16* cur = par == 0 ? G.xa : G.xb;
+      bf16* nxt = par == 0 ? G.xb : G.xa;
+      const Mat X{cur, G.m, G.n, G.n, G.nmat, mn};
+      auto& PG = args.gram[par][g];
+      LACT_TRY(make_operand(&PG.a[0], &PG.ai[0], X, 0, kBM, 0, 0));
+      LACT_TRY(make_operand(&PG.b[0], &PG.bi[0], X, 0, BT_MM, 0, 0));
+      PG.M = G.m; PG.N = G.m; PG.K = G.n; PG.batch = G.nmat;
+      LACT_TRY(make_output(&PG.out[0], &PG.oi[0], A, 0, 0));
+      LACT_TRY(make_output(&PG.out[1], &PG.oi[1], CA, 0, 0));
+      PG.ep = EpiNs{nullptr, 0.f, 0.f, mm, G.m, 0, 0};
+      auto& PU = args.upd[par][g];
+      LACT_TRY(make_operand(&PU.a[0], &PU.ai[0], PB, 0, kBM, 0, 0));
+      LACT_TRY(make_operand(&PU.b[0], &PU.bi[0], X, 1, BT_MN, 0, 0));
+      PU.M = G.m; PU.N = G.n; PU.K = G.m; PU.batch = G.nmat;
+      const Mat XN{nxt, G.m, G.n, G.n, G.nmat, mn};
+      LACT_TRY(make_output(&PU.out[0], &PU.oi[0], XN, 0, 0));
+      LACT_TRY(encode_map(&PU.res, X, kBM));
+      PU.res_enabled = 1;
+      PU.ep = EpiNs{nxt, 0.f, 0.f, mn, G.n, 0, 0};
+    }
+    auto& PP = args.poly[g];
+    LACT_TRY(make_operand(&PP.a[0], &PP.ai[0], CA, 0, kBM, 0, 0));
+    LACT_TRY(make_operand(&PP.b[0], &PP.bi[0], A, 0, BT_MM, 0, 0));
+    PP.M = G.m; PP.N = G.m; PP.K = G.m; PP.batch = G.nmat;
+    LACT_TRY(make_output(&PP.out[0], &PP.oi[0], PB, 0, 0));
+    LACT_TRY(encode_map(&PP.res, A, kBM));
+    PP.res_enabled = 1;
+    PP.ep = EpiNs{nullptr, 0.f, 0.f, mm, G.m, 0, 0};
+    args.transposed[g] = G.transposed;
+    args.m[g] = G.m;
+    max_tiles = std::max<int64_t>(max_tiles, static_cast<int64_t>(G.nmat) * ceil_div(G.m, kBM) * ceil_div(G.n, BT_MN) * ngroups);
+  }
+  for (int it = 0; it < steps; ++it) {
+    const float* co = const_coeffs ? kNsConst : kNsTuned[it];
+    args.coef[it][0] = co[0]; args.coef[it][1] = co[1]; args.coef[it][2] = co[2];
+  }
+  args.steps = steps;
+  args.ngroups = ngroups;
+  args.status = status;
+  args.barrier = barrier;
+  args.trace = trace;
+  LACT_CUDA(cudaMemsetAsync(barrier, 0, sizeof(uint32_t), stream));
+  const int grid = static_cast<int>(std::min<int64_t>(sm_count(), std::max<int64_t>(max_tiles, 8)));
+  void* kargs[] = {&args};
+  KernelScope scope(kClsNsFused, stream);
+  LACT_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kernel), dim3(grid), dim3(kGemmThreadsV2), kargs, smem,
+                                        stream));
+  return LACT_OK;
+}
+
+// Picks the fused kernel instantiated for the tile widths this problem wants; returns
+// LACT_ERR_CONFIG when there is none (the caller then runs the multi-launch path).
+int try_ns_fused(const NsGroup* grp, int ngroups, int steps, int const_coeffs, uint32_t* barrier, int32_t* status,
+                 cudaStream_t stream, const bf16** result, uint64_t* trace = nullptr) {
+  if (steps < 1 || steps > kNsFusedMaxSteps) return LACT_ERR_CONFIG;
+  if (!const_coeffs && steps != 5) return LACT_ERR_CONFIG;
+  {
+    // LACT_B200_NS_FUSED=0 selects the one-launch-per-GEMM path (same arithmetic, for comparison)
+    const char* env = std::getenv("LACT_B200_NS_FUSED");
+    if (env != nullptr && env[0] == '0') return LACT_ERR_CONFIG;
+  }
+  const NsGroup& G0 = grp[0];
+  const NsGroup& G1 = grp[ngroups - 1];
+  const int bt_mm = choose_bt({{G0.m, static_cast<int64_t>(G0.nmat) * G0.m}, {G1.m, static_cast<int64_t>(G1.nmat) * G1.m}});
+  const int bt_mn = choose_bt({{G0.n, static_cast<int64_t>(G0.nmat) * G0.m}, {G1.n, static_cast<int64_t>(G1.nmat) * G1.m}});
+  for (int g = 0; g < ngroups; ++g) result[g] = (steps % 2 == 0) ? grp[g].xa : grp[g].xb;
+  if (bt_mm == 192 && bt_mn == 192)
+    return launch_ns_fused<192, 192>(grp, ngroups, steps, const_coeffs, barrier, status, stream, trace);
+  if (bt_mm == 128 && bt_mn == 256)
+    return launch_ns_fused<128, 256>(grp, ngroups, steps, const_coeffs, barrier, status, stream, trace);
+  if (bt_mm == 128 && bt_mn == 128)
+    return launch_ns_fused<128, 128>(grp, ngroups, steps, const_coeffs, barrier, status, stream, trace);
+  return LACT_ERR_CONFIG;
+}
 
 // ------------------------------------------------------------------------------------------
 // workspace planning
@@ -396,28 +635,25 @@ struct NsPlan {
   NsGroup grp[2];
 };
 
-// Carves Newton-Schulz buffers.  separate: one group of 3B matrices [m][n] (w0 and w2 of batch b
-// at 2b, 2b+1; w1 of batch b at 2B + b).  concat: group 0 = [w0; w2] as B matrices, group 1 = w1.
-void plan_ns(Carver& c, int64_t B, int64_t D, int64_t H, int concat, NsPlan* plan) {
-  auto fill = [&](NsGroup& g, int64_t nmat, int64_t r, int64_t cc) {
-    g.nmat = static_cast<int32_t>(nmat);
-    g.m = static_cast<int32_t>(std::min(r, cc));
-    g.n = static_cast<int32_t>(std::max(r, cc));
-    const size_t mn = static_cast<size_t>(nmat) * g.m * g.n, mm = static_cast<size_t>(nmat) * g.m * g.m;
-    g.xa = c.take<bf16>(mn);
-    g.xb = c.take<bf16>(mn);
-    g.gram = c.take<bf16>(mm);
-    g.cgram = c.take<bf16>(mm);
-    g.poly = c.take<bf16>(mm);
-  };
-  if (concat) {
-    plan->ngroups = 2;
-    fill(plan->grp[0], B, 2 * H, D);
-    fill(plan->grp[1], B, D, H);
-  } else {
-    plan->ngroups = 1;
-    fill(plan->grp[0], 3 * B, H, D);
-  }
+void carve_ns_group(Carver& c, NsGroup& g) {
+  const size_t mn = static_cast<size_t>(g.nmat) * g.m * g.n, mm = static_cast<size_t>(g.nmat) * g.m * g.m;
+  g.xa = c.take<bf16>(mn);
+  g.xb = c.take<bf16>(mn);
+  g.gram = c.take<bf16>(mm);
+  g.cgram = c.take<bf16>(mm);
+  g.poly = c.take<bf16>(mm);
+  g.partial = c.take<float>(static_cast<size_t>(g.nmat) * kNsSlabs);
+}
+
+// Group 0 orthogonalises the [w0; w2] gradient (concat: B matrices [2H][D]; separate: 2B matrices
+// [H][D], w0 and w2 of batch b at 2b, 2b+1), group 1 the w1 gradient (B matrices [D][H]).
+void plan_ns(Carver& c, int64_t B, int64_t D, int64_t H, int concat, int gram_right, NsPlan* plan) {
+  plan->ngroups = 2;
+  if (concat) ns_group_init(plan->grp[0], B, 2 * H, D, gram_right);
+  else ns_group_init(plan->grp[0], 2 * B, H, D, gram_right);
+  ns_group_init(plan->grp[1], B, D, H, gram_right);
+  carve_ns_group(c, plan->grp[0]);
+  carve_ns_group(c, plan->grp[1]);
 }
 
 struct ScanPlan {
@@ -442,7 +678,7 @@ int plan_scan(const lact_scan_config& c, int32_t n_steps, const int32_t* kind, c
   }
   Carver cv(base);
   const size_t B = c.B, D = c.D, H = c.H;
-  p->status = cv.take<int32_t>(64);
+  p->status = cv.take<int32_t>(1024);  // status word, grid-barrier counter, phase trace
   p->W02 = cv.take<float>(B * 2 * H * D);
   p->W1 = cv.take<float>(B * D * H);
   p->W02c = cv.take<float>(B * 2 * H * D);
@@ -451,14 +687,14 @@ int plan_scan(const lact_scan_config& c, int32_t n_steps, const int32_t* kind, c
   p->n1 = cv.take<float>(B * D);
   p->G02 = cv.take<float>(B * 2 * H * D);
   p->G1 = cv.take<float>(B * D * H);
-  p->beta = cv.take<float>(B);
+  p->beta = cv.take<float>(B * static_cast<size_t>(std::max(1, n_steps)));
   p->W02b = cv.take<bf16>(B * 2 * H * D);
   p->W1b = cv.take<bf16>(B * D * H);
   p->hidden = cv.take<bf16>(B * static_cast<size_t>(max_apply) * H);
   p->dy02 = cv.take<bf16>(B * static_cast<size_t>(max_update) * 2 * H);
   p->hid = cv.take<bf16>(B * static_cast<size_t>(max_update) * H);
   p->ns.ngroups = 0;
-  if (c.use_muon && max_update > 0) plan_ns(cv, c.B, c.D, c.H, c.ns_concat, &p->ns);
+  if (c.use_muon && max_update > 0) plan_ns(cv, c.B, c.D, c.H, c.ns_concat, c.ns_gram_right, &p->ns);
   p->bytes = cv.off + 256;
   return LACT_OK;
 }
@@ -477,15 +713,12 @@ int validate_scan_config(const lact_scan_config& c) {
   return LACT_OK;
 }
 
-// Normalises `nmat` gradient matrices and writes the wide-orientation iterate.
-int launch_ns_prepare(const void* src, int src_f32, int64_t src_ms, int ld, int R, int C, int gram_right, bf16* X,
-                      int nmat, cudaStream_t stream) {
-  const int transpose = (R > C) || (R == C && gram_right);
-  KernelScope scope(kClsNsPrepare, stream);
-  ns_prepare_kernel<<<nmat, 512, 0, stream>>>(src, src_f32, src_ms, ld, R, C, transpose, X,
-                                              static_cast<int64_t>(R) * C);
-  LACT_CUDA(cudaGetLastError());
-  return LACT_OK;
+// True if an UPDATE step follows step i (then the fp32 copy of the normalised weights, which only
+// the final export reads in post-norm mode, need not be written).
+bool has_later_update(const int32_t* kind, int n_steps, int i) {
+  for (int j = i + 1; j < n_steps; ++j)
+    if (kind[j] == LACT_STEP_UPDATE) return true;
+  return false;
 }
 
 int scan_fwd(const lact_scan_config& c, const lact_scan_io& io, int32_t n_steps, const int32_t* kind,
@@ -506,7 +739,7 @@ int scan_fwd(const lact_scan_config& c, const lact_scan_io& io, int32_t n_steps,
       return LACT_ERR_STEPS;
 
   const int64_t B = c.B, D = c.D, H = c.H;
-  LACT_CUDA(cudaMemsetAsync(p.status, 0, 256, stream));
+  LACT_CUDA(cudaMemsetAsync(p.status, 0, 4096, stream));
   {
     const int64_t rows = B * (2 * H + D);
     KernelScope scope(kClsPrepare, stream);
@@ -528,6 +761,33 @@ int scan_fwd(const lact_scan_config& c, const lact_scan_io& io, int32_t n_steps,
     LACT_CUDA(cudaMemsetAsync(p.G1, 0, B * D * H * 4, stream));
   }
 
+  // per-update momentum factors, all steps at once
+  if (c.use_momentum) {
+    MeanArgs ma;
+    std::memset(&ma, 0, sizeof(ma));
+    int u = 0;
+    auto flush = [&](int first_u) -> int {
+      if (ma.n == 0) return LACT_OK;
+      KernelScope scope(kClsMomentumMean, stream);
+      momentum_mean_kernel<<<dim3(static_cast<unsigned>(B), ma.n), 256, 0, stream>>>(
+          io.momentum, c.mom_dtype == LACT_F32, c.L, ma, p.beta + static_cast<int64_t>(first_u) * B,
+          static_cast<int>(B));
+      LACT_CUDA(cudaGetLastError());
+      return LACT_OK;
+    };
+    ma.n = 0;
+    int first_u = 0;
+    for (int i = 0; i < n_steps; ++i) {
+      if (kind[i] != LACT_STEP_UPDATE) continue;
+      ma.s[ma.n] = static_cast<int32_t>(start[i]);
+      ma.e[ma.n] = static_cast<int32_t>(end[i]);
+      ++ma.n; ++u;
+      if (ma.n == kMeanBatch) { LACT_TRY(flush(first_u)); first_u = u; ma.n = 0; }
+    }
+    LACT_TRY(flush(first_u));
+  }
+
+  int update_idx = 0;
   for (int i = 0; i < n_steps; ++i) {
     if (kind[i] == LACT_STEP_APPLY) {
       ApplyArgs a{p.W02b, p.W1b, io.q, c.q_bs, c.q_ts, start[i], end[i], io.o, c.o_bs, c.o_ts, out_start[i],
@@ -535,67 +795,48 @@ int scan_fwd(const lact_scan_config& c, const lact_scan_io& io, int32_t n_steps,
       LACT_TRY(run_apply(a, p.status, stream));
       continue;
     }
-    const float* beta = nullptr;
-    if (c.use_momentum) {
-      KernelScope scope(kClsMomentumMean, stream);
-      momentum_mean_kernel<<<static_cast<int>(B), 256, 0, stream>>>(io.momentum, c.mom_dtype == LACT_F32, c.L,
-                                                                    static_cast<int>(start[i]),
-                                                                    static_cast<int>(end[i]), p.beta);
-      LACT_CUDA(cudaGetLastError());
-      beta = p.beta;
-    }
+    const float* beta = c.use_momentum ? p.beta + static_cast<int64_t>(update_idx) * B : nullptr;
+    ++update_idx;
     GradArgs g{p.W02b, p.W1b, io.k, io.v, c.k_bs, c.k_ts, c.v_bs, c.v_ts, start[i], end[i], io.lr0, io.lr1, io.lr2,
                c.lr_dtype == LACT_F32, c.L, c.w_scale, p.dy02, p.hid, p.G02, p.G1, 1, beta, B, D, H};
     LACT_TRY(run_grad(g, p.status, stream));
 
-    const bf16* xres[2] = {nullptr, nullptr};
-    if (c.use_muon) {
-      NsPlan& ns = p.ns;
-      if (c.ns_concat) {
-        LACT_TRY(launch_ns_prepare(p.G02, 1, 2 * H * D, static_cast<int>(D), static_cast<int>(2 * H),
-                                   static_cast<int>(D), c.ns_gram_right, ns.grp[0].xa, static_cast<int>(B), stream));
-        LACT_TRY(launch_ns_prepare(p.G1, 1, D * H, static_cast<int>(H), static_cast<int>(D), static_cast<int>(H),
-                                   c.ns_gram_right, ns.grp[1].xa, static_cast<int>(B), stream));
-      } else {
-        LACT_TRY(launch_ns_prepare(p.G02, 1, H * D, static_cast<int>(D), static_cast<int>(H), static_cast<int>(D),
-                                   c.ns_gram_right, ns.grp[0].xa, static_cast<int>(2 * B), stream));
-        LACT_TRY(launch_ns_prepare(p.G1, 1, D * H, static_cast<int>(H), static_cast<int>(D), static_cast<int>(H),
-                                   c.ns_gram_right, ns.grp[0].xa + 2 * B * H * D, static_cast<int>(B), stream));
-      }
-      LACT_TRY(run_ns_iterations(ns.grp, ns.ngroups, c.ns_steps, c.ns_const_coeffs, xres, p.status, stream));
-    }
-    // add + renormalise, one launch per weight array
+    // add + renormalise arguments (the update is the Newton-Schulz result when Muon is on)
+    const bool want_compute = c.prenorm || !has_later_update(kind, n_steps, i);
+    RenormArgs rn[2];
     for (int w = 0; w < 2; ++w) {
-      RenormArgs r;
+      RenormArgs& r = rn[w];
       std::memset(&r, 0, sizeof(r));
       const int R = static_cast<int>(w == 0 ? 2 * H : D), C = static_cast<int>(w == 0 ? D : H);
+      if (C > kRenormMaxCols) return LACT_ERR_SHAPE;
       r.master = w == 0 ? p.W02 : p.W1;
-      r.compute = w == 0 ? p.W02c : p.W1c;
+      r.compute = want_compute ? (w == 0 ? p.W02c : p.W1c) : nullptr;
       r.shadow = w == 0 ? p.W02b : p.W1b;
       r.n0 = w == 0 ? p.n02 : p.n1;
       r.g = w == 0 ? p.G02 : p.G1;
+      r.x = nullptr;
+      r.x_bs = static_cast<int64_t>(R) * C;
       r.B = static_cast<int>(B); r.R = R; r.C = C;
       r.mode = c.renorm; r.prenorm = c.prenorm; r.prenorm_bf16 = c.prenorm_bf16; r.quirk = c.overwrite_quirk;
-      if (c.use_muon) {
-        int mat_rows;  // rows of one orthogonalised matrix in the weight's own orientation
-        if (c.ns_concat) {
-          r.x = xres[w];
-          r.x_mats_per_b = 1; r.x_mat_off = 0;
-          mat_rows = R;
-        } else {
-          r.x = xres[0];
-          r.x_mats_per_b = w == 0 ? 2 : 1;
-          r.x_mat_off = w == 0 ? 0 : static_cast<int>(2 * B);
-          mat_rows = static_cast<int>(w == 0 ? H : D);
-        }
-        r.x_rows_per_mat = mat_rows;
-        r.x_ms = static_cast<int64_t>(mat_rows) * C;
-        r.x_transposed = (mat_rows > C) || (mat_rows == C && c.ns_gram_right);
-        r.x_ld = r.x_transposed ? mat_rows : C;
-      }
-      const int64_t rows = B * R;
+    }
+    if (c.use_muon) {
+      NsPlan& ns = p.ns;
+      const bf16* xres[2] = {nullptr, nullptr};
+      const void* srcs[2] = {p.G02, p.G1};
+      LACT_TRY(launch_ns_prepare(ns.grp, ns.ngroups, srcs, 1, c.ns_steps, stream));
+      int rc = try_ns_fused(ns.grp, ns.ngroups, c.ns_steps, c.ns_const_coeffs,
+                            reinterpret_cast<uint32_t*>(p.status) + 8, p.status, stream, xres,
+                            reinterpret_cast<uint64_t*>(p.status + 64));
+      if (rc == LACT_ERR_CONFIG)
+        rc = run_ns_iterations(ns.grp, ns.ngroups, c.ns_steps, c.ns_const_coeffs, xres, p.status, stream);
+      LACT_TRY(rc);
+      rn[0].x = xres[0];
+      rn[1].x = xres[1];
+    }
+    {
+      const int64_t rows = B * (2 * H + D);
       KernelScope scope(kClsRenorm, stream);
-      add_renorm_kernel<<<ceil_div(rows, 8), 256, 0, stream>>>(r);
+      add_renorm_kernel<<<ceil_div(rows, 8), 256, 0, stream>>>(rn[0], rn[1]);
       LACT_CUDA(cudaGetLastError());
     }
   }
@@ -822,21 +1063,15 @@ int lact_newton_schulz(const void* g, int32_t g_dtype, void* x, int64_t B, int64
   Carver cv(workspace);
   int32_t* status = cv.take<int32_t>(64);
   NsGroup grp;
-  const int64_t m = std::min(R, C), n = std::max(R, C);
-  grp.nmat = static_cast<int32_t>(B); grp.m = static_cast<int32_t>(m); grp.n = static_cast<int32_t>(n);
-  grp.xa = cv.take<bf16>(B * m * n);
-  grp.xb = cv.take<bf16>(B * m * n);
-  grp.gram = cv.take<bf16>(B * m * m);
-  grp.cgram = cv.take<bf16>(B * m * m);
-  grp.poly = cv.take<bf16>(B * m * m);
-  LACT_TRY(launch_ns_prepare(g, g_dtype == LACT_F32, R * C, static_cast<int>(C), static_cast<int>(R),
-                             static_cast<int>(C), 0, grp.xa, static_cast<int>(B), s));
+  ns_group_init(grp, B, R, C, 0);
+  carve_ns_group(cv, grp);
   const bf16* res = nullptr;
-  LACT_TRY(run_ns_iterations(&grp, 1, steps, const_coeffs, &res, status, s));
-  KernelScope scope(kClsOther, s);
-  ns_export_kernel<<<static_cast<int>(B), 512, 0, s>>>(res, m * n, static_cast<int>(R), static_cast<int>(C), R > C,
-                                                       static_cast<bf16*>(x), R * C);
-  LACT_CUDA(cudaGetLastError());
+  const void* srcs[2] = {g, g};
+  LACT_TRY(launch_ns_prepare(&grp, 1, srcs, g_dtype == LACT_F32, steps, s));
+  int rc = try_ns_fused(&grp, 1, steps, const_coeffs, reinterpret_cast<uint32_t*>(status) + 8, status, s, &res);
+  if (rc == LACT_ERR_CONFIG) rc = run_ns_iterations(&grp, 1, steps, const_coeffs, &res, status, s);
+  LACT_TRY(rc);
+  LACT_CUDA(cudaMemcpyAsync(x, res, static_cast<size_t>(B) * R * C * 2, cudaMemcpyDeviceToDevice, s));
   return LACT_OK;
 }
 
@@ -875,15 +1110,30 @@ int lact_bmm_bf16(const void* a, int32_t a_mn_major, const void* b, int32_t b_mn
   if (batch < 1 || batch > 65535 || M < 1 || N < 8 || K < 1 || (M % 8) || (N % 8) || (K % 8)) return LACT_ERR_SHAPE;
   const Mat A = a_mn_major ? Mat{a, K, M, M, batch, K * M} : Mat{a, M, K, K, batch, M * K};
   const Mat Bm = b_mn_major ? Mat{b, K, N, N, batch, K * N} : Mat{b, N, K, K, batch, N * K};
-  GemmArgs<OpStore, 1> g;
-  std::memset(&g, 0, sizeof(g));
-  auto& P = g.prob[0];
-  LACT_TRY(make_operand(&P.a[0], &P.ai[0], A, a_mn_major, kBM, 0, 0));
-  LACT_TRY(make_operand(&P.b[0], &P.bi[0], Bm, b_mn_major, OpStore::BN, 0, 0));
-  P.M = static_cast<int>(M); P.N = static_cast<int>(N); P.K = static_cast<int>(K); P.batch = static_cast<int>(batch);
-  P.ep = EpiStore{c, M * N, N, 0, c_dtype == LACT_F32};
-  g.status = status_word;
-  return launch_gemm(g, static_cast<cudaStream_t>(stream), kClsOther);
+  auto fill = [&](auto& g, int btv) -> int {
+    auto& P = g.prob[0];
+    LACT_TRY(make_operand(&P.a[0], &P.ai[0], A, a_mn_major, kBM, 0, 0));
+    LACT_TRY(make_operand(&P.b[0], &P.bi[0], Bm, b_mn_major, btv, 0, 0));
+    P.M = static_cast<int>(M); P.N = static_cast<int>(N); P.K = static_cast<int>(K);
+    P.batch = static_cast<int>(batch);
+    P.ep = EpiStore{c, M * N, N, 0, 1};
+    g.status = status_word;
+    return LACT_OK;
+  };
+  auto fill_bf16 = [&](auto& g, int btv) -> int {
+    auto& P = g.prob[0];
+    LACT_TRY(make_operand(&P.a[0], &P.ai[0], A, a_mn_major, kBM, 0, 0));
+    LACT_TRY(make_operand(&P.b[0], &P.bi[0], Bm, b_mn_major, btv, 0, 0));
+    LACT_TRY(make_output(&P.out[0], &P.oi[0], Mat{c, M, N, N, batch, M * N}, 0, 0));
+    P.M = static_cast<int>(M); P.N = static_cast<int>(N); P.K = static_cast<int>(K);
+    P.batch = static_cast<int>(batch);
+    g.status = status_word;
+    return LACT_OK;
+  };
+  const int bt = choose_bt({{N, 1}});
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (c_dtype == LACT_F32) return launch_op<OpStoreDirectT, 1>(bt, fill, s, kClsOther, 1);
+  return launch_op<OpBmmStore, 1>(bt, fill_bf16, s, kClsOther, 1);
 }
 
 }  // extern "C"

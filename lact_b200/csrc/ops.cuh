@@ -32,11 +32,12 @@ __device__ __forceinline__ void store_row32_f32(float* dst, const float* v, int 
     }
   }
 }
+// L2-only loads: the row may have been written by another SM earlier in the same kernel.
 __device__ __forceinline__ void load_row32_bf16(const bf16* src, float* v, int valid) {
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
     if (g * 8 < valid) {
-      const uint4 u = *reinterpret_cast<const uint4*>(src + g * 8);
+      const uint4 u = __ldcg(reinterpret_cast<const uint4*>(src + g * 8));
       const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -112,38 +113,11 @@ struct EpiDW {
 // arithmetic): t = bf16(acc); if res: t = bf16(bf16(alpha * res) + t); out = t;
 // if out2: out2 = bf16(gamma * t).
 struct EpiNs {
-  bf16* out;
-  bf16* out2;
-  const bf16* res;
+  bf16* out;         // used only for the transposed final write
   float alpha, gamma;
-  int64_t bs, ld;  // shared by out, out2 and res
-  __device__ __forceinline__ void operator()(int batch, int row, int col, int M, int N, const float* v) const {
-    if (row >= M) return;
-    const int valid = min(32, N - col);
-    const int64_t idx = batch * bs + static_cast<int64_t>(row) * ld + col;
-    float t[32];
-#pragma unroll
-    for (int j = 0; j < 32; ++j) t[j] = bf16_round(v[j]);
-    if (res != nullptr) {
-      float r[32];
-      load_row32_bf16(res + idx, r, valid);
-#pragma unroll
-      for (int j = 0; j < 32; ++j) t[j] = bf16_round(bf16_round(alpha * r[j]) + t[j]);
-    }
-    store_row32_bf16(out + idx, t, valid);
-    if (out2 != nullptr) {
-      float u[32];
-#pragma unroll
-      for (int j = 0; j < 32; ++j) u[j] = gamma * t[j];
-      store_row32_bf16(out2 + idx, u, valid);
-    }
-  }
-};
-
-// SwiGLU gate: hidden = silu(y0) * y2 (fp32), stored as bf16 [batch][row][col].
-struct EpiSwiglu {
-  bf16* out;
   int64_t bs, ld;
+  int32_t out_transposed;  // final iterate of a transposed group: write out[batch][col][row]
+  int32_t out_ld_t;
 };
 
 // Fast-weight-gradient pointwise stage: from y0 = k w0^T, y2 = k w2^T, dh = v w1 and the three
@@ -155,81 +129,180 @@ struct EpiFwGrad {
   int32_t tok_off;  // global token index of row 0
   int64_t lr_bs;    // batch stride of the lr tensors (token stride is 1)
   float w_scale;
-  bf16* dy02;  // [batch][row][2H]: dy0 at column c, dy2 at column H + c
-  int64_t dy_bs, dy_ld;
-  int32_t H;
-  bf16* hid;  // [batch][row][H]
-  int64_t hid_bs, hid_ld;
 };
 
 // ------------------------------------------------------------------------------------------
 // ops
 // ------------------------------------------------------------------------------------------
-template <class EpiT, int BN_, int STAGES_>
+// Ops without global epilogue operands prefetch nothing.
+struct NoPrefetch {};
+
+// ring depth that fits 227 KB next to `staging` bytes of output tiles
+__host__ __device__ constexpr int ring_depth(uint32_t stage_bytes, uint32_t staging) {
+  return static_cast<int>((232448u - 1024u - 256u - staging) / stage_bytes) > 8
+             ? 8
+             : static_cast<int>((232448u - 1024u - 256u - staging) / stage_bytes);
+}
+
+// c = a b^T, one accumulator, direct (register) epilogue `EpiT`; output tile 128 x BT.
+template <class EpiT, int BT_>
 struct OpBmm {
-  static constexpr int NA = 1, NB = 1, NACC = 1, BN = BN_, STAGES = STAGES_, NTERMS = 1;
+  static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 0;
+  static constexpr bool kSecondInPlace = false, kResidualTma = false;
+  static constexpr int STAGES = ring_depth(kATileBytes + BT_ * kBK * 2, 0);
   using Epi = EpiT;
   __host__ __device__ static constexpr int term_a(int) { return 0; }
   __host__ __device__ static constexpr int term_b(int) { return 0; }
-  __host__ __device__ static constexpr int term_acc(int) { return 0; }
+  __host__ __device__ static constexpr int term_col(int) { return 0; }
+  __host__ __device__ static constexpr int term_n(int) { return BT_; }
   __host__ __device__ static constexpr bool term_first(int) { return true; }
+  using Prefetch = NoPrefetch;
+  __device__ static __forceinline__ void prefetch(const Epi&, int, int, int, int, int, int, Prefetch&) {}
   __device__ static __forceinline__ void epilogue(const Epi& ep, int batch, int row, int col, int M, int N,
-                                                  const float (&v)[1][32]) {
+                                                  const float (&v)[1][32], Prefetch&, int) {
     ep(batch, row, col, M, N, v[0]);
   }
 };
 
-// y0 = x w0^T, y2 = x w2^T share the activation tile; epilogue = SwiGLU gate.
-struct OpSwigluGate {
-  static constexpr int NA = 1, NB = 2, NACC = 2, BN = 128, STAGES = 2, NTERMS = 2;
-  using Epi = EpiSwiglu;
+// c = bf16(a b^T) written through the staged TMA-store epilogue.
+struct EpiNone {};
+template <int BT_>
+struct OpBmmStore {
+  static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 1;
+  static constexpr bool kSecondInPlace = false, kResidualTma = false;
+  static constexpr int STAGES = ring_depth(kATileBytes + BT_ * kBK * 2, kBM * BT_ * 2);
+  using Epi = EpiNone;
   __host__ __device__ static constexpr int term_a(int) { return 0; }
-  __host__ __device__ static constexpr int term_b(int t) { return t; }
-  __host__ __device__ static constexpr int term_acc(int t) { return t; }
+  __host__ __device__ static constexpr int term_b(int) { return 0; }
+  __host__ __device__ static constexpr int term_col(int) { return 0; }
+  __host__ __device__ static constexpr int term_n(int) { return BT_; }
   __host__ __device__ static constexpr bool term_first(int) { return true; }
-  __device__ static __forceinline__ void epilogue(const Epi& ep, int batch, int row, int col, int M, int N,
-                                                  const float (&v)[2][32]) {
-    if (row >= M) return;
-    float h[32];
+  using Prefetch = NoPrefetch;
+  __device__ static __forceinline__ void prefetch(const Epi&, int, int, int, int, int, int, Prefetch&) {}
+  __device__ static __forceinline__ bool skip_store(const Epi&, int) { return false; }
+  __device__ static __forceinline__ void epilogue_staged(const Epi&, int, int, int, int, int, const float (&v)[1][32],
+                                                         float (&o)[1][32], Prefetch&, int) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      const float y0 = v[0][j];
-      h[j] = v[1][j] * (y0 * sigmoidf_fast(y0));
-    }
-    store_row32_bf16(ep.out + batch * ep.bs + static_cast<int64_t>(row) * ep.ld + col, h, min(32, N - col));
+    for (int j = 0; j < 32; ++j) o[0][j] = v[0][j];
   }
 };
 
-// y0 = k w0^T, y2 = k w2^T, dh = v w1: three accumulators, two activation tiles, three weights.
-struct OpFwGradPointwise {
-  static constexpr int NA = 2, NB = 3, NACC = 3, BN = 128, STAGES = 2, NTERMS = 3;
-  using Epi = EpiFwGrad;
-  __host__ __device__ static constexpr int term_a(int t) { return t == 2 ? 1 : 0; }
-  __host__ __device__ static constexpr int term_b(int t) { return t; }
-  __host__ __device__ static constexpr int term_acc(int t) { return t; }
+// Newton-Schulz GEMM with the reference's eager bf16 rounding: t = bf16(acc); with a residual,
+// t = bf16(bf16(alpha * res) + t); first output t, optional second output bf16(gamma * t) made in
+// place from the staged first output.  The last iterate of a transposed group is written from
+// registers in the gradient's own orientation instead.
+template <int BT_>
+struct OpNs {
+  static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 2;
+  static constexpr bool kSecondInPlace = true, kResidualTma = true;
+  static constexpr int STAGES = ring_depth(kATileBytes + BT_ * kBK * 2, kBM * BT_ * 2);
+  using Epi = EpiNs;
+  __host__ __device__ static constexpr int term_a(int) { return 0; }
+  __host__ __device__ static constexpr int term_b(int) { return 0; }
+  __host__ __device__ static constexpr int term_col(int) { return 0; }
+  __host__ __device__ static constexpr int term_n(int) { return BT_; }
   __host__ __device__ static constexpr bool term_first(int) { return true; }
-  __device__ static __forceinline__ void epilogue(const Epi& ep, int batch, int row, int col, int M, int N,
-                                                  const float (&v)[3][32]) {
-    if (row >= M) return;
-    const int64_t li = batch * ep.lr_bs + ep.tok_off + row;
-    const float l0 = load_scalar(ep.lr0, ep.lr_f32, li) * ep.w_scale;
-    const float l1 = load_scalar(ep.lr1, ep.lr_f32, li) * ep.w_scale;
-    const float l2 = load_scalar(ep.lr2, ep.lr_f32, li) * ep.w_scale;
-    float hid[32], dy0[32], dy2[32];
+  __device__ static __forceinline__ float second(const Epi& ep, float t) { return ep.gamma * t; }
+  __device__ static __forceinline__ bool skip_store(const Epi& ep, int o) { return o == 0 && ep.out_transposed; }
+  // The residual tile arrives by TMA in the staging tile; the engine hands each thread the 64
+  // bytes that sit where its result will be written.
+  struct Prefetch {
+    uint4 r[4];
+  };
+  __device__ static __forceinline__ void prefetch(const Epi&, int, int, int, int, int, int, Prefetch&) {}
+  __device__ static __forceinline__ void epilogue_staged(const Epi& ep, int batch, int row, int col, int M, int N,
+                                                         const float (&v)[1][32], float (&o)[1][32], Prefetch& pf,
+                                                         int has_res) {
+    const int valid = min(32, N - col);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) o[0][j] = bf16_round(v[0][j]);
+    if (has_res) {
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        const uint32_t w[4] = {pf.r[g].x, pf.r[g].y, pf.r[g].z, pf.r[g].w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float r0 = __uint_as_float(w[q] << 16), r1 = __uint_as_float(w[q] & 0xFFFF0000u);
+          o[0][g * 8 + 2 * q] = bf16_round(bf16_round(ep.alpha * r0) + o[0][g * 8 + 2 * q]);
+          o[0][g * 8 + 2 * q + 1] = bf16_round(bf16_round(ep.alpha * r1) + o[0][g * 8 + 2 * q + 1]);
+        }
+      }
+    }
+    if (ep.out_transposed && row < M) {
+      bf16* dst = ep.out + batch * ep.bs + static_cast<int64_t>(col) * ep.out_ld_t + row;
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < valid) dst[static_cast<int64_t>(j) * ep.out_ld_t] = __float2bfloat16_rn(o[0][j]);
+    }
+  }
+};
+
+// [y0 | y2] = x [w0 slice ; w2 slice]^T as ONE 128 x 2BT MMA (the two weight tiles are adjacent
+// in shared memory); epilogue = SwiGLU gate, staged.
+template <int BT_>
+struct OpSwigluGate {
+  static constexpr int NA = 1, NB = 2, NACC = 2, BT = BT_, NTERMS = 1, NOUT = 1;
+  static constexpr bool kSecondInPlace = false, kResidualTma = false;
+  static constexpr int STAGES = ring_depth(kATileBytes + 2 * BT_ * kBK * 2, kBM * BT_ * 2);
+  using Epi = EpiNone;
+  __host__ __device__ static constexpr int term_a(int) { return 0; }
+  __host__ __device__ static constexpr int term_b(int) { return 0; }
+  __host__ __device__ static constexpr int term_col(int) { return 0; }
+  __host__ __device__ static constexpr int term_n(int) { return 2 * BT_; }
+  __host__ __device__ static constexpr bool term_first(int) { return true; }
+  using Prefetch = NoPrefetch;
+  __device__ static __forceinline__ void prefetch(const Epi&, int, int, int, int, int, int, Prefetch&) {}
+  __device__ static __forceinline__ bool skip_store(const Epi&, int) { return false; }
+  __device__ static __forceinline__ void epilogue_staged(const Epi&, int, int, int, int, int, const float (&v)[2][32],
+                                                         float (&o)[1][32], Prefetch&, int) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const float y0 = v[0][j];
+      o[0][j] = v[1][j] * (y0 * sigmoidf_fast(y0));
+    }
+  }
+};
+
+// [y0 | y2] = k [w0 slice ; w2 slice]^T (one 128 x 128 MMA) and dh = v w1 slice (128 x 64 MMA):
+// three accumulators of 64 hidden columns, two activation tiles, three weight tiles; three staged
+// outputs (dy0, dy2, hidden * lr1).
+struct OpFwGradPointwise {
+  static constexpr int NA = 2, NB = 3, NACC = 3, BT = 64, NTERMS = 2, NOUT = 3;
+  static constexpr bool kSecondInPlace = false, kResidualTma = false;
+  static constexpr int STAGES = ring_depth(2 * kATileBytes + 3 * 64 * kBK * 2, 3 * kBM * 64 * 2);
+  using Epi = EpiFwGrad;
+  __host__ __device__ static constexpr int term_a(int t) { return t; }
+  __host__ __device__ static constexpr int term_b(int t) { return t == 0 ? 0 : 2; }
+  __host__ __device__ static constexpr int term_col(int t) { return t == 0 ? 0 : 128; }
+  __host__ __device__ static constexpr int term_n(int t) { return t == 0 ? 128 : 64; }
+  __host__ __device__ static constexpr bool term_first(int) { return true; }
+  struct Prefetch {
+    float l0, l1, l2;
+  };
+  __device__ static __forceinline__ void prefetch(const Epi& ep, int batch, int row, int, int, int M, int,
+                                                  Prefetch& pf) {
+    pf.l0 = pf.l1 = pf.l2 = 0.f;
+    if (row < M) {
+      const int64_t li = batch * ep.lr_bs + ep.tok_off + row;
+      pf.l0 = load_scalar(ep.lr0, ep.lr_f32, li) * ep.w_scale;
+      pf.l1 = load_scalar(ep.lr1, ep.lr_f32, li) * ep.w_scale;
+      pf.l2 = load_scalar(ep.lr2, ep.lr_f32, li) * ep.w_scale;
+    }
+  }
+  __device__ static __forceinline__ bool skip_store(const Epi&, int) { return false; }
+  __device__ static __forceinline__ void epilogue_staged(const Epi&, int, int, int, int, int,
+                                                         const float (&v)[3][32], float (&o)[3][32],
+                                                         Prefetch& pf, int) {
+    const float l0 = pf.l0, l1 = pf.l1, l2 = pf.l2;
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
       const float y0 = v[0][j], y2 = v[1][j], dh = v[2][j];
       const float sg = sigmoidf_fast(y0);
       const float sw = sg * y0;
-      hid[j] = sw * y2 * l1;
-      dy0[j] = sg * y2 * dh * (1.0f + y0 * (1.0f - sg)) * l0;
-      dy2[j] = sw * dh * l2;
+      o[0][j] = sg * y2 * dh * (1.0f + y0 * (1.0f - sg)) * l0;  // dy0
+      o[1][j] = sw * dh * l2;                                     // dy2
+      o[2][j] = sw * y2 * l1;                                     // hidden * lr1
     }
-    const int valid = min(32, N - col);
-    bf16* d = ep.dy02 + batch * ep.dy_bs + static_cast<int64_t>(row) * ep.dy_ld + col;
-    store_row32_bf16(d, dy0, valid);
-    store_row32_bf16(d + ep.H, dy2, valid);
-    store_row32_bf16(ep.hid + batch * ep.hid_bs + static_cast<int64_t>(row) * ep.hid_ld + col, hid, valid);
   }
 };
 
@@ -285,10 +358,17 @@ __global__ void prepare_weights_kernel(const void* w0, const void* w1, const voi
   if (lane == 0) *dn = sqrtf(ss);
 }
 
-// beta[b] = mean over tokens [s, e) of momentum[b, t]; one CTA per batch entry.
-__global__ void momentum_mean_kernel(const void* mom, int mom_f32, int64_t bs, int s, int e, float* beta) {
+// beta[u][b] = mean over tokens [s_u, e_u) of momentum[b, t] for up to kMeanBatch update steps per
+// launch; grid (batch entries, steps).
+constexpr int kMeanBatch = 64;
+struct MeanArgs {
+  int32_t n;
+  int32_t s[kMeanBatch], e[kMeanBatch];
+};
+__global__ void momentum_mean_kernel(const void* mom, int mom_f32, int64_t bs, const MeanArgs ma, float* beta, int B) {
   __shared__ float part[32];
-  const int b = blockIdx.x;
+  const int b = blockIdx.x, u = blockIdx.y;
+  const int s = ma.s[u], e = ma.e[u];
   float acc = 0.f;
   for (int t = s + threadIdx.x; t < e; t += blockDim.x) acc += load_scalar(mom, mom_f32, b * bs + t);
   acc = warp_sum(acc);
@@ -298,27 +378,53 @@ __global__ void momentum_mean_kernel(const void* mom, int mom_f32, int64_t bs, i
     float x = threadIdx.x < (blockDim.x >> 5) ? part[threadIdx.x] : 0.f;
     x = warp_sum(x);
     if (threadIdx.x == 0) {
-      float m = x / static_cast<float>(e - s);
-      beta[b] = mom_f32 ? m : bf16_round(m);
+      const float m = x / static_cast<float>(e - s);
+      beta[static_cast<int64_t>(u) * B + b] = mom_f32 ? m : bf16_round(m);
     }
   }
 }
 
-// Newton-Schulz start: X = bf16(G); X = X / (||X||_F + 1e-7) with bf16 rounding of the norm, of
-// the sum and of the quotient; written transposed when `transpose` (the iteration always runs
-// on the wide orientation).  One CTA per matrix; src is fp32 or bf16, [R][C] with row stride ld.
-__global__ void ns_prepare_kernel(const void* src, int src_f32, int64_t src_ms, int ld, int R, int C, int transpose,
-                                  bf16* X, int64_t x_ms) {
+// Newton-Schulz start for up to two groups of gradient matrices.
+struct NsPrepGroup {
+  const void* src;  // gradient matrices [nmat][R][C], contiguous
+  int32_t src_f32;
+  int32_t nmat, R, C;
+  int32_t transpose;  // write the iterate transposed ([C][R])
+  bf16* x0;           // first iterate
+  float* partial;     // [nmat][kNsSlabs]
+};
+struct NsPrepArgs {
+  NsPrepGroup grp[2];
+  int32_t ngroups;
+};
+constexpr int kNsSlabs = 16;
+
+// Part 1: partial sums of squares of bf16(G).  Grid (matrices of all groups, slabs): CTA (mat,
+// slab) reduces rows [slab * rows_per_slab, ...) and writes one float; part 2 adds the partials in
+// a fixed order, so the norm does not depend on scheduling.
+__global__ void __launch_bounds__(256) ns_sumsq_kernel(const NsPrepArgs args) {
   __shared__ float part[32];
-  __shared__ float den_s;
-  const int mat = blockIdx.x;
-  const int64_t base = mat * src_ms;
-  const int total = R * C;
+  int mat = blockIdx.x;
+  const int gi = (args.ngroups > 1 && mat >= args.grp[0].nmat) ? 1 : 0;
+  if (gi == 1) mat -= args.grp[0].nmat;
+  const NsPrepGroup& G = args.grp[gi];
+  const int slab = blockIdx.y;
+  const int rows_per_slab = (G.R + kNsSlabs - 1) / kNsSlabs;
+  const int r0 = slab * rows_per_slab, r1 = min(G.R, r0 + rows_per_slab);
+  const int64_t base = static_cast<int64_t>(mat) * G.R * G.C;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < total; i += blockDim.x) {
-    const int r = i / C, c = i - r * C;
-    const float x = bf16_round(load_scalar(src, src_f32, base + static_cast<int64_t>(r) * ld + c));
-    ss += x * x;
+  for (int r = r0 + (threadIdx.x >> 5); r < r1; r += (blockDim.x >> 5)) {
+    const int64_t rb = base + static_cast<int64_t>(r) * G.C;
+    for (int c0 = threadIdx.x & 31; c0 < G.C; c0 += 256) {
+      float xv[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) xv[i] = (c0 + 32 * i < G.C) ? load_scalar(G.src, G.src_f32, rb + c0 + 32 * i) : 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float x = bf16_round(xv[i]);
+        ss += x * x;
+      }
+    }
   }
   ss = warp_sum(ss);
   if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
@@ -326,87 +432,133 @@ __global__ void ns_prepare_kernel(const void* src, int src_f32, int64_t src_ms, 
   if (threadIdx.x < 32) {
     float x = threadIdx.x < (blockDim.x >> 5) ? part[threadIdx.x] : 0.f;
     x = warp_sum(x);
-    if (threadIdx.x == 0) den_s = bf16_round(bf16_round(sqrtf(x)) + 1e-7f);
-  }
-  __syncthreads();
-  const float den = den_s;
-  bf16* xo = X + mat * x_ms;
-  for (int i = threadIdx.x; i < total; i += blockDim.x) {
-    const int r = i / C, c = i - r * C;
-    const float x = bf16_round(load_scalar(src, src_f32, base + static_cast<int64_t>(r) * ld + c));
-    const bf16 y = __float2bfloat16_rn(x / den);
-    if (transpose) xo[static_cast<int64_t>(c) * R + r] = y;
-    else xo[static_cast<int64_t>(r) * C + c] = y;
+    if (threadIdx.x == 0) G.partial[mat * kNsSlabs + slab] = x;
   }
 }
 
-// Copies a bf16 Newton-Schulz result back to the caller's [R][C] orientation.
-__global__ void ns_export_kernel(const bf16* X, int64_t x_ms, int R, int C, int transposed, bf16* out, int64_t o_ms) {
-  const int mat = blockIdx.x;
-  const int total = R * C;
-  for (int i = threadIdx.x; i < total; i += blockDim.x) {
-    const int r = i / C, c = i - r * C;
-    out[mat * o_ms + i] = transposed ? X[mat * x_ms + static_cast<int64_t>(c) * R + r] : X[mat * x_ms + i];
+// Part 2: X = bf16(bf16(G) / (bf16(||bf16(G)||_F) + 1e-7)), every operation rounded to bf16 as in
+// the reference; written transposed (through a shared-memory tile, so both sides stay coalesced)
+// when the iteration runs on the other orientation.  Grid (matrices of all groups, 64x64 tiles).
+__global__ void __launch_bounds__(256) ns_scale_kernel(const NsPrepArgs args) {
+  __shared__ float tile[64][65];
+  int mat = blockIdx.x;
+  const int gi = (args.ngroups > 1 && mat >= args.grp[0].nmat) ? 1 : 0;
+  if (gi == 1) mat -= args.grp[0].nmat;
+  const NsPrepGroup& G = args.grp[gi];
+  const int tiles_c = (G.C + 63) / 64, tiles_r = (G.R + 63) / 64;
+  if (static_cast<int>(blockIdx.y) >= tiles_c * tiles_r) return;
+  const int tr = (blockIdx.y / tiles_c) * 64, tcx = (blockIdx.y % tiles_c) * 64;
+  float tot = 0.f;
+  for (int i = 0; i < kNsSlabs; ++i) tot += G.partial[mat * kNsSlabs + i];
+  const float den = bf16_round(bf16_round(sqrtf(tot)) + 1e-7f);
+  const int64_t base = static_cast<int64_t>(mat) * G.R * G.C;
+  const int lx = threadIdx.x & 63, ly = threadIdx.x >> 6;  // 64 x 4
+  float xv[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int r = tr + ly + 4 * i, c = tcx + lx;
+    xv[i] = (r < G.R && c < G.C) ? load_scalar(G.src, G.src_f32, base + static_cast<int64_t>(r) * G.C + c) : 0.f;
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) tile[ly + 4 * i][lx] = bf16_round(xv[i]) / den;
+  __syncthreads();
+  bf16* xo = G.x0 + base;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int rr = ly + 4 * i;
+    if (G.transpose) {
+      const int c = tcx + rr, r = tr + lx;  // output row = source column
+      if (c < G.C && r < G.R) xo[static_cast<int64_t>(c) * G.R + r] = __float2bfloat16_rn(tile[lx][rr]);
+    } else {
+      const int r = tr + rr, c = tcx + lx;
+      if (r < G.R && c < G.C) xo[static_cast<int64_t>(r) * G.C + c] = __float2bfloat16_rn(tile[rr][lx]);
+    }
   }
 }
 
 struct RenormArgs {
   float* master;     // [B][R][C] fp32, in/out
-  float* compute;    // [B][R][C] fp32 out: the weights the next step computes with
+  float* compute;    // [B][R][C] fp32 out (may be nullptr): the weights the next step computes with
   bf16* shadow;      // [B][R][C] bf16 out
   const float* n0;   // [B][R]
   const float* g;    // [B][R][C] fp32 gradient (after momentum)
-  const bf16* x;     // Newton-Schulz result or nullptr (then the update is g)
-  int64_t x_ms;      // matrix stride of x
-  int32_t x_mats_per_b, x_rows_per_mat;  // W rows [j*rows_per_mat, (j+1)*rows_per_mat) belong to matrix b*mats_per_b + j
-  int32_t x_mat_off;                     // index of this weight's first matrix in x
-  int32_t x_transposed, x_ld;            // x is stored [C][rows_per_mat] (transposed) or [rows_per_mat][C]
+  const bf16* x;     // Newton-Schulz result in the weight's own orientation, or nullptr (update = g)
+  int64_t x_bs;      // stride of x between batch entries
   int32_t B, R, C;
   int32_t mode;      // LACT_RENORM_*
   int32_t prenorm, prenorm_bf16, quirk;
 };
 
-// w_new = (quirk ? g : master) + update; normalise rows; one warp per row.
-__global__ void add_renorm_kernel(const RenormArgs a) {
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (row >= static_cast<int64_t>(a.B) * a.R) return;
-  const int lane = threadIdx.x & 31;
+constexpr int kRenormMaxCols = 1024;
+
+// One weight row: w_new = (quirk ? g : master) + update; normalise.  Lane l owns columns
+// 4l .. 4l+3 of every 128-column group (NV groups, row kept in registers).  The Newton-Schulz
+// result is read with L2-only loads (another SM may have written it earlier in the same kernel).
+template <int NV>
+__device__ __forceinline__ void renorm_row(const RenormArgs& a, int64_t row, int lane) {
   const int b = static_cast<int>(row / a.R), r = static_cast<int>(row % a.R);
   const int64_t off = row * a.C;
-  const bf16* xm = nullptr;
-  int lr = 0;
-  if (a.x != nullptr) {
-    const int j = r / a.x_rows_per_mat;
-    lr = r - j * a.x_rows_per_mat;
-    xm = a.x + static_cast<int64_t>(a.x_mat_off + b * a.x_mats_per_b + j) * a.x_ms;
-  }
+  const bf16* xr = a.x != nullptr ? a.x + b * a.x_bs + static_cast<int64_t>(r) * a.C : nullptr;
+  const bool use_g_base = a.quirk && xr != nullptr;
+  const float n0 = a.n0[row];
+  float4 w[NV];
   float ss = 0.f;
-  for (int c = lane; c < a.C; c += 32) {
-    const float g = a.g[off + c];
-    float upd = g;
-    if (xm != nullptr)
-      upd = __bfloat162float(a.x_transposed ? xm[static_cast<int64_t>(c) * a.x_ld + lr]
-                                            : xm[static_cast<int64_t>(lr) * a.x_ld + c]);
-    const float base = (a.quirk && xm != nullptr) ? g : a.master[off + c];
-    const float w = base + upd;
-    a.compute[off + c] = w;  // staged; normalised below
-    ss += w * w;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = 4 * lane + 128 * i;
+    w[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c < a.C) {
+      float4 upd;
+      if (xr != nullptr) {
+        const uint2 u = __ldcg(reinterpret_cast<const uint2*>(xr + c));
+        upd = make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xFFFF0000u),
+                          __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xFFFF0000u));
+      } else {
+        upd = *reinterpret_cast<const float4*>(a.g + off + c);
+      }
+      const float4 base = use_g_base ? *reinterpret_cast<const float4*>(a.g + off + c)
+                                     : *reinterpret_cast<const float4*>(a.master + off + c);
+      w[i] = make_float4(base.x + upd.x, base.y + upd.y, base.z + upd.z, base.w + upd.w);
+      ss += w[i].x * w[i].x + w[i].y * w[i].y + w[i].z * w[i].z + w[i].w * w[i].w;
+    }
   }
   ss = warp_sum(ss);
-  const float n0 = a.n0[row];
   const float den = sqrtf(ss) + 1e-5f;
   const float rstd = 1.0f / sqrtf(ss + 1e-5f);
-  __syncwarp();
-  for (int c = lane; c < a.C; c += 32) {
-    const float w = a.compute[off + c];
-    float y = w;
-    if (a.mode == 1) y = w / den * n0;
-    else if (a.mode == 2) y = w * rstd * n0;
-    if (a.prenorm && a.prenorm_bf16) y = bf16_round(y);
-    a.master[off + c] = a.prenorm ? w : y;
-    a.compute[off + c] = y;
-    a.shadow[off + c] = __float2bfloat16_rn(y);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = 4 * lane + 128 * i;
+    if (c < a.C) {
+      float y[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (a.mode == 1) y[q] = y[q] / den * n0;
+        else if (a.mode == 2) y[q] = y[q] * rstd * n0;
+        if (a.prenorm && a.prenorm_bf16) y[q] = bf16_round(y[q]);
+      }
+      const float4 yv = make_float4(y[0], y[1], y[2], y[3]);
+      *reinterpret_cast<float4*>(a.master + off + c) = a.prenorm ? w[i] : yv;
+      if (a.compute != nullptr) *reinterpret_cast<float4*>(a.compute + off + c) = yv;
+      *reinterpret_cast<uint2*>(a.shadow + off + c) = make_uint2(pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]));
+    }
   }
+}
+
+__device__ __forceinline__ void renorm_row_any(const RenormArgs& a, int64_t row, int lane) {
+  const int nv = (a.C + 127) / 128;
+  if (nv <= 1) renorm_row<1>(a, row, lane);
+  else if (nv <= 2) renorm_row<2>(a, row, lane);
+  else if (nv <= 3) renorm_row<3>(a, row, lane);
+  else if (nv <= 4) renorm_row<4>(a, row, lane);
+  else renorm_row<8>(a, row, lane);
+}
+
+// Both weight arrays in one launch; one warp per row.
+__global__ void __launch_bounds__(256) add_renorm_kernel(const RenormArgs a0, const RenormArgs a1) {
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t rows0 = static_cast<int64_t>(a0.B) * a0.R, rows1 = static_cast<int64_t>(a1.B) * a1.R;
+  if (row < rows0) renorm_row_any(a0, row, threadIdx.x & 31);
+  else if (row < rows0 + rows1) renorm_row_any(a1, row - rows0, threadIdx.x & 31);
 }
 
 // y = (x + x_add) * rsqrt(sum (x + x_add)^2 + eps) * scale[row]; one warp per row.

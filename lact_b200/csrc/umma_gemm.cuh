@@ -16,7 +16,6 @@ namespace lact {
 constexpr int kBM = 128;   // UMMA M (rows of the accumulator = TMEM lanes)
 constexpr int kBK = 64;    // k-block: 64 bf16 = 128 bytes = one swizzle row
 constexpr int kUmmaK = 16; // K of one tcgen05.mma for 16-bit operands
-constexpr int kGemmThreads = 192;
 constexpr uint32_t kATileBytes = kBM * kBK * 2;
 constexpr uint32_t kAtomBytes = 64 * kBK * 2;  // one 64(mn) x 64(k) MN-major atom column
 
@@ -27,12 +26,24 @@ struct OperandInfo {
   int32_t batch_off;  // added to the batch coordinate
 };
 
+// Where a staged (TMA-stored) output tile lands: tile (m0, n0) of batch entry b is stored at
+// coordinates (col_off + n0, row_off + m0, batch_off + b) of the output map, whose extents clip it.
+struct OutInfo {
+  int32_t row_off, col_off, batch_off, enabled;
+};
+
 template <class Op>
 struct GemmProblem {
   CUtensorMap a[Op::NA];
   CUtensorMap b[Op::NB];
+  CUtensorMap out[Op::NOUT > 0 ? Op::NOUT : 1];  // bf16 outputs written by TMA store (NOUT == 0: none)
   OperandInfo ai[Op::NA];
   OperandInfo bi[Op::NB];
+  OutInfo oi[Op::NOUT > 0 ? Op::NOUT : 1];
+  // optional residual operand of the epilogue (ops with kResidualTma): a bf16 matrix addressed
+  // like out[0]; its tile is TMA-loaded into the staging tile ahead of the epilogue
+  CUtensorMap res;
+  int32_t res_enabled;
   int32_t M, N, K, batch;
   typename Op::Epi ep;
 };
@@ -47,10 +58,32 @@ __host__ __device__ constexpr uint32_t tmem_cols_pow2(uint32_t n) {
   return n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : n <= 256 ? 256 : 512;
 }
 
+// An op describes the wiring of one GEMM kernel:
+//   NA, NB        operand tiles loaded per pipeline stage (A tiles: 128 rows; B tiles: BT rows)
+//   BT            width of the output tile in logical columns (= rows of every B operand tile)
+//   NACC          accumulators handed to the epilogue, accumulator a at TMEM columns [a*BT, (a+1)*BT)
+//   terms         each term issues MMAs  acc[cols term_col .. term_col + term_n) (+)= A[term_a] * B[term_b..]^T;
+//                 term_n may span several consecutive B tiles (they are adjacent in shared memory)
+//   STAGES        depth of the shared-memory ring
+// Accumulators are double-buffered in tensor memory (2 * NACC * BT <= 512 columns), so the epilogue
+// of tile i overlaps the main loop of tile i + 1.
+template <class Op>
+__host__ __device__ constexpr uint32_t gemm_stage_bytes() {
+  return Op::NA * kATileBytes + Op::NB * Op::BT * kBK * 2;
+}
+// bf16 staging tiles for TMA-stored outputs: NOUT x [128 rows][BT columns], 128-byte swizzled in
+// 64-column panels (the layout the output tensor maps expect)
+template <class Op>
+__host__ __device__ constexpr uint32_t gemm_staging_bytes() {
+  return (Op::kSecondInPlace ? 1 : Op::NOUT) * kBM * Op::BT * 2;
+}
 template <class Op>
 __host__ __device__ constexpr uint32_t gemm_smem_bytes() {
-  return Op::STAGES * (Op::NA * kATileBytes + Op::NB * Op::BN * kBK * 2) + 1024 /*alignment slack*/ + 256;
+  return Op::STAGES * gemm_stage_bytes<Op>() + gemm_staging_bytes<Op>() + 1024 /*alignment slack*/ + 256 /*barriers*/;
 }
+
+constexpr int kEpiWarps = 8;
+constexpr int kGemmThreadsV2 = 64 + 32 * kEpiWarps;  // producer warp + MMA warp + epilogue warps
 
 template <int ROWS>
 __device__ __forceinline__ void load_operand_tile(uint32_t dst, const CUtensorMap* map, const OperandInfo& oi,
@@ -70,154 +103,399 @@ __device__ __forceinline__ uint64_t operand_desc(uint32_t tile, int mn_major, in
   return mn_major ? make_smem_desc(tile + k4 * 2048, kAtomBytes, 1024) : make_smem_desc(tile + k4 * 32, 0, 1024);
 }
 
-template <class Op, int NPROB>
-__global__ void __launch_bounds__(kGemmThreads, 1)
-umma_gemm_kernel(const __grid_constant__ GemmArgs<Op, NPROB> args) {
-  constexpr int BN = Op::BN, NA = Op::NA, NB = Op::NB, NACC = Op::NACC, STAGES = Op::STAGES;
-  constexpr uint32_t kBTileBytes = BN * kBK * 2;
-  constexpr uint32_t kStageBytes = NA * kATileBytes + NB * kBTileBytes;
-  constexpr uint32_t kTmemCols = tmem_cols_pow2(NACC * BN);
-  static_assert(NACC * BN <= 512, "accumulators exceed tensor memory");
-  static_assert(BN % 64 == 0 && BN <= 256, "BN must be 64, 128, 192 or 256");
+struct TileCoord {
+  int prob, batch, m0, n0;
+};
 
-  const GemmProblem<Op>& P = args.prob[blockIdx.z];
-  const int tiles_n = (P.N + BN - 1) / BN;
-  const int tiles_m = (P.M + kBM - 1) / kBM;
-  if (static_cast<int>(blockIdx.x) >= tiles_m * tiles_n || static_cast<int>(blockIdx.y) >= P.batch) return;
-  if (*reinterpret_cast<volatile int32_t*>(args.status) != kStatusOk) return;  // an earlier CTA gave up
-  const int m0 = (blockIdx.x / tiles_n) * kBM;
-  const int n0 = (blockIdx.x % tiles_n) * BN;
-  const int batch = blockIdx.y;
-  const int num_kb = (P.K + kBK - 1) / kBK;
+// Per-thread view of the CTA's pipeline resources and of this thread's progress counters.  The
+// producer thread advances `it`, the MMA thread `it` and `tcount`, epilogue threads `tcount`;
+// all three walk the same tile sequence, so their private copies stay consistent.  The counters
+// run on across phases of a multi-phase kernel.
+struct GemmCtx {
+  uint32_t smem_base;     // 1024-byte aligned start of the stage ring
+  uint32_t stage_stride;  // bytes between ring stages (>= the op's stage bytes)
+  uint32_t staging;       // 1024-byte aligned start of the output staging tiles
+  uint64_t *full_bar, *empty_bar, *acc_full_bar, *acc_empty_bar, *res_bar;
+  volatile uint32_t* abort_flag;
+  uint32_t res_count = 0;  // residual tiles consumed so far (epilogue threads)
+  uint32_t tmem_base;
+  uint32_t it = 0, tcount = 0;
+  // optional diagnostics (CTA 0 only): per phase < 6 and tile < 4, globaltimer stamps of
+  // {loads issued, MMAs committed, epilogue started, epilogue finished} at trace[40 + 16*phase + 4*tile + k]
+  uint64_t* trace = nullptr;
+  uint32_t phase = 0;
+  __device__ __forceinline__ void stamp(int tile_i, int k) const {
+    if (trace != nullptr && blockIdx.x == 0 && phase < 6 && tile_i < 4) trace[40 + 16 * phase + 4 * tile_i + k] = globaltimer_ns();
+  }
+};
 
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t raw_addr = smem_u32(smem_raw);
-  const uint32_t smem_base = (raw_addr + 1023u) & ~1023u;
-  uint8_t* aligned = smem_raw + (smem_base - raw_addr);
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(aligned + STAGES * kStageBytes);
-  uint64_t* empty_bar = full_bar + STAGES;
-  uint64_t* tmem_full_bar = empty_bar + STAGES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full_bar + 1);
-  volatile uint32_t* abort_flag = tmem_slot + 1;
+struct NoPatch {
+  template <class Epi>
+  __device__ __forceinline__ void operator()(Epi&, int) const {}
+};
+
+// One GEMM phase: CTA c processes tiles c, c + gridDim.x, ... of the concatenated tile lists of
+// `nprob` problems.  Tiles of one batch entry are consecutive (n fastest), so CTAs that run at
+// the same time share operand tiles in L2.  Warp 0 = TMA producer, warp 1 = MMA issuer, warps
+// 2.. = epilogue.  Returns true if a bounded wait ran out.  No CTA-wide sync inside.
+template <class Op, int RING, class EpiPatch>
+__device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* probs, const int nprob,
+                                           EpiPatch patch) {
+  constexpr int BT = Op::BT, NA = Op::NA, NB = Op::NB, NACC = Op::NACC;
+  constexpr uint32_t kBTileBytes = BT * kBK * 2;
+  constexpr uint32_t kStageBytes = gemm_stage_bytes<Op>();
+  constexpr uint32_t kAccCols = NACC * BT;
+  constexpr int kMaxProb = 2;
+  static_assert(2 * kAccCols <= 512, "double-buffered accumulators exceed tensor memory");
+  static_assert(BT % 64 == 0 && BT <= 256, "BT must be 64, 128, 192 or 256");
+
+  int tiles_of[kMaxProb], tn_of[kMaxProb], tm_of[kMaxProb];
+  int total_tiles = 0;
+#pragma unroll
+  for (int p = 0; p < kMaxProb; ++p) {
+    if (p < nprob) {
+      tn_of[p] = (probs[p].N + BT - 1) / BT;
+      tm_of[p] = (probs[p].M + kBM - 1) / kBM;
+      tiles_of[p] = tn_of[p] * tm_of[p] * probs[p].batch;
+    } else {
+      tn_of[p] = tm_of[p] = 1;
+      tiles_of[p] = 0;
+    }
+    total_tiles += tiles_of[p];
+  }
+  auto coord = [&](int tile) {
+    TileCoord c;
+    c.prob = 0;
+    if (tile >= tiles_of[0]) { tile -= tiles_of[0]; c.prob = 1; }
+    const int per_batch = tn_of[c.prob] * tm_of[c.prob];
+    c.batch = tile / per_batch;
+    const int r = tile - c.batch * per_batch;
+    c.m0 = (r / tn_of[c.prob]) * kBM;
+    c.n0 = (r % tn_of[c.prob]) * BT;
+    return c;
+  };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], 1);
+  bool failed = false;
+  if (warp == 0) {
+    // ---------------- TMA producer (one thread); the ring keeps running across tiles
+    if (lane == 0) {
+      int tile_i = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x, ++tile_i) {
+        const TileCoord tc = coord(tile);
+        const GemmProblem<Op>& P = probs[tc.prob];
+        const int num_kb = (P.K + kBK - 1) / kBK;
+        for (int kb = 0; kb < num_kb; ++kb, ++cx.it) {
+          const int s = cx.it % RING;
+          const uint32_t ph = (cx.it / RING) & 1;
+          if (!mbar_wait(&cx.empty_bar[s], ph ^ 1, cx.abort_flag)) { failed = true; break; }
+          if (kb == num_kb - 1) cx.stamp(tile_i, 0);
+          mbar_expect_tx(&cx.full_bar[s], kStageBytes);
+          const uint32_t st = cx.smem_base + s * cx.stage_stride;
+          const int kc = kb * kBK;
+#pragma unroll
+          for (int i = 0; i < NA; ++i)
+            load_operand_tile<kBM>(st + i * kATileBytes, &P.a[i], P.ai[i], tc.m0, kc, tc.batch, &cx.full_bar[s]);
+#pragma unroll
+          for (int i = 0; i < NB; ++i)
+            load_operand_tile<BT>(st + NA * kATileBytes + i * kBTileBytes, &P.b[i], P.bi[i], tc.n0, kc, tc.batch,
+                                  &cx.full_bar[s]);
+        }
+      }
     }
-    mbar_init(tmem_full_bar, 1);
-    *abort_flag = 0;
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (one thread)
+    if (lane == 0) {
+      int tile_i = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x, ++cx.tcount, ++tile_i) {
+        const TileCoord tc = coord(tile);
+        const GemmProblem<Op>& P = probs[tc.prob];
+        const int num_kb = (P.K + kBK - 1) / kBK;
+        const uint32_t as = cx.tcount & 1, aph = (cx.tcount >> 1) & 1;
+        if (!mbar_wait(&cx.acc_empty_bar[as], aph ^ 1, cx.abort_flag)) { failed = true; break; }
+        tc_fence_after();
+        const uint32_t acc_base = cx.tmem_base + as * kAccCols;
+        for (int kb = 0; kb < num_kb; ++kb, ++cx.it) {
+          const int s = cx.it % RING;
+          const uint32_t ph = (cx.it / RING) & 1;
+          if (!mbar_wait(&cx.full_bar[s], ph, cx.abort_flag)) { failed = true; break; }
+          tc_fence_after();
+          const uint32_t st = cx.smem_base + s * cx.stage_stride;
+#pragma unroll
+          for (int t = 0; t < Op::NTERMS; ++t) {
+            const int ia = Op::term_a(t), ib = Op::term_b(t);
+            const int a_mn = P.ai[ia].mn_major, b_mn = P.bi[ib].mn_major;
+            const uint32_t idesc = make_idesc_bf16(kBM, Op::term_n(t), a_mn, b_mn);
+            const uint32_t a_tile = st + ia * kATileBytes;
+            const uint32_t b_tile = st + NA * kATileBytes + ib * kBTileBytes;
+#pragma unroll
+            for (int k4 = 0; k4 < kBK / kUmmaK; ++k4) {
+              const uint32_t acc = (kb > 0 || k4 > 0 || !Op::term_first(t)) ? 1u : 0u;
+              umma_bf16(acc_base + Op::term_col(t), operand_desc(a_tile, a_mn, k4), operand_desc(b_tile, b_mn, k4),
+                        idesc, acc);
+            }
+          }
+          umma_commit(&cx.empty_bar[s]);  // frees the stage once these MMAs have read it
+        }
+        if (!failed) umma_commit(&cx.acc_full_bar[as]);
+        cx.stamp(tile_i, 1);
+      }
+    }
+  } else {
+    // ---------------- epilogue: warp w may only touch TMEM lanes [32*(w%4), 32*(w%4)+32); the two
+    // warps of a lane quarter take alternate 32-column chunks.  Ops with NOUT > 0 round their
+    // results to bf16 into swizzled shared-memory tiles that one thread hands to TMA stores
+    // (full-line writes, clipped by the output map); other ops store from registers.
+    constexpr int NOUT = Op::NOUT;
+    constexpr int NSTG = Op::kSecondInPlace ? 1 : NOUT;  // staging tiles (an in-place second output reuses the first)
+    constexpr int kEpiThreads = kEpiWarps * 32;
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const bool elected = threadIdx.x == 64;
+    const int row_local = quarter * 32 + lane;
+    // Residual tile of `tile` -> staging (elected thread).  The previous TMA store must have
+    // finished reading the staging tile first.
+    auto issue_residual = [&](int tile) {
+      if constexpr (Op::kResidualTma) {
+        if (tile >= total_tiles) return;
+        const TileCoord t2 = coord(tile);
+        const GemmProblem<Op>& P2 = probs[t2.prob];
+        if (!P2.res_enabled) return;
+        bulk_wait_read_all();
+        int panels = 0;
+        for (int pnl = 0; pnl < BT / 64; ++pnl)
+          if (t2.n0 + pnl * 64 < P2.N) ++panels;
+        mbar_expect_tx(cx.res_bar, panels * (kBM * 128));
+        for (int pnl = 0; pnl < panels; ++pnl)
+          tma_load_3d(cx.staging + pnl * (kBM * 128), &P2.res, cx.res_bar, P2.oi[0].col_off + t2.n0 + pnl * 64,
+                      P2.oi[0].row_off + t2.m0, P2.oi[0].batch_off + t2.batch);
+      }
+    };
+    if (elected) issue_residual(blockIdx.x);
+    int tile_i = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++cx.tcount, ++tile_i) {
+      const TileCoord tc = coord(tile);
+      const GemmProblem<Op>& P = probs[tc.prob];
+      typename Op::Epi ep = P.ep;
+      patch(ep, tc.prob);
+      bool has_res = false;
+      if constexpr (Op::kResidualTma) has_res = P.res_enabled != 0;
+      const uint32_t as = cx.tcount & 1, aph = (cx.tcount >> 1) & 1;
+      const int row = tc.m0 + row_local;
+      // global operands of the epilogue are fetched while the tile's MMAs are still running
+      typename Op::Prefetch pf;
+      Op::prefetch(ep, tc.batch, row, tc.n0, half, P.M, P.N, pf);
+      bool got = mbar_wait(&cx.acc_full_bar[as], aph, cx.abort_flag);
+      tc_fence_after();
+      if (has_res) {
+        got = mbar_wait(cx.res_bar, cx.res_count & 1, cx.abort_flag) && got;
+        ++cx.res_count;
+      }
+      if (elected) cx.stamp(tile_i, 2);
+      const uint32_t acc_base = cx.tmem_base + as * kAccCols + (static_cast<uint32_t>(quarter * 32) << 16);
+      if constexpr (NOUT > 0) {
+        // A warp whose wait ran out must not leave the others stuck at a named barrier: it raises
+        // a flag that only epilogue warps write, and every warp decides after the barrier.
+        if (!got) cx.abort_flag[1] = 1;
+        // the previous tile's stores must have finished reading the staging tiles
+        if (elected) bulk_wait_read_all();
+        named_barrier_sync(1, kEpiThreads);
+        if (cx.abort_flag[1] != 0) { failed = true; break; }
+      } else {
+        if (!got) { failed = true; break; }
+      }
+      for (int c = half * 32; c < BT; c += 64) {
+        if (tc.n0 + c >= P.N) break;  // warp-uniform
+        float v[NACC][32];
+#pragma unroll
+        for (int a = 0; a < NACC; ++a) {
+          uint32_t bits[32];
+          tmem_ld32(acc_base + a * BT + c, bits);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[a][j] = __uint_as_float(bits[j]);
+        }
+        if constexpr (NOUT > 0) {
+          float ov[NSTG > 0 ? NSTG : 1][32];
+          const uint32_t rowaddr = (c >> 6) * (kBM * 128) + row_local * 128;
+          const uint32_t unit0 = (c & 63) >> 3;
+          if constexpr (Op::kResidualTma) {
+            if (has_res) {  // this thread's residual segment sits where its result will go
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                const uint32_t addr = cx.staging + rowaddr + (((unit0 + g) ^ (row_local & 7)) << 4);
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(pf.r[g].x), "=r"(pf.r[g].y), "=r"(pf.r[g].z), "=r"(pf.r[g].w)
+                             : "r"(addr)
+                             : "memory");
+              }
+            }
+          }
+          Op::epilogue_staged(ep, tc.batch, row, tc.n0 + c, P.M, P.N, v, ov, pf, has_res);
+#pragma unroll
+          for (int o = 0; o < NSTG; ++o) {
+            const uint32_t base = cx.staging + o * (kBM * BT * 2) + rowaddr;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const uint32_t addr = base + (((unit0 + g) ^ (row_local & 7)) << 4);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr),
+                           "r"(pack_bf16x2(ov[o][g * 8 + 0], ov[o][g * 8 + 1])),
+                           "r"(pack_bf16x2(ov[o][g * 8 + 2], ov[o][g * 8 + 3])),
+                           "r"(pack_bf16x2(ov[o][g * 8 + 4], ov[o][g * 8 + 5])),
+                           "r"(pack_bf16x2(ov[o][g * 8 + 6], ov[o][g * 8 + 7]))
+                           : "memory");
+            }
+          }
+        } else {
+          Op::epilogue(ep, tc.batch, row, tc.n0 + c, P.M, P.N, v, pf, c >> 6);
+        }
+      }
+      // all TMEM reads of this warp are complete (wait::ld above): hand the buffer back
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&cx.acc_empty_bar[as]);
+      if constexpr (NOUT > 0) {
+        fence_async_proxy();
+        named_barrier_sync(2, kEpiThreads);
+        if (elected) {
+#pragma unroll
+          for (int o = 0; o < NOUT; ++o) {
+            if (!P.oi[o].enabled || (o == 1 && Op::kSecondInPlace) || Op::skip_store(ep, o)) continue;
+            for (int pnl = 0; pnl < BT / 64; ++pnl) {
+              if (tc.n0 + pnl * 64 >= P.N) break;
+              tma_store_3d(&P.out[o], cx.staging + o * (kBM * BT * 2) + pnl * (kBM * 128),
+                           P.oi[o].col_off + tc.n0 + pnl * 64, P.oi[o].row_off + tc.m0, P.oi[o].batch_off + tc.batch);
+            }
+          }
+          bulk_commit_group();
+          cx.stamp(tile_i, 3);
+        }
+        if constexpr (Op::kSecondInPlace) {
+          // second output = f(first output), computed in place in the first staging tile
+          if (P.oi[1].enabled) {
+            if (elected) bulk_wait_read_all();
+            named_barrier_sync(1, kEpiThreads);
+            for (int c = half * 32; c < BT; c += 64) {
+              if (tc.n0 + c >= P.N) break;
+              const uint32_t base = cx.staging + (c >> 6) * (kBM * 128) + row_local * 128;
+              const uint32_t unit0 = (c & 63) >> 3;
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                const uint32_t addr = base + (((unit0 + g) ^ (row_local & 7)) << 4);
+                uint32_t w[4];
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
+                             : "r"(addr)
+                             : "memory");
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                  w[i] = pack_bf16x2(Op::second(ep, __uint_as_float(w[i] << 16)),
+                                     Op::second(ep, __uint_as_float(w[i] & 0xFFFF0000u)));
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+                             "r"(w[3])
+                             : "memory");
+              }
+            }
+            fence_async_proxy();
+            named_barrier_sync(2, kEpiThreads);
+            if (elected) {
+              for (int pnl = 0; pnl < BT / 64; ++pnl) {
+                if (tc.n0 + pnl * 64 >= P.N) break;
+                tma_store_3d(&P.out[1], cx.staging + pnl * (kBM * 128), P.oi[1].col_off + tc.n0 + pnl * 64,
+                             P.oi[1].row_off + tc.m0, P.oi[1].batch_off + tc.batch);
+              }
+              bulk_commit_group();
+            }
+          }
+        }
+        if (elected) issue_residual(tile + gridDim.x);
+      }
+    }
+    if constexpr (NOUT > 0) {
+      if (elected) bulk_wait_all();  // this CTA's output tiles are in global memory
+      if (elected) cx.stamp(3, 3);
+    }
+  }
+  return failed;
+}
+
+// Carves barriers out of shared memory behind a ring of `ring` stages of `stage_stride` bytes,
+// initialises them and allocates `tmem_cols` columns of tensor memory.  Ends with a CTA-wide sync.
+__device__ __forceinline__ void gemm_setup(GemmCtx& cx, uint8_t* smem_raw, int ring, uint32_t stage_stride,
+                                           uint32_t staging_bytes, uint32_t tmem_cols) {
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  cx.smem_base = (raw_addr + 1023u) & ~1023u;
+  cx.stage_stride = stage_stride;
+  cx.staging = cx.smem_base + ring * stage_stride;
+  uint8_t* aligned = smem_raw + (cx.smem_base - raw_addr);
+  cx.full_bar = reinterpret_cast<uint64_t*>(aligned + ring * stage_stride + staging_bytes);
+  cx.empty_bar = cx.full_bar + ring;
+  cx.acc_full_bar = cx.empty_bar + ring;    // [2]
+  cx.acc_empty_bar = cx.acc_full_bar + 2;   // [2]
+  cx.res_bar = cx.acc_empty_bar + 2;        // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(cx.res_bar + 1);
+  cx.abort_flag = tmem_slot + 1;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < ring; ++s) {
+      mbar_init(&cx.full_bar[s], 1);
+      mbar_init(&cx.empty_bar[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&cx.acc_full_bar[s], 1);
+      mbar_init(&cx.acc_empty_bar[s], kEpiWarps);
+    }
+    mbar_init(cx.res_bar, 1);
+    cx.abort_flag[0] = 0;
+    cx.abort_flag[1] = 0;
     fence_mbar_init();
   }
-  if (warp == 0 && lane == 0) {
-#pragma unroll
-    for (int i = 0; i < NA; ++i) tma_prefetch_desc(&P.a[i]);
-#pragma unroll
-    for (int i = 0; i < NB; ++i) tma_prefetch_desc(&P.b[i]);
-  }
-  if (warp == 1) {
-    tmem_alloc(tmem_slot, kTmemCols);
+  if ((threadIdx.x >> 5) == 1) {
+    tmem_alloc(tmem_slot, tmem_cols);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
+  cx.tmem_base = *tmem_slot;
+}
 
-  bool failed = false;
-  if (warp == 0) {
-    // ---------------- TMA producer
-    if (lane == 0) {
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (kb / STAGES) & 1;
-        if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag)) { failed = true; break; }
-        mbar_expect_tx(&full_bar[s], kStageBytes);
-        const uint32_t st = smem_base + s * kStageBytes;
-        const int kc = kb * kBK;
-#pragma unroll
-        for (int i = 0; i < NA; ++i)
-          load_operand_tile<kBM>(st + i * kATileBytes, &P.a[i], P.ai[i], m0, kc, batch, &full_bar[s]);
-#pragma unroll
-        for (int i = 0; i < NB; ++i)
-          load_operand_tile<BN>(st + NA * kATileBytes + i * kBTileBytes, &P.b[i], P.bi[i], n0, kc, batch,
-                                &full_bar[s]);
-      }
-    }
-  } else if (warp == 1) {
-    // ---------------- MMA issuer (single thread)
-    if (lane == 0) {
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (kb / STAGES) & 1;
-        if (!mbar_wait(&full_bar[s], ph, abort_flag)) { failed = true; break; }
-        tc_fence_after();
-        const uint32_t st = smem_base + s * kStageBytes;
-#pragma unroll
-        for (int t = 0; t < Op::NTERMS; ++t) {
-          const int ia = Op::term_a(t), ib = Op::term_b(t), ic = Op::term_acc(t);
-          const int a_mn = P.ai[ia].mn_major, b_mn = P.bi[ib].mn_major;
-          const uint32_t idesc = make_idesc_bf16(kBM, BN, a_mn, b_mn);
-          const uint32_t a_tile = st + ia * kATileBytes;
-          const uint32_t b_tile = st + NA * kATileBytes + ib * kBTileBytes;
-#pragma unroll
-          for (int k4 = 0; k4 < kBK / kUmmaK; ++k4) {
-            const uint32_t acc = (kb > 0 || k4 > 0 || !Op::term_first(t)) ? 1u : 0u;
-            umma_bf16(tmem_base + ic * BN, operand_desc(a_tile, a_mn, k4), operand_desc(b_tile, b_mn, k4), idesc,
-                      acc);
-          }
-        }
-        umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
-      }
-      if (!failed) umma_commit(tmem_full_bar);
-    }
-  } else {
-    // ---------------- epilogue: warp w may only touch TMEM lanes [32*(w%4), 32*(w%4)+32)
-    const int quarter = warp & 3;
-    const int row = m0 + quarter * 32 + lane;
-    bool ok = true;
-    if (num_kb > 0) {
-      ok = mbar_wait(tmem_full_bar, 0, abort_flag);
-      tc_fence_after();
-    }
-    if (ok) {
-      for (int c = 0; c < BN; c += 32) {
-        if (n0 + c >= P.N) break;  // warp-uniform
-        float v[NACC][32];
-        if (num_kb > 0) {
-#pragma unroll
-          for (int a = 0; a < NACC; ++a) {
-            uint32_t bits[32];
-            tmem_ld32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * BN + c, bits);
-            tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[a][j] = __uint_as_float(bits[j]);
-          }
-        } else {
-#pragma unroll
-          for (int a = 0; a < NACC; ++a)
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[a][j] = 0.f;
-        }
-        Op::epilogue(P.ep, batch, row, n0 + c, P.M, P.N, v);
-      }
-    } else {
-      failed = true;
-    }
-  }
+__device__ __forceinline__ void gemm_teardown(GemmCtx& cx, bool failed, int32_t* status, uint32_t tmem_cols) {
   if (failed) {
-    *abort_flag = 1;
-    atomicCAS(args.status, kStatusOk, kStatusWaitTimeout);
+    *cx.abort_flag = 1;
+    atomicCAS(status, kStatusOk, kStatusWaitTimeout);
   }
   tc_fence_before();
   __syncthreads();
-  if (*abort_flag && threadIdx.x == 0) {
+  if (*cx.abort_flag && threadIdx.x == 0) {
     // let bulk copies still in flight land before shared memory is released
     for (int i = 0; i < 256; ++i) __nanosleep(1000);
   }
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+  if ((threadIdx.x >> 5) == 1) tmem_dealloc(cx.tmem_base, tmem_cols);
+}
+
+// Persistent single-phase kernel.
+template <class Op, int NPROB>
+__global__ void __launch_bounds__(kGemmThreadsV2, 1)
+umma_gemm_kernel(const __grid_constant__ GemmArgs<Op, NPROB> args, const int nprob) {
+  static_assert(NPROB <= 2, "at most two problems per launch");
+  if (*reinterpret_cast<volatile int32_t*>(args.status) != kStatusOk) return;  // an earlier launch gave up
+  extern __shared__ uint8_t smem_raw[];
+  constexpr uint32_t kTmemCols = tmem_cols_pow2(2 * Op::NACC * Op::BT);
+  GemmCtx cx;
+  gemm_setup(cx, smem_raw, Op::STAGES, gemm_stage_bytes<Op>(), gemm_staging_bytes<Op>(), kTmemCols);
+  if (threadIdx.x == 32) {
+    for (int p = 0; p < nprob; ++p) {
+#pragma unroll
+      for (int i = 0; i < Op::NA; ++i) tma_prefetch_desc(&args.prob[p].a[i]);
+#pragma unroll
+      for (int i = 0; i < Op::NB; ++i) tma_prefetch_desc(&args.prob[p].b[i]);
+#pragma unroll
+      for (int i = 0; i < Op::NOUT; ++i) tma_prefetch_desc(&args.prob[p].out[i]);
+    }
+  }
+  const bool failed = gemm_phase<Op, Op::STAGES>(cx, args.prob, nprob, NoPatch{});
+  gemm_teardown(cx, failed, args.status, kTmemCols);
 }
 
 }  // namespace lact
