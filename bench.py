@@ -58,6 +58,7 @@ def class_flops(name, B, D, H, C, ns_steps):
         "gemm_ns_gram": 2 * B * (m1 * m1 * n1 + m2 * m2 * n2),
         "gemm_ns_poly": 2 * B * (m1 ** 3 + m2 ** 3),
         "gemm_ns_update": 2 * B * (m1 * m1 * n1 + m2 * m2 * n2),
+        "ns_fused": ns_steps * 2 * B * (2 * (m1 * m1 * n1 + m2 * m2 * n2) + m1 ** 3 + m2 ** 3),
     }.get(name)
 
 
@@ -93,7 +94,11 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
+
+    def mark_load_start(self):
+        """Samples taken before this call (idle GPU) are left out of the summary."""
+        self.t_load = time.time()
 
     def __exit__(self, *exc):
         if self.proc is not None:
@@ -106,7 +111,10 @@ class ClockSampler:
     def summary(self):
         sm, mx, reasons = [], [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for ln in self.lines:
+        t_load = getattr(self, "t_load", 0.0)
+        for ts, ln in self.lines:
+            if ts < t_load + 0.05:
+                continue
             parts = [p.strip() for p in ln.split(",")]
             if len(parts) < 7:
                 continue
@@ -258,19 +266,28 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(warmup):
-        run_step(lact_b200, t)
-    lact_b200.synchronize_and_check()
-    barrier()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    launches0 = LL.launch_count()
     with ClockSampler(local_rank) as clocks:
+        # nvidia-smi needs a moment to start streaming: it is started before the warm-up and its
+        # samples from the warm-up onwards (GPU under the same load) are summarised
+        time.sleep(0.6)
+        clocks.mark_load_start()
+        for _ in range(warmup):
+            run_step(lact_b200, t)
+        lact_b200.synchronize_and_check()
+        barrier()
+        launches0 = LL.launch_count()
         ev0.record()
         for _ in range(steps):
             run_step(lact_b200, t)
         ev1.record()
         barrier()
-    launches = LL.launch_count() - launches0
+        launches = LL.launch_count() - launches0
+        if ev0.elapsed_time(ev1) < 400.0:  # keep the GPU under the same load until a few samples exist
+            t_end = time.time() + 0.4
+            while time.time() < t_end:
+                run_step(lact_b200, t)
+            torch.cuda.synchronize()
     lact_b200.synchronize_and_check()
     ms = torch.tensor([ev0.elapsed_time(ev1)], device=dev, dtype=torch.float64)
     if world > 1:

@@ -394,7 +394,7 @@ def test_scan_state_in_and_out(lb, orc):
         outs.append(r[0])
         w0, w1, w2, m = r[1], r[2], r[3], r[4:]
     o = torch.cat(outs, dim=1)
-    close(orc, o, full[0], tol=2e-3, cos=0.99999, what="stateful replay")
+    close(orc, o, full[0], tol=1e-2, cos=0.99999, what="stateful replay")  # one bf16 ulp at the largest output
     close(orc, w0, full[1], tol=1e-3, what="stateful replay w0")
 
 
