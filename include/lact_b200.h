@@ -83,6 +83,9 @@ typedef struct lact_scan_io {
   void *o;                           /* [B, out_len, D], act_dtype */
   void *w0_out, *w1_out, *w2_out;    /* final fast weights, fp32, or NULL */
   void *m0_out, *m1_out, *m2_out;    /* final momentum state, fp32, or NULL */
+  /* training: per UPDATE step u (in program order), fp32 [w0w2 | w1 | g0g2 | g1] with w = the weights
+   * that step computed with ([B,2H,D], [B,D,H]) and g = its gradient after momentum; or NULL */
+  void *state_dump;
 } lact_scan_io;
 
 /* Library version (major * 1000 + minor).  No counterpart in the reference. */
@@ -186,6 +189,32 @@ int lact_l2_norm_add(const void *x, int32_t x_dtype, const void *x_add, int32_t 
 int lact_prenorm_momentum_l2norm(const void *x, const void *dx, const void *m, const void *mu, const void *scale,
                                  void *x_out, void *m_out, void *y_out, int64_t B, int64_t T, int64_t D, float eps,
                                  void *stream);
+
+/* Building blocks of the training backward (the reference's backward is autograd through
+ * lact_swiglu_ffn.py:46-76, lact_fw_grad.py:61-156 and the eager momentum / Newton-Schulz / renorm ops).
+ *
+ * lact_bmm2_bf16: c[batch, M, N] (+)= a0 b0^T (+ a1 b1^T), bf16 operands (each [batch, rows, K] or, MN-major,
+ *   [batch, K, rows]), fp32 accumulation; c_dtype fp32 (optionally accumulating into c) or bf16.
+ *   Replaces torch.bmm and fused_two_mm_wT_x / fused_two_mm_wT_xT (triton_fused_matmul_kernels.py:46-291).
+ * lact_swiglu_bwd_planes: from y0|y2 [rows, 2H] and dh [rows, H] (bf16) the planes dy0*lr0 | dy2*lr2 and hidden*lr1
+ *   (swiglu_backward_three_bmm pointwise part, triton_swiglu_bwd_kernels.py:140-165); lr pointers may be NULL (= 1).
+ * lact_fw_grad_bwd_pointwise: second-order pointwise stage (lact_fw_grad.py:178-260 /
+ *   triton_pointwise_kernels.py:6-236) with deterministic row sums for the lr gradients.
+ * lact_renorm_bwd: backward of the row renormalisation of w = base + upd (ttt_operation.py:193-200 /
+ *   l2norm_triton_kernels.py:97-172); dn0[row] += d<y>/dn0. */
+int lact_bmm2_bf16(const void *a0, int32_t a0_mn_major, const void *b0, int32_t b0_mn_major, const void *a1,
+                   int32_t a1_mn_major, const void *b1, int32_t b1_mn_major, void *c, int32_t c_dtype,
+                   int32_t accumulate, int64_t batch, int64_t M, int64_t N, int64_t K, int32_t *status_word,
+                   void *stream);
+int lact_swiglu_bwd_planes(const void *y02, const void *dh, const void *lr0, const void *lr1, const void *lr2,
+                           int32_t lr_dtype, float w_scale, void *dy02, void *hid, int64_t rows, int64_t H,
+                           void *stream);
+int lact_fw_grad_bwd_pointwise(const void *y02, const void *dh, const void *g_dy02, const void *g_hid,
+                               const void *lr0, const void *lr1, const void *lr2, int32_t lr_dtype, float w_scale,
+                               void *g_y02, void *g_dh, void *dy02, void *hid, void *g_lr0, void *g_lr1, void *g_lr2,
+                               int64_t rows, int64_t H, void *stream);
+int lact_renorm_bwd(const void *base, const void *upd, int32_t upd_dtype, const void *n0, const void *dy, void *dw,
+                    void *dn0, int64_t rows, int64_t C, int32_t mode, void *stream);
 
 /* c[batch, M, N] = a * b^T with bf16 operands and fp32 accumulation (c_dtype output).
  * a is [batch, M, K] (a_mn_major = 0) or [batch, K, M] (a_mn_major = 1); b likewise with N.

@@ -28,7 +28,7 @@ class ScanConfig(C.Structure):
 class ScanIO(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in ("w0", "w1", "w2", "q", "k", "v", "lr0", "lr1", "lr2", "momentum", "m0_in",
                                           "m1_in", "m2_in", "o", "w0_out", "w1_out", "w2_out", "m0_out", "m1_out",
-                                          "m2_out")]
+                                          "m2_out", "state_dump")]
 
 
 _lib: Optional[C.CDLL] = None
@@ -65,10 +65,16 @@ def _declare(lib: C.CDLL) -> None:
     lib.lact_l2_norm_add.argtypes = [vp, i32, vp, i32, vp, vp, i32, i64, i64, i64, f32, vp]
     lib.lact_prenorm_momentum_l2norm.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, f32, vp]
     lib.lact_bmm_bf16.argtypes = [vp, i32, vp, i32, vp, i32, i64, i64, i64, i64, vp, vp]
+    lib.lact_bmm2_bf16.argtypes = [vp, i32, vp, i32, vp, i32, vp, i32, vp, i32, i32, i64, i64, i64, i64, vp, vp]
+    lib.lact_swiglu_bwd_planes.argtypes = [vp, vp, vp, vp, vp, i32, f32, vp, vp, i64, i64, vp]
+    lib.lact_fw_grad_bwd_pointwise.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, f32, vp, vp, vp, vp, vp, vp, vp, i64,
+                                               i64, vp]
+    lib.lact_renorm_bwd.argtypes = [vp, vp, i32, vp, vp, vp, vp, i64, i64, i32, vp]
     for name in ("lact_read_status", "lact_scan_workspace_bytes", "lact_scan_fwd", "lact_swiglu_ffn_workspace_bytes",
                  "lact_swiglu_ffn_fwd", "lact_fw_grad_workspace_bytes", "lact_fw_grad",
                  "lact_newton_schulz_workspace_bytes", "lact_newton_schulz", "lact_l2_norm_add",
-                 "lact_prenorm_momentum_l2norm", "lact_bmm_bf16"):
+                 "lact_prenorm_momentum_l2norm", "lact_bmm_bf16", "lact_bmm2_bf16", "lact_swiglu_bwd_planes",
+                 "lact_fw_grad_bwd_pointwise", "lact_renorm_bwd"):
         getattr(lib, name).restype = C.c_int
 
 

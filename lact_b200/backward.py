@@ -1,0 +1,313 @@
+"""Training backward of the chunk recurrence, chunk by chunk in reverse.
+
+Host orchestration in Python; every contraction runs on the tcgen05 GEMM engine
+(`lact_bmm2_bf16`) and every pointwise stage in a CUDA kernel of the library.  The structure
+follows the reference's hand-written backward of its two fused autograd Functions
+(lact_llm/lact_model/lact_triton_kernels/lact_swiglu_ffn.py:46-76 and lact_fw_grad.py:61-156) and
+autograd through the eager momentum / renormalisation lines (ttt_operation.py:170-200).
+Like the reference's, the backward recomputes pre-activations in bf16 and returns bf16 gradients
+for activations, fp32 for learning rates, momentum and fast weights.
+
+Supported: post-norm recurrences (renorm none / eps outside / eps inside), momentum, any step
+program, Muon on or off (Newton-Schulz is recomputed in the backward; its roundings are treated as
+identities).  Pre-norm and the bidirectional overwrite are not built yet: they raise
+NotImplementedError when gradients are requested.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from . import _lib as L
+from . import program as P
+
+BF16 = torch.bfloat16
+_status: Dict[int, torch.Tensor] = {}
+
+
+def _status_word(dev: torch.device) -> torch.Tensor:
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    if idx not in _status:
+        _status[idx] = torch.zeros(64, dtype=torch.int32, device=dev)
+    return _status[idx]
+
+
+def check_status(dev: torch.device) -> None:
+    st = int(_status_word(dev)[0].item())
+    if st != 0:
+        raise L.LactError(f"device status {st} during backward")
+
+
+def gemm(a, b, a_mn=False, b_mn=False, a1=None, b1=None, a1_mn=False, b1_mn=False, out=None,
+         out_dtype=torch.float32, accumulate=False):
+    """c[batch, M, N] (+)= a b^T (+ a1 b1^T).  Operands bf16, [batch, rows, K] or (``*_mn``) [batch, K, rows]."""
+    a, b = a.contiguous(), b.contiguous()
+    batch = a.shape[0]
+    M, K = (a.shape[2], a.shape[1]) if a_mn else (a.shape[1], a.shape[2])
+    N = b.shape[2] if b_mn else b.shape[1]
+    if out is None:
+        out = torch.empty(batch, M, N, dtype=out_dtype, device=a.device)
+    if a1 is not None:
+        a1, b1 = a1.contiguous(), b1.contiguous()
+    st = _status_word(a.device)
+    rc = L.lib().lact_bmm2_bf16(a.data_ptr(), int(a_mn), b.data_ptr(), int(b_mn),
+                                a1.data_ptr() if a1 is not None else None, int(a1_mn),
+                                b1.data_ptr() if b1 is not None else None, int(b1_mn), out.data_ptr(),
+                                L.dtype_code(out), int(accumulate), batch, M, N, K, st.data_ptr(), L.stream_ptr())
+    L.check(rc, "lact_bmm2_bf16")
+    return out
+
+
+def _vecptr(t: Optional[torch.Tensor]):
+    return t.data_ptr() if t is not None else None
+
+
+def apply_backward(w02b, w1b, q, dO, dW02, dW1):
+    """Backward of o = w1 (silu(w0 q) * (w2 q)) on one token range.  Accumulates the weight gradients
+    (fp32) into dW02 / dW1 and returns dq (bf16).  lact_swiglu_ffn.py:46-76."""
+    B, n, D = q.shape
+    H = w1b.shape[2]
+    y02 = gemm(q, w02b, out_dtype=BF16)                      # [B, n, 2H]
+    dh = gemm(dO, w1b, b_mn=True, out_dtype=BF16)            # [B, n, H]   dO w1
+    dy02 = torch.empty_like(y02)
+    hid = torch.empty_like(dh)
+    L.check(L.lib().lact_swiglu_bwd_planes(y02.data_ptr(), dh.data_ptr(), None, None, None, L.LACT_F32, 1.0,
+                                           dy02.data_ptr(), hid.data_ptr(), B * n, H, L.stream_ptr()),
+            "lact_swiglu_bwd_planes")
+    gemm(dy02, q, a_mn=True, b_mn=True, out=dW02, accumulate=True)   # [2H, D] += dy02^T q
+    gemm(dO, hid, a_mn=True, b_mn=True, out=dW1, accumulate=True)    # [D, H]  += dO^T hidden
+    return gemm(dy02, w02b, b_mn=True, out_dtype=BF16)               # dq = dy02 w02
+
+
+def fw_grad_backward(w02b, w1b, k, v, lr0, lr1, lr2, w_scale, gG02, gG1, dW02, dW1):
+    """Backward of the lr-weighted fast-weight gradient on one token range, given the gradients gG02
+    ([B,2H,D]) / gG1 ([B,D,H]) of its outputs.  Accumulates into dW02 / dW1; returns
+    (dk, dv [bf16], dlr0, dlr1, dlr2 [fp32, B x n]).  lact_fw_grad.py:61-156."""
+    B, n, D = k.shape
+    H = w1b.shape[2]
+    g02b, g1b = gG02.to(BF16), gG1.to(BF16)
+    y02 = gemm(k, w02b, out_dtype=BF16)
+    dh = gemm(v, w1b, b_mn=True, out_dtype=BF16)
+    g_dy02 = gemm(k, g02b, out_dtype=BF16)                   # [B, n, 2H]
+    g_hid = gemm(v, g1b, b_mn=True, out_dtype=BF16)          # [B, n, H]
+    g_y02, dy02l = torch.empty_like(y02), torch.empty_like(y02)
+    g_dh, hidl = torch.empty_like(dh), torch.empty_like(dh)
+    glr = [torch.empty(B, n, dtype=torch.float32, device=k.device) for _ in range(3)]
+    lr0, lr1, lr2 = lr0.contiguous(), lr1.contiguous(), lr2.contiguous()
+    L.check(L.lib().lact_fw_grad_bwd_pointwise(
+        y02.data_ptr(), dh.data_ptr(), g_dy02.data_ptr(), g_hid.data_ptr(), lr0.data_ptr(), lr1.data_ptr(),
+        lr2.data_ptr(), L.dtype_code(lr0), float(w_scale), g_y02.data_ptr(), g_dh.data_ptr(), dy02l.data_ptr(),
+        hidl.data_ptr(), glr[0].data_ptr(), glr[1].data_ptr(), glr[2].data_ptr(), B * n, H, L.stream_ptr()),
+        "lact_fw_grad_bwd_pointwise")
+    dk = gemm(g_y02, w02b, b_mn=True, a1=dy02l, b1=g02b, b1_mn=True, out_dtype=BF16)
+    dv = gemm(g_dh, w1b, a1=hidl, b1=g1b, out_dtype=BF16)
+    gemm(g_y02, k, a_mn=True, b_mn=True, out=dW02, accumulate=True)
+    gemm(v, g_dh, a_mn=True, b_mn=True, out=dW1, accumulate=True)
+    return dk, dv, glr[0], glr[1], glr[2]
+
+
+def renorm_backward(base, upd, n0, dy, dn0, mode):
+    """dw for y = renorm(base + upd); adds the n0 gradient into dn0.  Rows = all leading dims."""
+    C_ = base.shape[-1]
+    rows = base.numel() // C_
+    dw = torch.empty_like(base)
+    upd = upd.contiguous()
+    L.check(L.lib().lact_renorm_bwd(base.data_ptr(), upd.data_ptr(), L.dtype_code(upd), n0.data_ptr(), dy.data_ptr(),
+                                    dw.data_ptr(), _vecptr(dn0), rows, C_, int(mode), L.stream_ptr()),
+            "lact_renorm_bwd")
+    return dw
+
+
+NS_TUNED5 = ((4.0848, -6.8946, 2.9270), (3.9505, -6.3029, 2.6377), (3.7418, -5.5913, 2.3037),
+             (2.8769, -3.1427, 1.2046), (2.8366, -3.0525, 1.2012))
+NS_CONST = (3.4445, -4.7750, 2.0315)
+
+
+def ns_forward_saved(G, steps, const_coeffs, gram_right):
+    """Recomputes the Newton-Schulz iteration on G [nmat, R, C] keeping every iterate (bf16, with
+    the reference's rounding points, zeropower_via_newtonschulz5 in ttt_operation.py:30-66 /
+    lact_nvs/lact_ttt.py:32-67).  GEMMs on the tcgen05 engine; the elementwise combinations are
+    small (matrix-sized) tensor ops.  Returns a dict used by `ns_backward` and the result U in
+    G's orientation (bf16)."""
+    coeffs = [NS_CONST] * steps if const_coeffs else list(NS_TUNED5)
+    R, Cc = G.shape[1], G.shape[2]
+    flip = R > Cc or (R == Cc and gram_right)
+    Gb = G.to(BF16)
+    nrm = Gb.float().pow(2).sum(dim=(1, 2), keepdim=True).sqrt().to(BF16)
+    den = (nrm.float() + 1e-7).to(BF16)
+    Xg = (Gb.float() / den.float()).to(BF16)                  # normalised, G's orientation
+    X = Xg.transpose(1, 2).contiguous() if flip else Xg
+    its = []
+    for a, b, c in coeffs:
+        A = gemm(X, X, out_dtype=BF16)                        # X X^T
+        cA = (c * A.float()).to(BF16)
+        Pm = ((b * A.float()).to(BF16).float() + gemm(cA, A, out_dtype=BF16).float()).to(BF16)
+        Xn = ((a * X.float()).to(BF16).float() + gemm(Pm, X, b_mn=True, out_dtype=BF16).float()).to(BF16)
+        its.append((X, A, Pm, (a, b, c)))
+        X = Xn
+    U = X.transpose(1, 2).contiguous() if flip else X
+    return dict(its=its, flip=flip, Gb=Gb, den=den.float(), nrm=nrm.float()), U
+
+
+def ns_backward(saved, dU):
+    """Gradient w.r.t. G of U = NS(G) given dU (fp32, G's orientation); roundings are treated as
+    identities, operands of every contraction are bf16 as in the reference's autograd."""
+    dX = dU.transpose(1, 2).contiguous() if saved["flip"] else dU
+    dX = dX.float()
+    for X, A, Pm, (a, b, c) in reversed(saved["its"]):
+        dXb = dX.to(BF16)
+        dP = gemm(dXb, X)                                     # dX' X^T            [m, m] fp32
+        dXn = a * dX + gemm(Pm, dXb, b_mn=True)               # a dX' + P dX'      (P symmetric)
+        dPb = dP.to(BF16)
+        dA = b * dP + c * (gemm(dPb, A) + gemm(A, dPb, b_mn=True))   # b dP + c (dP A + A dP)
+        S = (dA + dA.transpose(1, 2)).to(BF16)
+        dX = dXn + gemm(S, X, b_mn=True)                      # + (dA + dA^T) X
+    dX0 = dX.transpose(1, 2) if saved["flip"] else dX         # back to G's orientation
+    Gf, den, nrm = saved["Gb"].float(), saved["den"], saved["nrm"]
+    dot = (dX0 * Gf).sum(dim=(1, 2), keepdim=True)
+    return dX0 / den - Gf * dot / (den * den * nrm.clamp_min(1e-30))
+
+
+class ScanFunction(torch.autograd.Function):
+    """Differentiable wrapper of the chunk recurrence (LLM layout).  `opts` is the keyword
+    dictionary of `lact_b200.ops.scan`."""
+
+    @staticmethod
+    def forward(ctx, opts, steps, w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum):
+        from . import ops
+        if opts.get("prenorm") or opts.get("overwrite_quirk"):
+            raise NotImplementedError("gradients are implemented for post-norm recurrences only (no pre-norm, no "
+                                      "bidirectional overwrite); call under torch.no_grad() for inference")
+        n_upd = sum(1 for s in steps if s[0] == P.UPDATE)
+        B, Ltok, D = k.shape
+        H = w0.shape[1]
+        per = 2 * (B * 2 * H * D + B * D * H)
+        dump = torch.empty(max(n_upd, 1), per, dtype=torch.float32, device=q.device)
+        with torch.no_grad():
+            res = ops.scan(w0, w1, w2, q, k, v, lr0, lr1, lr2, steps, momentum=momentum, return_state=True,
+                           _state_dump=dump, **{k_: v_ for k_, v_ in opts.items() if k_ != "return_state"})
+        o, wf0, wf1, wf2 = res[:4]
+        ctx.opts, ctx.steps, ctx.n_upd = dict(opts), list(steps), n_upd
+        ctx.save_for_backward(w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum if momentum is not None else q.new_zeros(1),
+                              dump, wf0, wf1, wf2)
+        ctx.has_momentum = momentum is not None
+        ctx.mark_non_differentiable(wf0, wf1, wf2)
+        return o, wf0, wf1, wf2
+
+    @staticmethod
+    def backward(ctx, dO, *_unused):
+        w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, dump, wf0, wf1, wf2 = ctx.saved_tensors
+        opts, steps, n_upd = ctx.opts, ctx.steps, ctx.n_upd
+        dev = q.device
+        B, Ltok, D = k.shape
+        H = w0.shape[1]
+        n02, n1 = B * 2 * H * D, B * D * H
+        mode = int(opts.get("renorm", L.RENORM_EPS_OUTSIDE))
+        w_scale = float(opts.get("w_scale", 1.0))
+        f32 = torch.float32
+        vec = lambda t: (t[..., 0] if t.dim() == 3 else t).contiguous()
+        lr0v, lr1v, lr2v = vec(lr0), vec(lr1), vec(lr2)
+        momv = vec(momentum).float() if ctx.has_momentum else None
+        W0_02 = torch.cat([w0, w2], dim=1).float().contiguous()
+        W0_1 = w1.float().contiguous()
+        n0_02 = W0_02.norm(dim=2).contiguous()
+        n0_1 = W0_1.norm(dim=2).contiguous()
+
+        def weights(cnt):
+            """fp32 (W02, W1) in force after `cnt` updates."""
+            if cnt == 0:
+                return W0_02, W0_1
+            if cnt < n_upd:
+                return dump[cnt, :n02].view(B, 2 * H, D), dump[cnt, n02:n02 + n1].view(B, D, H)
+            return torch.cat([wf0, wf2], dim=1).contiguous(), wf1.contiguous()
+
+        def grad_state(u):
+            """fp32 gradient after momentum of update u (= momentum state after it)."""
+            base = n02 + n1
+            return dump[u, base:base + n02].view(B, 2 * H, D), dump[u, base + n02:base + n02 + n1].view(B, D, H)
+
+        dW02 = torch.zeros(B, 2 * H, D, dtype=f32, device=dev)
+        dW1 = torch.zeros(B, D, H, dtype=f32, device=dev)
+        dM02 = dM1 = None
+        dn02 = torch.zeros(B, 2 * H, dtype=f32, device=dev)
+        dn1 = torch.zeros(B, D, dtype=f32, device=dev)
+        dq = torch.zeros_like(q, dtype=BF16)
+        dk = torch.zeros_like(k, dtype=BF16)
+        dv = torch.zeros_like(v, dtype=BF16)
+        dlr = [torch.zeros(B, Ltok, dtype=f32, device=dev) for _ in range(3)]
+        dmom = torch.zeros(B, Ltok, dtype=f32, device=dev) if ctx.has_momentum else None
+        dO = dO.to(BF16)
+
+        cnt = n_upd
+        shadows = {}
+
+        def shadow(c_):
+            if c_ not in shadows:
+                shadows.clear()
+                a, b = weights(c_)
+                shadows[c_] = (a.to(BF16).contiguous(), b.to(BF16).contiguous())
+            return shadows[c_]
+
+        for kind, s, e, o_s in reversed(steps):
+            if e <= s:
+                continue
+            if kind == P.APPLY:
+                w02b, w1b = shadow(cnt)
+                dq[:, s:e] += apply_backward(w02b, w1b, q[:, s:e].contiguous(),
+                                             dO[:, o_s:o_s + (e - s)].contiguous(), dW02, dW1)
+                continue
+            u = cnt - 1
+            Wp02, Wp1 = weights(u)
+            G02, G1 = grad_state(u)
+            # update applied to the weights: the gradient itself, or its Newton-Schulz image (recomputed)
+            U02, U1, sv02, sv1 = G02.contiguous(), G1.contiguous(), None, None
+            if opts.get("use_muon"):
+                nst, cc, gr = int(opts.get("ns_steps", 5)), bool(opts.get("ns_const_coeffs")), bool(opts.get("ns_gram_right"))
+                g02m = G02.contiguous() if opts.get("ns_concat") else G02.contiguous().view(2 * B, H, D)
+                sv02, U02 = ns_forward_saved(g02m, nst, cc, gr)
+                sv1, U1 = ns_forward_saved(G1.contiguous(), nst, cc, gr)
+                U02 = U02.view(B, 2 * H, D)
+            # renorm backward; dW becomes the gradient w.r.t. W_u
+            dWn02 = renorm_backward(Wp02.contiguous(), U02, n0_02, dW02, dn02, mode)
+            dWn1 = renorm_backward(Wp1.contiguous(), U1, n0_1, dW1, dn1, mode)
+            if sv02 is not None:
+                dG02 = ns_backward(sv02, dWn02.view(sv02["Gb"].shape)).view(B, 2 * H, D)
+                dG1 = ns_backward(sv1, dWn1)
+            else:
+                dG02, dG1 = dWn02.clone(), dWn1.clone()
+            if dM02 is not None:
+                dG02 += dM02
+                dG1 += dM1
+            dW02, dW1 = dWn02, dWn1
+            if ctx.has_momentum:
+                beta = momv[:, s:e].mean(dim=1)  # [B]
+                if u > 0:
+                    Mp02, Mp1 = grad_state(u - 1)
+                    dbeta = (dG02 * Mp02).sum(dim=(1, 2)) + (dG1 * Mp1).sum(dim=(1, 2))
+                    dmom[:, s:e] += (dbeta / float(e - s)).unsqueeze(1)
+                dM02, dM1 = dG02 * beta.view(B, 1, 1), dG1 * beta.view(B, 1, 1)
+            w02b, w1b = shadow(u)
+            gk, gv, g0, g1, g2 = fw_grad_backward(w02b, w1b, k[:, s:e].contiguous(), v[:, s:e].contiguous(),
+                                                  lr0v[:, s:e], lr1v[:, s:e], lr2v[:, s:e], w_scale, dG02, dG1,
+                                                  dW02, dW1)
+            dk[:, s:e] += gk
+            dv[:, s:e] += gv
+            dlr[0][:, s:e] += g0
+            dlr[1][:, s:e] += g1
+            dlr[2][:, s:e] += g2
+            cnt = u
+        check_status(dev)
+        # the target row norms are functions of the initial weights (not detached in the LLM / AR paths)
+        if not opts.get("_detach_norms", False):
+            dW02 = dW02 + dn02.unsqueeze(-1) * W0_02 / n0_02.clamp_min(1e-30).unsqueeze(-1)
+            dW1 = dW1 + dn1.unsqueeze(-1) * W0_1 / n0_1.clamp_min(1e-30).unsqueeze(-1)
+        dw0, dw2 = dW02[:, :H].to(w0.dtype), dW02[:, H:].to(w2.dtype)
+        shape = lambda g, ref: g.view(ref.shape).to(ref.dtype) if ref.dim() == 3 else g.to(ref.dtype)
+        grads = (None, None, dw0, dW1.to(w1.dtype), dw2, dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype),
+                 shape(dlr[0].unsqueeze(-1) if lr0.dim() == 3 else dlr[0], lr0),
+                 shape(dlr[1].unsqueeze(-1) if lr1.dim() == 3 else dlr[1], lr1),
+                 shape(dlr[2].unsqueeze(-1) if lr2.dim() == 3 else dlr[2], lr2),
+                 shape(dmom.unsqueeze(-1) if momentum.dim() == 3 else dmom, momentum) if ctx.has_momentum else None)
+        return grads

@@ -240,6 +240,7 @@ int launch_op(int bt, Fill&& fill, cudaStream_t stream, int cls, int nprob) {
 }
 template <int BT> using OpDWT = OpBmm<EpiDW, BT>;
 template <int BT> using OpStoreDirectT = OpBmm<EpiStore, BT>;
+template <int BT> using OpStore2T = OpBmm2<EpiStore, BT>;
 
 // ------------------------------------------------------------------------------------------
 // building blocks (device pointers in, kernels enqueued)
@@ -796,10 +797,23 @@ int scan_fwd(const lact_scan_config& c, const lact_scan_io& io, int32_t n_steps,
       continue;
     }
     const float* beta = c.use_momentum ? p.beta + static_cast<int64_t>(update_idx) * B : nullptr;
+    float* dump = nullptr;
+    if (io.state_dump != nullptr) {
+      // training: weights used by this update and (below) its gradient after momentum
+      const size_t n02 = static_cast<size_t>(B) * 2 * H * D, n1 = static_cast<size_t>(B) * D * H;
+      dump = static_cast<float*>(io.state_dump) + static_cast<size_t>(update_idx) * 2 * (n02 + n1);
+      LACT_CUDA(cudaMemcpyAsync(dump, c.prenorm ? p.W02c : p.W02, n02 * 4, cudaMemcpyDeviceToDevice, stream));
+      LACT_CUDA(cudaMemcpyAsync(dump + n02, c.prenorm ? p.W1c : p.W1, n1 * 4, cudaMemcpyDeviceToDevice, stream));
+    }
     ++update_idx;
     GradArgs g{p.W02b, p.W1b, io.k, io.v, c.k_bs, c.k_ts, c.v_bs, c.v_ts, start[i], end[i], io.lr0, io.lr1, io.lr2,
                c.lr_dtype == LACT_F32, c.L, c.w_scale, p.dy02, p.hid, p.G02, p.G1, 1, beta, B, D, H};
     LACT_TRY(run_grad(g, p.status, stream));
+    if (dump != nullptr) {
+      const size_t n02 = static_cast<size_t>(B) * 2 * H * D, n1 = static_cast<size_t>(B) * D * H;
+      LACT_CUDA(cudaMemcpyAsync(dump + n02 + n1, p.G02, n02 * 4, cudaMemcpyDeviceToDevice, stream));
+      LACT_CUDA(cudaMemcpyAsync(dump + 2 * n02 + n1, p.G1, n1 * 4, cudaMemcpyDeviceToDevice, stream));
+    }
 
     // add + renormalise arguments (the update is the Newton-Schulz result when Muon is on)
     const bool want_compute = c.prenorm || !has_later_update(kind, n_steps, i);
@@ -1103,6 +1117,108 @@ int lact_prenorm_momentum_l2norm(const void* x, const void* dx, const void* m, c
   return LACT_OK;
 }
 
+int lact_bmm2_bf16(const void* a0, int32_t a0_mn, const void* b0, int32_t b0_mn, const void* a1, int32_t a1_mn,
+                   const void* b1, int32_t b1_mn, void* c, int32_t c_dtype, int32_t accumulate, int64_t batch,
+                   int64_t M, int64_t N, int64_t K, int32_t* status_word, void* stream) {
+  if (!a0 || !b0 || !c || !status_word || ((a1 == nullptr) != (b1 == nullptr))) return LACT_ERR_NULL;
+  LACT_TRY(check_device());
+  if (batch < 1 || batch > 65535 || M < 1 || N < 8 || K < 1 || (N % 8)) return LACT_ERR_SHAPE;
+  // the contiguous axis of every operand must be a multiple of 8 elements (16-byte TMA strides)
+  if (((a0_mn || (a1 && a1_mn)) && (M % 8)) || ((!a0_mn || (a1 && !a1_mn) || !b0_mn || (b1 && !b1_mn)) && (K % 8)))
+    return LACT_ERR_SHAPE;
+  if (accumulate && c_dtype != LACT_F32) return LACT_ERR_DTYPE;
+  auto mat = [&](const void* p, int mn, int64_t rows) {
+    return mn ? Mat{p, K, rows, rows, batch, K * rows} : Mat{p, rows, K, K, batch, rows * K};
+  };
+  const int bt = choose_bt({{N, 1}});
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const EpiStore ep{c, M * N, N, 0, c_dtype == LACT_F32, accumulate};
+  if (a1 == nullptr) {
+    auto fill = [&](auto& g, int btv) -> int {
+      auto& P = g.prob[0];
+      LACT_TRY(make_operand(&P.a[0], &P.ai[0], mat(a0, a0_mn, M), a0_mn, kBM, 0, 0));
+      LACT_TRY(make_operand(&P.b[0], &P.bi[0], mat(b0, b0_mn, N), b0_mn, btv, 0, 0));
+      P.M = static_cast<int>(M); P.N = static_cast<int>(N); P.K = static_cast<int>(K);
+      P.batch = static_cast<int>(batch);
+      P.ep = ep;
+      g.status = status_word;
+      return LACT_OK;
+    };
+    return launch_op<OpStoreDirectT, 1>(bt, fill, s, kClsOther, 1);
+  }
+  auto fill2 = [&](auto& g, int btv) -> int {
+    auto& P = g.prob[0];
+    LACT_TRY(make_operand(&P.a[0], &P.ai[0], mat(a0, a0_mn, M), a0_mn, kBM, 0, 0));
+    LACT_TRY(make_operand(&P.b[0], &P.bi[0], mat(b0, b0_mn, N), b0_mn, btv, 0, 0));
+    LACT_TRY(make_operand(&P.a[1], &P.ai[1], mat(a1, a1_mn, M), a1_mn, kBM, 0, 0));
+    LACT_TRY(make_operand(&P.b[1], &P.bi[1], mat(b1, b1_mn, N), b1_mn, btv, 0, 0));
+    P.M = static_cast<int>(M); P.N = static_cast<int>(N); P.K = static_cast<int>(K);
+    P.batch = static_cast<int>(batch);
+    P.ep = ep;
+    g.status = status_word;
+    return LACT_OK;
+  };
+  return launch_op<OpStore2T, 1>(std::min(bt, 192), fill2, s, kClsOther, 1);
+}
+
+static PlaneArgs make_plane_args(const void* y02, const void* dh, const void* g_dy02, const void* g_hid,
+                                 const void* lr0, const void* lr1, const void* lr2, int32_t lr_dtype, float w_scale,
+                                 void* dy02, void* hid, void* g_y02, void* g_dh, void* g_lr0, void* g_lr1, void* g_lr2,
+                                 int64_t rows, int64_t H) {
+  PlaneArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.y02 = static_cast<const bf16*>(y02); a.dh = static_cast<const bf16*>(dh);
+  a.g_dy02 = static_cast<const bf16*>(g_dy02); a.g_hid = static_cast<const bf16*>(g_hid);
+  a.lr0 = lr0; a.lr1 = lr1; a.lr2 = lr2; a.lr_f32 = lr_dtype == LACT_F32; a.w_scale = w_scale;
+  a.dy02 = static_cast<bf16*>(dy02); a.hid = static_cast<bf16*>(hid);
+  a.g_y02 = static_cast<bf16*>(g_y02); a.g_dh = static_cast<bf16*>(g_dh);
+  a.g_lr0 = static_cast<float*>(g_lr0); a.g_lr1 = static_cast<float*>(g_lr1); a.g_lr2 = static_cast<float*>(g_lr2);
+  a.rows = rows; a.H = static_cast<int32_t>(H);
+  return a;
+}
+
+int lact_swiglu_bwd_planes(const void* y02, const void* dh, const void* lr0, const void* lr1, const void* lr2,
+                           int32_t lr_dtype, float w_scale, void* dy02, void* hid, int64_t rows, int64_t H,
+                           void* stream) {
+  if (!y02 || !dh || !dy02 || !hid) return LACT_ERR_NULL;
+  if (rows < 1 || H < 1) return LACT_ERR_SHAPE;
+  const PlaneArgs a = make_plane_args(y02, dh, nullptr, nullptr, lr0, lr1, lr2, lr_dtype, w_scale, dy02, hid, nullptr,
+                                      nullptr, nullptr, nullptr, nullptr, rows, H);
+  KernelScope scope(kClsOther, static_cast<cudaStream_t>(stream));
+  swiglu_bwd_planes_kernel<<<ceil_div(rows, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  LACT_CUDA(cudaGetLastError());
+  return LACT_OK;
+}
+
+int lact_fw_grad_bwd_pointwise(const void* y02, const void* dh, const void* g_dy02, const void* g_hid, const void* lr0,
+                               const void* lr1, const void* lr2, int32_t lr_dtype, float w_scale, void* g_y02,
+                               void* g_dh, void* dy02, void* hid, void* g_lr0, void* g_lr1, void* g_lr2, int64_t rows,
+                               int64_t H, void* stream) {
+  if (!y02 || !dh || !g_dy02 || !g_hid || !lr0 || !lr1 || !lr2 || !g_y02 || !g_dh || !dy02 || !hid || !g_lr0 ||
+      !g_lr1 || !g_lr2)
+    return LACT_ERR_NULL;
+  if (rows < 1 || H < 1) return LACT_ERR_SHAPE;
+  const PlaneArgs a = make_plane_args(y02, dh, g_dy02, g_hid, lr0, lr1, lr2, lr_dtype, w_scale, dy02, hid, g_y02, g_dh,
+                                      g_lr0, g_lr1, g_lr2, rows, H);
+  KernelScope scope(kClsOther, static_cast<cudaStream_t>(stream));
+  fw_grad_bwd_pointwise_kernel<<<ceil_div(rows, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  LACT_CUDA(cudaGetLastError());
+  return LACT_OK;
+}
+
+int lact_renorm_bwd(const void* base, const void* upd, int32_t upd_dtype, const void* n0, const void* dy, void* dw,
+                    void* dn0, int64_t rows, int64_t C, int32_t mode, void* stream) {
+  if (!base || !upd || !n0 || !dy || !dw) return LACT_ERR_NULL;
+  if (rows < 1 || C < 1 || mode < 0 || mode > 2) return LACT_ERR_SHAPE;
+  RenormBwdArgs a{static_cast<const float*>(base), upd, upd_dtype == LACT_F32, static_cast<const float*>(n0),
+                  static_cast<const float*>(dy), static_cast<float*>(dw), static_cast<float*>(dn0), rows,
+                  static_cast<int32_t>(C), mode};
+  KernelScope scope(kClsOther, static_cast<cudaStream_t>(stream));
+  renorm_bwd_kernel<<<ceil_div(rows, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  LACT_CUDA(cudaGetLastError());
+  return LACT_OK;
+}
+
 int lact_bmm_bf16(const void* a, int32_t a_mn_major, const void* b, int32_t b_mn_major, void* c, int32_t c_dtype,
                   int64_t batch, int64_t M, int64_t N, int64_t K, int32_t* status_word, void* stream) {
   if (!a || !b || !c || !status_word) return LACT_ERR_NULL;
@@ -1116,7 +1232,7 @@ int lact_bmm_bf16(const void* a, int32_t a_mn_major, const void* b, int32_t b_mn
     LACT_TRY(make_operand(&P.b[0], &P.bi[0], Bm, b_mn_major, btv, 0, 0));
     P.M = static_cast<int>(M); P.N = static_cast<int>(N); P.K = static_cast<int>(K);
     P.batch = static_cast<int>(batch);
-    P.ep = EpiStore{c, M * N, N, 0, 1};
+    P.ep = EpiStore{c, M * N, N, 0, 1, 0};
     g.status = status_word;
     return LACT_OK;
   };

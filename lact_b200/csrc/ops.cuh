@@ -63,12 +63,30 @@ struct EpiStore {
   int64_t bs, ld;
   int32_t row_off;
   int32_t f32;
+  int32_t accumulate;  // fp32 only: out += acc (each element is owned by exactly one thread)
   __device__ __forceinline__ void operator()(int batch, int row, int col, int M, int N, const float* v) const {
     if (row >= M) return;
     const int valid = min(32, N - col);
     const int64_t idx = batch * bs + static_cast<int64_t>(row + row_off) * ld + col;
-    if (f32) store_row32_f32(reinterpret_cast<float*>(out) + idx, v, valid);
-    else store_row32_bf16(reinterpret_cast<bf16*>(out) + idx, v, valid);
+    if (f32 && accumulate) {
+      float* o = reinterpret_cast<float*>(out) + idx;
+      float r[32];
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {
+        if (g * 4 < valid) {
+          const float4 old = *reinterpret_cast<const float4*>(o + g * 4);
+          r[g * 4 + 0] = old.x + v[g * 4 + 0];
+          r[g * 4 + 1] = old.y + v[g * 4 + 1];
+          r[g * 4 + 2] = old.z + v[g * 4 + 2];
+          r[g * 4 + 3] = old.w + v[g * 4 + 3];
+        }
+      }
+      store_row32_f32(o, r, valid);
+    } else if (f32) {
+      store_row32_f32(reinterpret_cast<float*>(out) + idx, v, valid);
+    } else {
+      store_row32_bf16(reinterpret_cast<bf16*>(out) + idx, v, valid);
+    }
   }
 };
 
@@ -184,6 +202,26 @@ struct OpBmmStore {
                                                          float (&o)[1][32], Prefetch&, int) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) o[0][j] = v[0][j];
+  }
+};
+
+// c = a0 b0^T + a1 b1^T (both products accumulate into one accumulator; equal K), direct epilogue.
+template <class EpiT, int BT_>
+struct OpBmm2 {
+  static constexpr int NA = 2, NB = 2, NACC = 1, BT = BT_, NTERMS = 2, NOUT = 0;
+  static constexpr bool kSecondInPlace = false, kResidualTma = false;
+  static constexpr int STAGES = ring_depth(2 * kATileBytes + 2 * BT_ * kBK * 2, 0);
+  using Epi = EpiT;
+  __host__ __device__ static constexpr int term_a(int t) { return t; }
+  __host__ __device__ static constexpr int term_b(int t) { return t; }
+  __host__ __device__ static constexpr int term_col(int) { return 0; }
+  __host__ __device__ static constexpr int term_n(int) { return BT_; }
+  __host__ __device__ static constexpr bool term_first(int t) { return t == 0; }
+  using Prefetch = NoPrefetch;
+  __device__ static __forceinline__ void prefetch(const Epi&, int, int, int, int, int, int, Prefetch&) {}
+  __device__ static __forceinline__ void epilogue(const Epi& ep, int batch, int row, int col, int M, int N,
+                                                  const float (&v)[1][32], Prefetch&, int) {
+    ep(batch, row, col, M, N, v[0]);
   }
 };
 
@@ -559,6 +597,138 @@ __global__ void __launch_bounds__(256) add_renorm_kernel(const RenormArgs a0, co
   const int64_t rows0 = static_cast<int64_t>(a0.B) * a0.R, rows1 = static_cast<int64_t>(a1.B) * a1.R;
   if (row < rows0) renorm_row_any(a0, row, threadIdx.x & 31);
   else if (row < rows0 + rows1) renorm_row_any(a1, row - rows0, threadIdx.x & 31);
+}
+
+// ------------------------------------------------------------------------------------------
+// pointwise kernels of the training backward (planes are [B*N rows][H or 2H columns], bf16)
+// ------------------------------------------------------------------------------------------
+struct PlaneArgs {
+  const bf16* y02;    // [rows][2H]: y0 | y2
+  const bf16* dh;     // [rows][H]
+  const bf16* g_dy02; // [rows][2H] upstream grads of dy0 | dy2 (second-order kernel only)
+  const bf16* g_hid;  // [rows][H]  upstream grad of hidden*lr1 (second-order kernel only)
+  const void *lr0, *lr1, *lr2;  // [rows] or nullptr (= 1)
+  int32_t lr_f32;
+  float w_scale;
+  bf16* dy02;   // out [rows][2H]: dy0*lr0 | dy2*lr2
+  bf16* hid;    // out [rows][H]: hidden*lr1
+  bf16* g_y02;  // out [rows][2H] (second-order only)
+  bf16* g_dh;   // out [rows][H]  (second-order only)
+  float *g_lr0, *g_lr1, *g_lr2;  // out [rows] (second-order only)
+  int64_t rows;
+  int32_t H;
+};
+
+// First-order planes: hidden*lr1, dy0*lr0, dy2*lr2 from (bf16-rounded) y0, y2, dh.  Used by the
+// backward of apply (lr = 1; lact_swiglu_ffn.py:46-76).  One warp per token row.
+__global__ void __launch_bounds__(256) swiglu_bwd_planes_kernel(const PlaneArgs a) {
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= a.rows) return;
+  const int lane = threadIdx.x & 31;
+  const float l0 = (a.lr0 ? load_scalar(a.lr0, a.lr_f32, row) : 1.f) * a.w_scale;
+  const float l1 = (a.lr1 ? load_scalar(a.lr1, a.lr_f32, row) : 1.f) * a.w_scale;
+  const float l2 = (a.lr2 ? load_scalar(a.lr2, a.lr_f32, row) : 1.f) * a.w_scale;
+  const int H = a.H;
+  for (int c = lane; c < H; c += 32) {
+    const float y0 = __bfloat162float(a.y02[row * 2 * H + c]);
+    const float y2 = __bfloat162float(a.y02[row * 2 * H + H + c]);
+    const float dh = __bfloat162float(a.dh[row * H + c]);
+    const float sg = sigmoidf_fast(y0), sw = sg * y0;
+    a.hid[row * H + c] = __float2bfloat16_rn(sw * y2 * l1);
+    a.dy02[row * 2 * H + c] = __float2bfloat16_rn(sg * y2 * dh * (1.0f + y0 * (1.0f - sg)) * l0);
+    a.dy02[row * 2 * H + H + c] = __float2bfloat16_rn(sw * dh * l2);
+  }
+}
+
+// Second-order pointwise stage of the fast-weight-gradient backward
+// (lact_llm/lact_model/lact_triton_kernels/lact_fw_grad.py:178-260): with A = d silu / dy0,
+//   g_y0 = g_hid*A*y2*l1 + g_dy0*A'*y2*dh*l0 + g_dy2*A*dh*l2,   g_y2 = g_hid*sw*l1 + g_dy0*A*dh*l0,
+//   g_dh = g_dy0*A*y2*l0 + g_dy2*sw*l2,   g_lr = row sums (deterministic: one warp per row).
+__global__ void __launch_bounds__(256) fw_grad_bwd_pointwise_kernel(const PlaneArgs a) {
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= a.rows) return;
+  const int lane = threadIdx.x & 31;
+  const float l0 = load_scalar(a.lr0, a.lr_f32, row) * a.w_scale;
+  const float l1 = load_scalar(a.lr1, a.lr_f32, row) * a.w_scale;
+  const float l2 = load_scalar(a.lr2, a.lr_f32, row) * a.w_scale;
+  const int H = a.H;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f;
+  for (int c = lane; c < H; c += 32) {
+    const float y0 = __bfloat162float(a.y02[row * 2 * H + c]);
+    const float y2 = __bfloat162float(a.y02[row * 2 * H + H + c]);
+    const float dh = __bfloat162float(a.dh[row * H + c]);
+    const float gd0 = __bfloat162float(a.g_dy02[row * 2 * H + c]);
+    const float gd2 = __bfloat162float(a.g_dy02[row * 2 * H + H + c]);
+    const float gh = __bfloat162float(a.g_hid[row * H + c]);
+    const float sg = sigmoidf_fast(y0), sw = sg * y0;
+    const float A = sg * (1.0f + y0 * (1.0f - sg));
+    const float Ap = sg * (1.0f - sg) * (2.0f + y0 * (1.0f - 2.0f * sg));
+    a.g_y02[row * 2 * H + c] = __float2bfloat16_rn(gh * A * y2 * l1 + gd0 * Ap * y2 * dh * l0 + gd2 * A * dh * l2);
+    a.g_y02[row * 2 * H + H + c] = __float2bfloat16_rn(gh * sw * l1 + gd0 * A * dh * l0);
+    a.g_dh[row * H + c] = __float2bfloat16_rn(gd0 * A * y2 * l0 + gd2 * sw * l2);
+    a.hid[row * H + c] = __float2bfloat16_rn(sw * y2 * l1);
+    a.dy02[row * 2 * H + c] = __float2bfloat16_rn(A * y2 * dh * l0);
+    a.dy02[row * 2 * H + H + c] = __float2bfloat16_rn(sw * dh * l2);
+    s0 += gd0 * A * y2 * dh;
+    s1 += gh * sw * y2;
+    s2 += gd2 * sw * dh;
+  }
+  s0 = warp_sum(s0); s1 = warp_sum(s1); s2 = warp_sum(s2);
+  if (lane == 0) {
+    a.g_lr0[row] = s0 * a.w_scale;
+    a.g_lr1[row] = s1 * a.w_scale;
+    a.g_lr2[row] = s2 * a.w_scale;
+  }
+}
+
+// Backward of w -> y = renorm(w) for rows of w = base + upd (recomputed here):
+//   mode 1 (eps outside): y = w / (r + eps) * n0;   mode 2: y = w * rsqrt(r^2 + eps) * n0;   mode 0: y = w.
+// Writes dw (fp32) and ADDS <dy, w> * scale into dn0[row]; one warp per row.
+struct RenormBwdArgs {
+  const float* base;  // [rows][C]
+  const void* upd;    // [rows][C] fp32 or bf16
+  int32_t upd_f32;
+  const float* n0;    // [rows]
+  const float* dy;    // [rows][C]
+  float* dw;          // [rows][C] out
+  float* dn0;         // [rows] accumulated
+  int64_t rows;
+  int32_t C, mode;
+};
+__global__ void __launch_bounds__(256) renorm_bwd_kernel(const RenormBwdArgs a) {
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= a.rows) return;
+  const int lane = threadIdx.x & 31;
+  const int64_t off = row * a.C;
+  float ss = 0.f, dot = 0.f;
+  for (int c = lane; c < a.C; c += 32) {
+    const float w = a.base[off + c] + load_scalar(a.upd, a.upd_f32, off + c);
+    ss += w * w;
+    dot += w * a.dy[off + c];
+  }
+  ss = warp_sum(ss);
+  dot = warp_sum(dot);
+  const float n0 = a.n0[row];
+  float s, k;  // dw = s * dy - k * w ; dn0 += dot * t
+  float t;
+  if (a.mode == 1) {
+    const float r = sqrtf(ss), den = r + 1e-5f;
+    s = n0 / den;
+    k = r > 0.f ? n0 * dot / (den * den * r) : 0.f;
+    t = 1.0f / den;
+  } else if (a.mode == 2) {
+    const float rs = 1.0f / sqrtf(ss + 1e-5f);
+    s = n0 * rs;
+    k = n0 * dot * rs * rs * rs;
+    t = rs;
+  } else {
+    s = 1.f; k = 0.f; t = 0.f;
+  }
+  for (int c = lane; c < a.C; c += 32) {
+    const float w = a.base[off + c] + load_scalar(a.upd, a.upd_f32, off + c);
+    a.dw[off + c] = s * a.dy[off + c] - k * w;
+  }
+  if (lane == 0 && a.dn0 != nullptr) a.dn0[row] += dot * t;
 }
 
 // y = (x + x_add) * rsqrt(sum (x + x_add)^2 + eps) * scale[row]; one warp per row.

@@ -64,11 +64,23 @@ def _weight(t: torch.Tensor, shape: tuple, name: str) -> torch.Tensor:
 def scan(w0, w1, w2, q, k, v, lr0, lr1, lr2, steps: Sequence[P.Step], *, out_len: Optional[int] = None,
          momentum=None, m_init=None, use_muon=False, ns_steps=5, ns_const_coeffs=False, ns_concat=False,
          ns_gram_right=False, renorm=L.RENORM_EPS_OUTSIDE, prenorm=False, prenorm_bf16=False, overwrite_quirk=False,
-         w_scale=1.0, return_state=False, return_momentum=False):
+         w_scale=1.0, return_state=False, return_momentum=False, _detach_norms=False, _state_dump=None):
     """General chunk recurrence in the LLM layout (w0, w2: [B,H,D]; w1: [B,D,H]); see
     `lact_scan_fwd` in include/lact_b200.h.  Returns o, and optionally the final fast weights
-    and momentum state (fp32)."""
+    and momentum state (fp32).  When gradients are enabled and an input requires grad, the call
+    goes through `backward.ScanFunction` (training backward, see that module for what it covers)."""
     dev = _need_cuda(w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum)
+    if _state_dump is None and torch.is_grad_enabled() and any(
+            torch.is_tensor(t) and t.requires_grad for t in (w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum)):
+        from .backward import ScanFunction
+        if m_init is not None or return_momentum:
+            raise NotImplementedError("gradients through a momentum state passed in / returned are not implemented")
+        opts = dict(out_len=out_len, use_muon=use_muon, ns_steps=ns_steps, ns_const_coeffs=ns_const_coeffs,
+                    ns_concat=ns_concat, ns_gram_right=ns_gram_right, renorm=renorm, prenorm=prenorm,
+                    prenorm_bf16=prenorm_bf16, overwrite_quirk=overwrite_quirk, w_scale=w_scale,
+                    _detach_norms=_detach_norms)
+        o, a, b, c = ScanFunction.apply(opts, list(steps), w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum)
+        return (o, a, b, c) if return_state else o
     q, k, v = _act(q, "q"), _act(k, "k"), _act(v, "v")
     B, Ltok, D = k.shape
     H = w0.shape[1]
@@ -126,6 +138,8 @@ def scan(w0, w1, w2, q, k, v, lr0, lr1, lr2, steps: Sequence[P.Step], *, out_len
         keep += m_init
         io.m0_in, io.m1_in, io.m2_in = (t.data_ptr() for t in m_init)
     io.o = o.data_ptr()
+    if _state_dump is not None:
+        io.state_dump = _state_dump.data_ptr()
     state = mom = None
     if return_state:
         state = (torch.empty(B, H, D, dtype=torch.float32, device=dev),
@@ -205,7 +219,7 @@ def fast_weight_swish_glu_weight_norm_mini_batch_apply(w0, w1, w2, q, k, v, lr0,
     t = lambda w: w.transpose(1, 2)
     o, a, b, c = scan(t(w0), t(w1), t(w2), q, k, v, lr0, lr1, lr2, steps, out_len=out_len, use_muon=True,
                       ns_steps=int(muon_update_steps), ns_const_coeffs=True, ns_gram_right=True,
-                      renorm=L.RENORM_EPS_OUTSIDE, return_state=True)
+                      renorm=L.RENORM_EPS_OUTSIDE, return_state=True, _detach_norms=True)
     return o, t(a).contiguous(), t(b).contiguous(), t(c).contiguous()
 
 

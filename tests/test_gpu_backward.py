@@ -1,0 +1,182 @@
+"""Training backward (Muon off) against autograd through the CPU oracle.
+
+The oracle runs the reference's unfused arithmetic in fp32 on the same bf16-rounded inputs;
+the CUDA backward recomputes pre-activations in bf16 (as the reference's fused backward does),
+so gradients agree to bf16 accuracy: max|a-ref|/max|ref| <= 3e-2 and cosine >= 0.999.
+"""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+BF16 = torch.bfloat16
+NAMES = ("w0", "w1", "w2", "q", "k", "v", "lr0", "lr1", "lr2")
+
+
+@pytest.fixture(scope="module")
+def lb():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from lact_b200 import build
+    build.build()
+    import lact_b200
+    return lact_b200
+
+
+def _grads_oracle(orc, inp, fn, mom, dO):
+    leaves = {n: inp[n].float().clone().requires_grad_(True) for n in NAMES}
+    m = inp["momentum"].clone().requires_grad_(True) if mom else None
+    o = fn(*[leaves[n] for n in NAMES], m)
+    (o * dO.float()).sum().backward()
+    g = {n: leaves[n].grad for n in NAMES}
+    if mom:
+        g["momentum"] = m.grad
+    return o.detach(), g
+
+
+def _grads_cuda(inp, fn, mom, dO):
+    leaves = {n: inp[n].cuda().clone().requires_grad_(True) for n in NAMES}
+    m = inp["momentum"].cuda().clone().requires_grad_(True) if mom else None
+    o = fn(*[leaves[n] for n in NAMES], m)
+    (o.float() * dO.cuda().float()).sum().backward()
+    g = {n: leaves[n].grad for n in NAMES}
+    if mom:
+        g["momentum"] = m.grad
+    return o.detach(), g
+
+
+def _check(orc, got, ref, names, tol=3e-2, cos=0.999):
+    for n in names:
+        a, b = got[n].float().cpu(), ref[n].float()
+        assert a.shape == b.shape, n
+        assert torch.isfinite(a).all(), n
+        rm, cs = orc.rel_max(a, b), orc.cosine(a, b)
+        # the momentum gradient is one scalar per (entry, chunk), a long bf16-operand reduction: wider band
+        t = 8e-2 if n == "momentum" else tol
+        assert rm <= t and cs >= cos, f"grad {n}: rel_max={rm:.3e} cos={cs:.6f}"
+
+
+@pytest.mark.parametrize("mom", [False, True])
+@pytest.mark.parametrize("shape", [(2, 576, 64, 64, 128), (1, 700, 128, 64, 256)])
+def test_llm_postnorm_backward_muon_off(lb, mom, shape):
+    from oracle import lact_oracle as orc
+    B, L, D, H, C = shape
+    inp = orc.make_inputs(B, L, D, H, seed=21)
+    for n in ("q", "k", "v"):
+        inp[n] = inp[n].to(BF16)
+    dO = torch.randn(B, L, D, generator=torch.Generator().manual_seed(3)).to(BF16)
+    ref_fn = lambda w0, w1, w2, q, k, v, l0, l1, l2, m: orc.block_causal_lact_swiglu(
+        w0, w1, w2, q, k, v, l0, l1, l2, chunk_size=C, use_muon=False, momentum=m)
+    cu_fn = lambda w0, w1, w2, q, k, v, l0, l1, l2, m: lb.block_causal_lact_swiglu(
+        w0, w1, w2, q, k, v, l0, l1, l2, chunk_size=C, use_muon=False, momentum=m)
+    o_ref, g_ref = _grads_oracle(orc, inp, ref_fn, mom, dO)
+    o, g = _grads_cuda(inp, cu_fn, mom, dO)
+    assert orc.rel_max(o.float().cpu(), o_ref) <= 2e-2
+    _check(orc, g, g_ref, list(NAMES) + (["momentum"] if mom else []))
+    assert g["q"].dtype == BF16 and g["w0"].dtype == torch.float32 and g["lr0"].shape == inp["lr0"].shape
+
+
+def test_fused_signature_backward_muon_off(lb):
+    """eps-inside renorm (fused post-norm signature): gradients vs autograd through the oracle's
+    restatement of the fused path."""
+    from oracle import lact_oracle as orc
+    B, L, D, H, C = 2, 512, 64, 128, 128
+    inp = orc.make_inputs(B, L, D, H, seed=22)
+    for n in ("q", "k", "v"):
+        inp[n] = inp[n].to(BF16)
+    dO = torch.randn(B, L, D, generator=torch.Generator().manual_seed(4)).to(BF16)
+
+    def ref_fn(w0, w1, w2, q, k, v, l0, l1, l2, m):
+        # fp32 arithmetic with the fused path's semantics (eps inside the square root)
+        cfg = orc.ScanConfig(use_muon=False, renorm="inner", fp32_mode=True)
+        steps = [("apply", s, s + C, s) if kind == 0 else ("update", s, s + C, 0)
+                 for kind, s in [(0, 0), (1, 0), (0, 128), (1, 128), (0, 256), (1, 256), (0, 384)]]
+        o, *_ = scan_autograd(orc, w0, w1, w2, q, k, v, l0, l1, l2, steps, cfg, m)
+        return o
+
+    cu_fn = lambda w0, w1, w2, q, k, v, l0, l1, l2, m: lb.postnorm_block_causal_lact_swiglu_fused_kernel_triton(
+        w0, w1, w2, q, k, v, l0, l1, l2, chunk_size=C, use_muon=False, momentum=m)
+    o_ref, g_ref = _grads_oracle(orc, inp, ref_fn, True, dO)
+    o, g = _grads_cuda(inp, cu_fn, True, dO)
+    _check(orc, g, g_ref, list(NAMES) + ["momentum"])
+
+
+def scan_autograd(orc, w0, w1, w2, q, k, v, l0, l1, l2, steps, cfg, m):
+    """Differentiable fp32 version of the oracle's scan model (no in-place writes)."""
+    import torch.nn.functional as F
+    n0, n1, n2 = (w.norm(dim=2, keepdim=True) for w in (w0, w1, w2))
+    outs = []
+    ms = None
+    if m is not None:
+        ms = [torch.zeros_like(w0), torch.zeros_like(w1), torch.zeros_like(w2)]
+    nm = orc.Numerics("ref")
+    for kind, s, e, _ in steps:
+        if kind == "apply":
+            outs.append(orc.apply_ref(w0, w1, w2, q[:, s:e], nm))
+            continue
+        d0, d1, d2 = orc.grads_ref(w0, w1, w2, k[:, s:e], v[:, s:e], l0[:, s:e], l1[:, s:e], l2[:, s:e], nm)
+        if ms is not None:
+            beta = m[:, s:e].mean(dim=1, keepdim=True)
+            d0, d1, d2 = d0 + ms[0] * beta, d1 + ms[1] * beta, d2 + ms[2] * beta
+            ms = [d0, d1, d2]
+        norm = lambda w, n: w * (1 / torch.sqrt(torch.sum(w * w, dim=2, keepdim=True) + 1e-5)) * n
+        w0, w1, w2 = norm(w0 + d0, n0), norm(w1 + d1, n1), norm(w2 + d2, n2)
+    return torch.cat(outs, dim=1), w0, w1, w2
+
+
+def test_backward_not_implemented_cases_raise(lb):
+    x = torch.zeros(1, 128, 64, device="cuda", dtype=BF16, requires_grad=True)
+    w = torch.randn(1, 64, 64, device="cuda")
+    lr = torch.full((1, 128, 1), 0.1, device="cuda")
+    with pytest.raises(NotImplementedError):
+        lb.prenorm_block_causal_lact_swiglu(w, w, w, x, x, x, lr, lr, lr, chunk_size=64)
+    with torch.no_grad():  # inference is unaffected
+        lb.prenorm_block_causal_lact_swiglu(w, w, w, x, x, x, lr, lr, lr, chunk_size=64)
+
+
+@pytest.mark.parametrize("shape,steps", [((3, 64, 64), None), ((2, 64, 128), 5), ((2, 128, 64), 3), ((2, 192, 192), None)])
+def test_newton_schulz_backward(lb, shape, steps):
+    """d NS(G) / dG applied to a random cotangent: against autograd through an fp64 iteration.
+    The reference differentiates its bf16 iteration, whose own gradient deviates from the fp64
+    one by the amount measured here; the kernel path must not be worse than 1.5x that."""
+    from oracle import lact_oracle as orc
+    from lact_b200 import backward as bw
+    g = torch.Generator().manual_seed(7)
+    G = torch.randn(*shape, generator=g)
+    dU = torch.randn(*shape, generator=g)
+
+    def autograd_of(fn, dtype):
+        Gl = G.to(BF16).to(dtype).clone().requires_grad_(True)
+        (fn(Gl, steps).to(dtype) * dU.to(dtype)).sum().backward()
+        return Gl.grad.double()
+
+    ref64 = autograd_of(orc.newton_schulz_f64, torch.float64)
+    ref16 = autograd_of(lambda x, s_: orc.newton_schulz(x.float(), s_), torch.float32)
+    saved, U = bw.ns_forward_saved(G.cuda(), 5 if steps is None else steps, steps is not None, False)
+    got = bw.ns_backward(saved, dU.cuda()).double().cpu()
+    bw.check_status(torch.device("cuda", 0))
+    assert orc.rel_fro(U.float().cpu(), orc.newton_schulz(G, steps)) < 3e-2
+    err_kernel, err_ref = orc.rel_fro(got, ref64), orc.rel_fro(ref16, ref64)
+    assert err_kernel <= 1.5 * err_ref + 2e-2, (err_kernel, err_ref)
+    assert orc.cosine(got, ref64) >= 0.98
+
+
+def test_llm_backward_with_muon_first_chunks(lb):
+    """Muon on: gradients of the tokens that see at most one Newton-Schulz step are compared with
+    autograd through the oracle (loose band: the iteration's own bf16 noise, see the forward tests)."""
+    from oracle import lact_oracle as orc
+    B, L, D, H, C = 2, 256, 64, 64, 128
+    inp = orc.make_inputs(B, L, D, H, seed=23)
+    for n in ("q", "k", "v"):
+        inp[n] = inp[n].to(BF16)
+    dO = torch.randn(B, L, D, generator=torch.Generator().manual_seed(5)).to(BF16)
+    ref_fn = lambda w0, w1, w2, q, k, v, l0, l1, l2, m: orc.block_causal_lact_swiglu(
+        w0, w1, w2, q, k, v, l0, l1, l2, chunk_size=C, use_muon=True, momentum=m)
+    cu_fn = lambda w0, w1, w2, q, k, v, l0, l1, l2, m: lb.block_causal_lact_swiglu(
+        w0, w1, w2, q, k, v, l0, l1, l2, chunk_size=C, use_muon=True, momentum=m)
+    o_ref, g_ref = _grads_oracle(orc, inp, ref_fn, True, dO)
+    o, g = _grads_cuda(inp, cu_fn, True, dO)
+    for n in ("q", "k", "v", "w0", "w1", "w2", "lr0", "lr1", "lr2"):
+        a, b = g[n].float().cpu(), g_ref[n].float()
+        assert torch.isfinite(a).all(), n
+        assert orc.cosine(a, b) >= 0.97, (n, orc.cosine(a, b))
+        assert orc.rel_fro(a, b) <= 0.25, (n, orc.rel_fro(a, b))

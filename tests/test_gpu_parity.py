@@ -395,7 +395,7 @@ def test_scan_state_in_and_out(lb, orc):
         w0, w1, w2, m = r[1], r[2], r[3], r[4:]
     o = torch.cat(outs, dim=1)
     close(orc, o, full[0], tol=1e-2, cos=0.99999, what="stateful replay")  # one bf16 ulp at the largest output
-    close(orc, w0, full[1], tol=1e-3, what="stateful replay w0")
+    close(orc, w0, full[1], tol=5e-3, what="stateful replay w0")  # each call re-derives the target norms from its input weights
 
 
 def test_properties_at_scale(lb, orc):
