@@ -159,6 +159,31 @@ int check_device() {
   return LACT_OK;
 }
 
+// Launch with programmatic stream serialization: the kernel's prologue may overlap the tail of the
+// previous kernel in the stream; every kernel waits (griddepcontrol.wait) before it touches global memory.
+template <class... KArgs, class... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                       Args&&... args) {
+  cudaLaunchConfig_t cfg;
+  std::memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  // Off by default: measured 2 % slower on the benchmark workload (the early-launched CTAs of the next
+  // kernel compete with the running one); LACT_B200_PDL=1 turns the overlap on.
+  static const bool pdl = [] {
+    const char* env = std::getenv("LACT_B200_PDL");
+    return env != nullptr && env[0] == '1';
+  }();
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 int sm_count() {
   static int cached[64] = {0};
   int dev = 0;
@@ -197,8 +222,7 @@ int launch_gemm(const GemmArgs<Op, NPROB>& args, cudaStream_t stream, int cls, i
   if (tiles > (1ll << 30)) return LACT_ERR_SHAPE;
   const int grid = static_cast<int>(std::min<int64_t>(tiles, sm_count()));
   KernelScope scope(cls, stream);
-  kernel<<<grid, kGemmThreadsV2, smem, stream>>>(args, nprob);
-  LACT_CUDA(cudaGetLastError());
+  LACT_CUDA(launch_pdl(kernel, dim3(grid), dim3(kGemmThreadsV2), smem, stream, args, nprob));
   return LACT_OK;
 }
 
@@ -238,7 +262,6 @@ int launch_op(int bt, Fill&& fill, cudaStream_t stream, int cls, int nprob) {
   }
 #undef LACT_OP_CASE
 }
-template <int BT> using OpDWT = OpBmm<EpiDW, BT>;
 template <int BT> using OpStoreDirectT = OpBmm<EpiStore, BT>;
 template <int BT> using OpStore2T = OpBmm2<EpiStore, BT>;
 
@@ -316,7 +339,11 @@ struct GradArgs {
   int32_t g_f32;
   const float* beta;  // [B] or nullptr
   int64_t B, D, H;
+  float* partial02 = nullptr;  // optional per-tile sums of squares of the two outputs
+  float* partial1 = nullptr;
 };
+
+inline int contract_bt(int64_t D, int64_t H) { return choose_bt({{D, 2 * H}, {H, D}}); }
 
 int run_grad(const GradArgs& a, int32_t* status, cudaStream_t stream) {
   const int64_t len = a.end - a.start;
@@ -351,24 +378,25 @@ int run_grad(const GradArgs& a, int32_t* status, cudaStream_t stream) {
     LACT_TRY(launch_gemm(g, stream, kClsGradPointwise));
   }
   // token contraction: [dw0; dw2] = dy02^T k  and  dw1 = v^T hidden
-  const int bt = choose_bt({{a.D, 2 * a.H}, {a.H, a.D}});
+  const int bt = contract_bt(a.D, a.H);
   auto fill = [&](auto& g, int btv) -> int {
     auto& P0 = g.prob[0];
     LACT_TRY(make_operand(&P0.a[0], &P0.ai[0], dy, 1, kBM, 0, 0));
     LACT_TRY(make_operand(&P0.b[0], &P0.bi[0], km, 1, btv, 0, static_cast<int>(a.start)));
     P0.M = static_cast<int>(2 * a.H); P0.N = static_cast<int>(a.D); P0.K = static_cast<int>(len);
     P0.batch = static_cast<int>(a.B);
-    P0.ep = EpiDW{a.g02, 2 * a.H * a.D, a.D, a.beta, 1, a.g_f32};
+    P0.ep = EpiDW{a.g02, 2 * a.H * a.D, a.D, a.beta, 1, a.g_f32, a.partial02, ceil_div(2 * a.H, kBM),
+                  ceil_div(a.D, btv)};
     auto& P1 = g.prob[1];
     LACT_TRY(make_operand(&P1.a[0], &P1.ai[0], vm, 1, kBM, 0, static_cast<int>(a.start)));
     LACT_TRY(make_operand(&P1.b[0], &P1.bi[0], hid, 1, btv, 0, 0));
     P1.M = static_cast<int>(a.D); P1.N = static_cast<int>(a.H); P1.K = static_cast<int>(len);
     P1.batch = static_cast<int>(a.B);
-    P1.ep = EpiDW{a.g1, a.D * a.H, a.H, a.beta, 1, a.g_f32};
+    P1.ep = EpiDW{a.g1, a.D * a.H, a.H, a.beta, 1, a.g_f32, a.partial1, ceil_div(a.D, kBM), ceil_div(a.H, btv)};
     g.status = status;
     return LACT_OK;
   };
-  return launch_op<OpDWT, 2>(bt, fill, stream, kClsGradContract, 2);
+  return launch_op<OpDW, 2>(bt, fill, stream, kClsGradContract, 2);
 }
 
 // Newton-Schulz coefficient schedules.
@@ -379,6 +407,8 @@ const float kNsTuned[5][3] = {{4.0848f, -6.8946f, 2.9270f},
                               {2.8366f, -3.0525f, 1.2012f}};
 const float kNsConst[3] = {3.4445f, -4.7750f, 2.0315f};
 
+constexpr int kNsMaxParts = 512;
+
 // One group of equally shaped gradient matrices [R][C] under iteration.  The iteration runs on
 // X = [m][n] with m <= n: X = G^T when `transposed`.  The result is always delivered in the
 // gradient's own [R][C] orientation.
@@ -386,11 +416,11 @@ struct NsGroup {
   int32_t nmat, R, C, m, n, transposed;
   bf16 *xa, *xb;              // ping-pong iterates, nmat * m * n each
   bf16 *gram, *cgram, *poly;  // [nmat][m][m]
-  float* partial;             // [nmat][kNsSlabs] partial sums of squares
+  float* partial;             // [nmat][<= kNsMaxParts] partial sums of squares
 };
 
 inline size_t ns_group_bytes(int64_t nmat, int64_t m, int64_t n) {
-  return static_cast<size_t>(nmat) * (2 * m * n + 3 * m * m) * 2 + static_cast<size_t>(nmat) * kNsSlabs * 4 + 6 * 256;
+  return static_cast<size_t>(nmat) * (2 * m * n + 3 * m * m) * 2 + static_cast<size_t>(nmat) * kNsMaxParts * 4 + 6 * 256;
 }
 
 void ns_group_init(NsGroup& g, int64_t nmat, int64_t R, int64_t C, int gram_right) {
@@ -406,25 +436,30 @@ void ns_group_init(NsGroup& g, int64_t nmat, int64_t R, int64_t C, int gram_righ
 // contiguous) into each group's first iterate.  With steps == 0 the normalised matrix is the
 // result and is written untransposed.
 int launch_ns_prepare(const NsGroup* grp, int ngroups, const void* const* src, int src_f32, int steps,
-                      cudaStream_t stream) {
+                      cudaStream_t stream, const int* fused_parts = nullptr) {
+  // fused_parts[g] > 0: the partial sums of group g were already written (that many per matrix) by
+  // the kernel that produced the gradient; otherwise they are computed here, kNsSlabs per matrix
   NsPrepArgs pa;
   std::memset(&pa, 0, sizeof(pa));
   pa.ngroups = ngroups;
   int nmat = 0, tiles = 0;
+  bool need_sumsq = false;
   for (int g = 0; g < ngroups; ++g) {
     const NsGroup& G = grp[g];
-    pa.grp[g] = NsPrepGroup{src[g], src_f32, G.nmat, G.R, G.C, (G.transposed && steps > 0) ? 1 : 0, G.xa, G.partial};
+    const int parts = (fused_parts != nullptr && fused_parts[g] > 0) ? fused_parts[g] : kNsSlabs;
+    if (fused_parts == nullptr || fused_parts[g] <= 0) need_sumsq = true;
+    pa.grp[g] = NsPrepGroup{src[g], src_f32, G.nmat, G.R, G.C, (G.transposed && steps > 0) ? 1 : 0, G.xa, G.partial,
+                            parts};
     nmat += G.nmat;
     tiles = std::max(tiles, ceil_div(G.R, 64) * ceil_div(G.C, 64));
   }
-  {
+  if (need_sumsq) {
+    if (fused_parts != nullptr) return LACT_ERR_CONFIG;  // all groups or none
     KernelScope scope(kClsNsPrepare, stream);
-    ns_sumsq_kernel<<<dim3(nmat, kNsSlabs), 256, 0, stream>>>(pa);
-    LACT_CUDA(cudaGetLastError());
+    LACT_CUDA(launch_pdl(ns_sumsq_kernel, dim3(nmat, kNsSlabs), dim3(256), 0, stream, pa));
   }
   KernelScope scope(kClsNsPrepare, stream);
-  ns_scale_kernel<<<dim3(nmat, tiles), 256, 0, stream>>>(pa);
-  LACT_CUDA(cudaGetLastError());
+  LACT_CUDA(launch_pdl(ns_scale_kernel, dim3(nmat, tiles), dim3(256), 0, stream, pa));
   return LACT_OK;
 }
 
@@ -643,7 +678,7 @@ void carve_ns_group(Carver& c, NsGroup& g) {
   g.gram = c.take<bf16>(mm);
   g.cgram = c.take<bf16>(mm);
   g.poly = c.take<bf16>(mm);
-  g.partial = c.take<float>(static_cast<size_t>(g.nmat) * kNsSlabs);
+  g.partial = c.take<float>(static_cast<size_t>(g.nmat) * kNsMaxParts);
 }
 
 // Group 0 orthogonalises the [w0; w2] gradient (concat: B matrices [2H][D]; separate: 2B matrices
@@ -808,6 +843,25 @@ int scan_fwd(const lact_scan_config& c, const lact_scan_io& io, int32_t n_steps,
     ++update_idx;
     GradArgs g{p.W02b, p.W1b, io.k, io.v, c.k_bs, c.k_ts, c.v_bs, c.v_ts, start[i], end[i], io.lr0, io.lr1, io.lr2,
                c.lr_dtype == LACT_F32, c.L, c.w_scale, p.dy02, p.hid, p.G02, p.G1, 1, beta, B, D, H};
+    // The Frobenius norms Newton-Schulz needs are gathered per output tile by the contraction when a
+    // tile never straddles two matrices (concatenated [2H, D], or H a multiple of the 128-row tile).
+    int fused_parts[2] = {0, 0};
+    static const bool fuse_sumsq = [] {
+      const char* env = std::getenv("LACT_B200_FUSED_SUMSQ");
+      return !(env != nullptr && env[0] == '0');
+    }();
+    if (fuse_sumsq && c.use_muon && (c.ns_concat || H % kBM == 0)) {
+      const int bt = contract_bt(D, H);
+      const int tn0 = ceil_div(D, bt), tn1 = ceil_div(H, bt);
+      fused_parts[0] = (c.ns_concat ? ceil_div(2 * H, kBM) : static_cast<int>(H / kBM)) * tn0 * kEpiWarps;
+      fused_parts[1] = ceil_div(D, kBM) * tn1 * kEpiWarps;
+      if (fused_parts[0] <= kNsMaxParts && fused_parts[1] <= kNsMaxParts) {
+        g.partial02 = p.ns.grp[0].partial;
+        g.partial1 = p.ns.grp[1].partial;
+      } else {
+        fused_parts[0] = fused_parts[1] = 0;
+      }
+    }
     LACT_TRY(run_grad(g, p.status, stream));
     if (dump != nullptr) {
       const size_t n02 = static_cast<size_t>(B) * 2 * H * D, n1 = static_cast<size_t>(B) * D * H;
@@ -837,7 +891,8 @@ int scan_fwd(const lact_scan_config& c, const lact_scan_io& io, int32_t n_steps,
       NsPlan& ns = p.ns;
       const bf16* xres[2] = {nullptr, nullptr};
       const void* srcs[2] = {p.G02, p.G1};
-      LACT_TRY(launch_ns_prepare(ns.grp, ns.ngroups, srcs, 1, c.ns_steps, stream));
+      LACT_TRY(launch_ns_prepare(ns.grp, ns.ngroups, srcs, 1, c.ns_steps, stream,
+                                 fused_parts[0] > 0 ? fused_parts : nullptr));
       int rc = try_ns_fused(ns.grp, ns.ngroups, c.ns_steps, c.ns_const_coeffs,
                             reinterpret_cast<uint32_t*>(p.status) + 8, p.status, stream, xres,
                             reinterpret_cast<uint64_t*>(p.status + 64));
@@ -850,8 +905,7 @@ int scan_fwd(const lact_scan_config& c, const lact_scan_io& io, int32_t n_steps,
     {
       const int64_t rows = B * (2 * H + D);
       KernelScope scope(kClsRenorm, stream);
-      add_renorm_kernel<<<ceil_div(rows, 8), 256, 0, stream>>>(rn[0], rn[1]);
-      LACT_CUDA(cudaGetLastError());
+      LACT_CUDA(launch_pdl(add_renorm_kernel, dim3(ceil_div(rows, 8)), dim3(256), 0, stream, rn[0], rn[1]));
     }
   }
   // final state out

@@ -99,6 +99,7 @@ ns_fused_kernel(const __grid_constant__ NsFusedArgs<BT_MM, BT_MN> args) {
   constexpr int RING = ns_fused_ring<BT_MM, BT_MN>();
   constexpr uint32_t kStride = ns_fused_stage_stride<BT_MM, BT_MN>();
   constexpr uint32_t kTmemCols = 512;
+  griddep_launch_dependents();  // the next kernel may run its prologue while this one works
   if (*reinterpret_cast<volatile int32_t*>(args.status) != kStatusOk) return;  // uniform over the grid
   extern __shared__ uint8_t smem_raw[];
   GemmCtx cx;

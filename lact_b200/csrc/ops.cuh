@@ -98,7 +98,13 @@ struct EpiDW {
   const float* beta;  // per-batch momentum factor, or nullptr
   int32_t round_bf16;
   int32_t out_f32;
-  __device__ __forceinline__ void operator()(int batch, int row, int col, int M, int N, const float* v) const {
+  // optional: partial sums of squares of bf16(g), one per output tile and epilogue warp (the
+  // Frobenius norm that Newton-Schulz needs, gathered while the gradient is still in registers);
+  // index = ((batch * tiles_m + tile_m) * tiles_n + tile_n) * 8 + warp
+  float* partial;
+  int32_t tiles_m, tiles_n;
+  __device__ __forceinline__ void operator()(int batch, int row, int col, int M, int N, const float* v,
+                                             float* tile_acc = nullptr) const {
     if (row >= M) return;
     const int valid = min(32, N - col);
     const int64_t idx = batch * bs + static_cast<int64_t>(row) * ld + col;
@@ -123,6 +129,15 @@ struct EpiDW {
       store_row32_f32(gp, r, valid);
     } else {
       store_row32_bf16(reinterpret_cast<bf16*>(g) + idx, r, valid);
+    }
+    if (tile_acc != nullptr) {
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float x = bf16_round(r[j]);
+        ss += (j < valid) ? x * x : 0.f;
+      }
+      *tile_acc += ss;
     }
   }
 };
@@ -166,7 +181,7 @@ __host__ __device__ constexpr int ring_depth(uint32_t stage_bytes, uint32_t stag
 template <class EpiT, int BT_>
 struct OpBmm {
   static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 0;
-  static constexpr bool kSecondInPlace = false, kResidualTma = false;
+  static constexpr bool kSecondInPlace = false, kResidualTma = false, kTileReduce = false;
   static constexpr int STAGES = ring_depth(kATileBytes + BT_ * kBK * 2, 0);
   using Epi = EpiT;
   __host__ __device__ static constexpr int term_a(int) { return 0; }
@@ -182,12 +197,45 @@ struct OpBmm {
   }
 };
 
+// Token contraction of the fast-weight gradient: c = a b^T with the momentum epilogue; each tile
+// also leaves the sums of squares of its bf16-rounded results, one per epilogue warp (per-thread,
+// then warp shuffle; the consumer adds them in a fixed order, so the norm is deterministic).
+template <int BT_>
+struct OpDW {
+  static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 0;
+  static constexpr bool kSecondInPlace = false, kResidualTma = false, kTileReduce = true;
+  static constexpr int STAGES = ring_depth(kATileBytes + BT_ * kBK * 2, 0);
+  using Epi = EpiDW;
+  __host__ __device__ static constexpr int term_a(int) { return 0; }
+  __host__ __device__ static constexpr int term_b(int) { return 0; }
+  __host__ __device__ static constexpr int term_col(int) { return 0; }
+  __host__ __device__ static constexpr int term_n(int) { return BT_; }
+  __host__ __device__ static constexpr bool term_first(int) { return true; }
+  struct Prefetch {
+    float acc;
+  };
+  __device__ static __forceinline__ void prefetch(const Epi&, int, int, int, int, int, int, Prefetch& pf) {
+    pf.acc = 0.f;
+  }
+  __device__ static __forceinline__ void epilogue(const Epi& ep, int batch, int row, int col, int M, int N,
+                                                  const float (&v)[1][32], Prefetch& pf, int) {
+    ep(batch, row, col, M, N, v[0], ep.partial != nullptr ? &pf.acc : nullptr);
+  }
+  __device__ static __forceinline__ float tile_value(const Prefetch& pf) { return pf.acc; }
+  __device__ static __forceinline__ void tile_store(const Epi& ep, int batch, int tile_m, int tile_n, int warp_slot,
+                                                    float value) {
+    if (ep.partial != nullptr)
+      ep.partial[((static_cast<int64_t>(batch) * ep.tiles_m + tile_m) * ep.tiles_n + tile_n) * kEpiWarps + warp_slot] =
+          value;
+  }
+};
+
 // c = bf16(a b^T) written through the staged TMA-store epilogue.
 struct EpiNone {};
 template <int BT_>
 struct OpBmmStore {
   static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 1;
-  static constexpr bool kSecondInPlace = false, kResidualTma = false;
+  static constexpr bool kSecondInPlace = false, kResidualTma = false, kTileReduce = false;
   static constexpr int STAGES = ring_depth(kATileBytes + BT_ * kBK * 2, kBM * BT_ * 2);
   using Epi = EpiNone;
   __host__ __device__ static constexpr int term_a(int) { return 0; }
@@ -209,7 +257,7 @@ struct OpBmmStore {
 template <class EpiT, int BT_>
 struct OpBmm2 {
   static constexpr int NA = 2, NB = 2, NACC = 1, BT = BT_, NTERMS = 2, NOUT = 0;
-  static constexpr bool kSecondInPlace = false, kResidualTma = false;
+  static constexpr bool kSecondInPlace = false, kResidualTma = false, kTileReduce = false;
   static constexpr int STAGES = ring_depth(2 * kATileBytes + 2 * BT_ * kBK * 2, 0);
   using Epi = EpiT;
   __host__ __device__ static constexpr int term_a(int t) { return t; }
@@ -232,7 +280,7 @@ struct OpBmm2 {
 template <int BT_>
 struct OpNs {
   static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 2;
-  static constexpr bool kSecondInPlace = true, kResidualTma = true;
+  static constexpr bool kSecondInPlace = true, kResidualTma = true, kTileReduce = false;
   static constexpr int STAGES = ring_depth(kATileBytes + BT_ * kBK * 2, kBM * BT_ * 2);
   using Epi = EpiNs;
   __host__ __device__ static constexpr int term_a(int) { return 0; }
@@ -280,7 +328,7 @@ struct OpNs {
 template <int BT_>
 struct OpSwigluGate {
   static constexpr int NA = 1, NB = 2, NACC = 2, BT = BT_, NTERMS = 1, NOUT = 1;
-  static constexpr bool kSecondInPlace = false, kResidualTma = false;
+  static constexpr bool kSecondInPlace = false, kResidualTma = false, kTileReduce = false;
   static constexpr int STAGES = ring_depth(kATileBytes + 2 * BT_ * kBK * 2, kBM * BT_ * 2);
   using Epi = EpiNone;
   __host__ __device__ static constexpr int term_a(int) { return 0; }
@@ -306,7 +354,7 @@ struct OpSwigluGate {
 // outputs (dy0, dy2, hidden * lr1).
 struct OpFwGradPointwise {
   static constexpr int NA = 2, NB = 3, NACC = 3, BT = 64, NTERMS = 2, NOUT = 3;
-  static constexpr bool kSecondInPlace = false, kResidualTma = false;
+  static constexpr bool kSecondInPlace = false, kResidualTma = false, kTileReduce = false;
   static constexpr int STAGES = ring_depth(2 * kATileBytes + 3 * 64 * kBK * 2, 3 * kBM * 64 * 2);
   using Epi = EpiFwGrad;
   __host__ __device__ static constexpr int term_a(int t) { return t; }
@@ -359,6 +407,8 @@ __device__ __forceinline__ float warp_sum(float x) {
 __global__ void prepare_weights_kernel(const void* w0, const void* w1, const void* w2, int w_f32, int B, int H, int D,
                                        float* W02, float* W1, float* W02c, float* W1c, float* n02, float* n1,
                                        bf16* W02b, bf16* W1b) {
+  griddep_launch_dependents();
+  griddep_wait();
   const int rows_per_b = 2 * H + D;
   const int64_t r = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (r >= static_cast<int64_t>(B) * rows_per_b) return;
@@ -404,6 +454,8 @@ struct MeanArgs {
   int32_t s[kMeanBatch], e[kMeanBatch];
 };
 __global__ void momentum_mean_kernel(const void* mom, int mom_f32, int64_t bs, const MeanArgs ma, float* beta, int B) {
+  griddep_launch_dependents();
+  griddep_wait();
   __shared__ float part[32];
   const int b = blockIdx.x, u = blockIdx.y;
   const int s = ma.s[u], e = ma.e[u];
@@ -429,7 +481,8 @@ struct NsPrepGroup {
   int32_t nmat, R, C;
   int32_t transpose;  // write the iterate transposed ([C][R])
   bf16* x0;           // first iterate
-  float* partial;     // [nmat][kNsSlabs]
+  float* partial;     // [nmat][nparts] partial sums of squares, added in index order
+  int32_t nparts;
 };
 struct NsPrepArgs {
   NsPrepGroup grp[2];
@@ -441,6 +494,8 @@ constexpr int kNsSlabs = 16;
 // slab) reduces rows [slab * rows_per_slab, ...) and writes one float; part 2 adds the partials in
 // a fixed order, so the norm does not depend on scheduling.
 __global__ void __launch_bounds__(256) ns_sumsq_kernel(const NsPrepArgs args) {
+  griddep_launch_dependents();
+  griddep_wait();
   __shared__ float part[32];
   int mat = blockIdx.x;
   const int gi = (args.ngroups > 1 && mat >= args.grp[0].nmat) ? 1 : 0;
@@ -478,6 +533,8 @@ __global__ void __launch_bounds__(256) ns_sumsq_kernel(const NsPrepArgs args) {
 // the reference; written transposed (through a shared-memory tile, so both sides stay coalesced)
 // when the iteration runs on the other orientation.  Grid (matrices of all groups, 64x64 tiles).
 __global__ void __launch_bounds__(256) ns_scale_kernel(const NsPrepArgs args) {
+  griddep_launch_dependents();
+  griddep_wait();
   __shared__ float tile[64][65];
   int mat = blockIdx.x;
   const int gi = (args.ngroups > 1 && mat >= args.grp[0].nmat) ? 1 : 0;
@@ -487,7 +544,10 @@ __global__ void __launch_bounds__(256) ns_scale_kernel(const NsPrepArgs args) {
   if (static_cast<int>(blockIdx.y) >= tiles_c * tiles_r) return;
   const int tr = (blockIdx.y / tiles_c) * 64, tcx = (blockIdx.y % tiles_c) * 64;
   float tot = 0.f;
-  for (int i = 0; i < kNsSlabs; ++i) tot += G.partial[mat * kNsSlabs + i];
+  __shared__ float parts[512];
+  for (int i = threadIdx.x; i < G.nparts; i += blockDim.x) parts[i] = G.partial[static_cast<int64_t>(mat) * G.nparts + i];
+  __syncthreads();
+  for (int i = 0; i < G.nparts; ++i) tot += parts[i];  // same order in every thread and CTA
   const float den = bf16_round(bf16_round(sqrtf(tot)) + 1e-7f);
   const int64_t base = static_cast<int64_t>(mat) * G.R * G.C;
   const int lx = threadIdx.x & 63, ly = threadIdx.x >> 6;  // 64 x 4
@@ -593,6 +653,8 @@ __device__ __forceinline__ void renorm_row_any(const RenormArgs& a, int64_t row,
 
 // Both weight arrays in one launch; one warp per row.
 __global__ void __launch_bounds__(256) add_renorm_kernel(const RenormArgs a0, const RenormArgs a1) {
+  griddep_launch_dependents();
+  griddep_wait();
   const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int64_t rows0 = static_cast<int64_t>(a0.B) * a0.R, rows1 = static_cast<int64_t>(a1.B) * a1.R;
   if (row < rows0) renorm_row_any(a0, row, threadIdx.x & 31);

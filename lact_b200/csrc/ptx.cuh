@@ -63,6 +63,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-stream-serialization attribute may start while its
+// predecessor in the stream is still running.  griddep_wait() blocks until the predecessor has
+// completed and its memory is visible: nothing that reads or writes global memory may precede
+// it.  griddep_launch_dependents() allows the successor to start its own prologue early.
+// Both are no-ops for kernels launched without the attribute.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---------------------------------------------------------------- fences
 __device__ __forceinline__ void fence_async_proxy() {
   // makes generic-proxy shared-memory writes visible to the async proxy (TMA / tcgen05.mma)

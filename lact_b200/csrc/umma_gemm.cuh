@@ -354,6 +354,14 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&cx.acc_empty_bar[as]);
+      if constexpr (Op::kTileReduce) {
+        // per-tile, per-warp reduction of a per-thread value (no cross-warp synchronisation: the
+        // consumer adds the eight warp partials of every tile in a fixed order)
+        float tv = Op::tile_value(pf);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) tv += __shfl_xor_sync(0xFFFFFFFFu, tv, o);
+        if (lane == 0) Op::tile_store(ep, tc.batch, tc.m0 / kBM, tc.n0 / BT, warp - 2, tv);
+      }
       if constexpr (NOUT > 0) {
         fence_async_proxy();
         named_barrier_sync(2, kEpiThreads);
@@ -474,12 +482,12 @@ __device__ __forceinline__ void gemm_teardown(GemmCtx& cx, bool failed, int32_t*
   if ((threadIdx.x >> 5) == 1) tmem_dealloc(cx.tmem_base, tmem_cols);
 }
 
-// Persistent single-phase kernel.
+// Persistent single-phase kernel.  The prologue (barriers, tensor memory, descriptor prefetch)
+// touches no global memory and may overlap the tail of the previous kernel in the stream.
 template <class Op, int NPROB>
 __global__ void __launch_bounds__(kGemmThreadsV2, 1)
 umma_gemm_kernel(const __grid_constant__ GemmArgs<Op, NPROB> args, const int nprob) {
   static_assert(NPROB <= 2, "at most two problems per launch");
-  if (*reinterpret_cast<volatile int32_t*>(args.status) != kStatusOk) return;  // an earlier launch gave up
   extern __shared__ uint8_t smem_raw[];
   constexpr uint32_t kTmemCols = tmem_cols_pow2(2 * Op::NACC * Op::BT);
   GemmCtx cx;
@@ -494,7 +502,12 @@ umma_gemm_kernel(const __grid_constant__ GemmArgs<Op, NPROB> args, const int npr
       for (int i = 0; i < Op::NOUT; ++i) tma_prefetch_desc(&args.prob[p].out[i]);
     }
   }
-  const bool failed = gemm_phase<Op, Op::STAGES>(cx, args.prob, nprob, NoPatch{});
+  griddep_launch_dependents();
+  griddep_wait();
+  bool failed = false;
+  // an earlier launch gave up: do nothing but release the resources
+  if (*reinterpret_cast<volatile int32_t*>(args.status) == kStatusOk)
+    failed = gemm_phase<Op, Op::STAGES>(cx, args.prob, nprob, NoPatch{});
   gemm_teardown(cx, failed, args.status, kTmemCols);
 }
 
