@@ -643,9 +643,8 @@ int try_ns_fused(const NsGroup* grp, int ngroups, int steps, int const_coeffs, u
   for (int g = 0; g < ngroups; ++g) result[g] = (steps % 2 == 0) ? grp[g].xa : grp[g].xb;
   if (bt_mm == 192 && bt_mn == 192)
     return launch_ns_fused<192, 192>(grp, ngroups, steps, const_coeffs, barrier, status, stream, trace);
-  if (bt_mm == 128 && bt_mn == 256)
-    return launch_ns_fused<128, 256>(grp, ngroups, steps, const_coeffs, barrier, status, stream, trace);
-  if (bt_mm == 128 && bt_mn == 128)
+  // (a 256-wide update tile leaves no room for a useful ring next to two staging tiles: 128 is used)
+  if (bt_mm == 128 && (bt_mn == 128 || bt_mn == 256))
     return launch_ns_fused<128, 128>(grp, ngroups, steps, const_coeffs, barrier, status, stream, trace);
   return LACT_ERR_CONFIG;
 }

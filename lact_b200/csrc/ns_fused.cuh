@@ -78,7 +78,7 @@ __host__ __device__ constexpr uint32_t ns_fused_stage_stride() {
 }
 template <int BT_MM, int BT_MN>
 __host__ __device__ constexpr uint32_t ns_fused_staging() {
-  return kBM * (BT_MM > BT_MN ? BT_MM : BT_MN) * 2;
+  return 2 * kBM * (BT_MM > BT_MN ? BT_MM : BT_MN) * 2;  // double-buffered (OpNs::kStagingBuffers)
 }
 template <int BT_MM, int BT_MN>
 __host__ __device__ constexpr int ns_fused_ring() {

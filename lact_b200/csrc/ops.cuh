@@ -103,9 +103,10 @@ struct EpiDW {
   // index = ((batch * tiles_m + tile_m) * tiles_n + tile_n) * 8 + warp
   float* partial;
   int32_t tiles_m, tiles_n;
-  __device__ __forceinline__ void operator()(int batch, int row, int col, int M, int N, const float* v,
-                                             float* tile_acc = nullptr) const {
-    if (row >= M) return;
+  // returns the sum of squares of the bf16-rounded results of this row segment if `want_ss`
+  __device__ __forceinline__ float operator()(int batch, int row, int col, int M, int N, const float* v,
+                                              bool want_ss = false) const {
+    if (row >= M) return 0.f;
     const int valid = min(32, N - col);
     const int64_t idx = batch * bs + static_cast<int64_t>(row) * ld + col;
     float r[32];
@@ -130,15 +131,15 @@ struct EpiDW {
     } else {
       store_row32_bf16(reinterpret_cast<bf16*>(g) + idx, r, valid);
     }
-    if (tile_acc != nullptr) {
-      float ss = 0.f;
+    float ss = 0.f;
+    if (want_ss) {
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
         const float x = bf16_round(r[j]);
         ss += (j < valid) ? x * x : 0.f;
       }
-      *tile_acc += ss;
     }
+    return ss;
   }
 };
 
@@ -182,6 +183,7 @@ template <class EpiT, int BT_>
 struct OpBmm {
   static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 0;
   static constexpr bool kSecondInPlace = false, kResidualTma = false, kTileReduce = false;
+  static constexpr int kStagingBuffers = 1;
   static constexpr int STAGES = ring_depth(kATileBytes + BT_ * kBK * 2, 0);
   using Epi = EpiT;
   __host__ __device__ static constexpr int term_a(int) { return 0; }
@@ -204,6 +206,7 @@ template <int BT_>
 struct OpDW {
   static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 0;
   static constexpr bool kSecondInPlace = false, kResidualTma = false, kTileReduce = true;
+  static constexpr int kStagingBuffers = 1;
   static constexpr int STAGES = ring_depth(kATileBytes + BT_ * kBK * 2, 0);
   using Epi = EpiDW;
   __host__ __device__ static constexpr int term_a(int) { return 0; }
@@ -219,7 +222,7 @@ struct OpDW {
   }
   __device__ static __forceinline__ void epilogue(const Epi& ep, int batch, int row, int col, int M, int N,
                                                   const float (&v)[1][32], Prefetch& pf, int) {
-    ep(batch, row, col, M, N, v[0], ep.partial != nullptr ? &pf.acc : nullptr);
+    pf.acc += ep(batch, row, col, M, N, v[0], ep.partial != nullptr);
   }
   __device__ static __forceinline__ float tile_value(const Prefetch& pf) { return pf.acc; }
   __device__ static __forceinline__ void tile_store(const Epi& ep, int batch, int tile_m, int tile_n, int warp_slot,
@@ -236,6 +239,7 @@ template <int BT_>
 struct OpBmmStore {
   static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 1;
   static constexpr bool kSecondInPlace = false, kResidualTma = false, kTileReduce = false;
+  static constexpr int kStagingBuffers = 1;
   static constexpr int STAGES = ring_depth(kATileBytes + BT_ * kBK * 2, kBM * BT_ * 2);
   using Epi = EpiNone;
   __host__ __device__ static constexpr int term_a(int) { return 0; }
@@ -258,6 +262,7 @@ template <class EpiT, int BT_>
 struct OpBmm2 {
   static constexpr int NA = 2, NB = 2, NACC = 1, BT = BT_, NTERMS = 2, NOUT = 0;
   static constexpr bool kSecondInPlace = false, kResidualTma = false, kTileReduce = false;
+  static constexpr int kStagingBuffers = 1;
   static constexpr int STAGES = ring_depth(2 * kATileBytes + 2 * BT_ * kBK * 2, 0);
   using Epi = EpiT;
   __host__ __device__ static constexpr int term_a(int t) { return t; }
@@ -281,7 +286,9 @@ template <int BT_>
 struct OpNs {
   static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 2;
   static constexpr bool kSecondInPlace = true, kResidualTma = true, kTileReduce = false;
-  static constexpr int STAGES = ring_depth(kATileBytes + BT_ * kBK * 2, kBM * BT_ * 2);
+  // two staging tiles: while tile i is stored from one, the residual of tile i + 1 lands in the other
+  static constexpr int kStagingBuffers = 2;
+  static constexpr int STAGES = ring_depth(kATileBytes + BT_ * kBK * 2, 2 * kBM * BT_ * 2);
   using Epi = EpiNs;
   __host__ __device__ static constexpr int term_a(int) { return 0; }
   __host__ __device__ static constexpr int term_b(int) { return 0; }
@@ -329,6 +336,7 @@ template <int BT_>
 struct OpSwigluGate {
   static constexpr int NA = 1, NB = 2, NACC = 2, BT = BT_, NTERMS = 1, NOUT = 1;
   static constexpr bool kSecondInPlace = false, kResidualTma = false, kTileReduce = false;
+  static constexpr int kStagingBuffers = 1;
   static constexpr int STAGES = ring_depth(kATileBytes + 2 * BT_ * kBK * 2, kBM * BT_ * 2);
   using Epi = EpiNone;
   __host__ __device__ static constexpr int term_a(int) { return 0; }
@@ -355,6 +363,7 @@ struct OpSwigluGate {
 struct OpFwGradPointwise {
   static constexpr int NA = 2, NB = 3, NACC = 3, BT = 64, NTERMS = 2, NOUT = 3;
   static constexpr bool kSecondInPlace = false, kResidualTma = false, kTileReduce = false;
+  static constexpr int kStagingBuffers = 1;
   static constexpr int STAGES = ring_depth(2 * kATileBytes + 3 * 64 * kBK * 2, 3 * kBM * 64 * 2);
   using Epi = EpiFwGrad;
   __host__ __device__ static constexpr int term_a(int t) { return t; }

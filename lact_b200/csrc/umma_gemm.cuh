@@ -75,7 +75,7 @@ __host__ __device__ constexpr uint32_t gemm_stage_bytes() {
 // 64-column panels (the layout the output tensor maps expect)
 template <class Op>
 __host__ __device__ constexpr uint32_t gemm_staging_bytes() {
-  return (Op::kSecondInPlace ? 1 : Op::NOUT) * kBM * Op::BT * 2;
+  return Op::kStagingBuffers * (Op::kSecondInPlace ? 1 : Op::NOUT) * kBM * Op::BT * 2;
 }
 template <class Op>
 __host__ __device__ constexpr uint32_t gemm_smem_bytes() {
@@ -134,7 +134,14 @@ struct NoPatch {
   __device__ __forceinline__ void operator()(Epi&, int) const {}
 };
 
-// One GEMM phase: CTA c processes tiles c, c + gridDim.x, ... of the concatenated tile lists of
+// Round r of the persistent loop hands CTA c tile r*G + c in even rounds and r*G + (G-1-c) in odd
+// rounds ("snake"): with the problems listed heaviest first, a CTA that drew an expensive tile in
+// one round draws a cheap one (or none) in the next.
+__device__ __forceinline__ int snake_tile(int round, int grid, int cta) {
+  return round * grid + ((round & 1) ? (grid - 1 - cta) : cta);
+}
+
+// One GEMM phase: CTA c processes its snake sequence of tiles of the concatenated tile lists of
 // `nprob` problems.  Tiles of one batch entry are consecutive (n fastest), so CTAs that run at
 // the same time share operand tiles in L2.  Warp 0 = TMA producer, warp 1 = MMA issuer, warps
 // 2.. = epilogue.  Returns true if a bounded wait ran out.  No CTA-wide sync inside.
@@ -180,8 +187,10 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
   if (warp == 0) {
     // ---------------- TMA producer (one thread); the ring keeps running across tiles
     if (lane == 0) {
-      int tile_i = 0;
-      for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x, ++tile_i) {
+      const int rounds = (total_tiles + gridDim.x - 1) / gridDim.x;
+      for (int tile_i = 0; tile_i < rounds && !failed; ++tile_i) {
+        const int tile = snake_tile(tile_i, gridDim.x, blockIdx.x);
+        if (tile >= total_tiles) continue;
         const TileCoord tc = coord(tile);
         const GemmProblem<Op>& P = probs[tc.prob];
         const int num_kb = (P.K + kBK - 1) / kBK;
@@ -206,8 +215,10 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
   } else if (warp == 1) {
     // ---------------- MMA issuer (one thread)
     if (lane == 0) {
-      int tile_i = 0;
-      for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x, ++cx.tcount, ++tile_i) {
+      const int rounds = (total_tiles + gridDim.x - 1) / gridDim.x;
+      for (int tile_i = 0; tile_i < rounds && !failed; ++tile_i) {
+        const int tile = snake_tile(tile_i, gridDim.x, blockIdx.x);
+        if (tile >= total_tiles) continue;
         const TileCoord tc = coord(tile);
         const GemmProblem<Op>& P = probs[tc.prob];
         const int num_kb = (P.K + kBK - 1) / kBK;
@@ -239,6 +250,7 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
         }
         if (!failed) umma_commit(&cx.acc_full_bar[as]);
         cx.stamp(tile_i, 1);
+        ++cx.tcount;
       }
     }
   } else {
@@ -253,33 +265,47 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
     const int half = (warp - 2) >> 2;
     const bool elected = threadIdx.x == 64;
     const int row_local = quarter * 32 + lane;
-    // Residual tile of `tile` -> staging (elected thread).  The previous TMA store must have
-    // finished reading the staging tile first.
-    auto issue_residual = [&](int tile) {
+    constexpr uint32_t kStgBytes = NSTG * kBM * BT * 2;  // one staging buffer
+    constexpr bool kDoubleStg = Op::kStagingBuffers == 2;
+    // staging buffer of the tile with running count `tc_` (alternating when double-buffered)
+    auto stg_of = [&](uint32_t tc_) { return cx.staging + (kDoubleStg ? (tc_ & 1u) * kStgBytes : 0u); };
+    const int rounds = (total_tiles + gridDim.x - 1) / gridDim.x;
+    auto tile_of_round = [&](int r) {
+      if (r >= rounds) return -1;
+      const int t = snake_tile(r, gridDim.x, blockIdx.x);
+      return t < total_tiles ? t : -1;
+    };
+    // Residual tile of `tile` -> the staging buffer `dst` (elected thread).  Every TMA store that
+    // read `dst` must have finished reading (the caller waits for that).
+    auto issue_residual = [&](int tile, uint32_t dst) {
       if constexpr (Op::kResidualTma) {
-        if (tile >= total_tiles) return;
+        if (tile < 0) return;
         const TileCoord t2 = coord(tile);
         const GemmProblem<Op>& P2 = probs[t2.prob];
         if (!P2.res_enabled) return;
-        bulk_wait_read_all();
         int panels = 0;
         for (int pnl = 0; pnl < BT / 64; ++pnl)
           if (t2.n0 + pnl * 64 < P2.N) ++panels;
         mbar_expect_tx(cx.res_bar, panels * (kBM * 128));
         for (int pnl = 0; pnl < panels; ++pnl)
-          tma_load_3d(cx.staging + pnl * (kBM * 128), &P2.res, cx.res_bar, P2.oi[0].col_off + t2.n0 + pnl * 64,
+          tma_load_3d(dst + pnl * (kBM * 128), &P2.res, cx.res_bar, P2.oi[0].col_off + t2.n0 + pnl * 64,
                       P2.oi[0].row_off + t2.m0, P2.oi[0].batch_off + t2.batch);
       }
     };
-    if (elected) issue_residual(blockIdx.x);
-    int tile_i = 0;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++cx.tcount, ++tile_i) {
+    if (elected && Op::kResidualTma) {
+      bulk_wait_read_all();
+      issue_residual(tile_of_round(0), stg_of(cx.tcount));
+    }
+    for (int tile_i = 0; tile_i < rounds; ++tile_i) {
+      const int tile = tile_of_round(tile_i);
+      if (tile < 0) continue;
       const TileCoord tc = coord(tile);
       const GemmProblem<Op>& P = probs[tc.prob];
       typename Op::Epi ep = P.ep;
       patch(ep, tc.prob);
       bool has_res = false;
       if constexpr (Op::kResidualTma) has_res = P.res_enabled != 0;
+      const uint32_t stg = stg_of(cx.tcount);
       const uint32_t as = cx.tcount & 1, aph = (cx.tcount >> 1) & 1;
       const int row = tc.m0 + row_local;
       // global operands of the epilogue are fetched while the tile's MMAs are still running
@@ -298,7 +324,11 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
         // a flag that only epilogue warps write, and every warp decides after the barrier.
         if (!got) cx.abort_flag[1] = 1;
         // the previous tile's stores must have finished reading the staging tiles
-        if (elected) bulk_wait_read_all();
+        if (elected) {
+          bulk_wait_read_all();
+          // double-buffered: the other buffer is free now, fetch the next tile's residual into it
+          if (kDoubleStg && got) issue_residual(tile_of_round(tile_i + 1), stg_of(cx.tcount + 1));
+        }
         named_barrier_sync(1, kEpiThreads);
         if (cx.abort_flag[1] != 0) { failed = true; break; }
       } else {
@@ -323,7 +353,7 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
             if (has_res) {  // this thread's residual segment sits where its result will go
 #pragma unroll
               for (int g = 0; g < 4; ++g) {
-                const uint32_t addr = cx.staging + rowaddr + (((unit0 + g) ^ (row_local & 7)) << 4);
+                const uint32_t addr = stg + rowaddr + (((unit0 + g) ^ (row_local & 7)) << 4);
                 asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
                              : "=r"(pf.r[g].x), "=r"(pf.r[g].y), "=r"(pf.r[g].z), "=r"(pf.r[g].w)
                              : "r"(addr)
@@ -334,7 +364,7 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
           Op::epilogue_staged(ep, tc.batch, row, tc.n0 + c, P.M, P.N, v, ov, pf, has_res);
 #pragma unroll
           for (int o = 0; o < NSTG; ++o) {
-            const uint32_t base = cx.staging + o * (kBM * BT * 2) + rowaddr;
+            const uint32_t base = stg + o * (kBM * BT * 2) + rowaddr;
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
               const uint32_t addr = base + (((unit0 + g) ^ (row_local & 7)) << 4);
@@ -371,7 +401,7 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
             if (!P.oi[o].enabled || (o == 1 && Op::kSecondInPlace) || Op::skip_store(ep, o)) continue;
             for (int pnl = 0; pnl < BT / 64; ++pnl) {
               if (tc.n0 + pnl * 64 >= P.N) break;
-              tma_store_3d(&P.out[o], cx.staging + o * (kBM * BT * 2) + pnl * (kBM * 128),
+              tma_store_3d(&P.out[o], stg + o * (kBM * BT * 2) + pnl * (kBM * 128),
                            P.oi[o].col_off + tc.n0 + pnl * 64, P.oi[o].row_off + tc.m0, P.oi[o].batch_off + tc.batch);
             }
           }
@@ -385,7 +415,7 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
             named_barrier_sync(1, kEpiThreads);
             for (int c = half * 32; c < BT; c += 64) {
               if (tc.n0 + c >= P.N) break;
-              const uint32_t base = cx.staging + (c >> 6) * (kBM * 128) + row_local * 128;
+              const uint32_t base = stg + (c >> 6) * (kBM * 128) + row_local * 128;
               const uint32_t unit0 = (c & 63) >> 3;
 #pragma unroll
               for (int g = 0; g < 4; ++g) {
@@ -409,15 +439,19 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
             if (elected) {
               for (int pnl = 0; pnl < BT / 64; ++pnl) {
                 if (tc.n0 + pnl * 64 >= P.N) break;
-                tma_store_3d(&P.out[1], cx.staging + pnl * (kBM * 128), P.oi[1].col_off + tc.n0 + pnl * 64,
+                tma_store_3d(&P.out[1], stg + pnl * (kBM * 128), P.oi[1].col_off + tc.n0 + pnl * 64,
                              P.oi[1].row_off + tc.m0, P.oi[1].batch_off + tc.batch);
               }
               bulk_commit_group();
             }
           }
         }
-        if (elected) issue_residual(tile + gridDim.x);
+        if (!kDoubleStg && elected && Op::kResidualTma) {
+          bulk_wait_read_all();
+          issue_residual(tile_of_round(tile_i + 1), stg);
+        }
       }
+      ++cx.tcount;
     }
     if constexpr (NOUT > 0) {
       if (elected) bulk_wait_all();  // this CTA's output tiles are in global memory
