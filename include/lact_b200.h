@@ -216,6 +216,20 @@ int lact_fw_grad_bwd_pointwise(const void *y02, const void *dh, const void *g_dy
 int lact_renorm_bwd(const void *base, const void *upd, int32_t upd_dtype, const void *n0, const void *dy, void *dw,
                     void *dn0, int64_t rows, int64_t C, int32_t mode, void *stream);
 
+/* fp32 mode (fp32 activations; the reference's CPU configuration, e.g. bidirectional_lact_layer.py with fp32 inputs):
+ * plain FFMA kernels for accuracy, no tensor cores.  The Python package runs the step program with them.
+ *   lact_sgemm_f32: c[batch, M, N] = a b^T (+ beta[batch] * c when accumulate; beta NULL = 1), a stored [M][K] (a_t = 0) or [K][M], b stored [N][K] (b_t = 0) or [K][N]
+ *     (replaces torch.bmm on fp32 tensors, e.g. ttt_operation.py:141-168);
+ *   lact_swiglu_planes_f32: hidden (*lr1) and, when dh is given, dy0*lr0 | dy2*lr2 from y0|y2 (ttt_operation.py:149-160);
+ *   lact_add_renorm: w <- renorm((quirk ? g : w) + (x ? x : g)) on fp32 masters (ttt_operation.py:189-200). */
+int lact_sgemm_f32(const void *a, int32_t a_t, const void *b, int32_t b_t, void *c, int32_t accumulate,
+                   const void *beta, int64_t batch, int64_t M, int64_t N, int64_t K, void *stream);
+int lact_swiglu_planes_f32(const void *y02, const void *dh, const void *lr0, const void *lr1, const void *lr2,
+                           int32_t lr_dtype, float w_scale, void *dy02, void *hid, int64_t rows, int64_t H, void *stream);
+int lact_add_renorm(void *master, void *compute, void *shadow, const void *n0, const void *g, const void *x, int64_t B,
+                    int64_t R, int64_t C, int32_t mode, int32_t prenorm, int32_t prenorm_bf16, int32_t quirk,
+                    void *stream);
+
 /* c[batch, M, N] = a * b^T with bf16 operands and fp32 accumulation (c_dtype output).
  * a is [batch, M, K] (a_mn_major = 0) or [batch, K, M] (a_mn_major = 1); b likewise with N.
  * Test hook for the tcgen05 GEMM engine; no counterpart in the reference (it calls torch.bmm). */

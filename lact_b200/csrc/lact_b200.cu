@@ -1272,6 +1272,59 @@ int lact_renorm_bwd(const void* base, const void* upd, int32_t upd_dtype, const 
   return LACT_OK;
 }
 
+// ---------------------------------------------------------------- fp32 mode building blocks
+int lact_sgemm_f32(const void* a, int32_t a_t, const void* b, int32_t b_t, void* c, int32_t accumulate,
+                   const void* beta, int64_t batch, int64_t M, int64_t N, int64_t K, void* stream) {
+  if (!a || !b || !c) return LACT_ERR_NULL;
+  if (batch < 1 || batch > 65535 || M < 1 || N < 1 || K < 1) return LACT_ERR_SHAPE;
+  dim3 grid(ceil_div(N, 64), ceil_div(M, 64), static_cast<unsigned>(batch));
+  if (grid.y > 65535) return LACT_ERR_SHAPE;
+  KernelScope scope(kClsOther, static_cast<cudaStream_t>(stream));
+  sgemm_f32_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const float*>(a), a_t, static_cast<const float*>(b), b_t, static_cast<float*>(c), accumulate,
+      static_cast<const float*>(beta), static_cast<int>(M), static_cast<int>(N), static_cast<int>(K));
+  LACT_CUDA(cudaGetLastError());
+  return LACT_OK;
+}
+
+int lact_swiglu_planes_f32(const void* y02, const void* dh, const void* lr0, const void* lr1, const void* lr2,
+                           int32_t lr_dtype, float w_scale, void* dy02, void* hid, int64_t rows, int64_t H,
+                           void* stream) {
+  if (!y02 || !hid || (dh != nullptr && !dy02)) return LACT_ERR_NULL;
+  if (rows < 1 || H < 1) return LACT_ERR_SHAPE;
+  KernelScope scope(kClsOther, static_cast<cudaStream_t>(stream));
+  swiglu_planes_f32_kernel<<<ceil_div(rows, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const float*>(y02), static_cast<const float*>(dh), lr0, lr1, lr2, lr_dtype == LACT_F32, w_scale,
+      static_cast<float*>(dy02), static_cast<float*>(hid), rows, static_cast<int>(H));
+  LACT_CUDA(cudaGetLastError());
+  return LACT_OK;
+}
+
+int lact_add_renorm(void* master, void* compute, void* shadow, const void* n0, const void* g, const void* x,
+                    int64_t B, int64_t R, int64_t C, int32_t mode, int32_t prenorm, int32_t prenorm_bf16,
+                    int32_t quirk, void* stream) {
+  if (!master || !shadow || !n0 || !g) return LACT_ERR_NULL;
+  if (B < 1 || R < 1 || C < 4 || (C % 4) || C > kRenormMaxCols || mode < 0 || mode > 2) return LACT_ERR_SHAPE;
+  RenormArgs r;
+  std::memset(&r, 0, sizeof(r));
+  r.master = static_cast<float*>(master);
+  r.compute = static_cast<float*>(compute);
+  r.shadow = static_cast<bf16*>(shadow);
+  r.n0 = static_cast<const float*>(n0);
+  r.g = static_cast<const float*>(g);
+  r.x = static_cast<const bf16*>(x);
+  r.x_bs = R * C;
+  r.B = static_cast<int>(B); r.R = static_cast<int>(R); r.C = static_cast<int>(C);
+  r.mode = mode; r.prenorm = prenorm; r.prenorm_bf16 = prenorm_bf16; r.quirk = quirk;
+  RenormArgs none = r;
+  none.B = 0;
+  const int64_t rows = B * R;
+  KernelScope scope(kClsRenorm, static_cast<cudaStream_t>(stream));
+  add_renorm_kernel<<<ceil_div(rows, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(r, none);
+  LACT_CUDA(cudaGetLastError());
+  return LACT_OK;
+}
+
 int lact_bmm_bf16(const void* a, int32_t a_mn_major, const void* b, int32_t b_mn_major, void* c, int32_t c_dtype,
                   int64_t batch, int64_t M, int64_t N, int64_t K, int32_t* status_word, void* stream) {
   if (!a || !b || !c || !status_word) return LACT_ERR_NULL;

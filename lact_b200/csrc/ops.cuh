@@ -802,6 +802,84 @@ __global__ void __launch_bounds__(256) renorm_bwd_kernel(const RenormBwdArgs a) 
   if (lane == 0 && a.dn0 != nullptr) a.dn0[row] += dot * t;
 }
 
+// ------------------------------------------------------------------------------------------
+// fp32 mode (parity path for fp32 activations): plain FFMA kernels, no tensor cores.
+// tcgen05 has no fp32 x fp32 MMA; this path exists for accuracy (max relative error ~1e-6 when
+// Muon is off), not for throughput.
+// ------------------------------------------------------------------------------------------
+// c[b][m][n] = sum_k A(b, m, k) * B(b, n, k) (+ beta[b] * c[b][m][n] when accumulating; beta = 1
+// without a beta vector); A stored [M][K] (a_t = 0) or [K][M] (a_t = 1), B stored [N][K] (b_t = 0)
+// or [K][N] (b_t = 1); all contiguous.  64 x 64 tile, 256 threads, 4 x 4 per thread.
+__global__ void __launch_bounds__(256) sgemm_f32_kernel(const float* A, int a_t, const float* B, int b_t, float* C,
+                                                        int accumulate, const float* beta, int M, int N, int K) {
+  __shared__ float As[16][65];
+  __shared__ float Bs[16][65];
+  const int b = blockIdx.z;
+  A += static_cast<int64_t>(b) * M * K;
+  B += static_cast<int64_t>(b) * N * K;
+  C += static_cast<int64_t>(b) * M * N;
+  const float cb = beta != nullptr ? beta[b] : 1.f;
+  const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < K; k0 += 16) {
+    for (int i = threadIdx.x; i < 16 * 64; i += 256) {
+      const int kk = a_t ? i / 64 : i % 16, mm = a_t ? i % 64 : i / 16;
+      const int gm = m0 + mm, gk = k0 + kk;
+      As[kk][mm] = (gm < M && gk < K) ? (a_t ? A[static_cast<int64_t>(gk) * M + gm] : A[static_cast<int64_t>(gm) * K + gk]) : 0.f;
+      const int kb = b_t ? i / 64 : i % 16, nn = b_t ? i % 64 : i / 16;
+      const int gn = n0 + nn, gkb = k0 + kb;
+      Bs[kb][nn] = (gn < N && gkb < K) ? (b_t ? B[static_cast<int64_t>(gkb) * N + gn] : B[static_cast<int64_t>(gn) * K + gkb]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < 16; ++kk) {
+      float a[4], bb[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { a[i] = As[kk][ty * 4 + i]; bb[i] = Bs[kk][tx * 4 + i]; }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], bb[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int gm = m0 + ty * 4 + i, gn = n0 + tx * 4 + j;
+      if (gm < M && gn < N) {
+        float* o = C + static_cast<int64_t>(gm) * N + gn;
+        *o = accumulate ? fmaf(*o, cb, acc[i][j]) : acc[i][j];
+      }
+    }
+}
+
+// fp32 planes: hidden = silu(y0) * y2 (lr pointers null and dh null), or the lr-weighted gradient
+// planes (hidden*lr1, dy0*lr0, dy2*lr2).  Exact expf / division.  One warp per token row.
+__global__ void __launch_bounds__(256) swiglu_planes_f32_kernel(const float* y02, const float* dh, const void* lr0,
+                                                                const void* lr1, const void* lr2, int lr_f32,
+                                                                float w_scale, float* dy02, float* hid, int64_t rows,
+                                                                int H) {
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const float l0 = (lr0 ? load_scalar(lr0, lr_f32, row) : 1.f) * w_scale;
+  const float l1 = (lr1 ? load_scalar(lr1, lr_f32, row) : 1.f) * w_scale;
+  const float l2 = (lr2 ? load_scalar(lr2, lr_f32, row) : 1.f) * w_scale;
+  for (int c = lane; c < H; c += 32) {
+    const float y0 = y02[row * 2 * H + c], y2 = y02[row * 2 * H + H + c];
+    const float sg = 1.0f / (1.0f + expf(-y0)), sw = sg * y0;
+    hid[row * H + c] = sw * y2 * l1;
+    if (dh != nullptr) {
+      const float d = dh[row * H + c];
+      dy02[row * 2 * H + c] = sg * y2 * d * (1.0f + y0 * (1.0f - sg)) * l0;
+      dy02[row * 2 * H + H + c] = sw * d * l2;
+    }
+  }
+}
+
 // y = (x + x_add) * rsqrt(sum (x + x_add)^2 + eps) * scale[row]; one warp per row.
 __global__ void l2_norm_add_kernel(const void* x, int x_f32, const void* xa, int xa_f32, const float* scale, void* y,
                                    int y_f32, int64_t rows, int D, float eps) {

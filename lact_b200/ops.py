@@ -2,7 +2,8 @@
 
 Same names, positional order, keyword defaults and return types as the reference functions
 (cited per function); the arithmetic runs in the sm_100a kernels of liblact_b200.so through the
-C ABI.  Forward only: outputs do not carry autograd history.
+C ABI.  bf16 activations run the fused tcgen05 program (with a training backward); fp32 activations
+run the accuracy path of `fp32_mode` (forward only).
 """
 from __future__ import annotations
 
@@ -15,6 +16,14 @@ from . import _lib as L
 from . import program as P
 
 BF16 = torch.bfloat16
+
+
+def _no_trace(fn):
+    """The ops are ctypes calls into a CUDA library: TorchDynamo must not trace into them.  The
+    reference wraps its functions in @torch.compile; a caller that compiles its layer gets a graph
+    break around these calls instead of a tracing error."""
+    disable = getattr(getattr(torch, "compiler", None), "disable", None)
+    return disable(fn) if disable is not None else fn
 
 
 def _need_cuda(*ts: torch.Tensor) -> torch.device:
@@ -32,7 +41,7 @@ def _need_cuda(*ts: torch.Tensor) -> torch.device:
 
 def _act(t: torch.Tensor, name: str) -> torch.Tensor:
     if t.dtype != BF16:
-        raise TypeError(f"{name} must be bfloat16 (got {t.dtype}); cast the activations before the call")
+        raise TypeError(f"{name} must be bfloat16, or q, k, v all float32 (got {t.dtype})")
     if t.dim() != 3:
         raise ValueError(f"{name} must be [b, l, d]")
     if t.stride(2) != 1 or t.stride(1) % 8 or t.stride(0) % 8 or t.data_ptr() % 16:
@@ -61,6 +70,7 @@ def _weight(t: torch.Tensor, shape: tuple, name: str) -> torch.Tensor:
     return t.contiguous()
 
 
+@_no_trace
 def scan(w0, w1, w2, q, k, v, lr0, lr1, lr2, steps: Sequence[P.Step], *, out_len: Optional[int] = None,
          momentum=None, m_init=None, use_muon=False, ns_steps=5, ns_const_coeffs=False, ns_concat=False,
          ns_gram_right=False, renorm=L.RENORM_EPS_OUTSIDE, prenorm=False, prenorm_bf16=False, overwrite_quirk=False,
@@ -70,6 +80,12 @@ def scan(w0, w1, w2, q, k, v, lr0, lr1, lr2, steps: Sequence[P.Step], *, out_len
     and momentum state (fp32).  When gradients are enabled and an input requires grad, the call
     goes through `backward.ScanFunction` (training backward, see that module for what it covers)."""
     dev = _need_cuda(w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum)
+    if q.dtype == k.dtype == v.dtype == torch.float32:
+        return _scan_f32(dev, w0, w1, w2, q, k, v, lr0, lr1, lr2, steps, out_len, momentum, m_init,
+                         dict(use_muon=use_muon, ns_steps=ns_steps, ns_const_coeffs=ns_const_coeffs,
+                              ns_concat=ns_concat, ns_gram_right=ns_gram_right, renorm=renorm, prenorm=prenorm,
+                              prenorm_bf16=prenorm_bf16, overwrite_quirk=overwrite_quirk, w_scale=w_scale,
+                              return_state=return_state, return_momentum=return_momentum), _state_dump)
     if _state_dump is None and torch.is_grad_enabled() and any(
             torch.is_tensor(t) and t.requires_grad for t in (w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum)):
         from .backward import ScanFunction
@@ -161,6 +177,29 @@ def scan(w0, w1, w2, q, k, v, lr0, lr1, lr2, steps: Sequence[P.Step], *, out_len
     if return_momentum:
         res.extend(mom)
     return res[0] if len(res) == 1 else tuple(res)
+
+
+def _scan_f32(dev, w0, w1, w2, q, k, v, lr0, lr1, lr2, steps, out_len, momentum, m_init, opts, state_dump):
+    """fp32 activations: validate as `scan` does and run the step program in `fp32_mode`."""
+    from .fp32_mode import scan_f32
+    if state_dump is not None:
+        raise NotImplementedError("the per-update state dump is a bf16-mode feature")
+    if torch.is_grad_enabled() and any(torch.is_tensor(t) and t.requires_grad
+                                       for t in (w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum)):
+        raise NotImplementedError("fp32 mode is forward only; the training backward runs on bf16 activations")
+    for t, name in ((q, "q"), (k, "k"), (v, "v")):
+        if t.dim() != 3:
+            raise ValueError(f"{name} must be [b, l, d]")
+    B, Ltok, D = k.shape
+    H = w0.shape[1]
+    if q.shape[0] != B or q.shape[2] != D or v.shape != k.shape or q.shape[1] != Ltok:
+        raise ValueError("q, k, v shapes disagree")
+    w0, w1, w2 = _weight(w0, (B, H, D), "w0"), _weight(w1, (B, D, H), "w1"), _weight(w2, (B, H, D), "w2")
+    lr0, lr1, lr2 = (_vec(t, B, Ltok, n).float() for t, n in ((lr0, "lr0"), (lr1, "lr1"), (lr2, "lr2")))
+    if momentum is not None:
+        momentum = _vec(momentum, B, Ltok, "momentum")
+    return scan_f32(w0, w1, w2, q, k, v, lr0, lr1, lr2, steps, out_len=out_len, momentum=momentum, m_init=m_init,
+                    **opts)
 
 
 # ----------------------------------------------------------------------------------------------
@@ -293,6 +332,7 @@ def _bf16_contig(t: torch.Tensor, name: str) -> torch.Tensor:
     return t.contiguous()
 
 
+@_no_trace
 def fused_swiglu_ffn_fwd(W0_W2: torch.Tensor, W1: torch.Tensor, X: torch.Tensor) -> torch.Tensor:
     """lact_llm/lact_model/lact_triton_kernels/lact_swiglu_ffn.py:79-96: W0_W2 [B, 2H, D],
     W1 [B, D, H], X [B, N, D] (bf16) -> [B, N, D]."""
@@ -313,6 +353,7 @@ def fused_swiglu_ffn_fwd(W0_W2: torch.Tensor, W1: torch.Tensor, X: torch.Tensor)
     return out
 
 
+@_no_trace
 def fused_lact_swiglu_ffn_fast_weight_grads(W0_W2, W1, K, V, lr0, lr1, lr2):
     """lact_llm/lact_model/lact_triton_kernels/lact_fw_grad.py:159-175: returns (DW0_DW2
     [B, 2H, D], DW1 [B, D, H]) in bf16; lr0/1/2 are [B, N]."""
@@ -338,6 +379,7 @@ def fused_lact_swiglu_ffn_fast_weight_grads(W0_W2, W1, K, V, lr0, lr1, lr2):
     return dw02, dw1
 
 
+@_no_trace
 def zeropower_via_newtonschulz5(G: torch.Tensor, steps: Optional[int] = None) -> torch.Tensor:
     """Newton-Schulz orthogonalisation in bf16.  `steps=None`: the tuned 5-step schedule of
     lact_llm/lact_model/ttt_operation.py:30-66; `steps=int`: the constant-coefficient variant of
@@ -361,6 +403,7 @@ def zeropower_via_newtonschulz5(G: torch.Tensor, steps: Optional[int] = None) ->
     return x
 
 
+@_no_trace
 def l2_norm_add_fused(x, x_add, tgt_scale, eps: float = 1e-5, tgt_dtype=None) -> torch.Tensor:
     """lact_llm/lact_model/lact_triton_kernels/l2norm_triton_kernels.py:419-427."""
     dev = _need_cuda(x, x_add, tgt_scale)
@@ -380,6 +423,7 @@ def l2_norm_add_fused(x, x_add, tgt_scale, eps: float = 1e-5, tgt_dtype=None) ->
     return y
 
 
+@_no_trace
 def fused_prenorm_update_with_momentum_and_l2_norm(x_main, dx, dx_momentum, momentum_mu, tgt_scale, eps: float = 1e-5):
     """lact_llm/lact_model/lact_triton_kernels/triton_prenorm_update_with_momentum.py:379-401.
     Returns (y_main fp32, updated_momentum fp32, y_normalized bf16)."""
@@ -399,6 +443,7 @@ def fused_prenorm_update_with_momentum_and_l2_norm(x_main, dx, dx_momentum, mome
     return xo, mo, yo
 
 
+@_no_trace
 def bmm_bf16(a: torch.Tensor, b: torch.Tensor, a_mn_major: bool = False, b_mn_major: bool = False,
              out_dtype=torch.float32) -> torch.Tensor:
     """c = A B^T on the tcgen05 engine (test hook).  a: [batch, M, K] or, MN-major, [batch, K, M];
