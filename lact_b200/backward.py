@@ -8,10 +8,11 @@ autograd through the eager momentum / renormalisation lines (ttt_operation.py:17
 Like the reference's, the backward recomputes pre-activations in bf16 and returns bf16 gradients
 for activations, fp32 for learning rates, momentum and fast weights.
 
-Supported: post-norm recurrences (renorm none / eps outside / eps inside), momentum, any step
-program, Muon on or off (Newton-Schulz is recomputed in the backward; its roundings are treated as
-identities).  Pre-norm and the bidirectional overwrite are not built yet: they raise
-NotImplementedError when gradients are requested.
+Supported: post-norm and pre-norm recurrences (renorm none / eps outside / eps inside), the
+bidirectional overwrite (w <- renorm(NS(dw) + dw)), momentum, any step program, Muon on or off
+(Newton-Schulz is recomputed in the backward; its roundings are treated as identities).  Pre-norm
+keeps no per-update copy of the un-normalised master weights: they are rebuilt by one forward sweep
+over the saved gradients before the reverse sweep.
 """
 from __future__ import annotations
 
@@ -177,9 +178,8 @@ class ScanFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, opts, steps, w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum):
         from . import ops
-        if opts.get("prenorm") or opts.get("overwrite_quirk"):
-            raise NotImplementedError("gradients are implemented for post-norm recurrences only (no pre-norm, no "
-                                      "bidirectional overwrite); call under torch.no_grad() for inference")
+        if opts.get("prenorm") and opts.get("overwrite_quirk"):
+            raise NotImplementedError("no reference recurrence combines pre-norm with the bidirectional overwrite")
         n_upd = sum(1 for s in steps if s[0] == P.UPDATE)
         B, Ltok, D = k.shape
         H = w0.shape[1]
@@ -228,8 +228,33 @@ class ScanFunction(torch.autograd.Function):
             base = n02 + n1
             return dump[u, base:base + n02].view(B, 2 * H, D), dump[u, base + n02:base + n02 + n1].view(B, D, H)
 
+        prenorm, muon = bool(opts.get("prenorm")), bool(opts.get("use_muon"))
+        overwrite = bool(opts.get("overwrite_quirk")) and muon
+        nst, cc, gr = int(opts.get("ns_steps", 5)), bool(opts.get("ns_const_coeffs")), bool(opts.get("ns_gram_right"))
+
+        # pre-norm: master weights before each update, Wm_0 = W_0, Wm_{u+1} = Wm_u + U_u
+        masters = None
+        if prenorm:
+            from . import ops
+
+            def fast_ns(g):
+                st = nst if cc else None
+                if gr:
+                    return ops.zeropower_via_newtonschulz5(g.transpose(1, 2).contiguous(), st).transpose(1, 2)
+                return ops.zeropower_via_newtonschulz5(g, st)
+
+            masters = [(W0_02, W0_1)]
+            for u in range(n_upd - 1):
+                g02, g1 = grad_state(u)
+                if muon:
+                    g02 = fast_ns(g02) if opts.get("ns_concat") else torch.cat(
+                        [fast_ns(g02[:, :H]), fast_ns(g02[:, H:])], dim=1)
+                    g1 = fast_ns(g1)
+                masters.append((masters[-1][0] + g02.float(), masters[-1][1] + g1.float()))
+
         dW02 = torch.zeros(B, 2 * H, D, dtype=f32, device=dev)
         dW1 = torch.zeros(B, D, H, dtype=f32, device=dev)
+        dWm02 = dWm1 = None  # pre-norm: gradient w.r.t. the master weights after the current update
         dM02 = dM1 = None
         dn02 = torch.zeros(B, 2 * H, dtype=f32, device=dev)
         dn1 = torch.zeros(B, D, dtype=f32, device=dev)
@@ -263,24 +288,42 @@ class ScanFunction(torch.autograd.Function):
             G02, G1 = grad_state(u)
             # update applied to the weights: the gradient itself, or its Newton-Schulz image (recomputed)
             U02, U1, sv02, sv1 = G02.contiguous(), G1.contiguous(), None, None
-            if opts.get("use_muon"):
-                nst, cc, gr = int(opts.get("ns_steps", 5)), bool(opts.get("ns_const_coeffs")), bool(opts.get("ns_gram_right"))
+            if muon:
                 g02m = G02.contiguous() if opts.get("ns_concat") else G02.contiguous().view(2 * B, H, D)
                 sv02, U02 = ns_forward_saved(g02m, nst, cc, gr)
                 sv1, U1 = ns_forward_saved(G1.contiguous(), nst, cc, gr)
                 U02 = U02.view(B, 2 * H, D)
-            # renorm backward; dW becomes the gradient w.r.t. W_u
-            dWn02 = renorm_backward(Wp02.contiguous(), U02, n0_02, dW02, dn02, mode)
-            dWn1 = renorm_backward(Wp1.contiguous(), U1, n0_1, dW1, dn1, mode)
+            # renorm backward: dWn is the gradient w.r.t. (base + update); base is W_u, the master
+            # copy (pre-norm), or the gradient itself (bidirectional overwrite)
+            if prenorm:
+                b02, b1 = masters[u]
+            elif overwrite:
+                b02, b1 = G02, G1
+            else:
+                b02, b1 = Wp02, Wp1
+            dWn02 = renorm_backward(b02.contiguous(), U02, n0_02, dW02, dn02, mode)
+            dWn1 = renorm_backward(b1.contiguous(), U1, n0_1, dW1, dn1, mode)
+            if prenorm and dWm02 is not None:
+                dWn02 += dWm02
+                dWn1 += dWm1
             if sv02 is not None:
                 dG02 = ns_backward(sv02, dWn02.view(sv02["Gb"].shape)).view(B, 2 * H, D)
                 dG1 = ns_backward(sv1, dWn1)
+                if overwrite:
+                    dG02 = dG02 + dWn02
+                    dG1 = dG1 + dWn1
             else:
                 dG02, dG1 = dWn02.clone(), dWn1.clone()
             if dM02 is not None:
                 dG02 += dM02
                 dG1 += dM1
-            dW02, dW1 = dWn02, dWn1
+            if prenorm:        # the weights update u computed with receive gradient only from its own steps
+                dWm02, dWm1 = dWn02, dWn1
+                dW02, dW1 = torch.zeros_like(dWn02), torch.zeros_like(dWn1)
+            elif overwrite:    # the previous weights were overwritten: no direct path
+                dW02, dW1 = torch.zeros_like(dWn02), torch.zeros_like(dWn1)
+            else:
+                dW02, dW1 = dWn02, dWn1
             if ctx.has_momentum:
                 beta = momv[:, s:e].mean(dim=1)  # [B]
                 if u > 0:
@@ -299,6 +342,8 @@ class ScanFunction(torch.autograd.Function):
             dlr[2][:, s:e] += g2
             cnt = u
         check_status(dev)
+        if dWm02 is not None:  # W_0 is both the first master and the first compute copy
+            dW02, dW1 = dW02 + dWm02, dW1 + dWm1
         # the target row norms are functions of the initial weights (not detached in the LLM / AR paths)
         if not opts.get("_detach_norms", False):
             dW02 = dW02 + dn02.unsqueeze(-1) * W0_02 / n0_02.clamp_min(1e-30).unsqueeze(-1)

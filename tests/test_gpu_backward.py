@@ -123,14 +123,75 @@ def scan_autograd(orc, w0, w1, w2, q, k, v, l0, l1, l2, steps, cfg, m):
     return torch.cat(outs, dim=1), w0, w1, w2
 
 
-def test_backward_not_implemented_cases_raise(lb):
-    x = torch.zeros(1, 128, 64, device="cuda", dtype=BF16, requires_grad=True)
-    w = torch.randn(1, 64, 64, device="cuda")
-    lr = torch.full((1, 128, 1), 0.1, device="cuda")
-    with pytest.raises(NotImplementedError):
-        lb.prenorm_block_causal_lact_swiglu(w, w, w, x, x, x, lr, lr, lr, chunk_size=64)
-    with torch.no_grad():  # inference is unaffected
-        lb.prenorm_block_causal_lact_swiglu(w, w, w, x, x, x, lr, lr, lr, chunk_size=64)
+@pytest.mark.parametrize("mom", [False, True])
+def test_llm_prenorm_backward_muon_off(lb, mom):
+    """Pre-norm recurrence (un-normalised master copy, ttt_operation.py:217-364)."""
+    from oracle import lact_oracle as orc
+    B, L, D, H, C = 2, 576, 64, 64, 128
+    inp = orc.make_inputs(B, L, D, H, seed=24)
+    for n in ("q", "k", "v"):
+        inp[n] = inp[n].to(BF16)
+    dO = torch.randn(B, L, D, generator=torch.Generator().manual_seed(6)).to(BF16)
+    ref_fn = lambda w0, w1, w2, q, k, v, l0, l1, l2, m: orc.block_causal_lact_swiglu(
+        w0, w1, w2, q, k, v, l0, l1, l2, chunk_size=C, use_muon=False, momentum=m, prenorm=True)
+    cu_fn = lambda w0, w1, w2, q, k, v, l0, l1, l2, m: lb.prenorm_block_causal_lact_swiglu(
+        w0, w1, w2, q, k, v, l0, l1, l2, chunk_size=C, use_muon=False, momentum=m)
+    o_ref, g_ref = _grads_oracle(orc, inp, ref_fn, mom, dO)
+    o, g = _grads_cuda(inp, cu_fn, mom, dO)
+    assert orc.rel_max(o.float().cpu(), o_ref) <= 2e-2
+    _check(orc, g, g_ref, list(NAMES) + (["momentum"] if mom else []))
+
+
+def test_prenorm_fused_signature_backward_runs_with_muon(lb):
+    """bf16 normalised copy + Muon + momentum: finite gradients of the right shapes, and the
+    same gradients as the unfused pre-norm signature up to the bf16 copy."""
+    from oracle import lact_oracle as orc
+    B, L, D, H, C = 1, 384, 64, 64, 128
+    inp = orc.make_inputs(B, L, D, H, seed=25)
+    for n in ("q", "k", "v"):
+        inp[n] = inp[n].to(BF16)
+    dO = torch.randn(B, L, D, generator=torch.Generator().manual_seed(7)).to(BF16)
+    fn = lambda w0, w1, w2, q, k, v, l0, l1, l2, m: lb.prenorm_block_causal_lact_swiglu_fused_kernel_triton(
+        w0, w1, w2, q, k, v, l0, l1, l2, chunk_size=C, use_muon=True, momentum=m)
+    o, g = _grads_cuda(inp, fn, True, dO)
+    for n in list(NAMES) + ["momentum"]:
+        assert g[n] is not None and torch.isfinite(g[n]).all(), n
+    assert g["q"].shape == inp["q"].shape and g["w1"].shape == inp["w1"].shape
+    # tokens of chunk 0 see the initial weights only: their dq equals the Muon-off dq
+    fn0 = lambda w0, w1, w2, q, k, v, l0, l1, l2, m: lb.prenorm_block_causal_lact_swiglu_fused_kernel_triton(
+        w0, w1, w2, q, k, v, l0, l1, l2, chunk_size=C, use_muon=False, momentum=m)
+    _, g0 = _grads_cuda(inp, fn0, True, dO)
+    assert torch.equal(g["q"][:, :C], g0["q"][:, :C])
+
+
+@pytest.mark.parametrize("muon", [False, True])
+def test_bidirectional_backward(lb, muon):
+    """minimal_implementations/bidirectional_lact_layer.py:73-160 with gradients.  With Muon the
+    weights are overwritten, w <- renorm(NS(dw) + dw): the gradient reaches the initial weights
+    only through dw (and the target norms)."""
+    from oracle import lact_oracle as orc
+    B, L, D, H = 2, 256, 64, 64
+    inp = orc.make_inputs(B, L, D, H, seed=26)
+    for n in ("q", "k", "v"):
+        inp[n] = inp[n].to(BF16)
+    dO = torch.randn(B, L, D, generator=torch.Generator().manual_seed(8)).to(BF16)
+    ref_fn = lambda w0, w1, w2, q, k, v, l0, l1, l2, m: orc.bidirectional_lact_swiglu(
+        w0, w1, w2, q, k, v, l0, l1, l2, use_muon=muon)
+    cu_fn = lambda w0, w1, w2, q, k, v, l0, l1, l2, m: lb.bidirectional_lact_swiglu(
+        w0, w1, w2, q, k, v, l0, l1, l2, use_muon=muon)
+    o_ref, g_ref = _grads_oracle(orc, inp, ref_fn, False, dO)
+    o, g = _grads_cuda(inp, cu_fn, False, dO)
+    if not muon:
+        _check(orc, g, g_ref, list(NAMES))
+        return
+    for n in NAMES:  # one bf16 Newton-Schulz pass between inputs and output: loose band
+        a, b = g[n].float().cpu(), g_ref[n].float()
+        assert torch.isfinite(a).all(), n
+        if n == "q":  # dq depends on the updated weights only through the forward values
+            assert orc.cosine(a, b) >= 0.995, (n, orc.cosine(a, b))
+        else:
+            assert orc.cosine(a, b) >= 0.95, (n, orc.cosine(a, b))
+            assert orc.rel_fro(a, b) <= 0.35, (n, orc.rel_fro(a, b))
 
 
 @pytest.mark.parametrize("shape,steps", [((3, 64, 64), None), ((2, 64, 128), 5), ((2, 128, 64), 3), ((2, 192, 192), None)])
