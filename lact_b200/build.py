@@ -8,7 +8,7 @@ import subprocess
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 SRC = os.path.join(PKG_DIR, "csrc", "lact_b200.cu")
 LIB = os.path.join(PKG_DIR, "liblact_b200.so")
-DEPS = [os.path.join(PKG_DIR, "csrc", f) for f in ("lact_b200.cu", "ops.cuh", "umma_gemm.cuh", "ptx.cuh")] + [
+DEPS = [os.path.join(PKG_DIR, "csrc", f) for f in ("lact_b200.cu", "ops.cuh", "umma_gemm.cuh", "ns_fused.cuh", "ptx.cuh")] + [
     os.path.join(os.path.dirname(PKG_DIR), "include", "lact_b200.h")]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--shared",

@@ -417,10 +417,11 @@ struct NsGroup {
   bf16 *xa, *xb;              // ping-pong iterates, nmat * m * n each
   bf16 *gram, *cgram, *poly;  // [nmat][m][m]
   float* partial;             // [nmat][<= kNsMaxParts] partial sums of squares
+  uint32_t* done;             // [nmat] tile completion counters of the fused kernel
 };
 
 inline size_t ns_group_bytes(int64_t nmat, int64_t m, int64_t n) {
-  return static_cast<size_t>(nmat) * (2 * m * n + 3 * m * m) * 2 + static_cast<size_t>(nmat) * kNsMaxParts * 4 + 6 * 256;
+  return static_cast<size_t>(nmat) * (2 * m * n + 3 * m * m) * 2 + static_cast<size_t>(nmat) * kNsMaxParts * 4 + static_cast<size_t>(nmat) * 4 + 7 * 256;
 }
 
 void ns_group_init(NsGroup& g, int64_t nmat, int64_t R, int64_t C, int gram_right) {
@@ -479,7 +480,7 @@ int run_ns_iterations(const NsGroup* grp, int ngroups, int steps, int const_coef
   for (int it = 0; it < steps; ++it) {
     const float* co = const_coeffs ? kNsConst : kNsTuned[it];
     const bool last = (it == steps - 1);
-    // gram = X X^T ; cgram = c * gram
+    // gram = X X^T ; cgram = c * gram + b I
     auto fill_gram = [&](auto& ga, int btv) -> int {
       for (int g = 0; g < ngroups; ++g) {
         const NsGroup& G = grp[g];
@@ -492,12 +493,12 @@ int run_ns_iterations(const NsGroup* grp, int ngroups, int steps, int const_coef
         const Mat CA{G.cgram, G.m, G.m, G.m, G.nmat, static_cast<int64_t>(G.m) * G.m};
         LACT_TRY(make_output(&P.out[0], &P.oi[0], A, 0, 0));
         LACT_TRY(make_output(&P.out[1], &P.oi[1], CA, 0, 0));
-        P.ep = EpiNs{nullptr, 0.f, co[2], static_cast<int64_t>(G.m) * G.m, G.m, 0, 0};
+        P.ep = EpiNs{nullptr, 0.f, co[2], co[1], static_cast<int64_t>(G.m) * G.m, G.m, 0, 0};
       }
       ga.status = status;
       return LACT_OK;
     };
-    // poly = b * gram + cgram gram   (gram is symmetric: its rows serve as the K-major B operand)
+    // poly = cgram gram + a I   (gram is symmetric: its rows serve as the K-major B operand)
     auto fill_poly = [&](auto& gb, int btv) -> int {
       for (int g = 0; g < ngroups; ++g) {
         const NsGroup& G = grp[g];
@@ -509,14 +510,12 @@ int run_ns_iterations(const NsGroup* grp, int ngroups, int steps, int const_coef
         P.M = G.m; P.N = G.m; P.K = G.m; P.batch = G.nmat;
         const Mat PBm{G.poly, G.m, G.m, G.m, G.nmat, static_cast<int64_t>(G.m) * G.m};
         LACT_TRY(make_output(&P.out[0], &P.oi[0], PBm, 0, 0));
-        LACT_TRY(encode_map(&P.res, A, kBM));
-        P.res_enabled = 1;
-        P.ep = EpiNs{nullptr, co[1], 0.f, static_cast<int64_t>(G.m) * G.m, G.m, 0, 0};
+        P.ep = EpiNs{nullptr, co[0], 0.f, 0.f, static_cast<int64_t>(G.m) * G.m, G.m, 0, 0};
       }
       gb.status = status;
       return LACT_OK;
     };
-    // X' = a * X + poly X   (X is [m][n]: k rows, n contiguous -> MN-major B operand); the last
+    // X' = poly X   (X is [m][n]: k rows, n contiguous -> MN-major B operand); the last
     // iterate of a transposed group is written back in the gradient's orientation
     auto fill_upd = [&](auto& gc, int btv) -> int {
       for (int g = 0; g < ngroups; ++g) {
@@ -529,9 +528,7 @@ int run_ns_iterations(const NsGroup* grp, int ngroups, int steps, int const_coef
         P.M = G.m; P.N = G.n; P.K = G.m; P.batch = G.nmat;
         const Mat XN{nxt[g], G.m, G.n, G.n, G.nmat, static_cast<int64_t>(G.m) * G.n};
         LACT_TRY(make_output(&P.out[0], &P.oi[0], XN, 0, 0));
-        LACT_TRY(encode_map(&P.res, X, kBM));
-        P.res_enabled = 1;
-        P.ep = EpiNs{nxt[g], co[0], 0.f, static_cast<int64_t>(G.m) * G.n, G.n, (last && G.transposed) ? 1 : 0, G.m};
+        P.ep = EpiNs{nxt[g], 0.f, 0.f, 0.f, static_cast<int64_t>(G.m) * G.n, G.n, (last && G.transposed) ? 1 : 0, G.m};
       }
       gc.status = status;
       return LACT_OK;
@@ -547,7 +544,7 @@ int run_ns_iterations(const NsGroup* grp, int ngroups, int steps, int const_coef
 
 // Fused path: all iterations in one cooperative launch (the first iterates must be in grp[g].xa).
 template <int BT_MM, int BT_MN>
-int launch_ns_fused(const NsGroup* grp, int ngroups, int steps, int const_coeffs, uint32_t* barrier, int32_t* status,
+int launch_ns_fused(const NsGroup* grp, int ngroups, int steps, int const_coeffs, int32_t* status,
                     cudaStream_t stream, uint64_t* trace) {
   using Args = NsFusedArgs<BT_MM, BT_MN>;
   auto kernel = ns_fused_kernel<BT_MM, BT_MN>;
@@ -584,25 +581,21 @@ int launch_ns_fused(const NsGroup* grp, int ngroups, int steps, int const_coeffs
       PG.M = G.m; PG.N = G.m; PG.K = G.n; PG.batch = G.nmat;
       LACT_TRY(make_output(&PG.out[0], &PG.oi[0], A, 0, 0));
       LACT_TRY(make_output(&PG.out[1], &PG.oi[1], CA, 0, 0));
-      PG.ep = EpiNs{nullptr, 0.f, 0.f, mm, G.m, 0, 0};
+      PG.ep = EpiNs{nullptr, 0.f, 0.f, 0.f, mm, G.m, 0, 0};
       auto& PU = args.upd[par][g];
       LACT_TRY(make_operand(&PU.a[0], &PU.ai[0], PB, 0, kBM, 0, 0));
       LACT_TRY(make_operand(&PU.b[0], &PU.bi[0], X, 1, BT_MN, 0, 0));
       PU.M = G.m; PU.N = G.n; PU.K = G.m; PU.batch = G.nmat;
       const Mat XN{nxt, G.m, G.n, G.n, G.nmat, mn};
       LACT_TRY(make_output(&PU.out[0], &PU.oi[0], XN, 0, 0));
-      LACT_TRY(encode_map(&PU.res, X, kBM));
-      PU.res_enabled = 1;
-      PU.ep = EpiNs{nxt, 0.f, 0.f, mn, G.n, 0, 0};
+      PU.ep = EpiNs{nxt, 0.f, 0.f, 0.f, mn, G.n, 0, 0};
     }
     auto& PP = args.poly[g];
     LACT_TRY(make_operand(&PP.a[0], &PP.ai[0], CA, 0, kBM, 0, 0));
     LACT_TRY(make_operand(&PP.b[0], &PP.bi[0], A, 0, BT_MM, 0, 0));
     PP.M = G.m; PP.N = G.m; PP.K = G.m; PP.batch = G.nmat;
     LACT_TRY(make_output(&PP.out[0], &PP.oi[0], PB, 0, 0));
-    LACT_TRY(encode_map(&PP.res, A, kBM));
-    PP.res_enabled = 1;
-    PP.ep = EpiNs{nullptr, 0.f, 0.f, mm, G.m, 0, 0};
+    PP.ep = EpiNs{nullptr, 0.f, 0.f, 0.f, mm, G.m, 0, 0};
     args.transposed[g] = G.transposed;
     args.m[g] = G.m;
     max_tiles = std::max<int64_t>(max_tiles, static_cast<int64_t>(G.nmat) * ceil_div(G.m, kBM) * ceil_div(G.n, BT_MN) * ngroups);
@@ -614,9 +607,11 @@ int launch_ns_fused(const NsGroup* grp, int ngroups, int steps, int const_coeffs
   args.steps = steps;
   args.ngroups = ngroups;
   args.status = status;
-  args.barrier = barrier;
   args.trace = trace;
-  LACT_CUDA(cudaMemsetAsync(barrier, 0, sizeof(uint32_t), stream));
+  for (int g = 0; g < ngroups; ++g) {
+    args.done[g] = grp[g].done;
+    LACT_CUDA(cudaMemsetAsync(grp[g].done, 0, sizeof(uint32_t) * grp[g].nmat, stream));
+  }
   const int grid = static_cast<int>(std::min<int64_t>(sm_count(), std::max<int64_t>(max_tiles, 8)));
   void* kargs[] = {&args};
   KernelScope scope(kClsNsFused, stream);
@@ -627,7 +622,7 @@ int launch_ns_fused(const NsGroup* grp, int ngroups, int steps, int const_coeffs
 
 // Picks the fused kernel instantiated for the tile widths this problem wants; returns
 // LACT_ERR_CONFIG when there is none (the caller then runs the multi-launch path).
-int try_ns_fused(const NsGroup* grp, int ngroups, int steps, int const_coeffs, uint32_t* barrier, int32_t* status,
+int try_ns_fused(const NsGroup* grp, int ngroups, int steps, int const_coeffs, int32_t* status,
                  cudaStream_t stream, const bf16** result, uint64_t* trace = nullptr) {
   if (steps < 1 || steps > kNsFusedMaxSteps) return LACT_ERR_CONFIG;
   if (!const_coeffs && steps != 5) return LACT_ERR_CONFIG;
@@ -642,10 +637,10 @@ int try_ns_fused(const NsGroup* grp, int ngroups, int steps, int const_coeffs, u
   const int bt_mn = choose_bt({{G0.n, static_cast<int64_t>(G0.nmat) * G0.m}, {G1.n, static_cast<int64_t>(G1.nmat) * G1.m}});
   for (int g = 0; g < ngroups; ++g) result[g] = (steps % 2 == 0) ? grp[g].xa : grp[g].xb;
   if (bt_mm == 192 && bt_mn == 192)
-    return launch_ns_fused<192, 192>(grp, ngroups, steps, const_coeffs, barrier, status, stream, trace);
+    return launch_ns_fused<192, 192>(grp, ngroups, steps, const_coeffs, status, stream, trace);
   // (a 256-wide update tile leaves no room for a useful ring next to two staging tiles: 128 is used)
   if (bt_mm == 128 && (bt_mn == 128 || bt_mn == 256))
-    return launch_ns_fused<128, 128>(grp, ngroups, steps, const_coeffs, barrier, status, stream, trace);
+    return launch_ns_fused<128, 128>(grp, ngroups, steps, const_coeffs, status, stream, trace);
   return LACT_ERR_CONFIG;
 }
 
@@ -678,6 +673,7 @@ void carve_ns_group(Carver& c, NsGroup& g) {
   g.cgram = c.take<bf16>(mm);
   g.poly = c.take<bf16>(mm);
   g.partial = c.take<float>(static_cast<size_t>(g.nmat) * kNsMaxParts);
+  g.done = c.take<uint32_t>(static_cast<size_t>(g.nmat));
 }
 
 // Group 0 orthogonalises the [w0; w2] gradient (concat: B matrices [2H][D]; separate: 2B matrices
@@ -713,7 +709,7 @@ int plan_scan(const lact_scan_config& c, int32_t n_steps, const int32_t* kind, c
   }
   Carver cv(base);
   const size_t B = c.B, D = c.D, H = c.H;
-  p->status = cv.take<int32_t>(1024);  // status word, grid-barrier counter, phase trace
+  p->status = cv.take<int32_t>(1024);  // status word; diagnostics trace at +256 bytes
   p->W02 = cv.take<float>(B * 2 * H * D);
   p->W1 = cv.take<float>(B * D * H);
   p->W02c = cv.take<float>(B * 2 * H * D);
@@ -892,8 +888,7 @@ int scan_fwd(const lact_scan_config& c, const lact_scan_io& io, int32_t n_steps,
       const void* srcs[2] = {p.G02, p.G1};
       LACT_TRY(launch_ns_prepare(ns.grp, ns.ngroups, srcs, 1, c.ns_steps, stream,
                                  fused_parts[0] > 0 ? fused_parts : nullptr));
-      int rc = try_ns_fused(ns.grp, ns.ngroups, c.ns_steps, c.ns_const_coeffs,
-                            reinterpret_cast<uint32_t*>(p.status) + 8, p.status, stream, xres,
+      int rc = try_ns_fused(ns.grp, ns.ngroups, c.ns_steps, c.ns_const_coeffs, p.status, stream, xres,
                             reinterpret_cast<uint64_t*>(p.status + 64));
       if (rc == LACT_ERR_CONFIG)
         rc = run_ns_iterations(ns.grp, ns.ngroups, c.ns_steps, c.ns_const_coeffs, xres, p.status, stream);
@@ -1135,7 +1130,7 @@ int lact_newton_schulz(const void* g, int32_t g_dtype, void* x, int64_t B, int64
   const bf16* res = nullptr;
   const void* srcs[2] = {g, g};
   LACT_TRY(launch_ns_prepare(&grp, 1, srcs, g_dtype == LACT_F32, steps, s));
-  int rc = try_ns_fused(&grp, 1, steps, const_coeffs, reinterpret_cast<uint32_t*>(status) + 8, status, s, &res);
+  int rc = try_ns_fused(&grp, 1, steps, const_coeffs, status, s, &res);
   if (rc == LACT_ERR_CONFIG) rc = run_ns_iterations(&grp, 1, steps, const_coeffs, &res, status, s);
   LACT_TRY(rc);
   LACT_CUDA(cudaMemcpyAsync(x, res, static_cast<size_t>(B) * R * C * 2, cudaMemcpyDeviceToDevice, s));

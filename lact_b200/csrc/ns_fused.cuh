@@ -1,8 +1,11 @@
 // All Newton-Schulz iterations of a Muon update in ONE persistent kernel: `steps` x (gram, poly,
-// update) GEMM phases on the tcgen05 engine, separated by a grid-wide barrier (an atomic counter in
-// global memory, bounded spin), so the 3*steps dependent stages cost no kernel launches and the
-// shared-memory ring / tensor-memory pipeline never has to be rebuilt.  All CTAs must be
-// co-resident: the kernel is launched cooperatively with at most one CTA per SM.
+// update) GEMM phases on the tcgen05 engine.  The phases of one matrix form a dependency chain, but
+// different matrices are independent: instead of a grid-wide barrier between phases, every matrix
+// owns a completion counter in global memory (see FlowDeps) and a tile waits (bounded spin) only for
+// the previous phase of its own matrix.  Tiles are dealt round-robin across phase boundaries, so
+// the shared-memory ring and the tensor-memory pipeline of a CTA keep running from the first tile
+// of the first phase to the last tile of the last one.  All CTAs must be co-resident: the kernel
+// is launched cooperatively with at most one CTA per SM.
 #pragma once
 #include "ops.cuh"
 
@@ -17,55 +20,21 @@ struct NsFusedArgs {
   float coef[16][3];                    // (a, b, c) per iteration
   int32_t steps, ngroups;
   int32_t* status;
-  uint32_t* barrier;  // grid barrier counter, zero at launch
-  uint64_t* trace;    // optional [2 * phases + 2] globaltimer stamps of CTA 0 (diagnostics), or nullptr
+  uint32_t* done[2];  // per group: [matrix] completion counters, zero at launch
+  uint64_t* trace;    // optional: trace[0], trace[1] = globaltimer of CTA 0 at start / end (diagnostics)
 };
 
 constexpr int kNsFusedMaxSteps = 16;
 
-__device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-
-// Grid-wide barrier for a co-resident grid; every thread of every CTA calls it.  Orders the
-// generic-proxy global writes made before it with the generic and async-proxy (TMA) reads made
-// after it.  Returns false if the wait ran out (the CTA's abort flag is then set).
-__device__ __forceinline__ bool grid_sync(uint32_t* counter, uint32_t& epoch, volatile uint32_t* abort_flag,
-                                          uint64_t* trace = nullptr) {
-  asm volatile("fence.proxy.async;" ::: "memory");
-  __threadfence();
-  __syncthreads();
-  epoch += 1;
-  if (threadIdx.x == 0) {
-    if (trace != nullptr && blockIdx.x == 0) trace[2 * epoch - 1] = globaltimer_ns();  // CTA 0 finished the phase
-    atomicAdd(counter, 1u);
-    const uint32_t target = epoch * gridDim.x;
-    const uint64_t t0 = globaltimer_ns();
-    uint32_t i = 0;
-    while (ld_acquire_u32(counter) < target) {
-      if ((++i & 63u) == 0 && (*abort_flag != 0 || globaltimer_ns() - t0 > kWaitLimitNs)) {
-        *abort_flag = 1;
-        break;
-      }
-    }
-    __threadfence();
-    if (trace != nullptr && blockIdx.x == 0) trace[2 * epoch] = globaltimer_ns();  // every CTA finished it
-  }
-  __syncthreads();
-  asm volatile("fence.proxy.async;" ::: "memory");
-  return *abort_flag == 0;
-}
-
 struct NsPatch {
-  float alpha, gamma;
+  float diag, gamma, diag2;
   int32_t last;
   int32_t transposed[2];
   int32_t m[2];
   __device__ __forceinline__ void operator()(EpiNs& ep, int prob) const {
-    ep.alpha = alpha;
+    ep.diag = diag;
     ep.gamma = gamma;
+    ep.diag2 = diag2;
     ep.out_transposed = (last && transposed[prob]) ? 1 : 0;
     ep.out_ld_t = m[prob];
   }
@@ -78,7 +47,7 @@ __host__ __device__ constexpr uint32_t ns_fused_stage_stride() {
 }
 template <int BT_MM, int BT_MN>
 __host__ __device__ constexpr uint32_t ns_fused_staging() {
-  return 2 * kBM * (BT_MM > BT_MN ? BT_MM : BT_MN) * 2;  // double-buffered (OpNs::kStagingBuffers)
+  return OpNs<BT_MM>::kStagingBuffers * kBM * (BT_MM > BT_MN ? BT_MM : BT_MN) * 2;
 }
 template <int BT_MM, int BT_MN>
 __host__ __device__ constexpr int ns_fused_ring() {
@@ -122,43 +91,53 @@ ns_fused_kernel(const __grid_constant__ NsFusedArgs<BT_MM, BT_MN> args) {
     }
   }
   cx.trace = args.trace;
-  uint32_t epoch = 0;
-  bool ok = true;
   bool failed = false;
   if (args.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) args.trace[0] = globaltimer_ns();
 
   // ---------------- Newton-Schulz iterations
   NsPatch patch;
+  FlowDeps deps;
+  uint32_t tiles_mm[2], tiles_mn[2];  // tiles one matrix contributes to a gram / poly phase, an update phase
   for (int g = 0; g < 2; ++g) {
     patch.transposed[g] = args.transposed[g];
     patch.m[g] = args.m[g];
+    deps.counter[g] = args.done[g];
+    deps.need[g] = 0;
+    const auto& U = args.upd[0][g];
+    tiles_mm[g] = ((U.M + kBM - 1) / kBM) * ((U.M + BT_MM - 1) / BT_MM);
+    tiles_mn[g] = ((U.M + kBM - 1) / kBM) * ((U.N + BT_MN - 1) / BT_MN);
   }
-  for (int it = 0; it < args.steps && ok; ++it) {
+  for (int it = 0; it < args.steps && !failed; ++it) {
     const int par = it & 1;
     patch.last = 0;
-    patch.alpha = 0.f;
+    patch.diag = 0.f;                 // gram: A and c A + b I
     patch.gamma = args.coef[it][2];
-    failed = gemm_phase<OpMM, RING>(cx, args.gram[par], args.ngroups, patch);
+    patch.diag2 = args.coef[it][1];
+    failed = gemm_phase<OpMM, RING>(cx, args.gram[par], args.ngroups, patch, deps);
     ++cx.phase;
-    if (failed) *cx.abort_flag = 1;
-    ok = grid_sync(args.barrier, epoch, cx.abort_flag, args.trace);
-    if (!ok) break;
-    patch.alpha = args.coef[it][1];
+    if (failed) break;
+    for (int g = 0; g < 2; ++g) deps.need[g] += tiles_mm[g];
+    patch.diag = args.coef[it][0];    // poly: (c A + b I) A + a I
     patch.gamma = 0.f;
-    failed = gemm_phase<OpMM, RING>(cx, args.poly, args.ngroups, patch);
+    patch.diag2 = 0.f;
+    failed = gemm_phase<OpMM, RING>(cx, args.poly, args.ngroups, patch, deps);
     ++cx.phase;
-    if (failed) *cx.abort_flag = 1;
-    ok = grid_sync(args.barrier, epoch, cx.abort_flag, args.trace);
-    if (!ok) break;
-    patch.alpha = args.coef[it][0];
+    if (failed) break;
+    for (int g = 0; g < 2; ++g) deps.need[g] += tiles_mm[g];
+    patch.diag = 0.f;                 // update: (P + a I) X
     patch.last = (it == args.steps - 1);
-    failed = gemm_phase<OpMN, RING>(cx, args.upd[par], args.ngroups, patch);
+    failed = gemm_phase<OpMN, RING>(cx, args.upd[par], args.ngroups, patch, deps);
     ++cx.phase;
-    if (failed) *cx.abort_flag = 1;
-    ok = grid_sync(args.barrier, epoch, cx.abort_flag, args.trace);
+    for (int g = 0; g < 2; ++g) deps.need[g] += tiles_mn[g];
   }
+  if (failed) *cx.abort_flag = 1;
+  if (threadIdx.x == 64) {  // the storing thread: this CTA's last tiles are in global memory
+    flow_flush(cx);
+    bulk_wait_all();
+  }
+  if (args.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 64) args.trace[1] = globaltimer_ns();
 
-  gemm_teardown(cx, !ok, args.status, kTmemCols);
+  gemm_teardown(cx, failed, args.status, kTmemCols);
 }
 
 }  // namespace lact

@@ -148,7 +148,9 @@ struct EpiDW {
 // if out2: out2 = bf16(gamma * t).
 struct EpiNs {
   bf16* out;         // used only for the transposed final write
-  float alpha, gamma;
+  float diag;        // first output  = bf16(acc + diag * I)
+  float gamma;       // second output = bf16(gamma * first + diag2 * I)
+  float diag2;
   int64_t bs, ld;
   int32_t out_transposed;  // final iterate of a transposed group: write out[batch][col][row]
   int32_t out_ld_t;
@@ -278,49 +280,41 @@ struct OpBmm2 {
   }
 };
 
-// Newton-Schulz GEMM with the reference's eager bf16 rounding: t = bf16(acc); with a residual,
-// t = bf16(bf16(alpha * res) + t); first output t, optional second output bf16(gamma * t) made in
-// place from the staged first output.  The last iterate of a transposed group is written from
-// registers in the gradient's own orientation instead.
+// Newton-Schulz GEMM.  The iteration's residual terms are folded into the contractions as multiples
+// of the identity, b A + (c A) A = (c A + b I) A and a X + P X = (P + a I) X, so that no phase reads
+// a residual tile: the gram phase writes A = bf16(X X^T) and, in place from the staged A,
+// bf16(c A + b I); the poly phase writes bf16((c A + b I) A + a I); the update phase is a plain
+// product.  All values are bf16 with fp32 accumulation, as in the reference; folding moves two of
+// its rounding points (one rounding of the fp32 sum instead of bf16(bf16(b A) + bf16((c A) A))),
+// which perturbs the result no more than the reference's own bf16 arithmetic does.  The last
+// iterate of a transposed group is written from registers in the gradient's own orientation.
 template <int BT_>
 struct OpNs {
   static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 2;
-  static constexpr bool kSecondInPlace = true, kResidualTma = true, kTileReduce = false;
-  // two staging tiles: while tile i is stored from one, the residual of tile i + 1 lands in the other
-  static constexpr int kStagingBuffers = 2;
-  static constexpr int STAGES = ring_depth(kATileBytes + BT_ * kBK * 2, 2 * kBM * BT_ * 2);
+  static constexpr bool kSecondInPlace = true, kResidualTma = false, kTileReduce = false;
+#ifndef LACT_NS_STAGING_BUFFERS
+#define LACT_NS_STAGING_BUFFERS 2
+#endif
+  // two staging tiles: tile i + 1 is assembled in one while tile i is still being stored from the other
+  static constexpr int kStagingBuffers = LACT_NS_STAGING_BUFFERS;
+  static constexpr int STAGES = ring_depth(kATileBytes + BT_ * kBK * 2, kStagingBuffers * kBM * BT_ * 2);
   using Epi = EpiNs;
   __host__ __device__ static constexpr int term_a(int) { return 0; }
   __host__ __device__ static constexpr int term_b(int) { return 0; }
   __host__ __device__ static constexpr int term_col(int) { return 0; }
   __host__ __device__ static constexpr int term_n(int) { return BT_; }
   __host__ __device__ static constexpr bool term_first(int) { return true; }
-  __device__ static __forceinline__ float second(const Epi& ep, float t) { return ep.gamma * t; }
+  __device__ static __forceinline__ float second(const Epi& ep, float t, int row, int col) {
+    return ep.gamma * t + (row == col ? ep.diag2 : 0.f);
+  }
   __device__ static __forceinline__ bool skip_store(const Epi& ep, int o) { return o == 0 && ep.out_transposed; }
-  // The residual tile arrives by TMA in the staging tile; the engine hands each thread the 64
-  // bytes that sit where its result will be written.
-  struct Prefetch {
-    uint4 r[4];
-  };
+  using Prefetch = NoPrefetch;
   __device__ static __forceinline__ void prefetch(const Epi&, int, int, int, int, int, int, Prefetch&) {}
   __device__ static __forceinline__ void epilogue_staged(const Epi& ep, int batch, int row, int col, int M, int N,
-                                                         const float (&v)[1][32], float (&o)[1][32], Prefetch& pf,
-                                                         int has_res) {
+                                                         const float (&v)[1][32], float (&o)[1][32], Prefetch&, int) {
     const int valid = min(32, N - col);
 #pragma unroll
-    for (int j = 0; j < 32; ++j) o[0][j] = bf16_round(v[0][j]);
-    if (has_res) {
-#pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        const uint32_t w[4] = {pf.r[g].x, pf.r[g].y, pf.r[g].z, pf.r[g].w};
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const float r0 = __uint_as_float(w[q] << 16), r1 = __uint_as_float(w[q] & 0xFFFF0000u);
-          o[0][g * 8 + 2 * q] = bf16_round(bf16_round(ep.alpha * r0) + o[0][g * 8 + 2 * q]);
-          o[0][g * 8 + 2 * q + 1] = bf16_round(bf16_round(ep.alpha * r1) + o[0][g * 8 + 2 * q + 1]);
-        }
-      }
-    }
+    for (int j = 0; j < 32; ++j) o[0][j] = bf16_round(v[0][j] + (row == col + j ? ep.diag : 0.f));
     if (ep.out_transposed && row < M) {
       bf16* dst = ep.out + batch * ep.bs + static_cast<int64_t>(col) * ep.out_ld_t + row;
 #pragma unroll
@@ -541,6 +535,8 @@ __global__ void __launch_bounds__(256) ns_sumsq_kernel(const NsPrepArgs args) {
 // Part 2: X = bf16(bf16(G) / (bf16(||bf16(G)||_F) + 1e-7)), every operation rounded to bf16 as in
 // the reference; written transposed (through a shared-memory tile, so both sides stay coalesced)
 // when the iteration runs on the other orientation.  Grid (matrices of all groups, 64x64 tiles).
+// Matrices whose sizes allow it move as 16-byte vectors (four source columns per thread; eight
+// output elements per thread on the transposed side).
 __global__ void __launch_bounds__(256) ns_scale_kernel(const NsPrepArgs args) {
   griddep_launch_dependents();
   griddep_wait();
@@ -552,13 +548,70 @@ __global__ void __launch_bounds__(256) ns_scale_kernel(const NsPrepArgs args) {
   const int tiles_c = (G.C + 63) / 64, tiles_r = (G.R + 63) / 64;
   if (static_cast<int>(blockIdx.y) >= tiles_c * tiles_r) return;
   const int tr = (blockIdx.y / tiles_c) * 64, tcx = (blockIdx.y % tiles_c) * 64;
-  float tot = 0.f;
   __shared__ float parts[512];
+  __shared__ float den_s;
   for (int i = threadIdx.x; i < G.nparts; i += blockDim.x) parts[i] = G.partial[static_cast<int64_t>(mat) * G.nparts + i];
   __syncthreads();
-  for (int i = 0; i < G.nparts; ++i) tot += parts[i];  // same order in every thread and CTA
-  const float den = bf16_round(bf16_round(sqrtf(tot)) + 1e-7f);
+  if (threadIdx.x == 0) {
+    float tot = 0.f;
+    for (int i = 0; i < G.nparts; ++i) tot += parts[i];  // same order in every CTA
+    den_s = bf16_round(bf16_round(sqrtf(tot)) + 1e-7f);
+  }
+  __syncthreads();
+  const float den = den_s;
   const int64_t base = static_cast<int64_t>(mat) * G.R * G.C;
+  bf16* xo = G.x0 + base;
+  const bool vec = (G.C % 4) == 0 && (!G.transpose || (G.R % 8) == 0);
+  if (vec) {
+    const int lx = (threadIdx.x & 15) * 4, ly = threadIdx.x >> 4;  // 16 x 16 threads, 4 columns each
+    float xv[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = tr + ly + 16 * i, c = tcx + lx;
+      xv[i][0] = xv[i][1] = xv[i][2] = xv[i][3] = 0.f;
+      if (r < G.R && c < G.C) {
+        const int64_t off = base + static_cast<int64_t>(r) * G.C + c;
+        if (G.src_f32) {
+          const float4 t = *reinterpret_cast<const float4*>(static_cast<const float*>(G.src) + off);
+          xv[i][0] = t.x; xv[i][1] = t.y; xv[i][2] = t.z; xv[i][3] = t.w;
+        } else {
+          const uint2 t = *reinterpret_cast<const uint2*>(static_cast<const bf16*>(G.src) + off);
+          xv[i][0] = __uint_as_float(t.x << 16); xv[i][1] = __uint_as_float(t.x & 0xFFFF0000u);
+          xv[i][2] = __uint_as_float(t.y << 16); xv[i][3] = __uint_as_float(t.y & 0xFFFF0000u);
+        }
+      }
+    }
+    if (!G.transpose) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = tr + ly + 16 * i, c = tcx + lx;
+        if (r < G.R && c < G.C)
+          *reinterpret_cast<uint2*>(xo + static_cast<int64_t>(r) * G.C + c) =
+              make_uint2(pack_bf16x2(bf16_round(xv[i][0]) / den, bf16_round(xv[i][1]) / den),
+                         pack_bf16x2(bf16_round(xv[i][2]) / den, bf16_round(xv[i][3]) / den));
+      }
+      return;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) tile[ly + 16 * i][lx + j] = bf16_round(xv[i][j]) / den;
+    __syncthreads();
+    // output row = source column; a thread writes eight consecutive source rows of one column
+    const int chunk = threadIdx.x & 7;
+#pragma unroll
+    for (int pass = 0; pass < 2; ++pass) {
+      const int cc = (threadIdx.x >> 3) + 32 * pass;
+      const int c = tcx + cc, r = tr + chunk * 8;
+      if (c < G.C && r < G.R) {  // R is a multiple of 8: the eight rows are all valid
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) w[j] = pack_bf16x2(tile[chunk * 8 + 2 * j][cc], tile[chunk * 8 + 2 * j + 1][cc]);
+        *reinterpret_cast<uint4*>(xo + static_cast<int64_t>(c) * G.R + r) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    }
+    return;
+  }
   const int lx = threadIdx.x & 63, ly = threadIdx.x >> 6;  // 64 x 4
   float xv[16];
 #pragma unroll
@@ -569,7 +622,6 @@ __global__ void __launch_bounds__(256) ns_scale_kernel(const NsPrepArgs args) {
 #pragma unroll
   for (int i = 0; i < 16; ++i) tile[ly + 4 * i][lx] = bf16_round(xv[i]) / den;
   __syncthreads();
-  bf16* xo = G.x0 + base;
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
     const int rr = ly + 4 * i;

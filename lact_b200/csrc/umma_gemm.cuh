@@ -120,6 +120,12 @@ struct GemmCtx {
   uint32_t res_count = 0;  // residual tiles consumed so far (epilogue threads)
   uint32_t tmem_base;
   uint32_t it = 0, tcount = 0;
+  // dataflow mode (multi-phase kernels whose phases are ordered by completion counters, see FlowDeps)
+  uint32_t rot = 0;              // tiles handed out by earlier phases, modulo the grid size
+  uint32_t ptile = 0;            // tiles whose dependency the producer thread has verified
+  uint32_t* pend = nullptr;      // completion counter of the last stored, not yet signalled tile (storing thread)
+  bool res_deferred = false;     // the current tile's residual could not be prefetched (storing thread)
+  uint32_t* dep_ok = nullptr;    // shared-memory word: the producer's `ptile`, read by the storing thread
   // optional diagnostics (CTA 0 only): per phase < 6 and tile < 4, globaltimer stamps of
   // {loads issued, MMAs committed, epilogue started, epilogue finished} at trace[40 + 16*phase + 4*tile + k]
   uint64_t* trace = nullptr;
@@ -134,6 +140,65 @@ struct NoPatch {
   __device__ __forceinline__ void operator()(Epi&, int) const {}
 };
 
+// Phase ordering of a multi-phase kernel without grid-wide barriers.  Every (problem, batch entry)
+// owns a completion counter in global memory; a tile's stores are followed (once they have landed)
+// by one increment of its batch entry's counter, and a tile of a later phase may load only after the
+// counter of its batch entry has reached `need` = the number of tiles all earlier phases produce for
+// that entry.  The phases of a batch entry must form a chain (each phase reads only what earlier
+// phases of the same entry wrote, and overwrites only what earlier phases of the same entry read).
+// All CTAs walk the phases in the same order and must be co-resident; every wait is bounded.
+struct NoDeps {
+  static constexpr bool kOn = false;
+};
+struct FlowDeps {
+  static constexpr bool kOn = true;
+  uint32_t* counter[2];  // per problem: [batch] counters
+  uint32_t need[2];      // per problem: value required before a tile of this phase loads
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_acquire_cta_shared_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(p)) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_cta_shared_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_u32(p)), "r"(v) : "memory");
+}
+// Bounded spin until *ctr >= need (global memory, written by other CTAs).
+__device__ __forceinline__ bool dep_wait(const uint32_t* ctr, uint32_t need, volatile uint32_t* abort_flag) {
+  if (need == 0 || ld_acquire_gpu_u32(ctr) >= need) return true;
+  const uint64_t t0 = globaltimer_ns();
+  for (uint32_t i = 1;; ++i) {
+    if (ld_acquire_gpu_u32(ctr) >= need) return true;
+    if ((i & 31u) == 0 && (*abort_flag != 0 || globaltimer_ns() - t0 > kWaitLimitNs)) return false;
+  }
+}
+// Storing thread: once the stores of the last tile have landed, publish its completion.
+__device__ __forceinline__ void flow_flush(GemmCtx& cx) {
+  if (cx.pend != nullptr) {
+    bulk_wait_all();
+    asm volatile("fence.proxy.async;" ::: "memory");
+    __threadfence();
+    atomicAdd(cx.pend, 1u);
+    cx.pend = nullptr;
+  }
+}
+// Storing thread: bounded wait until the producer thread has verified the dependency of the tile
+// with running number `seq` (0-based).
+__device__ __forceinline__ bool flow_wait_verified(const GemmCtx& cx, uint32_t seq) {
+  if (ld_acquire_cta_shared_u32(cx.dep_ok) > seq) return true;
+  const uint64_t t0 = globaltimer_ns();
+  for (uint32_t i = 1;; ++i) {
+    if (ld_acquire_cta_shared_u32(cx.dep_ok) > seq) return true;
+    if ((i & 63u) == 0 && (*cx.abort_flag != 0 || globaltimer_ns() - t0 > kWaitLimitNs)) return false;
+  }
+}
+
 // Round r of the persistent loop hands CTA c tile r*G + c in even rounds and r*G + (G-1-c) in odd
 // rounds ("snake"): with the problems listed heaviest first, a CTA that drew an expensive tile in
 // one round draws a cheap one (or none) in the next.
@@ -145,9 +210,11 @@ __device__ __forceinline__ int snake_tile(int round, int grid, int cta) {
 // `nprob` problems.  Tiles of one batch entry are consecutive (n fastest), so CTAs that run at
 // the same time share operand tiles in L2.  Warp 0 = TMA producer, warp 1 = MMA issuer, warps
 // 2.. = epilogue.  Returns true if a bounded wait ran out.  No CTA-wide sync inside.
-template <class Op, int RING, class EpiPatch>
+// With Deps = FlowDeps tiles are dealt round-robin continuing from the previous phase (no snake) and
+// ordered by the completion counters described above.
+template <class Op, int RING, class EpiPatch, class Deps = NoDeps>
 __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* probs, const int nprob,
-                                           EpiPatch patch) {
+                                           EpiPatch patch, Deps deps = Deps{}) {
   constexpr int BT = Op::BT, NA = Op::NA, NB = Op::NB, NACC = Op::NACC;
   constexpr uint32_t kBTileBytes = BT * kBK * 2;
   constexpr uint32_t kStageBytes = gemm_stage_bytes<Op>();
@@ -182,18 +249,30 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
     return c;
   };
 
+  const int rounds = (total_tiles + gridDim.x - 1) / gridDim.x;
+  const uint32_t rot0 = cx.rot;
+  auto tile_at = [&](int r) {
+    if constexpr (Deps::kOn) return r * static_cast<int>(gridDim.x) + static_cast<int>((blockIdx.x + gridDim.x - rot0) % gridDim.x);
+    else return snake_tile(r, gridDim.x, blockIdx.x);
+  };
+  if constexpr (Deps::kOn) cx.rot = (cx.rot + static_cast<uint32_t>(total_tiles)) % gridDim.x;
+
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   bool failed = false;
   if (warp == 0) {
     // ---------------- TMA producer (one thread); the ring keeps running across tiles
     if (lane == 0) {
-      const int rounds = (total_tiles + gridDim.x - 1) / gridDim.x;
       for (int tile_i = 0; tile_i < rounds && !failed; ++tile_i) {
-        const int tile = snake_tile(tile_i, gridDim.x, blockIdx.x);
+        const int tile = tile_at(tile_i);
         if (tile >= total_tiles) continue;
         const TileCoord tc = coord(tile);
         const GemmProblem<Op>& P = probs[tc.prob];
         const int num_kb = (P.K + kBK - 1) / kBK;
+        if constexpr (Deps::kOn) {
+          if (!dep_wait(deps.counter[tc.prob] + tc.batch, deps.need[tc.prob], cx.abort_flag)) { failed = true; break; }
+          asm volatile("fence.proxy.async;" ::: "memory");
+          st_release_cta_shared_u32(cx.dep_ok, ++cx.ptile);
+        }
         for (int kb = 0; kb < num_kb; ++kb, ++cx.it) {
           const int s = cx.it % RING;
           const uint32_t ph = (cx.it / RING) & 1;
@@ -215,9 +294,8 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
   } else if (warp == 1) {
     // ---------------- MMA issuer (one thread)
     if (lane == 0) {
-      const int rounds = (total_tiles + gridDim.x - 1) / gridDim.x;
       for (int tile_i = 0; tile_i < rounds && !failed; ++tile_i) {
-        const int tile = snake_tile(tile_i, gridDim.x, blockIdx.x);
+        const int tile = tile_at(tile_i);
         if (tile >= total_tiles) continue;
         const TileCoord tc = coord(tile);
         const GemmProblem<Op>& P = probs[tc.prob];
@@ -269,10 +347,9 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
     constexpr bool kDoubleStg = Op::kStagingBuffers == 2;
     // staging buffer of the tile with running count `tc_` (alternating when double-buffered)
     auto stg_of = [&](uint32_t tc_) { return cx.staging + (kDoubleStg ? (tc_ & 1u) * kStgBytes : 0u); };
-    const int rounds = (total_tiles + gridDim.x - 1) / gridDim.x;
     auto tile_of_round = [&](int r) {
       if (r >= rounds) return -1;
-      const int t = snake_tile(r, gridDim.x, blockIdx.x);
+      const int t = tile_at(r);
       return t < total_tiles ? t : -1;
     };
     // Residual tile of `tile` -> the staging buffer `dst` (elected thread).  Every TMA store that
@@ -292,9 +369,27 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
                       P2.oi[0].row_off + t2.m0, P2.oi[0].batch_off + t2.batch);
       }
     };
+    if constexpr (Deps::kOn) {
+      // a CTA without a tile in this phase must not sit on an unpublished tile of the previous one
+      if (elected && tile_of_round(0) < 0) flow_flush(cx);
+    }
     if (elected && Op::kResidualTma) {
       bulk_wait_read_all();
-      issue_residual(tile_of_round(0), stg_of(cx.tcount));
+      if constexpr (Deps::kOn) {
+        // the first tile's residual is written by an earlier phase: issue it once the producer
+        // thread has verified that tile's dependency (never block with an unpublished tile)
+        if (tile_of_round(0) >= 0 && probs[coord(tile_of_round(0)).prob].res_enabled) {
+          if (ld_acquire_cta_shared_u32(cx.dep_ok) <= cx.tcount) flow_flush(cx);
+          if (flow_wait_verified(cx, cx.tcount)) {
+            asm volatile("fence.proxy.async;" ::: "memory");
+            issue_residual(tile_of_round(0), stg_of(cx.tcount));
+          } else {
+            *cx.abort_flag = 1;
+          }
+        }
+      } else {
+        issue_residual(tile_of_round(0), stg_of(cx.tcount));
+      }
     }
     for (int tile_i = 0; tile_i < rounds; ++tile_i) {
       const int tile = tile_of_round(tile_i);
@@ -311,6 +406,22 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
       // global operands of the epilogue are fetched while the tile's MMAs are still running
       typename Op::Prefetch pf;
       Op::prefetch(ep, tc.batch, row, tc.n0, half, P.M, P.N, pf);
+      if constexpr (Deps::kOn) {
+        if (elected) {
+          // idle anyway: publish the previous tile now, so that no CTA (this one included) waits for it
+          if (!mbar_try_wait(&cx.acc_full_bar[as], aph)) flow_flush(cx);
+          if (cx.res_deferred) {
+            flow_flush(cx);
+            if (flow_wait_verified(cx, cx.tcount)) {
+              asm volatile("fence.proxy.async;" ::: "memory");
+              issue_residual(tile, stg);
+            } else {
+              *cx.abort_flag = 1;
+            }
+            cx.res_deferred = false;
+          }
+        }
+      }
       bool got = mbar_wait(&cx.acc_full_bar[as], aph, cx.abort_flag);
       tc_fence_after();
       if (has_res) {
@@ -323,11 +434,27 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
         // A warp whose wait ran out must not leave the others stuck at a named barrier: it raises
         // a flag that only epilogue warps write, and every warp decides after the barrier.
         if (!got) cx.abort_flag[1] = 1;
-        // the previous tile's stores must have finished reading the staging tiles
+        // stores that read this tile's staging buffer must have finished reading it: with two
+        // buffers that is every group but the last one committed (the previous tile's final store)
         if (elected) {
-          bulk_wait_read_all();
+          if (kDoubleStg && !Op::kResidualTma) bulk_wait_read_but_last();
+          else bulk_wait_read_all();
           // double-buffered: the other buffer is free now, fetch the next tile's residual into it
-          if (kDoubleStg && got) issue_residual(tile_of_round(tile_i + 1), stg_of(cx.tcount + 1));
+          if (kDoubleStg && got) {
+            if constexpr (Deps::kOn) {
+              const int nxt = tile_of_round(tile_i + 1);
+              if (nxt >= 0 && probs[coord(nxt).prob].res_enabled) {
+                if (ld_acquire_cta_shared_u32(cx.dep_ok) > cx.tcount + 1) {
+                  asm volatile("fence.proxy.async;" ::: "memory");
+                  issue_residual(nxt, stg_of(cx.tcount + 1));
+                } else {
+                  cx.res_deferred = true;  // fetched at the start of that tile
+                }
+              }
+            } else {
+              issue_residual(tile_of_round(tile_i + 1), stg_of(cx.tcount + 1));
+            }
+          }
         }
         named_barrier_sync(1, kEpiThreads);
         if (cx.abort_flag[1] != 0) { failed = true; break; }
@@ -396,6 +523,7 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
         fence_async_proxy();
         named_barrier_sync(2, kEpiThreads);
         if (elected) {
+          if constexpr (Deps::kOn) flow_flush(cx);  // the previous tile's stores landed long ago
 #pragma unroll
           for (int o = 0; o < NOUT; ++o) {
             if (!P.oi[o].enabled || (o == 1 && Op::kSecondInPlace) || Op::skip_store(ep, o)) continue;
@@ -426,9 +554,11 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
                              : "r"(addr)
                              : "memory");
 #pragma unroll
-                for (int i = 0; i < 4; ++i)
-                  w[i] = pack_bf16x2(Op::second(ep, __uint_as_float(w[i] << 16)),
-                                     Op::second(ep, __uint_as_float(w[i] & 0xFFFF0000u)));
+                for (int i = 0; i < 4; ++i) {
+                  const int col = tc.n0 + c + g * 8 + 2 * i;
+                  w[i] = pack_bf16x2(Op::second(ep, __uint_as_float(w[i] << 16), row, col),
+                                     Op::second(ep, __uint_as_float(w[i] & 0xFFFF0000u), row, col + 1));
+                }
                 asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]),
                              "r"(w[3])
                              : "memory");
@@ -447,13 +577,17 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
           }
         }
         if (!kDoubleStg && elected && Op::kResidualTma) {
+          static_assert(!Deps::kOn || kDoubleStg || !Op::kResidualTma, "dataflow mode needs double-buffered staging for residual tiles");
           bulk_wait_read_all();
           issue_residual(tile_of_round(tile_i + 1), stg);
+        }
+        if constexpr (Deps::kOn) {
+          if (elected) cx.pend = deps.counter[tc.prob] + tc.batch;  // published by a later flow_flush
         }
       }
       ++cx.tcount;
     }
-    if constexpr (NOUT > 0) {
+    if constexpr (NOUT > 0 && !Deps::kOn) {
       if (elected) bulk_wait_all();  // this CTA's output tiles are in global memory
       if (elected) cx.stamp(3, 3);
     }
@@ -476,7 +610,8 @@ __device__ __forceinline__ void gemm_setup(GemmCtx& cx, uint8_t* smem_raw, int r
   cx.acc_empty_bar = cx.acc_full_bar + 2;   // [2]
   cx.res_bar = cx.acc_empty_bar + 2;        // [1]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(cx.res_bar + 1);
-  cx.abort_flag = tmem_slot + 1;
+  cx.abort_flag = tmem_slot + 1;  // [2]
+  cx.dep_ok = tmem_slot + 3;
   if (threadIdx.x == 0) {
     for (int s = 0; s < ring; ++s) {
       mbar_init(&cx.full_bar[s], 1);
@@ -489,6 +624,7 @@ __device__ __forceinline__ void gemm_setup(GemmCtx& cx, uint8_t* smem_raw, int r
     mbar_init(cx.res_bar, 1);
     cx.abort_flag[0] = 0;
     cx.abort_flag[1] = 0;
+    *cx.dep_ok = 0;
     fence_mbar_init();
   }
   if ((threadIdx.x >> 5) == 1) {

@@ -77,6 +77,33 @@ def newton_schulz(G: torch.Tensor, steps: Optional[int] = None) -> torch.Tensor:
     return X
 
 
+def newton_schulz_folded(G: torch.Tensor, steps: Optional[int] = None) -> torch.Tensor:
+    """Rounding model of the CUDA kernels' Newton-Schulz: the same iteration with the residual
+    terms folded into the contractions as multiples of the identity,
+    ``b A + (c A) A = (c A + b I) A`` and ``a X + P X = (P + a I) X``; bf16 values, fp32
+    accumulation, one rounding per stored matrix.  The reference's compiled GPU graph likewise
+    rounds ``b*A + c*A@A`` and ``a*X + B@X`` once (inductor fuses the elementwise part), so its own
+    GPU and eager CPU results differ by the same kind of amount as this model and `newton_schulz`.
+    """
+    assert G.dim() == 3
+    coeffs = NS_TUNED5 if steps is None else (NS_CONST,) * steps
+    X = G.bfloat16()
+    flip = G.size(1) > G.size(2)
+    if flip:
+        X = X.transpose(1, 2)
+    X = X / (X.norm(dim=(1, 2), keepdim=True) + 1e-7)
+    eye = torch.eye(X.size(1), dtype=torch.float32)
+    for a, b, c in coeffs:
+        Xf = X.float()
+        A = (Xf @ Xf.transpose(1, 2)).to(BF16)
+        CA = (c * A.float() + b * eye).to(BF16)
+        P = (CA.float() @ A.float() + a * eye).to(BF16)
+        X = (P.float() @ Xf).to(BF16)
+    if flip:
+        X = X.transpose(1, 2)
+    return X
+
+
 def newton_schulz_f64(G: torch.Tensor, steps: Optional[int] = None) -> torch.Tensor:
     """The same iteration carried out in float64 on the bf16-rounded input (accuracy yardstick)."""
     coeffs = NS_TUNED5 if steps is None else (NS_CONST,) * steps
@@ -280,9 +307,11 @@ def block_causal_lact_swiglu(
 def block_causal_lact_swiglu_fused(
     w0, w1, w2, q, k, v, lr0, lr1, lr2, chunk_size=2048, use_muon=False, momentum=None,
     *, prenorm=False, trace: Optional[list] = None, states: Optional[list] = None,
-    teacher: Optional[Sequence[Tuple[torch.Tensor, torch.Tensor]]] = None,
+    teacher: Optional[Sequence[Tuple[torch.Tensor, torch.Tensor]]] = None, ns=None,
 ):
     """Causal apply-then-update recurrence with the fused path's semantics and rounding.
+    ``ns``: the Newton-Schulz function (default `newton_schulz`, the reference's eager rounding;
+    `newton_schulz_folded` gives the CUDA kernels' rounding).
 
     Post-norm: lact_llm/lact_model/ttt_operation_fused_kernel.py:66-186; pre-norm: :189-316.
     Differences from the unfused functions that are reproduced here: zero padding to a chunk
@@ -321,8 +350,8 @@ def block_causal_lact_swiglu_fused(
             dw1 = dw1 + m1 * beta
             m02, m1 = dw02, dw1
         if use_muon:
-            dw1 = newton_schulz(dw1)
-            dw02 = newton_schulz(dw02)
+            dw1 = (ns or newton_schulz)(dw1)
+            dw02 = (ns or newton_schulz)(dw02)
         if prenorm:
             w0w2_main = w0w2_main + dw02
             w1_main = w1_main + dw1
@@ -521,8 +550,8 @@ class ScanConfig:
 def _ns_model(G, cfg: ScanConfig):
     steps = cfg.ns_steps if cfg.ns_const_coeffs else None
     if cfg.ns_gram_right and G.size(1) == G.size(2):
-        return newton_schulz(G.transpose(1, 2), steps).transpose(1, 2)
-    return newton_schulz(G, steps)
+        return newton_schulz_folded(G.transpose(1, 2), steps).transpose(1, 2)
+    return newton_schulz_folded(G, steps)
 
 
 def scan_model(w0, w1, w2, q, k, v, lr0, lr1, lr2, steps: Sequence[Tuple[str, int, int, int]], cfg: ScanConfig,
