@@ -185,6 +185,9 @@ cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
 }
 
 int sm_count() {
+#ifdef LACT_SM_LIMIT
+  return LACT_SM_LIMIT;  // experiments only: run the persistent grids on fewer SMs
+#endif
   static int cached[64] = {0};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
@@ -341,6 +344,8 @@ struct GradArgs {
   int64_t B, D, H;
   float* partial02 = nullptr;  // optional per-tile sums of squares of the two outputs
   float* partial1 = nullptr;
+  bf16* gb02 = nullptr;        // optional bf16 copies of the two outputs (Newton-Schulz input)
+  bf16* gb1 = nullptr;
 };
 
 inline int contract_bt(int64_t D, int64_t H) { return choose_bt({{D, 2 * H}, {H, D}}); }
@@ -386,13 +391,14 @@ int run_grad(const GradArgs& a, int32_t* status, cudaStream_t stream) {
     P0.M = static_cast<int>(2 * a.H); P0.N = static_cast<int>(a.D); P0.K = static_cast<int>(len);
     P0.batch = static_cast<int>(a.B);
     P0.ep = EpiDW{a.g02, 2 * a.H * a.D, a.D, a.beta, 1, a.g_f32, a.partial02, ceil_div(2 * a.H, kBM),
-                  ceil_div(a.D, btv)};
+                  ceil_div(a.D, btv), a.gb02};
     auto& P1 = g.prob[1];
     LACT_TRY(make_operand(&P1.a[0], &P1.ai[0], vm, 1, kBM, 0, static_cast<int>(a.start)));
     LACT_TRY(make_operand(&P1.b[0], &P1.bi[0], hid, 1, btv, 0, 0));
     P1.M = static_cast<int>(a.D); P1.N = static_cast<int>(a.H); P1.K = static_cast<int>(len);
     P1.batch = static_cast<int>(a.B);
-    P1.ep = EpiDW{a.g1, a.D * a.H, a.H, a.beta, 1, a.g_f32, a.partial1, ceil_div(a.D, kBM), ceil_div(a.H, btv)};
+    P1.ep = EpiDW{a.g1, a.D * a.H, a.H, a.beta, 1, a.g_f32, a.partial1, ceil_div(a.D, kBM), ceil_div(a.H, btv),
+                  a.gb1};
     g.status = status;
     return LACT_OK;
   };
@@ -409,19 +415,23 @@ const float kNsConst[3] = {3.4445f, -4.7750f, 2.0315f};
 
 constexpr int kNsMaxParts = 512;
 
-// One group of equally shaped gradient matrices [R][C] under iteration.  The iteration runs on
-// X = [m][n] with m <= n: X = G^T when `transposed`.  The result is always delivered in the
-// gradient's own [R][C] orientation.
+// One group of equally shaped gradient matrices [R][C] under iteration.  The iterate X keeps the
+// gradient's own [R][C] layout.  With m = min(R, C), n = max(R, C) the Gram matrix is m x m:
+//   wide (R <= C):               A = X X^T   (operands K-major),       X' = P X    (X read MN-major)
+//   tall (R > C, `transposed`):  A = X^T X   (operands MN-major),      X' = X P^T  (P's rows as K-major B operand)
+// which is the reference's "transpose, iterate, transpose back" without moving data.
 struct NsGroup {
   int32_t nmat, R, C, m, n, transposed;
-  bf16 *xa, *xb;              // ping-pong iterates, nmat * m * n each
+  bf16 *xa, *xb;              // ping-pong iterates, nmat * R * C each
   bf16 *gram, *cgram, *poly;  // [nmat][m][m]
   float* partial;             // [nmat][<= kNsMaxParts] partial sums of squares
+  float* scale;               // [nmat] 1 / (||G||_F + 1e-7) when the first iterate is the unscaled bf16(G)
   uint32_t* done;             // [nmat] tile completion counters of the fused kernel
 };
 
 inline size_t ns_group_bytes(int64_t nmat, int64_t m, int64_t n) {
-  return static_cast<size_t>(nmat) * (2 * m * n + 3 * m * m) * 2 + static_cast<size_t>(nmat) * kNsMaxParts * 4 + static_cast<size_t>(nmat) * 4 + 7 * 256;
+  return static_cast<size_t>(nmat) * (2 * m * n + 3 * m * m) * 2 + static_cast<size_t>(nmat) * kNsMaxParts * 4 +
+         static_cast<size_t>(nmat) * 8 + 8 * 256;
 }
 
 void ns_group_init(NsGroup& g, int64_t nmat, int64_t R, int64_t C, int gram_right) {
@@ -433,13 +443,17 @@ void ns_group_init(NsGroup& g, int64_t nmat, int64_t R, int64_t C, int gram_righ
   g.transposed = (R > C) || (R == C && gram_right);
 }
 
-// Frobenius normalisation of the gradient matrices of one or two groups (src[g]: [nmat][R][C],
-// contiguous) into each group's first iterate.  With steps == 0 the normalised matrix is the
-// result and is written untransposed.
-int launch_ns_prepare(const NsGroup* grp, int ngroups, const void* const* src, int src_f32, int steps,
+// columns of the update product's output: X' is [R][C] = [m][n] (wide) or [n][m] (tall)
+inline int ns_upd_cols(const NsGroup& g) { return g.transposed ? g.m : g.n; }
+inline int ns_upd_rows(const NsGroup& g) { return g.transposed ? g.n : g.m; }
+
+// Start of the iteration for one or two groups (src[g]: [nmat][R][C], contiguous).
+//   scaled = 1: the first iterate X0 = bf16(bf16(G) / (||G|| + 1e-7)) is written to grp[g].xa
+//               (norm partials from `fused_parts`, or computed here);
+//   scaled = 0: the first iterate is bf16(G), already in grp[g].xa with `fused_parts` partial sums
+//               per matrix; only the scale factors 1 / (||G|| + 1e-7) are computed.
+int launch_ns_prepare(const NsGroup* grp, int ngroups, const void* const* src, int src_f32, int scaled,
                       cudaStream_t stream, const int* fused_parts = nullptr) {
-  // fused_parts[g] > 0: the partial sums of group g were already written (that many per matrix) by
-  // the kernel that produced the gradient; otherwise they are computed here, kNsSlabs per matrix
   NsPrepArgs pa;
   std::memset(&pa, 0, sizeof(pa));
   pa.ngroups = ngroups;
@@ -449,8 +463,7 @@ int launch_ns_prepare(const NsGroup* grp, int ngroups, const void* const* src, i
     const NsGroup& G = grp[g];
     const int parts = (fused_parts != nullptr && fused_parts[g] > 0) ? fused_parts[g] : kNsSlabs;
     if (fused_parts == nullptr || fused_parts[g] <= 0) need_sumsq = true;
-    pa.grp[g] = NsPrepGroup{src[g], src_f32, G.nmat, G.R, G.C, (G.transposed && steps > 0) ? 1 : 0, G.xa, G.partial,
-                            parts};
+    pa.grp[g] = NsPrepGroup{src[g], src_f32, G.nmat, G.R, G.C, 0, G.xa, G.partial, parts, G.scale};
     nmat += G.nmat;
     tiles = std::max(tiles, ceil_div(G.R, 64) * ceil_div(G.C, 64));
   }
@@ -460,82 +473,88 @@ int launch_ns_prepare(const NsGroup* grp, int ngroups, const void* const* src, i
     LACT_CUDA(launch_pdl(ns_sumsq_kernel, dim3(nmat, kNsSlabs), dim3(256), 0, stream, pa));
   }
   KernelScope scope(kClsNsPrepare, stream);
-  LACT_CUDA(launch_pdl(ns_scale_kernel, dim3(nmat, tiles), dim3(256), 0, stream, pa));
+  if (scaled) LACT_CUDA(launch_pdl(ns_scale_kernel, dim3(nmat, tiles), dim3(256), 0, stream, pa));
+  else LACT_CUDA(launch_pdl(ns_den_kernel, dim3(ceil_div(nmat, 4)), dim3(128), 0, stream, pa));
   return LACT_OK;
 }
 
-// Runs `steps` iterations on one or two groups (every GEMM launch covers all groups).
-// result[g] = buffer holding the final iterate of group g, in [R][C] orientation.
+// Fills the three contractions of one iteration of group G, reading the iterate `cur` and writing
+// `nxt` (both [nmat][R][C]).  PG / PP / PU: GemmProblem<OpNs<..>> of the gram, poly and update phase.
+template <class PG, class PP, class PU>
+int wire_ns_group(const NsGroup& G, bf16* cur, bf16* nxt, int bt_mm, int bt_mn, PG& gram, PP& poly, PU& upd) {
+  const int64_t mm = static_cast<int64_t>(G.m) * G.m, rc = static_cast<int64_t>(G.R) * G.C;
+  const Mat X{cur, G.R, G.C, G.C, G.nmat, rc};
+  const Mat XN{nxt, G.R, G.C, G.C, G.nmat, rc};
+  const Mat A{G.gram, G.m, G.m, G.m, G.nmat, mm};
+  const Mat CA{G.cgram, G.m, G.m, G.m, G.nmat, mm};
+  const Mat PB{G.poly, G.m, G.m, G.m, G.nmat, mm};
+  const int tall = G.transposed;
+  // gram = X X^T (wide) / X^T X (tall); second output c * gram + b I
+  LACT_TRY(make_operand(&gram.a[0], &gram.ai[0], X, tall, kBM, 0, 0));
+  LACT_TRY(make_operand(&gram.b[0], &gram.bi[0], X, tall, bt_mm, 0, 0));
+  gram.M = G.m; gram.N = G.m; gram.K = G.n; gram.batch = G.nmat;
+  LACT_TRY(make_output(&gram.out[0], &gram.oi[0], A, 0, 0));
+  LACT_TRY(make_output(&gram.out[1], &gram.oi[1], CA, 0, 0));
+  // poly = (c gram + b I) gram + a I   (gram is exactly symmetric: its rows serve as the K-major B operand)
+  LACT_TRY(make_operand(&poly.a[0], &poly.ai[0], CA, 0, kBM, 0, 0));
+  LACT_TRY(make_operand(&poly.b[0], &poly.bi[0], A, 0, bt_mm, 0, 0));
+  poly.M = G.m; poly.N = G.m; poly.K = G.m; poly.batch = G.nmat;
+  LACT_TRY(make_output(&poly.out[0], &poly.oi[0], PB, 0, 0));
+  // update: X' = poly X (wide; X is [k][n]: MN-major B operand) / X' = X poly^T (tall)
+  if (!tall) {
+    LACT_TRY(make_operand(&upd.a[0], &upd.ai[0], PB, 0, kBM, 0, 0));
+    LACT_TRY(make_operand(&upd.b[0], &upd.bi[0], X, 1, bt_mn, 0, 0));
+  } else {
+    LACT_TRY(make_operand(&upd.a[0], &upd.ai[0], X, 0, kBM, 0, 0));
+    LACT_TRY(make_operand(&upd.b[0], &upd.bi[0], PB, 0, bt_mn, 0, 0));
+  }
+  upd.M = ns_upd_rows(G); upd.N = ns_upd_cols(G); upd.K = G.m; upd.batch = G.nmat;
+  LACT_TRY(make_output(&upd.out[0], &upd.oi[0], XN, 0, 0));
+  return LACT_OK;
+}
+
+inline void ns_tile_widths(const NsGroup* grp, int ngroups, int* bt_mm, int* bt_mn) {
+  const NsGroup& G0 = grp[0];
+  const NsGroup& G1 = grp[ngroups - 1];
+  *bt_mm = choose_bt({{G0.m, static_cast<int64_t>(G0.nmat) * G0.m}, {G1.m, static_cast<int64_t>(G1.nmat) * G1.m}});
+  *bt_mn = choose_bt({{ns_upd_cols(G0), static_cast<int64_t>(G0.nmat) * ns_upd_rows(G0)},
+                      {ns_upd_cols(G1), static_cast<int64_t>(G1.nmat) * ns_upd_rows(G1)}});
+}
+
+// Runs `steps` iterations on one or two groups, one launch per contraction (every launch covers
+// all groups).  The first iterate is grp[g].xa (scaled unless `unscaled_first`, in which case the
+// scale factors grp[g].scale are folded into the first iteration).
+// result[g] = buffer holding the final iterate of group g.
 int run_ns_iterations(const NsGroup* grp, int ngroups, int steps, int const_coeffs, const bf16** result,
-                      int32_t* status, cudaStream_t stream) {
+                      int32_t* status, cudaStream_t stream, int unscaled_first = 0) {
   if (ngroups < 1 || ngroups > 2) return LACT_ERR_CONFIG;
   if (!const_coeffs && steps != 5) return LACT_ERR_CONFIG;
   bf16* cur[2];
   bf16* nxt[2];
   for (int g = 0; g < ngroups; ++g) { cur[g] = grp[g].xa; nxt[g] = grp[g].xb; }
-  const NsGroup& G0 = grp[0];
-  const NsGroup& G1 = grp[ngroups - 1];
-  const int bt_mm = choose_bt({{G0.m, static_cast<int64_t>(G0.nmat) * G0.m}, {G1.m, static_cast<int64_t>(G1.nmat) * G1.m}});
-  const int bt_mn = choose_bt({{G0.n, static_cast<int64_t>(G0.nmat) * G0.m}, {G1.n, static_cast<int64_t>(G1.nmat) * G1.m}});
+  int bt_mm = 0, bt_mn = 0;
+  ns_tile_widths(grp, ngroups, &bt_mm, &bt_mn);
   for (int it = 0; it < steps; ++it) {
     const float* co = const_coeffs ? kNsConst : kNsTuned[it];
-    const bool last = (it == steps - 1);
-    // gram = X X^T ; cgram = c * gram + b I
-    auto fill_gram = [&](auto& ga, int btv) -> int {
+    const int fold = (it == 0 && unscaled_first) ? 1 : 0;
+    // which = 0 gram, 1 poly, 2 update: every fill wires all three and keeps the one it launches
+    auto fill = [&](auto& ga, int btv, int which) -> int {
+      using Prob = std::remove_reference_t<decltype(ga.prob[0])>;
       for (int g = 0; g < ngroups; ++g) {
-        const NsGroup& G = grp[g];
-        const Mat X{cur[g], G.m, G.n, G.n, G.nmat, static_cast<int64_t>(G.m) * G.n};
-        auto& P = ga.prob[g];
-        LACT_TRY(make_operand(&P.a[0], &P.ai[0], X, 0, kBM, 0, 0));
-        LACT_TRY(make_operand(&P.b[0], &P.bi[0], X, 0, btv, 0, 0));
-        P.M = G.m; P.N = G.m; P.K = G.n; P.batch = G.nmat;
-        const Mat A{G.gram, G.m, G.m, G.m, G.nmat, static_cast<int64_t>(G.m) * G.m};
-        const Mat CA{G.cgram, G.m, G.m, G.m, G.nmat, static_cast<int64_t>(G.m) * G.m};
-        LACT_TRY(make_output(&P.out[0], &P.oi[0], A, 0, 0));
-        LACT_TRY(make_output(&P.out[1], &P.oi[1], CA, 0, 0));
-        P.ep = EpiNs{nullptr, 0.f, co[2], co[1], static_cast<int64_t>(G.m) * G.m, G.m, 0, 0};
+        Prob pg, pp, pu;
+        std::memset(&pg, 0, sizeof(Prob)); std::memset(&pp, 0, sizeof(Prob)); std::memset(&pu, 0, sizeof(Prob));
+        LACT_TRY(wire_ns_group(grp[g], cur[g], nxt[g], btv, btv, pg, pp, pu));
+        const float* sc = fold ? grp[g].scale : nullptr;
+        if (which == 0) { ga.prob[g] = pg; ga.prob[g].ep = EpiNs{0.f, co[2], co[1], sc, fold ? 2 : 0}; }
+        if (which == 1) { ga.prob[g] = pp; ga.prob[g].ep = EpiNs{co[0], 0.f, 0.f, nullptr, 0}; }
+        if (which == 2) { ga.prob[g] = pu; ga.prob[g].ep = EpiNs{0.f, 0.f, 0.f, sc, fold ? 1 : 0}; }
       }
       ga.status = status;
       return LACT_OK;
     };
-    // poly = cgram gram + a I   (gram is symmetric: its rows serve as the K-major B operand)
-    auto fill_poly = [&](auto& gb, int btv) -> int {
-      for (int g = 0; g < ngroups; ++g) {
-        const NsGroup& G = grp[g];
-        const Mat A{G.gram, G.m, G.m, G.m, G.nmat, static_cast<int64_t>(G.m) * G.m};
-        const Mat CA{G.cgram, G.m, G.m, G.m, G.nmat, static_cast<int64_t>(G.m) * G.m};
-        auto& P = gb.prob[g];
-        LACT_TRY(make_operand(&P.a[0], &P.ai[0], CA, 0, kBM, 0, 0));
-        LACT_TRY(make_operand(&P.b[0], &P.bi[0], A, 0, btv, 0, 0));
-        P.M = G.m; P.N = G.m; P.K = G.m; P.batch = G.nmat;
-        const Mat PBm{G.poly, G.m, G.m, G.m, G.nmat, static_cast<int64_t>(G.m) * G.m};
-        LACT_TRY(make_output(&P.out[0], &P.oi[0], PBm, 0, 0));
-        P.ep = EpiNs{nullptr, co[0], 0.f, 0.f, static_cast<int64_t>(G.m) * G.m, G.m, 0, 0};
-      }
-      gb.status = status;
-      return LACT_OK;
-    };
-    // X' = poly X   (X is [m][n]: k rows, n contiguous -> MN-major B operand); the last
-    // iterate of a transposed group is written back in the gradient's orientation
-    auto fill_upd = [&](auto& gc, int btv) -> int {
-      for (int g = 0; g < ngroups; ++g) {
-        const NsGroup& G = grp[g];
-        const Mat X{cur[g], G.m, G.n, G.n, G.nmat, static_cast<int64_t>(G.m) * G.n};
-        const Mat PB{G.poly, G.m, G.m, G.m, G.nmat, static_cast<int64_t>(G.m) * G.m};
-        auto& P = gc.prob[g];
-        LACT_TRY(make_operand(&P.a[0], &P.ai[0], PB, 0, kBM, 0, 0));
-        LACT_TRY(make_operand(&P.b[0], &P.bi[0], X, 1, btv, 0, 0));
-        P.M = G.m; P.N = G.n; P.K = G.m; P.batch = G.nmat;
-        const Mat XN{nxt[g], G.m, G.n, G.n, G.nmat, static_cast<int64_t>(G.m) * G.n};
-        LACT_TRY(make_output(&P.out[0], &P.oi[0], XN, 0, 0));
-        P.ep = EpiNs{nxt[g], 0.f, 0.f, 0.f, static_cast<int64_t>(G.m) * G.n, G.n, (last && G.transposed) ? 1 : 0, G.m};
-      }
-      gc.status = status;
-      return LACT_OK;
-    };
-    LACT_TRY((launch_op<OpNs, 2>(bt_mm, fill_gram, stream, kClsNsGram, ngroups)));
-    LACT_TRY((launch_op<OpNs, 2>(bt_mm, fill_poly, stream, kClsNsPoly, ngroups)));
-    LACT_TRY((launch_op<OpNs, 2>(bt_mn, fill_upd, stream, kClsNsUpdate, ngroups)));
+    LACT_TRY((launch_op<OpNs, 2>(bt_mm, [&](auto& ga, int btv) { return fill(ga, btv, 0); }, stream, kClsNsGram, ngroups)));
+    LACT_TRY((launch_op<OpNs, 2>(bt_mm, [&](auto& ga, int btv) { return fill(ga, btv, 1); }, stream, kClsNsPoly, ngroups)));
+    LACT_TRY((launch_op<OpNs, 2>(bt_mn, [&](auto& ga, int btv) { return fill(ga, btv, 2); }, stream, kClsNsUpdate, ngroups)));
     for (int g = 0; g < ngroups; ++g) std::swap(cur[g], nxt[g]);
   }
   for (int g = 0; g < ngroups; ++g) result[g] = cur[g];
@@ -545,7 +564,7 @@ int run_ns_iterations(const NsGroup* grp, int ngroups, int steps, int const_coef
 // Fused path: all iterations in one cooperative launch (the first iterates must be in grp[g].xa).
 template <int BT_MM, int BT_MN>
 int launch_ns_fused(const NsGroup* grp, int ngroups, int steps, int const_coeffs, int32_t* status,
-                    cudaStream_t stream, uint64_t* trace) {
+                    cudaStream_t stream, uint64_t* trace, int unscaled_first) {
   using Args = NsFusedArgs<BT_MM, BT_MN>;
   auto kernel = ns_fused_kernel<BT_MM, BT_MN>;
   constexpr uint32_t smem = ns_fused_smem_bytes<BT_MM, BT_MN>();
@@ -567,38 +586,14 @@ int launch_ns_fused(const NsGroup* grp, int ngroups, int steps, int const_coeffs
   int64_t max_tiles = 1;
   for (int g = 0; g < ngroups; ++g) {
     const NsGroup& G = grp[g];
-    const int64_t mm = static_cast<int64_t>(G.m) * G.m, mn = static_cast<int64_t>(G.m) * G.n;
-    const Mat A{G.gram, G.m, G.m, G.m, G.nmat, mm};
-    const Mat CA{G.cgram, G.m, G.m, G.m, G.nmat, mm};
-    const Mat PB{G.poly, G.m, G.m, G.m, G.nmat, mm};
     for (int par = 0; par < 2; ++par) {
       bf16* cur = par == 0 ? G.xa : G.xb;
       bf16* nxt = par == 0 ? G.xb : G.xa;
-      const Mat X{cur, G.m, G.n, G.n, G.nmat, mn};
-      auto& PG = args.gram[par][g];
-      LACT_TRY(make_operand(&PG.a[0], &PG.ai[0], X, 0, kBM, 0, 0));
-      LACT_TRY(make_operand(&PG.b[0], &PG.bi[0], X, 0, BT_MM, 0, 0));
-      PG.M = G.m; PG.N = G.m; PG.K = G.n; PG.batch = G.nmat;
-      LACT_TRY(make_output(&PG.out[0], &PG.oi[0], A, 0, 0));
-      LACT_TRY(make_output(&PG.out[1], &PG.oi[1], CA, 0, 0));
-      PG.ep = EpiNs{nullptr, 0.f, 0.f, 0.f, mm, G.m, 0, 0};
-      auto& PU = args.upd[par][g];
-      LACT_TRY(make_operand(&PU.a[0], &PU.ai[0], PB, 0, kBM, 0, 0));
-      LACT_TRY(make_operand(&PU.b[0], &PU.bi[0], X, 1, BT_MN, 0, 0));
-      PU.M = G.m; PU.N = G.n; PU.K = G.m; PU.batch = G.nmat;
-      const Mat XN{nxt, G.m, G.n, G.n, G.nmat, mn};
-      LACT_TRY(make_output(&PU.out[0], &PU.oi[0], XN, 0, 0));
-      PU.ep = EpiNs{nxt, 0.f, 0.f, 0.f, mn, G.n, 0, 0};
+      LACT_TRY(wire_ns_group(G, cur, nxt, BT_MM, BT_MN, args.gram[par][g], args.poly[g], args.upd[par][g]));
     }
-    auto& PP = args.poly[g];
-    LACT_TRY(make_operand(&PP.a[0], &PP.ai[0], CA, 0, kBM, 0, 0));
-    LACT_TRY(make_operand(&PP.b[0], &PP.bi[0], A, 0, BT_MM, 0, 0));
-    PP.M = G.m; PP.N = G.m; PP.K = G.m; PP.batch = G.nmat;
-    LACT_TRY(make_output(&PP.out[0], &PP.oi[0], PB, 0, 0));
-    PP.ep = EpiNs{nullptr, 0.f, 0.f, 0.f, mm, G.m, 0, 0};
-    args.transposed[g] = G.transposed;
-    args.m[g] = G.m;
-    max_tiles = std::max<int64_t>(max_tiles, static_cast<int64_t>(G.nmat) * ceil_div(G.m, kBM) * ceil_div(G.n, BT_MN) * ngroups);
+    args.scale[g] = unscaled_first ? G.scale : nullptr;
+    max_tiles = std::max<int64_t>(max_tiles, static_cast<int64_t>(G.nmat) * ceil_div(ns_upd_rows(G), kBM) *
+                                                 ceil_div(ns_upd_cols(G), BT_MN) * ngroups);
   }
   for (int it = 0; it < steps; ++it) {
     const float* co = const_coeffs ? kNsConst : kNsTuned[it];
@@ -615,7 +610,7 @@ int launch_ns_fused(const NsGroup* grp, int ngroups, int steps, int const_coeffs
   const int grid = static_cast<int>(std::min<int64_t>(sm_count(), std::max<int64_t>(max_tiles, 8)));
   void* kargs[] = {&args};
   KernelScope scope(kClsNsFused, stream);
-  LACT_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kernel), dim3(grid), dim3(kGemmThreadsV2), kargs, smem,
+  LACT_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kernel), dim3(grid), dim3(kGemmThreadsFlow), kargs, smem,
                                         stream));
   return LACT_OK;
 }
@@ -623,7 +618,7 @@ int launch_ns_fused(const NsGroup* grp, int ngroups, int steps, int const_coeffs
 // Picks the fused kernel instantiated for the tile widths this problem wants; returns
 // LACT_ERR_CONFIG when there is none (the caller then runs the multi-launch path).
 int try_ns_fused(const NsGroup* grp, int ngroups, int steps, int const_coeffs, int32_t* status,
-                 cudaStream_t stream, const bf16** result, uint64_t* trace = nullptr) {
+                 cudaStream_t stream, const bf16** result, uint64_t* trace = nullptr, int unscaled_first = 0) {
   if (steps < 1 || steps > kNsFusedMaxSteps) return LACT_ERR_CONFIG;
   if (!const_coeffs && steps != 5) return LACT_ERR_CONFIG;
   {
@@ -631,16 +626,14 @@ int try_ns_fused(const NsGroup* grp, int ngroups, int steps, int const_coeffs, i
     const char* env = std::getenv("LACT_B200_NS_FUSED");
     if (env != nullptr && env[0] == '0') return LACT_ERR_CONFIG;
   }
-  const NsGroup& G0 = grp[0];
-  const NsGroup& G1 = grp[ngroups - 1];
-  const int bt_mm = choose_bt({{G0.m, static_cast<int64_t>(G0.nmat) * G0.m}, {G1.m, static_cast<int64_t>(G1.nmat) * G1.m}});
-  const int bt_mn = choose_bt({{G0.n, static_cast<int64_t>(G0.nmat) * G0.m}, {G1.n, static_cast<int64_t>(G1.nmat) * G1.m}});
+  int bt_mm = 0, bt_mn = 0;
+  ns_tile_widths(grp, ngroups, &bt_mm, &bt_mn);
   for (int g = 0; g < ngroups; ++g) result[g] = (steps % 2 == 0) ? grp[g].xa : grp[g].xb;
   if (bt_mm == 192 && bt_mn == 192)
-    return launch_ns_fused<192, 192>(grp, ngroups, steps, const_coeffs, status, stream, trace);
+    return launch_ns_fused<192, 192>(grp, ngroups, steps, const_coeffs, status, stream, trace, unscaled_first);
   // (a 256-wide update tile leaves no room for a useful ring next to two staging tiles: 128 is used)
   if (bt_mm == 128 && (bt_mn == 128 || bt_mn == 256))
-    return launch_ns_fused<128, 128>(grp, ngroups, steps, const_coeffs, status, stream, trace);
+    return launch_ns_fused<128, 128>(grp, ngroups, steps, const_coeffs, status, stream, trace, unscaled_first);
   return LACT_ERR_CONFIG;
 }
 
@@ -673,6 +666,7 @@ void carve_ns_group(Carver& c, NsGroup& g) {
   g.cgram = c.take<bf16>(mm);
   g.poly = c.take<bf16>(mm);
   g.partial = c.take<float>(static_cast<size_t>(g.nmat) * kNsMaxParts);
+  g.scale = c.take<float>(static_cast<size_t>(g.nmat));
   g.done = c.take<uint32_t>(static_cast<size_t>(g.nmat));
 }
 
@@ -853,6 +847,10 @@ int scan_fwd(const lact_scan_config& c, const lact_scan_io& io, int32_t n_steps,
       if (fused_parts[0] <= kNsMaxParts && fused_parts[1] <= kNsMaxParts) {
         g.partial02 = p.ns.grp[0].partial;
         g.partial1 = p.ns.grp[1].partial;
+        if (c.ns_steps > 0) {  // the iteration starts from bf16(G) itself, normalisation folded in
+          g.gb02 = p.ns.grp[0].xa;
+          g.gb1 = p.ns.grp[1].xa;
+        }
       } else {
         fused_parts[0] = fused_parts[1] = 0;
       }
@@ -886,12 +884,13 @@ int scan_fwd(const lact_scan_config& c, const lact_scan_io& io, int32_t n_steps,
       NsPlan& ns = p.ns;
       const bf16* xres[2] = {nullptr, nullptr};
       const void* srcs[2] = {p.G02, p.G1};
-      LACT_TRY(launch_ns_prepare(ns.grp, ns.ngroups, srcs, 1, c.ns_steps, stream,
+      const int unscaled = g.gb02 != nullptr ? 1 : 0;
+      LACT_TRY(launch_ns_prepare(ns.grp, ns.ngroups, srcs, 1, !unscaled, stream,
                                  fused_parts[0] > 0 ? fused_parts : nullptr));
       int rc = try_ns_fused(ns.grp, ns.ngroups, c.ns_steps, c.ns_const_coeffs, p.status, stream, xres,
-                            reinterpret_cast<uint64_t*>(p.status + 64));
+                            reinterpret_cast<uint64_t*>(p.status + 64), unscaled);
       if (rc == LACT_ERR_CONFIG)
-        rc = run_ns_iterations(ns.grp, ns.ngroups, c.ns_steps, c.ns_const_coeffs, xres, p.status, stream);
+        rc = run_ns_iterations(ns.grp, ns.ngroups, c.ns_steps, c.ns_const_coeffs, xres, p.status, stream, unscaled);
       LACT_TRY(rc);
       rn[0].x = xres[0];
       rn[1].x = xres[1];
@@ -1129,7 +1128,7 @@ int lact_newton_schulz(const void* g, int32_t g_dtype, void* x, int64_t B, int64
   carve_ns_group(cv, grp);
   const bf16* res = nullptr;
   const void* srcs[2] = {g, g};
-  LACT_TRY(launch_ns_prepare(&grp, 1, srcs, g_dtype == LACT_F32, steps, s));
+  LACT_TRY(launch_ns_prepare(&grp, 1, srcs, g_dtype == LACT_F32, 1, s));
   int rc = try_ns_fused(&grp, 1, steps, const_coeffs, status, s, &res);
   if (rc == LACT_ERR_CONFIG) rc = run_ns_iterations(&grp, 1, steps, const_coeffs, &res, status, s);
   LACT_TRY(rc);

@@ -16,7 +16,7 @@ struct NsFusedArgs {
   GemmProblem<OpNs<BT_MM>> gram[2][2];  // [iteration parity][group]
   GemmProblem<OpNs<BT_MM>> poly[2];     // [group]
   GemmProblem<OpNs<BT_MN>> upd[2][2];   // [iteration parity][group]
-  int32_t transposed[2], m[2];          // per group: iterate is the gradient's transpose; rows of the iterate
+  const float* scale[2];                // per group: [matrix] 1 / (||G|| + 1e-7) when the first iterate is unscaled
   float coef[16][3];                    // (a, b, c) per iteration
   int32_t steps, ngroups;
   int32_t* status;
@@ -28,15 +28,14 @@ constexpr int kNsFusedMaxSteps = 16;
 
 struct NsPatch {
   float diag, gamma, diag2;
-  int32_t last;
-  int32_t transposed[2];
-  int32_t m[2];
+  int32_t scale_pow;
+  const float* scale[2];
   __device__ __forceinline__ void operator()(EpiNs& ep, int prob) const {
     ep.diag = diag;
     ep.gamma = gamma;
     ep.diag2 = diag2;
-    ep.out_transposed = (last && transposed[prob]) ? 1 : 0;
-    ep.out_ld_t = m[prob];
+    ep.scale = scale[prob];
+    ep.scale_pow = scale_pow;
   }
 };
 
@@ -61,7 +60,7 @@ __host__ __device__ constexpr uint32_t ns_fused_smem_bytes() {
 }
 
 template <int BT_MM, int BT_MN>
-__global__ void __launch_bounds__(kGemmThreadsV2, 1)
+__global__ void __launch_bounds__(kGemmThreadsFlow, 1)
 ns_fused_kernel(const __grid_constant__ NsFusedArgs<BT_MM, BT_MN> args) {
   using OpMM = OpNs<BT_MM>;
   using OpMN = OpNs<BT_MN>;
@@ -99,17 +98,17 @@ ns_fused_kernel(const __grid_constant__ NsFusedArgs<BT_MM, BT_MN> args) {
   FlowDeps deps;
   uint32_t tiles_mm[2], tiles_mn[2];  // tiles one matrix contributes to a gram / poly phase, an update phase
   for (int g = 0; g < 2; ++g) {
-    patch.transposed[g] = args.transposed[g];
-    patch.m[g] = args.m[g];
+    patch.scale[g] = args.scale[g];
     deps.counter[g] = args.done[g];
     deps.need[g] = 0;
+    const auto& A = args.poly[g];
     const auto& U = args.upd[0][g];
-    tiles_mm[g] = ((U.M + kBM - 1) / kBM) * ((U.M + BT_MM - 1) / BT_MM);
+    tiles_mm[g] = ((A.M + kBM - 1) / kBM) * ((A.N + BT_MM - 1) / BT_MM);
     tiles_mn[g] = ((U.M + kBM - 1) / kBM) * ((U.N + BT_MN - 1) / BT_MN);
   }
   for (int it = 0; it < args.steps && !failed; ++it) {
     const int par = it & 1;
-    patch.last = 0;
+    patch.scale_pow = it == 0 ? 2 : 0;
     patch.diag = 0.f;                 // gram: A and c A + b I
     patch.gamma = args.coef[it][2];
     patch.diag2 = args.coef[it][1];
@@ -120,12 +119,13 @@ ns_fused_kernel(const __grid_constant__ NsFusedArgs<BT_MM, BT_MN> args) {
     patch.diag = args.coef[it][0];    // poly: (c A + b I) A + a I
     patch.gamma = 0.f;
     patch.diag2 = 0.f;
+    patch.scale_pow = 0;
     failed = gemm_phase<OpMM, RING>(cx, args.poly, args.ngroups, patch, deps);
     ++cx.phase;
     if (failed) break;
     for (int g = 0; g < 2; ++g) deps.need[g] += tiles_mm[g];
     patch.diag = 0.f;                 // update: (P + a I) X
-    patch.last = (it == args.steps - 1);
+    patch.scale_pow = it == 0 ? 1 : 0;
     failed = gemm_phase<OpMN, RING>(cx, args.upd[par], args.ngroups, patch, deps);
     ++cx.phase;
     for (int g = 0; g < 2; ++g) deps.need[g] += tiles_mn[g];

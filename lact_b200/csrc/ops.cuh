@@ -103,6 +103,8 @@ struct EpiDW {
   // index = ((batch * tiles_m + tile_m) * tiles_n + tile_n) * 8 + warp
   float* partial;
   int32_t tiles_m, tiles_n;
+  // optional: bf16 copy of g with the same strides (the first Newton-Schulz iterate before scaling)
+  bf16* gb;
   // returns the sum of squares of the bf16-rounded results of this row segment if `want_ss`
   __device__ __forceinline__ float operator()(int batch, int row, int col, int M, int N, const float* v,
                                               bool want_ss = false) const {
@@ -131,6 +133,7 @@ struct EpiDW {
     } else {
       store_row32_bf16(reinterpret_cast<bf16*>(g) + idx, r, valid);
     }
+    if (gb != nullptr) store_row32_bf16(gb + idx, r, valid);
     float ss = 0.f;
     if (want_ss) {
 #pragma unroll
@@ -147,13 +150,11 @@ struct EpiDW {
 // arithmetic): t = bf16(acc); if res: t = bf16(bf16(alpha * res) + t); out = t;
 // if out2: out2 = bf16(gamma * t).
 struct EpiNs {
-  bf16* out;         // used only for the transposed final write
-  float diag;        // first output  = bf16(acc + diag * I)
-  float gamma;       // second output = bf16(gamma * first + diag2 * I)
+  float diag;          // first output  = bf16(scale * acc + diag * I)
+  float gamma;         // second output = bf16(gamma * first + diag2 * I)
   float diag2;
-  int64_t bs, ld;
-  int32_t out_transposed;  // final iterate of a transposed group: write out[batch][col][row]
-  int32_t out_ld_t;
+  const float* scale;  // per-matrix 1 / (||G||_F + 1e-7), or nullptr
+  int32_t scale_pow;   // 0: no scaling, 1: acc * s, 2: acc * s * s
 };
 
 // Fast-weight-gradient pointwise stage: from y0 = k w0^T, y2 = k w2^T, dh = v w1 and the three
@@ -286,8 +287,10 @@ struct OpBmm2 {
 // bf16(c A + b I); the poly phase writes bf16((c A + b I) A + a I); the update phase is a plain
 // product.  All values are bf16 with fp32 accumulation, as in the reference; folding moves two of
 // its rounding points (one rounding of the fp32 sum instead of bf16(bf16(b A) + bf16((c A) A))),
-// which perturbs the result no more than the reference's own bf16 arithmetic does.  The last
-// iterate of a transposed group is written from registers in the gradient's own orientation.
+// which perturbs the result no more than the reference's own bf16 arithmetic does.
+// The Frobenius normalisation X0 = G / (||G|| + 1e-7) can be folded in as well: the first iteration
+// then runs on bf16(G) itself and its gram / update epilogues multiply the fp32 accumulator by
+// s^2 / s, s = 1 / (||G|| + 1e-7) (per matrix, `scale`).
 template <int BT_>
 struct OpNs {
   static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 2;
@@ -307,20 +310,22 @@ struct OpNs {
   __device__ static __forceinline__ float second(const Epi& ep, float t, int row, int col) {
     return ep.gamma * t + (row == col ? ep.diag2 : 0.f);
   }
-  __device__ static __forceinline__ bool skip_store(const Epi& ep, int o) { return o == 0 && ep.out_transposed; }
-  using Prefetch = NoPrefetch;
-  __device__ static __forceinline__ void prefetch(const Epi&, int, int, int, int, int, int, Prefetch&) {}
-  __device__ static __forceinline__ void epilogue_staged(const Epi& ep, int batch, int row, int col, int M, int N,
-                                                         const float (&v)[1][32], float (&o)[1][32], Prefetch&, int) {
-    const int valid = min(32, N - col);
-#pragma unroll
-    for (int j = 0; j < 32; ++j) o[0][j] = bf16_round(v[0][j] + (row == col + j ? ep.diag : 0.f));
-    if (ep.out_transposed && row < M) {
-      bf16* dst = ep.out + batch * ep.bs + static_cast<int64_t>(col) * ep.out_ld_t + row;
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (j < valid) dst[static_cast<int64_t>(j) * ep.out_ld_t] = __float2bfloat16_rn(o[0][j]);
+  __device__ static __forceinline__ bool skip_store(const Epi&, int) { return false; }
+  struct Prefetch {
+    float sc;
+  };
+  __device__ static __forceinline__ void prefetch(const Epi& ep, int batch, int, int, int, int, int, Prefetch& pf) {
+    pf.sc = 1.f;
+    if (ep.scale_pow != 0 && ep.scale != nullptr) {
+      const float s1 = ep.scale[batch];
+      pf.sc = ep.scale_pow == 2 ? s1 * s1 : s1;
     }
+  }
+  __device__ static __forceinline__ void epilogue_staged(const Epi& ep, int, int row, int col, int, int,
+                                                         const float (&v)[1][32], float (&o)[1][32], Prefetch& pf,
+                                                         int) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) o[0][j] = bf16_round(v[0][j] * pf.sc + (row == col + j ? ep.diag : 0.f));
   }
 };
 
@@ -486,6 +491,7 @@ struct NsPrepGroup {
   bf16* x0;           // first iterate
   float* partial;     // [nmat][nparts] partial sums of squares, added in index order
   int32_t nparts;
+  float* scale;       // [nmat] out of ns_den_kernel
 };
 struct NsPrepArgs {
   NsPrepGroup grp[2];
@@ -530,6 +536,25 @@ __global__ void __launch_bounds__(256) ns_sumsq_kernel(const NsPrepArgs args) {
     x = warp_sum(x);
     if (threadIdx.x == 0) G.partial[mat * kNsSlabs + slab] = x;
   }
+}
+
+// Scale factors for the folded normalisation: scale[mat] = 1 / (bf16(bf16(||bf16(G)||_F) + 1e-7)).
+// One warp per matrix: lane l adds partials l, l + 32, ... in order, then a fixed butterfly adds the
+// 32 lane sums, so the result does not depend on scheduling.
+__global__ void __launch_bounds__(128) ns_den_kernel(const NsPrepArgs args) {
+  griddep_launch_dependents();
+  griddep_wait();
+  int mat = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int total = args.grp[0].nmat + (args.ngroups > 1 ? args.grp[1].nmat : 0);
+  if (mat >= total) return;
+  const int gi = (args.ngroups > 1 && mat >= args.grp[0].nmat) ? 1 : 0;
+  if (gi == 1) mat -= args.grp[0].nmat;
+  const NsPrepGroup& G = args.grp[gi];
+  float tot = 0.f;
+  for (int i = lane; i < G.nparts; i += 32) tot += G.partial[static_cast<int64_t>(mat) * G.nparts + i];
+  tot = warp_sum(tot);
+  if (lane == 0) G.scale[mat] = 1.0f / bf16_round(bf16_round(sqrtf(tot)) + 1e-7f);
 }
 
 // Part 2: X = bf16(bf16(G) / (bf16(||bf16(G)||_F) + 1e-7)), every operation rounded to bf16 as in

@@ -84,6 +84,9 @@ __host__ __device__ constexpr uint32_t gemm_smem_bytes() {
 
 constexpr int kEpiWarps = 8;
 constexpr int kGemmThreadsV2 = 64 + 32 * kEpiWarps;  // producer warp + MMA warp + epilogue warps
+// dataflow kernels add a scout warp that walks the tile sequence ahead of the producer and checks
+// every tile's dependency, so that the global-memory latency of that check never stalls the loads
+constexpr int kGemmThreadsFlow = kGemmThreadsV2 + 32;
 
 template <int ROWS>
 __device__ __forceinline__ void load_operand_tile(uint32_t dst, const CUtensorMap* map, const OperandInfo& oi,
@@ -268,17 +271,25 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
         const TileCoord tc = coord(tile);
         const GemmProblem<Op>& P = probs[tc.prob];
         const int num_kb = (P.K + kBK - 1) / kBK;
+#ifdef LACT_TRACE_LOADS
+        if (cx.trace != nullptr && blockIdx.x == 0 && cx.phase == 2 && tile_i >= 1 && tile_i <= 2) cx.trace[240 + 2 * (tile_i - 1)] = globaltimer_ns();
+#endif
         if constexpr (Deps::kOn) {
-          if (!dep_wait(deps.counter[tc.prob] + tc.batch, deps.need[tc.prob], cx.abort_flag)) { failed = true; break; }
+          if (!flow_wait_verified(cx, cx.ptile++)) { failed = true; break; }  // the scout warp checked this tile
           asm volatile("fence.proxy.async;" ::: "memory");
-          st_release_cta_shared_u32(cx.dep_ok, ++cx.ptile);
         }
+#ifdef LACT_TRACE_LOADS
+        if (cx.trace != nullptr && blockIdx.x == 0 && cx.phase == 2 && tile_i >= 1 && tile_i <= 2) cx.trace[241 + 2 * (tile_i - 1)] = globaltimer_ns();
+#endif
         for (int kb = 0; kb < num_kb; ++kb, ++cx.it) {
           const int s = cx.it % RING;
           const uint32_t ph = (cx.it / RING) & 1;
           if (!mbar_wait(&cx.empty_bar[s], ph ^ 1, cx.abort_flag)) { failed = true; break; }
           if (kb == num_kb - 1) cx.stamp(tile_i, 0);
           mbar_expect_tx(&cx.full_bar[s], kStageBytes);
+#ifdef LACT_TRACE_LOADS
+          if (cx.trace != nullptr && blockIdx.x == 0 && cx.phase == 2 && tile_i >= 1 && tile_i <= 2 && kb < 8) cx.trace[200 + 20 * (tile_i - 1) + 2 * kb] = globaltimer_ns();
+#endif
           const uint32_t st = cx.smem_base + s * cx.stage_stride;
           const int kc = kb * kBK;
 #pragma unroll
@@ -302,12 +313,18 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
         const int num_kb = (P.K + kBK - 1) / kBK;
         const uint32_t as = cx.tcount & 1, aph = (cx.tcount >> 1) & 1;
         if (!mbar_wait(&cx.acc_empty_bar[as], aph ^ 1, cx.abort_flag)) { failed = true; break; }
+#ifdef LACT_TRACE_LOADS
+        if (cx.trace != nullptr && blockIdx.x == 0 && cx.phase == 2 && tile_i >= 1 && tile_i <= 2) cx.trace[250 + (tile_i - 1)] = globaltimer_ns();
+#endif
         tc_fence_after();
         const uint32_t acc_base = cx.tmem_base + as * kAccCols;
         for (int kb = 0; kb < num_kb; ++kb, ++cx.it) {
           const int s = cx.it % RING;
           const uint32_t ph = (cx.it / RING) & 1;
           if (!mbar_wait(&cx.full_bar[s], ph, cx.abort_flag)) { failed = true; break; }
+#ifdef LACT_TRACE_LOADS
+          if (cx.trace != nullptr && blockIdx.x == 0 && cx.phase == 2 && tile_i >= 1 && tile_i <= 2 && kb < 8) cx.trace[201 + 20 * (tile_i - 1) + 2 * kb] = globaltimer_ns();
+#endif
           tc_fence_after();
           const uint32_t st = cx.smem_base + s * cx.stage_stride;
 #pragma unroll
@@ -329,6 +346,20 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
         if (!failed) umma_commit(&cx.acc_full_bar[as]);
         cx.stamp(tile_i, 1);
         ++cx.tcount;
+      }
+    }
+  } else if (warp >= 2 + kEpiWarps) {
+    // ---------------- dependency scout (dataflow kernels only): one thread verifies, in tile order,
+    // that every tile's inputs are complete and publishes the count of verified tiles
+    if constexpr (Deps::kOn) {
+      if (lane == 0) {
+        for (int tile_i = 0; tile_i < rounds && !failed; ++tile_i) {
+          const int tile = tile_at(tile_i);
+          if (tile >= total_tiles) continue;
+          const TileCoord tc = coord(tile);
+          if (!dep_wait(deps.counter[tc.prob] + tc.batch, deps.need[tc.prob], cx.abort_flag)) { failed = true; break; }
+          st_release_cta_shared_u32(cx.dep_ok, ++cx.ptile);
+        }
       }
     }
   } else {

@@ -77,13 +77,16 @@ def newton_schulz(G: torch.Tensor, steps: Optional[int] = None) -> torch.Tensor:
     return X
 
 
-def newton_schulz_folded(G: torch.Tensor, steps: Optional[int] = None) -> torch.Tensor:
+def newton_schulz_folded(G: torch.Tensor, steps: Optional[int] = None, fold_norm: bool = False) -> torch.Tensor:
     """Rounding model of the CUDA kernels' Newton-Schulz: the same iteration with the residual
     terms folded into the contractions as multiples of the identity,
     ``b A + (c A) A = (c A + b I) A`` and ``a X + P X = (P + a I) X``; bf16 values, fp32
     accumulation, one rounding per stored matrix.  The reference's compiled GPU graph likewise
     rounds ``b*A + c*A@A`` and ``a*X + B@X`` once (inductor fuses the elementwise part), so its own
     GPU and eager CPU results differ by the same kind of amount as this model and `newton_schulz`.
+    ``fold_norm``: the chunk recurrence also folds the Frobenius normalisation into the first
+    iteration: it iterates on bf16(G) itself and multiplies the first Gram matrix by s^2 and the
+    first update by s, s = 1 / (||G|| + 1e-7), in fp32 before the rounding.
     """
     assert G.dim() == 3
     coeffs = NS_TUNED5 if steps is None else (NS_CONST,) * steps
@@ -91,14 +94,18 @@ def newton_schulz_folded(G: torch.Tensor, steps: Optional[int] = None) -> torch.
     flip = G.size(1) > G.size(2)
     if flip:
         X = X.transpose(1, 2)
-    X = X / (X.norm(dim=(1, 2), keepdim=True) + 1e-7)
+    den = X.norm(dim=(1, 2), keepdim=True) + 1e-7
+    s = (1.0 / den.float()) if (fold_norm and len(coeffs) > 0) else None
+    if s is None:
+        X = X / den
     eye = torch.eye(X.size(1), dtype=torch.float32)
-    for a, b, c in coeffs:
+    for i, (a, b, c) in enumerate(coeffs):
         Xf = X.float()
-        A = (Xf @ Xf.transpose(1, 2)).to(BF16)
+        s2, s1 = (s * s, s) if (s is not None and i == 0) else (1.0, 1.0)
+        A = ((Xf @ Xf.transpose(1, 2)) * s2).to(BF16)
         CA = (c * A.float() + b * eye).to(BF16)
         P = (CA.float() @ A.float() + a * eye).to(BF16)
-        X = (P.float() @ Xf).to(BF16)
+        X = ((P.float() @ Xf) * s1).to(BF16)
     if flip:
         X = X.transpose(1, 2)
     return X
@@ -550,8 +557,8 @@ class ScanConfig:
 def _ns_model(G, cfg: ScanConfig):
     steps = cfg.ns_steps if cfg.ns_const_coeffs else None
     if cfg.ns_gram_right and G.size(1) == G.size(2):
-        return newton_schulz_folded(G.transpose(1, 2), steps).transpose(1, 2)
-    return newton_schulz_folded(G, steps)
+        return newton_schulz_folded(G.transpose(1, 2), steps, fold_norm=True).transpose(1, 2)
+    return newton_schulz_folded(G, steps, fold_norm=True)
 
 
 def scan_model(w0, w1, w2, q, k, v, lr0, lr1, lr2, steps: Sequence[Tuple[str, int, int, int]], cfg: ScanConfig,
