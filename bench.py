@@ -33,6 +33,7 @@ import torch  # noqa: E402
 BF16 = torch.bfloat16
 CFG = dict(batch=8, heads=4, L=32768, D=384, H=384, chunk=2048, ns_steps=5)
 METRIC = "ttt_layer_fwd_tokens_per_s_760M_shape"
+E2E_SLABS = 8  # the end-to-end arm streams the batch through the device in this many slabs
 
 
 # ------------------------------------------------------------------------------------------ helpers
@@ -215,6 +216,45 @@ def workload_config(n):
             "l2": "inputs (3.2 GB per step) exceed L2; no explicit flush"}
 
 
+def train_step_timing(lb, t, dev, B, L, D, H, C, tokens_per_step, world, barrier, peaks, steps=3):
+    """Forward + backward of the same workload (the training configuration): one step = forward,
+    then backward from dO ~ N(0,1) bf16 to q, k, v, lr0/1/2, momentum and the initial W0/W1/W2."""
+    import torch.distributed as dist
+    leaves = {n: t[n].detach().clone().requires_grad_(True) for n in ARG_ORDER + ("momentum",)}
+    dO = torch.randn(B, L, D, device=dev, generator=torch.Generator(device=dev).manual_seed(99)).to(BF16)
+
+    def step():
+        for v in leaves.values():
+            v.grad = None
+        o = lb.postnorm_block_causal_lact_swiglu_fused_kernel_triton(
+            *[leaves[n] for n in ARG_ORDER], chunk_size=C, use_muon=True, momentum=leaves["momentum"])
+        o.backward(dO)
+
+    step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    barrier()
+    lb.synchronize_and_check()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_step = float(ms.item()) / steps
+    n_upd = len(range(0, L - C, C))
+    ns = lambda r, c: CFG["ns_steps"] * (4 * min(r, c) ** 2 * max(r, c) + 2 * min(r, c) ** 3)
+    fwd = algorithmic_flops(B, L, D, H, C, CFG["ns_steps"])
+    bwd = B * (12 * D * H * L + 24 * D * H * n_upd * C + 2 * n_upd * (ns(2 * H, D) + ns(D, H)))
+    tf = (fwd + bwd) / (ms_step * 1e-3) / 1e12
+    return {"ms_per_step": ms_step, "tokens_per_s": world * tokens_per_step / (ms_step * 1e-3), "steps": steps,
+            "algorithmic_flops_per_step_per_gpu": fwd + bwd, "tflops_per_gpu": tf,
+            "frac_of_bf16_peak_burst": tf / peaks["bf16_burst"],
+            "note": "forward on the fused kernels; backward = per-chunk reverse sweep driven from the host "
+                    "(recomputes pre-activations and the Newton-Schulz iterates)"}
+
+
 # ------------------------------------------------------------------------------------------ main arm
 def main():
     ap = argparse.ArgumentParser()
@@ -224,6 +264,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--train", action="store_true",
+                    help="also time forward + backward through the recurrence (gradients to q, k, v, lr, momentum "
+                         "and the initial fast weights, upstream gradient ~ N(0,1) bf16); reported under \"train\"")
     ap.add_argument("--batch", type=int, default=None,
                     help="override the batch size (profiler captures on a small case; not a headline number)")
     ap.add_argument("--seq-len", type=int, default=None, help="override the sequence length (same caveat)")
@@ -320,18 +363,17 @@ def main():
     # end to end through the public API with pinned host buffers
     e2e = None
     if not args.no_e2e:
+        from lact_b200.host_io import HostPipeline
         host = {k: v.cpu().pin_memory() for k, v in t.items()}
         h2d = sum(v.numel() * v.element_size() for v in host.values())
         out_host = torch.empty(B, L, D, dtype=BF16).pin_memory()
         d2h = out_host.numel() * out_host.element_size()
-        dev_bufs = {k: torch.empty_like(v, device=dev) for k, v in host.items()}
         n_e2e = max(2, min(steps, 4))
-
-        def e2e_step():
-            for k_, v_ in host.items():
-                dev_bufs[k_].copy_(v_, non_blocking=True)
-            o = run_step(lact_b200, dev_bufs)
-            out_host.copy_(o, non_blocking=True)
+        # the public call, fed from pinned host memory in slabs of (batch x head) entries so that the
+        # copies of one slab overlap the kernels of another (every entry is an independent recurrence)
+        n_slabs = E2E_SLABS if B % E2E_SLABS == 0 else 1
+        pipe = HostPipeline(lambda **kw: run_step(lact_b200, kw), host, out_host, n_slabs=n_slabs, device=dev)
+        e2e_step = pipe.run
 
         e2e_step()
         barrier()
@@ -345,7 +387,12 @@ def main():
             dist.all_reduce(ems, op=dist.ReduceOp.MAX)
         e2e = {"value": world * tokens_per_step / (float(ems.item()) / n_e2e * 1e-3), "unit": "tokens/s",
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": n_e2e}
-        del host, dev_bufs, out_host
+        e2e["slabs"] = n_slabs
+        del host, pipe, out_host
+
+    train = None
+    if args.train:
+        train = train_step_timing(lact_b200, t, dev, B, L, D, H, C, tokens_per_step, world, barrier, peaks)
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -364,6 +411,8 @@ def main():
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches,
             "clocks": clocks.summary(),
         }
+        if train is not None:
+            line["train"] = train
         if reduced:
             line["reduced_case"] = "batch/seq overridden for a profiler capture: not the benchmark workload"
         print(json.dumps(line), flush=True)

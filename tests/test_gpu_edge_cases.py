@@ -114,3 +114,26 @@ def test_nvs_block_shape(lb, orc):
     assert got[0].shape == (2, n_tgt, 192)
     for g, r, nm in zip(got, ref, ("o", "w0", "w1", "w2")):
         _close(orc, g, r, tol=2e-2, what="nvs " + nm)
+
+
+def test_host_pipeline_matches_direct_call(lb):
+    """Pinned host tensors streamed through the device in slabs of (batch x head) entries give the
+    bits of one call on device tensors (entries are independent recurrences)."""
+    from lact_b200.host_io import HostPipeline
+    from oracle import lact_oracle as orc
+    i = orc.make_inputs(8, 600, 64, 64, seed=31, act_dtype=torch.bfloat16)
+    names = ("w0", "w1", "w2", "q", "k", "v", "lr0", "lr1", "lr2")
+    fn = lambda **kw: lb.postnorm_block_causal_lact_swiglu_fused_kernel_triton(
+        *[kw[n] for n in names], chunk_size=128, use_muon=True, momentum=kw["momentum"])
+    direct = fn(**{k: v.cuda() for k, v in i.items() if torch.is_tensor(v)})
+    host = {k: v.pin_memory() for k, v in i.items() if torch.is_tensor(v)}
+    out = torch.empty(direct.shape, dtype=direct.dtype).pin_memory()
+    pipe = HostPipeline(fn, host, out, n_slabs=4, device=torch.device("cuda", 0))
+    for _ in range(2):
+        out.zero_()
+        pipe.run()
+        torch.cuda.synchronize()
+        assert torch.equal(out, direct.cpu())
+    with pytest.raises(ValueError):
+        HostPipeline(fn, host, out, n_slabs=3, device=torch.device("cuda", 0))
+    lb.synchronize_and_check()
