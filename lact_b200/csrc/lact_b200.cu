@@ -185,9 +185,6 @@ cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
 }
 
 int sm_count() {
-#ifdef LACT_SM_LIMIT
-  return LACT_SM_LIMIT;  // experiments only: run the persistent grids on fewer SMs
-#endif
   static int cached[64] = {0};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
@@ -463,7 +460,7 @@ int launch_ns_prepare(const NsGroup* grp, int ngroups, const void* const* src, i
     const NsGroup& G = grp[g];
     const int parts = (fused_parts != nullptr && fused_parts[g] > 0) ? fused_parts[g] : kNsSlabs;
     if (fused_parts == nullptr || fused_parts[g] <= 0) need_sumsq = true;
-    pa.grp[g] = NsPrepGroup{src[g], src_f32, G.nmat, G.R, G.C, 0, G.xa, G.partial, parts, G.scale};
+    pa.grp[g] = NsPrepGroup{src[g], src_f32, G.nmat, G.R, G.C, G.xa, G.partial, parts, G.scale};
     nmat += G.nmat;
     tiles = std::max(tiles, ceil_div(G.R, 64) * ceil_div(G.C, 64));
   }

@@ -185,7 +185,7 @@ __host__ __device__ constexpr int ring_depth(uint32_t stage_bytes, uint32_t stag
 template <class EpiT, int BT_>
 struct OpBmm {
   static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 0;
-  static constexpr bool kSecondInPlace = false, kResidualTma = false, kTileReduce = false;
+  static constexpr bool kSecondInPlace = false, kTileReduce = false;
   static constexpr int kStagingBuffers = 1;
   static constexpr int STAGES = ring_depth(kATileBytes + BT_ * kBK * 2, 0);
   using Epi = EpiT;
@@ -208,7 +208,7 @@ struct OpBmm {
 template <int BT_>
 struct OpDW {
   static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 0;
-  static constexpr bool kSecondInPlace = false, kResidualTma = false, kTileReduce = true;
+  static constexpr bool kSecondInPlace = false, kTileReduce = true;
   static constexpr int kStagingBuffers = 1;
   static constexpr int STAGES = ring_depth(kATileBytes + BT_ * kBK * 2, 0);
   using Epi = EpiDW;
@@ -241,7 +241,7 @@ struct EpiNone {};
 template <int BT_>
 struct OpBmmStore {
   static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 1;
-  static constexpr bool kSecondInPlace = false, kResidualTma = false, kTileReduce = false;
+  static constexpr bool kSecondInPlace = false, kTileReduce = false;
   static constexpr int kStagingBuffers = 1;
   static constexpr int STAGES = ring_depth(kATileBytes + BT_ * kBK * 2, kBM * BT_ * 2);
   using Epi = EpiNone;
@@ -254,7 +254,7 @@ struct OpBmmStore {
   __device__ static __forceinline__ void prefetch(const Epi&, int, int, int, int, int, int, Prefetch&) {}
   __device__ static __forceinline__ bool skip_store(const Epi&, int) { return false; }
   __device__ static __forceinline__ void epilogue_staged(const Epi&, int, int, int, int, int, const float (&v)[1][32],
-                                                         float (&o)[1][32], Prefetch&, int) {
+                                                         float (&o)[1][32], Prefetch&) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) o[0][j] = v[0][j];
   }
@@ -264,7 +264,7 @@ struct OpBmmStore {
 template <class EpiT, int BT_>
 struct OpBmm2 {
   static constexpr int NA = 2, NB = 2, NACC = 1, BT = BT_, NTERMS = 2, NOUT = 0;
-  static constexpr bool kSecondInPlace = false, kResidualTma = false, kTileReduce = false;
+  static constexpr bool kSecondInPlace = false, kTileReduce = false;
   static constexpr int kStagingBuffers = 1;
   static constexpr int STAGES = ring_depth(2 * kATileBytes + 2 * BT_ * kBK * 2, 0);
   using Epi = EpiT;
@@ -294,7 +294,7 @@ struct OpBmm2 {
 template <int BT_>
 struct OpNs {
   static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 2;
-  static constexpr bool kSecondInPlace = true, kResidualTma = false, kTileReduce = false;
+  static constexpr bool kSecondInPlace = true, kTileReduce = false;
 #ifndef LACT_NS_STAGING_BUFFERS
 #define LACT_NS_STAGING_BUFFERS 2
 #endif
@@ -322,8 +322,7 @@ struct OpNs {
     }
   }
   __device__ static __forceinline__ void epilogue_staged(const Epi& ep, int, int row, int col, int, int,
-                                                         const float (&v)[1][32], float (&o)[1][32], Prefetch& pf,
-                                                         int) {
+                                                         const float (&v)[1][32], float (&o)[1][32], Prefetch& pf) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) o[0][j] = bf16_round(v[0][j] * pf.sc + (row == col + j ? ep.diag : 0.f));
   }
@@ -334,7 +333,7 @@ struct OpNs {
 template <int BT_>
 struct OpSwigluGate {
   static constexpr int NA = 1, NB = 2, NACC = 2, BT = BT_, NTERMS = 1, NOUT = 1;
-  static constexpr bool kSecondInPlace = false, kResidualTma = false, kTileReduce = false;
+  static constexpr bool kSecondInPlace = false, kTileReduce = false;
   static constexpr int kStagingBuffers = 1;
   static constexpr int STAGES = ring_depth(kATileBytes + 2 * BT_ * kBK * 2, kBM * BT_ * 2);
   using Epi = EpiNone;
@@ -347,7 +346,7 @@ struct OpSwigluGate {
   __device__ static __forceinline__ void prefetch(const Epi&, int, int, int, int, int, int, Prefetch&) {}
   __device__ static __forceinline__ bool skip_store(const Epi&, int) { return false; }
   __device__ static __forceinline__ void epilogue_staged(const Epi&, int, int, int, int, int, const float (&v)[2][32],
-                                                         float (&o)[1][32], Prefetch&, int) {
+                                                         float (&o)[1][32], Prefetch&) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
       const float y0 = v[0][j];
@@ -361,7 +360,7 @@ struct OpSwigluGate {
 // outputs (dy0, dy2, hidden * lr1).
 struct OpFwGradPointwise {
   static constexpr int NA = 2, NB = 3, NACC = 3, BT = 64, NTERMS = 2, NOUT = 3;
-  static constexpr bool kSecondInPlace = false, kResidualTma = false, kTileReduce = false;
+  static constexpr bool kSecondInPlace = false, kTileReduce = false;
   static constexpr int kStagingBuffers = 1;
   static constexpr int STAGES = ring_depth(2 * kATileBytes + 3 * 64 * kBK * 2, 3 * kBM * 64 * 2);
   using Epi = EpiFwGrad;
@@ -386,7 +385,7 @@ struct OpFwGradPointwise {
   __device__ static __forceinline__ bool skip_store(const Epi&, int) { return false; }
   __device__ static __forceinline__ void epilogue_staged(const Epi&, int, int, int, int, int,
                                                          const float (&v)[3][32], float (&o)[3][32],
-                                                         Prefetch& pf, int) {
+                                                         Prefetch& pf) {
     const float l0 = pf.l0, l1 = pf.l1, l2 = pf.l2;
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
@@ -487,7 +486,6 @@ struct NsPrepGroup {
   const void* src;  // gradient matrices [nmat][R][C], contiguous
   int32_t src_f32;
   int32_t nmat, R, C;
-  int32_t transpose;  // write the iterate transposed ([C][R])
   bf16* x0;           // first iterate
   float* partial;     // [nmat][nparts] partial sums of squares, added in index order
   int32_t nparts;
@@ -558,14 +556,11 @@ __global__ void __launch_bounds__(128) ns_den_kernel(const NsPrepArgs args) {
 }
 
 // Part 2: X = bf16(bf16(G) / (bf16(||bf16(G)||_F) + 1e-7)), every operation rounded to bf16 as in
-// the reference; written transposed (through a shared-memory tile, so both sides stay coalesced)
-// when the iteration runs on the other orientation.  Grid (matrices of all groups, 64x64 tiles).
-// Matrices whose sizes allow it move as 16-byte vectors (four source columns per thread; eight
-// output elements per thread on the transposed side).
+// the reference, in the gradient's own layout.  Grid (matrices of all groups, 64x64 tiles); rows
+// whose length allows it move as 16-byte vectors.
 __global__ void __launch_bounds__(256) ns_scale_kernel(const NsPrepArgs args) {
   griddep_launch_dependents();
   griddep_wait();
-  __shared__ float tile[64][65];
   int mat = blockIdx.x;
   const int gi = (args.ngroups > 1 && mat >= args.grp[0].nmat) ? 1 : 0;
   if (gi == 1) mat -= args.grp[0].nmat;
@@ -586,76 +581,35 @@ __global__ void __launch_bounds__(256) ns_scale_kernel(const NsPrepArgs args) {
   const float den = den_s;
   const int64_t base = static_cast<int64_t>(mat) * G.R * G.C;
   bf16* xo = G.x0 + base;
-  const bool vec = (G.C % 4) == 0 && (!G.transpose || (G.R % 8) == 0);
-  if (vec) {
+  if ((G.C % 4) == 0) {
     const int lx = (threadIdx.x & 15) * 4, ly = threadIdx.x >> 4;  // 16 x 16 threads, 4 columns each
-    float xv[4][4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int r = tr + ly + 16 * i, c = tcx + lx;
-      xv[i][0] = xv[i][1] = xv[i][2] = xv[i][3] = 0.f;
-      if (r < G.R && c < G.C) {
-        const int64_t off = base + static_cast<int64_t>(r) * G.C + c;
-        if (G.src_f32) {
-          const float4 t = *reinterpret_cast<const float4*>(static_cast<const float*>(G.src) + off);
-          xv[i][0] = t.x; xv[i][1] = t.y; xv[i][2] = t.z; xv[i][3] = t.w;
-        } else {
-          const uint2 t = *reinterpret_cast<const uint2*>(static_cast<const bf16*>(G.src) + off);
-          xv[i][0] = __uint_as_float(t.x << 16); xv[i][1] = __uint_as_float(t.x & 0xFFFF0000u);
-          xv[i][2] = __uint_as_float(t.y << 16); xv[i][3] = __uint_as_float(t.y & 0xFFFF0000u);
-        }
+      if (r >= G.R || c >= G.C) continue;
+      const int64_t off = base + static_cast<int64_t>(r) * G.C + c;
+      float x0, x1, x2, x3;
+      if (G.src_f32) {
+        const float4 t = *reinterpret_cast<const float4*>(static_cast<const float*>(G.src) + off);
+        x0 = t.x; x1 = t.y; x2 = t.z; x3 = t.w;
+      } else {
+        const uint2 t = *reinterpret_cast<const uint2*>(static_cast<const bf16*>(G.src) + off);
+        x0 = __uint_as_float(t.x << 16); x1 = __uint_as_float(t.x & 0xFFFF0000u);
+        x2 = __uint_as_float(t.y << 16); x3 = __uint_as_float(t.y & 0xFFFF0000u);
       }
-    }
-    if (!G.transpose) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int r = tr + ly + 16 * i, c = tcx + lx;
-        if (r < G.R && c < G.C)
-          *reinterpret_cast<uint2*>(xo + static_cast<int64_t>(r) * G.C + c) =
-              make_uint2(pack_bf16x2(bf16_round(xv[i][0]) / den, bf16_round(xv[i][1]) / den),
-                         pack_bf16x2(bf16_round(xv[i][2]) / den, bf16_round(xv[i][3]) / den));
-      }
-      return;
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) tile[ly + 16 * i][lx + j] = bf16_round(xv[i][j]) / den;
-    __syncthreads();
-    // output row = source column; a thread writes eight consecutive source rows of one column
-    const int chunk = threadIdx.x & 7;
-#pragma unroll
-    for (int pass = 0; pass < 2; ++pass) {
-      const int cc = (threadIdx.x >> 3) + 32 * pass;
-      const int c = tcx + cc, r = tr + chunk * 8;
-      if (c < G.C && r < G.R) {  // R is a multiple of 8: the eight rows are all valid
-        uint32_t w[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) w[j] = pack_bf16x2(tile[chunk * 8 + 2 * j][cc], tile[chunk * 8 + 2 * j + 1][cc]);
-        *reinterpret_cast<uint4*>(xo + static_cast<int64_t>(c) * G.R + r) = make_uint4(w[0], w[1], w[2], w[3]);
-      }
+      *reinterpret_cast<uint2*>(xo + static_cast<int64_t>(r) * G.C + c) =
+          make_uint2(pack_bf16x2(bf16_round(x0) / den, bf16_round(x1) / den),
+                     pack_bf16x2(bf16_round(x2) / den, bf16_round(x3) / den));
     }
     return;
   }
   const int lx = threadIdx.x & 63, ly = threadIdx.x >> 6;  // 64 x 4
-  float xv[16];
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
     const int r = tr + ly + 4 * i, c = tcx + lx;
-    xv[i] = (r < G.R && c < G.C) ? load_scalar(G.src, G.src_f32, base + static_cast<int64_t>(r) * G.C + c) : 0.f;
-  }
-#pragma unroll
-  for (int i = 0; i < 16; ++i) tile[ly + 4 * i][lx] = bf16_round(xv[i]) / den;
-  __syncthreads();
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const int rr = ly + 4 * i;
-    if (G.transpose) {
-      const int c = tcx + rr, r = tr + lx;  // output row = source column
-      if (c < G.C && r < G.R) xo[static_cast<int64_t>(c) * G.R + r] = __float2bfloat16_rn(tile[lx][rr]);
-    } else {
-      const int r = tr + rr, c = tcx + lx;
-      if (r < G.R && c < G.C) xo[static_cast<int64_t>(r) * G.C + c] = __float2bfloat16_rn(tile[rr][lx]);
+    if (r < G.R && c < G.C) {
+      const int64_t off = static_cast<int64_t>(r) * G.C + c;
+      xo[off] = __float2bfloat16_rn(bf16_round(load_scalar(G.src, G.src_f32, base + off)) / den);
     }
   }
 }

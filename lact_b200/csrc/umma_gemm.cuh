@@ -40,10 +40,6 @@ struct GemmProblem {
   OperandInfo ai[Op::NA];
   OperandInfo bi[Op::NB];
   OutInfo oi[Op::NOUT > 0 ? Op::NOUT : 1];
-  // optional residual operand of the epilogue (ops with kResidualTma): a bf16 matrix addressed
-  // like out[0]; its tile is TMA-loaded into the staging tile ahead of the epilogue
-  CUtensorMap res;
-  int32_t res_enabled;
   int32_t M, N, K, batch;
   typename Op::Epi ep;
 };
@@ -118,16 +114,14 @@ struct GemmCtx {
   uint32_t smem_base;     // 1024-byte aligned start of the stage ring
   uint32_t stage_stride;  // bytes between ring stages (>= the op's stage bytes)
   uint32_t staging;       // 1024-byte aligned start of the output staging tiles
-  uint64_t *full_bar, *empty_bar, *acc_full_bar, *acc_empty_bar, *res_bar;
+  uint64_t *full_bar, *empty_bar, *acc_full_bar, *acc_empty_bar;
   volatile uint32_t* abort_flag;
-  uint32_t res_count = 0;  // residual tiles consumed so far (epilogue threads)
   uint32_t tmem_base;
   uint32_t it = 0, tcount = 0;
   // dataflow mode (multi-phase kernels whose phases are ordered by completion counters, see FlowDeps)
   uint32_t rot = 0;              // tiles handed out by earlier phases, modulo the grid size
   uint32_t ptile = 0;            // tiles whose dependency the producer thread has verified
   uint32_t* pend = nullptr;      // completion counter of the last stored, not yet signalled tile (storing thread)
-  bool res_deferred = false;     // the current tile's residual could not be prefetched (storing thread)
   uint32_t* dep_ok = nullptr;    // shared-memory word: the producer's `ptile`, read by the storing thread
   // optional diagnostics (CTA 0 only): per phase < 6 and tile < 4, globaltimer stamps of
   // {loads issued, MMAs committed, epilogue started, epilogue finished} at trace[40 + 16*phase + 4*tile + k]
@@ -271,25 +265,16 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
         const TileCoord tc = coord(tile);
         const GemmProblem<Op>& P = probs[tc.prob];
         const int num_kb = (P.K + kBK - 1) / kBK;
-#ifdef LACT_TRACE_LOADS
-        if (cx.trace != nullptr && blockIdx.x == 0 && cx.phase == 2 && tile_i >= 1 && tile_i <= 2) cx.trace[240 + 2 * (tile_i - 1)] = globaltimer_ns();
-#endif
         if constexpr (Deps::kOn) {
           if (!flow_wait_verified(cx, cx.ptile++)) { failed = true; break; }  // the scout warp checked this tile
           asm volatile("fence.proxy.async;" ::: "memory");
         }
-#ifdef LACT_TRACE_LOADS
-        if (cx.trace != nullptr && blockIdx.x == 0 && cx.phase == 2 && tile_i >= 1 && tile_i <= 2) cx.trace[241 + 2 * (tile_i - 1)] = globaltimer_ns();
-#endif
         for (int kb = 0; kb < num_kb; ++kb, ++cx.it) {
           const int s = cx.it % RING;
           const uint32_t ph = (cx.it / RING) & 1;
           if (!mbar_wait(&cx.empty_bar[s], ph ^ 1, cx.abort_flag)) { failed = true; break; }
           if (kb == num_kb - 1) cx.stamp(tile_i, 0);
           mbar_expect_tx(&cx.full_bar[s], kStageBytes);
-#ifdef LACT_TRACE_LOADS
-          if (cx.trace != nullptr && blockIdx.x == 0 && cx.phase == 2 && tile_i >= 1 && tile_i <= 2 && kb < 8) cx.trace[200 + 20 * (tile_i - 1) + 2 * kb] = globaltimer_ns();
-#endif
           const uint32_t st = cx.smem_base + s * cx.stage_stride;
           const int kc = kb * kBK;
 #pragma unroll
@@ -313,18 +298,12 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
         const int num_kb = (P.K + kBK - 1) / kBK;
         const uint32_t as = cx.tcount & 1, aph = (cx.tcount >> 1) & 1;
         if (!mbar_wait(&cx.acc_empty_bar[as], aph ^ 1, cx.abort_flag)) { failed = true; break; }
-#ifdef LACT_TRACE_LOADS
-        if (cx.trace != nullptr && blockIdx.x == 0 && cx.phase == 2 && tile_i >= 1 && tile_i <= 2) cx.trace[250 + (tile_i - 1)] = globaltimer_ns();
-#endif
         tc_fence_after();
         const uint32_t acc_base = cx.tmem_base + as * kAccCols;
         for (int kb = 0; kb < num_kb; ++kb, ++cx.it) {
           const int s = cx.it % RING;
           const uint32_t ph = (cx.it / RING) & 1;
           if (!mbar_wait(&cx.full_bar[s], ph, cx.abort_flag)) { failed = true; break; }
-#ifdef LACT_TRACE_LOADS
-          if (cx.trace != nullptr && blockIdx.x == 0 && cx.phase == 2 && tile_i >= 1 && tile_i <= 2 && kb < 8) cx.trace[201 + 20 * (tile_i - 1) + 2 * kb] = globaltimer_ns();
-#endif
           tc_fence_after();
           const uint32_t st = cx.smem_base + s * cx.stage_stride;
 #pragma unroll
@@ -383,44 +362,9 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
       const int t = tile_at(r);
       return t < total_tiles ? t : -1;
     };
-    // Residual tile of `tile` -> the staging buffer `dst` (elected thread).  Every TMA store that
-    // read `dst` must have finished reading (the caller waits for that).
-    auto issue_residual = [&](int tile, uint32_t dst) {
-      if constexpr (Op::kResidualTma) {
-        if (tile < 0) return;
-        const TileCoord t2 = coord(tile);
-        const GemmProblem<Op>& P2 = probs[t2.prob];
-        if (!P2.res_enabled) return;
-        int panels = 0;
-        for (int pnl = 0; pnl < BT / 64; ++pnl)
-          if (t2.n0 + pnl * 64 < P2.N) ++panels;
-        mbar_expect_tx(cx.res_bar, panels * (kBM * 128));
-        for (int pnl = 0; pnl < panels; ++pnl)
-          tma_load_3d(dst + pnl * (kBM * 128), &P2.res, cx.res_bar, P2.oi[0].col_off + t2.n0 + pnl * 64,
-                      P2.oi[0].row_off + t2.m0, P2.oi[0].batch_off + t2.batch);
-      }
-    };
     if constexpr (Deps::kOn) {
       // a CTA without a tile in this phase must not sit on an unpublished tile of the previous one
       if (elected && tile_of_round(0) < 0) flow_flush(cx);
-    }
-    if (elected && Op::kResidualTma) {
-      bulk_wait_read_all();
-      if constexpr (Deps::kOn) {
-        // the first tile's residual is written by an earlier phase: issue it once the producer
-        // thread has verified that tile's dependency (never block with an unpublished tile)
-        if (tile_of_round(0) >= 0 && probs[coord(tile_of_round(0)).prob].res_enabled) {
-          if (ld_acquire_cta_shared_u32(cx.dep_ok) <= cx.tcount) flow_flush(cx);
-          if (flow_wait_verified(cx, cx.tcount)) {
-            asm volatile("fence.proxy.async;" ::: "memory");
-            issue_residual(tile_of_round(0), stg_of(cx.tcount));
-          } else {
-            *cx.abort_flag = 1;
-          }
-        }
-      } else {
-        issue_residual(tile_of_round(0), stg_of(cx.tcount));
-      }
     }
     for (int tile_i = 0; tile_i < rounds; ++tile_i) {
       const int tile = tile_of_round(tile_i);
@@ -429,8 +373,6 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
       const GemmProblem<Op>& P = probs[tc.prob];
       typename Op::Epi ep = P.ep;
       patch(ep, tc.prob);
-      bool has_res = false;
-      if constexpr (Op::kResidualTma) has_res = P.res_enabled != 0;
       const uint32_t stg = stg_of(cx.tcount);
       const uint32_t as = cx.tcount & 1, aph = (cx.tcount >> 1) & 1;
       const int row = tc.m0 + row_local;
@@ -438,27 +380,11 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
       typename Op::Prefetch pf;
       Op::prefetch(ep, tc.batch, row, tc.n0, half, P.M, P.N, pf);
       if constexpr (Deps::kOn) {
-        if (elected) {
-          // idle anyway: publish the previous tile now, so that no CTA (this one included) waits for it
-          if (!mbar_try_wait(&cx.acc_full_bar[as], aph)) flow_flush(cx);
-          if (cx.res_deferred) {
-            flow_flush(cx);
-            if (flow_wait_verified(cx, cx.tcount)) {
-              asm volatile("fence.proxy.async;" ::: "memory");
-              issue_residual(tile, stg);
-            } else {
-              *cx.abort_flag = 1;
-            }
-            cx.res_deferred = false;
-          }
-        }
+        // idle anyway: publish the previous tile now, so that no CTA (this one included) waits for it
+        if (elected && !mbar_try_wait(&cx.acc_full_bar[as], aph)) flow_flush(cx);
       }
       bool got = mbar_wait(&cx.acc_full_bar[as], aph, cx.abort_flag);
       tc_fence_after();
-      if (has_res) {
-        got = mbar_wait(cx.res_bar, cx.res_count & 1, cx.abort_flag) && got;
-        ++cx.res_count;
-      }
       if (elected) cx.stamp(tile_i, 2);
       const uint32_t acc_base = cx.tmem_base + as * kAccCols + (static_cast<uint32_t>(quarter * 32) << 16);
       if constexpr (NOUT > 0) {
@@ -468,24 +394,8 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
         // stores that read this tile's staging buffer must have finished reading it: with two
         // buffers that is every group but the last one committed (the previous tile's final store)
         if (elected) {
-          if (kDoubleStg && !Op::kResidualTma) bulk_wait_read_but_last();
+          if (kDoubleStg) bulk_wait_read_but_last();
           else bulk_wait_read_all();
-          // double-buffered: the other buffer is free now, fetch the next tile's residual into it
-          if (kDoubleStg && got) {
-            if constexpr (Deps::kOn) {
-              const int nxt = tile_of_round(tile_i + 1);
-              if (nxt >= 0 && probs[coord(nxt).prob].res_enabled) {
-                if (ld_acquire_cta_shared_u32(cx.dep_ok) > cx.tcount + 1) {
-                  asm volatile("fence.proxy.async;" ::: "memory");
-                  issue_residual(nxt, stg_of(cx.tcount + 1));
-                } else {
-                  cx.res_deferred = true;  // fetched at the start of that tile
-                }
-              }
-            } else {
-              issue_residual(tile_of_round(tile_i + 1), stg_of(cx.tcount + 1));
-            }
-          }
         }
         named_barrier_sync(1, kEpiThreads);
         if (cx.abort_flag[1] != 0) { failed = true; break; }
@@ -507,19 +417,7 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
           float ov[NSTG > 0 ? NSTG : 1][32];
           const uint32_t rowaddr = (c >> 6) * (kBM * 128) + row_local * 128;
           const uint32_t unit0 = (c & 63) >> 3;
-          if constexpr (Op::kResidualTma) {
-            if (has_res) {  // this thread's residual segment sits where its result will go
-#pragma unroll
-              for (int g = 0; g < 4; ++g) {
-                const uint32_t addr = stg + rowaddr + (((unit0 + g) ^ (row_local & 7)) << 4);
-                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                             : "=r"(pf.r[g].x), "=r"(pf.r[g].y), "=r"(pf.r[g].z), "=r"(pf.r[g].w)
-                             : "r"(addr)
-                             : "memory");
-              }
-            }
-          }
-          Op::epilogue_staged(ep, tc.batch, row, tc.n0 + c, P.M, P.N, v, ov, pf, has_res);
+          Op::epilogue_staged(ep, tc.batch, row, tc.n0 + c, P.M, P.N, v, ov, pf);
 #pragma unroll
           for (int o = 0; o < NSTG; ++o) {
             const uint32_t base = stg + o * (kBM * BT * 2) + rowaddr;
@@ -607,11 +505,6 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
             }
           }
         }
-        if (!kDoubleStg && elected && Op::kResidualTma) {
-          static_assert(!Deps::kOn || kDoubleStg || !Op::kResidualTma, "dataflow mode needs double-buffered staging for residual tiles");
-          bulk_wait_read_all();
-          issue_residual(tile_of_round(tile_i + 1), stg);
-        }
         if constexpr (Deps::kOn) {
           if (elected) cx.pend = deps.counter[tc.prob] + tc.batch;  // published by a later flow_flush
         }
@@ -639,8 +532,7 @@ __device__ __forceinline__ void gemm_setup(GemmCtx& cx, uint8_t* smem_raw, int r
   cx.empty_bar = cx.full_bar + ring;
   cx.acc_full_bar = cx.empty_bar + ring;    // [2]
   cx.acc_empty_bar = cx.acc_full_bar + 2;   // [2]
-  cx.res_bar = cx.acc_empty_bar + 2;        // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(cx.res_bar + 1);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(cx.acc_empty_bar + 2);
   cx.abort_flag = tmem_slot + 1;  // [2]
   cx.dep_ok = tmem_slot + 3;
   if (threadIdx.x == 0) {
@@ -652,7 +544,6 @@ __device__ __forceinline__ void gemm_setup(GemmCtx& cx, uint8_t* smem_raw, int r
       mbar_init(&cx.acc_full_bar[s], 1);
       mbar_init(&cx.acc_empty_bar[s], kEpiWarps);
     }
-    mbar_init(cx.res_bar, 1);
     cx.abort_flag[0] = 0;
     cx.abort_flag[1] = 0;
     *cx.dep_ok = 0;
