@@ -33,6 +33,9 @@ import torch  # noqa: E402
 BF16 = torch.bfloat16
 CFG = dict(batch=8, heads=4, L=32768, D=384, H=384, chunk=2048, ns_steps=5)
 METRIC = "ttt_layer_fwd_tokens_per_s_760M_shape"
+# DRAM bytes (read + write) of ONE Newton-Schulz launch from an ncu capture of a 16-head case
+# (profiles/ns_fused_kernel_small_case.md: 14.3 MB + 34.9 MB); grows with the matrices per launch.
+NCU_DRAM_BYTES_NS_FUSED_16_HEADS = 49.2e6
 E2E_SLABS = 8  # the end-to-end arm streams the batch through the device in this many slabs
 
 
@@ -354,7 +357,9 @@ def main():
     flops = algorithmic_flops(B, L, D, H, C, CFG["ns_steps"])
     step_tflops = flops / (ms_per_step * 1e-3) / 1e12
     roofline = {"bound": "tensor", "kernel": top, "achieved": achieved, "peak": peaks["bf16_sustained"],
-                "unit": "TFLOP/s", "frac": achieved / peaks["bf16_sustained"], "traffic": None,
+                "unit": "TFLOP/s", "frac": achieved / peaks["bf16_sustained"],
+                "traffic": NCU_DRAM_BYTES_NS_FUSED_16_HEADS * B / 16.0 if top == "ns_fused" else None,
+                "traffic_note": "DRAM read+write bytes per launch, ncu capture at 16 heads scaled by heads per launch",
                 "peak_source": peaks["source"] + " (sustained cuBLAS bf16)",
                 "kernel_share_of_step": prof[top][0] / total_prof,
                 "classes": {k: {"ms_per_launch": v[0] / v[1], "launches_per_step": v[1] / prof_steps,

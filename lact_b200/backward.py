@@ -171,35 +171,30 @@ def ns_backward(saved, dU):
     return dX0 / den - Gf * dot / (den * den * nrm.clamp_min(1e-30))
 
 
-class ScanFunction(torch.autograd.Function):
-    """Differentiable wrapper of the chunk recurrence (LLM layout).  `opts` is the keyword
-    dictionary of `lact_b200.ops.scan`."""
+def scan_forward_saving(opts, steps, w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum):
+    """Forward of the recurrence that also records, per update, the weights it computed with and
+    its gradient after momentum (what `scan_backward` needs).  Returns (o, wf0, wf1, wf2, dump)."""
+    from . import ops
+    if opts.get("prenorm") and opts.get("overwrite_quirk"):
+        raise NotImplementedError("no reference recurrence combines pre-norm with the bidirectional overwrite")
+    n_upd = sum(1 for s in steps if s[0] == P.UPDATE)
+    B, Ltok, D = k.shape
+    H = w0.shape[1]
+    per = 2 * (B * 2 * H * D + B * D * H)
+    dump = torch.empty(max(n_upd, 1), per, dtype=torch.float32, device=q.device)
+    with torch.no_grad():
+        res = ops.scan_eager(w0, w1, w2, q, k, v, lr0, lr1, lr2, steps, momentum=momentum, return_state=True,
+                             _state_dump=dump, **{k_: v_ for k_, v_ in opts.items() if k_ not in ("return_state", "_detach_norms")})
+    o, wf0, wf1, wf2 = res[:4]
+    return o, wf0, wf1, wf2, dump
 
-    @staticmethod
-    def forward(ctx, opts, steps, w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum):
-        from . import ops
-        if opts.get("prenorm") and opts.get("overwrite_quirk"):
-            raise NotImplementedError("no reference recurrence combines pre-norm with the bidirectional overwrite")
-        n_upd = sum(1 for s in steps if s[0] == P.UPDATE)
-        B, Ltok, D = k.shape
-        H = w0.shape[1]
-        per = 2 * (B * 2 * H * D + B * D * H)
-        dump = torch.empty(max(n_upd, 1), per, dtype=torch.float32, device=q.device)
-        with torch.no_grad():
-            res = ops.scan(w0, w1, w2, q, k, v, lr0, lr1, lr2, steps, momentum=momentum, return_state=True,
-                           _state_dump=dump, **{k_: v_ for k_, v_ in opts.items() if k_ != "return_state"})
-        o, wf0, wf1, wf2 = res[:4]
-        ctx.opts, ctx.steps, ctx.n_upd = dict(opts), list(steps), n_upd
-        ctx.save_for_backward(w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum if momentum is not None else q.new_zeros(1),
-                              dump, wf0, wf1, wf2)
-        ctx.has_momentum = momentum is not None
-        ctx.mark_non_differentiable(wf0, wf1, wf2)
-        return o, wf0, wf1, wf2
 
-    @staticmethod
-    def backward(ctx, dO, *_unused):
-        w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, dump, wf0, wf1, wf2 = ctx.saved_tensors
-        opts, steps, n_upd = ctx.opts, ctx.steps, ctx.n_upd
+def scan_backward(opts, steps, w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, dump, wf0, wf1, wf2, dO):
+    """Reverse sweep over the step program.  `momentum` may be None.  Returns the gradients of
+    (w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum) (the last one None without momentum)."""
+    has_momentum = momentum is not None
+    n_upd = sum(1 for s_ in steps if s_[0] == P.UPDATE)
+    if True:
         dev = q.device
         B, Ltok, D = k.shape
         H = w0.shape[1]
@@ -209,7 +204,7 @@ class ScanFunction(torch.autograd.Function):
         f32 = torch.float32
         vec = lambda t: (t[..., 0] if t.dim() == 3 else t).contiguous()
         lr0v, lr1v, lr2v = vec(lr0), vec(lr1), vec(lr2)
-        momv = vec(momentum).float() if ctx.has_momentum else None
+        momv = vec(momentum).float() if has_momentum else None
         W0_02 = torch.cat([w0, w2], dim=1).float().contiguous()
         W0_1 = w1.float().contiguous()
         n0_02 = W0_02.norm(dim=2).contiguous()
@@ -262,7 +257,7 @@ class ScanFunction(torch.autograd.Function):
         dk = torch.zeros_like(k, dtype=BF16)
         dv = torch.zeros_like(v, dtype=BF16)
         dlr = [torch.zeros(B, Ltok, dtype=f32, device=dev) for _ in range(3)]
-        dmom = torch.zeros(B, Ltok, dtype=f32, device=dev) if ctx.has_momentum else None
+        dmom = torch.zeros(B, Ltok, dtype=f32, device=dev) if has_momentum else None
         dO = dO.to(BF16)
 
         cnt = n_upd
@@ -324,7 +319,7 @@ class ScanFunction(torch.autograd.Function):
                 dW02, dW1 = torch.zeros_like(dWn02), torch.zeros_like(dWn1)
             else:
                 dW02, dW1 = dWn02, dWn1
-            if ctx.has_momentum:
+            if has_momentum:
                 beta = momv[:, s:e].mean(dim=1)  # [B]
                 if u > 0:
                     Mp02, Mp1 = grad_state(u - 1)
@@ -350,9 +345,9 @@ class ScanFunction(torch.autograd.Function):
             dW1 = dW1 + dn1.unsqueeze(-1) * W0_1 / n0_1.clamp_min(1e-30).unsqueeze(-1)
         dw0, dw2 = dW02[:, :H].to(w0.dtype), dW02[:, H:].to(w2.dtype)
         shape = lambda g, ref: g.view(ref.shape).to(ref.dtype) if ref.dim() == 3 else g.to(ref.dtype)
-        grads = (None, None, dw0, dW1.to(w1.dtype), dw2, dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype),
+        grads = (dw0, dW1.to(w1.dtype), dw2, dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype),
                  shape(dlr[0].unsqueeze(-1) if lr0.dim() == 3 else dlr[0], lr0),
                  shape(dlr[1].unsqueeze(-1) if lr1.dim() == 3 else dlr[1], lr1),
                  shape(dlr[2].unsqueeze(-1) if lr2.dim() == 3 else dlr[2], lr2),
-                 shape(dmom.unsqueeze(-1) if momentum.dim() == 3 else dmom, momentum) if ctx.has_momentum else None)
+                 shape(dmom.unsqueeze(-1) if momentum.dim() == 3 else dmom, momentum) if has_momentum else None)
         return grads

@@ -147,7 +147,9 @@ def scan_f32(w0, w1, w2, q, k, v, lr0, lr1, lr2, steps: Sequence[P.Step], *, out
     res = [o]
     if return_state:
         a02, a1 = weights()
-        res += [a02[:, :H].contiguous(), a1.clone(), a02[:, H:].contiguous()]
+        res += [a02[:, :H].clone(memory_format=torch.contiguous_format), a1.clone(),
+                a02[:, H:].clone(memory_format=torch.contiguous_format)]
     if return_momentum:
-        res += [m02[:, :H].contiguous(), m1.clone(), m02[:, H:].contiguous()]
+        res += [m02[:, :H].clone(memory_format=torch.contiguous_format), m1.clone(),
+                m02[:, H:].clone(memory_format=torch.contiguous_format)]
     return res[0] if len(res) == 1 else tuple(res)

@@ -70,15 +70,12 @@ def _weight(t: torch.Tensor, shape: tuple, name: str) -> torch.Tensor:
     return t.contiguous()
 
 
-@_no_trace
-def scan(w0, w1, w2, q, k, v, lr0, lr1, lr2, steps: Sequence[P.Step], *, out_len: Optional[int] = None,
-         momentum=None, m_init=None, use_muon=False, ns_steps=5, ns_const_coeffs=False, ns_concat=False,
-         ns_gram_right=False, renorm=L.RENORM_EPS_OUTSIDE, prenorm=False, prenorm_bf16=False, overwrite_quirk=False,
-         w_scale=1.0, return_state=False, return_momentum=False, _detach_norms=False, _state_dump=None):
-    """General chunk recurrence in the LLM layout (w0, w2: [B,H,D]; w1: [B,D,H]); see
-    `lact_scan_fwd` in include/lact_b200.h.  Returns o, and optionally the final fast weights
-    and momentum state (fp32).  When gradients are enabled and an input requires grad, the call
-    goes through `backward.ScanFunction` (training backward, see that module for what it covers)."""
+def scan_eager(w0, w1, w2, q, k, v, lr0, lr1, lr2, steps: Sequence[P.Step], *, out_len: Optional[int] = None,
+               momentum=None, m_init=None, use_muon=False, ns_steps=5, ns_const_coeffs=False, ns_concat=False,
+               ns_gram_right=False, renorm=L.RENORM_EPS_OUTSIDE, prenorm=False, prenorm_bf16=False,
+               overwrite_quirk=False, w_scale=1.0, return_state=False, return_momentum=False, _state_dump=None):
+    """Forward of the general chunk recurrence, straight through the C ABI (`lact_scan_fwd`), no
+    autograd.  `scan` is the public, differentiable and compilable entry point."""
     dev = _need_cuda(w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum)
     if q.dtype == k.dtype == v.dtype == torch.float32:
         return _scan_f32(dev, w0, w1, w2, q, k, v, lr0, lr1, lr2, steps, out_len, momentum, m_init,
@@ -86,17 +83,6 @@ def scan(w0, w1, w2, q, k, v, lr0, lr1, lr2, steps: Sequence[P.Step], *, out_len
                               ns_concat=ns_concat, ns_gram_right=ns_gram_right, renorm=renorm, prenorm=prenorm,
                               prenorm_bf16=prenorm_bf16, overwrite_quirk=overwrite_quirk, w_scale=w_scale,
                               return_state=return_state, return_momentum=return_momentum), _state_dump)
-    if _state_dump is None and torch.is_grad_enabled() and any(
-            torch.is_tensor(t) and t.requires_grad for t in (w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum)):
-        from .backward import ScanFunction
-        if m_init is not None or return_momentum:
-            raise NotImplementedError("gradients through a momentum state passed in / returned are not implemented")
-        opts = dict(out_len=out_len, use_muon=use_muon, ns_steps=ns_steps, ns_const_coeffs=ns_const_coeffs,
-                    ns_concat=ns_concat, ns_gram_right=ns_gram_right, renorm=renorm, prenorm=prenorm,
-                    prenorm_bf16=prenorm_bf16, overwrite_quirk=overwrite_quirk, w_scale=w_scale,
-                    _detach_norms=_detach_norms)
-        o, a, b, c = ScanFunction.apply(opts, list(steps), w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum)
-        return (o, a, b, c) if return_state else o
     q, k, v = _act(q, "q"), _act(k, "k"), _act(v, "v")
     B, Ltok, D = k.shape
     H = w0.shape[1]
@@ -184,9 +170,6 @@ def _scan_f32(dev, w0, w1, w2, q, k, v, lr0, lr1, lr2, steps, out_len, momentum,
     from .fp32_mode import scan_f32
     if state_dump is not None:
         raise NotImplementedError("the per-update state dump is a bf16-mode feature")
-    if torch.is_grad_enabled() and any(torch.is_tensor(t) and t.requires_grad
-                                       for t in (w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum)):
-        raise NotImplementedError("fp32 mode is forward only; the training backward runs on bf16 activations")
     for t, name in ((q, "q"), (k, "k"), (v, "v")):
         if t.dim() != 3:
             raise ValueError(f"{name} must be [b, l, d]")
@@ -200,6 +183,149 @@ def _scan_f32(dev, w0, w1, w2, q, k, v, lr0, lr1, lr2, steps, out_len, momentum,
         momentum = _vec(momentum, B, Ltok, "momentum")
     return scan_f32(w0, w1, w2, q, k, v, lr0, lr1, lr2, steps, out_len=out_len, momentum=momentum, m_init=m_init,
                     **opts)
+
+
+# ----------------------------------------------------------------------------------------------
+# registered operators: the recurrence as `torch.ops.lact_b200.scan_fwd` / `scan_bwd`
+# ----------------------------------------------------------------------------------------------
+# The reference wraps its functions in @torch.compile.  TorchDynamo cannot trace ctypes calls, so
+# the recurrence is registered as a custom operator with a fake (shape-only) implementation and
+# an autograd formula: a compiled caller sees one opaque node, without a graph break.
+# cfg = [use_muon, ns_steps, ns_const_coeffs, ns_concat, ns_gram_right, renorm, prenorm,
+#        prenorm_bf16, overwrite_quirk, detach_norms, out_len (-1: all tokens), return_momentum, save]
+_CFG_KEYS = ("use_muon", "ns_steps", "ns_const_coeffs", "ns_concat", "ns_gram_right", "renorm", "prenorm",
+             "prenorm_bf16", "overwrite_quirk")
+
+
+def _opts_of(cfg: Sequence[int], w_scale: float) -> dict:
+    d = {k_: int(cfg[i]) for i, k_ in enumerate(_CFG_KEYS)}
+    for k_ in ("use_muon", "ns_const_coeffs", "ns_concat", "ns_gram_right", "prenorm", "prenorm_bf16", "overwrite_quirk"):
+        d[k_] = bool(d[k_])
+    d["w_scale"] = float(w_scale)
+    return d
+
+
+def _steps_of(flat: Sequence[int]) -> List[P.Step]:
+    return [tuple(int(x) for x in flat[i:i + 4]) for i in range(0, len(flat), 4)]
+
+
+@torch.library.custom_op("lact_b200::scan_fwd", mutates_args=(), device_types="cuda")
+def _scan_fwd_op(w0: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, q: torch.Tensor, k: torch.Tensor,
+                 v: torch.Tensor, lr0: torch.Tensor, lr1: torch.Tensor, lr2: torch.Tensor,
+                 momentum: Optional[torch.Tensor], m0: Optional[torch.Tensor], m1: Optional[torch.Tensor],
+                 m2: Optional[torch.Tensor], steps: List[int], cfg: List[int], w_scale: float) -> List[torch.Tensor]:
+    """[o, w0', w1', w2'] (+ [m0', m1', m2'] if cfg[11]) (+ [saved state] if cfg[12])."""
+    opts, st = _opts_of(cfg, w_scale), _steps_of(steps)
+    out_len = None if cfg[10] < 0 else int(cfg[10])
+    if cfg[12]:
+        from .backward import scan_forward_saving
+        opts["out_len"] = out_len
+        o, a, b, c, dump = scan_forward_saving(opts, st, w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum)
+        return [o, a, b, c, dump]
+    m_init = (m0, m1, m2) if m0 is not None else None
+    res = scan_eager(w0, w1, w2, q, k, v, lr0, lr1, lr2, st, out_len=out_len, momentum=momentum, m_init=m_init,
+                     return_state=True, return_momentum=bool(cfg[11]), **opts)
+    return list(res)
+
+
+@_scan_fwd_op.register_fake
+def _scan_fwd_fake(w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, m0, m1, m2, steps, cfg, w_scale):
+    B, Ltok, D = k.shape
+    H = w0.shape[1]
+    out_len = Ltok if cfg[10] < 0 else int(cfg[10])
+    f32 = torch.float32
+    outs = [q.new_empty((B, out_len, D)), q.new_empty((B, H, D), dtype=f32), q.new_empty((B, D, H), dtype=f32),
+            q.new_empty((B, H, D), dtype=f32)]
+    if cfg[11]:
+        outs += [q.new_empty((B, H, D), dtype=f32), q.new_empty((B, D, H), dtype=f32), q.new_empty((B, H, D), dtype=f32)]
+    if cfg[12]:
+        n_upd = sum(1 for i in range(0, len(steps), 4) if steps[i] == P.UPDATE)
+        outs.append(q.new_empty((max(n_upd, 1), 2 * (B * 2 * H * D + B * D * H)), dtype=f32))
+    return outs
+
+
+@torch.library.custom_op("lact_b200::scan_bwd", mutates_args=(), device_types="cuda")
+def _scan_bwd_op(w0: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, q: torch.Tensor, k: torch.Tensor,
+                 v: torch.Tensor, lr0: torch.Tensor, lr1: torch.Tensor, lr2: torch.Tensor,
+                 momentum: Optional[torch.Tensor], dump: torch.Tensor, wf0: torch.Tensor, wf1: torch.Tensor,
+                 wf2: torch.Tensor, dO: torch.Tensor, steps: List[int], cfg: List[int],
+                 w_scale: float) -> List[torch.Tensor]:
+    """Gradients of (w0, w1, w2, q, k, v, lr0, lr1, lr2[, momentum])."""
+    from .backward import scan_backward
+    opts = _opts_of(cfg, w_scale)
+    opts["_detach_norms"] = bool(cfg[9])
+    g = scan_backward(opts, _steps_of(steps), w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, dump, wf0, wf1, wf2,
+                      dO.contiguous())
+    # fresh, non-overlapping tensors (the w0 / w2 gradients are two halves of one buffer)
+    return [t.clone(memory_format=torch.contiguous_format) for t in g if t is not None]
+
+
+@_scan_bwd_op.register_fake
+def _scan_bwd_fake(w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, dump, wf0, wf1, wf2, dO, steps, cfg, w_scale):
+    outs = [torch.empty_like(t) for t in (w0, w1, w2, q, k, v, lr0, lr1, lr2)]
+    if momentum is not None:
+        outs.append(torch.empty_like(momentum))
+    return outs
+
+
+def _scan_setup_context(ctx, inputs, output):
+    w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, m0, m1, m2, steps, cfg, w_scale = inputs
+    ctx.steps, ctx.cfg, ctx.w_scale, ctx.has_momentum, ctx.saved = list(steps), list(cfg), float(w_scale), momentum is not None, bool(cfg[12])
+    if cfg[12]:
+        keep = [w0, w1, w2, q, k, v, lr0, lr1, lr2] + ([momentum] if momentum is not None else []) + \
+               [output[4], output[1], output[2], output[3]]
+        ctx.save_for_backward(*keep)
+
+
+def _scan_autograd(ctx, grads):
+    if not ctx.saved:
+        raise RuntimeError("lact_b200::scan_fwd was run without saving state for backward")
+    t = list(ctx.saved_tensors)
+    ins, rest = t[:9], t[9:]
+    momentum = rest.pop(0) if ctx.has_momentum else None
+    dump, wf0, wf1, wf2 = rest
+    dO = grads[0]
+    if dO is None:
+        q, k = ins[3], ins[4]
+        dO = q.new_zeros((q.shape[0], ctx.cfg[10] if ctx.cfg[10] >= 0 else k.shape[1], q.shape[2]))
+    g = torch.ops.lact_b200.scan_bwd(*ins, momentum, dump, wf0, wf1, wf2, dO, ctx.steps, ctx.cfg, ctx.w_scale)
+    dmom = g[9] if ctx.has_momentum else None
+    return (*g[:9], dmom, None, None, None, None, None, None)
+
+
+_scan_fwd_op.register_autograd(_scan_autograd, setup_context=_scan_setup_context)
+
+
+def scan(w0, w1, w2, q, k, v, lr0, lr1, lr2, steps: Sequence[P.Step], *, out_len: Optional[int] = None,
+         momentum=None, m_init=None, use_muon=False, ns_steps=5, ns_const_coeffs=False, ns_concat=False,
+         ns_gram_right=False, renorm=L.RENORM_EPS_OUTSIDE, prenorm=False, prenorm_bf16=False, overwrite_quirk=False,
+         w_scale=1.0, return_state=False, return_momentum=False, _detach_norms=False):
+    """General chunk recurrence in the LLM layout (w0, w2: [B,H,D]; w1: [B,D,H]); see
+    `lact_scan_fwd` in include/lact_b200.h.  Returns o, and optionally the final fast weights
+    and momentum state (fp32).  Runs as the registered operator `lact_b200::scan_fwd`; when
+    gradients are enabled and an input requires grad, its autograd formula (`backward.py`) applies."""
+    tensors = (w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum)
+    save = torch.is_grad_enabled() and any(torch.is_tensor(t) and t.requires_grad for t in tensors)
+    if save:
+        if m_init is not None or return_momentum:
+            raise NotImplementedError("gradients through a momentum state passed in / returned are not implemented")
+        if q.dtype == torch.float32:
+            raise NotImplementedError("fp32 mode is forward only; the training backward runs on bf16 activations")
+        if prenorm and overwrite_quirk:
+            raise NotImplementedError("no reference recurrence combines pre-norm with the bidirectional overwrite")
+    cfg = [int(use_muon), int(ns_steps), int(ns_const_coeffs), int(ns_concat), int(ns_gram_right), int(renorm),
+           int(prenorm), int(prenorm_bf16), int(overwrite_quirk), int(_detach_norms),
+           -1 if out_len is None else int(out_len), int(return_momentum), int(save)]
+    flat = [int(x) for s_ in steps for x in s_]
+    m = tuple(m_init) if m_init is not None else (None, None, None)
+    res = torch.ops.lact_b200.scan_fwd(w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, m[0], m[1], m[2], flat, cfg,
+                                       float(w_scale))
+    out = [res[0]]
+    if return_state:
+        out += list(res[1:4])
+    if return_momentum:
+        out += list(res[4:7])
+    return out[0] if len(out) == 1 else tuple(out)
 
 
 # ----------------------------------------------------------------------------------------------

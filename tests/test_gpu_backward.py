@@ -241,3 +241,29 @@ def test_llm_backward_with_muon_first_chunks(lb):
         assert torch.isfinite(a).all(), n
         assert orc.cosine(a, b) >= 0.97, (n, orc.cosine(a, b))
         assert orc.rel_fro(a, b) <= 0.25, (n, orc.rel_fro(a, b))
+
+
+def test_compiled_caller_sees_one_operator(lb):
+    """A caller wrapped in torch.compile (as the reference's layers are) traces through the public
+    function without a graph break (fullgraph=True) and gets the eager results, forward and backward."""
+    from oracle import lact_oracle as orc
+    B, L, D, H, C = 2, 512, 64, 64, 128
+    inp = orc.make_inputs(B, L, D, H, seed=27)
+    for n in ("q", "k", "v"):
+        inp[n] = inp[n].to(BF16)
+    dO = torch.randn(B, L, D, generator=torch.Generator().manual_seed(9)).to(BF16)
+
+    def layer(w0, w1, w2, q, k, v, l0, l1, l2, m):
+        o = lb.postnorm_block_causal_lact_swiglu_fused_kernel_triton(w0, w1, w2, q * 1.0, k, v, l0, l1, l2, chunk_size=C,
+                                                                     use_muon=True, momentum=m)
+        return o * 2.0
+
+    compiled = torch.compile(layer, backend="aot_eager", fullgraph=True)
+    o_e, g_e = _grads_cuda(inp, layer, True, dO)
+    o_c, g_c = _grads_cuda(inp, compiled, True, dO)
+    assert torch.equal(o_e, o_c)
+    for n in list(NAMES) + ["momentum"]:
+        assert torch.equal(g_e[n], g_c[n]), n
+    with torch.no_grad():
+        c = {k: v.cuda() for k, v in inp.items() if torch.is_tensor(v)}
+        assert torch.equal(compiled(*[c[n] for n in NAMES], c["momentum"]), layer(*[c[n] for n in NAMES], c["momentum"]))

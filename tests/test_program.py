@@ -88,3 +88,32 @@ def test_ar_inference_program(L, mini, upd, rep):
 def test_bad_chunk_size():
     with pytest.raises(ValueError):
         P.causal_program(10, 0)
+
+
+def test_registered_operator_shapes_under_fake_tensors():
+    """The recurrence is a registered operator (`lact_b200::scan_fwd`) with a shape-only
+    implementation, so a tracing compiler sees one opaque node: under FakeTensorMode the public
+    functions return tensors of the reference's shapes and dtypes without touching the library."""
+    import torch
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    import lact_b200
+    with FakeTensorMode():
+        B, L, D, H = 2, 520, 64, 128
+        w0 = torch.empty(B, H, D, device="cuda")
+        w1 = torch.empty(B, D, H, device="cuda")
+        q = torch.empty(B, L, D, device="cuda", dtype=torch.bfloat16)
+        lr = torch.empty(B, L, 1, device="cuda")
+        o = lact_b200.postnorm_block_causal_lact_swiglu_fused_kernel_triton(w0, w1, w0, q, q, q, lr, lr, lr, chunk_size=128,
+                                                                            use_muon=True, momentum=lr)
+        assert o.shape == (B, L, D) and o.dtype == torch.bfloat16
+        res = lact_b200.ar_fast_weight_swish_glu_weight_norm_mini_batch_inference_with_momentum(
+            w0, w1, w0, q, q, q, lr, lr, lr, 1.0, mini_batch_size=260, do_update=True, use_moun=True, num_moun_iters=5,
+            fw_momentum=lr, use_momentum=True)
+        assert len(res) == 7 and res[1].shape == (B, H, D) and res[5].shape == (B, D, H) and res[4].dtype == torch.float32
+        t = lambda w: w.transpose(1, 2)
+        o2, a, b, c = lact_b200.fast_weight_swish_glu_weight_norm_mini_batch_apply(
+            t(w0), t(w1), t(w0), q, q, q, lr, lr, lr, [lact_b200.TTTOperator(0, 400, True, False),
+                                                         lact_b200.TTTOperator(400, 520, False, True)], muon_update_steps=5)
+        assert o2.shape == (B, 120, D) and a.shape == (B, D, H) and b.shape == (B, H, D)
+        o3 = lact_b200.bidirectional_lact_swiglu(w0, w1, w0, q.float(), q.float(), q.float(), lr, lr, lr)
+        assert o3.dtype == torch.float32
