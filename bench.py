@@ -36,7 +36,7 @@ METRIC = "ttt_layer_fwd_tokens_per_s_760M_shape"
 # DRAM bytes (read + write) of ONE Newton-Schulz launch from an ncu capture of a 16-head case
 # (profiles/ns_fused_kernel_small_case.md: 14.3 MB + 34.9 MB); grows with the matrices per launch.
 NCU_DRAM_BYTES_NS_FUSED_16_HEADS = 49.2e6
-E2E_SLABS = 8  # the end-to-end arm streams the batch through the device in this many slabs
+E2E_SLABS = 4  # the end-to-end arm streams the batch through the device in this many slabs
 
 
 # ------------------------------------------------------------------------------------------ helpers
