@@ -127,11 +127,11 @@ NS_CONST = (3.4445, -4.7750, 2.0315)
 
 
 def ns_forward_saved(G, steps, const_coeffs, gram_right):
-    """Recomputes the Newton-Schulz iteration on G [nmat, R, C] keeping every iterate (bf16, with
-    the reference's rounding points, zeropower_via_newtonschulz5 in ttt_operation.py:30-66 /
-    lact_nvs/lact_ttt.py:32-67).  GEMMs on the tcgen05 engine; the elementwise combinations are
-    small (matrix-sized) tensor ops.  Returns a dict used by `ns_backward` and the result U in
-    G's orientation (bf16)."""
+    """Recomputes the Newton-Schulz iteration on G [nmat, R, C] keeping every iterate (bf16), in the
+    folded form the forward kernels use: A = X X^T, CA = c A + b I, P = CA A + a I, X' = P X
+    (zeropower_via_newtonschulz5, ttt_operation.py:30-66 / lact_nvs/lact_ttt.py:32-67, with
+    b A + (c A) A = (c A + b I) A and a X + P X = (P + a I) X).  Contractions on the tcgen05 engine.
+    Returns a dict used by `ns_backward` and the result U in G's orientation (bf16)."""
     coeffs = [NS_CONST] * steps if const_coeffs else list(NS_TUNED5)
     R, Cc = G.shape[1], G.shape[2]
     flip = R > Cc or (R == Cc and gram_right)
@@ -143,10 +143,14 @@ def ns_forward_saved(G, steps, const_coeffs, gram_right):
     its = []
     for a, b, c in coeffs:
         A = gemm(X, X, out_dtype=BF16)                        # X X^T
-        cA = (c * A.float()).to(BF16)
-        Pm = ((b * A.float()).to(BF16).float() + gemm(cA, A, out_dtype=BF16).float()).to(BF16)
-        Xn = ((a * X.float()).to(BF16).float() + gemm(Pm, X, b_mn=True, out_dtype=BF16).float()).to(BF16)
-        its.append((X, A, Pm, (a, b, c)))
+        CA = A.float().mul_(c)
+        CA.diagonal(dim1=1, dim2=2).add_(b)
+        CA = CA.to(BF16)                                      # c A + b I
+        Pm = gemm(CA, A)                                      # (c A + b I) A   (A symmetric: rows = columns)
+        Pm.diagonal(dim1=1, dim2=2).add_(a)
+        Pm = Pm.to(BF16)                                      # ... + a I
+        Xn = gemm(Pm, X, b_mn=True, out_dtype=BF16)           # (P + a I) X
+        its.append((X, CA, Pm, b))
         X = Xn
     U = X.transpose(1, 2).contiguous() if flip else X
     return dict(its=its, flip=flip, Gb=Gb, den=den.float(), nrm=nrm.float()), U
@@ -154,17 +158,19 @@ def ns_forward_saved(G, steps, const_coeffs, gram_right):
 
 def ns_backward(saved, dU):
     """Gradient w.r.t. G of U = NS(G) given dU (fp32, G's orientation); roundings are treated as
-    identities, operands of every contraction are bf16 as in the reference's autograd."""
+    identities, operands of every contraction are bf16 as in the reference's autograd.  Per
+    iteration, with P and CA symmetric and Q = dP + dP^T:
+        dP = dX' X^T,   dX = P dX' + S X,   S = dA + dA^T = CA Q + (CA Q)^T - b Q."""
     dX = dU.transpose(1, 2).contiguous() if saved["flip"] else dU
     dX = dX.float()
-    for X, A, Pm, (a, b, c) in reversed(saved["its"]):
+    for X, CA, Pm, b in reversed(saved["its"]):
         dXb = dX.to(BF16)
         dP = gemm(dXb, X)                                     # dX' X^T            [m, m] fp32
-        dXn = a * dX + gemm(Pm, dXb, b_mn=True)               # a dX' + P dX'      (P symmetric)
-        dPb = dP.to(BF16)
-        dA = b * dP + c * (gemm(dPb, A) + gemm(A, dPb, b_mn=True))   # b dP + c (dP A + A dP)
-        S = (dA + dA.transpose(1, 2)).to(BF16)
-        dX = dXn + gemm(S, X, b_mn=True)                      # + (dA + dA^T) X
+        Q = (dP + dP.transpose(1, 2)).to(BF16)
+        T = gemm(CA, Q)                                       # CA Q (Q symmetric)
+        S = (T + T.transpose(1, 2)).sub_(Q, alpha=b).to(BF16)
+        dXn = gemm(Pm, dXb, b_mn=True)                        # P dX'              (P symmetric, includes a I)
+        dX = gemm(S, X, b_mn=True, out=dXn, accumulate=True)  # + (dA + dA^T) X
     dX0 = dX.transpose(1, 2) if saved["flip"] else dX         # back to G's orientation
     Gf, den, nrm = saved["Gb"].float(), saved["den"], saved["nrm"]
     dot = (dX0 * Gf).sum(dim=(1, 2), keepdim=True)
