@@ -219,6 +219,59 @@ def workload_config(n):
             "l2": "inputs (3.2 GB per step) exceed L2; no explicit flush"}
 
 
+def other_config_timings(lb, dev, steps=5):
+    """Forward time of the other BASELINE configurations on seeded synthetic inputs of their shapes
+    (q, k L2-normalised N(0,1), v N(0,1), lr = softplus(N(-2,1)), momentum = sigmoid(N(0,1)))."""
+    g = torch.Generator(device=dev).manual_seed(5)
+    rn = lambda *s: torch.randn(*s, device=dev, generator=g)
+
+    def inputs(B, L, D, H, dtype):
+        q, k, v = rn(B, L, D), rn(B, L, D), rn(B, L, D)
+        q, k = q / q.norm(dim=-1, keepdim=True), k / k.norm(dim=-1, keepdim=True)
+        lr = [torch.nn.functional.softplus(rn(B, L, 1) - 2.0) for _ in range(3)]
+        return dict(w0=rn(B, H, D) / D ** 0.5, w1=rn(B, D, H) / H ** 0.5, w2=rn(B, H, D) / D ** 0.5, q=q.to(dtype),
+                    k=k.to(dtype), v=v.to(dtype), lr=lr, mom=torch.sigmoid(rn(B, L, 1)))
+
+    def timed(fn, tokens):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        return {"ms_per_step": ms, "tokens_per_s": tokens / (ms * 1e-3)}
+
+    out = {}
+    # config 1: bidirectional layer, fp32, batch 1 x 4 heads of 192, 4096 tokens, Muon on (accuracy mode: FFMA contractions)
+    i = inputs(4, 4096, 192, 192, torch.float32)
+    out["bidirectional_fp32_b1_l4096_4x192"] = timed(
+        lambda: lb.bidirectional_lact_swiglu(i["w0"], i["w1"], i["w2"], i["q"], i["k"], i["v"], *i["lr"], use_muon=True), 4096)
+    ib = {k_: (v_.to(BF16) if k_ in ("q", "k", "v") else v_) for k_, v_ in i.items()}
+    out["bidirectional_bf16_b1_l4096_4x192"] = timed(
+        lambda: lb.bidirectional_lact_swiglu(ib["w0"], ib["w1"], ib["w2"], ib["q"], ib["k"], ib["v"], *ib["lr"], use_muon=True), 4096)
+    # config 4: NVS block, batch 4 x 4 heads of 192, update on 49152 input tokens, apply to 4096 target tokens
+    i = inputs(16, 53248, 192, 192, BF16)
+    t_ = lambda w: w.transpose(1, 2).contiguous()
+    nw = (t_(i["w0"]), t_(i["w1"]), t_(i["w2"]))
+    order = [lb.TTTOperator(0, 49152, True, False), lb.TTTOperator(49152, 53248, False, True)]
+    out["nvs_b4_48views_4x192"] = timed(
+        lambda: lb.fast_weight_swish_glu_weight_norm_mini_batch_apply(*nw, i["q"], i["k"], i["v"], *i["lr"], order,
+                                                                      muon_update_steps=5), 4 * 53248)
+    del i, nw
+    # config 5: AR video layer, batch 1 x 12 heads of 128, hidden 256, 21 frames of 1560 tokens
+    i = inputs(12, 32760, 128, 256, BF16)
+    out["ar_video_b1_12x128_h256_21x1560"] = timed(
+        lambda: lb.ar_fast_weight_swish_glu_weight_norm_mini_batch_with_momentum(
+            i["w0"], i["w1"], i["w2"], i["q"], i["k"], i["v"], *i["lr"], 1.0, mini_batch_size=1560, update_every=1560,
+            use_moun=True, num_moun_iters=5, fw_momentum=i["mom"], use_momentum=True), 32760)
+    lb.synchronize_and_check()
+    return out
+
+
 def train_step_timing(lb, t, dev, B, L, D, H, C, tokens_per_step, world, barrier, peaks, steps=3):
     """Forward + backward of the same workload (the training configuration): one step = forward,
     then backward from dO ~ N(0,1) bf16 to q, k, v, lr0/1/2, momentum and the initial W0/W1/W2."""
@@ -267,6 +320,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--other-configs", action="store_true",
+                    help="also time the other BASELINE configurations (bidirectional fp32, NVS block, AR video layer) "
+                         "on one GPU; reported under \"other_configs\" (not the headline metric)")
     ap.add_argument("--train", action="store_true",
                     help="also time forward + backward through the recurrence (gradients to q, k, v, lr, momentum "
                          "and the initial fast weights, upstream gradient ~ N(0,1) bf16); reported under \"train\"")
@@ -395,6 +451,9 @@ def main():
         e2e["slabs"] = n_slabs
         del host, pipe, out_host
 
+    others = None
+    if args.other_configs and rank == 0:
+        others = other_config_timings(lact_b200, dev)
     train = None
     if args.train:
         train = train_step_timing(lact_b200, t, dev, B, L, D, H, C, tokens_per_step, world, barrier, peaks)
@@ -418,6 +477,8 @@ def main():
         }
         if train is not None:
             line["train"] = train
+        if others is not None:
+            line["other_configs"] = others
         if reduced:
             line["reduced_case"] = "batch/seq overridden for a profiler capture: not the benchmark workload"
         print(json.dumps(line), flush=True)
