@@ -295,11 +295,8 @@ template <int BT_>
 struct OpNs {
   static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 2;
   static constexpr bool kSecondInPlace = true, kTileReduce = false;
-#ifndef LACT_NS_STAGING_BUFFERS
-#define LACT_NS_STAGING_BUFFERS 2
-#endif
   // two staging tiles: tile i + 1 is assembled in one while tile i is still being stored from the other
-  static constexpr int kStagingBuffers = LACT_NS_STAGING_BUFFERS;
+  static constexpr int kStagingBuffers = 2;
   static constexpr int STAGES = ring_depth(kATileBytes + BT_ * kBK * 2, kStagingBuffers * kBM * BT_ * 2);
   using Epi = EpiNs;
   __host__ __device__ static constexpr int term_a(int) { return 0; }
