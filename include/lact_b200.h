@@ -206,6 +206,18 @@ int lact_bmm2_bf16(const void *a0, int32_t a0_mn_major, const void *b0, int32_t 
                    int32_t a1_mn_major, const void *b1, int32_t b1_mn_major, void *c, int32_t c_dtype,
                    int32_t accumulate, int64_t batch, int64_t M, int64_t N, int64_t K, int32_t *status_word,
                    void *stream);
+/* Newton-Schulz with every iterate kept, and its backward (the reference differentiates
+ * zeropower_via_newtonschulz5, ttt_operation.py:30-66 / lact_nvs/lact_ttt.py:32-67, by autograd):
+ *   lact_ns_trace_fwd: x_out[B, R, C] (bf16) = Newton-Schulz(g), the iterates and Gram polynomials stay in `trace`
+ *     (lact_ns_trace_bytes; 256-byte aligned); status_word: device status word as for lact_bmm2_bf16;
+ *   lact_ns_trace_bwd: dx0[B, R, C] (fp32) = gradient w.r.t. the NORMALISED first iterate bf16(g) / (||g|| + 1e-7),
+ *     from du[B, R, C] (bf16) = gradient w.r.t. x_out, using the trace of the matching forward call. */
+int lact_ns_trace_bytes(int64_t B, int64_t R, int64_t C, int32_t steps, size_t *bytes_out);
+int lact_ns_trace_fwd(const void *g, int32_t g_dtype, void *x_out, int64_t B, int64_t R, int64_t C, int32_t steps,
+                      int32_t const_coeffs, int32_t gram_right, void *trace, size_t trace_bytes, int32_t *status_word,
+                      void *stream);
+int lact_ns_trace_bwd(const void *du, void *dx0, int64_t B, int64_t R, int64_t C, int32_t steps, int32_t const_coeffs,
+                      int32_t gram_right, void *trace, size_t trace_bytes, int32_t *status_word, void *stream);
 int lact_swiglu_bwd_planes(const void *y02, const void *dh, const void *lr0, const void *lr1, const void *lr2,
                            int32_t lr_dtype, float w_scale, void *dy02, void *hid, int64_t rows, int64_t H,
                            void *stream);

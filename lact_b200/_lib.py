@@ -70,6 +70,9 @@ def _declare(lib: C.CDLL) -> None:
     lib.lact_fw_grad_bwd_pointwise.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, f32, vp, vp, vp, vp, vp, vp, vp, i64,
                                                i64, vp]
     lib.lact_renorm_bwd.argtypes = [vp, vp, i32, vp, vp, vp, vp, i64, i64, i32, vp]
+    lib.lact_ns_trace_bytes.argtypes = [i64, i64, i64, i32, C.POINTER(C.c_size_t)]
+    lib.lact_ns_trace_fwd.argtypes = [vp, i32, vp, i64, i64, i64, i32, i32, i32, vp, C.c_size_t, vp, vp]
+    lib.lact_ns_trace_bwd.argtypes = [vp, vp, i64, i64, i64, i32, i32, i32, vp, C.c_size_t, vp, vp]
     lib.lact_sgemm_f32.argtypes = [vp, i32, vp, i32, vp, i32, vp, i64, i64, i64, i64, vp]
     lib.lact_swiglu_planes_f32.argtypes = [vp, vp, vp, vp, vp, i32, f32, vp, vp, i64, i64, vp]
     lib.lact_add_renorm.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, i32, i32, i32, i32, vp]
@@ -78,7 +81,7 @@ def _declare(lib: C.CDLL) -> None:
                  "lact_newton_schulz_workspace_bytes", "lact_newton_schulz", "lact_l2_norm_add",
                  "lact_prenorm_momentum_l2norm", "lact_bmm_bf16", "lact_bmm2_bf16", "lact_swiglu_bwd_planes",
                  "lact_fw_grad_bwd_pointwise", "lact_renorm_bwd", "lact_sgemm_f32", "lact_swiglu_planes_f32",
-                 "lact_add_renorm"):
+                 "lact_add_renorm", "lact_ns_trace_bytes", "lact_ns_trace_fwd", "lact_ns_trace_bwd"):
         getattr(lib, name).restype = C.c_int
 
 

@@ -127,51 +127,41 @@ NS_CONST = (3.4445, -4.7750, 2.0315)
 
 
 def ns_forward_saved(G, steps, const_coeffs, gram_right):
-    """Recomputes the Newton-Schulz iteration on G [nmat, R, C] keeping every iterate (bf16), in the
-    folded form the forward kernels use: A = X X^T, CA = c A + b I, P = CA A + a I, X' = P X
-    (zeropower_via_newtonschulz5, ttt_operation.py:30-66 / lact_nvs/lact_ttt.py:32-67, with
-    b A + (c A) A = (c A + b I) A and a X + P X = (P + a I) X).  Contractions on the tcgen05 engine.
+    """Recomputes the Newton-Schulz iteration on G [nmat, R, C] keeping every iterate
+    (`lact_ns_trace_fwd`: the forward kernels' own arithmetic, iterates in a trace buffer).
     Returns a dict used by `ns_backward` and the result U in G's orientation (bf16)."""
-    coeffs = [NS_CONST] * steps if const_coeffs else list(NS_TUNED5)
-    R, Cc = G.shape[1], G.shape[2]
-    flip = R > Cc or (R == Cc and gram_right)
+    G = G.contiguous()
+    nmat, R, Cc = G.shape
+    if G.dtype not in (torch.float32, BF16):
+        G = G.float()
+    need = C.c_size_t(0)
+    L.check(L.lib().lact_ns_trace_bytes(nmat, R, Cc, int(steps), C.byref(need)), "lact_ns_trace_bytes")
+    trace = torch.empty(need.value, dtype=torch.uint8, device=G.device)
+    U = torch.empty(nmat, R, Cc, dtype=BF16, device=G.device)
+    with torch.cuda.device(G.device):
+        L.check(L.lib().lact_ns_trace_fwd(G.data_ptr(), L.dtype_code(G), U.data_ptr(), nmat, R, Cc, int(steps),
+                                          int(bool(const_coeffs)), int(bool(gram_right)), trace.data_ptr(), trace.numel(),
+                                          _status_word(G.device).data_ptr(), L.stream_ptr()), "lact_ns_trace_fwd")
     Gb = G.to(BF16)
     nrm = Gb.float().pow(2).sum(dim=(1, 2), keepdim=True).sqrt().to(BF16)
     den = (nrm.float() + 1e-7).to(BF16)
-    Xg = (Gb.float() / den.float()).to(BF16)                  # normalised, G's orientation
-    X = Xg.transpose(1, 2).contiguous() if flip else Xg
-    its = []
-    for a, b, c in coeffs:
-        A = gemm(X, X, out_dtype=BF16)                        # X X^T
-        CA = A.float().mul_(c)
-        CA.diagonal(dim1=1, dim2=2).add_(b)
-        CA = CA.to(BF16)                                      # c A + b I
-        Pm = gemm(CA, A)                                      # (c A + b I) A   (A symmetric: rows = columns)
-        Pm.diagonal(dim1=1, dim2=2).add_(a)
-        Pm = Pm.to(BF16)                                      # ... + a I
-        Xn = gemm(Pm, X, b_mn=True, out_dtype=BF16)           # (P + a I) X
-        its.append((X, CA, Pm, b))
-        X = Xn
-    U = X.transpose(1, 2).contiguous() if flip else X
-    return dict(its=its, flip=flip, Gb=Gb, den=den.float(), nrm=nrm.float()), U
+    return dict(trace=trace, shape=(nmat, R, Cc), steps=int(steps), cc=int(bool(const_coeffs)), gr=int(bool(gram_right)),
+                Gb=Gb, den=den.float(), nrm=nrm.float()), U
 
 
 def ns_backward(saved, dU):
-    """Gradient w.r.t. G of U = NS(G) given dU (fp32, G's orientation); roundings are treated as
-    identities, operands of every contraction are bf16 as in the reference's autograd.  Per
-    iteration, with P and CA symmetric and Q = dP + dP^T:
-        dP = dX' X^T,   dX = P dX' + S X,   S = dA + dA^T = CA Q + (CA Q)^T - b Q."""
-    dX = dU.transpose(1, 2).contiguous() if saved["flip"] else dU
-    dX = dX.float()
-    for X, CA, Pm, b in reversed(saved["its"]):
-        dXb = dX.to(BF16)
-        dP = gemm(dXb, X)                                     # dX' X^T            [m, m] fp32
-        Q = (dP + dP.transpose(1, 2)).to(BF16)
-        T = gemm(CA, Q)                                       # CA Q (Q symmetric)
-        S = (T + T.transpose(1, 2)).sub_(Q, alpha=b).to(BF16)
-        dXn = gemm(Pm, dXb, b_mn=True)                        # P dX'              (P symmetric, includes a I)
-        dX = gemm(S, X, b_mn=True, out=dXn, accumulate=True)  # + (dA + dA^T) X
-    dX0 = dX.transpose(1, 2) if saved["flip"] else dX         # back to G's orientation
+    """Gradient w.r.t. G of U = NS(G) given dU (fp32, G's orientation): `lact_ns_trace_bwd` walks
+    the saved iterates backwards (three two-product contractions per iteration, roundings treated
+    as identities, bf16 operands as in the reference's autograd), then the Frobenius
+    normalisation X0 = bf16(G) / (||G|| + 1e-7) is differentiated here."""
+    nmat, R, Cc = saved["shape"]
+    du = dU.to(BF16).contiguous()
+    dX0 = torch.empty(nmat, R, Cc, dtype=torch.float32, device=du.device)
+    trace = saved["trace"]
+    with torch.cuda.device(du.device):
+        L.check(L.lib().lact_ns_trace_bwd(du.data_ptr(), dX0.data_ptr(), nmat, R, Cc, saved["steps"], saved["cc"],
+                                          saved["gr"], trace.data_ptr(), trace.numel(),
+                                          _status_word(du.device).data_ptr(), L.stream_ptr()), "lact_ns_trace_bwd")
     Gf, den, nrm = saved["Gb"].float(), saved["den"], saved["nrm"]
     dot = (dX0 * Gf).sum(dim=(1, 2), keepdim=True)
     return dX0 / den - Gf * dot / (den * den * nrm.clamp_min(1e-30))

@@ -523,16 +523,18 @@ inline void ns_tile_widths(const NsGroup* grp, int ngroups, int* bt_mm, int* bt_
 // scale factors grp[g].scale are folded into the first iteration).
 // result[g] = buffer holding the final iterate of group g.
 int run_ns_iterations(const NsGroup* grp, int ngroups, int steps, int const_coeffs, const bf16** result,
-                      int32_t* status, cudaStream_t stream, int unscaled_first = 0) {
+                      int32_t* status, cudaStream_t stream, int unscaled_first = 0, int coef_offset = 0) {
+  // `steps` iterations of the schedule starting at iteration `coef_offset` (the tuned table has five
+  // entries; the public entry points insist on all five)
   if (ngroups < 1 || ngroups > 2) return LACT_ERR_CONFIG;
-  if (!const_coeffs && steps != 5) return LACT_ERR_CONFIG;
+  if (!const_coeffs && steps + coef_offset > 5) return LACT_ERR_CONFIG;
   bf16* cur[2];
   bf16* nxt[2];
   for (int g = 0; g < ngroups; ++g) { cur[g] = grp[g].xa; nxt[g] = grp[g].xb; }
   int bt_mm = 0, bt_mn = 0;
   ns_tile_widths(grp, ngroups, &bt_mm, &bt_mn);
   for (int it = 0; it < steps; ++it) {
-    const float* co = const_coeffs ? kNsConst : kNsTuned[it];
+    const float* co = const_coeffs ? kNsConst : kNsTuned[it + coef_offset];
     const int fold = (it == 0 && unscaled_first) ? 1 : 0;
     // which = 0 gram, 1 poly, 2 update: every fill wires all three and keeps the one it launches
     auto fill = [&](auto& ga, int btv, int which) -> int {
@@ -1130,6 +1132,116 @@ int lact_newton_schulz(const void* g, int32_t g_dtype, void* x, int64_t B, int64
   if (rc == LACT_ERR_CONFIG) rc = run_ns_iterations(&grp, 1, steps, const_coeffs, &res, status, s);
   LACT_TRY(rc);
   LACT_CUDA(cudaMemcpyAsync(x, res, static_cast<size_t>(B) * R * C * 2, cudaMemcpyDeviceToDevice, s));
+  return LACT_OK;
+}
+
+// ---------------------------------------------------------------- Newton-Schulz with saved iterates, and its backward
+// Trace layout in the caller's buffer (bf16 unless noted): group scratch (norm partials,
+// scale factors); X[0..steps] ([B][R][C] each); gram A, c A + b I, poly P per iteration ([B][m][m]);
+// then the backward's temporaries: c A + (b/2) I, Q, S ([B][m][m]) and two [B][R][C] gradient buffers.
+struct NsTrace {
+  NsGroup grp;
+  bf16* X;   // (steps + 1) iterates
+  bf16 *A, *CA, *P;  // steps matrices each
+  bf16 *CB, *Q, *S, *dXa, *dXb;
+  size_t bytes;
+};
+
+static int plan_ns_trace(void* base, int64_t B, int64_t R, int64_t C, int steps, int gram_right, NsTrace* t) {
+  if (B < 1 || B > 65535 || R < 8 || C < 8 || (R % 8) || (C % 8) || steps < 1 || steps > 16) return LACT_ERR_SHAPE;
+  Carver cv(base);
+  ns_group_init(t->grp, B, R, C, gram_right);
+  const size_t rc = static_cast<size_t>(B) * R * C, mm = static_cast<size_t>(B) * t->grp.m * t->grp.m;
+  t->grp.partial = cv.take<float>(static_cast<size_t>(B) * kNsMaxParts);
+  t->grp.scale = cv.take<float>(B);
+  t->grp.done = cv.take<uint32_t>(static_cast<size_t>(B) + 64);
+  t->X = cv.take<bf16>(rc * (steps + 1));
+  t->A = cv.take<bf16>(mm * steps);
+  t->CA = cv.take<bf16>(mm * steps);
+  t->P = cv.take<bf16>(mm * steps);
+  t->CB = cv.take<bf16>(mm);
+  t->Q = cv.take<bf16>(mm);
+  t->S = cv.take<bf16>(mm);
+  t->dXa = cv.take<bf16>(rc);
+  t->dXb = cv.take<bf16>(rc);
+  t->bytes = cv.off + 256;
+  return LACT_OK;
+}
+
+int lact_ns_trace_bytes(int64_t B, int64_t R, int64_t C, int32_t steps, size_t* bytes_out) {
+  if (!bytes_out) return LACT_ERR_NULL;
+  NsTrace t;
+  LACT_TRY(plan_ns_trace(nullptr, B, R, C, steps, 0, &t));
+  *bytes_out = t.bytes;
+  return LACT_OK;
+}
+
+int lact_ns_trace_fwd(const void* g, int32_t g_dtype, void* x_out, int64_t B, int64_t R, int64_t C, int32_t steps,
+                      int32_t const_coeffs, int32_t gram_right, void* trace, size_t trace_bytes, int32_t* status_word,
+                      void* stream) {
+  if (!g || !x_out || !trace || !status_word) return LACT_ERR_NULL;
+  LACT_TRY(check_device());
+  if ((reinterpret_cast<uintptr_t>(trace) & 255) != 0) return LACT_ERR_WORKSPACE;
+  if (!const_coeffs && steps != 5) return LACT_ERR_CONFIG;
+  NsTrace t;
+  LACT_TRY(plan_ns_trace(trace, B, R, C, steps, gram_right, &t));
+  if (t.bytes > trace_bytes) return LACT_ERR_WORKSPACE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t rc = static_cast<size_t>(B) * R * C, mm = static_cast<size_t>(B) * t.grp.m * t.grp.m;
+  t.grp.xa = t.X;
+  const void* srcs[2] = {g, g};
+  LACT_TRY(launch_ns_prepare(&t.grp, 1, srcs, g_dtype == LACT_F32, 1, s));  // X[0] = normalised bf16(g)
+  for (int it = 0; it < steps; ++it) {
+    NsGroup gi = t.grp;
+    gi.xa = t.X + rc * it;
+    gi.xb = t.X + rc * (it + 1);
+    gi.gram = t.A + mm * it;
+    gi.cgram = t.CA + mm * it;
+    gi.poly = t.P + mm * it;
+    const bf16* res = nullptr;
+    LACT_TRY(run_ns_iterations(&gi, 1, 1, const_coeffs, &res, status_word, s, 0, const_coeffs ? 0 : it));
+  }
+  LACT_CUDA(cudaMemcpyAsync(x_out, t.X + rc * steps, rc * 2, cudaMemcpyDeviceToDevice, s));
+  return LACT_OK;
+}
+
+// dx0 (fp32) = gradient w.r.t. the normalised first iterate X[0], given du = bf16 gradient w.r.t. the
+// result X[steps]; roundings are treated as identities and every operand is bf16 (the reference
+// differentiates its bf16 iteration the same way).  With Q = dP + dP^T (dP = dX' X^T) and
+// CB = c A + (b/2) I the three products per iteration are, for a wide iterate ([m][n], A = X X^T):
+//   Q = dX' X^T + X dX'^T,   S = CB Q + Q CB,   dX = P dX' + S X,
+// and for a tall one ([n][m], A = X^T X, X' = X P^T):  Q = dX'^T X + X^T dX',  dX = dX' P + X S.
+int lact_ns_trace_bwd(const void* du, void* dx0, int64_t B, int64_t R, int64_t C, int32_t steps, int32_t const_coeffs,
+                      int32_t gram_right, void* trace, size_t trace_bytes, int32_t* status_word, void* stream) {
+  if (!du || !dx0 || !trace || !status_word) return LACT_ERR_NULL;
+  LACT_TRY(check_device());
+  NsTrace t;
+  LACT_TRY(plan_ns_trace(trace, B, R, C, steps, gram_right, &t));
+  if (t.bytes > trace_bytes) return LACT_ERR_WORKSPACE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t m = t.grp.m, n = t.grp.n;
+  const size_t rc = static_cast<size_t>(B) * R * C, mm = static_cast<size_t>(B) * m * m;
+  const int tall = t.grp.transposed;
+  const bf16* dX = static_cast<const bf16*>(du);
+  for (int it = steps - 1; it >= 0; --it) {
+    const float* co = const_coeffs ? kNsConst : kNsTuned[it];
+    const bf16* X = t.X + rc * it;
+    const bf16* P = t.P + mm * it;
+    {
+      KernelScope scope(kClsOther, s);
+      diag_shift_kernel<<<ceil_div(static_cast<int64_t>(mm), 256 * 8), 256, 0, s>>>(t.CA + mm * it, t.CB, static_cast<int>(m),
+                                                                                    static_cast<int64_t>(mm), -0.5f * co[1]);
+      LACT_CUDA(cudaGetLastError());
+    }
+    // Q [m][m]: contraction over the long side n
+    LACT_TRY(lact_bmm2_bf16(dX, tall, X, tall, X, tall, dX, tall, t.Q, LACT_BF16, 0, B, m, m, n, status_word, stream));
+    LACT_TRY(lact_bmm2_bf16(t.CB, 0, t.Q, 0, t.Q, 0, t.CB, 0, t.S, LACT_BF16, 0, B, m, m, m, status_word, stream));
+    void* out = it == 0 ? dx0 : static_cast<void*>((it & 1) ? t.dXa : t.dXb);
+    const int out_dt = it == 0 ? LACT_F32 : LACT_BF16;
+    if (!tall) LACT_TRY(lact_bmm2_bf16(P, 0, dX, 1, t.S, 0, X, 1, out, out_dt, 0, B, m, n, m, status_word, stream));
+    else LACT_TRY(lact_bmm2_bf16(dX, 0, P, 1, X, 0, t.S, 0, out, out_dt, 0, B, n, m, m, status_word, stream));
+    dX = static_cast<const bf16*>(out);
+  }
   return LACT_OK;
 }
 

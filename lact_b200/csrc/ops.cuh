@@ -611,6 +611,24 @@ __global__ void __launch_bounds__(256) ns_scale_kernel(const NsPrepArgs args) {
   }
 }
 
+// dst = src + delta * I for [nmat] square bf16 matrices of side m (8 elements per thread).
+__global__ void __launch_bounds__(256) diag_shift_kernel(const bf16* src, bf16* dst, int m, int64_t total, float delta) {
+  const int64_t i0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 8;
+  if (i0 >= total) return;
+  uint4 u = *reinterpret_cast<const uint4*>(src + i0);
+  const int64_t in_mat = i0 % (static_cast<int64_t>(m) * m);
+  const int row = static_cast<int>(in_mat / m), col = static_cast<int>(in_mat % m);
+  if (row >= col && row < col + 8) {  // the diagonal element of this row lies in this 8-element segment
+    uint32_t* w = reinterpret_cast<uint32_t*>(&u);
+    const int j = row - col;
+    const uint32_t word = w[j >> 1];
+    float lo = __uint_as_float(word << 16), hi = __uint_as_float(word & 0xFFFF0000u);
+    if (j & 1) hi += delta; else lo += delta;
+    w[j >> 1] = pack_bf16x2(lo, hi);
+  }
+  *reinterpret_cast<uint4*>(dst + i0) = u;
+}
+
 struct RenormArgs {
   float* master;     // [B][R][C] fp32, in/out
   float* compute;    // [B][R][C] fp32 out (may be nullptr): the weights the next step computes with
