@@ -60,15 +60,48 @@ int encode_map(CUtensorMap* map, const Mat& m, uint32_t box_rows) {
   return r == CUDA_SUCCESS ? LACT_OK : LACT_ERR_CUDA;
 }
 
-// Operand of a GEMM: `m` used K-major (mn = rows, k = cols) or MN-major (k = rows, mn = cols).
-int make_operand(CUtensorMap* map, OperandInfo* info, const Mat& m, int mn_major, int tile_rows, int mn_off, int k_off,
-                 int batch_off = 0) {
+// Encodes a 4-D map (64 cols of a k-block, rows, k-blocks, batch) of a matrix whose column count is a
+// multiple of 64, with a {64, box_rows, kb, 1} box: one load brings `kb` consecutive k-blocks of a row
+// block, laid out in shared memory k-block after k-block.
+int encode_map_kblocks(CUtensorMap* map, const Mat& m, uint32_t box_rows, uint32_t kb) {
+  EncodeFn fn = get_encode_fn();
+  if (fn == nullptr) return LACT_ERR_CUDA;
+  if ((reinterpret_cast<uintptr_t>(m.ptr) & 15) != 0 || (m.ld % 8) != 0 || (m.batch > 1 && (m.bs % 8) != 0))
+    return LACT_ERR_SHAPE;
+  if (m.rows < 1 || m.cols < 64 || (m.cols % 64) != 0 || m.batch < 1 || box_rows > 256) return LACT_ERR_SHAPE;
+  cuuint64_t dims[4] = {64, static_cast<cuuint64_t>(m.rows), static_cast<cuuint64_t>(m.cols / 64),
+                        static_cast<cuuint64_t>(m.batch)};
+  const int64_t bs = m.batch > 1 ? m.bs : m.ld * m.rows;
+  cuuint64_t strides[3] = {static_cast<cuuint64_t>(m.ld) * 2, 128, static_cast<cuuint64_t>(bs) * 2};
+  cuuint32_t box[4] = {64, box_rows, kb, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(m.ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? LACT_OK : LACT_ERR_CUDA;
+}
+
+template <class Op>
+constexpr int kb_of(const GemmProblem<Op>&) { return Op::KB; }
+
+// Operand of a GEMM: `m` used K-major (mn = rows, k = cols) or MN-major (k = rows, mn = cols); `kb` =
+// k-blocks per ring stage of the op that reads it.  With two k-blocks per stage a K-major operand
+// whose k extent is whole k-blocks gets the 4-D map (one box per stage), an MN-major operand a box of
+// 128 k rows per 64-wide atom.
+int make_operand(int kb, CUtensorMap* map, OperandInfo* info, const Mat& m, int mn_major, int tile_rows, int mn_off,
+                 int k_off, int batch_off = 0) {
   info->mn_major = mn_major;
+  info->k4d = 0;
   info->mn_off = mn_off;
   info->k_off = k_off;
   info->batch_off = batch_off;
   if (((mn_major ? mn_off : k_off) % 8) != 0) return LACT_ERR_SHAPE;  // innermost TMA coordinate: 16-byte rule
-  return encode_map(map, m, mn_major ? 64 : static_cast<uint32_t>(tile_rows));
+  if (mn_major) return encode_map(map, m, static_cast<uint32_t>(64 * kb));
+  if (kb == 2 && (m.cols % 64) == 0 && (k_off % 64) == 0) {
+    info->k4d = 1;
+    return encode_map_kblocks(map, m, static_cast<uint32_t>(tile_rows), 2);
+  }
+  return encode_map(map, m, static_cast<uint32_t>(tile_rows));
 }
 
 // Output of a staged epilogue: bf16 matrix `m` whose extents clip the stored tiles.
@@ -286,9 +319,9 @@ int launch_gate(const ApplyArgs& a, const Mat& x, const Mat& w02, int64_t len, i
   GemmArgs<OpSwigluGate<BT>, 1> g;
   std::memset(&g, 0, sizeof(g));
   auto& P = g.prob[0];
-  LACT_TRY(make_operand(&P.a[0], &P.ai[0], x, 0, kBM, static_cast<int>(a.start), 0));
-  LACT_TRY(make_operand(&P.b[0], &P.bi[0], w02, 0, BT, 0, 0));
-  LACT_TRY(make_operand(&P.b[1], &P.bi[1], w02, 0, BT, static_cast<int>(a.H), 0));
+  LACT_TRY(make_operand(kb_of(P), &P.a[0], &P.ai[0], x, 0, kBM, static_cast<int>(a.start), 0));
+  LACT_TRY(make_operand(kb_of(P), &P.b[0], &P.bi[0], w02, 0, BT, 0, 0));
+  LACT_TRY(make_operand(kb_of(P), &P.b[1], &P.bi[1], w02, 0, BT, static_cast<int>(a.H), 0));
   const Mat hid{a.hidden, len, a.H, a.H, a.B, len * a.H};
   LACT_TRY(make_output(&P.out[0], &P.oi[0], hid, 0, 0));
   P.M = static_cast<int>(len); P.N = static_cast<int>(a.H); P.K = static_cast<int>(a.D);
@@ -309,8 +342,8 @@ int run_apply(const ApplyArgs& a, int32_t* status, cudaStream_t stream) {
   const int bt = choose_bt({{a.D, 1}});
   auto fill = [&](auto& g, int btv) -> int {
     auto& P = g.prob[0];
-    LACT_TRY(make_operand(&P.a[0], &P.ai[0], hid, 0, kBM, 0, 0));
-    LACT_TRY(make_operand(&P.b[0], &P.bi[0], w1, 0, btv, 0, 0));
+    LACT_TRY(make_operand(kb_of(P), &P.a[0], &P.ai[0], hid, 0, kBM, 0, 0));
+    LACT_TRY(make_operand(kb_of(P), &P.b[0], &P.bi[0], w1, 0, btv, 0, 0));
     // rows beyond the range's end must not be written: the map ends at out_start + len
     const Mat om{a.out, a.out_start + len, a.D, a.o_ts, a.B, a.o_bs};
     LACT_TRY(make_output(&P.out[0], &P.oi[0], om, static_cast<int>(a.out_start), 0));
@@ -361,12 +394,12 @@ int run_grad(const GradArgs& a, int32_t* status, cudaStream_t stream) {
     std::memset(&g, 0, sizeof(g));
     auto& P = g.prob[0];
     constexpr int BT = OpFwGradPointwise::BT;
-    LACT_TRY(make_operand(&P.a[0], &P.ai[0], km, 0, kBM, static_cast<int>(a.start), 0));
-    LACT_TRY(make_operand(&P.a[1], &P.ai[1], vm, 0, kBM, static_cast<int>(a.start), 0));
-    LACT_TRY(make_operand(&P.b[0], &P.bi[0], w02, 0, BT, 0, 0));
-    LACT_TRY(make_operand(&P.b[1], &P.bi[1], w02, 0, BT, static_cast<int>(a.H), 0));
+    LACT_TRY(make_operand(kb_of(P), &P.a[0], &P.ai[0], km, 0, kBM, static_cast<int>(a.start), 0));
+    LACT_TRY(make_operand(kb_of(P), &P.a[1], &P.ai[1], vm, 0, kBM, static_cast<int>(a.start), 0));
+    LACT_TRY(make_operand(kb_of(P), &P.b[0], &P.bi[0], w02, 0, BT, 0, 0));
+    LACT_TRY(make_operand(kb_of(P), &P.b[1], &P.bi[1], w02, 0, BT, static_cast<int>(a.H), 0));
     // dh = v w1: w1 is [D][H], i.e. k (= D) rows with the n (= H) axis contiguous
-    LACT_TRY(make_operand(&P.b[2], &P.bi[2], w1, 1, BT, 0, 0));
+    LACT_TRY(make_operand(kb_of(P), &P.b[2], &P.bi[2], w1, 1, BT, 0, 0));
     P.M = static_cast<int>(len); P.N = static_cast<int>(a.H); P.K = static_cast<int>(a.D);
     P.batch = static_cast<int>(a.B);
     P.ep = EpiFwGrad{a.lr0, a.lr1, a.lr2, a.lr_f32, static_cast<int32_t>(a.start), a.lr_bs, a.w_scale};
@@ -383,15 +416,15 @@ int run_grad(const GradArgs& a, int32_t* status, cudaStream_t stream) {
   const int bt = contract_bt(a.D, a.H);
   auto fill = [&](auto& g, int btv) -> int {
     auto& P0 = g.prob[0];
-    LACT_TRY(make_operand(&P0.a[0], &P0.ai[0], dy, 1, kBM, 0, 0));
-    LACT_TRY(make_operand(&P0.b[0], &P0.bi[0], km, 1, btv, 0, static_cast<int>(a.start)));
+    LACT_TRY(make_operand(kb_of(P0), &P0.a[0], &P0.ai[0], dy, 1, kBM, 0, 0));
+    LACT_TRY(make_operand(kb_of(P0), &P0.b[0], &P0.bi[0], km, 1, btv, 0, static_cast<int>(a.start)));
     P0.M = static_cast<int>(2 * a.H); P0.N = static_cast<int>(a.D); P0.K = static_cast<int>(len);
     P0.batch = static_cast<int>(a.B);
     P0.ep = EpiDW{a.g02, 2 * a.H * a.D, a.D, a.beta, 1, a.g_f32, a.partial02, ceil_div(2 * a.H, kBM),
                   ceil_div(a.D, btv), a.gb02};
     auto& P1 = g.prob[1];
-    LACT_TRY(make_operand(&P1.a[0], &P1.ai[0], vm, 1, kBM, 0, static_cast<int>(a.start)));
-    LACT_TRY(make_operand(&P1.b[0], &P1.bi[0], hid, 1, btv, 0, 0));
+    LACT_TRY(make_operand(kb_of(P1), &P1.a[0], &P1.ai[0], vm, 1, kBM, 0, static_cast<int>(a.start)));
+    LACT_TRY(make_operand(kb_of(P1), &P1.b[0], &P1.bi[0], hid, 1, btv, 0, 0));
     P1.M = static_cast<int>(a.D); P1.N = static_cast<int>(a.H); P1.K = static_cast<int>(len);
     P1.batch = static_cast<int>(a.B);
     P1.ep = EpiDW{a.g1, a.D * a.H, a.H, a.beta, 1, a.g_f32, a.partial1, ceil_div(a.D, kBM), ceil_div(a.H, btv),
@@ -487,23 +520,23 @@ int wire_ns_group(const NsGroup& G, bf16* cur, bf16* nxt, int bt_mm, int bt_mn, 
   const Mat PB{G.poly, G.m, G.m, G.m, G.nmat, mm};
   const int tall = G.transposed;
   // gram = X X^T (wide) / X^T X (tall); second output c * gram + b I
-  LACT_TRY(make_operand(&gram.a[0], &gram.ai[0], X, tall, kBM, 0, 0));
-  LACT_TRY(make_operand(&gram.b[0], &gram.bi[0], X, tall, bt_mm, 0, 0));
+  LACT_TRY(make_operand(kb_of(gram), &gram.a[0], &gram.ai[0], X, tall, kBM, 0, 0));
+  LACT_TRY(make_operand(kb_of(gram), &gram.b[0], &gram.bi[0], X, tall, bt_mm, 0, 0));
   gram.M = G.m; gram.N = G.m; gram.K = G.n; gram.batch = G.nmat;
   LACT_TRY(make_output(&gram.out[0], &gram.oi[0], A, 0, 0));
   LACT_TRY(make_output(&gram.out[1], &gram.oi[1], CA, 0, 0));
   // poly = (c gram + b I) gram + a I   (gram is exactly symmetric: its rows serve as the K-major B operand)
-  LACT_TRY(make_operand(&poly.a[0], &poly.ai[0], CA, 0, kBM, 0, 0));
-  LACT_TRY(make_operand(&poly.b[0], &poly.bi[0], A, 0, bt_mm, 0, 0));
+  LACT_TRY(make_operand(kb_of(poly), &poly.a[0], &poly.ai[0], CA, 0, kBM, 0, 0));
+  LACT_TRY(make_operand(kb_of(poly), &poly.b[0], &poly.bi[0], A, 0, bt_mm, 0, 0));
   poly.M = G.m; poly.N = G.m; poly.K = G.m; poly.batch = G.nmat;
   LACT_TRY(make_output(&poly.out[0], &poly.oi[0], PB, 0, 0));
   // update: X' = poly X (wide; X is [k][n]: MN-major B operand) / X' = X poly^T (tall)
   if (!tall) {
-    LACT_TRY(make_operand(&upd.a[0], &upd.ai[0], PB, 0, kBM, 0, 0));
-    LACT_TRY(make_operand(&upd.b[0], &upd.bi[0], X, 1, bt_mn, 0, 0));
+    LACT_TRY(make_operand(kb_of(upd), &upd.a[0], &upd.ai[0], PB, 0, kBM, 0, 0));
+    LACT_TRY(make_operand(kb_of(upd), &upd.b[0], &upd.bi[0], X, 1, bt_mn, 0, 0));
   } else {
-    LACT_TRY(make_operand(&upd.a[0], &upd.ai[0], X, 0, kBM, 0, 0));
-    LACT_TRY(make_operand(&upd.b[0], &upd.bi[0], PB, 0, bt_mn, 0, 0));
+    LACT_TRY(make_operand(kb_of(upd), &upd.a[0], &upd.ai[0], X, 0, kBM, 0, 0));
+    LACT_TRY(make_operand(kb_of(upd), &upd.b[0], &upd.bi[0], PB, 0, bt_mn, 0, 0));
   }
   upd.M = ns_upd_rows(G); upd.N = ns_upd_cols(G); upd.K = G.m; upd.batch = G.nmat;
   LACT_TRY(make_output(&upd.out[0], &upd.oi[0], XN, 0, 0));
@@ -568,7 +601,7 @@ int launch_ns_fused(const NsGroup* grp, int ngroups, int steps, int const_coeffs
   auto kernel = ns_fused_kernel<BT_MM, BT_MN>;
   constexpr uint32_t smem = ns_fused_smem_bytes<BT_MM, BT_MN>();
   static_assert(smem <= 232448, "shared memory budget exceeded");
-  static_assert(ns_fused_ring<BT_MM, BT_MN>() >= 3, "ring too shallow");
+  static_assert(ns_fused_ring<BT_MM, BT_MN>() >= 2, "ring too shallow");
   static std::mutex mu;
   static bool configured[64] = {false};
   int dev = 0;
@@ -1292,8 +1325,8 @@ int lact_bmm2_bf16(const void* a0, int32_t a0_mn, const void* b0, int32_t b0_mn,
   if (a1 == nullptr) {
     auto fill = [&](auto& g, int btv) -> int {
       auto& P = g.prob[0];
-      LACT_TRY(make_operand(&P.a[0], &P.ai[0], mat(a0, a0_mn, M), a0_mn, kBM, 0, 0));
-      LACT_TRY(make_operand(&P.b[0], &P.bi[0], mat(b0, b0_mn, N), b0_mn, btv, 0, 0));
+      LACT_TRY(make_operand(kb_of(P), &P.a[0], &P.ai[0], mat(a0, a0_mn, M), a0_mn, kBM, 0, 0));
+      LACT_TRY(make_operand(kb_of(P), &P.b[0], &P.bi[0], mat(b0, b0_mn, N), b0_mn, btv, 0, 0));
       P.M = static_cast<int>(M); P.N = static_cast<int>(N); P.K = static_cast<int>(K);
       P.batch = static_cast<int>(batch);
       P.ep = ep;
@@ -1304,10 +1337,10 @@ int lact_bmm2_bf16(const void* a0, int32_t a0_mn, const void* b0, int32_t b0_mn,
   }
   auto fill2 = [&](auto& g, int btv) -> int {
     auto& P = g.prob[0];
-    LACT_TRY(make_operand(&P.a[0], &P.ai[0], mat(a0, a0_mn, M), a0_mn, kBM, 0, 0));
-    LACT_TRY(make_operand(&P.b[0], &P.bi[0], mat(b0, b0_mn, N), b0_mn, btv, 0, 0));
-    LACT_TRY(make_operand(&P.a[1], &P.ai[1], mat(a1, a1_mn, M), a1_mn, kBM, 0, 0));
-    LACT_TRY(make_operand(&P.b[1], &P.bi[1], mat(b1, b1_mn, N), b1_mn, btv, 0, 0));
+    LACT_TRY(make_operand(kb_of(P), &P.a[0], &P.ai[0], mat(a0, a0_mn, M), a0_mn, kBM, 0, 0));
+    LACT_TRY(make_operand(kb_of(P), &P.b[0], &P.bi[0], mat(b0, b0_mn, N), b0_mn, btv, 0, 0));
+    LACT_TRY(make_operand(kb_of(P), &P.a[1], &P.ai[1], mat(a1, a1_mn, M), a1_mn, kBM, 0, 0));
+    LACT_TRY(make_operand(kb_of(P), &P.b[1], &P.bi[1], mat(b1, b1_mn, N), b1_mn, btv, 0, 0));
     P.M = static_cast<int>(M); P.N = static_cast<int>(N); P.K = static_cast<int>(K);
     P.batch = static_cast<int>(batch);
     P.ep = ep;
@@ -1437,8 +1470,8 @@ int lact_bmm_bf16(const void* a, int32_t a_mn_major, const void* b, int32_t b_mn
   const Mat Bm = b_mn_major ? Mat{b, K, N, N, batch, K * N} : Mat{b, N, K, K, batch, N * K};
   auto fill = [&](auto& g, int btv) -> int {
     auto& P = g.prob[0];
-    LACT_TRY(make_operand(&P.a[0], &P.ai[0], A, a_mn_major, kBM, 0, 0));
-    LACT_TRY(make_operand(&P.b[0], &P.bi[0], Bm, b_mn_major, btv, 0, 0));
+    LACT_TRY(make_operand(kb_of(P), &P.a[0], &P.ai[0], A, a_mn_major, kBM, 0, 0));
+    LACT_TRY(make_operand(kb_of(P), &P.b[0], &P.bi[0], Bm, b_mn_major, btv, 0, 0));
     P.M = static_cast<int>(M); P.N = static_cast<int>(N); P.K = static_cast<int>(K);
     P.batch = static_cast<int>(batch);
     P.ep = EpiStore{c, M * N, N, 0, 1, 0};
@@ -1447,8 +1480,8 @@ int lact_bmm_bf16(const void* a, int32_t a_mn_major, const void* b, int32_t b_mn
   };
   auto fill_bf16 = [&](auto& g, int btv) -> int {
     auto& P = g.prob[0];
-    LACT_TRY(make_operand(&P.a[0], &P.ai[0], A, a_mn_major, kBM, 0, 0));
-    LACT_TRY(make_operand(&P.b[0], &P.bi[0], Bm, b_mn_major, btv, 0, 0));
+    LACT_TRY(make_operand(kb_of(P), &P.a[0], &P.ai[0], A, a_mn_major, kBM, 0, 0));
+    LACT_TRY(make_operand(kb_of(P), &P.b[0], &P.bi[0], Bm, b_mn_major, btv, 0, 0));
     LACT_TRY(make_output(&P.out[0], &P.oi[0], Mat{c, M, N, N, batch, M * N}, 0, 0));
     P.M = static_cast<int>(M); P.N = static_cast<int>(N); P.K = static_cast<int>(K);
     P.batch = static_cast<int>(batch);

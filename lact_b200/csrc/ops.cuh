@@ -174,6 +174,12 @@ struct EpiFwGrad {
 // Ops without global epilogue operands prefetch nothing.
 struct NoPrefetch {};
 
+// k-blocks per ring stage: two when two such stages fit next to `staging` bytes (each operand tile of a
+// stage then arrives as ONE TMA box spanning both k-blocks: the load path is bound by the number of
+// boxes, not by bytes), else one
+__host__ __device__ constexpr int kb_per_stage(uint32_t kblock_bytes, uint32_t staging) {
+  return (232448u - 1024u - 256u - staging) / (2 * kblock_bytes) >= 2 ? 2 : 1;
+}
 // ring depth that fits 227 KB next to `staging` bytes of output tiles
 __host__ __device__ constexpr int ring_depth(uint32_t stage_bytes, uint32_t staging) {
   return static_cast<int>((232448u - 1024u - 256u - staging) / stage_bytes) > 8
@@ -187,7 +193,8 @@ struct OpBmm {
   static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 0;
   static constexpr bool kSecondInPlace = false, kTileReduce = false;
   static constexpr int kStagingBuffers = 1;
-  static constexpr int STAGES = ring_depth(kATileBytes + BT_ * kBK * 2, 0);
+  static constexpr int KB = 1;  // measured: two-k-block stages slow the training backward's products by 7 %
+  static constexpr int STAGES = ring_depth(KB * (kATileBytes + BT_ * kBK * 2), 0);
   using Epi = EpiT;
   __host__ __device__ static constexpr int term_a(int) { return 0; }
   __host__ __device__ static constexpr int term_b(int) { return 0; }
@@ -210,7 +217,8 @@ struct OpDW {
   static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 0;
   static constexpr bool kSecondInPlace = false, kTileReduce = true;
   static constexpr int kStagingBuffers = 1;
-  static constexpr int STAGES = ring_depth(kATileBytes + BT_ * kBK * 2, 0);
+  static constexpr int KB = kb_per_stage(kATileBytes + BT_ * kBK * 2, 0);
+  static constexpr int STAGES = ring_depth(KB * (kATileBytes + BT_ * kBK * 2), 0);
   using Epi = EpiDW;
   __host__ __device__ static constexpr int term_a(int) { return 0; }
   __host__ __device__ static constexpr int term_b(int) { return 0; }
@@ -243,7 +251,8 @@ struct OpBmmStore {
   static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 1;
   static constexpr bool kSecondInPlace = false, kTileReduce = false;
   static constexpr int kStagingBuffers = 1;
-  static constexpr int STAGES = ring_depth(kATileBytes + BT_ * kBK * 2, kBM * BT_ * 2);
+  static constexpr int KB = 1;  // measured: two-k-block stages are 5 % slower for this op (K-major operands, short K)
+  static constexpr int STAGES = ring_depth(KB * (kATileBytes + BT_ * kBK * 2), kBM * BT_ * 2);
   using Epi = EpiNone;
   __host__ __device__ static constexpr int term_a(int) { return 0; }
   __host__ __device__ static constexpr int term_b(int) { return 0; }
@@ -266,7 +275,8 @@ struct OpBmm2 {
   static constexpr int NA = 2, NB = 2, NACC = 1, BT = BT_, NTERMS = 2, NOUT = 0;
   static constexpr bool kSecondInPlace = false, kTileReduce = false;
   static constexpr int kStagingBuffers = 1;
-  static constexpr int STAGES = ring_depth(2 * kATileBytes + 2 * BT_ * kBK * 2, 0);
+  static constexpr int KB = 1;
+  static constexpr int STAGES = ring_depth(KB * (2 * kATileBytes + 2 * BT_ * kBK * 2), 0);
   using Epi = EpiT;
   __host__ __device__ static constexpr int term_a(int t) { return t; }
   __host__ __device__ static constexpr int term_b(int t) { return t; }
@@ -295,9 +305,10 @@ template <int BT_>
 struct OpNs {
   static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 2;
   static constexpr bool kSecondInPlace = true, kTileReduce = false;
-  // two staging tiles: tile i + 1 is assembled in one while tile i is still being stored from the other
-  static constexpr int kStagingBuffers = 2;
-  static constexpr int STAGES = ring_depth(kATileBytes + BT_ * kBK * 2, kStagingBuffers * kBM * BT_ * 2);
+  // one staging tile (a second one would leave room for a single two-k-block stage only)
+  static constexpr int kStagingBuffers = 1;
+  static constexpr int KB = kb_per_stage(kATileBytes + BT_ * kBK * 2, kStagingBuffers * kBM * BT_ * 2);
+  static constexpr int STAGES = ring_depth(KB * (kATileBytes + BT_ * kBK * 2), kStagingBuffers * kBM * BT_ * 2);
   using Epi = EpiNs;
   __host__ __device__ static constexpr int term_a(int) { return 0; }
   __host__ __device__ static constexpr int term_b(int) { return 0; }
@@ -325,19 +336,22 @@ struct OpNs {
   }
 };
 
-// [y0 | y2] = x [w0 slice ; w2 slice]^T as ONE 128 x 2BT MMA (the two weight tiles are adjacent
-// in shared memory); epilogue = SwiGLU gate, staged.
+// [y0 | y2] = x [w0 slice ; w2 slice]^T; epilogue = SwiGLU gate, staged.  With one k-block per stage
+// the two weight tiles are adjacent in shared memory and one 128 x 2BT MMA covers both; with two
+// k-blocks per stage each tile holds its k-blocks back to back, so the product is two 128 x BT MMAs
+// into adjacent accumulator columns.
 template <int BT_>
 struct OpSwigluGate {
-  static constexpr int NA = 1, NB = 2, NACC = 2, BT = BT_, NTERMS = 1, NOUT = 1;
+  static constexpr int KB = 1;  // measured: two-k-block stages (a 2-deep ring here) are 7 % slower for this op
+  static constexpr int NA = 1, NB = 2, NACC = 2, BT = BT_, NTERMS = KB, NOUT = 1;
   static constexpr bool kSecondInPlace = false, kTileReduce = false;
   static constexpr int kStagingBuffers = 1;
-  static constexpr int STAGES = ring_depth(kATileBytes + 2 * BT_ * kBK * 2, kBM * BT_ * 2);
+  static constexpr int STAGES = ring_depth(KB * (kATileBytes + 2 * BT_ * kBK * 2), kBM * BT_ * 2);
   using Epi = EpiNone;
   __host__ __device__ static constexpr int term_a(int) { return 0; }
-  __host__ __device__ static constexpr int term_b(int) { return 0; }
-  __host__ __device__ static constexpr int term_col(int) { return 0; }
-  __host__ __device__ static constexpr int term_n(int) { return 2 * BT_; }
+  __host__ __device__ static constexpr int term_b(int t) { return t; }
+  __host__ __device__ static constexpr int term_col(int t) { return t * BT_; }
+  __host__ __device__ static constexpr int term_n(int) { return KB == 2 ? BT_ : 2 * BT_; }
   __host__ __device__ static constexpr bool term_first(int) { return true; }
   using Prefetch = NoPrefetch;
   __device__ static __forceinline__ void prefetch(const Epi&, int, int, int, int, int, int, Prefetch&) {}
@@ -359,7 +373,8 @@ struct OpFwGradPointwise {
   static constexpr int NA = 2, NB = 3, NACC = 3, BT = 64, NTERMS = 2, NOUT = 3;
   static constexpr bool kSecondInPlace = false, kTileReduce = false;
   static constexpr int kStagingBuffers = 1;
-  static constexpr int STAGES = ring_depth(2 * kATileBytes + 3 * 64 * kBK * 2, 3 * kBM * 64 * 2);
+  static constexpr int KB = 1;  // two k-blocks of this op's five tiles would leave a one-stage ring
+  static constexpr int STAGES = ring_depth(KB * (2 * kATileBytes + 3 * 64 * kBK * 2), 3 * kBM * 64 * 2);
   using Epi = EpiFwGrad;
   __host__ __device__ static constexpr int term_a(int t) { return t; }
   __host__ __device__ static constexpr int term_b(int t) { return t == 0 ? 0 : 2; }

@@ -21,6 +21,7 @@ constexpr uint32_t kAtomBytes = 64 * kBK * 2;  // one 64(mn) x 64(k) MN-major at
 
 struct OperandInfo {
   int32_t mn_major;   // 0: global [mn][k] (k contiguous); 1: global [k][mn] (mn contiguous)
+  int32_t k4d;        // K-major only: the map is 4-D (64 k, rows, k-blocks, batch) and one box spans the stage's k-blocks
   int32_t mn_off;     // added to the mn coordinate
   int32_t k_off;      // added to the k coordinate
   int32_t batch_off;  // added to the batch coordinate
@@ -46,6 +47,7 @@ struct GemmProblem {
 
 template <class Op, int NPROB>
 struct GemmArgs {
+  using OpType = Op;
   GemmProblem<Op> prob[NPROB];
   int32_t* status;  // device status word (0 = ok)
 };
@@ -65,7 +67,7 @@ __host__ __device__ constexpr uint32_t tmem_cols_pow2(uint32_t n) {
 // of tile i overlaps the main loop of tile i + 1.
 template <class Op>
 __host__ __device__ constexpr uint32_t gemm_stage_bytes() {
-  return Op::NA * kATileBytes + Op::NB * Op::BT * kBK * 2;
+  return Op::KB * (Op::NA * kATileBytes + Op::NB * Op::BT * kBK * 2);
 }
 // bf16 staging tiles for TMA-stored outputs: NOUT x [128 rows][BT columns], 128-byte swizzled in
 // 64-column panels (the layout the output tensor maps expect)
@@ -84,22 +86,36 @@ constexpr int kGemmThreadsV2 = 64 + 32 * kEpiWarps;  // producer warp + MMA warp
 // every tile's dependency, so that the global-memory latency of that check never stalls the loads
 constexpr int kGemmThreadsFlow = kGemmThreadsV2 + 32;
 
-template <int ROWS>
+// One operand tile of a ring stage: ROWS (mn) x KB k-blocks.  Shared-memory layout:
+//   K-major:  [k-block][ROWS rows][64 k] (KB tiles of ROWS x 128 bytes back to back);
+//   MN-major: per 64-wide mn atom [KB * 64 k rows][64 mn] (atoms KB * 8 KB apart).
+// With KB = 2 a K-major tile arrives as one box of a 4-D map when the operand allows it (k4d), an
+// MN-major tile as one 128-k-row box per atom.
+template <int ROWS, int KB>
 __device__ __forceinline__ void load_operand_tile(uint32_t dst, const CUtensorMap* map, const OperandInfo& oi,
                                                   int mn0, int kc, int batch, uint64_t* bar) {
   if (!oi.mn_major) {
-    tma_load_3d(dst, map, bar, oi.k_off + kc, oi.mn_off + mn0, oi.batch_off + batch);
+    if (KB == 2 && oi.k4d) {
+      tma_load_4d(dst, map, bar, 0, oi.mn_off + mn0, (oi.k_off + kc) / kBK, oi.batch_off + batch);
+    } else {
+#pragma unroll
+      for (int kk = 0; kk < KB; ++kk)
+        tma_load_3d(dst + kk * (ROWS * kBK * 2), map, bar, oi.k_off + kc + kk * kBK, oi.mn_off + mn0, oi.batch_off + batch);
+    }
   } else {
 #pragma unroll
     for (int j = 0; j < ROWS / 64; ++j)
-      tma_load_3d(dst + j * kAtomBytes, map, bar, oi.mn_off + mn0 + 64 * j, oi.k_off + kc, oi.batch_off + batch);
+      tma_load_3d(dst + j * (KB * kAtomBytes), map, bar, oi.mn_off + mn0 + 64 * j, oi.k_off + kc, oi.batch_off + batch);
   }
 }
 
-__device__ __forceinline__ uint64_t operand_desc(uint32_t tile, int mn_major, int k4) {
+// Descriptor of the k-block `kk`, 16-element k-slice `k4`, of an operand tile of ROWS_BYTES = rows * 128.
+template <int KB>
+__device__ __forceinline__ uint64_t operand_desc(uint32_t tile, int mn_major, uint32_t rows_bytes, int kk, int k4) {
   // K-major: advance 16 elements (32 bytes) inside the swizzled 128-byte row.
-  // MN-major: advance 16 k-rows (2 groups of 8 rows x 128 bytes).
-  return mn_major ? make_smem_desc(tile + k4 * 2048, kAtomBytes, 1024) : make_smem_desc(tile + k4 * 32, 0, 1024);
+  // MN-major: advance 16 k-rows (2 groups of 8 rows x 128 bytes); atoms are KB * 8 KB apart.
+  return mn_major ? make_smem_desc(tile + kk * kAtomBytes + k4 * 2048, KB * kAtomBytes, 1024)
+                  : make_smem_desc(tile + kk * rows_bytes + k4 * 32, 0, 1024);
 }
 
 struct TileCoord {
@@ -212,8 +228,8 @@ __device__ __forceinline__ int snake_tile(int round, int grid, int cta) {
 template <class Op, int RING, class EpiPatch, class Deps = NoDeps>
 __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* probs, const int nprob,
                                            EpiPatch patch, Deps deps = Deps{}) {
-  constexpr int BT = Op::BT, NA = Op::NA, NB = Op::NB, NACC = Op::NACC;
-  constexpr uint32_t kBTileBytes = BT * kBK * 2;
+  constexpr int BT = Op::BT, NA = Op::NA, NB = Op::NB, NACC = Op::NACC, KB = Op::KB;
+  constexpr uint32_t kBTileBytes = BT * kBK * 2;  // one k-block of a B tile
   constexpr uint32_t kStageBytes = gemm_stage_bytes<Op>();
   constexpr uint32_t kAccCols = NACC * BT;
   constexpr int kMaxProb = 2;
@@ -269,21 +285,22 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
           if (!flow_wait_verified(cx, cx.ptile++)) { failed = true; break; }  // the scout warp checked this tile
           asm volatile("fence.proxy.async;" ::: "memory");
         }
-        for (int kb = 0; kb < num_kb; ++kb, ++cx.it) {
+        const int num_sb = (num_kb + KB - 1) / KB;  // ring stages of KB k-blocks
+        for (int sb = 0; sb < num_sb; ++sb, ++cx.it) {
           const int s = cx.it % RING;
           const uint32_t ph = (cx.it / RING) & 1;
           if (!mbar_wait(&cx.empty_bar[s], ph ^ 1, cx.abort_flag)) { failed = true; break; }
-          if (kb == num_kb - 1) cx.stamp(tile_i, 0);
+          if (sb == num_sb - 1) cx.stamp(tile_i, 0);
           mbar_expect_tx(&cx.full_bar[s], kStageBytes);
           const uint32_t st = cx.smem_base + s * cx.stage_stride;
-          const int kc = kb * kBK;
+          const int kc = sb * KB * kBK;
 #pragma unroll
           for (int i = 0; i < NA; ++i)
-            load_operand_tile<kBM>(st + i * kATileBytes, &P.a[i], P.ai[i], tc.m0, kc, tc.batch, &cx.full_bar[s]);
+            load_operand_tile<kBM, KB>(st + i * (KB * kATileBytes), &P.a[i], P.ai[i], tc.m0, kc, tc.batch, &cx.full_bar[s]);
 #pragma unroll
           for (int i = 0; i < NB; ++i)
-            load_operand_tile<BT>(st + NA * kATileBytes + i * kBTileBytes, &P.b[i], P.bi[i], tc.n0, kc, tc.batch,
-                                  &cx.full_bar[s]);
+            load_operand_tile<BT, KB>(st + NA * (KB * kATileBytes) + i * (KB * kBTileBytes), &P.b[i], P.bi[i], tc.n0, kc,
+                                      tc.batch, &cx.full_bar[s]);
         }
       }
     }
@@ -300,24 +317,29 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
         if (!mbar_wait(&cx.acc_empty_bar[as], aph ^ 1, cx.abort_flag)) { failed = true; break; }
         tc_fence_after();
         const uint32_t acc_base = cx.tmem_base + as * kAccCols;
-        for (int kb = 0; kb < num_kb; ++kb, ++cx.it) {
+        const int num_sb = (num_kb + KB - 1) / KB;
+        for (int sb = 0; sb < num_sb; ++sb, ++cx.it) {
           const int s = cx.it % RING;
           const uint32_t ph = (cx.it / RING) & 1;
           if (!mbar_wait(&cx.full_bar[s], ph, cx.abort_flag)) { failed = true; break; }
           tc_fence_after();
           const uint32_t st = cx.smem_base + s * cx.stage_stride;
 #pragma unroll
-          for (int t = 0; t < Op::NTERMS; ++t) {
-            const int ia = Op::term_a(t), ib = Op::term_b(t);
-            const int a_mn = P.ai[ia].mn_major, b_mn = P.bi[ib].mn_major;
-            const uint32_t idesc = make_idesc_bf16(kBM, Op::term_n(t), a_mn, b_mn);
-            const uint32_t a_tile = st + ia * kATileBytes;
-            const uint32_t b_tile = st + NA * kATileBytes + ib * kBTileBytes;
+          for (int kk = 0; kk < KB; ++kk) {
+            if (sb * KB + kk >= num_kb) break;  // a trailing half-empty stage
 #pragma unroll
-            for (int k4 = 0; k4 < kBK / kUmmaK; ++k4) {
-              const uint32_t acc = (kb > 0 || k4 > 0 || !Op::term_first(t)) ? 1u : 0u;
-              umma_bf16(acc_base + Op::term_col(t), operand_desc(a_tile, a_mn, k4), operand_desc(b_tile, b_mn, k4),
-                        idesc, acc);
+            for (int t = 0; t < Op::NTERMS; ++t) {
+              const int ia = Op::term_a(t), ib = Op::term_b(t);
+              const int a_mn = P.ai[ia].mn_major, b_mn = P.bi[ib].mn_major;
+              const uint32_t idesc = make_idesc_bf16(kBM, Op::term_n(t), a_mn, b_mn);
+              const uint32_t a_tile = st + ia * (KB * kATileBytes);
+              const uint32_t b_tile = st + NA * (KB * kATileBytes) + ib * (KB * kBTileBytes);
+#pragma unroll
+              for (int k4 = 0; k4 < kBK / kUmmaK; ++k4) {
+                const uint32_t acc = (sb > 0 || kk > 0 || k4 > 0 || !Op::term_first(t)) ? 1u : 0u;
+                umma_bf16(acc_base + Op::term_col(t), operand_desc<KB>(a_tile, a_mn, kATileBytes, kk, k4),
+                          operand_desc<KB>(b_tile, b_mn, kBTileBytes, kk, k4), idesc, acc);
+              }
             }
           }
           umma_commit(&cx.empty_bar[s]);  // frees the stage once these MMAs have read it
