@@ -131,10 +131,7 @@ ns_fused_kernel(const __grid_constant__ NsFusedArgs<BT_MM, BT_MN> args) {
     for (int g = 0; g < 2; ++g) deps.need[g] += tiles_mn[g];
   }
   if (failed) *cx.abort_flag = 1;
-  if (threadIdx.x == 64) {  // the storing thread: this CTA's last tiles are in global memory
-    flow_flush(cx);
-    bulk_wait_all();
-  }
+  // (the storing thread published every tile of this CTA after its stores had landed)
   if (args.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 64) args.trace[1] = globaltimer_ns();
 
   gemm_teardown(cx, failed, args.status, kTmemCols);

@@ -105,43 +105,57 @@ struct EpiDW {
   int32_t tiles_m, tiles_n;
   // optional: bf16 copy of g with the same strides (the first Newton-Schulz iterate before scaling)
   bf16* gb;
-  // returns the sum of squares of the bf16-rounded results of this row segment if `want_ss`
-  __device__ __forceinline__ float operator()(int batch, int row, int col, int M, int N, const float* v,
-                                              bool want_ss = false) const {
-    if (row >= M) return 0.f;
-    const int valid = min(32, N - col);
-    const int64_t idx = batch * bs + static_cast<int64_t>(row) * ld + col;
-    float r[32];
+  // One warp's 32 x 32 block of results, thread `lane` holding row `row0 + lane` in v[0..31].  The block goes
+  // through `scratch` (this warp's 32 x 144 bytes of shared memory) so that the read-modify-write of the fp32
+  // state is issued with eight lanes per 128-byte row segment (four full lines per instruction) instead of one
+  // row per lane.  Returns this lane's share of the sum of squares of the bf16-rounded results if `want_ss`.
+  __device__ __forceinline__ float warp_block(int batch, int row0, int col, int M, int N, const float* v,
+                                              uint32_t scratch, int lane, bool want_ss) const {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) r[j] = round_bf16 ? bf16_round(v[j]) : v[j];
-    if (out_f32) {
-      float* gp = reinterpret_cast<float*>(g) + idx;
-      if (beta != nullptr) {
-        const float bt = beta[batch];
+    for (int gq = 0; gq < 8; ++gq) {
+      float r[4];
 #pragma unroll
-        for (int gq = 0; gq < 8; ++gq) {
-          if (gq * 4 < valid) {
-            const float4 old = *reinterpret_cast<const float4*>(gp + gq * 4);
-            r[gq * 4 + 0] += old.x * bt;
-            r[gq * 4 + 1] += old.y * bt;
-            r[gq * 4 + 2] += old.z * bt;
-            r[gq * 4 + 3] += old.w * bt;
-          }
-        }
-      }
-      store_row32_f32(gp, r, valid);
-    } else {
-      store_row32_bf16(reinterpret_cast<bf16*>(g) + idx, r, valid);
+      for (int j = 0; j < 4; ++j) r[j] = round_bf16 ? bf16_round(v[gq * 4 + j]) : v[gq * 4 + j];
+      asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(scratch + lane * 144 + gq * 16), "f"(r[0]), "f"(r[1]),
+                   "f"(r[2]), "f"(r[3])
+                   : "memory");
     }
-    if (gb != nullptr) store_row32_bf16(gb + idx, r, valid);
+    __syncwarp();
+    const int u = lane & 7, rsub = lane >> 3;
+    const bool col_ok = col + u * 4 + 4 <= N;
+    const bool rmw = out_f32 && beta != nullptr;
+    const float bt = rmw ? beta[batch] : 0.f;
+    const int64_t base = batch * bs + col + u * 4;
+    float4 old[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int row = row0 + i * 4 + rsub;
+      old[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (rmw && col_ok && row < M)
+        old[i] = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(g) + base + static_cast<int64_t>(row) * ld);
+    }
     float ss = 0.f;
-    if (want_ss) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const float x = bf16_round(r[j]);
-        ss += (j < valid) ? x * x : 0.f;
+    for (int i = 0; i < 8; ++i) {
+      const int rr = i * 4 + rsub, row = row0 + rr;
+      if (!col_ok || row >= M) continue;
+      float4 x;
+      asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                   : "=f"(x.x), "=f"(x.y), "=f"(x.z), "=f"(x.w)
+                   : "r"(scratch + rr * 144 + u * 16)
+                   : "memory");
+      x.x += old[i].x * bt; x.y += old[i].y * bt; x.z += old[i].z * bt; x.w += old[i].w * bt;
+      const int64_t idx = base + static_cast<int64_t>(row) * ld;
+      const uint2 xb = make_uint2(pack_bf16x2(x.x, x.y), pack_bf16x2(x.z, x.w));
+      if (out_f32) *reinterpret_cast<float4*>(reinterpret_cast<float*>(g) + idx) = x;
+      else *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(g) + idx) = xb;
+      if (gb != nullptr) *reinterpret_cast<uint2*>(gb + idx) = xb;
+      if (want_ss) {
+        const float a = bf16_round(x.x), b = bf16_round(x.y), c = bf16_round(x.z), d = bf16_round(x.w);
+        ss += a * a + b * b + c * c + d * d;
       }
     }
+    __syncwarp();  // the scratch block is rewritten by the next call
     return ss;
   }
 };
@@ -193,6 +207,8 @@ struct OpBmm {
   static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 0;
   static constexpr bool kSecondInPlace = false, kTileReduce = false;
   static constexpr int kStagingBuffers = 1;
+  static constexpr bool kWarpTranspose = false, kReverseBatch = false;
+  static constexpr uint32_t kEpiScratch = 0;
   static constexpr int KB = 1;  // measured: two-k-block stages slow the training backward's products by 7 %
   static constexpr int STAGES = ring_depth(KB * (kATileBytes + BT_ * kBK * 2), 0);
   using Epi = EpiT;
@@ -217,8 +233,11 @@ struct OpDW {
   static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 0;
   static constexpr bool kSecondInPlace = false, kTileReduce = true;
   static constexpr int kStagingBuffers = 1;
-  static constexpr int KB = kb_per_stage(kATileBytes + BT_ * kBK * 2, 0);
-  static constexpr int STAGES = ring_depth(KB * (kATileBytes + BT_ * kBK * 2), 0);
+  static constexpr bool kWarpTranspose = true;                   // results reach global memory through `EpiDW::warp_block`
+  static constexpr bool kReverseBatch = true;                    // reads the planes the pointwise kernel has just written
+  static constexpr uint32_t kEpiScratch = kEpiWarps * 32 * 144;  // one 32 x 32 fp32 block (rows padded to 144 bytes) per epilogue warp
+  static constexpr int KB = kb_per_stage(kATileBytes + BT_ * kBK * 2, kEpiScratch);
+  static constexpr int STAGES = ring_depth(KB * (kATileBytes + BT_ * kBK * 2), kEpiScratch);
   using Epi = EpiDW;
   __host__ __device__ static constexpr int term_a(int) { return 0; }
   __host__ __device__ static constexpr int term_b(int) { return 0; }
@@ -231,9 +250,10 @@ struct OpDW {
   __device__ static __forceinline__ void prefetch(const Epi&, int, int, int, int, int, int, Prefetch& pf) {
     pf.acc = 0.f;
   }
-  __device__ static __forceinline__ void epilogue(const Epi& ep, int batch, int row, int col, int M, int N,
-                                                  const float (&v)[1][32], Prefetch& pf, int) {
-    pf.acc += ep(batch, row, col, M, N, v[0], ep.partial != nullptr);
+  __device__ static __forceinline__ void epilogue_warp(const Epi& ep, int batch, int row0, int col, int M, int N,
+                                                       const float (&v)[1][32], Prefetch& pf, uint32_t scratch,
+                                                       int lane) {
+    pf.acc += ep.warp_block(batch, row0, col, M, N, v[0], scratch, lane, ep.partial != nullptr);
   }
   __device__ static __forceinline__ float tile_value(const Prefetch& pf) { return pf.acc; }
   __device__ static __forceinline__ void tile_store(const Epi& ep, int batch, int tile_m, int tile_n, int warp_slot,
@@ -251,6 +271,8 @@ struct OpBmmStore {
   static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 1;
   static constexpr bool kSecondInPlace = false, kTileReduce = false;
   static constexpr int kStagingBuffers = 1;
+  static constexpr bool kWarpTranspose = false, kReverseBatch = false;
+  static constexpr uint32_t kEpiScratch = 0;
   static constexpr int KB = 1;  // measured: two-k-block stages are 5 % slower for this op (K-major operands, short K)
   static constexpr int STAGES = ring_depth(KB * (kATileBytes + BT_ * kBK * 2), kBM * BT_ * 2);
   using Epi = EpiNone;
@@ -275,6 +297,8 @@ struct OpBmm2 {
   static constexpr int NA = 2, NB = 2, NACC = 1, BT = BT_, NTERMS = 2, NOUT = 0;
   static constexpr bool kSecondInPlace = false, kTileReduce = false;
   static constexpr int kStagingBuffers = 1;
+  static constexpr bool kWarpTranspose = false, kReverseBatch = false;
+  static constexpr uint32_t kEpiScratch = 0;
   static constexpr int KB = 1;
   static constexpr int STAGES = ring_depth(KB * (2 * kATileBytes + 2 * BT_ * kBK * 2), 0);
   using Epi = EpiT;
@@ -307,6 +331,8 @@ struct OpNs {
   static constexpr bool kSecondInPlace = true, kTileReduce = false;
   // one staging tile (a second one would leave room for a single two-k-block stage only)
   static constexpr int kStagingBuffers = 1;
+  static constexpr bool kWarpTranspose = false, kReverseBatch = false;
+  static constexpr uint32_t kEpiScratch = 0;
   static constexpr int KB = kb_per_stage(kATileBytes + BT_ * kBK * 2, kStagingBuffers * kBM * BT_ * 2);
   static constexpr int STAGES = ring_depth(KB * (kATileBytes + BT_ * kBK * 2), kStagingBuffers * kBM * BT_ * 2);
   using Epi = EpiNs;
@@ -346,6 +372,8 @@ struct OpSwigluGate {
   static constexpr int NA = 1, NB = 2, NACC = 2, BT = BT_, NTERMS = KB, NOUT = 1;
   static constexpr bool kSecondInPlace = false, kTileReduce = false;
   static constexpr int kStagingBuffers = 1;
+  static constexpr bool kWarpTranspose = false, kReverseBatch = false;
+  static constexpr uint32_t kEpiScratch = 0;
   static constexpr int STAGES = ring_depth(KB * (kATileBytes + 2 * BT_ * kBK * 2), kBM * BT_ * 2);
   using Epi = EpiNone;
   __host__ __device__ static constexpr int term_a(int) { return 0; }
@@ -373,6 +401,8 @@ struct OpFwGradPointwise {
   static constexpr int NA = 2, NB = 3, NACC = 3, BT = 64, NTERMS = 2, NOUT = 3;
   static constexpr bool kSecondInPlace = false, kTileReduce = false;
   static constexpr int kStagingBuffers = 1;
+  static constexpr bool kWarpTranspose = false, kReverseBatch = false;
+  static constexpr uint32_t kEpiScratch = 0;
   static constexpr int KB = 1;  // two k-blocks of this op's five tiles would leave a one-stage ring
   static constexpr int STAGES = ring_depth(KB * (2 * kATileBytes + 3 * 64 * kBK * 2), 3 * kBM * 64 * 2);
   using Epi = EpiFwGrad;

@@ -73,7 +73,7 @@ __host__ __device__ constexpr uint32_t gemm_stage_bytes() {
 // 64-column panels (the layout the output tensor maps expect)
 template <class Op>
 __host__ __device__ constexpr uint32_t gemm_staging_bytes() {
-  return Op::kStagingBuffers * (Op::kSecondInPlace ? 1 : Op::NOUT) * kBM * Op::BT * 2;
+  return Op::kStagingBuffers * (Op::kSecondInPlace ? 1 : Op::NOUT) * kBM * Op::BT * 2 + Op::kEpiScratch;
 }
 template <class Op>
 __host__ __device__ constexpr uint32_t gemm_smem_bytes() {
@@ -84,7 +84,7 @@ constexpr int kEpiWarps = 8;
 constexpr int kGemmThreadsV2 = 64 + 32 * kEpiWarps;  // producer warp + MMA warp + epilogue warps
 // dataflow kernels add a scout warp that walks the tile sequence ahead of the producer and checks
 // every tile's dependency, so that the global-memory latency of that check never stalls the loads
-constexpr int kGemmThreadsFlow = kGemmThreadsV2 + 32;
+constexpr int kGemmThreadsFlow = kGemmThreadsV2 + 64;  // + dependency scout warp + storing warp
 
 // One operand tile of a ring stage: ROWS (mn) x KB k-blocks.  Shared-memory layout:
 //   K-major:  [k-block][ROWS rows][64 k] (KB tiles of ROWS x 128 bytes back to back);
@@ -131,13 +131,14 @@ struct GemmCtx {
   uint32_t stage_stride;  // bytes between ring stages (>= the op's stage bytes)
   uint32_t staging;       // 1024-byte aligned start of the output staging tiles
   uint64_t *full_bar, *empty_bar, *acc_full_bar, *acc_empty_bar;
+  uint64_t *stg_full_bar, *stg_empty_bar;  // dataflow kernels: staging tile handed to / returned by the storing warp
   volatile uint32_t* abort_flag;
   uint32_t tmem_base;
   uint32_t it = 0, tcount = 0;
   // dataflow mode (multi-phase kernels whose phases are ordered by completion counters, see FlowDeps)
   uint32_t rot = 0;              // tiles handed out by earlier phases, modulo the grid size
   uint32_t ptile = 0;            // tiles whose dependency the producer thread has verified
-  uint32_t* pend = nullptr;      // completion counter of the last stored, not yet signalled tile (storing thread)
+  uint32_t sround = 0;           // staging hand-overs so far (epilogue threads and the storing thread count alike)
   uint32_t* dep_ok = nullptr;    // shared-memory word: the producer's `ptile`, read by the storing thread
   // optional diagnostics (CTA 0 only): per phase < 6 and tile < 4, globaltimer stamps of
   // {loads issued, MMAs committed, epilogue started, epilogue finished} at trace[40 + 16*phase + 4*tile + k]
@@ -191,18 +192,15 @@ __device__ __forceinline__ bool dep_wait(const uint32_t* ctr, uint32_t need, vol
     if ((i & 31u) == 0 && (*abort_flag != 0 || globaltimer_ns() - t0 > kWaitLimitNs)) return false;
   }
 }
-// Storing thread: once the stores of the last tile have landed, publish its completion.
-__device__ __forceinline__ void flow_flush(GemmCtx& cx) {
-  if (cx.pend != nullptr) {
-    bulk_wait_all();
-    asm volatile("fence.proxy.async;" ::: "memory");
-    __threadfence();
-    atomicAdd(cx.pend, 1u);
-    cx.pend = nullptr;
-  }
+// Storing thread: once all its stores have landed, publish the completion of a tile.
+__device__ __forceinline__ void flow_publish(uint32_t* counter) {
+  bulk_wait_all();
+  asm volatile("fence.proxy.async;" ::: "memory");
+  __threadfence();
+  atomicAdd(counter, 1u);
 }
-// Storing thread: bounded wait until the producer thread has verified the dependency of the tile
-// with running number `seq` (0-based).
+// Producer thread: bounded wait until the scout warp has verified the dependency of the tile with
+// running number `seq` (0-based).
 __device__ __forceinline__ bool flow_wait_verified(const GemmCtx& cx, uint32_t seq) {
   if (ld_acquire_cta_shared_u32(cx.dep_ok) > seq) return true;
   const uint64_t t0 = globaltimer_ns();
@@ -257,6 +255,9 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
     const int per_batch = tn_of[c.prob] * tm_of[c.prob];
     c.batch = tile / per_batch;
     const int r = tile - c.batch * per_batch;
+    // a consumer of large intermediates walks the batch entries backwards: the entries its producer wrote last
+    // are the ones still in L2
+    if constexpr (Op::kReverseBatch) c.batch = probs[c.prob].batch - 1 - c.batch;
     c.m0 = (r / tn_of[c.prob]) * kBM;
     c.n0 = (r % tn_of[c.prob]) * BT;
     return c;
@@ -349,7 +350,7 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
         ++cx.tcount;
       }
     }
-  } else if (warp >= 2 + kEpiWarps) {
+  } else if (warp == 2 + kEpiWarps) {
     // ---------------- dependency scout (dataflow kernels only): one thread verifies, in tile order,
     // that every tile's inputs are complete and publishes the count of verified tiles
     if constexpr (Deps::kOn) {
@@ -360,6 +361,47 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
           const TileCoord tc = coord(tile);
           if (!dep_wait(deps.counter[tc.prob] + tc.batch, deps.need[tc.prob], cx.abort_flag)) { failed = true; break; }
           st_release_cta_shared_u32(cx.dep_ok, ++cx.ptile);
+        }
+      }
+    }
+  } else if (warp > 2 + kEpiWarps) {
+    // ---------------- storing thread (dataflow kernels only): takes each staged tile from the epilogue
+    // warps, issues its TMA stores, returns the staging tile as soon as the stores have read it, and
+    // publishes the tile's completion as soon as they have landed -- the epilogue warps never wait for
+    // global memory, and dependent tiles of other CTAs see the result about a tile's duration earlier
+    // than if the epilogue published it on its next pass
+    if constexpr (Deps::kOn && Op::NOUT > 0) {
+      static_assert(Op::kStagingBuffers == 1, "the storing warp hands over a single staging tile");
+      if (lane == 0) {
+        for (int tile_i = 0; tile_i < rounds && !failed; ++tile_i) {
+          const int tile = tile_at(tile_i);
+          if (tile >= total_tiles) continue;
+          const TileCoord tc = coord(tile);
+          const GemmProblem<Op>& P = probs[tc.prob];
+          typename Op::Epi ep = P.ep;
+          patch(ep, tc.prob);
+          const uint32_t stg = cx.staging;
+          const int nrounds = (Op::kSecondInPlace && P.oi[1].enabled) ? 2 : 1;
+          for (int r = 0; r < nrounds; ++r, ++cx.sround) {
+            if (!mbar_wait(&cx.stg_full_bar[0], cx.sround & 1, cx.abort_flag)) { failed = true; break; }
+#pragma unroll
+            for (int o = 0; o < Op::NOUT; ++o) {
+              if (Op::kSecondInPlace ? (o != r) : (r != 0)) continue;
+              if (!P.oi[o].enabled || Op::skip_store(ep, o)) continue;
+              const uint32_t src = stg + (Op::kSecondInPlace ? 0 : o) * (kBM * BT * 2);
+              for (int pnl = 0; pnl < BT / 64; ++pnl) {
+                if (tc.n0 + pnl * 64 >= P.N) break;
+                tma_store_3d(&P.out[o], src + pnl * (kBM * 128), P.oi[o].col_off + tc.n0 + pnl * 64,
+                             P.oi[o].row_off + tc.m0, P.oi[o].batch_off + tc.batch);
+              }
+            }
+            bulk_commit_group();
+            if (r == 0) cx.stamp(tile_i, 3);
+            bulk_wait_read_all();
+            mbar_arrive(&cx.stg_empty_bar[0]);
+          }
+          if (failed) break;
+          flow_publish(deps.counter[tc.prob] + tc.batch);
         }
       }
     }
@@ -384,10 +426,6 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
       const int t = tile_at(r);
       return t < total_tiles ? t : -1;
     };
-    if constexpr (Deps::kOn) {
-      // a CTA without a tile in this phase must not sit on an unpublished tile of the previous one
-      if (elected && tile_of_round(0) < 0) flow_flush(cx);
-    }
     for (int tile_i = 0; tile_i < rounds; ++tile_i) {
       const int tile = tile_of_round(tile_i);
       if (tile < 0) continue;
@@ -401,10 +439,6 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
       // global operands of the epilogue are fetched while the tile's MMAs are still running
       typename Op::Prefetch pf;
       Op::prefetch(ep, tc.batch, row, tc.n0, half, P.M, P.N, pf);
-      if constexpr (Deps::kOn) {
-        // idle anyway: publish the previous tile now, so that no CTA (this one included) waits for it
-        if (elected && !mbar_try_wait(&cx.acc_full_bar[as], aph)) flow_flush(cx);
-      }
       bool got = mbar_wait(&cx.acc_full_bar[as], aph, cx.abort_flag);
       tc_fence_after();
       if (elected) cx.stamp(tile_i, 2);
@@ -416,8 +450,14 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
         // stores that read this tile's staging buffer must have finished reading it: with two
         // buffers that is every group but the last one committed (the previous tile's final store)
         if (elected) {
-          if (kDoubleStg) bulk_wait_read_but_last();
-          else bulk_wait_read_all();
+          if constexpr (Deps::kOn) {
+            // the storing warp returns the staging tile once its stores have read it
+            if (cx.sround > 0 && !mbar_wait(&cx.stg_empty_bar[0], (cx.sround - 1) & 1, cx.abort_flag)) cx.abort_flag[1] = 1;
+          } else if (kDoubleStg) {
+            bulk_wait_read_but_last();
+          } else {
+            bulk_wait_read_all();
+          }
         }
         named_barrier_sync(1, kEpiThreads);
         if (cx.abort_flag[1] != 0) { failed = true; break; }
@@ -455,7 +495,11 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
             }
           }
         } else {
-          Op::epilogue(ep, tc.batch, row, tc.n0 + c, P.M, P.N, v, pf, c >> 6);
+          if constexpr (Op::kWarpTranspose)
+            Op::epilogue_warp(ep, tc.batch, tc.m0 + quarter * 32, tc.n0 + c, P.M, P.N, v, pf,
+                              cx.staging + (warp - 2) * (32 * 144), lane);
+          else
+            Op::epilogue(ep, tc.batch, row, tc.n0 + c, P.M, P.N, v, pf, c >> 6);
         }
       }
       // all TMEM reads of this warp are complete (wait::ld above): hand the buffer back
@@ -473,8 +517,10 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
       if constexpr (NOUT > 0) {
         fence_async_proxy();
         named_barrier_sync(2, kEpiThreads);
-        if (elected) {
-          if constexpr (Deps::kOn) flow_flush(cx);  // the previous tile's stores landed long ago
+        if constexpr (Deps::kOn) {
+          if (elected) mbar_arrive(&cx.stg_full_bar[0]);  // the storing warp issues the stores and publishes the tile
+          ++cx.sround;
+        } else if (elected) {
 #pragma unroll
           for (int o = 0; o < NOUT; ++o) {
             if (!P.oi[o].enabled || (o == 1 && Op::kSecondInPlace) || Op::skip_store(ep, o)) continue;
@@ -490,8 +536,15 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
         if constexpr (Op::kSecondInPlace) {
           // second output = f(first output), computed in place in the first staging tile
           if (P.oi[1].enabled) {
-            if (elected) bulk_wait_read_all();
+            if (elected) {
+              if constexpr (Deps::kOn) {
+                if (!mbar_wait(&cx.stg_empty_bar[0], (cx.sround - 1) & 1, cx.abort_flag)) cx.abort_flag[1] = 1;
+              } else {
+                bulk_wait_read_all();
+              }
+            }
             named_barrier_sync(1, kEpiThreads);
+            if (cx.abort_flag[1] != 0) { failed = true; break; }
             for (int c = half * 32; c < BT; c += 64) {
               if (tc.n0 + c >= P.N) break;
               const uint32_t base = stg + (c >> 6) * (kBM * 128) + row_local * 128;
@@ -517,7 +570,10 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
             }
             fence_async_proxy();
             named_barrier_sync(2, kEpiThreads);
-            if (elected) {
+            if constexpr (Deps::kOn) {
+              if (elected) mbar_arrive(&cx.stg_full_bar[0]);
+              ++cx.sround;
+            } else if (elected) {
               for (int pnl = 0; pnl < BT / 64; ++pnl) {
                 if (tc.n0 + pnl * 64 >= P.N) break;
                 tma_store_3d(&P.out[1], stg + pnl * (kBM * 128), P.oi[1].col_off + tc.n0 + pnl * 64,
@@ -526,9 +582,6 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
               bulk_commit_group();
             }
           }
-        }
-        if constexpr (Deps::kOn) {
-          if (elected) cx.pend = deps.counter[tc.prob] + tc.batch;  // published by a later flow_flush
         }
       }
       ++cx.tcount;
@@ -554,7 +607,9 @@ __device__ __forceinline__ void gemm_setup(GemmCtx& cx, uint8_t* smem_raw, int r
   cx.empty_bar = cx.full_bar + ring;
   cx.acc_full_bar = cx.empty_bar + ring;    // [2]
   cx.acc_empty_bar = cx.acc_full_bar + 2;   // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(cx.acc_empty_bar + 2);
+  cx.stg_full_bar = cx.acc_empty_bar + 2;   // [1]
+  cx.stg_empty_bar = cx.stg_full_bar + 1;   // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(cx.stg_empty_bar + 1);
   cx.abort_flag = tmem_slot + 1;  // [2]
   cx.dep_ok = tmem_slot + 3;
   if (threadIdx.x == 0) {
@@ -566,6 +621,8 @@ __device__ __forceinline__ void gemm_setup(GemmCtx& cx, uint8_t* smem_raw, int r
       mbar_init(&cx.acc_full_bar[s], 1);
       mbar_init(&cx.acc_empty_bar[s], kEpiWarps);
     }
+    mbar_init(&cx.stg_full_bar[0], 1);
+    mbar_init(&cx.stg_empty_bar[0], 1);
     cx.abort_flag[0] = 0;
     cx.abort_flag[1] = 0;
     *cx.dep_ok = 0;
