@@ -34,8 +34,8 @@ BF16 = torch.bfloat16
 CFG = dict(batch=8, heads=4, L=32768, D=384, H=384, chunk=2048, ns_steps=5)
 METRIC = "ttt_layer_fwd_tokens_per_s_760M_shape"
 # DRAM bytes (read + write) of ONE Newton-Schulz launch from an ncu capture of a 16-head case
-# (profiles/ns_fused_kernel_small_case.md: 14.3 MB + 34.9 MB); grows with the matrices per launch.
-NCU_DRAM_BYTES_NS_FUSED_16_HEADS = 49.2e6
+# (profiles/ns_fused_kernel_small_case.md: 14.3 MB + 36.4 MB); grows with the matrices per launch.
+NCU_DRAM_BYTES_NS_FUSED_16_HEADS = 50.8e6
 E2E_SLABS = 4  # the end-to-end arm streams the batch through the device in this many slabs
 
 
@@ -312,6 +312,47 @@ def train_step_timing(lb, t, dev, B, L, D, H, C, tokens_per_step, world, barrier
 
 
 # ------------------------------------------------------------------------------------------ main arm
+def engine_probe():
+    """Steady-state cost of one output tile of the GEMM engine by tile width and contraction length, operands
+    L2-resident: c = a b^T with M = 4096 / 8192 rows and N = 37 tile widths (8 / 16 rounds of 148 tiles); the
+    difference of the two launches divided by 8 is the time of one tile with the launch overhead cancelled."""
+    from lact_b200 import _lib as L
+    dev = torch.device("cuda", 0)
+    status = torch.zeros(64, dtype=torch.int32, device=dev)
+
+    def run(M, N, K, iters=20):
+        a = torch.randn(1, M, K, device=dev).to(BF16)
+        b = torch.randn(1, N, K, device=dev).to(BF16)
+        c = torch.empty(1, M, N, dtype=BF16, device=dev)
+
+        def call():
+            L.check(L.lib().lact_bmm_bf16(a.data_ptr(), 0, b.data_ptr(), 0, c.data_ptr(), L.dtype_code(c), 1, M, N, K,
+                                          status.data_ptr(), L.stream_ptr()), "lact_bmm_bf16")
+        for _ in range(3):
+            call()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            call()
+        e1.record()
+        torch.cuda.synchronize()
+        if int(status[0].item()) != 0:
+            raise RuntimeError("device status %d" % int(status[0].item()))
+        return e0.elapsed_time(e1) / iters * 1e3
+
+    rows = []
+    for bt in (64, 128, 192, 256):
+        for K in (384, 768, 2048):
+            t8, t16 = run(4096, 37 * bt, K), run(8192, 37 * bt, K)
+            tile_us = (t16 - t8) / 8
+            rows.append(dict(tile_n=bt, K=K, us_per_tile=round(tile_us, 3), us_per_kblock=round(tile_us / (K // 64), 3),
+                             steady_tflops=round(2 * 128 * bt * K / tile_us * 148 / 1e6, 1),
+                             launch_fixed_us=round(t8 - 8 * tile_us, 1)))
+    print(json.dumps({"engine_probe": rows, "note": "128 x tile_n output tiles, bf16 in / bf16 out, fp32 accumulate, "
+                      "148 tiles per round, launches back to back in one stream"}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -326,6 +367,9 @@ def main():
     ap.add_argument("--train", action="store_true",
                     help="also time forward + backward through the recurrence (gradients to q, k, v, lr, momentum "
                          "and the initial fast weights, upstream gradient ~ N(0,1) bf16); reported under \"train\"")
+    ap.add_argument("--engine-probe", action="store_true",
+                    help="micro-benchmark of the GEMM engine alone (time per output tile by tile width and "
+                         "contraction length); prints its own JSON line and exits")
     ap.add_argument("--batch", type=int, default=None,
                     help="override the batch size (profiler captures on a small case; not a headline number)")
     ap.add_argument("--seq-len", type=int, default=None, help="override the sequence length (same caveat)")
@@ -340,6 +384,10 @@ def main():
         CFG["L"] = args.seq_len
     if args.impl == "reference":
         reference_arm(args, rank)
+        return
+    if args.engine_probe:
+        if rank == 0:
+            engine_probe()
         return
     warmup = args.warmup if reduced else max(3, args.warmup)
     steps = max(1, args.steps)

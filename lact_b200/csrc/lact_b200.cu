@@ -493,7 +493,7 @@ int launch_ns_prepare(const NsGroup* grp, int ngroups, const void* const* src, i
     const NsGroup& G = grp[g];
     const int parts = (fused_parts != nullptr && fused_parts[g] > 0) ? fused_parts[g] : kNsSlabs;
     if (fused_parts == nullptr || fused_parts[g] <= 0) need_sumsq = true;
-    pa.grp[g] = NsPrepGroup{src[g], src_f32, G.nmat, G.R, G.C, G.xa, G.partial, parts, G.scale};
+    pa.grp[g] = NsPrepGroup{src[g], src_f32, G.nmat, G.R, G.C, G.xa, G.partial, parts, G.scale, G.done};
     nmat += G.nmat;
     tiles = std::max(tiles, ceil_div(G.R, 64) * ceil_div(G.C, 64));
   }
@@ -593,7 +593,8 @@ int run_ns_iterations(const NsGroup* grp, int ngroups, int steps, int const_coef
   return LACT_OK;
 }
 
-// Fused path: all iterations in one cooperative launch (the first iterates must be in grp[g].xa).
+// Fused path: all iterations in one cooperative launch.  launch_ns_prepare must have run on the same groups
+// just before: it leaves the first iterates in grp[g].xa and clears the completion counters grp[g].done.
 template <int BT_MM, int BT_MN>
 int launch_ns_fused(const NsGroup* grp, int ngroups, int steps, int const_coeffs, int32_t* status,
                     cudaStream_t stream, uint64_t* trace, int unscaled_first) {
@@ -635,10 +636,7 @@ int launch_ns_fused(const NsGroup* grp, int ngroups, int steps, int const_coeffs
   args.ngroups = ngroups;
   args.status = status;
   args.trace = trace;
-  for (int g = 0; g < ngroups; ++g) {
-    args.done[g] = grp[g].done;
-    LACT_CUDA(cudaMemsetAsync(grp[g].done, 0, sizeof(uint32_t) * grp[g].nmat, stream));
-  }
+  for (int g = 0; g < ngroups; ++g) args.done[g] = grp[g].done;  // cleared by launch_ns_prepare
   const int grid = static_cast<int>(std::min<int64_t>(sm_count(), std::max<int64_t>(max_tiles, 8)));
   void* kargs[] = {&args};
   KernelScope scope(kClsNsFused, stream);

@@ -64,29 +64,46 @@ struct EpiStore {
   int32_t row_off;
   int32_t f32;
   int32_t accumulate;  // fp32 only: out += acc (each element is owned by exactly one thread)
-  __device__ __forceinline__ void operator()(int batch, int row, int col, int M, int N, const float* v) const {
-    if (row >= M) return;
-    const int valid = min(32, N - col);
-    const int64_t idx = batch * bs + static_cast<int64_t>(row + row_off) * ld + col;
-    if (f32 && accumulate) {
-      float* o = reinterpret_cast<float*>(out) + idx;
-      float r[32];
+  static constexpr uint32_t kScratch = kEpiWarps * 32 * 144;
+  // One warp's 32 x 32 block of results, thread `lane` holding row `row0 + lane` in v[0..31]: the block goes through
+  // `scratch` (this warp's 32 x 144 bytes of shared memory) so that eight lanes cover a 128-byte row segment and every
+  // global access of the warp touches four full lines instead of 32.
+  __device__ __forceinline__ void warp_block(int batch, int row0, int col, int M, int N, const float* v, uint32_t scratch,
+                                             int lane) const {
 #pragma unroll
-      for (int g = 0; g < 8; ++g) {
-        if (g * 4 < valid) {
-          const float4 old = *reinterpret_cast<const float4*>(o + g * 4);
-          r[g * 4 + 0] = old.x + v[g * 4 + 0];
-          r[g * 4 + 1] = old.y + v[g * 4 + 1];
-          r[g * 4 + 2] = old.z + v[g * 4 + 2];
-          r[g * 4 + 3] = old.w + v[g * 4 + 3];
-        }
-      }
-      store_row32_f32(o, r, valid);
-    } else if (f32) {
-      store_row32_f32(reinterpret_cast<float*>(out) + idx, v, valid);
-    } else {
-      store_row32_bf16(reinterpret_cast<bf16*>(out) + idx, v, valid);
+    for (int gq = 0; gq < 8; ++gq)
+      asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(scratch + lane * 144 + gq * 16), "f"(v[gq * 4]),
+                   "f"(v[gq * 4 + 1]), "f"(v[gq * 4 + 2]), "f"(v[gq * 4 + 3])
+                   : "memory");
+    __syncwarp();
+    const int u = lane & 7, rsub = lane >> 3;
+    const bool col_ok = col + u * 4 + 4 <= N;
+    const bool rmw = f32 && accumulate;
+    const int64_t base = batch * bs + col + u * 4;
+    float4 old[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int row = row0 + i * 4 + rsub;
+      old[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (rmw && col_ok && row < M)
+        old[i] = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(out) + base +
+                                                  static_cast<int64_t>(row + row_off) * ld);
     }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int rr = i * 4 + rsub, row = row0 + rr;
+      if (!col_ok || row >= M) continue;
+      float4 x;
+      asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                   : "=f"(x.x), "=f"(x.y), "=f"(x.z), "=f"(x.w)
+                   : "r"(scratch + rr * 144 + u * 16)
+                   : "memory");
+      x.x += old[i].x; x.y += old[i].y; x.z += old[i].z; x.w += old[i].w;
+      const int64_t idx = base + static_cast<int64_t>(row + row_off) * ld;
+      if (f32) *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + idx) = x;
+      else *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(out) + idx) = make_uint2(pack_bf16x2(x.x, x.y), pack_bf16x2(x.z, x.w));
+    }
+    __syncwarp();  // the scratch block is rewritten by the next call
   }
 };
 
@@ -207,10 +224,10 @@ struct OpBmm {
   static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 0;
   static constexpr bool kSecondInPlace = false, kTileReduce = false;
   static constexpr int kStagingBuffers = 1;
-  static constexpr bool kWarpTranspose = false, kReverseBatch = false;
-  static constexpr uint32_t kEpiScratch = 0;
+  static constexpr bool kWarpTranspose = true, kReverseBatch = false;
+  static constexpr uint32_t kEpiScratch = EpiT::kScratch;
   static constexpr int KB = 1;  // measured: two-k-block stages slow the training backward's products by 7 %
-  static constexpr int STAGES = ring_depth(KB * (kATileBytes + BT_ * kBK * 2), 0);
+  static constexpr int STAGES = ring_depth(KB * (kATileBytes + BT_ * kBK * 2), kEpiScratch);
   using Epi = EpiT;
   __host__ __device__ static constexpr int term_a(int) { return 0; }
   __host__ __device__ static constexpr int term_b(int) { return 0; }
@@ -219,9 +236,9 @@ struct OpBmm {
   __host__ __device__ static constexpr bool term_first(int) { return true; }
   using Prefetch = NoPrefetch;
   __device__ static __forceinline__ void prefetch(const Epi&, int, int, int, int, int, int, Prefetch&) {}
-  __device__ static __forceinline__ void epilogue(const Epi& ep, int batch, int row, int col, int M, int N,
-                                                  const float (&v)[1][32], Prefetch&, int) {
-    ep(batch, row, col, M, N, v[0]);
+  __device__ static __forceinline__ void epilogue_warp(const Epi& ep, int batch, int row0, int col, int M, int N,
+                                                       const float (&v)[1][32], Prefetch&, uint32_t scratch, int lane) {
+    ep.warp_block(batch, row0, col, M, N, v[0], scratch, lane);
   }
 };
 
@@ -271,7 +288,7 @@ struct OpBmmStore {
   static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 1;
   static constexpr bool kSecondInPlace = false, kTileReduce = false;
   static constexpr int kStagingBuffers = 1;
-  static constexpr bool kWarpTranspose = false, kReverseBatch = false;
+  static constexpr bool kWarpTranspose = false, kReverseBatch = true;
   static constexpr uint32_t kEpiScratch = 0;
   static constexpr int KB = 1;  // measured: two-k-block stages are 5 % slower for this op (K-major operands, short K)
   static constexpr int STAGES = ring_depth(KB * (kATileBytes + BT_ * kBK * 2), kBM * BT_ * 2);
@@ -297,10 +314,10 @@ struct OpBmm2 {
   static constexpr int NA = 2, NB = 2, NACC = 1, BT = BT_, NTERMS = 2, NOUT = 0;
   static constexpr bool kSecondInPlace = false, kTileReduce = false;
   static constexpr int kStagingBuffers = 1;
-  static constexpr bool kWarpTranspose = false, kReverseBatch = false;
-  static constexpr uint32_t kEpiScratch = 0;
+  static constexpr bool kWarpTranspose = true, kReverseBatch = false;
+  static constexpr uint32_t kEpiScratch = EpiT::kScratch;
   static constexpr int KB = 1;
-  static constexpr int STAGES = ring_depth(KB * (2 * kATileBytes + 2 * BT_ * kBK * 2), 0);
+  static constexpr int STAGES = ring_depth(KB * (2 * kATileBytes + 2 * BT_ * kBK * 2), kEpiScratch);
   using Epi = EpiT;
   __host__ __device__ static constexpr int term_a(int t) { return t; }
   __host__ __device__ static constexpr int term_b(int t) { return t; }
@@ -309,9 +326,9 @@ struct OpBmm2 {
   __host__ __device__ static constexpr bool term_first(int t) { return t == 0; }
   using Prefetch = NoPrefetch;
   __device__ static __forceinline__ void prefetch(const Epi&, int, int, int, int, int, int, Prefetch&) {}
-  __device__ static __forceinline__ void epilogue(const Epi& ep, int batch, int row, int col, int M, int N,
-                                                  const float (&v)[1][32], Prefetch&, int) {
-    ep(batch, row, col, M, N, v[0]);
+  __device__ static __forceinline__ void epilogue_warp(const Epi& ep, int batch, int row0, int col, int M, int N,
+                                                       const float (&v)[1][32], Prefetch&, uint32_t scratch, int lane) {
+    ep.warp_block(batch, row0, col, M, N, v[0], scratch, lane);
   }
 };
 
@@ -532,6 +549,7 @@ struct NsPrepGroup {
   float* partial;     // [nmat][nparts] partial sums of squares, added in index order
   int32_t nparts;
   float* scale;       // [nmat] out of ns_den_kernel
+  uint32_t* done;     // [nmat] completion counters of the fused iteration kernel, cleared here (or nullptr)
 };
 struct NsPrepArgs {
   NsPrepGroup grp[2];
@@ -594,7 +612,10 @@ __global__ void __launch_bounds__(128) ns_den_kernel(const NsPrepArgs args) {
   float tot = 0.f;
   for (int i = lane; i < G.nparts; i += 32) tot += G.partial[static_cast<int64_t>(mat) * G.nparts + i];
   tot = warp_sum(tot);
-  if (lane == 0) G.scale[mat] = 1.0f / bf16_round(bf16_round(sqrtf(tot)) + 1e-7f);
+  if (lane == 0) {
+    G.scale[mat] = 1.0f / bf16_round(bf16_round(sqrtf(tot)) + 1e-7f);
+    if (G.done != nullptr) G.done[mat] = 0;
+  }
 }
 
 // Part 2: X = bf16(bf16(G) / (bf16(||bf16(G)||_F) + 1e-7)), every operation rounded to bf16 as in
@@ -609,6 +630,7 @@ __global__ void __launch_bounds__(256) ns_scale_kernel(const NsPrepArgs args) {
   const NsPrepGroup& G = args.grp[gi];
   const int tiles_c = (G.C + 63) / 64, tiles_r = (G.R + 63) / 64;
   if (static_cast<int>(blockIdx.y) >= tiles_c * tiles_r) return;
+  if (blockIdx.y == 0 && threadIdx.x == 0 && G.done != nullptr) G.done[mat] = 0;
   const int tr = (blockIdx.y / tiles_c) * 64, tcx = (blockIdx.y % tiles_c) * 64;
   __shared__ float parts[512];
   __shared__ float den_s;

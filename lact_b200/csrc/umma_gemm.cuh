@@ -137,9 +137,9 @@ struct GemmCtx {
   uint32_t it = 0, tcount = 0;
   // dataflow mode (multi-phase kernels whose phases are ordered by completion counters, see FlowDeps)
   uint32_t rot = 0;              // tiles handed out by earlier phases, modulo the grid size
-  uint32_t ptile = 0;            // tiles whose dependency the producer thread has verified
+  uint32_t ptile = 0;            // tiles whose dependency has been verified (scout) / consumed (producer)
   uint32_t sround = 0;           // staging hand-overs so far (epilogue threads and the storing thread count alike)
-  uint32_t* dep_ok = nullptr;    // shared-memory word: the producer's `ptile`, read by the storing thread
+  uint32_t* dep_ok = nullptr;    // shared-memory word: tiles verified by the scout warp, read by the producer thread
   // optional diagnostics (CTA 0 only): per phase < 6 and tile < 4, globaltimer stamps of
   // {loads issued, MMAs committed, epilogue started, epilogue finished} at trace[40 + 16*phase + 4*tile + k]
   uint64_t* trace = nullptr;
@@ -368,8 +368,7 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
     // ---------------- storing thread (dataflow kernels only): takes each staged tile from the epilogue
     // warps, issues its TMA stores, returns the staging tile as soon as the stores have read it, and
     // publishes the tile's completion as soon as they have landed -- the epilogue warps never wait for
-    // global memory, and dependent tiles of other CTAs see the result about a tile's duration earlier
-    // than if the epilogue published it on its next pass
+    // global memory, and no CTA can wait on a tile it has not yet published itself
     if constexpr (Deps::kOn && Op::NOUT > 0) {
       static_assert(Op::kStagingBuffers == 1, "the storing warp hands over a single staging tile");
       if (lane == 0) {
