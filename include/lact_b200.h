@@ -206,6 +206,13 @@ int lact_bmm2_bf16(const void *a0, int32_t a0_mn_major, const void *b0, int32_t 
                    int32_t a1_mn_major, const void *b1, int32_t b1_mn_major, void *c, int32_t c_dtype,
                    int32_t accumulate, int64_t batch, int64_t M, int64_t N, int64_t K, int32_t *status_word,
                    void *stream);
+/* The same product on strided operands and result (views of larger tensors, e.g. a token range of [B, L, D]):
+ * *_ld = row stride, *_bs = batch stride, in elements (multiples of 8; base pointers 16-byte aligned). */
+int lact_bmm2_strided_bf16(const void *a0, int32_t a0_mn_major, int64_t a0_ld, int64_t a0_bs, const void *b0,
+                           int32_t b0_mn_major, int64_t b0_ld, int64_t b0_bs, const void *a1, int32_t a1_mn_major,
+                           int64_t a1_ld, int64_t a1_bs, const void *b1, int32_t b1_mn_major, int64_t b1_ld,
+                           int64_t b1_bs, void *c, int32_t c_dtype, int64_t c_ld, int64_t c_bs, int32_t accumulate,
+                           int64_t batch, int64_t M, int64_t N, int64_t K, int32_t *status_word, void *stream);
 /* Newton-Schulz with every iterate kept, and its backward (the reference differentiates
  * zeropower_via_newtonschulz5, ttt_operation.py:30-66 / lact_nvs/lact_ttt.py:32-67, by autograd):
  *   lact_ns_trace_fwd: x_out[B, R, C] (bf16) = Newton-Schulz(g), the iterates and Gram polynomials stay in `trace`

@@ -41,23 +41,37 @@ def check_status(dev: torch.device) -> None:
         raise L.LactError(f"device status {st} during backward")
 
 
+def _strided(t):
+    """A [batch, rows, cols] bf16 tensor as (tensor, row stride, batch stride) for the strided GEMM entry; views
+    whose innermost axis is contiguous and whose strides / base keep 16-byte alignment pass through uncopied."""
+    if t.stride(2) != 1 or t.stride(1) % 8 or t.stride(0) % 8 or t.data_ptr() % 16 or t.stride(1) < t.shape[2]:
+        t = t.contiguous()
+    return t, t.stride(1), t.stride(0)
+
+
 def gemm(a, b, a_mn=False, b_mn=False, a1=None, b1=None, a1_mn=False, b1_mn=False, out=None,
          out_dtype=torch.float32, accumulate=False):
-    """c[batch, M, N] (+)= a b^T (+ a1 b1^T).  Operands bf16, [batch, rows, K] or (``*_mn``) [batch, K, rows]."""
-    a, b = a.contiguous(), b.contiguous()
+    """c[batch, M, N] (+)= a b^T (+ a1 b1^T).  Operands bf16, [batch, rows, K] or (``*_mn``) [batch, K, rows];
+    operands and `out` may be views into larger tensors (token ranges)."""
+    a, a_ld, a_bs = _strided(a)
+    b, b_ld, b_bs = _strided(b)
     batch = a.shape[0]
     M, K = (a.shape[2], a.shape[1]) if a_mn else (a.shape[1], a.shape[2])
     N = b.shape[2] if b_mn else b.shape[1]
     if out is None:
         out = torch.empty(batch, M, N, dtype=out_dtype, device=a.device)
+    assert out.stride(2) == 1 and out.shape == (batch, M, N)
+    a1_ld = a1_bs = b1_ld = b1_bs = 0
     if a1 is not None:
-        a1, b1 = a1.contiguous(), b1.contiguous()
+        a1, a1_ld, a1_bs = _strided(a1)
+        b1, b1_ld, b1_bs = _strided(b1)
     st = _status_word(a.device)
-    rc = L.lib().lact_bmm2_bf16(a.data_ptr(), int(a_mn), b.data_ptr(), int(b_mn),
-                                a1.data_ptr() if a1 is not None else None, int(a1_mn),
-                                b1.data_ptr() if b1 is not None else None, int(b1_mn), out.data_ptr(),
-                                L.dtype_code(out), int(accumulate), batch, M, N, K, st.data_ptr(), L.stream_ptr())
-    L.check(rc, "lact_bmm2_bf16")
+    rc = L.lib().lact_bmm2_strided_bf16(a.data_ptr(), int(a_mn), a_ld, a_bs, b.data_ptr(), int(b_mn), b_ld, b_bs,
+                                        a1.data_ptr() if a1 is not None else None, int(a1_mn), a1_ld, a1_bs,
+                                        b1.data_ptr() if b1 is not None else None, int(b1_mn), b1_ld, b1_bs,
+                                        out.data_ptr(), L.dtype_code(out), out.stride(1), out.stride(0), int(accumulate),
+                                        batch, M, N, K, st.data_ptr(), L.stream_ptr())
+    L.check(rc, "lact_bmm2_strided_bf16")
     return out
 
 
@@ -65,9 +79,10 @@ def _vecptr(t: Optional[torch.Tensor]):
     return t.data_ptr() if t is not None else None
 
 
-def apply_backward(w02b, w1b, q, dO, dW02, dW1):
+def apply_backward(w02b, w1b, q, dO, dW02, dW1, dq_out=None):
     """Backward of o = w1 (silu(w0 q) * (w2 q)) on one token range.  Accumulates the weight gradients
-    (fp32) into dW02 / dW1 and returns dq (bf16).  lact_swiglu_ffn.py:46-76."""
+    (fp32) into dW02 / dW1 and returns dq (bf16; written into the view `dq_out` if given).
+    lact_swiglu_ffn.py:46-76."""
     B, n, D = q.shape
     H = w1b.shape[2]
     y02 = gemm(q, w02b, out_dtype=BF16)                      # [B, n, 2H]
@@ -79,13 +94,14 @@ def apply_backward(w02b, w1b, q, dO, dW02, dW1):
             "lact_swiglu_bwd_planes")
     gemm(dy02, q, a_mn=True, b_mn=True, out=dW02, accumulate=True)   # [2H, D] += dy02^T q
     gemm(dO, hid, a_mn=True, b_mn=True, out=dW1, accumulate=True)    # [D, H]  += dO^T hidden
-    return gemm(dy02, w02b, b_mn=True, out_dtype=BF16)               # dq = dy02 w02
+    return gemm(dy02, w02b, b_mn=True, out=dq_out, out_dtype=BF16)   # dq = dy02 w02
 
 
-def fw_grad_backward(w02b, w1b, k, v, lr0, lr1, lr2, w_scale, gG02, gG1, dW02, dW1):
+def fw_grad_backward(w02b, w1b, k, v, lr0, lr1, lr2, w_scale, gG02, gG1, dW02, dW1, dk_out=None, dv_out=None):
     """Backward of the lr-weighted fast-weight gradient on one token range, given the gradients gG02
     ([B,2H,D]) / gG1 ([B,D,H]) of its outputs.  Accumulates into dW02 / dW1; returns
-    (dk, dv [bf16], dlr0, dlr1, dlr2 [fp32, B x n]).  lact_fw_grad.py:61-156."""
+    (dk, dv [bf16; written into the views `dk_out` / `dv_out` if given], dlr0, dlr1, dlr2 [fp32, B x n]).
+    lact_fw_grad.py:61-156."""
     B, n, D = k.shape
     H = w1b.shape[2]
     g02b, g1b = gG02.to(BF16), gG1.to(BF16)
@@ -102,8 +118,8 @@ def fw_grad_backward(w02b, w1b, k, v, lr0, lr1, lr2, w_scale, gG02, gG1, dW02, d
         lr2.data_ptr(), L.dtype_code(lr0), float(w_scale), g_y02.data_ptr(), g_dh.data_ptr(), dy02l.data_ptr(),
         hidl.data_ptr(), glr[0].data_ptr(), glr[1].data_ptr(), glr[2].data_ptr(), B * n, H, L.stream_ptr()),
         "lact_fw_grad_bwd_pointwise")
-    dk = gemm(g_y02, w02b, b_mn=True, a1=dy02l, b1=g02b, b1_mn=True, out_dtype=BF16)
-    dv = gemm(g_dh, w1b, a1=hidl, b1=g1b, out_dtype=BF16)
+    dk = gemm(g_y02, w02b, b_mn=True, a1=dy02l, b1=g02b, b1_mn=True, out=dk_out, out_dtype=BF16)
+    dv = gemm(g_dh, w1b, a1=hidl, b1=g1b, out=dv_out, out_dtype=BF16)
     gemm(g_y02, k, a_mn=True, b_mn=True, out=dW02, accumulate=True)
     gemm(v, g_dh, a_mn=True, b_mn=True, out=dW1, accumulate=True)
     return dk, dv, glr[0], glr[1], glr[2]
@@ -258,6 +274,13 @@ def scan_backward(opts, steps, w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, dum
 
         cnt = n_upd
         shadows = {}
+        q_done, kv_done = [], []  # token ranges whose dq / dk, dv have been written
+
+        def fresh(done, s_, e_):
+            """True (and records the range) if no earlier step wrote a gradient for tokens [s_, e_)."""
+            ok = all(e_ <= a_ or s_ >= b_ for a_, b_ in done)
+            done.append((s_, e_))
+            return ok
 
         def shadow(c_):
             if c_ not in shadows:
@@ -271,8 +294,10 @@ def scan_backward(opts, steps, w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, dum
                 continue
             if kind == P.APPLY:
                 w02b, w1b = shadow(cnt)
-                dq[:, s:e] += apply_backward(w02b, w1b, q[:, s:e].contiguous(),
-                                             dO[:, o_s:o_s + (e - s)].contiguous(), dW02, dW1)
+                if fresh(q_done, s, e):   # first gradient for these tokens: the product writes it in place
+                    apply_backward(w02b, w1b, q[:, s:e], dO[:, o_s:o_s + (e - s)], dW02, dW1, dq_out=dq[:, s:e])
+                else:
+                    dq[:, s:e] += apply_backward(w02b, w1b, q[:, s:e], dO[:, o_s:o_s + (e - s)], dW02, dW1)
                 continue
             u = cnt - 1
             Wp02, Wp1 = weights(u)
@@ -323,11 +348,15 @@ def scan_backward(opts, steps, w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, dum
                     dmom[:, s:e] += (dbeta / float(e - s)).unsqueeze(1)
                 dM02, dM1 = dG02 * beta.view(B, 1, 1), dG1 * beta.view(B, 1, 1)
             w02b, w1b = shadow(u)
-            gk, gv, g0, g1, g2 = fw_grad_backward(w02b, w1b, k[:, s:e].contiguous(), v[:, s:e].contiguous(),
-                                                  lr0v[:, s:e], lr1v[:, s:e], lr2v[:, s:e], w_scale, dG02, dG1,
-                                                  dW02, dW1)
-            dk[:, s:e] += gk
-            dv[:, s:e] += gv
+            if fresh(kv_done, s, e):
+                _, _, g0, g1, g2 = fw_grad_backward(w02b, w1b, k[:, s:e], v[:, s:e], lr0v[:, s:e], lr1v[:, s:e],
+                                                    lr2v[:, s:e], w_scale, dG02, dG1, dW02, dW1, dk_out=dk[:, s:e],
+                                                    dv_out=dv[:, s:e])
+            else:
+                gk, gv, g0, g1, g2 = fw_grad_backward(w02b, w1b, k[:, s:e], v[:, s:e], lr0v[:, s:e], lr1v[:, s:e],
+                                                      lr2v[:, s:e], w_scale, dG02, dG1, dW02, dW1)
+                dk[:, s:e] += gk
+                dv[:, s:e] += gv
             dlr[0][:, s:e] += g0
             dlr[1][:, s:e] += g1
             dlr[2][:, s:e] += g2

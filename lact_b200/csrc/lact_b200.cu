@@ -1304,9 +1304,11 @@ int lact_prenorm_momentum_l2norm(const void* x, const void* dx, const void* m, c
   return LACT_OK;
 }
 
-int lact_bmm2_bf16(const void* a0, int32_t a0_mn, const void* b0, int32_t b0_mn, const void* a1, int32_t a1_mn,
-                   const void* b1, int32_t b1_mn, void* c, int32_t c_dtype, int32_t accumulate, int64_t batch,
-                   int64_t M, int64_t N, int64_t K, int32_t* status_word, void* stream) {
+int lact_bmm2_strided_bf16(const void* a0, int32_t a0_mn, int64_t a0_ld, int64_t a0_bs, const void* b0, int32_t b0_mn,
+                           int64_t b0_ld, int64_t b0_bs, const void* a1, int32_t a1_mn, int64_t a1_ld, int64_t a1_bs,
+                           const void* b1, int32_t b1_mn, int64_t b1_ld, int64_t b1_bs, void* c, int32_t c_dtype,
+                           int64_t c_ld, int64_t c_bs, int32_t accumulate, int64_t batch, int64_t M, int64_t N, int64_t K,
+                           int32_t* status_word, void* stream) {
   if (!a0 || !b0 || !c || !status_word || ((a1 == nullptr) != (b1 == nullptr))) return LACT_ERR_NULL;
   LACT_TRY(check_device());
   if (batch < 1 || batch > 65535 || M < 1 || N < 8 || K < 1 || (N % 8)) return LACT_ERR_SHAPE;
@@ -1314,17 +1316,24 @@ int lact_bmm2_bf16(const void* a0, int32_t a0_mn, const void* b0, int32_t b0_mn,
   if (((a0_mn || (a1 && a1_mn)) && (M % 8)) || ((!a0_mn || (a1 && !a1_mn) || !b0_mn || (b1 && !b1_mn)) && (K % 8)))
     return LACT_ERR_SHAPE;
   if (accumulate && c_dtype != LACT_F32) return LACT_ERR_DTYPE;
-  auto mat = [&](const void* p, int mn, int64_t rows) {
-    return mn ? Mat{p, K, rows, rows, batch, K * rows} : Mat{p, rows, K, K, batch, rows * K};
+  // c is written in 16-byte (fp32) / 8-byte (bf16) units
+  if ((reinterpret_cast<uintptr_t>(c) & 15) != 0 || c_ld < N || (c_ld % 8) != 0 || (batch > 1 && (c_bs % 8) != 0))
+    return LACT_ERR_SHAPE;
+  // operand as a matrix of `rows` = M or N: [rows][K] with row stride ld, or (MN-major) [K][rows]
+  auto mat = [&](const void* p, int mn, int64_t rows, int64_t ld, int64_t bs) {
+    return mn ? Mat{p, K, rows, ld, batch, bs} : Mat{p, rows, K, ld, batch, bs};
   };
+  auto bad = [&](int mn, int64_t rows, int64_t ld) { return ld < (mn ? rows : K); };
+  if (bad(a0_mn, M, a0_ld) || bad(b0_mn, N, b0_ld) || (a1 && (bad(a1_mn, M, a1_ld) || bad(b1_mn, N, b1_ld))))
+    return LACT_ERR_SHAPE;
   const int bt = choose_bt({{N, 1}});
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const EpiStore ep{c, M * N, N, 0, c_dtype == LACT_F32, accumulate};
+  const EpiStore ep{c, c_bs, c_ld, 0, c_dtype == LACT_F32, accumulate};
   if (a1 == nullptr) {
     auto fill = [&](auto& g, int btv) -> int {
       auto& P = g.prob[0];
-      LACT_TRY(make_operand(kb_of(P), &P.a[0], &P.ai[0], mat(a0, a0_mn, M), a0_mn, kBM, 0, 0));
-      LACT_TRY(make_operand(kb_of(P), &P.b[0], &P.bi[0], mat(b0, b0_mn, N), b0_mn, btv, 0, 0));
+      LACT_TRY(make_operand(kb_of(P), &P.a[0], &P.ai[0], mat(a0, a0_mn, M, a0_ld, a0_bs), a0_mn, kBM, 0, 0));
+      LACT_TRY(make_operand(kb_of(P), &P.b[0], &P.bi[0], mat(b0, b0_mn, N, b0_ld, b0_bs), b0_mn, btv, 0, 0));
       P.M = static_cast<int>(M); P.N = static_cast<int>(N); P.K = static_cast<int>(K);
       P.batch = static_cast<int>(batch);
       P.ep = ep;
@@ -1335,10 +1344,10 @@ int lact_bmm2_bf16(const void* a0, int32_t a0_mn, const void* b0, int32_t b0_mn,
   }
   auto fill2 = [&](auto& g, int btv) -> int {
     auto& P = g.prob[0];
-    LACT_TRY(make_operand(kb_of(P), &P.a[0], &P.ai[0], mat(a0, a0_mn, M), a0_mn, kBM, 0, 0));
-    LACT_TRY(make_operand(kb_of(P), &P.b[0], &P.bi[0], mat(b0, b0_mn, N), b0_mn, btv, 0, 0));
-    LACT_TRY(make_operand(kb_of(P), &P.a[1], &P.ai[1], mat(a1, a1_mn, M), a1_mn, kBM, 0, 0));
-    LACT_TRY(make_operand(kb_of(P), &P.b[1], &P.bi[1], mat(b1, b1_mn, N), b1_mn, btv, 0, 0));
+    LACT_TRY(make_operand(kb_of(P), &P.a[0], &P.ai[0], mat(a0, a0_mn, M, a0_ld, a0_bs), a0_mn, kBM, 0, 0));
+    LACT_TRY(make_operand(kb_of(P), &P.b[0], &P.bi[0], mat(b0, b0_mn, N, b0_ld, b0_bs), b0_mn, btv, 0, 0));
+    LACT_TRY(make_operand(kb_of(P), &P.a[1], &P.ai[1], mat(a1, a1_mn, M, a1_ld, a1_bs), a1_mn, kBM, 0, 0));
+    LACT_TRY(make_operand(kb_of(P), &P.b[1], &P.bi[1], mat(b1, b1_mn, N, b1_ld, b1_bs), b1_mn, btv, 0, 0));
     P.M = static_cast<int>(M); P.N = static_cast<int>(N); P.K = static_cast<int>(K);
     P.batch = static_cast<int>(batch);
     P.ep = ep;
@@ -1346,6 +1355,16 @@ int lact_bmm2_bf16(const void* a0, int32_t a0_mn, const void* b0, int32_t b0_mn,
     return LACT_OK;
   };
   return launch_op<OpStore2T, 1>(std::min(bt, 192), fill2, s, kClsOther, 1);
+}
+
+int lact_bmm2_bf16(const void* a0, int32_t a0_mn, const void* b0, int32_t b0_mn, const void* a1, int32_t a1_mn,
+                   const void* b1, int32_t b1_mn, void* c, int32_t c_dtype, int32_t accumulate, int64_t batch,
+                   int64_t M, int64_t N, int64_t K, int32_t* status_word, void* stream) {
+  // contiguous operands: [batch][rows][K] or (MN-major) [batch][K][rows]
+  auto ld = [&](int mn, int64_t rows) { return mn ? rows : K; };
+  return lact_bmm2_strided_bf16(a0, a0_mn, ld(a0_mn, M), M * K, b0, b0_mn, ld(b0_mn, N), N * K, a1, a1_mn, ld(a1_mn, M),
+                                M * K, b1, b1_mn, ld(b1_mn, N), N * K, c, c_dtype, N, M * N, accumulate, batch, M, N, K,
+                                status_word, stream);
 }
 
 static PlaneArgs make_plane_args(const void* y02, const void* dh, const void* g_dy02, const void* g_hid,

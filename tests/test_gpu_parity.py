@@ -64,6 +64,34 @@ def test_bmm_engine(lb, amn, bmn, shape):
     assert float((c16.double() - ref).abs().max() / ref.abs().max()) < 1e-2
 
 
+@pytest.mark.parametrize("out_dtype", [torch.float32, BF16])
+def test_two_product_gemm_on_token_range_views(lb, out_dtype):
+    """The training backward multiplies token ranges of [B, L, D] tensors in place (no copies) and writes
+    gradients into such ranges: strided operands, strided result, accumulation, two products."""
+    from lact_b200 import backward as bw
+    g = torch.Generator(device="cuda").manual_seed(3)
+    Bt, Ltok, D, H, s, e = 3, 520, 136, 72, 128, 392
+    x = torch.randn(Bt, Ltok, D, device="cuda", generator=g).bfloat16()
+    y = torch.randn(Bt, Ltok, D, device="cuda", generator=g).bfloat16()
+    w = torch.randn(Bt, H, D, device="cuda", generator=g).bfloat16()
+    w1 = torch.randn(Bt, H, D, device="cuda", generator=g).bfloat16()
+    xs, ys = x[:, s:e], y[:, s:e]
+    assert not xs.is_contiguous()
+    ref = torch.bmm(xs.double(), w.double().transpose(1, 2)) + torch.bmm(ys.double(), w1.double().transpose(1, 2))
+    big = torch.zeros(Bt, Ltok, H, device="cuda", dtype=out_dtype)
+    got = bw.gemm(xs, w, a1=ys, b1=w1, out=big[:, s:e], out_dtype=out_dtype)
+    assert got.data_ptr() == big[:, s:e].data_ptr()
+    tol = 2e-5 if out_dtype == torch.float32 else 1e-2
+    assert float((big[:, s:e].double() - ref).abs().max() / ref.abs().max()) < tol
+    assert float(big[:, :s].abs().max()) == 0.0 and float(big[:, e:].abs().max()) == 0.0  # nothing outside the range
+    # token contraction of a range (MN-major views), accumulated into an fp32 result
+    acc = torch.ones(Bt, D, D, device="cuda")
+    bw.gemm(xs, ys, a_mn=True, b_mn=True, out=acc, accumulate=True)
+    ref2 = 1.0 + torch.bmm(xs.double().transpose(1, 2), ys.double())
+    assert float((acc.double() - ref2).abs().max() / ref2.abs().max()) < 2e-5
+    bw.check_status(x.device)
+
+
 # ------------------------------------------------------------------------------- sub-ops
 @pytest.mark.parametrize("B,H,D,N", [(2, 128, 64, 200), (2, 384, 384, 512), (1, 192, 192, 300), (3, 64, 128, 77),
                                      (1, 256, 128, 1560)])
