@@ -159,7 +159,7 @@ def ns_forward_saved(G, steps, const_coeffs, gram_right):
                                           int(bool(const_coeffs)), int(bool(gram_right)), trace.data_ptr(), trace.numel(),
                                           _status_word(G.device).data_ptr(), L.stream_ptr()), "lact_ns_trace_fwd")
     Gb = G.to(BF16)
-    nrm = Gb.float().pow(2).sum(dim=(1, 2), keepdim=True).sqrt().to(BF16)
+    nrm = torch.linalg.vector_norm(Gb, dim=(1, 2), keepdim=True, dtype=torch.float32).to(BF16)
     den = (nrm.float() + 1e-7).to(BF16)
     return dict(trace=trace, shape=(nmat, R, Cc), steps=int(steps), cc=int(bool(const_coeffs)), gr=int(bool(gram_right)),
                 Gb=Gb, den=den.float(), nrm=nrm.float()), U
@@ -180,7 +180,8 @@ def ns_backward(saved, dU):
                                           _status_word(du.device).data_ptr(), L.stream_ptr()), "lact_ns_trace_bwd")
     Gf, den, nrm = saved["Gb"].float(), saved["den"], saved["nrm"]
     dot = (dX0 * Gf).sum(dim=(1, 2), keepdim=True)
-    return dX0 / den - Gf * dot / (den * den * nrm.clamp_min(1e-30))
+    # dX0 / den - G <dX0, G> / (den^2 ||G||), in place in dX0
+    return dX0.mul_(1.0 / den).addcmul_(Gf, dot / (den * den * nrm.clamp_min(1e-30)), value=-1.0)
 
 
 def scan_forward_saving(opts, steps, w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum):

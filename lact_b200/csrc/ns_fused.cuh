@@ -46,7 +46,7 @@ __host__ __device__ constexpr uint32_t ns_fused_stage_stride() {
 }
 template <int BT_MM, int BT_MN>
 __host__ __device__ constexpr uint32_t ns_fused_staging() {
-  return OpNs<BT_MM>::kStagingBuffers * kBM * (BT_MM > BT_MN ? BT_MM : BT_MN) * 2;
+  return kBM * (BT_MM > BT_MN ? BT_MM : BT_MN) * 2;
 }
 template <int BT_MM, int BT_MN>
 __host__ __device__ constexpr int ns_fused_ring() {

@@ -8,48 +8,7 @@ namespace lact {
 
 using bf16 = __nv_bfloat16;
 
-// ------------------------------------------------------------------------------------------
-// epilogue store helpers: each epilogue thread owns one accumulator row and 32 columns
-// ------------------------------------------------------------------------------------------
-__device__ __forceinline__ void store_row32_bf16(bf16* dst, const float* v, int valid) {
-#pragma unroll
-  for (int g = 0; g < 4; ++g) {
-    if (g * 8 < valid) {
-      uint4 u;
-      u.x = pack_bf16x2(v[g * 8 + 0], v[g * 8 + 1]);
-      u.y = pack_bf16x2(v[g * 8 + 2], v[g * 8 + 3]);
-      u.z = pack_bf16x2(v[g * 8 + 4], v[g * 8 + 5]);
-      u.w = pack_bf16x2(v[g * 8 + 6], v[g * 8 + 7]);
-      *reinterpret_cast<uint4*>(dst + g * 8) = u;
-    }
-  }
-}
-__device__ __forceinline__ void store_row32_f32(float* dst, const float* v, int valid) {
-#pragma unroll
-  for (int g = 0; g < 8; ++g) {
-    if (g * 4 < valid) {
-      *reinterpret_cast<float4*>(dst + g * 4) = make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
-    }
-  }
-}
-// L2-only loads: the row may have been written by another SM earlier in the same kernel.
-__device__ __forceinline__ void load_row32_bf16(const bf16* src, float* v, int valid) {
-#pragma unroll
-  for (int g = 0; g < 4; ++g) {
-    if (g * 8 < valid) {
-      const uint4 u = __ldcg(reinterpret_cast<const uint4*>(src + g * 8));
-      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        v[g * 8 + 2 * i] = __uint_as_float(w[i] << 16);
-        v[g * 8 + 2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) v[g * 8 + i] = 0.f;
-    }
-  }
-}
+// one value of an fp32 or bf16 vector
 __device__ __forceinline__ float load_scalar(const void* p, int is_f32, int64_t idx) {
   return is_f32 ? reinterpret_cast<const float*>(p)[idx] : __bfloat162float(reinterpret_cast<const bf16*>(p)[idx]);
 }
@@ -63,7 +22,7 @@ struct EpiStore {
   int64_t bs, ld;
   int32_t row_off;
   int32_t f32;
-  int32_t accumulate;  // fp32 only: out += acc (each element is owned by exactly one thread)
+  int32_t accumulate;  // fp32 only: out += acc (each element is owned by exactly one lane)
   static constexpr uint32_t kScratch = kEpiWarps * 32 * 144;
   // One warp's 32 x 32 block of results, thread `lane` holding row `row0 + lane` in v[0..31]: the block goes through
   // `scratch` (this warp's 32 x 144 bytes of shared memory) so that eight lanes cover a 128-byte row segment and every
@@ -223,7 +182,6 @@ template <class EpiT, int BT_>
 struct OpBmm {
   static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 0;
   static constexpr bool kSecondInPlace = false, kTileReduce = false;
-  static constexpr int kStagingBuffers = 1;
   static constexpr bool kWarpTranspose = true, kReverseBatch = false;
   static constexpr uint32_t kEpiScratch = EpiT::kScratch;
   static constexpr int KB = 1;  // measured: two-k-block stages slow the training backward's products by 7 %
@@ -249,7 +207,6 @@ template <int BT_>
 struct OpDW {
   static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 0;
   static constexpr bool kSecondInPlace = false, kTileReduce = true;
-  static constexpr int kStagingBuffers = 1;
   static constexpr bool kWarpTranspose = true;                   // results reach global memory through `EpiDW::warp_block`
   static constexpr bool kReverseBatch = true;                    // reads the planes the pointwise kernel has just written
   static constexpr uint32_t kEpiScratch = kEpiWarps * 32 * 144;  // one 32 x 32 fp32 block (rows padded to 144 bytes) per epilogue warp
@@ -287,7 +244,6 @@ template <int BT_>
 struct OpBmmStore {
   static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 1;
   static constexpr bool kSecondInPlace = false, kTileReduce = false;
-  static constexpr int kStagingBuffers = 1;
   static constexpr bool kWarpTranspose = false, kReverseBatch = true;
   static constexpr uint32_t kEpiScratch = 0;
   static constexpr int KB = 1;  // measured: two-k-block stages are 5 % slower for this op (K-major operands, short K)
@@ -313,7 +269,6 @@ template <class EpiT, int BT_>
 struct OpBmm2 {
   static constexpr int NA = 2, NB = 2, NACC = 1, BT = BT_, NTERMS = 2, NOUT = 0;
   static constexpr bool kSecondInPlace = false, kTileReduce = false;
-  static constexpr int kStagingBuffers = 1;
   static constexpr bool kWarpTranspose = true, kReverseBatch = false;
   static constexpr uint32_t kEpiScratch = EpiT::kScratch;
   static constexpr int KB = 1;
@@ -346,12 +301,10 @@ template <int BT_>
 struct OpNs {
   static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 2;
   static constexpr bool kSecondInPlace = true, kTileReduce = false;
-  // one staging tile (a second one would leave room for a single two-k-block stage only)
-  static constexpr int kStagingBuffers = 1;
   static constexpr bool kWarpTranspose = false, kReverseBatch = false;
   static constexpr uint32_t kEpiScratch = 0;
-  static constexpr int KB = kb_per_stage(kATileBytes + BT_ * kBK * 2, kStagingBuffers * kBM * BT_ * 2);
-  static constexpr int STAGES = ring_depth(KB * (kATileBytes + BT_ * kBK * 2), kStagingBuffers * kBM * BT_ * 2);
+  static constexpr int KB = kb_per_stage(kATileBytes + BT_ * kBK * 2, kBM * BT_ * 2);
+  static constexpr int STAGES = ring_depth(KB * (kATileBytes + BT_ * kBK * 2), kBM * BT_ * 2);
   using Epi = EpiNs;
   __host__ __device__ static constexpr int term_a(int) { return 0; }
   __host__ __device__ static constexpr int term_b(int) { return 0; }
@@ -388,7 +341,6 @@ struct OpSwigluGate {
   static constexpr int KB = 1;  // measured: two-k-block stages (a 2-deep ring here) are 7 % slower for this op
   static constexpr int NA = 1, NB = 2, NACC = 2, BT = BT_, NTERMS = KB, NOUT = 1;
   static constexpr bool kSecondInPlace = false, kTileReduce = false;
-  static constexpr int kStagingBuffers = 1;
   static constexpr bool kWarpTranspose = false, kReverseBatch = false;
   static constexpr uint32_t kEpiScratch = 0;
   static constexpr int STAGES = ring_depth(KB * (kATileBytes + 2 * BT_ * kBK * 2), kBM * BT_ * 2);
@@ -417,7 +369,6 @@ struct OpSwigluGate {
 struct OpFwGradPointwise {
   static constexpr int NA = 2, NB = 3, NACC = 3, BT = 64, NTERMS = 2, NOUT = 3;
   static constexpr bool kSecondInPlace = false, kTileReduce = false;
-  static constexpr int kStagingBuffers = 1;
   static constexpr bool kWarpTranspose = false, kReverseBatch = false;
   static constexpr uint32_t kEpiScratch = 0;
   static constexpr int KB = 1;  // two k-blocks of this op's five tiles would leave a one-stage ring

@@ -121,7 +121,6 @@ __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bul
 // waits until the sources of all committed bulk groups have been read (shared memory reusable)
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 // all but the most recently committed group have finished reading shared memory
-__device__ __forceinline__ void bulk_wait_read_but_last() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 // waits until all committed bulk groups have completed (global writes performed)
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // named barrier among `count` threads (barrier 0 is __syncthreads)

@@ -73,7 +73,7 @@ __host__ __device__ constexpr uint32_t gemm_stage_bytes() {
 // 64-column panels (the layout the output tensor maps expect)
 template <class Op>
 __host__ __device__ constexpr uint32_t gemm_staging_bytes() {
-  return Op::kStagingBuffers * (Op::kSecondInPlace ? 1 : Op::NOUT) * kBM * Op::BT * 2 + Op::kEpiScratch;
+  return (Op::kSecondInPlace ? 1 : Op::NOUT) * kBM * Op::BT * 2 + Op::kEpiScratch;
 }
 template <class Op>
 __host__ __device__ constexpr uint32_t gemm_smem_bytes() {
@@ -370,7 +370,6 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
     // publishes the tile's completion as soon as they have landed -- the epilogue warps never wait for
     // global memory, and no CTA can wait on a tile it has not yet published itself
     if constexpr (Deps::kOn && Op::NOUT > 0) {
-      static_assert(Op::kStagingBuffers == 1, "the storing warp hands over a single staging tile");
       if (lane == 0) {
         for (int tile_i = 0; tile_i < rounds && !failed; ++tile_i) {
           const int tile = tile_at(tile_i);
@@ -416,10 +415,6 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
     const int half = (warp - 2) >> 2;
     const bool elected = threadIdx.x == 64;
     const int row_local = quarter * 32 + lane;
-    constexpr uint32_t kStgBytes = NSTG * kBM * BT * 2;  // one staging buffer
-    constexpr bool kDoubleStg = Op::kStagingBuffers == 2;
-    // staging buffer of the tile with running count `tc_` (alternating when double-buffered)
-    auto stg_of = [&](uint32_t tc_) { return cx.staging + (kDoubleStg ? (tc_ & 1u) * kStgBytes : 0u); };
     auto tile_of_round = [&](int r) {
       if (r >= rounds) return -1;
       const int t = tile_at(r);
@@ -432,7 +427,7 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
       const GemmProblem<Op>& P = probs[tc.prob];
       typename Op::Epi ep = P.ep;
       patch(ep, tc.prob);
-      const uint32_t stg = stg_of(cx.tcount);
+      const uint32_t stg = cx.staging;
       const uint32_t as = cx.tcount & 1, aph = (cx.tcount >> 1) & 1;
       const int row = tc.m0 + row_local;
       // global operands of the epilogue are fetched while the tile's MMAs are still running
@@ -446,14 +441,11 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
         // A warp whose wait ran out must not leave the others stuck at a named barrier: it raises
         // a flag that only epilogue warps write, and every warp decides after the barrier.
         if (!got) cx.abort_flag[1] = 1;
-        // stores that read this tile's staging buffer must have finished reading it: with two
-        // buffers that is every group but the last one committed (the previous tile's final store)
+        // the previous tile's stores must have finished reading the staging tile
         if (elected) {
           if constexpr (Deps::kOn) {
             // the storing warp returns the staging tile once its stores have read it
             if (cx.sround > 0 && !mbar_wait(&cx.stg_empty_bar[0], (cx.sround - 1) & 1, cx.abort_flag)) cx.abort_flag[1] = 1;
-          } else if (kDoubleStg) {
-            bulk_wait_read_but_last();
           } else {
             bulk_wait_read_all();
           }
