@@ -453,7 +453,7 @@ constexpr int kNsMaxParts = 512;
 struct NsGroup {
   int32_t nmat, R, C, m, n, transposed;
   bf16 *xa, *xb;              // ping-pong iterates, nmat * R * C each
-  bf16 *gram, *cgram, *poly;  // [nmat][m][m]
+  bf16 *gram, *poly;  // [nmat][m][m]: shifted Gram matrix S = A + (b / 2c) I and polynomial P
   float* partial;             // [nmat][<= kNsMaxParts] partial sums of squares
   float* scale;               // [nmat] 1 / (||G||_F + 1e-7) when the first iterate is the unscaled bf16(G)
   uint32_t* done;             // [nmat] tile completion counters of the fused kernel
@@ -515,19 +515,17 @@ int wire_ns_group(const NsGroup& G, bf16* cur, bf16* nxt, int bt_mm, int bt_mn, 
   const int64_t mm = static_cast<int64_t>(G.m) * G.m, rc = static_cast<int64_t>(G.R) * G.C;
   const Mat X{cur, G.R, G.C, G.C, G.nmat, rc};
   const Mat XN{nxt, G.R, G.C, G.C, G.nmat, rc};
-  const Mat A{G.gram, G.m, G.m, G.m, G.nmat, mm};
-  const Mat CA{G.cgram, G.m, G.m, G.m, G.nmat, mm};
+  const Mat S{G.gram, G.m, G.m, G.m, G.nmat, mm};
   const Mat PB{G.poly, G.m, G.m, G.m, G.nmat, mm};
   const int tall = G.transposed;
-  // gram = X X^T (wide) / X^T X (tall); second output c * gram + b I
+  // gram: S = X X^T (wide) / X^T X (tall) + (b / 2c) I
   LACT_TRY(make_operand(kb_of(gram), &gram.a[0], &gram.ai[0], X, tall, kBM, 0, 0));
   LACT_TRY(make_operand(kb_of(gram), &gram.b[0], &gram.bi[0], X, tall, bt_mm, 0, 0));
   gram.M = G.m; gram.N = G.m; gram.K = G.n; gram.batch = G.nmat;
-  LACT_TRY(make_output(&gram.out[0], &gram.oi[0], A, 0, 0));
-  LACT_TRY(make_output(&gram.out[1], &gram.oi[1], CA, 0, 0));
-  // poly = (c gram + b I) gram + a I   (gram is exactly symmetric: its rows serve as the K-major B operand)
-  LACT_TRY(make_operand(kb_of(poly), &poly.a[0], &poly.ai[0], CA, 0, kBM, 0, 0));
-  LACT_TRY(make_operand(kb_of(poly), &poly.b[0], &poly.bi[0], A, 0, bt_mm, 0, 0));
+  LACT_TRY(make_output(&gram.out[0], &gram.oi[0], S, 0, 0));
+  // poly: P = c S S + (a - b^2 / 4c) I   (S is exactly symmetric: its rows serve as the K-major B operand too)
+  LACT_TRY(make_operand(kb_of(poly), &poly.a[0], &poly.ai[0], S, 0, kBM, 0, 0));
+  LACT_TRY(make_operand(kb_of(poly), &poly.b[0], &poly.bi[0], S, 0, bt_mm, 0, 0));
   poly.M = G.m; poly.N = G.m; poly.K = G.m; poly.batch = G.nmat;
   LACT_TRY(make_output(&poly.out[0], &poly.oi[0], PB, 0, 0));
   // update: X' = poly X (wide; X is [k][n]: MN-major B operand) / X' = X poly^T (tall)
@@ -577,9 +575,12 @@ int run_ns_iterations(const NsGroup* grp, int ngroups, int steps, int const_coef
         std::memset(&pg, 0, sizeof(Prob)); std::memset(&pp, 0, sizeof(Prob)); std::memset(&pu, 0, sizeof(Prob));
         LACT_TRY(wire_ns_group(grp[g], cur[g], nxt[g], btv, btv, pg, pp, pu));
         const float* sc = fold ? grp[g].scale : nullptr;
-        if (which == 0) { ga.prob[g] = pg; ga.prob[g].ep = EpiNs{0.f, co[2], co[1], sc, fold ? 2 : 0}; }
-        if (which == 1) { ga.prob[g] = pp; ga.prob[g].ep = EpiNs{co[0], 0.f, 0.f, nullptr, 0}; }
-        if (which == 2) { ga.prob[g] = pu; ga.prob[g].ep = EpiNs{0.f, 0.f, 0.f, sc, fold ? 1 : 0}; }
+        if (which == 0) { ga.prob[g] = pg; ga.prob[g].ep = EpiNs{co[1] / (2.f * co[2]), 1.f, sc, fold ? 2 : 0}; }
+        if (which == 1) {
+          ga.prob[g] = pp;
+          ga.prob[g].ep = EpiNs{co[0] - co[1] * co[1] / (4.f * co[2]), co[2], nullptr, 0};
+        }
+        if (which == 2) { ga.prob[g] = pu; ga.prob[g].ep = EpiNs{0.f, 1.f, sc, fold ? 1 : 0}; }
       }
       ga.status = status;
       return LACT_OK;
@@ -693,7 +694,6 @@ void carve_ns_group(Carver& c, NsGroup& g) {
   g.xa = c.take<bf16>(mn);
   g.xb = c.take<bf16>(mn);
   g.gram = c.take<bf16>(mm);
-  g.cgram = c.take<bf16>(mm);
   g.poly = c.take<bf16>(mm);
   g.partial = c.take<float>(static_cast<size_t>(g.nmat) * kNsMaxParts);
   g.scale = c.take<float>(static_cast<size_t>(g.nmat));
@@ -1168,12 +1168,12 @@ int lact_newton_schulz(const void* g, int32_t g_dtype, void* x, int64_t B, int64
 
 // ---------------------------------------------------------------- Newton-Schulz with saved iterates, and its backward
 // Trace layout in the caller's buffer (bf16 unless noted): group scratch (norm partials,
-// scale factors); X[0..steps] ([B][R][C] each); gram A, c A + b I, poly P per iteration ([B][m][m]);
-// then the backward's temporaries: c A + (b/2) I, Q, S ([B][m][m]) and two [B][R][C] gradient buffers.
+// scale factors); X[0..steps] ([B][R][C] each); shifted Gram matrix A + (b/2c) I and polynomial P per iteration
+// ([B][m][m]); then the backward's temporaries: c A + (b/2) I, Q, S ([B][m][m]) and two [B][R][C] gradient buffers.
 struct NsTrace {
   NsGroup grp;
   bf16* X;   // (steps + 1) iterates
-  bf16 *A, *CA, *P;  // steps matrices each
+  bf16 *A, *P;  // steps matrices each (A: the shifted Gram matrix)
   bf16 *CB, *Q, *S, *dXa, *dXb;
   size_t bytes;
 };
@@ -1188,7 +1188,6 @@ static int plan_ns_trace(void* base, int64_t B, int64_t R, int64_t C, int steps,
   t->grp.done = cv.take<uint32_t>(static_cast<size_t>(B) + 64);
   t->X = cv.take<bf16>(rc * (steps + 1));
   t->A = cv.take<bf16>(mm * steps);
-  t->CA = cv.take<bf16>(mm * steps);
   t->P = cv.take<bf16>(mm * steps);
   t->CB = cv.take<bf16>(mm);
   t->Q = cv.take<bf16>(mm);
@@ -1227,7 +1226,6 @@ int lact_ns_trace_fwd(const void* g, int32_t g_dtype, void* x_out, int64_t B, in
     gi.xa = t.X + rc * it;
     gi.xb = t.X + rc * (it + 1);
     gi.gram = t.A + mm * it;
-    gi.cgram = t.CA + mm * it;
     gi.poly = t.P + mm * it;
     const bf16* res = nullptr;
     LACT_TRY(run_ns_iterations(&gi, 1, 1, const_coeffs, &res, status_word, s, 0, const_coeffs ? 0 : it));
@@ -1260,8 +1258,9 @@ int lact_ns_trace_bwd(const void* du, void* dx0, int64_t B, int64_t R, int64_t C
     const bf16* P = t.P + mm * it;
     {
       KernelScope scope(kClsOther, s);
-      diag_shift_kernel<<<ceil_div(static_cast<int64_t>(mm), 256 * 8), 256, 0, s>>>(t.CA + mm * it, t.CB, static_cast<int>(m),
-                                                                                    static_cast<int64_t>(mm), -0.5f * co[1]);
+      // c A + (b/2) I = c (A + (b/2c) I)
+      scale_bf16_kernel<<<ceil_div(static_cast<int64_t>(mm), 256 * 8), 256, 0, s>>>(t.A + mm * it, t.CB,
+                                                                                    static_cast<int64_t>(mm), co[2]);
       LACT_CUDA(cudaGetLastError());
     }
     // Q [m][m]: contraction over the long side n

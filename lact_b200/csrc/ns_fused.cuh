@@ -27,13 +27,12 @@ struct NsFusedArgs {
 constexpr int kNsFusedMaxSteps = 16;
 
 struct NsPatch {
-  float diag, gamma, diag2;
+  float diag, acc_scale;
   int32_t scale_pow;
   const float* scale[2];
   __device__ __forceinline__ void operator()(EpiNs& ep, int prob) const {
     ep.diag = diag;
-    ep.gamma = gamma;
-    ep.diag2 = diag2;
+    ep.acc_scale = acc_scale;
     ep.scale = scale[prob];
     ep.scale_pow = scale_pow;
   }
@@ -80,7 +79,6 @@ ns_fused_kernel(const __grid_constant__ NsFusedArgs<BT_MM, BT_MN> args) {
         tma_prefetch_desc(&args.upd[par][g].a[0]);
         tma_prefetch_desc(&args.upd[par][g].b[0]);
         tma_prefetch_desc(&args.gram[par][g].out[0]);
-        tma_prefetch_desc(&args.gram[par][g].out[1]);
         tma_prefetch_desc(&args.upd[par][g].out[0]);
       }
     for (int g = 0; g < args.ngroups; ++g) {
@@ -108,23 +106,23 @@ ns_fused_kernel(const __grid_constant__ NsFusedArgs<BT_MM, BT_MN> args) {
   }
   for (int it = 0; it < args.steps && !failed; ++it) {
     const int par = it & 1;
+    const float a = args.coef[it][0], b = args.coef[it][1], c = args.coef[it][2];
     patch.scale_pow = it == 0 ? 2 : 0;
-    patch.diag = 0.f;                 // gram: A and c A + b I
-    patch.gamma = args.coef[it][2];
-    patch.diag2 = args.coef[it][1];
+    patch.diag = b / (2.f * c);       // gram: S = X X^T + (b / 2c) I
+    patch.acc_scale = 1.f;
     failed = gemm_phase<OpMM, RING>(cx, args.gram[par], args.ngroups, patch, deps);
     ++cx.phase;
     if (failed) break;
     for (int g = 0; g < 2; ++g) deps.need[g] += tiles_mm[g];
-    patch.diag = args.coef[it][0];    // poly: (c A + b I) A + a I
-    patch.gamma = 0.f;
-    patch.diag2 = 0.f;
+    patch.diag = a - b * b / (4.f * c);  // poly: P = c S S + (a - b^2 / 4c) I
+    patch.acc_scale = c;
     patch.scale_pow = 0;
     failed = gemm_phase<OpMM, RING>(cx, args.poly, args.ngroups, patch, deps);
     ++cx.phase;
     if (failed) break;
     for (int g = 0; g < 2; ++g) deps.need[g] += tiles_mm[g];
-    patch.diag = 0.f;                 // update: (P + a I) X
+    patch.diag = 0.f;                 // update: X' = P X
+    patch.acc_scale = 1.f;
     patch.scale_pow = it == 0 ? 1 : 0;
     failed = gemm_phase<OpMN, RING>(cx, args.upd[par], args.ngroups, patch, deps);
     ++cx.phase;

@@ -136,15 +136,12 @@ struct EpiDW {
   }
 };
 
-// Newton-Schulz epilogue, bf16 rounding after every elementwise op (the reference's eager
-// arithmetic): t = bf16(acc); if res: t = bf16(bf16(alpha * res) + t); out = t;
-// if out2: out2 = bf16(gamma * t).
+// Newton-Schulz epilogue: out = bf16(acc * acc_scale * s^scale_pow + diag * I), s = scale[matrix].
 struct EpiNs {
-  float diag;          // first output  = bf16(scale * acc + diag * I)
-  float gamma;         // second output = bf16(gamma * first + diag2 * I)
-  float diag2;
+  float diag;
+  float acc_scale;
   const float* scale;  // per-matrix 1 / (||G||_F + 1e-7), or nullptr
-  int32_t scale_pow;   // 0: no scaling, 1: acc * s, 2: acc * s * s
+  int32_t scale_pow;   // 0: no per-matrix scaling, 1: s, 2: s * s
 };
 
 // Fast-weight-gradient pointwise stage: from y0 = k w0^T, y2 = k w2^T, dh = v w1 and the three
@@ -181,7 +178,7 @@ __host__ __device__ constexpr int ring_depth(uint32_t stage_bytes, uint32_t stag
 template <class EpiT, int BT_>
 struct OpBmm {
   static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 0;
-  static constexpr bool kSecondInPlace = false, kTileReduce = false;
+  static constexpr bool kTileReduce = false;
   static constexpr bool kWarpTranspose = true, kReverseBatch = false;
   static constexpr uint32_t kEpiScratch = EpiT::kScratch;
   static constexpr int KB = 1;  // measured: two-k-block stages slow the training backward's products by 7 %
@@ -206,7 +203,7 @@ struct OpBmm {
 template <int BT_>
 struct OpDW {
   static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 0;
-  static constexpr bool kSecondInPlace = false, kTileReduce = true;
+  static constexpr bool kTileReduce = true;
   static constexpr bool kWarpTranspose = true;                   // results reach global memory through `EpiDW::warp_block`
   static constexpr bool kReverseBatch = true;                    // reads the planes the pointwise kernel has just written
   static constexpr uint32_t kEpiScratch = kEpiWarps * 32 * 144;  // one 32 x 32 fp32 block (rows padded to 144 bytes) per epilogue warp
@@ -243,7 +240,7 @@ struct EpiNone {};
 template <int BT_>
 struct OpBmmStore {
   static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 1;
-  static constexpr bool kSecondInPlace = false, kTileReduce = false;
+  static constexpr bool kTileReduce = false;
   static constexpr bool kWarpTranspose = false, kReverseBatch = true;
   static constexpr uint32_t kEpiScratch = 0;
   static constexpr int KB = 1;  // measured: two-k-block stages are 5 % slower for this op (K-major operands, short K)
@@ -268,7 +265,7 @@ struct OpBmmStore {
 template <class EpiT, int BT_>
 struct OpBmm2 {
   static constexpr int NA = 2, NB = 2, NACC = 1, BT = BT_, NTERMS = 2, NOUT = 0;
-  static constexpr bool kSecondInPlace = false, kTileReduce = false;
+  static constexpr bool kTileReduce = false;
   static constexpr bool kWarpTranspose = true, kReverseBatch = false;
   static constexpr uint32_t kEpiScratch = EpiT::kScratch;
   static constexpr int KB = 1;
@@ -287,20 +284,21 @@ struct OpBmm2 {
   }
 };
 
-// Newton-Schulz GEMM.  The iteration's residual terms are folded into the contractions as multiples
-// of the identity, b A + (c A) A = (c A + b I) A and a X + P X = (P + a I) X, so that no phase reads
-// a residual tile: the gram phase writes A = bf16(X X^T) and, in place from the staged A,
-// bf16(c A + b I); the poly phase writes bf16((c A + b I) A + a I); the update phase is a plain
-// product.  All values are bf16 with fp32 accumulation, as in the reference; folding moves two of
-// its rounding points (one rounding of the fp32 sum instead of bf16(bf16(b A) + bf16((c A) A))),
-// which perturbs the result no more than the reference's own bf16 arithmetic does.
-// The Frobenius normalisation X0 = G / (||G|| + 1e-7) can be folded in as well: the first iteration
-// then runs on bf16(G) itself and its gram / update epilogues multiply the fp32 accumulator by
-// s^2 / s, s = 1 / (||G|| + 1e-7) (per matrix, `scale`).
+// Newton-Schulz GEMM.  One iteration X' = a X + (b A + c A A) X, A = X X^T, runs as three plain products with
+// the polynomial's residual terms folded in as multiples of the identity (completing the square):
+//   gram:    S = A + (b / 2c) I                         (diagonal add in the epilogue)
+//   poly:    P = c S S + (a - b^2 / 4c) I = a I + b A + c A A   (S is symmetric: its rows serve as both operands)
+//   update:  X' = P X
+// so no phase reads a residual tile or writes a second output.  All stored values are bf16 with fp32
+// accumulation, as in the reference; the folding moves its rounding points (one rounding per stored matrix),
+// which against an fp64 iteration is about twice as accurate as the reference's eager bf16 arithmetic.
+// The Frobenius normalisation X0 = G / (||G|| + 1e-7) can be folded in as well: the first iteration then runs
+// on bf16(G) itself and its gram / update epilogues multiply the fp32 accumulator by s^2 / s,
+// s = 1 / (||G|| + 1e-7) (per matrix, `scale`).
 template <int BT_>
 struct OpNs {
-  static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 2;
-  static constexpr bool kSecondInPlace = true, kTileReduce = false;
+  static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 1;
+  static constexpr bool kTileReduce = false;
   static constexpr bool kWarpTranspose = false, kReverseBatch = false;
   static constexpr uint32_t kEpiScratch = 0;
   static constexpr int KB = kb_per_stage(kATileBytes + BT_ * kBK * 2, kBM * BT_ * 2);
@@ -311,18 +309,15 @@ struct OpNs {
   __host__ __device__ static constexpr int term_col(int) { return 0; }
   __host__ __device__ static constexpr int term_n(int) { return BT_; }
   __host__ __device__ static constexpr bool term_first(int) { return true; }
-  __device__ static __forceinline__ float second(const Epi& ep, float t, int row, int col) {
-    return ep.gamma * t + (row == col ? ep.diag2 : 0.f);
-  }
   __device__ static __forceinline__ bool skip_store(const Epi&, int) { return false; }
   struct Prefetch {
     float sc;
   };
   __device__ static __forceinline__ void prefetch(const Epi& ep, int batch, int, int, int, int, int, Prefetch& pf) {
-    pf.sc = 1.f;
+    pf.sc = ep.acc_scale;
     if (ep.scale_pow != 0 && ep.scale != nullptr) {
       const float s1 = ep.scale[batch];
-      pf.sc = ep.scale_pow == 2 ? s1 * s1 : s1;
+      pf.sc *= ep.scale_pow == 2 ? s1 * s1 : s1;
     }
   }
   __device__ static __forceinline__ void epilogue_staged(const Epi& ep, int, int row, int col, int, int,
@@ -340,7 +335,7 @@ template <int BT_>
 struct OpSwigluGate {
   static constexpr int KB = 1;  // measured: two-k-block stages (a 2-deep ring here) are 7 % slower for this op
   static constexpr int NA = 1, NB = 2, NACC = 2, BT = BT_, NTERMS = KB, NOUT = 1;
-  static constexpr bool kSecondInPlace = false, kTileReduce = false;
+  static constexpr bool kTileReduce = false;
   static constexpr bool kWarpTranspose = false, kReverseBatch = false;
   static constexpr uint32_t kEpiScratch = 0;
   static constexpr int STAGES = ring_depth(KB * (kATileBytes + 2 * BT_ * kBK * 2), kBM * BT_ * 2);
@@ -368,7 +363,7 @@ struct OpSwigluGate {
 // outputs (dy0, dy2, hidden * lr1).
 struct OpFwGradPointwise {
   static constexpr int NA = 2, NB = 3, NACC = 3, BT = 64, NTERMS = 2, NOUT = 3;
-  static constexpr bool kSecondInPlace = false, kTileReduce = false;
+  static constexpr bool kTileReduce = false;
   static constexpr bool kWarpTranspose = false, kReverseBatch = false;
   static constexpr uint32_t kEpiScratch = 0;
   static constexpr int KB = 1;  // two k-blocks of this op's five tiles would leave a one-stage ring
@@ -629,21 +624,15 @@ __global__ void __launch_bounds__(256) ns_scale_kernel(const NsPrepArgs args) {
   }
 }
 
-// dst = src + delta * I for [nmat] square bf16 matrices of side m (8 elements per thread).
-__global__ void __launch_bounds__(256) diag_shift_kernel(const bf16* src, bf16* dst, int m, int64_t total, float delta) {
+// dst = bf16(factor * src), 8 elements per thread.
+__global__ void __launch_bounds__(256) scale_bf16_kernel(const bf16* src, bf16* dst, int64_t total, float factor) {
   const int64_t i0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 8;
   if (i0 >= total) return;
   uint4 u = *reinterpret_cast<const uint4*>(src + i0);
-  const int64_t in_mat = i0 % (static_cast<int64_t>(m) * m);
-  const int row = static_cast<int>(in_mat / m), col = static_cast<int>(in_mat % m);
-  if (row >= col && row < col + 8) {  // the diagonal element of this row lies in this 8-element segment
-    uint32_t* w = reinterpret_cast<uint32_t*>(&u);
-    const int j = row - col;
-    const uint32_t word = w[j >> 1];
-    float lo = __uint_as_float(word << 16), hi = __uint_as_float(word & 0xFFFF0000u);
-    if (j & 1) hi += delta; else lo += delta;
-    w[j >> 1] = pack_bf16x2(lo, hi);
-  }
+  uint32_t* w = reinterpret_cast<uint32_t*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    w[i] = pack_bf16x2(factor * __uint_as_float(w[i] << 16), factor * __uint_as_float(w[i] & 0xFFFF0000u));
   *reinterpret_cast<uint4*>(dst + i0) = u;
 }
 

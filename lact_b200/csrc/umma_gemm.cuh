@@ -73,7 +73,7 @@ __host__ __device__ constexpr uint32_t gemm_stage_bytes() {
 // 64-column panels (the layout the output tensor maps expect)
 template <class Op>
 __host__ __device__ constexpr uint32_t gemm_staging_bytes() {
-  return (Op::kSecondInPlace ? 1 : Op::NOUT) * kBM * Op::BT * 2 + Op::kEpiScratch;
+  return Op::NOUT * kBM * Op::BT * 2 + Op::kEpiScratch;
 }
 template <class Op>
 __host__ __device__ constexpr uint32_t gemm_smem_bytes() {
@@ -379,26 +379,21 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
           typename Op::Epi ep = P.ep;
           patch(ep, tc.prob);
           const uint32_t stg = cx.staging;
-          const int nrounds = (Op::kSecondInPlace && P.oi[1].enabled) ? 2 : 1;
-          for (int r = 0; r < nrounds; ++r, ++cx.sround) {
-            if (!mbar_wait(&cx.stg_full_bar[0], cx.sround & 1, cx.abort_flag)) { failed = true; break; }
+          if (!mbar_wait(&cx.stg_full_bar[0], cx.sround & 1, cx.abort_flag)) { failed = true; break; }
 #pragma unroll
-            for (int o = 0; o < Op::NOUT; ++o) {
-              if (Op::kSecondInPlace ? (o != r) : (r != 0)) continue;
-              if (!P.oi[o].enabled || Op::skip_store(ep, o)) continue;
-              const uint32_t src = stg + (Op::kSecondInPlace ? 0 : o) * (kBM * BT * 2);
-              for (int pnl = 0; pnl < BT / 64; ++pnl) {
-                if (tc.n0 + pnl * 64 >= P.N) break;
-                tma_store_3d(&P.out[o], src + pnl * (kBM * 128), P.oi[o].col_off + tc.n0 + pnl * 64,
-                             P.oi[o].row_off + tc.m0, P.oi[o].batch_off + tc.batch);
-              }
+          for (int o = 0; o < Op::NOUT; ++o) {
+            if (!P.oi[o].enabled || Op::skip_store(ep, o)) continue;
+            for (int pnl = 0; pnl < BT / 64; ++pnl) {
+              if (tc.n0 + pnl * 64 >= P.N) break;
+              tma_store_3d(&P.out[o], stg + o * (kBM * BT * 2) + pnl * (kBM * 128), P.oi[o].col_off + tc.n0 + pnl * 64,
+                           P.oi[o].row_off + tc.m0, P.oi[o].batch_off + tc.batch);
             }
-            bulk_commit_group();
-            if (r == 0) cx.stamp(tile_i, 3);
-            bulk_wait_read_all();
-            mbar_arrive(&cx.stg_empty_bar[0]);
           }
-          if (failed) break;
+          bulk_commit_group();
+          cx.stamp(tile_i, 3);
+          bulk_wait_read_all();
+          mbar_arrive(&cx.stg_empty_bar[0]);
+          ++cx.sround;
           flow_publish(deps.counter[tc.prob] + tc.batch);
         }
       }
@@ -409,7 +404,7 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
     // results to bf16 into swizzled shared-memory tiles that one thread hands to TMA stores
     // (full-line writes, clipped by the output map); other ops store from registers.
     constexpr int NOUT = Op::NOUT;
-    constexpr int NSTG = Op::kSecondInPlace ? 1 : NOUT;  // staging tiles (an in-place second output reuses the first)
+    constexpr int NSTG = NOUT;  // staging tiles
     constexpr int kEpiThreads = kEpiWarps * 32;
     const int quarter = warp & 3;
     const int half = (warp - 2) >> 2;
@@ -514,7 +509,7 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
         } else if (elected) {
 #pragma unroll
           for (int o = 0; o < NOUT; ++o) {
-            if (!P.oi[o].enabled || (o == 1 && Op::kSecondInPlace) || Op::skip_store(ep, o)) continue;
+            if (!P.oi[o].enabled || Op::skip_store(ep, o)) continue;
             for (int pnl = 0; pnl < BT / 64; ++pnl) {
               if (tc.n0 + pnl * 64 >= P.N) break;
               tma_store_3d(&P.out[o], stg + o * (kBM * BT * 2) + pnl * (kBM * 128),
@@ -523,56 +518,6 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
           }
           bulk_commit_group();
           cx.stamp(tile_i, 3);
-        }
-        if constexpr (Op::kSecondInPlace) {
-          // second output = f(first output), computed in place in the first staging tile
-          if (P.oi[1].enabled) {
-            if (elected) {
-              if constexpr (Deps::kOn) {
-                if (!mbar_wait(&cx.stg_empty_bar[0], (cx.sround - 1) & 1, cx.abort_flag)) cx.abort_flag[1] = 1;
-              } else {
-                bulk_wait_read_all();
-              }
-            }
-            named_barrier_sync(1, kEpiThreads);
-            if (cx.abort_flag[1] != 0) { failed = true; break; }
-            for (int c = half * 32; c < BT; c += 64) {
-              if (tc.n0 + c >= P.N) break;
-              const uint32_t base = stg + (c >> 6) * (kBM * 128) + row_local * 128;
-              const uint32_t unit0 = (c & 63) >> 3;
-#pragma unroll
-              for (int g = 0; g < 4; ++g) {
-                const uint32_t addr = base + (((unit0 + g) ^ (row_local & 7)) << 4);
-                uint32_t w[4];
-                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                             : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
-                             : "r"(addr)
-                             : "memory");
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  const int col = tc.n0 + c + g * 8 + 2 * i;
-                  w[i] = pack_bf16x2(Op::second(ep, __uint_as_float(w[i] << 16), row, col),
-                                     Op::second(ep, __uint_as_float(w[i] & 0xFFFF0000u), row, col + 1));
-                }
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]),
-                             "r"(w[3])
-                             : "memory");
-              }
-            }
-            fence_async_proxy();
-            named_barrier_sync(2, kEpiThreads);
-            if constexpr (Deps::kOn) {
-              if (elected) mbar_arrive(&cx.stg_full_bar[0]);
-              ++cx.sround;
-            } else if (elected) {
-              for (int pnl = 0; pnl < BT / 64; ++pnl) {
-                if (tc.n0 + pnl * 64 >= P.N) break;
-                tma_store_3d(&P.out[1], stg + pnl * (kBM * 128), P.oi[1].col_off + tc.n0 + pnl * 64,
-                             P.oi[1].row_off + tc.m0, P.oi[1].batch_off + tc.batch);
-              }
-              bulk_commit_group();
-            }
-          }
         }
       }
       ++cx.tcount;

@@ -78,12 +78,12 @@ def newton_schulz(G: torch.Tensor, steps: Optional[int] = None) -> torch.Tensor:
 
 
 def newton_schulz_folded(G: torch.Tensor, steps: Optional[int] = None, fold_norm: bool = False) -> torch.Tensor:
-    """Rounding model of the CUDA kernels' Newton-Schulz: the same iteration with the residual
-    terms folded into the contractions as multiples of the identity,
-    ``b A + (c A) A = (c A + b I) A`` and ``a X + P X = (P + a I) X``; bf16 values, fp32
-    accumulation, one rounding per stored matrix.  The reference's compiled GPU graph likewise
-    rounds ``b*A + c*A@A`` and ``a*X + B@X`` once (inductor fuses the elementwise part), so its own
-    GPU and eager CPU results differ by the same kind of amount as this model and `newton_schulz`.
+    """Rounding model of the CUDA kernels' Newton-Schulz: the same iteration with the residual terms
+    folded into the contractions as multiples of the identity by completing the square,
+    ``S = A + (b/2c) I``, ``a I + b A + c A A = c S S + (a - b^2/4c) I``, ``X' = P X``; bf16 values,
+    fp32 accumulation, one rounding per stored matrix (S, P, X').  The reference's compiled GPU graph
+    likewise rounds ``b*A + c*A@A`` and ``a*X + B@X`` once (inductor fuses the elementwise part), so its
+    own GPU and eager CPU results differ by the same kind of amount as this model and `newton_schulz`.
     ``fold_norm``: the chunk recurrence also folds the Frobenius normalisation into the first
     iteration: it iterates on bf16(G) itself and multiplies the first Gram matrix by s^2 and the
     first update by s, s = 1 / (||G|| + 1e-7), in fp32 before the rounding.
@@ -102,9 +102,8 @@ def newton_schulz_folded(G: torch.Tensor, steps: Optional[int] = None, fold_norm
     for i, (a, b, c) in enumerate(coeffs):
         Xf = X.float()
         s2, s1 = (s * s, s) if (s is not None and i == 0) else (1.0, 1.0)
-        A = ((Xf @ Xf.transpose(1, 2)) * s2).to(BF16)
-        CA = (c * A.float() + b * eye).to(BF16)
-        P = (CA.float() @ A.float() + a * eye).to(BF16)
+        S = ((Xf @ Xf.transpose(1, 2)) * s2 + (b / (2.0 * c)) * eye).to(BF16)
+        P = (c * (S.float() @ S.float()) + (a - b * b / (4.0 * c)) * eye).to(BF16)
         X = ((P.float() @ Xf) * s1).to(BF16)
     if flip:
         X = X.transpose(1, 2)
