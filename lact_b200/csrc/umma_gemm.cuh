@@ -453,13 +453,15 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
       for (int c = half * 32; c < BT; c += 64) {
         if (tc.n0 + c >= P.N) break;  // warp-uniform
         float v[NACC][32];
+        {
+          uint32_t bits[NACC][32];
 #pragma unroll
-        for (int a = 0; a < NACC; ++a) {
-          uint32_t bits[32];
-          tmem_ld32(acc_base + a * BT + c, bits);
-          tmem_ld_wait();
+          for (int a = 0; a < NACC; ++a) tmem_ld32(acc_base + a * BT + c, bits[a]);
+          tmem_ld_wait();  // one wait for the loads of all accumulators
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[a][j] = __uint_as_float(bits[j]);
+          for (int a = 0; a < NACC; ++a)
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[a][j] = __uint_as_float(bits[a][j]);
         }
         if constexpr (NOUT > 0) {
           float ov[NSTG > 0 ? NSTG : 1][32];
