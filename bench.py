@@ -34,8 +34,8 @@ BF16 = torch.bfloat16
 CFG = dict(batch=8, heads=4, L=32768, D=384, H=384, chunk=2048, ns_steps=5)
 METRIC = "ttt_layer_fwd_tokens_per_s_760M_shape"
 # DRAM bytes (read + write) of ONE Newton-Schulz launch from an ncu capture of a 16-head case
-# (profiles/ns_fused_kernel_small_case.md: 14.3 MB + 36.4 MB); grows with the matrices per launch.
-NCU_DRAM_BYTES_NS_FUSED_16_HEADS = 50.8e6
+# (profiles/ns_fused_kernel_small_case.md: 14.3 MB + 8.5 MB); grows with the matrices per launch.
+NCU_DRAM_BYTES_NS_FUSED_16_HEADS = 22.7e6
 E2E_SLABS = 4  # the end-to-end arm streams the batch through the device in this many slabs
 
 
