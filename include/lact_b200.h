@@ -190,6 +190,16 @@ int lact_prenorm_momentum_l2norm(const void *x, const void *dx, const void *m, c
                                  void *x_out, void *m_out, void *y_out, int64_t B, int64_t T, int64_t D, float eps,
                                  void *stream);
 
+/* Fast-weight inputs of the LLM layer from the projected activations, in one pass (replaces the SiLU, l2_norm and
+ * head split / merge passes of lact_llm/lact_model/layer_lact_swiglu.py:399-414, `ttt_nope` branch, and
+ * ttt_operation.py:19-26): q, k <- l2_norm(silu(x)) per head, v <- silu(x) (qkv_silu = 0: no SiLU; v_silu = 0:
+ * none on v), every intermediate rounded to bf16 as in the reference's eager arithmetic.
+ * xq, xk, xv: bf16 [b][s][n_heads * d] with row stride ld_* and batch stride bs_* (elements; views of a fused
+ * projection are fine); q, k, v: bf16 [(b n_heads)][s][d] contiguous.  d <= 1024, a multiple of 8. */
+int lact_qkv_prologue(const void *xq, const void *xk, const void *xv, int64_t ld_q, int64_t ld_k, int64_t ld_v,
+                      int64_t bs_q, int64_t bs_k, int64_t bs_v, void *q, void *k, void *v, int64_t b, int64_t s,
+                      int64_t n_heads, int64_t d, int32_t qkv_silu, int32_t v_silu, void *stream);
+
 /* Building blocks of the training backward (the reference's backward is autograd through
  * lact_swiglu_ffn.py:46-76, lact_fw_grad.py:61-156 and the eager momentum / Newton-Schulz / renorm ops).
  *

@@ -1275,6 +1275,41 @@ int lact_ns_trace_bwd(const void* du, void* dx0, int64_t B, int64_t R, int64_t C
   return LACT_OK;
 }
 
+int lact_qkv_prologue(const void* xq, const void* xk, const void* xv, int64_t ld_q, int64_t ld_k, int64_t ld_v,
+                      int64_t bs_q, int64_t bs_k, int64_t bs_v, void* q, void* k, void* v, int64_t b, int64_t s,
+                      int64_t n_heads, int64_t d, int32_t qkv_silu, int32_t v_silu, void* stream) {
+  if (!xq || !xk || !xv || !q || !k || !v) return LACT_ERR_NULL;
+  LACT_TRY(check_device());
+  if (b < 1 || s < 1 || n_heads < 1 || d < 8 || d > 1024 || (d % 8) != 0) return LACT_ERR_SHAPE;
+  if (b * s * n_heads > (1ll << 40) || b > 65535 || s > (1ll << 30)) return LACT_ERR_SHAPE;
+  const void* xs[3] = {xq, xk, xv};
+  void* outs[3] = {q, k, v};
+  const int64_t lds[3] = {ld_q, ld_k, ld_v}, bss[3] = {bs_q, bs_k, bs_v};
+  PrologueArgs a;
+  std::memset(&a, 0, sizeof(a));
+  for (int t = 0; t < 3; ++t) {
+    // rows move as 16-byte vectors
+    if ((reinterpret_cast<uintptr_t>(xs[t]) & 15) != 0 || (reinterpret_cast<uintptr_t>(outs[t]) & 15) != 0 ||
+        lds[t] < n_heads * d || (lds[t] % 8) != 0 || (bss[t] % 8) != 0)
+      return LACT_ERR_SHAPE;
+    a.x[t] = static_cast<const bf16*>(xs[t]);
+    a.out[t] = static_cast<bf16*>(outs[t]);
+    a.ld[t] = lds[t];
+    a.bs[t] = bss[t];
+  }
+  a.b = static_cast<int32_t>(b); a.s = static_cast<int32_t>(s);
+  a.n_h = static_cast<int32_t>(n_heads); a.d = static_cast<int32_t>(d);
+  a.silu[0] = a.silu[1] = qkv_silu ? 1 : 0;
+  a.silu[2] = (qkv_silu && v_silu) ? 1 : 0;
+  a.l2norm[0] = a.l2norm[1] = 1;
+  a.l2norm[2] = 0;
+  const int64_t rows = b * s * n_heads;
+  KernelScope scope(kClsOther, static_cast<cudaStream_t>(stream));
+  qkv_prologue_kernel<<<static_cast<unsigned>(ceil_div(rows, 8)), 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  LACT_CUDA(cudaGetLastError());
+  return LACT_OK;
+}
+
 int lact_l2_norm_add(const void* x, int32_t x_dtype, const void* x_add, int32_t add_dtype, const void* scale, void* y,
                      int32_t y_dtype, int64_t B, int64_t T, int64_t D, float eps, void* stream) {
   if (!x || !x_add || !scale || !y) return LACT_ERR_NULL;

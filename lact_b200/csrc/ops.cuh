@@ -980,4 +980,76 @@ __global__ void prenorm_momentum_kernel(const float* x, const bf16* dx, const fl
   for (int c = lane; c < D; c += 32) yo[off + c] = __float2bfloat16_rn(xo[off + c] / den * sc);
 }
 
+// ------------------------------------------------------------------------------------------
+// layer prologue: fast-weight inputs from the projected activations
+// ------------------------------------------------------------------------------------------
+struct PrologueArgs {
+  const bf16* x[3];      // q, k, v projections: [b][s][n_h * d], row stride ld[i], batch stride bs[i] (elements)
+  int64_t ld[3], bs[3];
+  bf16* out[3];          // [(b n_h)][s][d] contiguous
+  int32_t b, s, n_h, d;
+  int32_t silu[3];       // apply SiLU to q / k / v
+  int32_t l2norm[3];     // per-head l2 norm (q and k in the reference layer)
+};
+
+// One warp per (batch, token, head): y = silu(x) rounded to bf16, then y / (bf16(||y||) + 1e-5) with the norm, the
+// sum and the quotient rounded to bf16 one after the other, as the reference's bf16 eager arithmetic does
+// (layer_lact_swiglu.py:404-414, ttt_operation.py:19-26); rows are written head-major, so the head split costs no
+// extra pass.  d <= 1024, a multiple of 8.
+__global__ void __launch_bounds__(256) qkv_prologue_kernel(const PrologueArgs a) {
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t rows = static_cast<int64_t>(a.b) * a.s * a.n_h;
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const int h = static_cast<int>(row % a.n_h);
+  const int64_t bs_idx = row / a.n_h;
+  const int tok = static_cast<int>(bs_idx % a.s), bi = static_cast<int>(bs_idx / a.s);
+  const int64_t out_off = ((static_cast<int64_t>(bi) * a.n_h + h) * a.s + tok) * a.d;
+#pragma unroll
+  for (int t = 0; t < 3; ++t) {
+    const bf16* src = a.x[t] + bi * a.bs[t] + tok * a.ld[t] + static_cast<int64_t>(h) * a.d;
+    float y[4][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int col = (c * 32 + lane) * 8;
+      if (col < a.d) {
+        const uint4 u = *reinterpret_cast<const uint4*>(src + col);
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float lo = __uint_as_float(w[i] << 16), hi = __uint_as_float(w[i] & 0xFFFF0000u);
+          if (a.silu[t]) {
+            // fast exponential and divide: their fp32 error (a few ulp) moves the bf16 rounding of about one value
+            // in ten thousand by one ulp
+            lo = bf16_round(__fdividef(lo, 1.f + __expf(-lo)));
+            hi = bf16_round(__fdividef(hi, 1.f + __expf(-hi)));
+          }
+          y[c][2 * i] = lo;
+          y[c][2 * i + 1] = hi;
+          ss += lo * lo + hi * hi;
+        }
+      }
+    }
+    float inv_den = 1.f;
+    if (a.l2norm[t]) {
+      ss = warp_sum(ss);
+      inv_den = 1.f / bf16_round(bf16_round(sqrtf(ss)) + 1e-5f);
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int col = (c * 32 + lane) * 8;
+      if (col < a.d) {
+        uint4 u;
+        uint32_t* w = reinterpret_cast<uint32_t*>(&u);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          w[i] = pack_bf16x2(y[c][2 * i] * inv_den, y[c][2 * i + 1] * inv_den);
+        }
+        *reinterpret_cast<uint4*>(a.out[t] + out_off + col) = u;
+      }
+    }
+  }
+}
+
 }  // namespace lact

@@ -665,3 +665,29 @@ def make_inputs(B: int, L: int, D: int, H: int, seed: int = 0, act_dtype=torch.f
     beta = torch.sigmoid(torch.randn(B, L, 1, generator=g))
     return dict(w0=w0, w1=w1, w2=w2, q=q.to(act_dtype), k=k.to(act_dtype), v=v.to(act_dtype),
                 lr0=lr0, lr1=lr1, lr2=lr2, momentum=beta)
+
+
+# ---------------------------------------------------------------------------------------------------
+# layer prologue (inputs of the recurrence)
+# ---------------------------------------------------------------------------------------------------
+def qkv_prologue(xq: torch.Tensor, xk: torch.Tensor, xv: torch.Tensor, n_heads: int, qkv_silu: bool = True,
+                 v_silu: bool = True):
+    """Fast-weight inputs of the LLM layer without RoPE (lact_llm/lact_model/layer_lact_swiglu.py:399-414):
+    split [b, s, n_h*d] into heads merged with the batch ([(b n_h), s, d]), SiLU on q and k (and v unless
+    `no_v_silu`), then the per-head `l2_norm` of q and k (ttt_operation.py:19-26): x / (||x|| + 1e-5) with the
+    norm, the sum and the quotient each rounded to the input dtype (bf16 under the layer's autocast)."""
+    def heads(t):
+        b, s, nd = t.shape
+        d = nd // n_heads
+        return t.reshape(b, s, n_heads, d).permute(0, 2, 1, 3).reshape(b * n_heads, s, d)
+
+    def l2n(x):
+        return (x / (x.norm(dim=-1, keepdim=True) + 1e-5)).type(x.dtype)
+
+    q, k, v = heads(xq), heads(xk), heads(xv)
+    if qkv_silu:
+        q, k = F.silu(q), F.silu(k)
+        if v_silu:
+            v = F.silu(v)
+    return l2n(q).contiguous(), l2n(k).contiguous(), v.contiguous()
+

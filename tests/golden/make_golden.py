@@ -3,7 +3,8 @@
 Run in a container that holds the reference tree (default /root/reference, or
 LACT_REFERENCE_ROOT):
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py              # chunk drivers and sub-ops -> ref_outputs.pt
+    python tests/golden/make_golden.py --prologue   # layer prologue             -> layer_prologue.pt
 
 The reference ships no golden vectors for this path, so these fixtures are outputs of the
 reference itself (eager mode, CPU) on seeded inputs produced by `oracle.lact_oracle.make_inputs`.
@@ -153,7 +154,40 @@ def subop_cases():
     return res
 
 
+PROLOGUE_OUT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "layer_prologue.pt")
+
+
+def prologue_cases():
+    """Fast-weight input prologue of the LLM layer (lact_llm/lact_model/layer_lact_swiglu.py:399-414, the
+    `ttt_nope` branch): head split, SiLU on q, k (and v), per-head `l2_norm` of q, k -- executed with the
+    reference's own `l2_norm` (ttt_operation.py:19-26), `F.silu` and the same einops patterns, bf16 as under
+    the layer's autocast."""
+    import torch.nn.functional as F
+    from einops import rearrange
+    l2_norm = ref_loader.llm_unfused().l2_norm
+    res = {}
+    for name, (b, s, n_h, d, v_silu, seed) in dict(a=(2, 37, 4, 64, True, 200), b=(1, 130, 2, 384, False, 201),
+                                                    c=(3, 16, 3, 192, True, 202)).items():
+        g = torch.Generator().manual_seed(seed)
+        xq, xk, xv = (torch.randn(b, s, n_h * d, generator=g).to(BF16) * 1.5 for _ in range(3))
+        fq, fk, fv = (rearrange(t, "b s (n_h d) -> (b n_h) s d", n_h=n_h) for t in (xq, xk, xv))
+        fq, fk = F.silu(fq), F.silu(fk)
+        if v_silu:
+            fv = F.silu(fv)
+        fq, fk = l2_norm(fq), l2_norm(fk)
+        res[name] = dict(spec=dict(b=b, s=s, n_h=n_h, d=d, v_silu=v_silu, seed=seed),
+                         q=fq.contiguous(), k=fk.contiguous(), v=fv.contiguous())
+        print("prologue", name, tuple(fq.shape), fq.dtype)
+    return res
+
+
 def main():
+    if "--prologue" in sys.argv:
+        assert ref_loader.available(), "reference tree not found"
+        torch.set_num_threads(1)
+        torch.save(prologue_cases(), PROLOGUE_OUT)
+        print("wrote", PROLOGUE_OUT, os.path.getsize(PROLOGUE_OUT) // 1024, "KiB")
+        return
     assert ref_loader.available(), "reference tree not found"
     torch.set_num_threads(1)  # fixtures must not depend on the thread count
     blob = {"cases": {}, "subops": subop_cases(), "torch": torch.__version__}

@@ -1,0 +1,85 @@
+"""Layer prologue on the GPU against the CPU oracle (which is pinned bit-exact to the reference's own outputs,
+tests/test_oracle_golden.py) and against the reference fixtures directly."""
+import os
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+BF16 = torch.bfloat16
+
+
+@pytest.fixture(scope="module")
+def lb():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from lact_b200 import build
+    build.build()
+    import lact_b200
+    return lact_b200
+
+
+@pytest.fixture(scope="module")
+def orc():
+    from oracle import lact_oracle
+    return lact_oracle
+
+
+def _ulp_report(got: torch.Tensor, ref: torch.Tensor):
+    """(fraction of elements that differ, largest difference in bf16 ulps of the reference value)."""
+    g, r = got.float().cpu(), ref.float().cpu()
+    diff = (g - r).abs()
+    ulp = torch.maximum(r.abs(), torch.full_like(r, 2.0 ** -126)).log2().floor().exp2() * 2.0 ** -7
+    return float((diff > 0).float().mean()), float((diff / ulp).max())
+
+
+def _check(got, ref, what):
+    frac, worst = _ulp_report(got, ref)
+    # expf and the order of the fp32 row sum may move a value across a bf16 rounding boundary: at most one ulp of
+    # the element (two where the row norm itself moved by one ulp), and only for a small share of the elements
+    assert worst <= 2.0 and frac <= 0.02, f"{what}: {frac:.4%} of elements differ, worst {worst} ulp"
+
+
+@pytest.mark.parametrize("b,s,n_h,d,v_silu", [(2, 37, 4, 64, True), (1, 130, 2, 384, False), (3, 16, 3, 192, True),
+                                              (1, 5, 1, 1024, True), (2, 9, 6, 8, True)])
+def test_qkv_prologue_against_oracle(lb, orc, b, s, n_h, d, v_silu):
+    from lact_b200 import layer_ops
+    g = torch.Generator().manual_seed(7)
+    xq, xk, xv = (torch.randn(b, s, n_h * d, generator=g).to(BF16) * 1.5 for _ in range(3))
+    rq, rk, rv = orc.qkv_prologue(xq, xk, xv, n_h, True, v_silu)
+    q, k, v = layer_ops.qkv_prologue(xq.cuda(), xk.cuda(), xv.cuda(), n_h, qkv_silu=True, no_v_silu=not v_silu)
+    assert q.shape == rq.shape and q.dtype == BF16 and q.is_contiguous()
+    _check(q, rq, "q"); _check(k, rk, "k"); _check(v, rv, "v")
+    # without SiLU the values of v pass through untouched and q, k are only normalised
+    rq, rk, rv = orc.qkv_prologue(xq, xk, xv, n_h, False, v_silu)
+    q, k, v = layer_ops.qkv_prologue(xq.cuda(), xk.cuda(), xv.cuda(), n_h, qkv_silu=False)
+    _check(q, rq, "q (no silu)"); _check(k, rk, "k (no silu)")
+    assert torch.equal(v.cpu(), rv)
+
+
+def test_qkv_prologue_reference_fixtures_and_fused_projection_views(lb, orc):
+    from lact_b200 import layer_ops
+    blob = torch.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "layer_prologue.pt"),
+                      map_location="cpu", weights_only=False)
+    for name, case in blob.items():
+        sp = case["spec"]
+        g = torch.Generator().manual_seed(sp["seed"])
+        xq, xk, xv = (torch.randn(sp["b"], sp["s"], sp["n_h"] * sp["d"], generator=g).to(BF16) * 1.5 for _ in range(3))
+        # the three projections as column blocks of one fused [b, s, 3 n_h d] tensor (strided views)
+        fused = torch.cat([xq, xk, xv], dim=-1).cuda()
+        nd = sp["n_h"] * sp["d"]
+        vq, vk, vv = fused[..., :nd], fused[..., nd:2 * nd], fused[..., 2 * nd:]
+        assert not vq.is_contiguous()
+        q, k, v = layer_ops.qkv_prologue(vq, vk, vv, sp["n_h"], no_v_silu=not sp["v_silu"])
+        _check(q, case["q"], name + " q"); _check(k, case["k"], name + " k"); _check(v, case["v"], name + " v")
+
+
+def test_qkv_prologue_rejects_bad_arguments(lb):
+    from lact_b200 import layer_ops
+    x = torch.zeros(1, 4, 24, dtype=BF16, device="cuda")
+    with pytest.raises(ValueError):
+        layer_ops.qkv_prologue(x, x, x, 2)          # d = 12 is not a multiple of 8
+    with pytest.raises(ValueError):
+        layer_ops.qkv_prologue(x.cpu(), x.cpu(), x.cpu(), 3)
+    with pytest.raises(AssertionError):
+        layer_ops.qkv_prologue(x.float(), x.float(), x.float(), 3)

@@ -128,3 +128,20 @@ def test_scan_model_tracks_reference_without_muon(golden):
     o, *_ = orc.scan_model(inp["w0"], inp["w1"], inp["w2"], inp["q"], inp["k"], inp["v"], inp["lr0"], inp["lr1"],
                            inp["lr2"], trace, cfg, momentum=inp["momentum"])
     assert orc.rel_max(o, case["out"]["o"]) < 1e-4
+
+
+def test_layer_prologue_matches_reference_outputs():
+    """`qkv_prologue` (silu, per-head l2 norm, head split) against outputs of the reference's own functions
+    (tests/golden/layer_prologue.pt, written by make_golden.py --prologue): bit-exact."""
+    import os
+    import torch
+    from oracle import lact_oracle as orc
+    blob = torch.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "layer_prologue.pt"),
+                      map_location="cpu", weights_only=False)
+    for name, case in blob.items():
+        sp = case["spec"]
+        g = torch.Generator().manual_seed(sp["seed"])
+        xq, xk, xv = (torch.randn(sp["b"], sp["s"], sp["n_h"] * sp["d"], generator=g).to(torch.bfloat16) * 1.5
+                      for _ in range(3))
+        q, k, v = orc.qkv_prologue(xq, xk, xv, sp["n_h"], True, sp["v_silu"])
+        assert torch.equal(q, case["q"]) and torch.equal(k, case["k"]) and torch.equal(v, case["v"]), name
