@@ -269,6 +269,17 @@ def other_config_timings(lb, dev, steps=5):
             i["w0"], i["w1"], i["w2"], i["q"], i["k"], i["v"], *i["lr"], 1.0, mini_batch_size=1560, update_every=1560,
             use_moun=True, num_moun_iters=5, fw_momentum=i["mom"], use_momentum=True), 32760)
     lb.synchronize_and_check()
+    # layer prologue at the benchmark shape: head split + SiLU + per-head l2 norm of q, k (SiLU of v) in one pass over
+    # the three column blocks of a fused [b, s, 3 n_h d] projection; HBM-bound work: bytes = read + write
+    from lact_b200 import layer_ops
+    b_, s_, nh_, d_ = CFG["batch"], CFG["L"], CFG["heads"], CFG["D"]
+    fused = rn(b_, s_, 3 * nh_ * d_).to(BF16)
+    nd = nh_ * d_
+    r = timed(lambda: layer_ops.qkv_prologue(fused[..., :nd], fused[..., nd:2 * nd], fused[..., 2 * nd:], nh_), b_ * s_)
+    moved = 2 * 3 * b_ * s_ * nd * 2
+    r["gb_per_s"] = moved / (r["ms_per_step"] * 1e-3) / 1e9
+    r["frac_of_hbm_peak"] = r["gb_per_s"] / measured_peaks()["hbm_gbs"]
+    out["qkv_prologue_760M_shape"] = r
     return out
 
 
