@@ -1421,7 +1421,7 @@ int lact_swiglu_bwd_planes(const void* y02, const void* dh, const void* lr0, con
                            int32_t lr_dtype, float w_scale, void* dy02, void* hid, int64_t rows, int64_t H,
                            void* stream) {
   if (!y02 || !dh || !dy02 || !hid) return LACT_ERR_NULL;
-  if (rows < 1 || H < 1) return LACT_ERR_SHAPE;
+  if (rows < 1 || H < 8 || (H % 8) != 0) return LACT_ERR_SHAPE;  // planes move as 16-byte vectors
   const PlaneArgs a = make_plane_args(y02, dh, nullptr, nullptr, lr0, lr1, lr2, lr_dtype, w_scale, dy02, hid, nullptr,
                                       nullptr, nullptr, nullptr, nullptr, rows, H);
   KernelScope scope(kClsOther, static_cast<cudaStream_t>(stream));
@@ -1437,7 +1437,7 @@ int lact_fw_grad_bwd_pointwise(const void* y02, const void* dh, const void* g_dy
   if (!y02 || !dh || !g_dy02 || !g_hid || !lr0 || !lr1 || !lr2 || !g_y02 || !g_dh || !dy02 || !hid || !g_lr0 ||
       !g_lr1 || !g_lr2)
     return LACT_ERR_NULL;
-  if (rows < 1 || H < 1) return LACT_ERR_SHAPE;
+  if (rows < 1 || H < 8 || (H % 8) != 0) return LACT_ERR_SHAPE;  // planes move as 16-byte vectors
   const PlaneArgs a = make_plane_args(y02, dh, g_dy02, g_hid, lr0, lr1, lr2, lr_dtype, w_scale, dy02, hid, g_y02, g_dh,
                                       g_lr0, g_lr1, g_lr2, rows, H);
   KernelScope scope(kClsOther, static_cast<cudaStream_t>(stream));
@@ -1478,7 +1478,7 @@ int lact_swiglu_planes_f32(const void* y02, const void* dh, const void* lr0, con
                            int32_t lr_dtype, float w_scale, void* dy02, void* hid, int64_t rows, int64_t H,
                            void* stream) {
   if (!y02 || !hid || (dh != nullptr && !dy02)) return LACT_ERR_NULL;
-  if (rows < 1 || H < 1) return LACT_ERR_SHAPE;
+  if (rows < 1 || H < 8 || (H % 8) != 0) return LACT_ERR_SHAPE;  // planes move as 16-byte vectors
   KernelScope scope(kClsOther, static_cast<cudaStream_t>(stream));
   swiglu_planes_f32_kernel<<<ceil_div(rows, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const float*>(y02), static_cast<const float*>(dh), lr0, lr1, lr2, lr_dtype == LACT_F32, w_scale,

@@ -743,6 +743,23 @@ struct PlaneArgs {
   int32_t H;
 };
 
+// eight consecutive bf16 values as floats / back (16-byte accesses; column counts here are multiples of 8)
+__device__ __forceinline__ void load8_bf16(const bf16* p, float (&v)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+__device__ __forceinline__ void store8_bf16(bf16* p, const float (&v)[8]) {
+  uint4 u;
+  u.x = pack_bf16x2(v[0], v[1]); u.y = pack_bf16x2(v[2], v[3]);
+  u.z = pack_bf16x2(v[4], v[5]); u.w = pack_bf16x2(v[6], v[7]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+
 // First-order planes: hidden*lr1, dy0*lr0, dy2*lr2 from (bf16-rounded) y0, y2, dh.  Used by the
 // backward of apply (lr = 1; lact_swiglu_ffn.py:46-76).  One warp per token row.
 __global__ void __launch_bounds__(256) swiglu_bwd_planes_kernel(const PlaneArgs a) {
@@ -753,14 +770,21 @@ __global__ void __launch_bounds__(256) swiglu_bwd_planes_kernel(const PlaneArgs 
   const float l1 = (a.lr1 ? load_scalar(a.lr1, a.lr_f32, row) : 1.f) * a.w_scale;
   const float l2 = (a.lr2 ? load_scalar(a.lr2, a.lr_f32, row) : 1.f) * a.w_scale;
   const int H = a.H;
-  for (int c = lane; c < H; c += 32) {
-    const float y0 = __bfloat162float(a.y02[row * 2 * H + c]);
-    const float y2 = __bfloat162float(a.y02[row * 2 * H + H + c]);
-    const float dh = __bfloat162float(a.dh[row * H + c]);
-    const float sg = sigmoidf_fast(y0), sw = sg * y0;
-    a.hid[row * H + c] = __float2bfloat16_rn(sw * y2 * l1);
-    a.dy02[row * 2 * H + c] = __float2bfloat16_rn(sg * y2 * dh * (1.0f + y0 * (1.0f - sg)) * l0);
-    a.dy02[row * 2 * H + H + c] = __float2bfloat16_rn(sw * dh * l2);
+  for (int c = lane * 8; c < H; c += 256) {
+    float y0[8], y2[8], dh[8], oh[8], o0[8], o2[8];
+    load8_bf16(a.y02 + row * 2 * H + c, y0);
+    load8_bf16(a.y02 + row * 2 * H + H + c, y2);
+    load8_bf16(a.dh + row * H + c, dh);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float sg = sigmoidf_fast(y0[j]), sw = sg * y0[j];
+      oh[j] = sw * y2[j] * l1;
+      o0[j] = sg * y2[j] * dh[j] * (1.0f + y0[j] * (1.0f - sg)) * l0;
+      o2[j] = sw * dh[j] * l2;
+    }
+    store8_bf16(a.hid + row * H + c, oh);
+    store8_bf16(a.dy02 + row * 2 * H + c, o0);
+    store8_bf16(a.dy02 + row * 2 * H + H + c, o2);
   }
 }
 
@@ -777,25 +801,36 @@ __global__ void __launch_bounds__(256) fw_grad_bwd_pointwise_kernel(const PlaneA
   const float l2 = load_scalar(a.lr2, a.lr_f32, row) * a.w_scale;
   const int H = a.H;
   float s0 = 0.f, s1 = 0.f, s2 = 0.f;
-  for (int c = lane; c < H; c += 32) {
-    const float y0 = __bfloat162float(a.y02[row * 2 * H + c]);
-    const float y2 = __bfloat162float(a.y02[row * 2 * H + H + c]);
-    const float dh = __bfloat162float(a.dh[row * H + c]);
-    const float gd0 = __bfloat162float(a.g_dy02[row * 2 * H + c]);
-    const float gd2 = __bfloat162float(a.g_dy02[row * 2 * H + H + c]);
-    const float gh = __bfloat162float(a.g_hid[row * H + c]);
-    const float sg = sigmoidf_fast(y0), sw = sg * y0;
-    const float A = sg * (1.0f + y0 * (1.0f - sg));
-    const float Ap = sg * (1.0f - sg) * (2.0f + y0 * (1.0f - 2.0f * sg));
-    a.g_y02[row * 2 * H + c] = __float2bfloat16_rn(gh * A * y2 * l1 + gd0 * Ap * y2 * dh * l0 + gd2 * A * dh * l2);
-    a.g_y02[row * 2 * H + H + c] = __float2bfloat16_rn(gh * sw * l1 + gd0 * A * dh * l0);
-    a.g_dh[row * H + c] = __float2bfloat16_rn(gd0 * A * y2 * l0 + gd2 * sw * l2);
-    a.hid[row * H + c] = __float2bfloat16_rn(sw * y2 * l1);
-    a.dy02[row * 2 * H + c] = __float2bfloat16_rn(A * y2 * dh * l0);
-    a.dy02[row * 2 * H + H + c] = __float2bfloat16_rn(sw * dh * l2);
-    s0 += gd0 * A * y2 * dh;
-    s1 += gh * sw * y2;
-    s2 += gd2 * sw * dh;
+  for (int c = lane * 8; c < H; c += 256) {
+    float y0[8], y2[8], dh[8], gd0[8], gd2[8], gh[8];
+    load8_bf16(a.y02 + row * 2 * H + c, y0);
+    load8_bf16(a.y02 + row * 2 * H + H + c, y2);
+    load8_bf16(a.dh + row * H + c, dh);
+    load8_bf16(a.g_dy02 + row * 2 * H + c, gd0);
+    load8_bf16(a.g_dy02 + row * 2 * H + H + c, gd2);
+    load8_bf16(a.g_hid + row * H + c, gh);
+    float gy0[8], gy2[8], gdh[8], oh[8], o0[8], o2[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float sg = sigmoidf_fast(y0[j]), sw = sg * y0[j];
+      const float A = sg * (1.0f + y0[j] * (1.0f - sg));
+      const float Ap = sg * (1.0f - sg) * (2.0f + y0[j] * (1.0f - 2.0f * sg));
+      gy0[j] = gh[j] * A * y2[j] * l1 + gd0[j] * Ap * y2[j] * dh[j] * l0 + gd2[j] * A * dh[j] * l2;
+      gy2[j] = gh[j] * sw * l1 + gd0[j] * A * dh[j] * l0;
+      gdh[j] = gd0[j] * A * y2[j] * l0 + gd2[j] * sw * l2;
+      oh[j] = sw * y2[j] * l1;
+      o0[j] = A * y2[j] * dh[j] * l0;
+      o2[j] = sw * dh[j] * l2;
+      s0 += gd0[j] * A * y2[j] * dh[j];
+      s1 += gh[j] * sw * y2[j];
+      s2 += gd2[j] * sw * dh[j];
+    }
+    store8_bf16(a.g_y02 + row * 2 * H + c, gy0);
+    store8_bf16(a.g_y02 + row * 2 * H + H + c, gy2);
+    store8_bf16(a.g_dh + row * H + c, gdh);
+    store8_bf16(a.hid + row * H + c, oh);
+    store8_bf16(a.dy02 + row * 2 * H + c, o0);
+    store8_bf16(a.dy02 + row * 2 * H + H + c, o2);
   }
   s0 = warp_sum(s0); s1 = warp_sum(s1); s2 = warp_sum(s2);
   if (lane == 0) {
