@@ -200,6 +200,14 @@ int lact_qkv_prologue(const void *xq, const void *xk, const void *xv, int64_t ld
                       int64_t bs_q, int64_t bs_k, int64_t bs_v, void *q, void *k, void *v, int64_t b, int64_t s,
                       int64_t n_heads, int64_t d, int32_t qkv_silu, int32_t v_silu, void *stream);
 
+/* Per-token learning rates and momentum of the LLM layer (layer_lact_swiglu.py:463-480, 245-249):
+ * lr = softplus(float(lr_proj) + base_lr_inv), lr_proj [b][s][n_heads * 3] (row stride proj_ld) -> lr0, lr1, lr2
+ * fp32 [(b n_heads)][s]; momentum = float(sigmoid(logits) rounded to the logits' dtype), logits [b][s][n_heads]
+ * (row stride logits_ld) -> fp32 [(b n_heads)][s]; mom_logits and momentum may both be NULL. */
+int lact_lr_prologue(const void *lr_proj, int32_t proj_dtype, int64_t proj_ld, float base_lr_inv, const void *mom_logits,
+                     int32_t logits_dtype, int64_t logits_ld, void *lr0, void *lr1, void *lr2, void *momentum, int64_t b,
+                     int64_t s, int64_t n_heads, void *stream);
+
 /* Building blocks of the training backward (the reference's backward is autograd through
  * lact_swiglu_ffn.py:46-76, lact_fw_grad.py:61-156 and the eager momentum / Newton-Schulz / renorm ops).
  *

@@ -1310,6 +1310,32 @@ int lact_qkv_prologue(const void* xq, const void* xk, const void* xv, int64_t ld
   return LACT_OK;
 }
 
+int lact_lr_prologue(const void* lr_proj, int32_t proj_dtype, int64_t proj_ld, float base_lr_inv, const void* mom_logits,
+                     int32_t logits_dtype, int64_t logits_ld, void* lr0, void* lr1, void* lr2, void* momentum, int64_t b,
+                     int64_t s, int64_t n_heads, void* stream) {
+  if (!lr_proj || !lr0 || !lr1 || !lr2 || ((mom_logits == nullptr) != (momentum == nullptr))) return LACT_ERR_NULL;
+  LACT_TRY(check_device());
+  if (b < 1 || s < 1 || n_heads < 1 || b > 65535 || s > (1ll << 30) || n_heads > 4096) return LACT_ERR_SHAPE;
+  if (proj_ld < 3 * n_heads || (mom_logits && logits_ld < n_heads)) return LACT_ERR_SHAPE;
+  if ((proj_dtype != LACT_F32 && proj_dtype != LACT_BF16) ||
+      (mom_logits && logits_dtype != LACT_F32 && logits_dtype != LACT_BF16))
+    return LACT_ERR_DTYPE;
+  LrPrologueArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.proj = lr_proj; a.logits = mom_logits;
+  a.proj_f32 = proj_dtype == LACT_F32; a.logits_f32 = logits_dtype == LACT_F32;
+  a.proj_ld = proj_ld; a.logits_ld = logits_ld;
+  a.base_lr_inv = base_lr_inv;
+  a.lr[0] = static_cast<float*>(lr0); a.lr[1] = static_cast<float*>(lr1); a.lr[2] = static_cast<float*>(lr2);
+  a.mom = static_cast<float*>(momentum);
+  a.b = static_cast<int32_t>(b); a.s = static_cast<int32_t>(s); a.n_h = static_cast<int32_t>(n_heads);
+  const int64_t total = b * s * n_heads;
+  KernelScope scope(kClsOther, static_cast<cudaStream_t>(stream));
+  lr_prologue_kernel<<<static_cast<unsigned>(ceil_div(total, 256)), 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  LACT_CUDA(cudaGetLastError());
+  return LACT_OK;
+}
+
 int lact_l2_norm_add(const void* x, int32_t x_dtype, const void* x_add, int32_t add_dtype, const void* scale, void* y,
                      int32_t y_dtype, int64_t B, int64_t T, int64_t D, float eps, void* stream) {
   if (!x || !x_add || !scale || !y) return LACT_ERR_NULL;

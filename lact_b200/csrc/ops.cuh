@@ -1087,4 +1087,38 @@ __global__ void __launch_bounds__(256) qkv_prologue_kernel(const PrologueArgs a)
   }
 }
 
+// Learning rates and momentum of the layer: lr = softplus(proj + base_lr_inv) in fp32 (torch's threshold of 20),
+// proj [b][s][n_h * 3] -> three [(b n_h)][s] fp32 vectors; momentum = float(round_to_input_dtype(sigmoid(logit))),
+// logits [b][s][n_h] -> [(b n_h)][s] (layer_lact_swiglu.py:463-480, 245-249).  One thread per (batch, token, head).
+struct LrPrologueArgs {
+  const void* proj;    // bf16 or fp32
+  const void* logits;  // bf16 or fp32, or nullptr
+  int32_t proj_f32, logits_f32;
+  int64_t proj_ld, logits_ld;  // row strides in elements (rows = b * s)
+  float base_lr_inv;
+  float* lr[3];
+  float* mom;          // or nullptr
+  int32_t b, s, n_h;
+};
+__global__ void __launch_bounds__(256) lr_prologue_kernel(const LrPrologueArgs a) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t total = static_cast<int64_t>(a.b) * a.s * a.n_h;
+  if (i >= total) return;
+  // consecutive threads walk the tokens of one (batch, head): coalesced stores, strided (small) loads
+  const int tok = static_cast<int>(i % a.s);
+  const int64_t bh = i / a.s;
+  const int h = static_cast<int>(bh % a.n_h), bi = static_cast<int>(bh / a.n_h);
+  const int64_t row = static_cast<int64_t>(bi) * a.s + tok;
+#pragma unroll
+  for (int j = 0; j < 3; ++j) {
+    const float x = load_scalar(a.proj, a.proj_f32, row * a.proj_ld + h * 3 + j) + a.base_lr_inv;
+    a.lr[j][i] = x > 20.f ? x : log1pf(expf(x));
+  }
+  if (a.mom != nullptr) {
+    const float x = load_scalar(a.logits, a.logits_f32, row * a.logits_ld + h);
+    const float sg = 1.f / (1.f + expf(-x));
+    a.mom[i] = a.logits_f32 ? sg : bf16_round(sg);
+  }
+}
+
 }  // namespace lact

@@ -37,3 +37,37 @@ def qkv_prologue(xq: torch.Tensor, xk: torch.Tensor, xv: torch.Tensor, num_heads
                                           k.data_ptr(), v.data_ptr(), b, s, num_heads, d, int(bool(qkv_silu)),
                                           int(not no_v_silu), L.stream_ptr()), "lact_qkv_prologue")
     return q, k, v
+
+
+def lr_prologue(lr_proj: torch.Tensor, num_heads: int, base_lr: float, momentum_logits: torch.Tensor = None):
+    """fw_lr1, fw_lr2, fw_lr3 (and momentum) of layer_lact_swiglu.py:463-480: softplus(lr_proj.float() +
+    inv_softplus(base_lr)) split per head into three fp32 [(b n_h), s, 1] tensors; `momentum_logits` is the output of
+    the momentum Linear BEFORE its Sigmoid ([b, s, n_h]); the result is sigmoid(.) in the logits' dtype, as float."""
+    import math
+    if not lr_proj.is_cuda:
+        raise ValueError("lr_prologue needs CUDA tensors (there is no CPU implementation)")
+    assert lr_proj.dim() == 3 and lr_proj.shape[2] == 3 * num_heads
+    b, s, _ = lr_proj.shape
+
+    def rows(t):
+        if t.stride(2) != 1 or t.stride(0) != s * t.stride(1):
+            t = t.contiguous()
+        return t
+
+    lr_proj = rows(lr_proj)
+    base_lr_inv = base_lr + math.log(-math.expm1(-base_lr))
+    outs = [torch.empty(b * num_heads, s, 1, dtype=torch.float32, device=lr_proj.device) for _ in range(3)]
+    mom = None
+    lg_ptr, lg_code, lg_ld = None, L.LACT_F32, 0
+    if momentum_logits is not None:
+        assert momentum_logits.shape == (b, s, num_heads)
+        momentum_logits = rows(momentum_logits)
+        mom = torch.empty(b * num_heads, s, 1, dtype=torch.float32, device=lr_proj.device)
+        lg_ptr, lg_code, lg_ld = momentum_logits.data_ptr(), L.dtype_code(momentum_logits), momentum_logits.stride(1)
+    with torch.cuda.device(lr_proj.device):
+        L.check(L.lib().lact_lr_prologue(lr_proj.data_ptr(), L.dtype_code(lr_proj), lr_proj.stride(1), float(base_lr_inv),
+                                         lg_ptr, lg_code, lg_ld, outs[0].data_ptr(), outs[1].data_ptr(),
+                                         outs[2].data_ptr(), mom.data_ptr() if mom is not None else None, b, s, num_heads,
+                                         L.stream_ptr()), "lact_lr_prologue")
+    return outs[0], outs[1], outs[2], mom
+

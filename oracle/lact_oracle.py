@@ -691,3 +691,21 @@ def qkv_prologue(xq: torch.Tensor, xk: torch.Tensor, xv: torch.Tensor, n_heads: 
             v = F.silu(v)
     return l2n(q).contiguous(), l2n(k).contiguous(), v.contiguous()
 
+
+def lr_prologue(lr_proj: torch.Tensor, n_heads: int, base_lr: float, momentum_logits: Optional[torch.Tensor] = None):
+    """Per-token learning rates and momentum of the LLM layer (lact_llm/lact_model/layer_lact_swiglu.py:463-480 and
+    245-249): lr = softplus(lr_proj.float() + inv_softplus(base_lr)) ([b, s, n_h * 3], three per head), split into
+    three [(b n_h), s, 1] fp32 tensors; momentum = sigmoid of the projection in its own dtype (bf16 under autocast),
+    then .float(), as [(b n_h), s, 1]."""
+    import math
+    b, s, n3 = lr_proj.shape
+    base_lr_inv = base_lr + math.log(-math.expm1(-base_lr))  # inv_softplus, layer_lact_swiglu.py:44-49
+    lr = F.softplus(lr_proj.float() + base_lr_inv)
+    lr = lr.reshape(b, s, n_heads, 3).permute(0, 2, 1, 3).reshape(b * n_heads, s, 3)
+    outs = [lr[..., i:i + 1].contiguous() for i in range(3)]
+    mom = None
+    if momentum_logits is not None:
+        m = torch.sigmoid(momentum_logits).float()
+        mom = m.reshape(b, s, n_heads, 1).permute(0, 2, 1, 3).reshape(b * n_heads, s, 1).contiguous()
+    return outs[0], outs[1], outs[2], mom
+

@@ -178,6 +178,22 @@ def prologue_cases():
         res[name] = dict(spec=dict(b=b, s=s, n_h=n_h, d=d, v_silu=v_silu, seed=seed),
                          q=fq.contiguous(), k=fk.contiguous(), v=fv.contiguous())
         print("prologue", name, tuple(fq.shape), fq.dtype)
+    # learning rates and momentum of the same layer (layer_lact_swiglu.py:463-480, 245-249): softplus of the fp32
+    # projection plus inv_softplus(base_lr), split per head into three [(b n_h), s, 1] tensors; momentum = Sigmoid
+    # (inside momentum_proj, bf16 under autocast) then .float(), head-merged
+    import math
+    for name, (b, s, n_h, base_lr, seed) in dict(lr_a=(2, 37, 4, 1e-2, 210), lr_b=(3, 16, 3, 1e-3, 211)).items():
+        g = torch.Generator().manual_seed(seed)
+        proj = (torch.randn(b, s, n_h * 3, generator=g) * 2.0).to(BF16)        # lr_proj output under autocast
+        mlogit = (torch.randn(b, s, n_h, generator=g) * 2.0).to(BF16)          # momentum Linear output under autocast
+        base_lr_inv = base_lr + math.log(-math.expm1(-base_lr))                # inv_softplus, layer_lact_swiglu.py:44-49
+        lr = F.softplus(proj.float() + base_lr_inv)
+        fw_lr = rearrange(lr, "b s (n_h lr_dim) -> (b n_h) s lr_dim", n_h=n_h)
+        l1, l2, l3 = fw_lr.chunk(3, dim=-1)
+        mom = rearrange(torch.sigmoid(mlogit).float(), "b s (n_h d) -> (b n_h) s d", n_h=n_h)
+        res[name] = dict(spec=dict(b=b, s=s, n_h=n_h, base_lr=base_lr, seed=seed), lr0=l1.contiguous(), lr1=l2.contiguous(),
+                         lr2=l3.contiguous(), momentum=mom.contiguous())
+        print("lr prologue", name, tuple(l1.shape), l1.dtype, tuple(mom.shape))
     return res
 
 

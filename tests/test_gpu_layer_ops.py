@@ -62,6 +62,8 @@ def test_qkv_prologue_reference_fixtures_and_fused_projection_views(lb, orc):
     blob = torch.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "layer_prologue.pt"),
                       map_location="cpu", weights_only=False)
     for name, case in blob.items():
+        if name.startswith("lr_"):
+            continue
         sp = case["spec"]
         g = torch.Generator().manual_seed(sp["seed"])
         xq, xk, xv = (torch.randn(sp["b"], sp["s"], sp["n_h"] * sp["d"], generator=g).to(BF16) * 1.5 for _ in range(3))
@@ -83,3 +85,30 @@ def test_qkv_prologue_rejects_bad_arguments(lb):
         layer_ops.qkv_prologue(x.cpu(), x.cpu(), x.cpu(), 3)
     with pytest.raises(AssertionError):
         layer_ops.qkv_prologue(x.float(), x.float(), x.float(), 3)
+
+
+@pytest.mark.parametrize("dtype", [BF16, torch.float32])
+def test_lr_prologue_against_oracle_and_reference_fixtures(lb, orc, dtype):
+    from lact_b200 import layer_ops
+    blob = torch.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "layer_prologue.pt"),
+                      map_location="cpu", weights_only=False)
+    for name, case in blob.items():
+        if not name.startswith("lr_"):
+            continue
+        sp = case["spec"]
+        g = torch.Generator().manual_seed(sp["seed"])
+        proj = (torch.randn(sp["b"], sp["s"], sp["n_h"] * 3, generator=g) * 2.0).to(BF16).to(dtype)
+        mlogit = (torch.randn(sp["b"], sp["s"], sp["n_h"], generator=g) * 2.0).to(BF16).to(dtype)
+        ref = orc.lr_prologue(proj, sp["n_h"], sp["base_lr"], mlogit)
+        got = layer_ops.lr_prologue(proj.cuda(), sp["n_h"], sp["base_lr"], mlogit.cuda())
+        for r, x, what in zip(ref, got, ("lr0", "lr1", "lr2", "momentum")):
+            assert x.shape == r.shape and x.dtype == torch.float32
+            # fp32 softplus / sigmoid: a few ulp of expf / log1pf; the bf16-rounded sigmoid may move by one bf16 ulp
+            tol = 2.0 ** -7 if (what == "momentum" and dtype == BF16) else 2e-6
+            assert float(((x.cpu() - r).abs() / r.abs().clamp_min(1e-30)).max()) <= tol, (name, what)
+        if dtype == BF16:  # the bf16 run is the reference fixture's own case
+            assert float((got[0].cpu() - case["lr0"]).abs().max()) <= 2e-6 * float(case["lr0"].abs().max())
+            assert float((got[3].cpu() != case["momentum"]).float().mean()) <= 0.01
+    no_mom = layer_ops.lr_prologue(torch.zeros(1, 3, 6, device="cuda"), 2, 1e-2)
+    assert no_mom[3] is None and abs(float(no_mom[0][0, 0, 0]) - 1e-2) < 1e-6  # softplus(inv_softplus(base_lr)) = base_lr
+

@@ -139,9 +139,34 @@ def test_layer_prologue_matches_reference_outputs():
     blob = torch.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "layer_prologue.pt"),
                       map_location="cpu", weights_only=False)
     for name, case in blob.items():
+        if name.startswith("lr_"):
+            continue
         sp = case["spec"]
         g = torch.Generator().manual_seed(sp["seed"])
         xq, xk, xv = (torch.randn(sp["b"], sp["s"], sp["n_h"] * sp["d"], generator=g).to(torch.bfloat16) * 1.5
                       for _ in range(3))
         q, k, v = orc.qkv_prologue(xq, xk, xv, sp["n_h"], True, sp["v_silu"])
         assert torch.equal(q, case["q"]) and torch.equal(k, case["k"]) and torch.equal(v, case["v"]), name
+
+
+def test_lr_prologue_matches_reference_outputs():
+    """`lr_prologue` (softplus learning rates, sigmoid momentum, head split) against the reference expressions'
+    outputs in tests/golden/layer_prologue.pt: bit-exact."""
+    import os
+    import torch
+    from oracle import lact_oracle as orc
+    blob = torch.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "layer_prologue.pt"),
+                      map_location="cpu", weights_only=False)
+    seen = 0
+    for name, case in blob.items():
+        if not name.startswith("lr_"):
+            continue
+        sp = case["spec"]
+        g = torch.Generator().manual_seed(sp["seed"])
+        proj = (torch.randn(sp["b"], sp["s"], sp["n_h"] * 3, generator=g) * 2.0).to(torch.bfloat16)
+        mlogit = (torch.randn(sp["b"], sp["s"], sp["n_h"], generator=g) * 2.0).to(torch.bfloat16)
+        l0, l1, l2, mom = orc.lr_prologue(proj, sp["n_h"], sp["base_lr"], mlogit)
+        assert torch.equal(l0, case["lr0"]) and torch.equal(l1, case["lr1"]) and torch.equal(l2, case["lr2"]), name
+        assert torch.equal(mom, case["momentum"]), name
+        seen += 1
+    assert seen == 2
