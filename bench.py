@@ -280,6 +280,14 @@ def other_config_timings(lb, dev, steps=5):
     r["gb_per_s"] = moved / (r["ms_per_step"] * 1e-3) / 1e9
     r["frac_of_hbm_peak"] = r["gb_per_s"] / measured_peaks()["hbm_gbs"]
     out["qkv_prologue_760M_shape"] = r
+    # output side: per-head RMSNorm * silu(gate projection), head merge, residual add, one pass
+    fw_x = rn(b_ * nh_, s_, d_).to(BF16)
+    gate, o_attn, wn = rn(b_, s_, nd).to(BF16), rn(b_, s_, nd).to(BF16), torch.ones(d_, device=dev)
+    r = timed(lambda: layer_ops.out_epilogue(fw_x, wn, nh_, gate, o_attn), b_ * s_)
+    moved = 4 * b_ * s_ * nd * 2
+    r["gb_per_s"] = moved / (r["ms_per_step"] * 1e-3) / 1e9
+    r["frac_of_hbm_peak"] = r["gb_per_s"] / measured_peaks()["hbm_gbs"]
+    out["out_epilogue_760M_shape"] = r
     return out
 
 

@@ -208,6 +208,15 @@ int lact_lr_prologue(const void *lr_proj, int32_t proj_dtype, int64_t proj_ld, f
                      int32_t logits_dtype, int64_t logits_ld, void *lr0, void *lr1, void *lr2, void *momentum, int64_t b,
                      int64_t s, int64_t n_heads, void *stream);
 
+/* Output side of the LLM layer in one pass (layer_lact_swiglu.py:556-568): per-head RMSNorm of the recurrence's
+ * output (fp32 arithmetic x * rsqrt(mean(x^2) + eps) * weight, rounded to bf16: the arithmetic of the
+ * fla.modules.RMSNorm kernel the reference calls), times bf16(silu(gate_proj)), heads merged back, plus `resid`.
+ * fw_x: bf16 [(b n_heads)][s][d] contiguous; weight: fp32 [d]; gate_proj, resid (either may be NULL), out:
+ * bf16 [b][s][n_heads * d] with row strides *_ld (elements); out may alias resid.  d <= 1024, a multiple of 8. */
+int lact_out_epilogue(const void *fw_x, const void *weight, const void *gate_proj, int64_t gate_ld, const void *resid,
+                      int64_t resid_ld, void *out, int64_t out_ld, int64_t b, int64_t s, int64_t n_heads, int64_t d,
+                      float eps, void *stream);
+
 /* Building blocks of the training backward (the reference's backward is autograd through
  * lact_swiglu_ffn.py:46-76, lact_fw_grad.py:61-156 and the eager momentum / Newton-Schulz / renorm ops).
  *

@@ -70,6 +70,7 @@ def _declare(lib: C.CDLL) -> None:
                                            i32, i64, i64, i32, i64, i64, i64, i64, vp, vp]
     lib.lact_qkv_prologue.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, vp, vp, vp, i64, i64, i64, i64, i32, i32, vp]
     lib.lact_lr_prologue.argtypes = [vp, i32, i64, f32, vp, i32, i64, vp, vp, vp, vp, i64, i64, i64, vp]
+    lib.lact_out_epilogue.argtypes = [vp, vp, vp, i64, vp, i64, vp, i64, i64, i64, i64, i64, f32, vp]
     lib.lact_swiglu_bwd_planes.argtypes = [vp, vp, vp, vp, vp, i32, f32, vp, vp, i64, i64, vp]
     lib.lact_fw_grad_bwd_pointwise.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, f32, vp, vp, vp, vp, vp, vp, vp, i64,
                                                i64, vp]
@@ -85,7 +86,7 @@ def _declare(lib: C.CDLL) -> None:
                  "lact_newton_schulz_workspace_bytes", "lact_newton_schulz", "lact_l2_norm_add",
                  "lact_prenorm_momentum_l2norm", "lact_bmm_bf16", "lact_bmm2_bf16", "lact_bmm2_strided_bf16", "lact_swiglu_bwd_planes",
                  "lact_fw_grad_bwd_pointwise", "lact_renorm_bwd", "lact_sgemm_f32", "lact_swiglu_planes_f32",
-                 "lact_add_renorm", "lact_qkv_prologue", "lact_lr_prologue", "lact_ns_trace_bytes", "lact_ns_trace_fwd", "lact_ns_trace_bwd"):
+                 "lact_add_renorm", "lact_qkv_prologue", "lact_lr_prologue", "lact_out_epilogue", "lact_ns_trace_bytes", "lact_ns_trace_fwd", "lact_ns_trace_bwd"):
         getattr(lib, name).restype = C.c_int
 
 

@@ -1336,6 +1336,37 @@ int lact_lr_prologue(const void* lr_proj, int32_t proj_dtype, int64_t proj_ld, f
   return LACT_OK;
 }
 
+int lact_out_epilogue(const void* fw_x, const void* weight, const void* gate_proj, int64_t gate_ld, const void* resid,
+                      int64_t resid_ld, void* out, int64_t out_ld, int64_t b, int64_t s, int64_t n_heads, int64_t d,
+                      float eps, void* stream) {
+  if (!fw_x || !weight || !out) return LACT_ERR_NULL;
+  LACT_TRY(check_device());
+  if (b < 1 || s < 1 || n_heads < 1 || d < 8 || d > 1024 || (d % 8) != 0 || b > 65535 || s > (1ll << 30))
+    return LACT_ERR_SHAPE;
+  auto bad = [&](const void* p, int64_t ld) {
+    return p != nullptr && ((reinterpret_cast<uintptr_t>(p) & 15) != 0 || ld < n_heads * d || (ld % 8) != 0);
+  };
+  if ((reinterpret_cast<uintptr_t>(fw_x) & 15) != 0 || (reinterpret_cast<uintptr_t>(weight) & 15) != 0 ||
+      bad(gate_proj, gate_ld) || bad(resid, resid_ld) || bad(out, out_ld))
+    return LACT_ERR_SHAPE;
+  EpilogueArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.x = static_cast<const bf16*>(fw_x);
+  a.weight = static_cast<const float*>(weight);
+  a.gate = static_cast<const bf16*>(gate_proj);
+  a.resid = static_cast<const bf16*>(resid);
+  a.out = static_cast<bf16*>(out);
+  a.gate_ld = gate_ld; a.resid_ld = resid_ld; a.out_ld = out_ld;
+  a.b = static_cast<int32_t>(b); a.s = static_cast<int32_t>(s);
+  a.n_h = static_cast<int32_t>(n_heads); a.d = static_cast<int32_t>(d);
+  a.eps = eps;
+  const int64_t rows = b * s * n_heads;
+  KernelScope scope(kClsOther, static_cast<cudaStream_t>(stream));
+  out_epilogue_kernel<<<static_cast<unsigned>(ceil_div(rows, 8)), 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  LACT_CUDA(cudaGetLastError());
+  return LACT_OK;
+}
+
 int lact_l2_norm_add(const void* x, int32_t x_dtype, const void* x_add, int32_t add_dtype, const void* scale, void* y,
                      int32_t y_dtype, int64_t B, int64_t T, int64_t D, float eps, void* stream) {
   if (!x || !x_add || !scale || !y) return LACT_ERR_NULL;

@@ -1121,4 +1121,65 @@ __global__ void __launch_bounds__(256) lr_prologue_kernel(const LrPrologueArgs a
   }
 }
 
+// Output side of the layer: y = bf16(x * rsqrt(mean(x^2) + eps) * weight) per head row (fp32 arithmetic, as the
+// RMSNorm kernel the reference calls), times bf16(silu(gate projection)) rounded to bf16, heads merged back to
+// [b][s][n_h * d], plus the attention output (layer_lact_swiglu.py:556-568).  One warp per (batch, token, head).
+struct EpilogueArgs {
+  const bf16* x;        // [(b n_h)][s][d] contiguous: output of the recurrence
+  const float* weight;  // [d]
+  const bf16* gate;     // [b][s][n_h * d] gate projection before its SiLU, or nullptr
+  const bf16* resid;    // [b][s][n_h * d] tensor the result is added to, or nullptr
+  bf16* out;            // [b][s][n_h * d]
+  int64_t gate_ld, resid_ld, out_ld;  // row strides in elements (rows = b * s)
+  int32_t b, s, n_h, d;
+  float eps;
+};
+__global__ void __launch_bounds__(256) out_epilogue_kernel(const EpilogueArgs a) {
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t rows = static_cast<int64_t>(a.b) * a.s * a.n_h;
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const int h = static_cast<int>(row % a.n_h);
+  const int64_t bs_idx = row / a.n_h;  // batch * s + token
+  const int tok = static_cast<int>(bs_idx % a.s), bi = static_cast<int>(bs_idx / a.s);
+  const bf16* src = a.x + ((static_cast<int64_t>(bi) * a.n_h + h) * a.s + tok) * a.d;
+  float v[4][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const int col = (c * 32 + lane) * 8;
+    if (col < a.d) {
+      load8_bf16(src + col, v[c]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += v[c][j] * v[c][j];
+    }
+  }
+  ss = warp_sum(ss);
+  const float rstd = 1.f / sqrtf(ss / static_cast<float>(a.d) + a.eps);
+  const int64_t off = static_cast<int64_t>(h) * a.d;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const int col = (c * 32 + lane) * 8;
+    if (col >= a.d) continue;
+    float y[8];
+    const float4 w0 = *reinterpret_cast<const float4*>(a.weight + col), w1 = *reinterpret_cast<const float4*>(a.weight + col + 4);
+    const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) y[j] = bf16_round(v[c][j] * rstd * w[j]);
+    if (a.gate != nullptr) {
+      float gt[8];
+      load8_bf16(a.gate + bs_idx * a.gate_ld + off + col, gt);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) y[j] = bf16_round(y[j] * bf16_round(__fdividef(gt[j], 1.f + __expf(-gt[j]))));
+    }
+    if (a.resid != nullptr) {
+      float r[8];
+      load8_bf16(a.resid + bs_idx * a.resid_ld + off + col, r);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) y[j] += r[j];
+    }
+    store8_bf16(a.out + bs_idx * a.out_ld + off + col, y);
+  }
+}
+
 }  // namespace lact

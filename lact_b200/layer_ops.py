@@ -71,3 +71,34 @@ def lr_prologue(lr_proj: torch.Tensor, num_heads: int, base_lr: float, momentum_
                                          L.stream_ptr()), "lact_lr_prologue")
     return outs[0], outs[1], outs[2], mom
 
+
+def out_epilogue(fw_x: torch.Tensor, norm_weight: torch.Tensor, num_heads: int, scale_proj: torch.Tensor = None,
+                 o: torch.Tensor = None, eps: float = 1e-5) -> torch.Tensor:
+    """`o + merge_heads(ttt_norm(fw_x) * silu(scale_proj))` of layer_lact_swiglu.py:556-568 in one pass.
+    fw_x: [(b n_h), s, d] bf16 (output of the recurrence); norm_weight: [d]; scale_proj (the output of
+    `ttt_scale_proj`, before its SiLU) and o (attention output): [b, s, n_h * d] bf16 or None."""
+    if not fw_x.is_cuda:
+        raise ValueError("out_epilogue needs CUDA tensors (there is no CPU implementation)")
+    assert fw_x.dim() == 3 and fw_x.dtype == BF16 and fw_x.shape[0] % num_heads == 0
+    fw_x = fw_x.contiguous()
+    B, s, d = fw_x.shape
+    b = B // num_heads
+    w = norm_weight.detach().float().contiguous()
+    assert w.shape == (d,)
+
+    def rows(t, name):
+        assert t.shape == (b, s, num_heads * d), f"{name}: expected [b, s, n_heads * d]"
+        t = _rows(t, name)
+        return t if t.stride(0) == s * t.stride(1) else t.contiguous()
+
+    gate = rows(scale_proj, "scale_proj") if scale_proj is not None else None
+    res = rows(o, "o") if o is not None else None
+    out = torch.empty(b, s, num_heads * d, dtype=BF16, device=fw_x.device)
+    with torch.cuda.device(fw_x.device):
+        L.check(L.lib().lact_out_epilogue(fw_x.data_ptr(), w.data_ptr(), gate.data_ptr() if gate is not None else None,
+                                          gate.stride(1) if gate is not None else 0,
+                                          res.data_ptr() if res is not None else None,
+                                          res.stride(1) if res is not None else 0, out.data_ptr(), out.stride(1), b, s,
+                                          num_heads, d, float(eps), L.stream_ptr()), "lact_out_epilogue")
+    return out
+

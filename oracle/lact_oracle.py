@@ -709,3 +709,21 @@ def lr_prologue(lr_proj: torch.Tensor, n_heads: int, base_lr: float, momentum_lo
         mom = m.reshape(b, s, n_heads, 1).permute(0, 2, 1, 3).reshape(b * n_heads, s, 1).contiguous()
     return outs[0], outs[1], outs[2], mom
 
+
+def out_epilogue(fw_x: torch.Tensor, weight: torch.Tensor, n_heads: int, scale_proj: Optional[torch.Tensor] = None,
+                 o_attn: Optional[torch.Tensor] = None, eps: float = 1e-5) -> torch.Tensor:
+    """Output side of the LLM layer (lact_llm/lact_model/layer_lact_swiglu.py:556-568): per-head RMSNorm of the
+    recurrence's output fw_x [(b n_h), s, d] (the reference uses `fla.modules.RMSNorm`, flash-linear-attention 0.5.1,
+    a Triton kernel whose arithmetic is x * rsqrt(mean(x^2) + eps) * weight in fp32, rounded to x's dtype), times the
+    gate silu(scale_proj) (both bf16 under autocast, product rounded), heads merged back to [b, s, n_h * d] and
+    added to the attention output."""
+    B, s, d = fw_x.shape
+    b = B // n_heads
+    xf = fw_x.float()
+    y = (xf * (1 / torch.sqrt(xf.square().mean(dim=-1, keepdim=True) + eps)) * weight.float()).to(fw_x.dtype)
+    if scale_proj is not None:
+        gate = F.silu(scale_proj).reshape(b, s, n_heads, d).permute(0, 2, 1, 3).reshape(B, s, d)
+        y = y * gate
+    y = y.reshape(b, n_heads, s, d).permute(0, 2, 1, 3).reshape(b, s, n_heads * d)
+    return (o_attn + y) if o_attn is not None else y.contiguous()
+

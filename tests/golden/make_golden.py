@@ -194,6 +194,24 @@ def prologue_cases():
         res[name] = dict(spec=dict(b=b, s=s, n_h=n_h, base_lr=base_lr, seed=seed), lr0=l1.contiguous(), lr1=l2.contiguous(),
                          lr2=l3.contiguous(), momentum=mom.contiguous())
         print("lr prologue", name, tuple(l1.shape), l1.dtype, tuple(mom.shape))
+    # output epilogue of the same layer (layer_lact_swiglu.py:556-568): per-head RMSNorm of the recurrence's output
+    # (`fla.modules.RMSNorm`, a Triton kernel in the reference; its own PyTorch restatement `rms_norm_ref` with
+    # upcast=True is executed here), gate silu(ttt_scale_proj(x)), head merge, residual add to the attention output
+    import fla
+    from fla.modules.layernorm import rms_norm_ref
+    for name, (b, s, n_h, d, seed) in dict(out_a=(2, 37, 4, 64, 220), out_b=(1, 50, 2, 384, 221)).items():
+        g = torch.Generator().manual_seed(seed)
+        fw_x = (torch.randn(b * n_h, s, d, generator=g) * 2.0).to(BF16)
+        weight = 1.0 + 0.1 * torch.randn(d, generator=g)
+        sproj = (torch.randn(b, s, n_h * d, generator=g) * 1.5).to(BF16)
+        o_attn = torch.randn(b, s, n_h * d, generator=g).to(BF16)
+        normed = rms_norm_ref(fw_x, weight, None, eps=1e-5, upcast=True)
+        scale = rearrange(F.silu(sproj, inplace=False), "b s (n_h d) -> (b n_h) s d", n_h=n_h)
+        normed = normed * scale
+        merged = rearrange(normed, "(b n_h) s d -> b s (n_h d)", n_h=n_h)
+        res[name] = dict(spec=dict(b=b, s=s, n_h=n_h, d=d, seed=seed), out=(o_attn + merged).contiguous(),
+                         fla=fla.__version__)
+        print("epilogue", name, tuple(merged.shape), merged.dtype)
     return res
 
 

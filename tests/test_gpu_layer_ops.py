@@ -62,7 +62,7 @@ def test_qkv_prologue_reference_fixtures_and_fused_projection_views(lb, orc):
     blob = torch.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "layer_prologue.pt"),
                       map_location="cpu", weights_only=False)
     for name, case in blob.items():
-        if name.startswith("lr_"):
+        if name.startswith(("lr_", "out_")):
             continue
         sp = case["spec"]
         g = torch.Generator().manual_seed(sp["seed"])
@@ -111,4 +111,41 @@ def test_lr_prologue_against_oracle_and_reference_fixtures(lb, orc, dtype):
             assert float((got[3].cpu() != case["momentum"]).float().mean()) <= 0.01
     no_mom = layer_ops.lr_prologue(torch.zeros(1, 3, 6, device="cuda"), 2, 1e-2)
     assert no_mom[3] is None and abs(float(no_mom[0][0, 0, 0]) - 1e-2) < 1e-6  # softplus(inv_softplus(base_lr)) = base_lr
+
+
+@pytest.mark.parametrize("b,s,n_h,d", [(2, 37, 4, 64), (1, 50, 2, 384), (2, 9, 3, 8), (1, 3, 1, 1024)])
+def test_out_epilogue_against_oracle(lb, orc, b, s, n_h, d):
+    from lact_b200 import layer_ops
+    g = torch.Generator().manual_seed(11)
+    fw_x = (torch.randn(b * n_h, s, d, generator=g) * 2.0).to(BF16)
+    weight = 1.0 + 0.1 * torch.randn(d, generator=g)
+    sproj = (torch.randn(b, s, n_h * d, generator=g) * 1.5).to(BF16)
+    o_attn = torch.randn(b, s, n_h * d, generator=g).to(BF16)
+    for use_gate, use_res in ((True, True), (False, True), (True, False), (False, False)):
+        ref = orc.out_epilogue(fw_x, weight, n_h, sproj if use_gate else None, o_attn if use_res else None)
+        got = layer_ops.out_epilogue(fw_x.cuda(), weight.cuda(), n_h, sproj.cuda() if use_gate else None,
+                                     o_attn.cuda() if use_res else None)
+        assert got.shape == ref.shape and got.dtype == BF16
+        # chained bf16 roundings: a one-ulp move of the normalised value or of the gate moves the result by an ulp or two
+        frac, worst = _ulp_report(got, ref)
+        assert worst <= 4.0 and frac <= 0.03, (use_gate, use_res, frac, worst)
+
+
+def test_out_epilogue_reference_fixtures(lb, orc):
+    from lact_b200 import layer_ops
+    blob = torch.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "layer_prologue.pt"),
+                      map_location="cpu", weights_only=False)
+    for name, case in blob.items():
+        if not name.startswith("out_"):
+            continue
+        sp = case["spec"]
+        b, s, n_h, d = sp["b"], sp["s"], sp["n_h"], sp["d"]
+        g = torch.Generator().manual_seed(sp["seed"])
+        fw_x = (torch.randn(b * n_h, s, d, generator=g) * 2.0).to(BF16)
+        weight = 1.0 + 0.1 * torch.randn(d, generator=g)
+        sproj = (torch.randn(b, s, n_h * d, generator=g) * 1.5).to(BF16)
+        o_attn = torch.randn(b, s, n_h * d, generator=g).to(BF16)
+        got = layer_ops.out_epilogue(fw_x.cuda(), weight.cuda(), n_h, sproj.cuda(), o_attn.cuda())
+        frac, worst = _ulp_report(got, case["out"])
+        assert worst <= 4.0 and frac <= 0.03, (name, frac, worst)
 

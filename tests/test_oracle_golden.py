@@ -139,7 +139,7 @@ def test_layer_prologue_matches_reference_outputs():
     blob = torch.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "layer_prologue.pt"),
                       map_location="cpu", weights_only=False)
     for name, case in blob.items():
-        if name.startswith("lr_"):
+        if name.startswith(("lr_", "out_")):
             continue
         sp = case["spec"]
         g = torch.Generator().manual_seed(sp["seed"])
@@ -168,5 +168,29 @@ def test_lr_prologue_matches_reference_outputs():
         l0, l1, l2, mom = orc.lr_prologue(proj, sp["n_h"], sp["base_lr"], mlogit)
         assert torch.equal(l0, case["lr0"]) and torch.equal(l1, case["lr1"]) and torch.equal(l2, case["lr2"]), name
         assert torch.equal(mom, case["momentum"]), name
+        seen += 1
+    assert seen == 2
+
+
+def test_out_epilogue_matches_reference_outputs():
+    """`out_epilogue` (per-head RMSNorm, silu gate, head merge, residual add) against the fixture written with
+    flash-linear-attention's own `rms_norm_ref` and the layer's expressions: bit-exact."""
+    import os
+    import torch
+    from oracle import lact_oracle as orc
+    blob = torch.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "layer_prologue.pt"),
+                      map_location="cpu", weights_only=False)
+    seen = 0
+    for name, case in blob.items():
+        if not name.startswith("out_"):
+            continue
+        sp = case["spec"]
+        b, s, n_h, d = sp["b"], sp["s"], sp["n_h"], sp["d"]
+        g = torch.Generator().manual_seed(sp["seed"])
+        fw_x = (torch.randn(b * n_h, s, d, generator=g) * 2.0).to(torch.bfloat16)
+        weight = 1.0 + 0.1 * torch.randn(d, generator=g)
+        sproj = (torch.randn(b, s, n_h * d, generator=g) * 1.5).to(torch.bfloat16)
+        o_attn = torch.randn(b, s, n_h * d, generator=g).to(torch.bfloat16)
+        assert torch.equal(orc.out_epilogue(fw_x, weight, n_h, sproj, o_attn), case["out"]), name
         seen += 1
     assert seen == 2
