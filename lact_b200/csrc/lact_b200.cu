@@ -1305,7 +1305,14 @@ int lact_qkv_prologue(const void* xq, const void* xk, const void* xv, int64_t ld
   a.l2norm[2] = 0;
   const int64_t rows = b * s * n_heads;
   KernelScope scope(kClsOther, static_cast<cudaStream_t>(stream));
-  qkv_prologue_kernel<<<static_cast<unsigned>(ceil_div(rows, 8)), 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  const unsigned grid = static_cast<unsigned>(ceil_div(rows, 8));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (ceil_div(d, 256)) {
+    case 1: qkv_prologue_kernel<1><<<grid, 256, 0, st>>>(a); break;
+    case 2: qkv_prologue_kernel<2><<<grid, 256, 0, st>>>(a); break;
+    case 3: qkv_prologue_kernel<3><<<grid, 256, 0, st>>>(a); break;
+    default: qkv_prologue_kernel<4><<<grid, 256, 0, st>>>(a); break;
+  }
   LACT_CUDA(cudaGetLastError());
   return LACT_OK;
 }
@@ -1362,7 +1369,14 @@ int lact_out_epilogue(const void* fw_x, const void* weight, const void* gate_pro
   a.eps = eps;
   const int64_t rows = b * s * n_heads;
   KernelScope scope(kClsOther, static_cast<cudaStream_t>(stream));
-  out_epilogue_kernel<<<static_cast<unsigned>(ceil_div(rows, 8)), 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  const unsigned grid = static_cast<unsigned>(ceil_div(rows, 8));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (ceil_div(d, 256)) {
+    case 1: out_epilogue_kernel<1><<<grid, 256, 0, st>>>(a); break;
+    case 2: out_epilogue_kernel<2><<<grid, 256, 0, st>>>(a); break;
+    case 3: out_epilogue_kernel<3><<<grid, 256, 0, st>>>(a); break;
+    default: out_epilogue_kernel<4><<<grid, 256, 0, st>>>(a); break;
+  }
   LACT_CUDA(cudaGetLastError());
   return LACT_OK;
 }

@@ -1031,6 +1031,8 @@ struct PrologueArgs {
 // sum and the quotient rounded to bf16 one after the other, as the reference's bf16 eager arithmetic does
 // (layer_lact_swiglu.py:404-414, ttt_operation.py:19-26); rows are written head-major, so the head split costs no
 // extra pass.  d <= 1024, a multiple of 8.
+// NCH = ceil(d / 256): 16-byte chunks per lane (the register footprint, hence the occupancy, follows the head size).
+template <int NCH>
 __global__ void __launch_bounds__(256) qkv_prologue_kernel(const PrologueArgs a) {
   const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int64_t rows = static_cast<int64_t>(a.b) * a.s * a.n_h;
@@ -1043,10 +1045,10 @@ __global__ void __launch_bounds__(256) qkv_prologue_kernel(const PrologueArgs a)
 #pragma unroll
   for (int t = 0; t < 3; ++t) {
     const bf16* src = a.x[t] + bi * a.bs[t] + tok * a.ld[t] + static_cast<int64_t>(h) * a.d;
-    float y[4][8];
+    float y[NCH][8];
     float ss = 0.f;
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
+    for (int c = 0; c < NCH; ++c) {
       const int col = (c * 32 + lane) * 8;
       if (col < a.d) {
         const uint4 u = *reinterpret_cast<const uint4*>(src + col);
@@ -1072,7 +1074,7 @@ __global__ void __launch_bounds__(256) qkv_prologue_kernel(const PrologueArgs a)
       inv_den = 1.f / bf16_round(bf16_round(sqrtf(ss)) + 1e-5f);
     }
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
+    for (int c = 0; c < NCH; ++c) {
       const int col = (c * 32 + lane) * 8;
       if (col < a.d) {
         uint4 u;
@@ -1134,6 +1136,7 @@ struct EpilogueArgs {
   int32_t b, s, n_h, d;
   float eps;
 };
+template <int NCH>
 __global__ void __launch_bounds__(256) out_epilogue_kernel(const EpilogueArgs a) {
   const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int64_t rows = static_cast<int64_t>(a.b) * a.s * a.n_h;
@@ -1143,10 +1146,10 @@ __global__ void __launch_bounds__(256) out_epilogue_kernel(const EpilogueArgs a)
   const int64_t bs_idx = row / a.n_h;  // batch * s + token
   const int tok = static_cast<int>(bs_idx % a.s), bi = static_cast<int>(bs_idx / a.s);
   const bf16* src = a.x + ((static_cast<int64_t>(bi) * a.n_h + h) * a.s + tok) * a.d;
-  float v[4][8];
+  float v[NCH][8];
   float ss = 0.f;
 #pragma unroll
-  for (int c = 0; c < 4; ++c) {
+  for (int c = 0; c < NCH; ++c) {
     const int col = (c * 32 + lane) * 8;
     if (col < a.d) {
       load8_bf16(src + col, v[c]);
@@ -1158,7 +1161,7 @@ __global__ void __launch_bounds__(256) out_epilogue_kernel(const EpilogueArgs a)
   const float rstd = 1.f / sqrtf(ss / static_cast<float>(a.d) + a.eps);
   const int64_t off = static_cast<int64_t>(h) * a.d;
 #pragma unroll
-  for (int c = 0; c < 4; ++c) {
+  for (int c = 0; c < NCH; ++c) {
     const int col = (c * 32 + lane) * 8;
     if (col >= a.d) continue;
     float y[8];
