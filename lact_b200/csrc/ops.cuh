@@ -1033,7 +1033,7 @@ struct PrologueArgs {
 // extra pass.  d <= 1024, a multiple of 8.
 // NCH = ceil(d / 256): 16-byte chunks per lane (the register footprint, hence the occupancy, follows the head size).
 template <int NCH>
-__global__ void __launch_bounds__(256) qkv_prologue_kernel(const PrologueArgs a) {
+__global__ void __launch_bounds__(256, NCH <= 2 ? 8 : 4) qkv_prologue_kernel(const PrologueArgs a) {
   const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int64_t rows = static_cast<int64_t>(a.b) * a.s * a.n_h;
   if (row >= rows) return;
@@ -1137,7 +1137,7 @@ struct EpilogueArgs {
   float eps;
 };
 template <int NCH>
-__global__ void __launch_bounds__(256) out_epilogue_kernel(const EpilogueArgs a) {
+__global__ void __launch_bounds__(256, NCH <= 2 ? 8 : 4) out_epilogue_kernel(const EpilogueArgs a) {
   const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int64_t rows = static_cast<int64_t>(a.b) * a.s * a.n_h;
   if (row >= rows) return;
