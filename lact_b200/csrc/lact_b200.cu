@@ -754,6 +754,23 @@ int plan_scan(const lact_scan_config& c, int32_t n_steps, const int32_t* kind, c
   return LACT_OK;
 }
 
+// add + renormalise of one or two weight arrays (a1.B = 0: one); rows of up to 1024 elements
+int launch_add_renorm(const RenormArgs& a0, const RenormArgs& a1, cudaStream_t stream) {
+  const int64_t rows = static_cast<int64_t>(a0.B) * a0.R + static_cast<int64_t>(a1.B) * a1.R;
+  const int nv = ceil_div(std::max(a0.C, a1.B > 0 ? a1.C : 0), 128);
+  if (rows < 1 || nv > 8) return LACT_ERR_SHAPE;
+  const dim3 grid(ceil_div(rows, 8)), block(256);
+  KernelScope scope(kClsRenorm, stream);
+  switch (nv) {
+    case 1: LACT_CUDA(launch_pdl(add_renorm_kernel<1>, grid, block, 0, stream, a0, a1)); break;
+    case 2: LACT_CUDA(launch_pdl(add_renorm_kernel<2>, grid, block, 0, stream, a0, a1)); break;
+    case 3: LACT_CUDA(launch_pdl(add_renorm_kernel<3>, grid, block, 0, stream, a0, a1)); break;
+    case 4: LACT_CUDA(launch_pdl(add_renorm_kernel<4>, grid, block, 0, stream, a0, a1)); break;
+    default: LACT_CUDA(launch_pdl(add_renorm_kernel<8>, grid, block, 0, stream, a0, a1)); break;
+  }
+  return LACT_OK;
+}
+
 int validate_scan_config(const lact_scan_config& c) {
   if (c.B < 1 || c.L < 1 || c.D < 16 || c.H < 16 || c.out_len < 0) return LACT_ERR_SHAPE;
   if ((c.D % 16) != 0 || (c.H % 16) != 0) return LACT_ERR_SHAPE;
@@ -925,11 +942,7 @@ int scan_fwd(const lact_scan_config& c, const lact_scan_io& io, int32_t n_steps,
       rn[0].x = xres[0];
       rn[1].x = xres[1];
     }
-    {
-      const int64_t rows = B * (2 * H + D);
-      KernelScope scope(kClsRenorm, stream);
-      LACT_CUDA(launch_pdl(add_renorm_kernel, dim3(ceil_div(rows, 8)), dim3(256), 0, stream, rn[0], rn[1]));
-    }
+    LACT_TRY(launch_add_renorm(rn[0], rn[1], stream));
   }
   // final state out
   if (io.w0_out) LACT_CUDA(cudaMemcpy2DAsync(io.w0_out, H * D * 4, p.W02c, 2 * H * D * 4, H * D * 4, B,
@@ -1576,11 +1589,7 @@ int lact_add_renorm(void* master, void* compute, void* shadow, const void* n0, c
   r.mode = mode; r.prenorm = prenorm; r.prenorm_bf16 = prenorm_bf16; r.quirk = quirk;
   RenormArgs none = r;
   none.B = 0;
-  const int64_t rows = B * R;
-  KernelScope scope(kClsRenorm, static_cast<cudaStream_t>(stream));
-  add_renorm_kernel<<<ceil_div(rows, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(r, none);
-  LACT_CUDA(cudaGetLastError());
-  return LACT_OK;
+  return launch_add_renorm(r, none, static_cast<cudaStream_t>(stream));
 }
 
 int lact_bmm_bf16(const void* a, int32_t a_mn_major, const void* b, int32_t b_mn_major, void* c, int32_t c_dtype,

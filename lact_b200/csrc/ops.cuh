@@ -704,23 +704,16 @@ __device__ __forceinline__ void renorm_row(const RenormArgs& a, int64_t row, int
   }
 }
 
-__device__ __forceinline__ void renorm_row_any(const RenormArgs& a, int64_t row, int lane) {
-  const int nv = (a.C + 127) / 128;
-  if (nv <= 1) renorm_row<1>(a, row, lane);
-  else if (nv <= 2) renorm_row<2>(a, row, lane);
-  else if (nv <= 3) renorm_row<3>(a, row, lane);
-  else if (nv <= 4) renorm_row<4>(a, row, lane);
-  else renorm_row<8>(a, row, lane);
-}
-
-// Both weight arrays in one launch; one warp per row.
-__global__ void __launch_bounds__(256) add_renorm_kernel(const RenormArgs a0, const RenormArgs a1) {
+// Both weight arrays in one launch; one warp per row; NV = float4 per lane (row length <= 128 * NV).  The register
+// footprint follows the row length, so short rows run at higher occupancy.
+template <int NV>
+__global__ void __launch_bounds__(256, NV <= 3 ? 6 : (NV <= 4 ? 4 : 2)) add_renorm_kernel(const RenormArgs a0, const RenormArgs a1) {
   griddep_launch_dependents();
   griddep_wait();
   const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int64_t rows0 = static_cast<int64_t>(a0.B) * a0.R, rows1 = static_cast<int64_t>(a1.B) * a1.R;
-  if (row < rows0) renorm_row_any(a0, row, threadIdx.x & 31);
-  else if (row < rows0 + rows1) renorm_row_any(a1, row - rows0, threadIdx.x & 31);
+  if (row < rows0) renorm_row<NV>(a0, row, threadIdx.x & 31);
+  else if (row < rows0 + rows1) renorm_row<NV>(a1, row - rows0, threadIdx.x & 31);
 }
 
 // ------------------------------------------------------------------------------------------
