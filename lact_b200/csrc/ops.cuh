@@ -785,7 +785,7 @@ __global__ void __launch_bounds__(256) swiglu_bwd_planes_kernel(const PlaneArgs 
 // (lact_llm/lact_model/lact_triton_kernels/lact_fw_grad.py:178-260): with A = d silu / dy0,
 //   g_y0 = g_hid*A*y2*l1 + g_dy0*A'*y2*dh*l0 + g_dy2*A*dh*l2,   g_y2 = g_hid*sw*l1 + g_dy0*A*dh*l0,
 //   g_dh = g_dy0*A*y2*l0 + g_dy2*sw*l2,   g_lr = row sums (deterministic: one warp per row).
-__global__ void __launch_bounds__(256) fw_grad_bwd_pointwise_kernel(const PlaneArgs a) {
+__global__ void __launch_bounds__(256, 4) fw_grad_bwd_pointwise_kernel(const PlaneArgs a) {
   const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= a.rows) return;
   const int lane = threadIdx.x & 31;
