@@ -3,17 +3,19 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
 
 One "step" = one forward of the causal fused post-norm TTT op
-(`postnorm_block_causal_lact_swiglu_fused_kernel_triton` signature) over one batch:
-batch 8 x 4 heads (B = 32 merged), 32768 tokens, head dim = fast-weight hidden = 384, chunk 2048,
-bf16 q/k/v/lr, fp32 fast weights, per-chunk momentum, 5-step Newton-Schulz, L2 renorm.
-Synthetic seeded inputs (no dataset exists for this op).  Multi-GPU is weak scaling: every rank
-runs the same per-GPU workload on its own data, no collective on the data path.
+(`postnorm_block_causal_lact_swiglu_fused_kernel_triton` signature) over ONE fixed problem:
+batch 8 x 4 heads (32 merged (batch x head) units), 32768 tokens, head dim = fast-weight hidden =
+384, chunk 2048, bf16 q/k/v/lr, fp32 fast weights, per-chunk momentum, 5-step Newton-Schulz, L2
+renorm.  Synthetic seeded inputs (no dataset exists for this op).  With N GPUs the 32 units are
+partitioned into contiguous blocks of 32 / N per rank (strong scaling, no collective on the data
+path); `replicas` additionally reports N independent copies of the whole problem (weak scaling).
 
 Prints ONE JSON line (rank 0).  `value` = tokens/s with inputs resident in HBM; `e2e` = the same
 through the public Python API with pinned host buffers (H2D of all inputs and D2H of the output
-inside the timed region); `roofline` = the dominant kernel class against the measured bf16 peak;
-`cpu_baseline` = the CPU oracle (a port of the reference arithmetic) on a bounded sample.
-`--impl reference` times that CPU port alone with all host threads.
+inside the timed region); `roofline` = the dominant kernel class against the measured bf16 peak,
+with per-class DRAM traffic from the ncu table in profiles/; `train` = forward + backward of the
+same workload; `cpu_baseline` = the CPU oracle (a port of the reference arithmetic) on a bounded
+sample.  `--impl reference` times that CPU port alone with all host threads.
 """
 from __future__ import annotations
 
@@ -33,10 +35,26 @@ import torch  # noqa: E402
 BF16 = torch.bfloat16
 CFG = dict(batch=8, heads=4, L=32768, D=384, H=384, chunk=2048, ns_steps=5)
 METRIC = "ttt_layer_fwd_tokens_per_s_760M_shape"
-# DRAM bytes (read + write) of ONE Newton-Schulz launch from an ncu capture of a 16-head case
-# (profiles/ns_fused_kernel_small_case.md: 14.3 MB + 8.5 MB); grows with the matrices per launch.
-NCU_DRAM_BYTES_NS_FUSED_16_HEADS = 22.7e6
-E2E_SLABS = 4  # the end-to-end arm streams the batch through the device in this many slabs
+TRAFFIC_TABLE = os.path.join(ROOT, "profiles", "dram_traffic_per_launch_small_case.md")
+MIN_TRAFFIC_BYTES_FWD = 3.29e9  # q, k, v, o in bf16 + lr, momentum + fast weights in and out, whole problem
+
+
+def dram_traffic_table():
+    """Per kernel class: (units in the capture, DRAM bytes read, DRAM bytes written) per launch, from the
+    ncu table committed under profiles/ (rows `| class | units | read | write |`)."""
+    table = {}
+    if not os.path.exists(TRAFFIC_TABLE):
+        return table
+    with open(TRAFFIC_TABLE) as fh:
+        for line in fh:
+            cells = [c.strip().strip("`") for c in line.strip().strip("|").split("|")]
+            if len(cells) < 4:
+                continue
+            try:
+                table[cells[0]] = (int(cells[1]), float(cells[2]), float(cells[3]))
+            except ValueError:
+                continue
+    return table
 
 
 # ------------------------------------------------------------------------------------------ helpers
@@ -137,26 +155,30 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def make_inputs(device, seed, pinned_host=False):
-    """Seeded synthetic inputs of the benchmark shape, generated on `device` in slabs."""
-    B, L, D, H = CFG["batch"] * CFG["heads"], CFG["L"], CFG["D"], CFG["H"]
-    g = torch.Generator(device=device).manual_seed(seed)
-    rn = lambda *s: torch.randn(*s, device=device, generator=g)
-    out = {}
-    for name in ("q", "k", "v"):
-        t = torch.empty(B, L, D, dtype=BF16, device=device)
-        for b in range(B):
+def make_inputs(device, seed, first_unit, n_units):
+    """Seeded synthetic inputs of units [first_unit, first_unit + n_units) of the benchmark problem, generated on
+    `device`.  Every (batch x head) unit has its own generator, so a unit's data does not depend on how the
+    problem is partitioned."""
+    L, D, H = CFG["L"], CFG["D"], CFG["H"]
+    out = {n: torch.empty(n_units, L, D, dtype=BF16, device=device) for n in ("q", "k", "v")}
+    out.update({n: torch.empty(n_units, H, D, device=device) for n in ("w0", "w2")})
+    out["w1"] = torch.empty(n_units, D, H, device=device)
+    out.update({n: torch.empty(n_units, L, 1, dtype=BF16, device=device) for n in ("lr0", "lr1", "lr2")})
+    out["momentum"] = torch.empty(n_units, L, 1, device=device)
+    for b in range(n_units):
+        g = torch.Generator(device=device).manual_seed(seed * 100003 + first_unit + b)
+        rn = lambda *s: torch.randn(*s, device=device, generator=g)
+        for name in ("q", "k", "v"):
             x = rn(L, D)
             if name != "v":
                 x = x / x.norm(dim=-1, keepdim=True)
-            t[b] = x.to(BF16)
-        out[name] = t
-    out["w0"] = rn(B, H, D) / D ** 0.5
-    out["w1"] = rn(B, D, H) / H ** 0.5
-    out["w2"] = rn(B, H, D) / D ** 0.5
-    for name in ("lr0", "lr1", "lr2"):
-        out[name] = torch.nn.functional.softplus(rn(B, L, 1) - 2.0).to(BF16)
-    out["momentum"] = torch.sigmoid(rn(B, L, 1))
+            out[name][b] = x.to(BF16)
+        out["w0"][b] = rn(H, D) / D ** 0.5
+        out["w1"][b] = rn(D, H) / H ** 0.5
+        out["w2"][b] = rn(H, D) / D ** 0.5
+        for name in ("lr0", "lr1", "lr2"):
+            out[name][b] = torch.nn.functional.softplus(rn(L, 1) - 2.0).to(BF16)
+        out["momentum"][b] = torch.sigmoid(rn(L, 1))
     return out
 
 
@@ -170,11 +192,12 @@ def run_step(lb, t):
 
 # ------------------------------------------------------------------------------------------ CPU arm
 def cpu_reference_sample(steps: int, warmup: int, threads: int):
-    """Times the CPU port of the reference's fused arithmetic (oracle) on a bounded sample:
-    one batch element (4 heads) x 8192 tokens (4 chunks) of the benchmark workload per step."""
+    """Times the CPU port of the reference's fused arithmetic (oracle) on a bounded sample: one batch element
+    (4 heads) x the full 32768 tokens (16 chunks, 15 updates) of the benchmark workload per step; the batch
+    elements are independent, so the whole problem costs 8 such samples."""
     from oracle import lact_oracle as orc
     torch.set_num_threads(threads)
-    Ls, heads = 8192, CFG["heads"]
+    Ls, heads = CFG["L"], CFG["heads"]
     i = orc.make_inputs(heads, Ls, CFG["D"], CFG["H"], seed=0, act_dtype=BF16, lr_dtype=BF16)
     fn = lambda: orc.block_causal_lact_swiglu_fused(i["w0"], i["w1"], i["w2"], i["q"], i["k"], i["v"], i["lr0"],
                                                     i["lr1"], i["lr2"], chunk_size=CFG["chunk"], use_muon=True,
@@ -185,7 +208,8 @@ def cpu_reference_sample(steps: int, warmup: int, threads: int):
     for _ in range(steps):
         fn()
     dt = (time.perf_counter() - t0) / steps
-    sample = f"1 batch element ({heads} heads) x {Ls} tokens ({Ls // CFG['chunk']} chunks) per step"
+    sample = (f"1 of {CFG['batch']} batch elements ({heads} heads) x {Ls} tokens ({Ls // CFG['chunk']} chunks) per step; "
+              "tokens/s of the sample = tokens/s of the whole problem (independent batch elements)")
     return Ls / dt, dt, sample
 
 
@@ -197,7 +221,7 @@ def reference_arm(args, rank):
     val, dt, sample = cpu_reference_sample(steps, warmup, threads)
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": "tokens/s", "n_gpus": args.gpus,
-        "steps": steps, "warmup": warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "steps": steps, "warmup": warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": workload_config(args.gpus),
         "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
@@ -210,13 +234,15 @@ def reference_arm(args, rank):
 
 
 def workload_config(n):
+    units = CFG["batch"] * CFG["heads"]
     return {"workload": "causal LaCT TTT layer forward, 760M-LLM shape: batch 8 x seq 32768, 4 heads of dim 384, "
                         "fast-weight hidden 384, chunk 2048, apply-then-update, momentum + Muon(5) + L2 renorm, "
                         "bf16 q/k/v/lr, fp32 fast weights",
             "signature": "postnorm_block_causal_lact_swiglu_fused_kernel_triton",
-            "batch_per_gpu": CFG["batch"], "global_batch": CFG["batch"] * n, "seq_len": CFG["L"],
-            "parallelism": f"(batch x head) partition, {n} rank(s), no collective",
-            "l2": "inputs (3.2 GB per step) exceed L2; no explicit flush"}
+            "global_batch": CFG["batch"], "seq_len": CFG["L"], "units": units,
+            "units_per_gpu": [(units + n - 1 - r) // n for r in range(n)] if n > 1 else units,
+            "parallelism": f"ONE problem, its {units} (batch x head) units partitioned over {n} rank(s), no collective",
+            "l2": "inputs (3.2 GB per step over all ranks; 0.4 GB per rank at 8 ranks) exceed L2; no explicit flush"}
 
 
 def other_config_timings(lb, dev, steps=5):
@@ -291,9 +317,9 @@ def other_config_timings(lb, dev, steps=5):
     return out
 
 
-def train_step_timing(lb, t, dev, B, L, D, H, C, tokens_per_step, world, barrier, peaks, steps=3):
-    """Forward + backward of the same workload (the training configuration): one step = forward,
-    then backward from dO ~ N(0,1) bf16 to q, k, v, lr0/1/2, momentum and the initial W0/W1/W2."""
+def train_step_timing(lb, t, dev, B, L, D, H, C, global_tokens, world, barrier, peaks, steps=3):
+    """Forward + backward of the same workload (the training configuration) on this rank's units: one step =
+    forward, then backward from dO ~ N(0,1) bf16 to q, k, v, lr0/1/2, momentum and the initial W0/W1/W2."""
     import torch.distributed as dist
     leaves = {n: t[n].detach().clone().requires_grad_(True) for n in ARG_ORDER + ("momentum",)}
     dO = torch.randn(B, L, D, device=dev, generator=torch.Generator(device=dev).manual_seed(99)).to(BF16)
@@ -323,11 +349,11 @@ def train_step_timing(lb, t, dev, B, L, D, H, C, tokens_per_step, world, barrier
     fwd = algorithmic_flops(B, L, D, H, C, CFG["ns_steps"])
     bwd = B * (12 * D * H * L + 24 * D * H * n_upd * C + 2 * n_upd * (ns(2 * H, D) + ns(D, H)))
     tf = (fwd + bwd) / (ms_step * 1e-3) / 1e12
-    return {"ms_per_step": ms_step, "tokens_per_s": world * tokens_per_step / (ms_step * 1e-3), "steps": steps,
+    return {"ms_per_step": ms_step, "tokens_per_s": global_tokens / (ms_step * 1e-3), "steps": steps,
             "algorithmic_flops_per_step_per_gpu": fwd + bwd, "tflops_per_gpu": tf,
             "frac_of_bf16_peak_burst": tf / peaks["bf16_burst"],
-            "note": "forward on the fused kernels; backward = per-chunk reverse sweep driven from the host "
-                    "(recomputes pre-activations and the Newton-Schulz iterates)"}
+            "note": "forward on the fused kernels with the per-update state kept; backward = per-chunk reverse "
+                    "sweep driven from the host (recomputes pre-activations and the Newton-Schulz iterates)"}
 
 
 # ------------------------------------------------------------------------------------------ main arm
@@ -380,12 +406,12 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-train", action="store_true", help="skip the forward + backward timing (\"train\")")
+    ap.add_argument("--no-replicas", action="store_true",
+                    help="N > 1: skip the weak-scaling run of N independent copies of the whole problem (\"replicas\")")
     ap.add_argument("--other-configs", action="store_true",
                     help="also time the other BASELINE configurations (bidirectional fp32, NVS block, AR video layer) "
                          "on one GPU; reported under \"other_configs\" (not the headline metric)")
-    ap.add_argument("--train", action="store_true",
-                    help="also time forward + backward through the recurrence (gradients to q, k, v, lr, momentum "
-                         "and the initial fast weights, upstream gradient ~ N(0,1) bf16); reported under \"train\"")
     ap.add_argument("--engine-probe", action="store_true",
                     help="micro-benchmark of the GEMM engine alone (time per output tile by tile width and "
                          "contraction length); prints its own JSON line and exits")
@@ -424,10 +450,15 @@ def main():
         dist.barrier()
     import lact_b200
     from lact_b200 import _lib as LL
+    from lact_b200 import parallel
 
-    B, L, D, H, C = CFG["batch"] * CFG["heads"], CFG["L"], CFG["D"], CFG["H"], CFG["chunk"]
-    tokens_per_step = CFG["batch"] * L
-    t = make_inputs(dev, seed=rank)
+    units, L, D, H, C = CFG["batch"] * CFG["heads"], CFG["L"], CFG["D"], CFG["H"], CFG["chunk"]
+    global_tokens = CFG["batch"] * L
+    first, last = parallel.partition(units, world, rank)
+    B = last - first  # (batch x head) units of this rank
+    if B < 1:
+        raise SystemExit("more ranks than (batch x head) units")
+    t = make_inputs(dev, 0, first, B)
 
     def barrier():
         torch.cuda.synchronize()
@@ -435,34 +466,39 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    def timed_steps(tensors, n_steps, n_warm):
+        """`n_steps` steps after `n_warm` untimed ones, bracketed by barrier + synchronize; max over ranks, ms."""
+        for _ in range(n_warm):
+            run_step(lact_b200, tensors)
+        lact_b200.synchronize_and_check()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0 = LL.launch_count()
+        e0.record()
+        for _ in range(n_steps):
+            run_step(lact_b200, tensors)
+        e1.record()
+        barrier()
+        n_launch = LL.launch_count() - l0
+        ms_ = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(ms_, op=dist.ReduceOp.MAX)
+        return float(ms_.item()), n_launch
+
     with ClockSampler(local_rank) as clocks:
         # nvidia-smi needs a moment to start streaming: it is started before the warm-up and its
         # samples from the warm-up onwards (GPU under the same load) are summarised
         time.sleep(0.6)
         clocks.mark_load_start()
-        for _ in range(warmup):
-            run_step(lact_b200, t)
-        lact_b200.synchronize_and_check()
-        barrier()
-        launches0 = LL.launch_count()
-        ev0.record()
-        for _ in range(steps):
-            run_step(lact_b200, t)
-        ev1.record()
-        barrier()
-        launches = LL.launch_count() - launches0
-        if ev0.elapsed_time(ev1) < 400.0:  # keep the GPU under the same load until a few samples exist
+        total_ms, launches = timed_steps(t, steps, warmup)
+        if total_ms < 400.0:  # keep the GPU under the same load until a few samples exist
             t_end = time.time() + 0.4
             while time.time() < t_end:
                 run_step(lact_b200, t)
             torch.cuda.synchronize()
     lact_b200.synchronize_and_check()
-    ms = torch.tensor([ev0.elapsed_time(ev1)], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    ms_per_step = float(ms.item()) / steps
-    value = world * tokens_per_step / (ms_per_step * 1e-3)
+    ms_per_step = total_ms / steps
+    value = global_tokens / (ms_per_step * 1e-3)
 
     # per-kernel-class durations (CUDA events around every launch, on the launching stream), second pass
     peaks = measured_peaks()
@@ -479,14 +515,28 @@ def main():
     achieved = class_flops(top, B, D, H, C, CFG["ns_steps"]) / (top_ms * 1e-3) / 1e12
     flops = algorithmic_flops(B, L, D, H, C, CFG["ns_steps"])
     step_tflops = flops / (ms_per_step * 1e-3) / 1e12
+    # DRAM traffic per launch from the committed ncu table (captured on a smaller case; every class's traffic
+    # grows in proportion to the units per launch), and the forward's total against its algorithmic minimum
+    table = dram_traffic_table()
+    traffic_of = lambda k: (table[k][1] + table[k][2]) * B / table[k][0] if k in table else None
+    classes = {}
+    fwd_traffic = 0.0
+    for k, v in sorted(prof.items()):
+        f = class_flops(k, B, D, H, C, CFG["ns_steps"])
+        classes[k] = {"ms_per_launch": v[0] / v[1], "launches_per_step": v[1] / prof_steps, "share": v[0] / total_prof,
+                      "tflops": f / (v[0] / v[1] * 1e-3) / 1e12 if f else None, "dram_bytes_per_launch": traffic_of(k)}
+        if traffic_of(k) is not None:
+            fwd_traffic += traffic_of(k) * v[1] / prof_steps
     roofline = {"bound": "tensor", "kernel": top, "achieved": achieved, "peak": peaks["bf16_sustained"],
                 "unit": "TFLOP/s", "frac": achieved / peaks["bf16_sustained"],
-                "traffic": NCU_DRAM_BYTES_NS_FUSED_16_HEADS * B / 16.0 if top == "ns_fused" else None,
-                "traffic_note": "DRAM read+write bytes per launch, ncu capture at 16 heads scaled by heads per launch",
+                "traffic": traffic_of(top),
+                "traffic_note": "DRAM read+write bytes per launch: ncu capture of a smaller case "
+                                "(profiles/dram_traffic_per_launch_small_case.md) scaled by the units per launch",
                 "peak_source": peaks["source"] + " (sustained cuBLAS bf16)",
                 "kernel_share_of_step": prof[top][0] / total_prof,
-                "classes": {k: {"ms_per_launch": v[0] / v[1], "launches_per_step": v[1] / prof_steps,
-                                "share": v[0] / total_prof} for k, v in sorted(prof.items())}}
+                "step_dram_bytes": fwd_traffic if fwd_traffic > 0 else None,
+                "step_dram_bytes_min": MIN_TRAFFIC_BYTES_FWD * B / units if not reduced else None,
+                "classes": classes}
 
     # end to end through the public API with pinned host buffers
     e2e = None
@@ -499,31 +549,47 @@ def main():
         n_e2e = max(2, min(steps, 4))
         # the public call, fed from pinned host memory in slabs of (batch x head) entries so that the
         # copies of one slab overlap the kernels of another (every entry is an independent recurrence)
-        n_slabs = E2E_SLABS if B % E2E_SLABS == 0 else 1
+        n_slabs = 4 if B % 4 == 0 and B >= 16 else (2 if B % 2 == 0 and B >= 8 else 1)
         pipe = HostPipeline(lambda **kw: run_step(lact_b200, kw), host, out_host, n_slabs=n_slabs, device=dev)
         e2e_step = pipe.run
 
         e2e_step()
         barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record()
         for _ in range(n_e2e):
             e2e_step()
         ev1.record()
         barrier()
         ems = torch.tensor([ev0.elapsed_time(ev1)], device=dev, dtype=torch.float64)
+        hb = torch.tensor([float(h2d), float(d2h)], device=dev, dtype=torch.float64)
         if world > 1:
             dist.all_reduce(ems, op=dist.ReduceOp.MAX)
-        e2e = {"value": world * tokens_per_step / (float(ems.item()) / n_e2e * 1e-3), "unit": "tokens/s",
-               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": n_e2e}
-        e2e["slabs"] = n_slabs
+            dist.all_reduce(hb, op=dist.ReduceOp.SUM)
+        e2e = {"value": global_tokens / (float(ems.item()) / n_e2e * 1e-3), "unit": "tokens/s",
+               "h2d_bytes_per_step": int(hb[0].item()), "d2h_bytes_per_step": int(hb[1].item()), "steps": n_e2e,
+               "slabs": n_slabs}
         del host, pipe, out_host
 
     others = None
     if args.other_configs and rank == 0:
         others = other_config_timings(lact_b200, dev)
     train = None
-    if args.train:
-        train = train_step_timing(lact_b200, t, dev, B, L, D, H, C, tokens_per_step, world, barrier, peaks)
+    if not args.no_train:
+        train = train_step_timing(lact_b200, t, dev, B, L, D, H, C, global_tokens, world, barrier, peaks)
+
+    # weak scaling for comparison: every rank runs the WHOLE problem on its own data
+    replicas = None
+    if world > 1 and not args.no_replicas and not reduced:
+        del t
+        torch.cuda.empty_cache()
+        t_full = make_inputs(dev, 1 + rank, 0, units)
+        rms, _ = timed_steps(t_full, max(2, min(steps, 5)), 2)
+        rms /= max(2, min(steps, 5))
+        replicas = {"value": world * global_tokens / (rms * 1e-3), "unit": "tokens/s", "ms_per_step": rms,
+                    "scaling": "weak", "units_per_gpu": units,
+                    "note": "N independent copies of the whole problem, one per GPU"}
+        del t_full
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -534,7 +600,7 @@ def main():
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": warmup,
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
             "step_tflops_per_gpu": step_tflops, "frac_of_bf16_peak_burst": step_tflops / peaks["bf16_burst"],
             "frac_of_bf16_peak_sustained": step_tflops / peaks["bf16_sustained"],
@@ -544,6 +610,8 @@ def main():
         }
         if train is not None:
             line["train"] = train
+        if replicas is not None:
+            line["replicas"] = replicas
         if others is not None:
             line["other_configs"] = others
         if reduced:

@@ -108,8 +108,21 @@ const char *lact_profile_class_name(int cls);
 int lact_profile_read(double *ms, int64_t *launches);
 
 /* Reads the device status word of a workspace after synchronising `stream`.
- * Returns 0 (ok), a positive device status (101 = a bounded wait timed out) or LACT_ERR_CUDA. */
+ * Returns 0 (ok), a positive device status (101 = a bounded wait timed out) or LACT_ERR_CUDA.
+ * This and lact_static_status are the only entry points that wait for a stream;
+ * lact_stream_sync_count returns how often the library has done so in this process.
+ * No counterpart in the reference. */
 int lact_read_status(const void *workspace, void *stream);
+int64_t lact_stream_sync_count(void);
+
+/* Every device-side wait of the kernels (mbarrier waits, completion-counter spins) gives up after
+ * this many nanoseconds of wall time and records status 101 instead of hanging (default 2 s;
+ * 0 restores the default).  Applies to kernels launched afterwards on the current device.
+ * lact_debug_wait_timeout launches one thread that waits on a barrier nobody arrives on, so the
+ * time-out path can be exercised without any fault: `status_word` (device memory, zero before
+ * the call) holds 101 once the kernel has run.  No counterpart in the reference. */
+int lact_set_wait_limit_ns(uint64_t limit_ns);
+int lact_debug_wait_timeout(int32_t *status_word, void *stream);
 
 /* Scratch bytes needed by lact_scan_fwd for this configuration and step list. */
 int lact_scan_workspace_bytes(const lact_scan_config *cfg, int32_t n_steps, const int32_t *kind,
@@ -150,6 +163,11 @@ int lact_swiglu_ffn_fwd(const void *w0w2, const void *w1, const void *x, void *o
  * B = 4, N = 2048, H = 384).  Larger problems return LACT_ERR_STATIC_LIMIT and enqueue nothing.
  * Every GPU that loads the library holds that array until the process exits.
  *
+ * The kernels' status word (see lact_read_status) sits at the head of that array, where the
+ * caller cannot point: lact_static_status(stream) synchronises `stream` and returns it (0, 101
+ * or LACT_ERR_CUDA), also without allocating.  Read it before the next static call on the
+ * device, which clears the word.
+ *
  * The first call on a device looks up the array's device address (once per device, with that
  * device current); make that first call before starting any stream capture.  The call itself
  * allocates and frees nothing, on the device or through any library.
@@ -160,6 +178,7 @@ int lact_swiglu_ffn_fwd(const void *w0w2, const void *w1, const void *x, void *o
 size_t lact_static_scratch_bytes(void);
 int lact_swiglu_ffn_fwd_static(const void *w0w2, const void *w1, const void *x, void *out, int64_t B, int64_t N,
                                int64_t D, int64_t H, void *stream);
+int lact_static_status(void *stream);
 
 /* dw0w2[B, 2H, D], dw1[B, D, H] (bf16) = per-token-lr weighted fast-weight gradient.
  * Replaces fused_lact_swiglu_ffn_fast_weight_grads

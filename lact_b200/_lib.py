@@ -41,6 +41,10 @@ def _declare(lib: C.CDLL) -> None:
     lib.lact_error_string.restype = C.c_char_p
     lib.lact_error_string.argtypes = [C.c_int]
     lib.lact_read_status.argtypes = [vp, vp]
+    lib.lact_stream_sync_count.restype = C.c_int64
+    lib.lact_set_wait_limit_ns.argtypes = [C.c_uint64]
+    lib.lact_debug_wait_timeout.argtypes = [vp, vp]
+    lib.lact_static_status.argtypes = [vp]
     lib.lact_launch_count.restype = C.c_int64
     lib.lact_profile_enable.argtypes = [C.c_int]
     lib.lact_profile_enable.restype = C.c_int
@@ -81,7 +85,8 @@ def _declare(lib: C.CDLL) -> None:
     lib.lact_sgemm_f32.argtypes = [vp, i32, vp, i32, vp, i32, vp, i64, i64, i64, i64, vp]
     lib.lact_swiglu_planes_f32.argtypes = [vp, vp, vp, vp, vp, i32, f32, vp, vp, i64, i64, vp]
     lib.lact_add_renorm.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, i32, i32, i32, i32, vp]
-    for name in ("lact_read_status", "lact_scan_workspace_bytes", "lact_scan_fwd", "lact_swiglu_ffn_workspace_bytes",
+    for name in ("lact_read_status", "lact_set_wait_limit_ns", "lact_debug_wait_timeout", "lact_static_status",
+                 "lact_scan_workspace_bytes", "lact_scan_fwd", "lact_swiglu_ffn_workspace_bytes",
                  "lact_swiglu_ffn_fwd", "lact_fw_grad_workspace_bytes", "lact_fw_grad",
                  "lact_newton_schulz_workspace_bytes", "lact_newton_schulz", "lact_l2_norm_add",
                  "lact_prenorm_momentum_l2norm", "lact_bmm_bf16", "lact_bmm2_bf16", "lact_bmm2_strided_bf16", "lact_swiglu_bwd_planes",
@@ -131,16 +136,16 @@ def stream_ptr() -> int:
 # One growing scratch buffer per (device, stream), taken from PyTorch's caching allocator.  Kernels
 # of consecutive calls on one stream are ordered, so reuse is safe.
 _workspaces: Dict[tuple, torch.Tensor] = {}
-_pending: Dict[tuple, bool] = {}
 SYNC_CHECK = os.environ.get("LACT_B200_SYNC_CHECK", "0") == "1"
 
 
+def _key(device: torch.device) -> tuple:
+    return (device.index if device.index is not None else torch.cuda.current_device(), stream_ptr())
+
+
 def workspace(nbytes: int, device: torch.device) -> torch.Tensor:
-    key = (device.index if device.index is not None else torch.cuda.current_device(), stream_ptr())
-    if _pending.get(key):
-        # the previous call on this stream left a status word behind: read it before reuse
-        read_status(_workspaces[key])
-        _pending[key] = False
+    """Scratch for one call on the current stream.  Never waits for the device."""
+    key = _key(device)
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes:
         buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
@@ -148,28 +153,99 @@ def workspace(nbytes: int, device: torch.device) -> torch.Tensor:
     return buf
 
 
+class _StatusRing:
+    """Device status words of finished calls, copied to pinned host memory WITHOUT waiting.
+
+    Every call's kernels leave a status word at the head of its workspace (0 = ok, 101 = a bounded
+    wait ran out).  The next call on the stream clears that word, so right after a call has been
+    enqueued an asynchronous 4-byte copy into the next slot of a pinned ring is enqueued behind
+    it.  The host looks at slots whose copy has completed (an event query, no wait) whenever a
+    later call is made, and at all of them in `synchronize_and_check`.  A slot is waited for only
+    when the ring wraps around while its copy is still in flight (256 calls ahead of the device).
+    """
+    SLOTS = 256
+
+    def __init__(self):
+        self.host = torch.zeros(self.SLOTS, dtype=torch.int32).pin_memory()
+        self.events = [None] * self.SLOTS
+        self.head = 0  # next slot to use
+        self.tail = 0  # oldest slot not yet examined
+
+    def _examine(self, slot: int) -> None:
+        self.events[slot] = None
+        st = int(self.host[slot])
+        if st != 0:
+            self.host[slot] = 0
+            raise LactError("device status: " + lib().lact_error_string(st).decode() + f" (code {st})")
+
+    def poll(self, wait: bool = False) -> None:
+        """Examines finished slots in order; with `wait`, all of them."""
+        while self.tail != self.head:
+            slot = self.tail % self.SLOTS
+            ev = self.events[slot]
+            if ev is not None:
+                if wait:
+                    ev.synchronize()
+                elif not ev.query():
+                    return
+            self.tail += 1
+            self._examine(slot)
+
+    def post(self, ws: torch.Tensor) -> None:
+        if self.head - self.tail >= self.SLOTS:  # the ring is full: the oldest copy must have landed
+            slot = self.tail % self.SLOTS
+            if self.events[slot] is not None:
+                self.events[slot].synchronize()
+            self.tail += 1
+            self._examine(slot)
+        slot = self.head % self.SLOTS
+        self.host[slot:slot + 1].copy_(ws[:4].view(torch.int32), non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.events[slot] = ev
+        self.head += 1
+
+
+_rings: Dict[int, _StatusRing] = {}
+
+
 def mark_pending(ws: torch.Tensor) -> None:
-    """Remembers that `ws` holds a device status word to be examined (lazily, or now if
-    LACT_B200_SYNC_CHECK=1)."""
+    """Called after a library call has been enqueued with `ws` as its workspace: arranges for the
+    call's device status word to reach the host without blocking (see `_StatusRing`), and raises
+    for any EARLIER call whose word has arrived non-zero.  Inside CUDA-graph stream capture
+    nothing is recorded.  LACT_B200_SYNC_CHECK=1 checks synchronously instead (debugging)."""
+    if torch.cuda.is_current_stream_capturing():
+        return
     if SYNC_CHECK:
         read_status(ws)
         return
-    key = (ws.device.index, stream_ptr())
-    _pending[key] = True
+    idx = ws.device.index
+    ring = _rings.get(idx)
+    if ring is None:
+        ring = _rings[idx] = _StatusRing()
+    with torch.cuda.device(ws.device):
+        ring.post(ws)
+        ring.poll()
 
 
 def read_status(ws: torch.Tensor) -> None:
+    """Synchronises the current stream and raises if the workspace's status word is non-zero."""
     rc = lib().lact_read_status(ws.data_ptr(), stream_ptr())
     if rc != 0:
         raise LactError("device status: " + lib().lact_error_string(rc).decode() + f" (code {rc})")
 
 
 def synchronize_and_check() -> None:
-    """Synchronises and raises if any earlier call recorded a device-side error."""
-    for key, buf in list(_workspaces.items()):
-        if _pending.get(key):
-            read_status(buf)
-            _pending[key] = False
+    """Waits for every status word posted so far and raises if any call recorded a device-side
+    error (a bounded wait that ran out).  The op calls themselves never wait."""
+    for idx, ring in list(_rings.items()):
+        with torch.cuda.device(idx):
+            ring.poll(wait=True)
+
+
+def stream_sync_count() -> int:
+    """cudaStreamSynchronize calls made inside the library in this process so far."""
+    return int(lib().lact_stream_sync_count())
 
 
 def launch_count() -> int:

@@ -25,19 +25,30 @@ from . import _lib as L
 from . import program as P
 
 BF16 = torch.bfloat16
-_status: Dict[int, torch.Tensor] = {}
+_status: Dict[tuple, torch.Tensor] = {}
 
 
 def _status_word(dev: torch.device) -> torch.Tensor:
-    idx = dev.index if dev.index is not None else torch.cuda.current_device()
-    if idx not in _status:
-        _status[idx] = torch.zeros(64, dtype=torch.int32, device=dev)
-    return _status[idx]
+    """Device status word of the backward kernels, one per (device, stream)."""
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(), L.stream_ptr())
+    if key not in _status:
+        _status[key] = torch.zeros(64, dtype=torch.int32, device=dev)
+    return _status[key]
+
+
+def reset_status(dev: torch.device) -> None:
+    """Clears the word (stream-ordered): kernels return early while it is non-zero, so a sweep must
+    not inherit the failure of an earlier one."""
+    _status_word(dev).zero_()
 
 
 def check_status(dev: torch.device) -> None:
-    st = int(_status_word(dev)[0].item())
+    """Raises if a bounded wait ran out during the sweep; the word is cleared first, so the next
+    backward call starts clean."""
+    word = _status_word(dev)
+    st = int(word[0].item())
     if st != 0:
+        word.zero_()
         raise L.LactError(f"device status {st} during backward")
 
 
@@ -202,178 +213,188 @@ def scan_forward_saving(opts, steps, w0, w1, w2, q, k, v, lr0, lr1, lr2, momentu
     return o, wf0, wf1, wf2, dump
 
 
-def scan_backward(opts, steps, w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, dump, wf0, wf1, wf2, dO):
-    """Reverse sweep over the step program.  `momentum` may be None.  Returns the gradients of
+def scan_backward(opts, steps, w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, dump, wf0, wf1, wf2, dO, gwf=None):
+    """Reverse sweep over the step program.  `momentum` may be None.  `gwf` = optional cotangents
+    (g_w0, g_w1, g_w2; any may be None) of the final fast weights the forward returned: they seed
+    the weight gradient the sweep starts from (in the reference the returned weights carry autograd
+    history, e.g. lact_nvs/lact_ttt.py:147).  Returns the gradients of
     (w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum) (the last one None without momentum)."""
     has_momentum = momentum is not None
     n_upd = sum(1 for s_ in steps if s_[0] == P.UPDATE)
-    if True:
-        dev = q.device
-        B, Ltok, D = k.shape
-        H = w0.shape[1]
-        n02, n1 = B * 2 * H * D, B * D * H
-        mode = int(opts.get("renorm", L.RENORM_EPS_OUTSIDE))
-        w_scale = float(opts.get("w_scale", 1.0))
-        f32 = torch.float32
-        vec = lambda t: (t[..., 0] if t.dim() == 3 else t).contiguous()
-        lr0v, lr1v, lr2v = vec(lr0), vec(lr1), vec(lr2)
-        momv = vec(momentum).float() if has_momentum else None
-        W0_02 = torch.cat([w0, w2], dim=1).float().contiguous()
-        W0_1 = w1.float().contiguous()
-        n0_02 = W0_02.norm(dim=2).contiguous()
-        n0_1 = W0_1.norm(dim=2).contiguous()
+    reset_status(q.device)
+    dev = q.device
+    B, Ltok, D = k.shape
+    H = w0.shape[1]
+    n02, n1 = B * 2 * H * D, B * D * H
+    mode = int(opts.get("renorm", L.RENORM_EPS_OUTSIDE))
+    w_scale = float(opts.get("w_scale", 1.0))
+    f32 = torch.float32
+    vec = lambda t: (t[..., 0] if t.dim() == 3 else t).contiguous()
+    lr0v, lr1v, lr2v = vec(lr0), vec(lr1), vec(lr2)
+    momv = vec(momentum).float() if has_momentum else None
+    W0_02 = torch.cat([w0, w2], dim=1).float().contiguous()
+    W0_1 = w1.float().contiguous()
+    n0_02 = W0_02.norm(dim=2).contiguous()
+    n0_1 = W0_1.norm(dim=2).contiguous()
 
-        def weights(cnt):
-            """fp32 (W02, W1) in force after `cnt` updates."""
-            if cnt == 0:
-                return W0_02, W0_1
-            if cnt < n_upd:
-                return dump[cnt, :n02].view(B, 2 * H, D), dump[cnt, n02:n02 + n1].view(B, D, H)
-            return torch.cat([wf0, wf2], dim=1).contiguous(), wf1.contiguous()
+    def weights(cnt):
+        """fp32 (W02, W1) in force after `cnt` updates."""
+        if cnt == 0:
+            return W0_02, W0_1
+        if cnt < n_upd:
+            return dump[cnt, :n02].view(B, 2 * H, D), dump[cnt, n02:n02 + n1].view(B, D, H)
+        return torch.cat([wf0, wf2], dim=1).contiguous(), wf1.contiguous()
 
-        def grad_state(u):
-            """fp32 gradient after momentum of update u (= momentum state after it)."""
-            base = n02 + n1
-            return dump[u, base:base + n02].view(B, 2 * H, D), dump[u, base + n02:base + n02 + n1].view(B, D, H)
+    def grad_state(u):
+        """fp32 gradient after momentum of update u (= momentum state after it)."""
+        base = n02 + n1
+        return dump[u, base:base + n02].view(B, 2 * H, D), dump[u, base + n02:base + n02 + n1].view(B, D, H)
 
-        prenorm, muon = bool(opts.get("prenorm")), bool(opts.get("use_muon"))
-        overwrite = bool(opts.get("overwrite_quirk")) and muon
-        nst, cc, gr = int(opts.get("ns_steps", 5)), bool(opts.get("ns_const_coeffs")), bool(opts.get("ns_gram_right"))
+    prenorm, muon = bool(opts.get("prenorm")), bool(opts.get("use_muon"))
+    overwrite = bool(opts.get("overwrite_quirk")) and muon
+    nst, cc, gr = int(opts.get("ns_steps", 5)), bool(opts.get("ns_const_coeffs")), bool(opts.get("ns_gram_right"))
 
-        # pre-norm: master weights before each update, Wm_0 = W_0, Wm_{u+1} = Wm_u + U_u
-        masters = None
-        if prenorm:
-            from . import ops
+    # pre-norm: master weights before each update, Wm_0 = W_0, Wm_{u+1} = Wm_u + U_u
+    masters = None
+    if prenorm:
+        from . import ops
 
-            def fast_ns(g):
-                st = nst if cc else None
-                if gr:
-                    return ops.zeropower_via_newtonschulz5(g.transpose(1, 2).contiguous(), st).transpose(1, 2)
-                return ops.zeropower_via_newtonschulz5(g, st)
+        def fast_ns(g):
+            st = nst if cc else None
+            if gr:
+                return ops.zeropower_via_newtonschulz5(g.transpose(1, 2).contiguous(), st).transpose(1, 2)
+            return ops.zeropower_via_newtonschulz5(g, st)
 
-            masters = [(W0_02, W0_1)]
-            for u in range(n_upd - 1):
-                g02, g1 = grad_state(u)
-                if muon:
-                    g02 = fast_ns(g02) if opts.get("ns_concat") else torch.cat(
-                        [fast_ns(g02[:, :H]), fast_ns(g02[:, H:])], dim=1)
-                    g1 = fast_ns(g1)
-                masters.append((masters[-1][0] + g02.float(), masters[-1][1] + g1.float()))
-
-        dW02 = torch.zeros(B, 2 * H, D, dtype=f32, device=dev)
-        dW1 = torch.zeros(B, D, H, dtype=f32, device=dev)
-        dWm02 = dWm1 = None  # pre-norm: gradient w.r.t. the master weights after the current update
-        dM02 = dM1 = None
-        dn02 = torch.zeros(B, 2 * H, dtype=f32, device=dev)
-        dn1 = torch.zeros(B, D, dtype=f32, device=dev)
-        dq = torch.zeros_like(q, dtype=BF16)
-        dk = torch.zeros_like(k, dtype=BF16)
-        dv = torch.zeros_like(v, dtype=BF16)
-        dlr = [torch.zeros(B, Ltok, dtype=f32, device=dev) for _ in range(3)]
-        dmom = torch.zeros(B, Ltok, dtype=f32, device=dev) if has_momentum else None
-        dO = dO.to(BF16)
-
-        cnt = n_upd
-        shadows = {}
-        q_done, kv_done = [], []  # token ranges whose dq / dk, dv have been written
-
-        def fresh(done, s_, e_):
-            """True (and records the range) if no earlier step wrote a gradient for tokens [s_, e_)."""
-            ok = all(e_ <= a_ or s_ >= b_ for a_, b_ in done)
-            done.append((s_, e_))
-            return ok
-
-        def shadow(c_):
-            if c_ not in shadows:
-                shadows.clear()
-                a, b = weights(c_)
-                shadows[c_] = (a.to(BF16).contiguous(), b.to(BF16).contiguous())
-            return shadows[c_]
-
-        for kind, s, e, o_s in reversed(steps):
-            if e <= s:
-                continue
-            if kind == P.APPLY:
-                w02b, w1b = shadow(cnt)
-                if fresh(q_done, s, e):   # first gradient for these tokens: the product writes it in place
-                    apply_backward(w02b, w1b, q[:, s:e], dO[:, o_s:o_s + (e - s)], dW02, dW1, dq_out=dq[:, s:e])
-                else:
-                    dq[:, s:e] += apply_backward(w02b, w1b, q[:, s:e], dO[:, o_s:o_s + (e - s)], dW02, dW1)
-                continue
-            u = cnt - 1
-            Wp02, Wp1 = weights(u)
-            G02, G1 = grad_state(u)
-            # update applied to the weights: the gradient itself, or its Newton-Schulz image (recomputed)
-            U02, U1, sv02, sv1 = G02.contiguous(), G1.contiguous(), None, None
+        masters = [(W0_02, W0_1)]
+        for u in range(n_upd - 1):
+            g02, g1 = grad_state(u)
             if muon:
-                g02m = G02.contiguous() if opts.get("ns_concat") else G02.contiguous().view(2 * B, H, D)
-                sv02, U02 = ns_forward_saved(g02m, nst, cc, gr)
-                sv1, U1 = ns_forward_saved(G1.contiguous(), nst, cc, gr)
-                U02 = U02.view(B, 2 * H, D)
-            # renorm backward: dWn is the gradient w.r.t. (base + update); base is W_u, the master
-            # copy (pre-norm), or the gradient itself (bidirectional overwrite)
-            if prenorm:
-                b02, b1 = masters[u]
-            elif overwrite:
-                b02, b1 = G02, G1
+                g02 = fast_ns(g02) if opts.get("ns_concat") else torch.cat(
+                    [fast_ns(g02[:, :H]), fast_ns(g02[:, H:])], dim=1)
+                g1 = fast_ns(g1)
+            masters.append((masters[-1][0] + g02.float(), masters[-1][1] + g1.float()))
+
+    dW02 = torch.zeros(B, 2 * H, D, dtype=f32, device=dev)
+    dW1 = torch.zeros(B, D, H, dtype=f32, device=dev)
+    if gwf is not None:  # cotangents of the returned final weights (the compute copy after the last update)
+        if gwf[0] is not None:
+            dW02[:, :H] = gwf[0]
+        if gwf[2] is not None:
+            dW02[:, H:] = gwf[2]
+        if gwf[1] is not None:
+            dW1.copy_(gwf[1])
+    dWm02 = dWm1 = None  # pre-norm: gradient w.r.t. the master weights after the current update
+    dM02 = dM1 = None
+    dn02 = torch.zeros(B, 2 * H, dtype=f32, device=dev)
+    dn1 = torch.zeros(B, D, dtype=f32, device=dev)
+    dq = torch.zeros_like(q, dtype=BF16)
+    dk = torch.zeros_like(k, dtype=BF16)
+    dv = torch.zeros_like(v, dtype=BF16)
+    dlr = [torch.zeros(B, Ltok, dtype=f32, device=dev) for _ in range(3)]
+    dmom = torch.zeros(B, Ltok, dtype=f32, device=dev) if has_momentum else None
+    dO = dO.to(BF16)
+
+    cnt = n_upd
+    shadows = {}
+    q_done, kv_done = [], []  # token ranges whose dq / dk, dv have been written
+
+    def fresh(done, s_, e_):
+        """True (and records the range) if no earlier step wrote a gradient for tokens [s_, e_)."""
+        ok = all(e_ <= a_ or s_ >= b_ for a_, b_ in done)
+        done.append((s_, e_))
+        return ok
+
+    def shadow(c_):
+        if c_ not in shadows:
+            shadows.clear()
+            a, b = weights(c_)
+            shadows[c_] = (a.to(BF16).contiguous(), b.to(BF16).contiguous())
+        return shadows[c_]
+
+    for kind, s, e, o_s in reversed(steps):
+        if e <= s:
+            continue
+        if kind == P.APPLY:
+            w02b, w1b = shadow(cnt)
+            if fresh(q_done, s, e):   # first gradient for these tokens: the product writes it in place
+                apply_backward(w02b, w1b, q[:, s:e], dO[:, o_s:o_s + (e - s)], dW02, dW1, dq_out=dq[:, s:e])
             else:
-                b02, b1 = Wp02, Wp1
-            dWn02 = renorm_backward(b02.contiguous(), U02, n0_02, dW02, dn02, mode)
-            dWn1 = renorm_backward(b1.contiguous(), U1, n0_1, dW1, dn1, mode)
-            if prenorm and dWm02 is not None:
-                dWn02 += dWm02
-                dWn1 += dWm1
-            if sv02 is not None:
-                dG02 = ns_backward(sv02, dWn02.view(sv02["Gb"].shape)).view(B, 2 * H, D)
-                dG1 = ns_backward(sv1, dWn1)
-                if overwrite:
-                    dG02 = dG02 + dWn02
-                    dG1 = dG1 + dWn1
-            else:
-                dG02, dG1 = dWn02.clone(), dWn1.clone()
-            if dM02 is not None:
-                dG02 += dM02
-                dG1 += dM1
-            if prenorm:        # the weights update u computed with receive gradient only from its own steps
-                dWm02, dWm1 = dWn02, dWn1
-                dW02, dW1 = torch.zeros_like(dWn02), torch.zeros_like(dWn1)
-            elif overwrite:    # the previous weights were overwritten: no direct path
-                dW02, dW1 = torch.zeros_like(dWn02), torch.zeros_like(dWn1)
-            else:
-                dW02, dW1 = dWn02, dWn1
-            if has_momentum:
-                beta = momv[:, s:e].mean(dim=1)  # [B]
-                if u > 0:
-                    Mp02, Mp1 = grad_state(u - 1)
-                    dbeta = (dG02 * Mp02).sum(dim=(1, 2)) + (dG1 * Mp1).sum(dim=(1, 2))
-                    dmom[:, s:e] += (dbeta / float(e - s)).unsqueeze(1)
-                dM02, dM1 = dG02 * beta.view(B, 1, 1), dG1 * beta.view(B, 1, 1)
-            w02b, w1b = shadow(u)
-            if fresh(kv_done, s, e):
-                _, _, g0, g1, g2 = fw_grad_backward(w02b, w1b, k[:, s:e], v[:, s:e], lr0v[:, s:e], lr1v[:, s:e],
-                                                    lr2v[:, s:e], w_scale, dG02, dG1, dW02, dW1, dk_out=dk[:, s:e],
-                                                    dv_out=dv[:, s:e])
-            else:
-                gk, gv, g0, g1, g2 = fw_grad_backward(w02b, w1b, k[:, s:e], v[:, s:e], lr0v[:, s:e], lr1v[:, s:e],
-                                                      lr2v[:, s:e], w_scale, dG02, dG1, dW02, dW1)
-                dk[:, s:e] += gk
-                dv[:, s:e] += gv
-            dlr[0][:, s:e] += g0
-            dlr[1][:, s:e] += g1
-            dlr[2][:, s:e] += g2
-            cnt = u
-        check_status(dev)
-        if dWm02 is not None:  # W_0 is both the first master and the first compute copy
-            dW02, dW1 = dW02 + dWm02, dW1 + dWm1
-        # the target row norms are functions of the initial weights (not detached in the LLM / AR paths)
-        if not opts.get("_detach_norms", False):
-            dW02 = dW02 + dn02.unsqueeze(-1) * W0_02 / n0_02.clamp_min(1e-30).unsqueeze(-1)
-            dW1 = dW1 + dn1.unsqueeze(-1) * W0_1 / n0_1.clamp_min(1e-30).unsqueeze(-1)
-        dw0, dw2 = dW02[:, :H].to(w0.dtype), dW02[:, H:].to(w2.dtype)
-        shape = lambda g, ref: g.view(ref.shape).to(ref.dtype) if ref.dim() == 3 else g.to(ref.dtype)
-        grads = (dw0, dW1.to(w1.dtype), dw2, dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype),
-                 shape(dlr[0].unsqueeze(-1) if lr0.dim() == 3 else dlr[0], lr0),
-                 shape(dlr[1].unsqueeze(-1) if lr1.dim() == 3 else dlr[1], lr1),
-                 shape(dlr[2].unsqueeze(-1) if lr2.dim() == 3 else dlr[2], lr2),
-                 shape(dmom.unsqueeze(-1) if momentum.dim() == 3 else dmom, momentum) if has_momentum else None)
-        return grads
+                dq[:, s:e] += apply_backward(w02b, w1b, q[:, s:e], dO[:, o_s:o_s + (e - s)], dW02, dW1)
+            continue
+        u = cnt - 1
+        Wp02, Wp1 = weights(u)
+        G02, G1 = grad_state(u)
+        # update applied to the weights: the gradient itself, or its Newton-Schulz image (recomputed)
+        U02, U1, sv02, sv1 = G02.contiguous(), G1.contiguous(), None, None
+        if muon:
+            g02m = G02.contiguous() if opts.get("ns_concat") else G02.contiguous().view(2 * B, H, D)
+            sv02, U02 = ns_forward_saved(g02m, nst, cc, gr)
+            sv1, U1 = ns_forward_saved(G1.contiguous(), nst, cc, gr)
+            U02 = U02.view(B, 2 * H, D)
+        # renorm backward: dWn is the gradient w.r.t. (base + update); base is W_u, the master
+        # copy (pre-norm), or the gradient itself (bidirectional overwrite)
+        if prenorm:
+            b02, b1 = masters[u]
+        elif overwrite:
+            b02, b1 = G02, G1
+        else:
+            b02, b1 = Wp02, Wp1
+        dWn02 = renorm_backward(b02.contiguous(), U02, n0_02, dW02, dn02, mode)
+        dWn1 = renorm_backward(b1.contiguous(), U1, n0_1, dW1, dn1, mode)
+        if prenorm and dWm02 is not None:
+            dWn02 += dWm02
+            dWn1 += dWm1
+        if sv02 is not None:
+            dG02 = ns_backward(sv02, dWn02.view(sv02["Gb"].shape)).view(B, 2 * H, D)
+            dG1 = ns_backward(sv1, dWn1)
+            if overwrite:
+                dG02 = dG02 + dWn02
+                dG1 = dG1 + dWn1
+        else:
+            dG02, dG1 = dWn02.clone(), dWn1.clone()
+        if dM02 is not None:
+            dG02 += dM02
+            dG1 += dM1
+        if prenorm:        # the weights update u computed with receive gradient only from its own steps
+            dWm02, dWm1 = dWn02, dWn1
+            dW02, dW1 = torch.zeros_like(dWn02), torch.zeros_like(dWn1)
+        elif overwrite:    # the previous weights were overwritten: no direct path
+            dW02, dW1 = torch.zeros_like(dWn02), torch.zeros_like(dWn1)
+        else:
+            dW02, dW1 = dWn02, dWn1
+        if has_momentum:
+            beta = momv[:, s:e].mean(dim=1)  # [B]
+            if u > 0:
+                Mp02, Mp1 = grad_state(u - 1)
+                dbeta = (dG02 * Mp02).sum(dim=(1, 2)) + (dG1 * Mp1).sum(dim=(1, 2))
+                dmom[:, s:e] += (dbeta / float(e - s)).unsqueeze(1)
+            dM02, dM1 = dG02 * beta.view(B, 1, 1), dG1 * beta.view(B, 1, 1)
+        w02b, w1b = shadow(u)
+        if fresh(kv_done, s, e):
+            _, _, g0, g1, g2 = fw_grad_backward(w02b, w1b, k[:, s:e], v[:, s:e], lr0v[:, s:e], lr1v[:, s:e],
+                                                lr2v[:, s:e], w_scale, dG02, dG1, dW02, dW1, dk_out=dk[:, s:e],
+                                                dv_out=dv[:, s:e])
+        else:
+            gk, gv, g0, g1, g2 = fw_grad_backward(w02b, w1b, k[:, s:e], v[:, s:e], lr0v[:, s:e], lr1v[:, s:e],
+                                                  lr2v[:, s:e], w_scale, dG02, dG1, dW02, dW1)
+            dk[:, s:e] += gk
+            dv[:, s:e] += gv
+        dlr[0][:, s:e] += g0
+        dlr[1][:, s:e] += g1
+        dlr[2][:, s:e] += g2
+        cnt = u
+    check_status(dev)
+    if dWm02 is not None:  # W_0 is both the first master and the first compute copy
+        dW02, dW1 = dW02 + dWm02, dW1 + dWm1
+    # the target row norms are functions of the initial weights (not detached in the LLM / AR paths)
+    if not opts.get("_detach_norms", False):
+        dW02 = dW02 + dn02.unsqueeze(-1) * W0_02 / n0_02.clamp_min(1e-30).unsqueeze(-1)
+        dW1 = dW1 + dn1.unsqueeze(-1) * W0_1 / n0_1.clamp_min(1e-30).unsqueeze(-1)
+    dw0, dw2 = dW02[:, :H].to(w0.dtype), dW02[:, H:].to(w2.dtype)
+    shape = lambda g, ref: g.view(ref.shape).to(ref.dtype) if ref.dim() == 3 else g.to(ref.dtype)
+    grads = (dw0, dW1.to(w1.dtype), dw2, dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype),
+             shape(dlr[0].unsqueeze(-1) if lr0.dim() == 3 else dlr[0], lr0),
+             shape(dlr[1].unsqueeze(-1) if lr1.dim() == 3 else dlr[1], lr1),
+             shape(dlr[2].unsqueeze(-1) if lr2.dim() == 3 else dlr[2], lr2),
+             shape(dmom.unsqueeze(-1) if momentum.dim() == 3 else dmom, momentum) if has_momentum else None)
+    return grads

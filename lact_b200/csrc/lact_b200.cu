@@ -141,6 +141,7 @@ struct Profiler {
   }
 };
 Profiler g_prof;
+std::atomic<int64_t> g_stream_syncs{0};  // cudaStreamSynchronize calls made by the library
 
 // Counts one kernel launch; when timing is enabled, brackets it with two events on its stream.
 struct KernelScope {
@@ -203,15 +204,11 @@ cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
   cfg.blockDim = block;
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  // Off by default: measured 2 % slower on the benchmark workload (the early-launched CTAs of the next
-  // kernel compete with the running one); LACT_B200_PDL=1 turns the overlap on.
-  static const bool pdl = [] {
-    const char* env = std::getenv("LACT_B200_PDL");
-    return env != nullptr && env[0] == '1';
-  }();
+  // The overlap is left off: measured 2 % slower on the 32-head workload (the early-launched CTAs of the
+  // next kernel compete with the running one).
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
+  attr[0].val.programmaticStreamSerializationAllowed = 0;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
@@ -598,7 +595,7 @@ int run_ns_iterations(const NsGroup* grp, int ngroups, int steps, int const_coef
 // just before: it leaves the first iterates in grp[g].xa and clears the completion counters grp[g].done.
 template <int BT_MM, int BT_MN>
 int launch_ns_fused(const NsGroup* grp, int ngroups, int steps, int const_coeffs, int32_t* status,
-                    cudaStream_t stream, uint64_t* trace, int unscaled_first) {
+                    cudaStream_t stream, int unscaled_first) {
   using Args = NsFusedArgs<BT_MM, BT_MN>;
   auto kernel = ns_fused_kernel<BT_MM, BT_MN>;
   constexpr uint32_t smem = ns_fused_smem_bytes<BT_MM, BT_MN>();
@@ -636,7 +633,6 @@ int launch_ns_fused(const NsGroup* grp, int ngroups, int steps, int const_coeffs
   args.steps = steps;
   args.ngroups = ngroups;
   args.status = status;
-  args.trace = trace;
   for (int g = 0; g < ngroups; ++g) args.done[g] = grp[g].done;  // cleared by launch_ns_prepare
   const int grid = static_cast<int>(std::min<int64_t>(sm_count(), std::max<int64_t>(max_tiles, 8)));
   void* kargs[] = {&args};
@@ -649,22 +645,29 @@ int launch_ns_fused(const NsGroup* grp, int ngroups, int steps, int const_coeffs
 // Picks the fused kernel instantiated for the tile widths this problem wants; returns
 // LACT_ERR_CONFIG when there is none (the caller then runs the multi-launch path).
 int try_ns_fused(const NsGroup* grp, int ngroups, int steps, int const_coeffs, int32_t* status,
-                 cudaStream_t stream, const bf16** result, uint64_t* trace = nullptr, int unscaled_first = 0) {
+                 cudaStream_t stream, const bf16** result, int unscaled_first = 0) {
   if (steps < 1 || steps > kNsFusedMaxSteps) return LACT_ERR_CONFIG;
   if (!const_coeffs && steps != 5) return LACT_ERR_CONFIG;
-  {
-    // LACT_B200_NS_FUSED=0 selects the one-launch-per-GEMM path (same arithmetic, for comparison)
-    const char* env = std::getenv("LACT_B200_NS_FUSED");
-    if (env != nullptr && env[0] == '0') return LACT_ERR_CONFIG;
-  }
   int bt_mm = 0, bt_mn = 0;
   ns_tile_widths(grp, ngroups, &bt_mm, &bt_mn);
   for (int g = 0; g < ngroups; ++g) result[g] = (steps % 2 == 0) ? grp[g].xa : grp[g].xb;
-  if (bt_mm == 192 && bt_mn == 192)
-    return launch_ns_fused<192, 192>(grp, ngroups, steps, const_coeffs, status, stream, trace, unscaled_first);
+  // Few matrices per launch (a small (batch x head) shard): the kernel is bound by the 15-phase chain of each
+  // matrix, not by throughput, so narrower tiles that spread every phase over more SMs (and shorten the serial
+  // work per tile) win.  Tiles of the Gram phase at width bt over all groups:
+  auto gram_tiles = [&](int bt) {
+    int64_t t = 0;
+    for (int g = 0; g < ngroups; ++g) t += static_cast<int64_t>(grp[g].nmat) * ceil_div(grp[g].m, kBM) * ceil_div(grp[g].m, bt);
+    return t;
+  };
+  const int64_t want = static_cast<int64_t>(sm_count()) * 3 / 4;
+  if (bt_mm == 192 && bt_mn == 192 && gram_tiles(192) >= want)
+    return launch_ns_fused<192, 192>(grp, ngroups, steps, const_coeffs, status, stream, unscaled_first);
   // (a 256-wide update tile leaves no room for a useful ring next to two staging tiles: 128 is used)
-  if (bt_mm == 128 && (bt_mn == 128 || bt_mn == 256))
-    return launch_ns_fused<128, 128>(grp, ngroups, steps, const_coeffs, status, stream, trace, unscaled_first);
+  const bool ok128 = (bt_mm == 192 && bt_mn == 192) || (bt_mm == 128 && (bt_mn == 128 || bt_mn == 256));
+  if (ok128 && (gram_tiles(128) >= want || gram_tiles(64) == gram_tiles(128)))
+    return launch_ns_fused<128, 128>(grp, ngroups, steps, const_coeffs, status, stream, unscaled_first);
+  if (ok128 || (bt_mm == 64 && bt_mn == 64))
+    return launch_ns_fused<64, 64>(grp, ngroups, steps, const_coeffs, status, stream, unscaled_first);
   return LACT_ERR_CONFIG;
 }
 
@@ -733,7 +736,7 @@ int plan_scan(const lact_scan_config& c, int32_t n_steps, const int32_t* kind, c
   }
   Carver cv(base);
   const size_t B = c.B, D = c.D, H = c.H;
-  p->status = cv.take<int32_t>(1024);  // status word; diagnostics trace at +256 bytes
+  p->status = cv.take<int32_t>(64);  // device status word
   p->W02 = cv.take<float>(B * 2 * H * D);
   p->W1 = cv.take<float>(B * D * H);
   p->W02c = cv.take<float>(B * 2 * H * D);
@@ -811,7 +814,7 @@ int scan_fwd(const lact_scan_config& c, const lact_scan_io& io, int32_t n_steps,
       return LACT_ERR_STEPS;
 
   const int64_t B = c.B, D = c.D, H = c.H;
-  LACT_CUDA(cudaMemsetAsync(p.status, 0, 4096, stream));
+  LACT_CUDA(cudaMemsetAsync(p.status, 0, 256, stream));
   {
     const int64_t rows = B * (2 * H + D);
     KernelScope scope(kClsPrepare, stream);
@@ -882,11 +885,7 @@ int scan_fwd(const lact_scan_config& c, const lact_scan_io& io, int32_t n_steps,
     // The Frobenius norms Newton-Schulz needs are gathered per output tile by the contraction when a
     // tile never straddles two matrices (concatenated [2H, D], or H a multiple of the 128-row tile).
     int fused_parts[2] = {0, 0};
-    static const bool fuse_sumsq = [] {
-      const char* env = std::getenv("LACT_B200_FUSED_SUMSQ");
-      return !(env != nullptr && env[0] == '0');
-    }();
-    if (fuse_sumsq && c.use_muon && (c.ns_concat || H % kBM == 0)) {
+    if (c.use_muon && (c.ns_concat || H % kBM == 0)) {
       const int bt = contract_bt(D, H);
       const int tn0 = ceil_div(D, bt), tn1 = ceil_div(H, bt);
       fused_parts[0] = (c.ns_concat ? ceil_div(2 * H, kBM) : static_cast<int>(H / kBM)) * tn0 * kEpiWarps;
@@ -934,8 +933,7 @@ int scan_fwd(const lact_scan_config& c, const lact_scan_io& io, int32_t n_steps,
       const int unscaled = g.gb02 != nullptr ? 1 : 0;
       LACT_TRY(launch_ns_prepare(ns.grp, ns.ngroups, srcs, 1, !unscaled, stream,
                                  fused_parts[0] > 0 ? fused_parts : nullptr));
-      int rc = try_ns_fused(ns.grp, ns.ngroups, c.ns_steps, c.ns_const_coeffs, p.status, stream, xres,
-                            reinterpret_cast<uint64_t*>(p.status + 64), unscaled);
+      int rc = try_ns_fused(ns.grp, ns.ngroups, c.ns_steps, c.ns_const_coeffs, p.status, stream, xres, unscaled);
       if (rc == LACT_ERR_CONFIG)
         rc = run_ns_iterations(ns.grp, ns.ngroups, c.ns_steps, c.ns_const_coeffs, xres, p.status, stream, unscaled);
       LACT_TRY(rc);
@@ -1020,13 +1018,45 @@ int lact_profile_read(double* ms, int64_t* launches) {
   return rc;
 }
 
+// Copies one status word to the host; the only place where the library waits for a stream.
+static int read_status_word(const void* device_word, cudaStream_t stream) {
+  int32_t st = 0;
+  g_stream_syncs.fetch_add(1, std::memory_order_relaxed);
+  if (cudaMemcpyAsync(&st, device_word, 4, cudaMemcpyDeviceToHost, stream) != cudaSuccess) return LACT_ERR_CUDA;
+  if (cudaStreamSynchronize(stream) != cudaSuccess) return LACT_ERR_CUDA;
+  return st;
+}
+
 int lact_read_status(const void* workspace, void* stream) {
   if (!workspace) return LACT_ERR_NULL;
-  int32_t st = 0;
-  if (cudaMemcpyAsync(&st, workspace, 4, cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)) != cudaSuccess)
-    return LACT_ERR_CUDA;
-  if (cudaStreamSynchronize(static_cast<cudaStream_t>(stream)) != cudaSuccess) return LACT_ERR_CUDA;
-  return st;
+  return read_status_word(workspace, static_cast<cudaStream_t>(stream));
+}
+
+int64_t lact_stream_sync_count(void) { return g_stream_syncs.load(); }
+
+int lact_set_wait_limit_ns(uint64_t limit_ns) {
+  if (limit_ns == 0) limit_ns = kDefaultWaitLimitNs;
+  LACT_CUDA(cudaMemcpyToSymbol(g_wait_limit_ns, &limit_ns, sizeof(limit_ns)));
+  return LACT_OK;
+}
+
+// One CTA whose single waiting thread sits on an mbarrier that nobody arrives on: the bounded
+// wait runs out and the kernel records kStatusWaitTimeout, exactly as the GEMM kernels do.
+__global__ void wait_timeout_probe_kernel(int32_t* status) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    fence_mbar_init();
+    if (!mbar_wait(&bar, 0)) atomicCAS(status, kStatusOk, kStatusWaitTimeout);
+  }
+}
+
+int lact_debug_wait_timeout(int32_t* status_word, void* stream) {
+  if (!status_word) return LACT_ERR_NULL;
+  LACT_TRY(check_device());
+  wait_timeout_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(status_word);
+  LACT_CUDA(cudaGetLastError());
+  return LACT_OK;
 }
 
 int lact_scan_workspace_bytes(const lact_scan_config* cfg, int32_t n_steps, const int32_t* kind,
@@ -1107,9 +1137,11 @@ int lact_swiglu_ffn_fwd_static(const void* w0w2, const void* w1, const void* x, 
                                int64_t D, int64_t H, void* stream) {
   if (!w0w2 || !w1 || !x || !out) return LACT_ERR_NULL;
   LACT_TRY(check_device());
-  size_t need = 0;
-  LACT_TRY(lact_swiglu_ffn_workspace_bytes(B, N, D, H, &need));
-  if (need > LACT_STATIC_SCRATCH_BYTES) return LACT_ERR_STATIC_LIMIT;
+  LACT_TRY(check_dims(B, N, D, H));
+  // status word (256 bytes reserved) + hidden activations [B, N, H] bf16
+  const unsigned long long hidden_bytes = static_cast<unsigned long long>(B) * static_cast<unsigned long long>(N) *
+                                          static_cast<unsigned long long>(H) * 2ull;
+  if (hidden_bytes > LACT_STATIC_SCRATCH_BYTES - 256ull) return LACT_ERR_STATIC_LIMIT;
   void* scratch = nullptr;
   LACT_TRY(static_scratch_address(&scratch));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -1119,6 +1151,13 @@ int lact_swiglu_ffn_fwd_static(const void* w0w2, const void* w1, const void* x, 
   ApplyArgs a{static_cast<const bf16*>(w0w2), static_cast<const bf16*>(w1), x, N * D, D, 0, N, out, N * D, D, 0,
               reinterpret_cast<bf16*>(static_cast<uint8_t*>(scratch) + 256), B, D, H};
   return run_apply(a, static_cast<int32_t*>(scratch), s);
+}
+
+int lact_static_status(void* stream) {
+  LACT_TRY(check_device());
+  void* scratch = nullptr;
+  LACT_TRY(static_scratch_address(&scratch));
+  return read_status_word(scratch, static_cast<cudaStream_t>(stream));
 }
 
 int lact_fw_grad_workspace_bytes(int64_t B, int64_t N, int64_t D, int64_t H, size_t* bytes_out) {

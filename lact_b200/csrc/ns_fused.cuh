@@ -21,7 +21,6 @@ struct NsFusedArgs {
   int32_t steps, ngroups;
   int32_t* status;
   uint32_t* done[2];  // per group: [matrix] completion counters, zero at launch
-  uint64_t* trace;    // optional: trace[0], trace[1] = globaltimer of CTA 0 at start / end (diagnostics)
 };
 
 constexpr int kNsFusedMaxSteps = 16;
@@ -87,9 +86,7 @@ ns_fused_kernel(const __grid_constant__ NsFusedArgs<BT_MM, BT_MN> args) {
       tma_prefetch_desc(&args.poly[g].out[0]);
     }
   }
-  cx.trace = args.trace;
   bool failed = false;
-  if (args.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) args.trace[0] = globaltimer_ns();
 
   // ---------------- Newton-Schulz iterations
   NsPatch patch;
@@ -111,26 +108,22 @@ ns_fused_kernel(const __grid_constant__ NsFusedArgs<BT_MM, BT_MN> args) {
     patch.diag = b / (2.f * c);       // gram: S = X X^T + (b / 2c) I
     patch.acc_scale = 1.f;
     failed = gemm_phase<OpMM, RING>(cx, args.gram[par], args.ngroups, patch, deps);
-    ++cx.phase;
     if (failed) break;
     for (int g = 0; g < 2; ++g) deps.need[g] += tiles_mm[g];
     patch.diag = a - b * b / (4.f * c);  // poly: P = c S S + (a - b^2 / 4c) I
     patch.acc_scale = c;
     patch.scale_pow = 0;
     failed = gemm_phase<OpMM, RING>(cx, args.poly, args.ngroups, patch, deps);
-    ++cx.phase;
     if (failed) break;
     for (int g = 0; g < 2; ++g) deps.need[g] += tiles_mm[g];
     patch.diag = 0.f;                 // update: X' = P X
     patch.acc_scale = 1.f;
     patch.scale_pow = it == 0 ? 1 : 0;
     failed = gemm_phase<OpMN, RING>(cx, args.upd[par], args.ngroups, patch, deps);
-    ++cx.phase;
     for (int g = 0; g < 2; ++g) deps.need[g] += tiles_mn[g];
   }
   if (failed) *cx.abort_flag = 1;
   // (the storing thread published every tile of this CTA after its stores had landed)
-  if (args.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 64) args.trace[1] = globaltimer_ns();
 
   gemm_teardown(cx, failed, args.status, kTmemCols);
 }

@@ -43,22 +43,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after kWaitLimitNs of wall time (or as soon as the CTA's abort flag is
+// Bounded wait: gives up after the wait limit (wall time; or as soon as the CTA's abort flag is
 // raised), so a missing arrival can never hang the device.
 __device__ __forceinline__ uint64_t globaltimer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-constexpr uint64_t kWaitLimitNs = 2000000000ull;
+// The limit (nanoseconds of wall time) lives in constant memory so that the host can change it
+// (lact_set_wait_limit_ns); it is read only on the slow path, after a first failed try.
+constexpr uint64_t kDefaultWaitLimitNs = 2000000000ull;
+__constant__ uint64_t g_wait_limit_ns = kDefaultWaitLimitNs;
+__device__ __forceinline__ uint64_t wait_limit_ns() { return g_wait_limit_ns; }
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag = nullptr) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
+  const uint64_t limit = wait_limit_ns();
   for (uint32_t i = 1;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 63u) == 0) {
       if (abort_flag != nullptr && *abort_flag != 0) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) return false;
+      if (globaltimer_ns() - t0 > limit) return false;
     }
   }
 }

@@ -140,13 +140,6 @@ struct GemmCtx {
   uint32_t ptile = 0;            // tiles whose dependency has been verified (scout) / consumed (producer)
   uint32_t sround = 0;           // staging hand-overs so far (epilogue threads and the storing thread count alike)
   uint32_t* dep_ok = nullptr;    // shared-memory word: tiles verified by the scout warp, read by the producer thread
-  // optional diagnostics (CTA 0 only): per phase < 6 and tile < 4, globaltimer stamps of
-  // {loads issued, MMAs committed, epilogue started, epilogue finished} at trace[40 + 16*phase + 4*tile + k]
-  uint64_t* trace = nullptr;
-  uint32_t phase = 0;
-  __device__ __forceinline__ void stamp(int tile_i, int k) const {
-    if (trace != nullptr && blockIdx.x == 0 && phase < 6 && tile_i < 4) trace[40 + 16 * phase + 4 * tile_i + k] = globaltimer_ns();
-  }
 };
 
 struct NoPatch {
@@ -189,7 +182,7 @@ __device__ __forceinline__ bool dep_wait(const uint32_t* ctr, uint32_t need, vol
   const uint64_t t0 = globaltimer_ns();
   for (uint32_t i = 1;; ++i) {
     if (ld_acquire_gpu_u32(ctr) >= need) return true;
-    if ((i & 31u) == 0 && (*abort_flag != 0 || globaltimer_ns() - t0 > kWaitLimitNs)) return false;
+    if ((i & 31u) == 0 && (*abort_flag != 0 || globaltimer_ns() - t0 > wait_limit_ns())) return false;
   }
 }
 // Storing thread: once all its stores have landed, publish the completion of a tile.
@@ -206,7 +199,7 @@ __device__ __forceinline__ bool flow_wait_verified(const GemmCtx& cx, uint32_t s
   const uint64_t t0 = globaltimer_ns();
   for (uint32_t i = 1;; ++i) {
     if (ld_acquire_cta_shared_u32(cx.dep_ok) > seq) return true;
-    if ((i & 63u) == 0 && (*cx.abort_flag != 0 || globaltimer_ns() - t0 > kWaitLimitNs)) return false;
+    if ((i & 63u) == 0 && (*cx.abort_flag != 0 || globaltimer_ns() - t0 > wait_limit_ns())) return false;
   }
 }
 
@@ -291,7 +284,6 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
           const int s = cx.it % RING;
           const uint32_t ph = (cx.it / RING) & 1;
           if (!mbar_wait(&cx.empty_bar[s], ph ^ 1, cx.abort_flag)) { failed = true; break; }
-          if (sb == num_sb - 1) cx.stamp(tile_i, 0);
           mbar_expect_tx(&cx.full_bar[s], kStageBytes);
           const uint32_t st = cx.smem_base + s * cx.stage_stride;
           const int kc = sb * KB * kBK;
@@ -346,7 +338,6 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
           umma_commit(&cx.empty_bar[s]);  // frees the stage once these MMAs have read it
         }
         if (!failed) umma_commit(&cx.acc_full_bar[as]);
-        cx.stamp(tile_i, 1);
         ++cx.tcount;
       }
     }
@@ -390,7 +381,6 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
             }
           }
           bulk_commit_group();
-          cx.stamp(tile_i, 3);
           bulk_wait_read_all();
           mbar_arrive(&cx.stg_empty_bar[0]);
           ++cx.sround;
@@ -430,7 +420,6 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
       Op::prefetch(ep, tc.batch, row, tc.n0, half, P.M, P.N, pf);
       bool got = mbar_wait(&cx.acc_full_bar[as], aph, cx.abort_flag);
       tc_fence_after();
-      if (elected) cx.stamp(tile_i, 2);
       const uint32_t acc_base = cx.tmem_base + as * kAccCols + (static_cast<uint32_t>(quarter * 32) << 16);
       if constexpr (NOUT > 0) {
         // A warp whose wait ran out must not leave the others stuck at a named barrier: it raises
@@ -519,14 +508,12 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
             }
           }
           bulk_commit_group();
-          cx.stamp(tile_i, 3);
         }
       }
       ++cx.tcount;
     }
     if constexpr (NOUT > 0 && !Deps::kOn) {
       if (elected) bulk_wait_all();  // this CTA's output tiles are in global memory
-      if (elected) cx.stamp(3, 3);
     }
   }
   return failed;

@@ -67,7 +67,7 @@ def scan_f32(w0, w1, w2, q, k, v, lr0, lr1, lr2, steps: Sequence[P.Step], *, out
         raise ValueError("fp32 mode needs head dimensions that are multiples of 4")
     q, k, v = (t.contiguous() for t in (q, k, v))
     out_len = Ltok if out_len is None else int(out_len)
-    o = torch.empty(B, out_len, D, dtype=F32, device=dev)
+    o = torch.zeros(B, out_len, D, dtype=F32, device=dev)
 
     # masters: W0|W2 stacked [B, 2H, D] (one contraction with the tokens), W1 [B, D, H]
     w02 = torch.cat([w0.float(), w2.float()], dim=1).contiguous()

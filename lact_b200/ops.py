@@ -101,7 +101,17 @@ def scan_eager(w0, w1, w2, q, k, v, lr0, lr1, lr2, steps: Sequence[P.Step], *, o
     if q.shape[1] != Ltok:
         raise ValueError("q and k must have the same number of tokens")
     out_len = Ltok if out_len is None else int(out_len)
-    o = torch.empty(B, out_len, D, dtype=BF16, device=dev)
+    # The reference drivers start from torch.zeros_like(q): tokens no APPLY step covers stay zero (e.g. the tail
+    # beyond update_length of the autoregressive-video drivers).  Zero-filling costs a full pass over o, so it is
+    # done only when the program leaves a gap.
+    covered, full = 0, True
+    for s_ in sorted((int(st[3]), int(st[3]) + int(st[2]) - int(st[1])) for st in steps if st[0] == P.APPLY):
+        if s_[0] > covered:
+            full = False
+            break
+        covered = max(covered, s_[1])
+    full = full and covered >= out_len
+    o = (torch.empty if full else torch.zeros)(B, out_len, D, dtype=BF16, device=dev)
 
     cfg = L.ScanConfig()
     cfg.B, cfg.L, cfg.D, cfg.H, cfg.out_len = B, Ltok, D, H, out_len
@@ -248,20 +258,24 @@ def _scan_fwd_fake(w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, m0, m1, m2, ste
 def _scan_bwd_op(w0: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, q: torch.Tensor, k: torch.Tensor,
                  v: torch.Tensor, lr0: torch.Tensor, lr1: torch.Tensor, lr2: torch.Tensor,
                  momentum: Optional[torch.Tensor], dump: torch.Tensor, wf0: torch.Tensor, wf1: torch.Tensor,
-                 wf2: torch.Tensor, dO: torch.Tensor, steps: List[int], cfg: List[int],
+                 wf2: torch.Tensor, dO: torch.Tensor, gw0: Optional[torch.Tensor], gw1: Optional[torch.Tensor],
+                 gw2: Optional[torch.Tensor], steps: List[int], cfg: List[int],
                  w_scale: float) -> List[torch.Tensor]:
-    """Gradients of (w0, w1, w2, q, k, v, lr0, lr1, lr2[, momentum])."""
+    """Gradients of (w0, w1, w2, q, k, v, lr0, lr1, lr2[, momentum]) from the cotangents of o (dO) and,
+    optionally, of the returned final fast weights (gw0, gw1, gw2)."""
     from .backward import scan_backward
     opts = _opts_of(cfg, w_scale)
     opts["_detach_norms"] = bool(cfg[9])
+    gwf = (gw0, gw1, gw2) if (gw0 is not None or gw1 is not None or gw2 is not None) else None
     g = scan_backward(opts, _steps_of(steps), w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, dump, wf0, wf1, wf2,
-                      dO.contiguous())
+                      dO.contiguous(), gwf)
     # fresh, non-overlapping tensors (the w0 / w2 gradients are two halves of one buffer)
     return [t.clone(memory_format=torch.contiguous_format) for t in g if t is not None]
 
 
 @_scan_bwd_op.register_fake
-def _scan_bwd_fake(w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, dump, wf0, wf1, wf2, dO, steps, cfg, w_scale):
+def _scan_bwd_fake(w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, dump, wf0, wf1, wf2, dO, gw0, gw1, gw2, steps, cfg,
+                   w_scale):
     outs = [torch.empty_like(t) for t in (w0, w1, w2, q, k, v, lr0, lr1, lr2)]
     if momentum is not None:
         outs.append(torch.empty_like(momentum))
@@ -271,6 +285,9 @@ def _scan_bwd_fake(w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, dump, wf0, wf1,
 def _scan_setup_context(ctx, inputs, output):
     w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, m0, m1, m2, steps, cfg, w_scale = inputs
     ctx.steps, ctx.cfg, ctx.w_scale, ctx.has_momentum, ctx.saved = list(steps), list(cfg), float(w_scale), momentum is not None, bool(cfg[12])
+    # unused outputs (the final weights when the caller drops them, the saved-state buffer always) must not
+    # arrive in the backward as materialised zero tensors: the saved state alone is gigabytes
+    ctx.set_materialize_grads(False)
     if cfg[12]:
         keep = [w0, w1, w2, q, k, v, lr0, lr1, lr2] + ([momentum] if momentum is not None else []) + \
                [output[4], output[1], output[2], output[3]]
@@ -288,7 +305,10 @@ def _scan_autograd(ctx, grads):
     if dO is None:
         q, k = ins[3], ins[4]
         dO = q.new_zeros((q.shape[0], ctx.cfg[10] if ctx.cfg[10] >= 0 else k.shape[1], q.shape[2]))
-    g = torch.ops.lact_b200.scan_bwd(*ins, momentum, dump, wf0, wf1, wf2, dO, ctx.steps, ctx.cfg, ctx.w_scale)
+    # cotangents of the returned final weights (None when the caller did not use them)
+    gw = [g_.float().contiguous() if g_ is not None else None for g_ in grads[1:4]]
+    g = torch.ops.lact_b200.scan_bwd(*ins, momentum, dump, wf0, wf1, wf2, dO, gw[0], gw[1], gw[2], ctx.steps, ctx.cfg,
+                                     ctx.w_scale)
     dmom = g[9] if ctx.has_momentum else None
     return (*g[:9], dmom, None, None, None, None, None, None)
 

@@ -5,6 +5,8 @@ LACT_REFERENCE_ROOT):
 
     python tests/golden/make_golden.py              # chunk drivers and sub-ops -> ref_outputs.pt
     python tests/golden/make_golden.py --prologue   # layer prologue             -> layer_prologue.pt
+    python tests/golden/make_golden.py --baseline-shapes   # drivers at the benchmark configurations' head shapes
+                                                           # and chunk sizes (token-subsampled) -> baseline_shapes.pt
 
 The reference ships no golden vectors for this path, so these fixtures are outputs of the
 reference itself (eager mode, CPU) on seeded inputs produced by `oracle.lact_oracle.make_inputs`.
@@ -215,7 +217,55 @@ def prologue_cases():
     return res
 
 
+BASELINE_OUT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline_shapes.pt")
+
+
+def baseline_shape_cases():
+    """(name, kind, input spec, kwargs, token stride of the stored subsample): the reference drivers at the head
+    shapes and chunk sizes of the benchmark configurations.  Full outputs would be tens of megabytes, so only every
+    `stride`-th output token (all heads, all features) is stored; inputs are regenerated from the seed."""
+    out = []
+    for muon in (False, True):
+        # configuration 1: bidirectional layer, fp32, 4 heads of 192, 4096 tokens, one update then apply
+        out.append((f"cfg1_bidi_fp32_muon{int(muon)}", "bidi", dict(B=4, L=4096, D=192, H=192, seed=31),
+                    dict(use_muon=muon), 64))
+        # configuration 2, one batch element: causal LLM op (unfused signature; the fused one needs Triton),
+        # bf16 autocast, 4 heads of 384, chunk 2048, 4 chunks, momentum
+        out.append((f"cfg2_llm_bf16_muon{int(muon)}", "llm_post_autocast", dict(B=4, L=8192, D=384, H=384, seed=32),
+                    dict(chunk_size=2048, use_muon=muon, mom=True), 128))
+        # configuration 5: autoregressive video layer, 12 heads of 128, hidden 256, 21 frames of 1560 tokens, momentum
+        out.append((f"cfg5_ar_muon{int(muon)}", "ar_mom", dict(B=12, L=32760, D=128, H=256, seed=35),
+                    dict(w_scale=1.0, mini_batch_size=1560, update_every=1560, use_moun=muon, num_moun_iters=5,
+                         use_momentum=True), 390))
+    # configuration 4, one batch element: NVS operator list, 4 heads of 192, one update on 16384 tokens, apply to 4096
+    out.append(("cfg4_nvs_steps5", "nvs", dict(B=4, L=20480, D=192, H=192, seed=34),
+                dict(order=[(0, 16384, True, False), (16384, 20480, False, True)], steps=5), 64))
+    return out
+
+
+def baseline_shapes_main():
+    import time
+    blob = {"cases": {}, "torch": torch.__version__}
+    for name, kind, spec, kw, stride in baseline_shape_cases():
+        t0 = time.time()
+        inp = orc.make_inputs(**spec)
+        res = run_reference(kind, inp, kw)
+        sub = {"o": res["o"].detach()[:, ::stride].contiguous().clone()}
+        for wn in ("w0", "w1", "w2"):  # final fast weights: first 8 rows of every head
+            if res.get(wn) is not None:
+                sub[wn] = res[wn].detach()[:, :8].contiguous().clone()
+        blob["cases"][name] = dict(kind=kind, spec=spec, kw=kw, stride=stride, checksum=checksum(inp), out=sub)
+        print(f"{name:28s} {time.time() - t0:6.1f} s  " +
+              " ".join(f"{k}:{tuple(v.shape)}:{str(v.dtype)[6:]}" for k, v in sub.items()))
+    torch.save(blob, BASELINE_OUT)
+    print("wrote", BASELINE_OUT, os.path.getsize(BASELINE_OUT) // 1024, "KiB")
+
+
 def main():
+    if "--baseline-shapes" in sys.argv:
+        assert ref_loader.available(), "reference tree not found"
+        baseline_shapes_main()
+        return
     if "--prologue" in sys.argv:
         assert ref_loader.available(), "reference tree not found"
         torch.set_num_threads(1)

@@ -1,0 +1,239 @@
+"""GPU parity at the benchmark configurations' own head shapes and chunk sizes.
+
+Each case is compared (i) with the CPU oracle run here on the same seeded inputs (full output) and
+(ii) with the committed token-subsample of the REFERENCE's output at that shape
+(tests/golden/baseline_shapes.pt, reproduced bit-exactly by the oracle on the build machine).
+
+Tolerances are the stated ones: bf16-in / fp32-accumulate max|a-ref|/max|ref| <= 2e-2 and cosine
+>= 0.999; fp32 mode <= 1e-3.  After a Newton-Schulz (Muon) pass two non-bit-identical
+implementations differ by about 1e-2 (the reference's bf16 iteration amplifies one input ulp that
+much), so Muon cases are held to the stated tolerance where no Newton-Schulz result is involved
+(chunk 0; every chunk when teacher-forced), and otherwise to a band measured in the same test from
+the reference arithmetic's own response to a one-ulp input change.
+"""
+import os
+
+import pytest
+import torch
+
+from oracle_drivers import run_oracle
+
+pytestmark = pytest.mark.gpu
+BF16 = torch.bfloat16
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+NAMES = ("w0", "w1", "w2", "q", "k", "v", "lr0", "lr1", "lr2")
+TOL, COS = 2e-2, 0.999
+
+
+@pytest.fixture(scope="module")
+def lb():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from lact_b200 import build
+    build.build()
+    import lact_b200
+    return lact_b200
+
+
+@pytest.fixture(scope="module")
+def orc():
+    from oracle import lact_oracle
+    return lact_oracle
+
+
+@pytest.fixture(scope="module")
+def shapes():
+    return torch.load(os.path.join(ROOT, "tests", "golden", "baseline_shapes.pt"), map_location="cpu",
+                      weights_only=False)
+
+
+def cu(d):
+    return {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in d.items()}
+
+
+def bf(i):
+    j = dict(i)
+    for n in ("q", "k", "v"):
+        j[n] = i[n].to(BF16)
+    return j
+
+
+def args(i):
+    return [i[n] for n in NAMES]
+
+
+def close(orc, got, ref, tol=TOL, cos=COS, what=""):
+    got, ref = got.detach().float().cpu(), ref.detach().float().cpu()
+    assert got.shape == ref.shape, (what, got.shape, ref.shape)
+    assert torch.isfinite(got).all(), what
+    rm, cs = orc.rel_max(got, ref), orc.cosine(got, ref)
+    assert rm <= tol and cs >= cos, f"{what}: rel_max={rm:.3e} cos={cs:.6f}"
+    return rm
+
+
+# ------------------------------------------------------------------------------ configuration 2
+def test_cfg2_fused_signature_muon_off_all_chunks(lb, orc):
+    """One batch element of the benchmark workload (4 heads of 384, 8192 tokens, chunk 2048, momentum),
+    fused post-norm signature, Muon off: all four chunks against the restatement of
+    ttt_operation_fused_kernel.py:103-186."""
+    i = bf(orc.make_inputs(4, 8192, 384, 384, seed=32))
+    ref = orc.block_causal_lact_swiglu_fused(*args(i), chunk_size=2048, use_muon=False, momentum=i["momentum"])
+    c = cu(i)
+    o = lb.postnorm_block_causal_lact_swiglu_fused_kernel_triton(*args(c), chunk_size=2048, use_muon=False,
+                                                                 momentum=c["momentum"])
+    lb.synchronize_and_check()
+    for ci in range(4):
+        close(orc, o[:, ci * 2048:(ci + 1) * 2048], ref[:, ci * 2048:(ci + 1) * 2048], what=f"cfg2 fused chunk {ci}")
+    close(orc, o, ref, what="cfg2 fused, Muon off")
+
+
+def test_cfg2_unfused_signature_against_reference_output(lb, orc, shapes):
+    """Same shape through block_causal_lact_swiglu against the reference's own bf16-autocast output
+    (ttt_operation.py:69-214 run on CPU; stored subsample), Muon off."""
+    case = shapes["cases"]["cfg2_llm_bf16_muon0"]
+    i = cu(bf(orc.make_inputs(**case["spec"])))
+    o = lb.block_causal_lact_swiglu(*args(i), chunk_size=2048, use_muon=False, momentum=i["momentum"])
+    lb.synchronize_and_check()
+    close(orc, o[:, ::case["stride"]], case["out"]["o"], what="cfg2 unfused vs reference")
+
+
+def test_cfg2_fused_signature_muon_on(lb, orc, shapes):
+    """Muon + momentum at the benchmark shape: chunk 0 at the stated tolerance, chunk 1 within the band of
+    one Newton-Schulz pass, every chunk teacher-forced from the oracle's state at the stated tolerance."""
+    from lact_b200 import program as P
+    B, L, D, H, Cs = 4, 8192, 384, 384, 2048
+    i = bf(orc.make_inputs(B, L, D, H, seed=32))
+    states = []
+    ref = orc.block_causal_lact_swiglu_fused(*args(i), chunk_size=Cs, use_muon=True, momentum=i["momentum"],
+                                             states=states)
+    model = orc.block_causal_lact_swiglu_fused(*args(i), chunk_size=Cs, use_muon=True, momentum=i["momentum"],
+                                               ns=orc.newton_schulz_folded)
+    c = cu(i)
+    o = lb.postnorm_block_causal_lact_swiglu_fused_kernel_triton(*args(c), chunk_size=Cs, use_muon=True,
+                                                                 momentum=c["momentum"])
+    close(orc, o[:, :Cs], ref[:, :Cs], what="cfg2 muon chunk 0")
+    # chunk 1: against the restatement with the kernels' rounding points, and (twice the band) against the
+    # reference's eager rounding; printed so that the run's log carries the measured figures
+    e_model = close(orc, o[:, Cs:2 * Cs], model[:, Cs:2 * Cs], tol=3e-2, cos=0.998, what="cfg2 muon chunk 1 vs folded model")
+    e_eager = close(orc, o[:, Cs:2 * Cs], ref[:, Cs:2 * Cs], tol=2 * TOL, cos=0.998, what="cfg2 muon chunk 1 vs eager model")
+    print(f"cfg2 muon chunk 1: rel_max vs folded model {e_model:.3e}, vs eager model {e_eager:.3e}")
+    for ci in range(1, len(states) + 1):
+        w02, w1 = states[ci - 1]
+        w0s, w2s = w02[:, :H].contiguous(), w02[:, H:].contiguous()
+        s, e = ci * Cs, min((ci + 1) * Cs, L)
+        got = lb.scan(w0s.cuda(), w1.cuda(), w2s.cuda(), c["q"], c["k"], c["v"], c["lr0"], c["lr1"], c["lr2"],
+                      [(P.APPLY, s, e, s)])
+        close(orc, got[:, s:e], ref[:, s:e], tol=1e-2, cos=0.9999, what=f"cfg2 teacher-forced chunk {ci}")
+    # the unfused signature's chunk 0 against the reference's own output with Muon on
+    case = shapes["cases"]["cfg2_llm_bf16_muon1"]
+    o2 = lb.block_causal_lact_swiglu(*args(c), chunk_size=Cs, use_muon=True, momentum=c["momentum"])
+    n0 = Cs // case["stride"]
+    close(orc, o2[:, ::case["stride"]][:, :n0], case["out"]["o"][:, :n0], what="cfg2 unfused muon chunk 0 vs reference")
+    lb.synchronize_and_check()
+
+
+# ------------------------------------------------------------------------------ configuration 1
+@pytest.mark.parametrize("muon", [False, True])
+def test_cfg1_bidirectional_fp32_full_size(lb, orc, shapes, muon):
+    """bidirectional_lact_swiglu, fp32, 4 heads of 192, 4096 tokens (the reference's CPU configuration) against
+    the reference's own output.  Muon off: the fp32 tolerance.  Muon on: the reference rounds the gradient to
+    bf16 inside Newton-Schulz, so the band is its own response to a 2^-8 change of one input element."""
+    case = shapes["cases"][f"cfg1_bidi_fp32_muon{int(muon)}"]
+    i = orc.make_inputs(**case["spec"])
+    o = lb.bidirectional_lact_swiglu(*args(cu(i)), use_muon=muon)
+    lb.synchronize_and_check()
+    assert o.dtype == torch.float32
+    got, ref = o[:, ::case["stride"]].cpu(), case["out"]["o"]
+    if not muon:
+        close(orc, got, ref, tol=1e-3, what="cfg1 fp32 Muon off")
+        return
+    full = orc.bidirectional_lact_swiglu(*args(i), use_muon=True)
+    g = dict(i)
+    g["v"] = i["v"].clone()
+    g["v"][0, 5, 7] *= 1.0 + 2.0 ** -8
+    noise = orc.rel_max(orc.bidirectional_lact_swiglu(*args(g), use_muon=True), full)
+    err = orc.rel_max(o.cpu(), full)
+    print(f"cfg1 fp32 Muon on: rel_max {err:.3e}, reference's one-ulp response {noise:.3e}")
+    assert err <= max(1e-3, 3.0 * noise) and err <= 6e-2, (err, noise)
+    assert orc.cosine(o.cpu(), full) >= 0.999
+    assert orc.rel_max(got, ref) <= max(1e-3, 3.0 * noise)
+
+
+# ------------------------------------------------------------------------------ configuration 4
+def test_cfg4_nvs_large_single_update(lb, orc, shapes):
+    """NVS operator list at 4 heads of 192: one update over 16384 tokens, then apply to 4096 others, five
+    constant-coefficient Newton-Schulz steps (a single Muon update: the 3e-2 band of the small NVS cases)."""
+    case = shapes["cases"]["cfg4_nvs_steps5"]
+    i = cu(bf(orc.make_inputs(**case["spec"])))
+    t = lambda w: w.transpose(1, 2).contiguous()
+    order = [lb.TTTOperator(*op) for op in case["kw"]["order"]]
+    o, a, b, c = lb.fast_weight_swish_glu_weight_norm_mini_batch_apply(
+        t(i["w0"]), t(i["w1"]), t(i["w2"]), i["q"], i["k"], i["v"], i["lr0"], i["lr1"], i["lr2"], order,
+        muon_update_steps=case["kw"]["steps"])
+    lb.synchronize_and_check()
+    assert o.shape == (4, 4096, 192)
+    close(orc, o[:, ::case["stride"]], case["out"]["o"], tol=3e-2, cos=0.998, what="cfg4 o")
+    for got, key in ((a, "w0"), (b, "w1"), (c, "w2")):
+        close(orc, got[:, :8], case["out"][key], tol=3e-2, cos=0.998, what=f"cfg4 {key}")
+
+
+# ------------------------------------------------------------------------------ configuration 5
+def test_cfg5_ar_video_all_frames_muon_off(lb, orc, shapes):
+    """12 heads of 128, hidden 256, 21 frames of 1560 tokens with momentum, Muon off: every frame, end to end,
+    against the reference's output, and the final fast weights."""
+    case = shapes["cases"]["cfg5_ar_muon0"]
+    i = cu(bf(orc.make_inputs(**case["spec"])))
+    o, a, b, c = lb.ar_fast_weight_swish_glu_weight_norm_mini_batch_with_momentum(
+        *args(i), fw_momentum=i["momentum"], **case["kw"])
+    lb.synchronize_and_check()
+    close(orc, o[:, ::case["stride"]], case["out"]["o"], what="cfg5 Muon off, all frames")
+    for got, key in ((a, "w0"), (b, "w1"), (c, "w2")):
+        close(orc, got[:, :8], case["out"][key], what=f"cfg5 Muon off {key}")
+
+
+def test_cfg5_ar_video_muon_first_update(lb, orc):
+    """Same configuration with Muon: the first frame after the first update has one Newton-Schulz pass
+    behind it and is bounded by the reference arithmetic's own one-ulp response (3 frames are run)."""
+    spec = dict(B=12, L=3 * 1560, D=128, H=256, seed=35)
+    kw = dict(w_scale=1.0, mini_batch_size=1560, update_every=1560, use_moun=True, num_moun_iters=5, use_momentum=True)
+    f = bf(orc.make_inputs(**spec))
+    ff = {k: (v.float() if torch.is_tensor(v) else v) for k, v in f.items()}
+    base = orc.ar_mini_batch(*args(ff), fw_momentum=ff["momentum"], **kw)[0]
+    g = dict(ff)
+    vb = f["v"].clone()
+    vb.view(torch.int16)[0, 3, 7] += 1
+    g["v"] = vb.float()
+    noisy = orc.ar_mini_batch(*args(g), fw_momentum=ff["momentum"], **kw)[0]
+    i = cu(f)
+    o = lb.ar_fast_weight_swish_glu_weight_norm_mini_batch_with_momentum(*args(i), fw_momentum=i["momentum"], **kw)[0]
+    lb.synchronize_and_check()
+    noise = orc.rel_fro(noisy[:, :1560], base[:, :1560])
+    err = orc.rel_fro(o[:, :1560].float().cpu(), base[:, :1560])
+    print(f"cfg5 Muon on, frame 0: rel_fro {err:.3e}, reference's one-ulp response {noise:.3e}")
+    assert err <= max(TOL, 4.0 * noise) and err <= 8e-2, (err, noise)
+    assert orc.cosine(o[:, :1560].float().cpu(), base[:, :1560]) >= 0.997
+
+
+# ------------------------------------------------------------------------------ configuration 3 (backward)
+def test_cfg3_backward_at_benchmark_head_shape(lb, orc):
+    """Gradients at D = H = 384, chunk 2048, three chunks (two updates, so that the momentum gradient is
+    exercised), Muon off, fused signature: against autograd through the CPU oracle in fp32 on the same
+    bf16-rounded inputs."""
+    from test_gpu_backward import _check, _grads_cuda, _grads_oracle, scan_autograd
+    B, L, D, H, C = 2, 6144, 384, 384, 2048
+    inp = bf(orc.make_inputs(B, L, D, H, seed=33))
+    dO = torch.randn(B, L, D, generator=torch.Generator().manual_seed(5)).to(BF16)
+
+    def ref_fn(w0, w1, w2, q, k, v, l0, l1, l2, m):
+        cfg = orc.ScanConfig(use_muon=False, renorm="inner", fp32_mode=True)
+        steps = [("apply", 0, C, 0), ("update", 0, C, 0), ("apply", C, 2 * C, C), ("update", C, 2 * C, 0),
+                 ("apply", 2 * C, 3 * C, 2 * C)]
+        o, *_ = scan_autograd(orc, w0, w1, w2, q, k, v, l0, l1, l2, steps, cfg, m)
+        return o
+
+    cu_fn = lambda w0, w1, w2, q, k, v, l0, l1, l2, m: lb.postnorm_block_causal_lact_swiglu_fused_kernel_triton(
+        w0, w1, w2, q, k, v, l0, l1, l2, chunk_size=C, use_muon=False, momentum=m)
+    _, g_ref = _grads_oracle(orc, inp, ref_fn, True, dO)
+    _, g = _grads_cuda(inp, cu_fn, True, dO)
+    lb.synchronize_and_check()
+    _check(orc, g, g_ref, list(NAMES) + ["momentum"])

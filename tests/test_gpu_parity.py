@@ -164,7 +164,10 @@ def _flip_one_ulp(G):
 @pytest.mark.parametrize("shape", [(2, 64, 64), (2, 64, 128), (2, 128, 64), (3, 384, 384), (2, 768, 384),
                                    (2, 128, 256), (2, 192, 192),
                                    # contraction lengths that are not whole 64-wide k-blocks, odd k-block counts
-                                   (2, 72, 200), (1, 200, 72), (1, 136, 328)])
+                                   (2, 72, 200), (1, 200, 72), (1, 136, 328),
+                                   # enough matrices per launch for the wide-tile variants of the fused kernel (few
+                                   # matrices select narrower tiles: the cases above)
+                                   (24, 384, 384), (20, 768, 384), (16, 192, 192)])
 @pytest.mark.parametrize("steps", [None, 0, 3, 5])
 def test_newton_schulz(lb, orc, shape, steps):
     g = torch.Generator().manual_seed(2)
