@@ -478,15 +478,15 @@ def _bf16_contig(t: torch.Tensor, name: str) -> torch.Tensor:
     return t.contiguous()
 
 
-@_no_trace
-def fused_swiglu_ffn_fwd(W0_W2: torch.Tensor, W1: torch.Tensor, X: torch.Tensor) -> torch.Tensor:
-    """lact_llm/lact_model/lact_triton_kernels/lact_swiglu_ffn.py:79-96: W0_W2 [B, 2H, D],
-    W1 [B, D, H], X [B, N, D] (bf16) -> [B, N, D]."""
-    dev = _need_cuda(W0_W2, W1, X)
-    W0_W2, W1, X = _bf16_contig(W0_W2, "W0_W2"), _bf16_contig(W1, "W1"), _bf16_contig(X, "X")
+# The three fused sub-ops that the reference wraps in autograd Functions (FusedSwiGLUFFNFwd, FusedLactSwiGLUFFNBwd,
+# L2NormAddFunction) are registered operators with a fake implementation and an autograd formula: a caller that
+# differentiates through them, or compiles them, gets what the reference's Functions give.
+@torch.library.custom_op("lact_b200::swiglu_ffn_fwd", mutates_args=(), device_types="cuda")
+def _swiglu_ffn_fwd_op(W0_W2: torch.Tensor, W1: torch.Tensor, X: torch.Tensor) -> torch.Tensor:
+    dev = X.device
+    W0_W2, W1, X = W0_W2.contiguous(), W1.contiguous(), X.contiguous()
     B, N, D = X.shape
     H = W0_W2.shape[1] // 2
-    assert W0_W2.shape == (B, 2 * H, D) and W1.shape == (B, D, H)
     out = torch.empty(B, N, D, dtype=BF16, device=dev)
     lib = L.lib()
     need = C.c_size_t(0)
@@ -499,18 +499,56 @@ def fused_swiglu_ffn_fwd(W0_W2: torch.Tensor, W1: torch.Tensor, X: torch.Tensor)
     return out
 
 
-@_no_trace
-def fused_lact_swiglu_ffn_fast_weight_grads(W0_W2, W1, K, V, lr0, lr1, lr2):
-    """lact_llm/lact_model/lact_triton_kernels/lact_fw_grad.py:159-175: returns (DW0_DW2
-    [B, 2H, D], DW1 [B, D, H]) in bf16; lr0/1/2 are [B, N]."""
-    dev = _need_cuda(W0_W2, W1, K, V, lr0, lr1, lr2)
-    W0_W2, W1 = _bf16_contig(W0_W2, "W0_W2"), _bf16_contig(W1, "W1")
-    K, V = _bf16_contig(K, "K"), _bf16_contig(V, "V")
+@_swiglu_ffn_fwd_op.register_fake
+def _swiglu_ffn_fwd_fake(W0_W2, W1, X):
+    return X.new_empty(X.shape)
+
+
+@torch.library.custom_op("lact_b200::swiglu_ffn_bwd", mutates_args=(), device_types="cuda")
+def _swiglu_ffn_bwd_op(W0_W2: torch.Tensor, W1: torch.Tensor, X: torch.Tensor,
+                       grad_out: torch.Tensor) -> List[torch.Tensor]:
+    """(grad_W0_W2, grad_W1, grad_X), bf16: lact_swiglu_ffn.py:46-76 (pre-activations recomputed)."""
+    from .backward import apply_backward, check_status, reset_status
+    reset_status(X.device)
+    dW02 = torch.zeros(W0_W2.shape, dtype=torch.float32, device=X.device)
+    dW1 = torch.zeros(W1.shape, dtype=torch.float32, device=X.device)
+    dX = apply_backward(W0_W2.contiguous(), W1.contiguous(), X.contiguous(), grad_out.to(BF16).contiguous(), dW02, dW1)
+    return [dW02.to(BF16), dW1.to(BF16), dX]
+
+
+@_swiglu_ffn_bwd_op.register_fake
+def _swiglu_ffn_bwd_fake(W0_W2, W1, X, grad_out):
+    return [torch.empty_like(W0_W2), torch.empty_like(W1), torch.empty_like(X)]
+
+
+def _swiglu_ffn_setup(ctx, inputs, output):
+    ctx.save_for_backward(*inputs)
+
+
+def _swiglu_ffn_autograd(ctx, grad_out):
+    return tuple(torch.ops.lact_b200.swiglu_ffn_bwd(*ctx.saved_tensors, grad_out))
+
+
+_swiglu_ffn_fwd_op.register_autograd(_swiglu_ffn_autograd, setup_context=_swiglu_ffn_setup)
+
+
+def fused_swiglu_ffn_fwd(W0_W2: torch.Tensor, W1: torch.Tensor, X: torch.Tensor) -> torch.Tensor:
+    """lact_llm/lact_model/lact_triton_kernels/lact_swiglu_ffn.py:79-96: W0_W2 [B, 2H, D],
+    W1 [B, D, H], X [B, N, D] (bf16) -> [B, N, D].  Differentiable as FusedSwiGLUFFNFwd (:19-76) is."""
+    _need_cuda(W0_W2, W1, X)
+    W0_W2, W1, X = _bf16_contig(W0_W2, "W0_W2"), _bf16_contig(W1, "W1"), _bf16_contig(X, "X")
+    B, N, D = X.shape
+    H = W0_W2.shape[1] // 2
+    assert W0_W2.shape == (B, 2 * H, D) and W1.shape == (B, D, H)
+    return torch.ops.lact_b200.swiglu_ffn_fwd(W0_W2, W1, X)
+
+
+@torch.library.custom_op("lact_b200::fw_grads_fwd", mutates_args=(), device_types="cuda")
+def _fw_grads_fwd_op(W0_W2: torch.Tensor, W1: torch.Tensor, K: torch.Tensor, V: torch.Tensor, lr0: torch.Tensor,
+                     lr1: torch.Tensor, lr2: torch.Tensor) -> List[torch.Tensor]:
+    dev = K.device
     B, N, D = K.shape
     H = W0_W2.shape[1] // 2
-    lr0, lr1, lr2 = (_vec(t, B, N, "lr") for t in (lr0, lr1, lr2))
-    if not (lr0.dtype == lr1.dtype == lr2.dtype):
-        lr0, lr1, lr2 = lr0.float(), lr1.float(), lr2.float()
     dw02 = torch.empty(B, 2 * H, D, dtype=BF16, device=dev)
     dw1 = torch.empty(B, D, H, dtype=BF16, device=dev)
     lib = L.lib()
@@ -522,6 +560,58 @@ def fused_lact_swiglu_ffn_fast_weight_grads(W0_W2, W1, K, V, lr0, lr1, lr2):
                                  lr1.data_ptr(), lr2.data_ptr(), L.dtype_code(lr0), dw02.data_ptr(), dw1.data_ptr(),
                                  B, N, D, H, ws.data_ptr(), ws.numel(), L.stream_ptr()), "lact_fw_grad")
     L.mark_pending(ws)
+    return [dw02, dw1]
+
+
+@_fw_grads_fwd_op.register_fake
+def _fw_grads_fwd_fake(W0_W2, W1, K, V, lr0, lr1, lr2):
+    return [torch.empty_like(W0_W2), torch.empty_like(W1)]
+
+
+@torch.library.custom_op("lact_b200::fw_grads_bwd", mutates_args=(), device_types="cuda")
+def _fw_grads_bwd_op(W0_W2: torch.Tensor, W1: torch.Tensor, K: torch.Tensor, V: torch.Tensor, lr0: torch.Tensor,
+                     lr1: torch.Tensor, lr2: torch.Tensor, g02: torch.Tensor, g1: torch.Tensor) -> List[torch.Tensor]:
+    """Gradients of (W0_W2, W1, K, V, lr0, lr1, lr2) given those of (DW0_DW2, DW1): the hand-written second-order
+    backward of lact_fw_grad.py:61-156 (bf16 for weights and activations, fp32 row sums for the learning rates)."""
+    from .backward import fw_grad_backward, reset_status
+    reset_status(K.device)
+    dW02 = torch.zeros(W0_W2.shape, dtype=torch.float32, device=K.device)
+    dW1 = torch.zeros(W1.shape, dtype=torch.float32, device=K.device)
+    dk, dv, g0, g1_, g2 = fw_grad_backward(W0_W2, W1, K, V, lr0, lr1, lr2, 1.0, g02, g1, dW02, dW1)
+    return [dW02.to(BF16), dW1.to(BF16), dk, dv, g0.to(lr0.dtype), g1_.to(lr1.dtype), g2.to(lr2.dtype)]
+
+
+@_fw_grads_bwd_op.register_fake
+def _fw_grads_bwd_fake(W0_W2, W1, K, V, lr0, lr1, lr2, g02, g1):
+    return [torch.empty_like(t) for t in (W0_W2, W1, K, V, lr0, lr1, lr2)]
+
+
+def _fw_grads_setup(ctx, inputs, output):
+    ctx.save_for_backward(*inputs)
+    ctx.set_materialize_grads(False)
+
+
+def _fw_grads_autograd(ctx, grads):
+    W0_W2, W1 = ctx.saved_tensors[:2]
+    g02 = grads[0] if grads[0] is not None else torch.zeros_like(W0_W2)
+    g1 = grads[1] if grads[1] is not None else torch.zeros_like(W1)
+    return tuple(torch.ops.lact_b200.fw_grads_bwd(*ctx.saved_tensors, g02.contiguous(), g1.contiguous()))
+
+
+_fw_grads_fwd_op.register_autograd(_fw_grads_autograd, setup_context=_fw_grads_setup)
+
+
+def fused_lact_swiglu_ffn_fast_weight_grads(W0_W2, W1, K, V, lr0, lr1, lr2):
+    """lact_llm/lact_model/lact_triton_kernels/lact_fw_grad.py:159-175: returns (DW0_DW2
+    [B, 2H, D], DW1 [B, D, H]) in bf16; lr0/1/2 are [B, N].  Differentiable as FusedLactSwiGLUFFNBwd (:21-156) is."""
+    _need_cuda(W0_W2, W1, K, V, lr0, lr1, lr2)
+    W0_W2, W1 = _bf16_contig(W0_W2, "W0_W2"), _bf16_contig(W1, "W1")
+    K, V = _bf16_contig(K, "K"), _bf16_contig(V, "V")
+    B, N, D = K.shape
+    lr0, lr1, lr2 = (_vec(t, B, N, "lr") for t in (lr0, lr1, lr2))
+    if not (lr0.dtype == lr1.dtype == lr2.dtype):
+        lr0, lr1, lr2 = lr0.float(), lr1.float(), lr2.float()
+    dw02, dw1 = torch.ops.lact_b200.fw_grads_fwd(W0_W2, W1, K, V, lr0, lr1, lr2)
     return dw02, dw1
 
 
@@ -549,24 +639,73 @@ def zeropower_via_newtonschulz5(G: torch.Tensor, steps: Optional[int] = None) ->
     return x
 
 
-@_no_trace
-def l2_norm_add_fused(x, x_add, tgt_scale, eps: float = 1e-5, tgt_dtype=None) -> torch.Tensor:
-    """lact_llm/lact_model/lact_triton_kernels/l2norm_triton_kernels.py:419-427."""
-    dev = _need_cuda(x, x_add, tgt_scale)
-    tgt_dtype = x.dtype if tgt_dtype is None else tgt_dtype
-    if tgt_dtype not in (torch.float32, BF16):
-        raise TypeError("tgt_dtype must be float32 or bfloat16")
+@torch.library.custom_op("lact_b200::l2_norm_add_fwd", mutates_args=(), device_types="cuda")
+def _l2_norm_add_fwd_op(x: torch.Tensor, x_add: torch.Tensor, tgt_scale: torch.Tensor, eps: float,
+                        out_bf16: bool) -> torch.Tensor:
+    dev = x.device
     x, x_add = x.contiguous(), x_add.contiguous()
     B, T, D = x.shape
-    if tgt_scale.dim() == 3:
-        tgt_scale = tgt_scale.squeeze(-1)
-    sc = tgt_scale.float().contiguous()
-    y = torch.empty(B, T, D, dtype=tgt_dtype, device=dev)
+    sc = tgt_scale.reshape(B, T).float().contiguous()
+    y = torch.empty(B, T, D, dtype=BF16 if out_bf16 else torch.float32, device=dev)
     with torch.cuda.device(dev):
         L.check(L.lib().lact_l2_norm_add(x.data_ptr(), L.dtype_code(x), x_add.data_ptr(), L.dtype_code(x_add),
                                          sc.data_ptr(), y.data_ptr(), L.dtype_code(y), B, T, D, float(eps),
                                          L.stream_ptr()), "lact_l2_norm_add")
     return y
+
+
+@_l2_norm_add_fwd_op.register_fake
+def _l2_norm_add_fwd_fake(x, x_add, tgt_scale, eps, out_bf16):
+    return x.new_empty(x.shape, dtype=BF16 if out_bf16 else torch.float32)
+
+
+@torch.library.custom_op("lact_b200::l2_norm_add_bwd", mutates_args=(), device_types="cuda")
+def _l2_norm_add_bwd_op(x: torch.Tensor, x_add: torch.Tensor, tgt_scale: torch.Tensor, dy: torch.Tensor,
+                        eps: float) -> List[torch.Tensor]:
+    """(dx, dx_add, dtgt_scale) of y = (x + x_add) * rsqrt(sum (x + x_add)^2 + eps) * tgt_scale
+    (l2norm_triton_kernels.py:97-172, 409-416); the row is recomputed from the inputs."""
+    from .backward import renorm_backward
+    if abs(float(eps) - 1e-5) > 1e-12:
+        raise NotImplementedError("the backward of l2_norm_add_fused is built for eps = 1e-5 (the value every caller uses)")
+    B, T, D = x.shape
+    sc = tgt_scale.reshape(B, T).float().contiguous()
+    dsc = torch.zeros(B, T, dtype=torch.float32, device=x.device)
+    dw = renorm_backward(x.float().contiguous(), x_add, sc, dy.float().contiguous(), dsc, L.RENORM_EPS_INSIDE)
+    return [dw.to(x.dtype), dw.to(x_add.dtype), dsc.reshape(tgt_scale.shape).to(tgt_scale.dtype)]
+
+
+@_l2_norm_add_bwd_op.register_fake
+def _l2_norm_add_bwd_fake(x, x_add, tgt_scale, dy, eps):
+    return [torch.empty_like(x), torch.empty_like(x_add), torch.empty_like(tgt_scale)]
+
+
+def _l2_norm_add_setup(ctx, inputs, output):
+    x, x_add, tgt_scale, eps, _ = inputs
+    ctx.save_for_backward(x, x_add, tgt_scale)
+    ctx.eps = float(eps)
+
+
+def _l2_norm_add_autograd(ctx, dy):
+    x, x_add, tgt_scale = ctx.saved_tensors
+    dx, dxa, dsc = torch.ops.lact_b200.l2_norm_add_bwd(x, x_add, tgt_scale, dy.contiguous(), ctx.eps)
+    return dx, dxa, dsc, None, None
+
+
+_l2_norm_add_fwd_op.register_autograd(_l2_norm_add_autograd, setup_context=_l2_norm_add_setup)
+
+
+def l2_norm_add_fused(x, x_add, tgt_scale, eps: float = 1e-5, tgt_dtype=None) -> torch.Tensor:
+    """lact_llm/lact_model/lact_triton_kernels/l2norm_triton_kernels.py:419-427.  Differentiable as
+    L2NormAddFunction (:386-416) is."""
+    _need_cuda(x, x_add, tgt_scale)
+    tgt_dtype = x.dtype if tgt_dtype is None else tgt_dtype
+    if tgt_dtype not in (torch.float32, BF16):
+        raise TypeError("tgt_dtype must be float32 or bfloat16")
+    if x.dtype not in (torch.float32, BF16):
+        x = x.float()
+    if x_add.dtype not in (torch.float32, BF16):
+        x_add = x_add.float()
+    return torch.ops.lact_b200.l2_norm_add_fwd(x, x_add, tgt_scale, float(eps), tgt_dtype == BF16)
 
 
 @_no_trace

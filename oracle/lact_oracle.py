@@ -444,14 +444,16 @@ def nvs_mini_batch_apply(w0, w1, w2, q, k, v, lr0, lr1, lr2, ttt_ua_order, muon_
 def ar_mini_batch(
     w0, w1, w2, q, k, v, lr0, lr1, lr2, w_scale, num_repeat=1, mini_batch_size=-1, update_length=-1,
     update_every=-1, use_moun=False, num_moun_iters=3, weight_norm=True, fw_momentum=None, use_momentum=False,
-    *, nm: Numerics = Numerics(), trace: Optional[list] = None,
+    *, nm: Numerics = Numerics(), trace: Optional[list] = None, ns=None,
 ):
     """Autoregressive-video training driver (update-then-apply with an `update_every` stride).
+    `ns` replaces the Newton-Schulz function (default: the reference's eager arithmetic, `newton_schulz`).
 
     Without momentum: lact_ar_video/minVid/models/blocks/ar_lact_swa_repeat.py:22-168 (the
     `num_repeat` loop wraps the chunk loop).  With momentum:
     ar_lact_swa_repeat_sp.py:27-193 (which has no `num_repeat` loop: one pass).
     """
+    ns = newton_schulz if ns is None else ns
     L = k.shape[1]
     if update_length == -1:
         update_length = L
@@ -477,9 +479,9 @@ def ar_mini_batch(
                 dw0, dw1, dw2 = dw0 + m0 * beta, dw1 + m1 * beta, dw2 + m2 * beta
                 m0, m1, m2 = dw0, dw1, dw2
             if use_moun:
-                dw1 = newton_schulz(dw1, num_moun_iters)
-                dw0 = newton_schulz(dw0, num_moun_iters)
-                dw2 = newton_schulz(dw2, num_moun_iters)
+                dw1 = ns(dw1, num_moun_iters)
+                dw0 = ns(dw0, num_moun_iters)
+                dw2 = ns(dw2, num_moun_iters)
             w1, w0, w2 = w1 + dw1, w0 + dw0, w2 + dw2
             if weight_norm:
                 w0, w1, w2 = _renorm_outer(w0, n0), _renorm_outer(w1, n1), _renorm_outer(w2, n2)

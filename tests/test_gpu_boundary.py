@@ -73,9 +73,9 @@ def test_bounded_wait_runs_out_is_reported_and_the_next_call_is_clean(lb, orc):
         LL.check(lib.lact_debug_wait_timeout(ws.data_ptr(), LL.stream_ptr()), "lact_debug_wait_timeout")
         # raw C ABI: the status word reads 101
         assert lib.lact_read_status(ws.data_ptr(), LL.stream_ptr()) == 101
-        # shim: the word reaches the host through the non-blocking ring and raises at the next check
-        LL.mark_pending(ws)
+        # shim: the word reaches the host through the non-blocking ring and raises at the next look at it
         with pytest.raises(LL.LactError):
+            LL.mark_pending(ws)
             lb.synchronize_and_check()
     finally:
         LL.check(lib.lact_set_wait_limit_ns(0), "lact_set_wait_limit_ns")  # back to the default
