@@ -219,6 +219,16 @@ int lact_qkv_prologue(const void *xq, const void *xk, const void *xv, int64_t ld
                       int64_t bs_q, int64_t bs_k, int64_t bs_v, void *q, void *k, void *v, int64_t b, int64_t s,
                       int64_t n_heads, int64_t d, int32_t qkv_silu, int32_t v_silu, void *stream);
 
+/* The same pass followed by the rotary position embedding the layer applies to fast q and k when `ttt_nope` is off
+ * (layer_lact_swiglu.py:417-446: heads merged back, re-split into attention heads of rope_head_dim features, rotated by
+ * fla.modules.RotaryEmbedding in its non-interleaved layout, split into fast-weight heads again).  cos, sin: bf16
+ * [n_positions][rope_head_dim / 2] (the module's cached tables, in the activations' dtype); token t of every sequence
+ * uses row seqlen_offset + t.  rope_head_dim: a power of two in [32, 1024] that divides d.  v is not rotated. */
+int lact_qkv_prologue_rope(const void *xq, const void *xk, const void *xv, int64_t ld_q, int64_t ld_k, int64_t ld_v,
+                           int64_t bs_q, int64_t bs_k, int64_t bs_v, void *q, void *k, void *v, int64_t b, int64_t s,
+                           int64_t n_heads, int64_t d, int32_t qkv_silu, int32_t v_silu, const void *cos, const void *sin,
+                           int64_t rope_head_dim, int64_t n_positions, int64_t seqlen_offset, void *stream);
+
 /* Per-token learning rates and momentum of the LLM layer (layer_lact_swiglu.py:463-480, 245-249):
  * lr = softplus(float(lr_proj) + base_lr_inv), lr_proj [b][s][n_heads * 3] (row stride proj_ld) -> lr0, lr1, lr2
  * fp32 [(b n_heads)][s]; momentum = float(sigmoid(logits) rounded to the logits' dtype), logits [b][s][n_heads]

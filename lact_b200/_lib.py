@@ -73,6 +73,9 @@ def _declare(lib: C.CDLL) -> None:
     lib.lact_bmm2_strided_bf16.argtypes = [vp, i32, i64, i64, vp, i32, i64, i64, vp, i32, i64, i64, vp, i32, i64, i64, vp,
                                            i32, i64, i64, i32, i64, i64, i64, i64, vp, vp]
     lib.lact_qkv_prologue.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, vp, vp, vp, i64, i64, i64, i64, i32, i32, vp]
+    lib.lact_qkv_prologue_rope.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, vp, vp, vp, i64, i64, i64, i64, i32, i32,
+                                           vp, vp, i64, i64, i64, vp]
+    lib.lact_qkv_prologue_rope.restype = C.c_int
     lib.lact_lr_prologue.argtypes = [vp, i32, i64, f32, vp, i32, i64, vp, vp, vp, vp, i64, i64, i64, vp]
     lib.lact_out_epilogue.argtypes = [vp, vp, vp, i64, vp, i64, vp, i64, i64, i64, i64, i64, f32, vp]
     lib.lact_swiglu_bwd_planes.argtypes = [vp, vp, vp, vp, vp, i32, f32, vp, vp, i64, i64, vp]

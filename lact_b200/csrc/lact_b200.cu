@@ -1328,9 +1328,11 @@ int lact_ns_trace_bwd(const void* du, void* dx0, int64_t B, int64_t R, int64_t C
   return LACT_OK;
 }
 
-int lact_qkv_prologue(const void* xq, const void* xk, const void* xv, int64_t ld_q, int64_t ld_k, int64_t ld_v,
-                      int64_t bs_q, int64_t bs_k, int64_t bs_v, void* q, void* k, void* v, int64_t b, int64_t s,
-                      int64_t n_heads, int64_t d, int32_t qkv_silu, int32_t v_silu, void* stream) {
+static int qkv_prologue_impl(const void* xq, const void* xk, const void* xv, int64_t ld_q, int64_t ld_k, int64_t ld_v,
+                             int64_t bs_q, int64_t bs_k, int64_t bs_v, void* q, void* k, void* v, int64_t b, int64_t s,
+                             int64_t n_heads, int64_t d, int32_t qkv_silu, int32_t v_silu, const void* cos,
+                             const void* sin, int64_t rope_head_dim, int64_t n_positions, int64_t seqlen_offset,
+                             void* stream) {
   if (!xq || !xk || !xv || !q || !k || !v) return LACT_ERR_NULL;
   LACT_TRY(check_device());
   if (b < 1 || s < 1 || n_heads < 1 || d < 8 || d > 1024 || (d % 8) != 0) return LACT_ERR_SHAPE;
@@ -1356,18 +1358,55 @@ int lact_qkv_prologue(const void* xq, const void* xk, const void* xv, int64_t ld
   a.silu[2] = (qkv_silu && v_silu) ? 1 : 0;
   a.l2norm[0] = a.l2norm[1] = 1;
   a.l2norm[2] = 0;
+  if (rope_head_dim != 0) {
+    if (!cos || !sin) return LACT_ERR_NULL;
+    // attention heads of a power-of-two size that tile every fast-weight head; positions inside the tables
+    if (rope_head_dim < 32 || rope_head_dim > 1024 || (rope_head_dim & (rope_head_dim - 1)) != 0 ||
+        (d % rope_head_dim) != 0 || seqlen_offset < 0 || seqlen_offset + s > n_positions)
+      return LACT_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(cos) & 15) != 0 || (reinterpret_cast<uintptr_t>(sin) & 15) != 0) return LACT_ERR_SHAPE;
+    a.cos = static_cast<const bf16*>(cos);
+    a.sin = static_cast<const bf16*>(sin);
+    a.rope_hd = static_cast<int32_t>(rope_head_dim);
+    a.pos0 = static_cast<int32_t>(seqlen_offset);
+  }
   const int64_t rows = b * s * n_heads;
   KernelScope scope(kClsOther, static_cast<cudaStream_t>(stream));
   const unsigned grid = static_cast<unsigned>(ceil_div(rows, 8));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  switch (ceil_div(d, 256)) {
-    case 1: qkv_prologue_kernel<1><<<grid, 256, 0, st>>>(a); break;
-    case 2: qkv_prologue_kernel<2><<<grid, 256, 0, st>>>(a); break;
-    case 3: qkv_prologue_kernel<3><<<grid, 256, 0, st>>>(a); break;
-    default: qkv_prologue_kernel<4><<<grid, 256, 0, st>>>(a); break;
+  if (a.rope_hd != 0) {
+    switch (ceil_div(d, 256)) {
+      case 1: qkv_prologue_kernel<1, true><<<grid, 256, 0, st>>>(a); break;
+      case 2: qkv_prologue_kernel<2, true><<<grid, 256, 0, st>>>(a); break;
+      case 3: qkv_prologue_kernel<3, true><<<grid, 256, 0, st>>>(a); break;
+      default: qkv_prologue_kernel<4, true><<<grid, 256, 0, st>>>(a); break;
+    }
+  } else {
+    switch (ceil_div(d, 256)) {
+      case 1: qkv_prologue_kernel<1, false><<<grid, 256, 0, st>>>(a); break;
+      case 2: qkv_prologue_kernel<2, false><<<grid, 256, 0, st>>>(a); break;
+      case 3: qkv_prologue_kernel<3, false><<<grid, 256, 0, st>>>(a); break;
+      default: qkv_prologue_kernel<4, false><<<grid, 256, 0, st>>>(a); break;
+    }
   }
   LACT_CUDA(cudaGetLastError());
   return LACT_OK;
+}
+
+int lact_qkv_prologue(const void* xq, const void* xk, const void* xv, int64_t ld_q, int64_t ld_k, int64_t ld_v,
+                      int64_t bs_q, int64_t bs_k, int64_t bs_v, void* q, void* k, void* v, int64_t b, int64_t s,
+                      int64_t n_heads, int64_t d, int32_t qkv_silu, int32_t v_silu, void* stream) {
+  return qkv_prologue_impl(xq, xk, xv, ld_q, ld_k, ld_v, bs_q, bs_k, bs_v, q, k, v, b, s, n_heads, d, qkv_silu, v_silu,
+                           nullptr, nullptr, 0, 0, 0, stream);
+}
+
+int lact_qkv_prologue_rope(const void* xq, const void* xk, const void* xv, int64_t ld_q, int64_t ld_k, int64_t ld_v,
+                           int64_t bs_q, int64_t bs_k, int64_t bs_v, void* q, void* k, void* v, int64_t b, int64_t s,
+                           int64_t n_heads, int64_t d, int32_t qkv_silu, int32_t v_silu, const void* cos, const void* sin,
+                           int64_t rope_head_dim, int64_t n_positions, int64_t seqlen_offset, void* stream) {
+  if (rope_head_dim == 0) return LACT_ERR_SHAPE;
+  return qkv_prologue_impl(xq, xk, xv, ld_q, ld_k, ld_v, bs_q, bs_k, bs_v, q, k, v, b, s, n_heads, d, qkv_silu, v_silu,
+                           cos, sin, rope_head_dim, n_positions, seqlen_offset, stream);
 }
 
 int lact_lr_prologue(const void* lr_proj, int32_t proj_dtype, int64_t proj_ld, float base_lr_inv, const void* mom_logits,

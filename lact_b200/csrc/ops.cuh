@@ -1018,6 +1018,13 @@ struct PrologueArgs {
   int32_t b, s, n_h, d;
   int32_t silu[3];       // apply SiLU to q / k / v
   int32_t l2norm[3];     // per-head l2 norm (q and k in the reference layer)
+  // rotary position embedding on q and k after the l2 norm (layer_lact_swiglu.py:417-446), or rope_hd = 0 for none.
+  // The merged feature axis (n_h * d) is cut into attention heads of rope_hd features (a power of two, 32..1024,
+  // dividing d); within each, feature j < rope_hd / 2 pairs with j + rope_hd / 2 (non-interleaved layout):
+  //   y[j] = x[j] cos[p][j] - x[j + hd/2] sin[p][j],   y[j + hd/2] = x[j] sin[p][j] + x[j + hd/2] cos[p][j]
+  // in fp32 from the bf16 inputs, rounded once (the arithmetic of the rotary kernel the reference calls).
+  const bf16 *cos, *sin;  // [positions][rope_hd / 2], bf16 (the reference caches them in the activations' dtype)
+  int32_t rope_hd, pos0;  // position of token 0
 };
 
 // One warp per (batch, token, head): y = silu(x) rounded to bf16, then y / (bf16(||y||) + 1e-5) with the norm, the
@@ -1025,8 +1032,9 @@ struct PrologueArgs {
 // (layer_lact_swiglu.py:404-414, ttt_operation.py:19-26); rows are written head-major, so the head split costs no
 // extra pass.  d <= 1024, a multiple of 8.
 // NCH = ceil(d / 256): 16-byte chunks per lane (the register footprint, hence the occupancy, follows the head size).
-template <int NCH>
-__global__ void __launch_bounds__(256, NCH <= 2 ? 8 : 4) qkv_prologue_kernel(const PrologueArgs a) {
+// ROPE: the rotary variant (more registers: compiled separately so that the plain pass keeps its occupancy).
+template <int NCH, bool ROPE>
+__global__ void __launch_bounds__(256, ROPE ? (NCH <= 2 ? 4 : 2) : (NCH <= 2 ? 8 : 4)) qkv_prologue_kernel(const PrologueArgs a) {
   const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int64_t rows = static_cast<int64_t>(a.b) * a.s * a.n_h;
   if (row >= rows) return;
@@ -1043,6 +1051,8 @@ __global__ void __launch_bounds__(256, NCH <= 2 ? 8 : 4) qkv_prologue_kernel(con
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {
       const int col = (c * 32 + lane) * 8;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) y[c][i] = 0.f;
       if (col < a.d) {
         const uint4 u = *reinterpret_cast<const uint4*>(src + col);
         const uint32_t w[4] = {u.x, u.y, u.z, u.w};
@@ -1065,6 +1075,50 @@ __global__ void __launch_bounds__(256, NCH <= 2 ? 8 : 4) qkv_prologue_kernel(con
     if (a.l2norm[t]) {
       ss = warp_sum(ss);
       inv_den = 1.f / bf16_round(bf16_round(sqrtf(ss)) + 1e-5f);
+    }
+    if (ROPE && t < 2) {
+      // the normalised row, rounded to bf16 as the reference's l2_norm returns it, is rotated in registers: the
+      // partner of a feature sits rope_hd / 2 columns away, i.e. rope_hd / 16 lanes away (same 16-byte chunk index)
+      // or, from rope_hd = 512 up, rope_hd / 512 chunks away in the same lane
+      const int half = a.rope_hd >> 1;
+      const int64_t trow = static_cast<int64_t>(a.pos0 + tok) * half;
+#pragma unroll
+      for (int c = 0; c < NCH; ++c)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) y[c][i] = bf16_round(y[c][i] * inv_den);
+      float other[NCH][8];
+#pragma unroll
+      for (int c = 0; c < NCH; ++c)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          if (half < 256) other[c][i] = __shfl_xor_sync(0xFFFFFFFFu, y[c][i], half >> 3);
+          else other[c][i] = y[(c ^ (half >> 8)) < NCH ? (c ^ (half >> 8)) : c][i];
+        }
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        const int col = (c * 32 + lane) * 8;
+        if (col < a.d) {
+          const int j = (static_cast<int>(h) * a.d + col) % a.rope_hd;  // column inside its attention head
+          const bool first = j < half;
+          const uint4 cu = *reinterpret_cast<const uint4*>(a.cos + trow + (first ? j : j - half));
+          const uint4 su = *reinterpret_cast<const uint4*>(a.sin + trow + (first ? j : j - half));
+          const uint32_t cw[4] = {cu.x, cu.y, cu.z, cu.w}, sw[4] = {su.x, su.y, su.z, su.w};
+          uint4 u;
+          uint32_t* w = reinterpret_cast<uint32_t*>(&u);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float c0 = __uint_as_float(cw[i] << 16), c1 = __uint_as_float(cw[i] & 0xFFFF0000u);
+            const float s0 = __uint_as_float(sw[i] << 16), s1 = __uint_as_float(sw[i] & 0xFFFF0000u);
+            const float x0 = y[c][2 * i], x1 = y[c][2 * i + 1], p0 = other[c][2 * i], p1 = other[c][2 * i + 1];
+            // first half: x cos - partner sin; second half: partner sin + x cos
+            const float r0 = first ? __fsub_rn(__fmul_rn(x0, c0), __fmul_rn(p0, s0)) : __fadd_rn(__fmul_rn(p0, s0), __fmul_rn(x0, c0));
+            const float r1 = first ? __fsub_rn(__fmul_rn(x1, c1), __fmul_rn(p1, s1)) : __fadd_rn(__fmul_rn(p1, s1), __fmul_rn(x1, c1));
+            w[i] = pack_bf16x2(r0, r1);
+          }
+          *reinterpret_cast<uint4*>(a.out[t] + out_off + col) = u;
+        }
+      }
+      continue;
     }
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {

@@ -1,13 +1,75 @@
 """Row-wise stages of the LaCT layer around the chunk recurrence (the layer's own code,
 lact_llm/lact_model/layer_lact_swiglu.py, is outside this package; these are the passes over
-[b, s, n_h * d] that sit directly on the recurrence's inputs)."""
+[b, s, n_h * d] that sit directly on the recurrence's inputs and output).
+
+Forward: one fused CUDA pass each.  Backward (training): each pass is an autograd Function whose backward
+re-evaluates the same formula with plain PyTorch operations in fp32 on the saved inputs and differentiates that
+(several elementwise passes instead of one; the forward values the rest of the graph sees are the fused kernel's)."""
 from __future__ import annotations
 
+import math
+from typing import Optional, Tuple
+
 import torch
+import torch.nn.functional as F
 
 from . import _lib as L
 
 BF16 = torch.bfloat16
+
+
+def _heads(t: torch.Tensor, n_h: int) -> torch.Tensor:
+    b, s, nd = t.shape
+    return t.reshape(b, s, n_h, nd // n_h).permute(0, 2, 1, 3).reshape(b * n_h, s, nd // n_h)
+
+
+def _unheads(t: torch.Tensor, n_h: int) -> torch.Tensor:
+    B, s, d = t.shape
+    return t.reshape(B // n_h, n_h, s, d).permute(0, 2, 1, 3).reshape(B // n_h, s, n_h * d)
+
+
+def _eager_qkv(xq, xk, xv, n_h, qkv_silu, v_silu, rope):
+    """fp32 restatement of the pass (layer_lact_swiglu.py:399-446), differentiable."""
+    def one(x, silu, norm, rot):
+        y = _heads(x.float(), n_h)
+        if silu:
+            y = F.silu(y)
+        if norm:
+            y = y / (y.norm(dim=-1, keepdim=True) + 1e-5)
+        if rot and rope is not None:
+            cos, sin, hd, off = rope
+            s = y.shape[1]
+            m = _unheads(y, n_h)
+            b, _, nd = m.shape
+            m = m.reshape(b, s, nd // hd, hd)
+            c = cos[off:off + s].float()[:, None, :]
+            sn = sin[off:off + s].float()[:, None, :]
+            x1, x2 = m[..., :hd // 2], m[..., hd // 2:]
+            m = torch.cat([x1 * c - x2 * sn, x1 * sn + x2 * c], dim=-1).reshape(b, s, nd)
+            y = _heads(m, n_h)
+        return y
+    return one(xq, qkv_silu, True, True), one(xk, qkv_silu, True, True), one(xv, qkv_silu and v_silu, False, False)
+
+
+class _QkvPrologue(torch.autograd.Function):
+    """Forward: the fused kernel.  Backward: autograd through `_eager_qkv` on the saved projections."""
+    @staticmethod
+    def forward(ctx, xq, xk, xv, num_heads, qkv_silu, v_silu, cos, sin, rope_hd, offset):
+        ctx.save_for_backward(xq, xk, xv, *((cos, sin) if cos is not None else ()))
+        ctx.cfg = (num_heads, qkv_silu, v_silu, rope_hd, offset)
+        return _qkv_prologue_fwd(xq, xk, xv, num_heads, qkv_silu, v_silu, cos, sin, rope_hd, offset)
+
+    @staticmethod
+    def backward(ctx, dq, dk, dv):
+        saved = ctx.saved_tensors
+        xq, xk, xv = saved[:3]
+        n_h, qkv_silu, v_silu, rope_hd, offset = ctx.cfg
+        rope = (saved[3], saved[4], rope_hd, offset) if len(saved) == 5 else None
+        with torch.enable_grad():
+            leaves = [t.detach().float().requires_grad_(True) for t in (xq, xk, xv)]
+            outs = _eager_qkv(*leaves, n_h, qkv_silu, v_silu, rope)
+            g = torch.autograd.grad(outs, leaves, [t.float() for t in (dq, dk, dv)])
+        return (*[gi.to(x.dtype) for gi, x in zip(g, (xq, xk, xv))], None, None, None, None, None, None, None)
 
 
 def _rows(t: torch.Tensor, name: str) -> torch.Tensor:
@@ -18,32 +80,97 @@ def _rows(t: torch.Tensor, name: str) -> torch.Tensor:
     return t
 
 
-def qkv_prologue(xq: torch.Tensor, xk: torch.Tensor, xv: torch.Tensor, num_heads: int, qkv_silu: bool = True,
-                 no_v_silu: bool = False):
-    """fast_q, fast_k, fast_v of layer_lact_swiglu.py:399-414 (the `ttt_nope` branch) in one pass:
-    `[b, s, (n_h d)] -> [(b n_h), s, d]`, SiLU on q, k (and v unless `no_v_silu`), per-head l2_norm of q and k
-    (ttt_operation.py:19-26).  Inputs may be views of a fused projection."""
-    if not (xq.is_cuda and xk.is_cuda and xv.is_cuda):
-        raise ValueError("qkv_prologue needs CUDA tensors (there is no CPU implementation)")
+def rotary_tables(head_dim: int, n_positions: int, base: float = 500000.0, device=None, dtype=BF16):
+    """cos / sin tables [n_positions, head_dim / 2] as fla.modules.RotaryEmbedding(dim=head_dim, base=rope_theta)
+    caches them (fp32 inverse frequencies and positions, result cast to the activations' dtype)."""
+    inv_freq = 1.0 / (base ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=device) / head_dim))
+    freqs = torch.outer(torch.arange(n_positions, dtype=torch.float32, device=device), inv_freq)
+    return torch.cos(freqs).to(dtype), torch.sin(freqs).to(dtype)
+
+
+def _qkv_prologue_fwd(xq, xk, xv, num_heads, qkv_silu, v_silu, cos, sin, rope_hd, offset):
     xq, xk, xv = _rows(xq, "xq"), _rows(xk, "xk"), _rows(xv, "xv")
-    assert xq.shape == xk.shape == xv.shape
     b, s, nd = xq.shape
-    assert nd % num_heads == 0
     d = nd // num_heads
     q, k, v = (torch.empty(b * num_heads, s, d, dtype=BF16, device=xq.device) for _ in range(3))
+    lib = L.lib()
     with torch.cuda.device(xq.device):
-        L.check(L.lib().lact_qkv_prologue(xq.data_ptr(), xk.data_ptr(), xv.data_ptr(), xq.stride(1), xk.stride(1),
+        if cos is None:
+            L.check(lib.lact_qkv_prologue(xq.data_ptr(), xk.data_ptr(), xv.data_ptr(), xq.stride(1), xk.stride(1),
                                           xv.stride(1), xq.stride(0), xk.stride(0), xv.stride(0), q.data_ptr(),
                                           k.data_ptr(), v.data_ptr(), b, s, num_heads, d, int(bool(qkv_silu)),
-                                          int(not no_v_silu), L.stream_ptr()), "lact_qkv_prologue")
+                                          int(bool(v_silu)), L.stream_ptr()), "lact_qkv_prologue")
+        else:
+            L.check(lib.lact_qkv_prologue_rope(xq.data_ptr(), xk.data_ptr(), xv.data_ptr(), xq.stride(1), xk.stride(1),
+                                               xv.stride(1), xq.stride(0), xk.stride(0), xv.stride(0), q.data_ptr(),
+                                               k.data_ptr(), v.data_ptr(), b, s, num_heads, d, int(bool(qkv_silu)),
+                                               int(bool(v_silu)), cos.data_ptr(), sin.data_ptr(), int(rope_hd),
+                                               cos.shape[0], int(offset), L.stream_ptr()), "lact_qkv_prologue_rope")
     return q, k, v
 
 
+def qkv_prologue(xq: torch.Tensor, xk: torch.Tensor, xv: torch.Tensor, num_heads: int, qkv_silu: bool = True,
+                 no_v_silu: bool = False, rotary: Optional[Tuple[torch.Tensor, torch.Tensor, int]] = None,
+                 seqlen_offset: int = 0):
+    """fast_q, fast_k, fast_v of layer_lact_swiglu.py:399-446 in one pass: `[b, s, (n_h d)] -> [(b n_h), s, d]`, SiLU
+    on q, k (and v unless `no_v_silu`), per-head l2_norm of q and k (ttt_operation.py:19-26) and, when `rotary` =
+    (cos, sin, attention_head_dim) is given (`ttt_nope` off), the rotary embedding of q and k over attention heads of
+    that size (tables as `rotary_tables` / fla.modules.RotaryEmbedding build them, bf16 [positions, head_dim / 2]).
+    Inputs may be views of a fused projection.  Differentiable (see the module docstring)."""
+    if not (xq.is_cuda and xk.is_cuda and xv.is_cuda):
+        raise ValueError("qkv_prologue needs CUDA tensors (there is no CPU implementation)")
+    assert xq.shape == xk.shape == xv.shape and xq.dim() == 3 and xq.shape[2] % num_heads == 0
+    cos = sin = None
+    rope_hd = 0
+    if rotary is not None:
+        cos, sin, rope_hd = rotary
+        assert cos.dtype == BF16 and sin.dtype == BF16 and cos.shape == sin.shape and cos.shape[1] * 2 == rope_hd
+        cos, sin = cos.contiguous(), sin.contiguous()
+    if torch.is_grad_enabled() and any(t.requires_grad for t in (xq, xk, xv)):
+        return _QkvPrologue.apply(xq, xk, xv, num_heads, bool(qkv_silu), not no_v_silu, cos, sin, int(rope_hd),
+                                  int(seqlen_offset))
+    return _qkv_prologue_fwd(xq, xk, xv, num_heads, bool(qkv_silu), not no_v_silu, cos, sin, int(rope_hd), int(seqlen_offset))
+
+
+class _LrPrologue(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, lr_proj, momentum_logits, num_heads, base_lr):
+        ctx.save_for_backward(lr_proj, *((momentum_logits,) if momentum_logits is not None else ()))
+        ctx.cfg = (num_heads, base_lr)
+        outs = _lr_prologue_fwd(lr_proj, num_heads, base_lr, momentum_logits)
+        return outs if outs[3] is not None else (outs[0], outs[1], outs[2])
+
+    @staticmethod
+    def backward(ctx, *grads):
+        saved = ctx.saved_tensors
+        n_h, base_lr = ctx.cfg
+        base_lr_inv = base_lr + math.log(-math.expm1(-base_lr))
+        with torch.enable_grad():
+            p = saved[0].detach().float().requires_grad_(True)
+            lr = _heads(F.softplus(p + base_lr_inv), n_h)  # [(b n_h), s, 3]
+            outs, leaves = [lr[..., i:i + 1] for i in range(3)], [p]
+            if len(saved) == 2:
+                m = saved[1].detach().float().requires_grad_(True)
+                outs.append(_heads(torch.sigmoid(m), n_h))
+                leaves.append(m)
+            g = torch.autograd.grad(outs, leaves, [gi.float() for gi in grads[:len(outs)]])
+        gm = g[1].to(saved[1].dtype) if len(saved) == 2 else None
+        return g[0].to(saved[0].dtype), gm, None, None
+
+
 def lr_prologue(lr_proj: torch.Tensor, num_heads: int, base_lr: float, momentum_logits: torch.Tensor = None):
+    """fw_lr1, fw_lr2, fw_lr3 (and momentum) of layer_lact_swiglu.py:463-480; see `_lr_prologue_fwd`.  Differentiable
+    with respect to the projections (see the module docstring)."""
+    if torch.is_grad_enabled() and (lr_proj.requires_grad or (momentum_logits is not None and momentum_logits.requires_grad)):
+        outs = _LrPrologue.apply(lr_proj, momentum_logits, num_heads, float(base_lr))
+        return (outs[0], outs[1], outs[2], outs[3] if len(outs) == 4 else None)
+    return _lr_prologue_fwd(lr_proj, num_heads, base_lr, momentum_logits)
+
+
+def _lr_prologue_fwd(lr_proj: torch.Tensor, num_heads: int, base_lr: float, momentum_logits: torch.Tensor = None):
     """fw_lr1, fw_lr2, fw_lr3 (and momentum) of layer_lact_swiglu.py:463-480: softplus(lr_proj.float() +
     inv_softplus(base_lr)) split per head into three fp32 [(b n_h), s, 1] tensors; `momentum_logits` is the output of
     the momentum Linear BEFORE its Sigmoid ([b, s, n_h]); the result is sigmoid(.) in the logits' dtype, as float."""
-    import math
     if not lr_proj.is_cuda:
         raise ValueError("lr_prologue needs CUDA tensors (there is no CPU implementation)")
     assert lr_proj.dim() == 3 and lr_proj.shape[2] == 3 * num_heads
@@ -72,8 +199,48 @@ def lr_prologue(lr_proj: torch.Tensor, num_heads: int, base_lr: float, momentum_
     return outs[0], outs[1], outs[2], mom
 
 
+def _eager_out(fw_x, w, n_h, scale_proj, o, eps):
+    x = fw_x.float()
+    y = x * torch.rsqrt(x.square().mean(dim=-1, keepdim=True) + eps) * w.float()
+    if scale_proj is not None:
+        y = y * _heads(F.silu(scale_proj.float()), n_h)
+    y = _unheads(y, n_h)
+    return y + o.float() if o is not None else y
+
+
+class _OutEpilogue(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, fw_x, norm_weight, scale_proj, o, num_heads, eps):
+        ctx.save_for_backward(fw_x, norm_weight, *((scale_proj,) if scale_proj is not None else ()))
+        ctx.cfg = (num_heads, eps, scale_proj is not None, o is not None)
+        return _out_epilogue_fwd(fw_x, norm_weight, num_heads, scale_proj, o, eps)
+
+    @staticmethod
+    def backward(ctx, dout):
+        saved = ctx.saved_tensors
+        n_h, eps, has_gate, has_o = ctx.cfg
+        with torch.enable_grad():
+            x = saved[0].detach().float().requires_grad_(True)
+            w = saved[1].detach().float().requires_grad_(True)
+            gate = saved[2].detach().float().requires_grad_(True) if has_gate else None
+            leaves = [x, w] + ([gate] if has_gate else [])
+            g = torch.autograd.grad(_eager_out(x, w, n_h, gate, None, eps), leaves, dout.float())
+        return (g[0].to(saved[0].dtype), g[1].to(saved[1].dtype), g[2].to(saved[2].dtype) if has_gate else None,
+                dout if has_o else None, None, None)
+
+
 def out_epilogue(fw_x: torch.Tensor, norm_weight: torch.Tensor, num_heads: int, scale_proj: torch.Tensor = None,
                  o: torch.Tensor = None, eps: float = 1e-5) -> torch.Tensor:
+    """`o + merge_heads(ttt_norm(fw_x) * silu(scale_proj))` of layer_lact_swiglu.py:556-568 in one pass; see
+    `_out_epilogue_fwd`.  Differentiable with respect to fw_x, the norm weight, scale_proj and o (module docstring)."""
+    ts = [t for t in (fw_x, norm_weight, scale_proj, o) if t is not None]
+    if torch.is_grad_enabled() and any(t.requires_grad for t in ts):
+        return _OutEpilogue.apply(fw_x, norm_weight, scale_proj, o, num_heads, float(eps))
+    return _out_epilogue_fwd(fw_x, norm_weight, num_heads, scale_proj, o, eps)
+
+
+def _out_epilogue_fwd(fw_x: torch.Tensor, norm_weight: torch.Tensor, num_heads: int, scale_proj: torch.Tensor = None,
+                      o: torch.Tensor = None, eps: float = 1e-5) -> torch.Tensor:
     """`o + merge_heads(ttt_norm(fw_x) * silu(scale_proj))` of layer_lact_swiglu.py:556-568 in one pass.
     fw_x: [(b n_h), s, d] bf16 (output of the recurrence); norm_weight: [d]; scale_proj (the output of
     `ttt_scale_proj`, before its SiLU) and o (attention output): [b, s, n_h * d] bf16 or None."""

@@ -694,6 +694,51 @@ def qkv_prologue(xq: torch.Tensor, xk: torch.Tensor, xv: torch.Tensor, n_heads: 
     return l2n(q).contiguous(), l2n(k).contiguous(), v.contiguous()
 
 
+def rotary_tables(head_dim: int, n_positions: int, base: float = 500000.0, dtype=BF16):
+    """cos / sin tables of `fla.modules.RotaryEmbedding(dim=head_dim, base=rope_theta)` (flash-linear-attention 0.5.1,
+    `_update_cos_sin_cache`): inv_freq = 1 / base^(arange(0, dim, 2) / dim) in fp32, positions in fp32, outer product,
+    cos / sin cast to the activations' dtype.  The reference layer builds it with base = rope_theta (default 500000,
+    lact_llm/lact_model/layer_lact_swiglu.py:141, 170).  Returns (cos, sin), each [n_positions, head_dim / 2]."""
+    inv_freq = 1.0 / (base ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))
+    freqs = torch.outer(torch.arange(n_positions, dtype=torch.float32), inv_freq)
+    return torch.cos(freqs).to(dtype), torch.sin(freqs).to(dtype)
+
+
+def rotary(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, seqlen_offset: int = 0, policy: str = "ref"):
+    """Rotary embedding of x [b, s, heads, head_dim] in the non-interleaved layout (first half pairs with second half).
+    policy "ref": the arithmetic of fla's own PyTorch restatement `rotary_embedding_ref` (x * cos + rotate_half(x) *
+    sin in x's dtype: every product and the sum rounded); policy "fused": fp32 products and sum from the bf16 inputs,
+    one rounding (what a fused kernel does; the reference's Triton kernel computes in fp32 as well)."""
+    s, hd = x.shape[1], x.shape[-1]
+    c = cos[seqlen_offset:seqlen_offset + s]
+    sn = sin[seqlen_offset:seqlen_offset + s]
+    if policy == "ref":
+        c2 = torch.cat([c, c], dim=-1)[:, None, :]
+        s2 = torch.cat([sn, sn], dim=-1)[:, None, :]
+        x1, x2 = x[..., :hd // 2], x[..., hd // 2:]
+        return x * c2 + torch.cat([-x2, x1], dim=-1) * s2
+    xf, cf, sf = x.float(), c.float()[:, None, :], sn.float()[:, None, :]
+    x1, x2 = xf[..., :hd // 2], xf[..., hd // 2:]
+    return torch.cat([x1 * cf - x2 * sf, x1 * sf + x2 * cf], dim=-1).to(x.dtype)
+
+
+def qkv_prologue_rope(xq, xk, xv, n_heads: int, rope_head_dim: int, cos, sin, seqlen_offset: int = 0,
+                      qkv_silu: bool = True, v_silu: bool = True, policy: str = "ref"):
+    """`qkv_prologue` followed by the rotary embedding of fast q and k as the layer applies it when `ttt_nope` is off
+    (lact_llm/lact_model/layer_lact_swiglu.py:417-446): fast-weight heads merged back to [b, s, n_h * d], re-split
+    into attention heads of `rope_head_dim` features, rotated, and split into fast-weight heads again."""
+    q, k, v = qkv_prologue(xq, xk, xv, n_heads, qkv_silu, v_silu)
+    b, s, nd = xq.shape
+    d = nd // n_heads
+
+    def rot(t):
+        merged = t.reshape(b, n_heads, s, d).permute(0, 2, 1, 3).reshape(b, s, nd)
+        r = rotary(merged.reshape(b, s, nd // rope_head_dim, rope_head_dim), cos, sin, seqlen_offset, policy)
+        return r.reshape(b, s, n_heads, d).permute(0, 2, 1, 3).reshape(b * n_heads, s, d).contiguous()
+
+    return rot(q), rot(k), v
+
+
 def lr_prologue(lr_proj: torch.Tensor, n_heads: int, base_lr: float, momentum_logits: Optional[torch.Tensor] = None):
     """Per-token learning rates and momentum of the LLM layer (lact_llm/lact_model/layer_lact_swiglu.py:463-480 and
     245-249): lr = softplus(lr_proj.float() + inv_softplus(base_lr)) ([b, s, n_h * 3], three per head), split into

@@ -159,6 +159,11 @@ def subop_cases():
 PROLOGUE_OUT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "layer_prologue.pt")
 
 
+def fla_version():
+    import fla
+    return fla.__version__
+
+
 def prologue_cases():
     """Fast-weight input prologue of the LLM layer (lact_llm/lact_model/layer_lact_swiglu.py:399-414, the
     `ttt_nope` branch): head split, SiLU on q, k (and v), per-head `l2_norm` of q, k -- executed with the
@@ -180,6 +185,29 @@ def prologue_cases():
         res[name] = dict(spec=dict(b=b, s=s, n_h=n_h, d=d, v_silu=v_silu, seed=seed),
                          q=fq.contiguous(), k=fk.contiguous(), v=fv.contiguous())
         print("prologue", name, tuple(fq.shape), fq.dtype)
+    # rotary embedding of fast q, k (layer_lact_swiglu.py:417-446): the layer's own module fla.modules.RotaryEmbedding
+    # supplies the cos / sin tables (`_update_cos_sin_cache`, pure PyTorch); its rotation kernel is Triton-only, so
+    # fla's PyTorch restatement `rotary_embedding_ref` of the same file is executed on the reference's l2-normed q, k
+    from fla.modules import RotaryEmbedding
+    from fla.modules.rotary import rotary_embedding_ref
+    for name, (b, s, n_h, d, hd, off, seed) in dict(rope_a=(2, 37, 4, 64, 64, 0, 230), rope_b=(1, 130, 2, 384, 128, 5, 231),
+                                                     rope_c=(2, 16, 2, 128, 32, 3, 232)).items():
+        g = torch.Generator().manual_seed(seed)
+        xq, xk = (torch.randn(b, s, n_h * d, generator=g).to(BF16) * 1.5 for _ in range(2))
+        fq, fk = (l2_norm(F.silu(rearrange(t, "b s (n_h d) -> (b n_h) s d", n_h=n_h))) for t in (xq, xk))
+        rot = RotaryEmbedding(dim=hd, base=500000.0)
+        rot._update_cos_sin_cache(off + s, device=xq.device, dtype=BF16)
+        cos, sin = rot._cos_cached[off:off + s], rot._sin_cached[off:off + s]
+        outs = []
+        for t in (fq, fk):
+            m = rearrange(t, "(b n_h) s d -> b s (n_h d)", n_h=n_h)
+            m = rearrange(m, "b s (a hd) -> b s a hd", hd=hd)
+            m = rotary_embedding_ref(m, cos, sin)
+            m = rearrange(m, "b s a hd -> b s (a hd)")
+            outs.append(rearrange(m, "b s (n_h d) -> (b n_h) s d", n_h=n_h).contiguous())
+        res[name] = dict(spec=dict(b=b, s=s, n_h=n_h, d=d, hd=hd, off=off, seed=seed), q=outs[0], k=outs[1],
+                         cos=rot._cos_cached.clone(), sin=rot._sin_cached.clone(), fla=fla_version())
+        print("rope", name, tuple(outs[0].shape), outs[0].dtype)
     # learning rates and momentum of the same layer (layer_lact_swiglu.py:463-480, 245-249): softplus of the fp32
     # projection plus inv_softplus(base_lr), split per head into three [(b n_h), s, 1] tensors; momentum = Sigmoid
     # (inside momentum_proj, bf16 under autocast) then .float(), head-merged

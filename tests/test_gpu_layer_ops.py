@@ -62,7 +62,7 @@ def test_qkv_prologue_reference_fixtures_and_fused_projection_views(lb, orc):
     blob = torch.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "layer_prologue.pt"),
                       map_location="cpu", weights_only=False)
     for name, case in blob.items():
-        if name.startswith(("lr_", "out_")):
+        if name.startswith(("lr_", "out_", "rope_")):
             continue
         sp = case["spec"]
         g = torch.Generator().manual_seed(sp["seed"])
@@ -149,3 +149,80 @@ def test_out_epilogue_reference_fixtures(lb, orc):
         frac, worst = _ulp_report(got, case["out"])
         assert worst <= 4.0 and frac <= 0.03, (name, frac, worst)
 
+
+
+@pytest.mark.parametrize("b,s,n_h,d,hd,off", [(2, 37, 4, 64, 64, 0), (1, 130, 2, 384, 128, 5), (2, 16, 2, 128, 32, 3),
+                                              (1, 9, 1, 512, 256, 0), (1, 7, 1, 1024, 512, 2), (1, 6, 2, 256, 128, 1)])
+def test_qkv_prologue_with_rotary_embedding(lb, orc, b, s, n_h, d, hd, off):
+    """Rotary embedding of fast q, k fused into the pass (layer_lact_swiglu.py:417-446): against the oracle's fused
+    (fp32, single rounding) arithmetic within the band of the plain pass, and against the restatement of fla's own
+    PyTorch rotation (three bf16 roundings) within two more ulps at the inputs' scale; v is untouched by the rotation."""
+    from lact_b200 import layer_ops
+    g = torch.Generator().manual_seed(11)
+    xq, xk, xv = (torch.randn(b, s, n_h * d, generator=g).to(BF16) * 1.5 for _ in range(3))
+    cos, sin = orc.rotary_tables(hd, off + s + 3)
+    dcos, dsin = layer_ops.rotary_tables(hd, off + s + 3, device="cuda")
+    assert torch.equal(dcos.cpu(), cos) or float((dcos.cpu().float() - cos.float()).abs().max()) <= 2.0 ** -8
+    q, k, v = layer_ops.qkv_prologue(xq.cuda(), xk.cuda(), xv.cuda(), n_h, rotary=(cos.cuda(), sin.cuda(), hd),
+                                     seqlen_offset=off)
+    fq, fk, fv = orc.qkv_prologue_rope(xq, xk, xv, n_h, hd, cos, sin, off, policy="fused")
+    rq, rk, _ = orc.qkv_prologue_rope(xq, xk, xv, n_h, hd, cos, sin, off, policy="ref")
+    for got, fused, ref, what in ((q, fq, rq, "q"), (k, fk, rk, "k")):
+        gf = got.float().cpu()
+        # a one-ulp difference of an l2-normed input (fast exponential, order of the row sum) rotates into both
+        # partners: measured against the scale of the row (|x| <= 1), not of the single element
+        scale = 2.0 ** -8
+        assert float((gf - fused.float()).abs().max()) <= 2 * scale, what
+        assert float(((gf - fused.float()).abs() > 0).float().mean()) <= 0.05, what
+        assert float((gf - ref.float()).abs().max()) <= 3 * scale, what
+    _check(v, fv, "v")
+    # the first token at offset 0 is not rotated (cos = 1, sin = 0)
+    if off == 0:
+        pq, _, _ = layer_ops.qkv_prologue(xq.cuda(), xk.cuda(), xv.cuda(), n_h)
+        assert torch.equal(q[:, 0], pq[:, 0])
+    # argument errors: head size that does not tile the fast-weight head, positions beyond the table
+    with pytest.raises(ValueError):
+        layer_ops.qkv_prologue(xq.cuda(), xk.cuda(), xv.cuda(), n_h, rotary=(cos.cuda(), sin.cuda(), hd),
+                               seqlen_offset=off + 10)
+
+
+def test_layer_passes_are_differentiable(lb, orc):
+    """Gradients of the three layer passes against autograd through the oracle's formulas in fp32."""
+    from lact_b200 import layer_ops
+    b, s, n_h, d, hd = 2, 24, 2, 128, 64
+    g = torch.Generator().manual_seed(12)
+    xs = [(torch.randn(b, s, n_h * d, generator=g) * 1.5).to(BF16) for _ in range(3)]
+    cos, sin = orc.rotary_tables(hd, s)
+    dO = [torch.randn(b * n_h, s, d, generator=g) for _ in range(3)]
+    # reference gradients: fp32 autograd through the oracle (fused rounding policy has no roundings in fp32)
+    leaves = [t.float().clone().requires_grad_(True) for t in xs]
+    ref = torch.autograd.grad(orc.qkv_prologue_rope(*leaves, n_h, hd, cos.float(), sin.float(), 0, policy="fused"), leaves, dO)
+    cl = [t.cuda().clone().requires_grad_(True) for t in xs]
+    q, k, v = layer_ops.qkv_prologue(*cl, n_h, rotary=(cos.cuda(), sin.cuda(), hd))
+    torch.autograd.backward([q, k, v], [t.cuda().to(BF16) for t in dO])
+    for got, want, what in zip(cl, ref, ("dxq", "dxk", "dxv")):
+        assert got.grad is not None and got.grad.dtype == BF16
+        assert orc.rel_max(got.grad.float().cpu(), want) <= 2e-2 and orc.cosine(got.grad.float().cpu(), want) >= 0.999, what
+    # learning rates / momentum
+    proj = (torch.randn(b, s, n_h * 3, generator=g) * 2).to(BF16)
+    logit = (torch.randn(b, s, n_h, generator=g) * 2).to(BF16)
+    gl = [torch.randn(b * n_h, s, 1, generator=g) for _ in range(4)]
+    pl, ml = proj.float().clone().requires_grad_(True), logit.float().clone().requires_grad_(True)
+    ref = torch.autograd.grad(orc.lr_prologue(pl, n_h, 1e-2, ml), [pl, ml], gl)
+    cp, cm = proj.cuda().clone().requires_grad_(True), logit.cuda().clone().requires_grad_(True)
+    o4 = layer_ops.lr_prologue(cp, n_h, 1e-2, cm)
+    torch.autograd.backward(list(o4), [t.cuda() for t in gl])
+    assert orc.rel_max(cp.grad.float().cpu(), ref[0]) <= 1e-2 and orc.rel_max(cm.grad.float().cpu(), ref[1]) <= 1e-2
+    # output epilogue
+    fw_x = (torch.randn(b * n_h, s, d, generator=g) * 2).to(BF16)
+    w = 1.0 + 0.1 * torch.randn(d, generator=g)
+    sp, oa = torch.randn(b, s, n_h * d, generator=g).to(BF16), torch.randn(b, s, n_h * d, generator=g).to(BF16)
+    gout = torch.randn(b, s, n_h * d, generator=g)
+    L4 = [t.float().clone().requires_grad_(True) for t in (fw_x, w, sp, oa)]
+    ref = torch.autograd.grad(orc.out_epilogue(L4[0], L4[1], n_h, L4[2], L4[3]), L4, gout)
+    C4 = [t.cuda().clone().requires_grad_(True) for t in (fw_x, w, sp, oa)]
+    out = layer_ops.out_epilogue(C4[0], C4[1], n_h, C4[2], C4[3])
+    out.backward(gout.cuda().to(out.dtype))
+    for got, want, what in zip(C4, ref, ("d fw_x", "d weight", "d scale_proj", "d o")):
+        assert got.grad is not None, what
+        assert orc.rel_max(got.grad.float().cpu(), want) <= 2e-2 and orc.cosine(got.grad.float().cpu(), want) >= 0.999, what

@@ -106,7 +106,7 @@ def test_layer_prologue_matches_reference_outputs():
     blob = torch.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "layer_prologue.pt"),
                       map_location="cpu", weights_only=False)
     for name, case in blob.items():
-        if name.startswith(("lr_", "out_")):
+        if name.startswith(("lr_", "out_", "rope_")):
             continue
         sp = case["spec"]
         g = torch.Generator().manual_seed(sp["seed"])
@@ -114,6 +114,35 @@ def test_layer_prologue_matches_reference_outputs():
                       for _ in range(3))
         q, k, v = orc.qkv_prologue(xq, xk, xv, sp["n_h"], True, sp["v_silu"])
         assert torch.equal(q, case["q"]) and torch.equal(k, case["k"]) and torch.equal(v, case["v"]), name
+
+
+def test_rotary_prologue_matches_reference_outputs():
+    """`qkv_prologue_rope` against the fixtures written with the layer's own RotaryEmbedding tables and fla's PyTorch
+    restatement of its rotation (make_golden.py --prologue): the cos / sin tables and, with the `ref` rounding policy,
+    the rotated q and k are bit-exact; the fused (single-rounding) policy stays within one bf16 ulp of them."""
+    import os
+    import torch
+    from oracle import lact_oracle as orc
+    blob = torch.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "layer_prologue.pt"),
+                      map_location="cpu", weights_only=False)
+    names = [n for n in blob if n.startswith("rope_")]
+    assert len(names) == 3
+    for name in names:
+        case = blob[name]
+        sp = case["spec"]
+        g = torch.Generator().manual_seed(sp["seed"])
+        xq, xk = (torch.randn(sp["b"], sp["s"], sp["n_h"] * sp["d"], generator=g).to(torch.bfloat16) * 1.5
+                  for _ in range(2))
+        cos, sin = orc.rotary_tables(sp["hd"], sp["off"] + sp["s"])
+        assert torch.equal(cos, case["cos"]) and torch.equal(sin, case["sin"]), name
+        q, k, _ = orc.qkv_prologue_rope(xq, xk, xk, sp["n_h"], sp["hd"], cos, sin, sp["off"], policy="ref")
+        assert torch.equal(q, case["q"]) and torch.equal(k, case["k"]), name
+        qf, kf, _ = orc.qkv_prologue_rope(xq, xk, xk, sp["n_h"], sp["hd"], cos, sin, sp["off"], policy="fused")
+        for got, ref in ((qf, case["q"]), (kf, case["k"])):
+            ulp = torch.maximum(ref.float().abs(), torch.tensor(2.0 ** -126)).log2().floor().exp2() * 2.0 ** -7
+            # near a cancellation (x cos ~ partner sin) the two roundings of the eager arithmetic are not small
+            # relative to the result; against the scale of the inputs (|x| <= 1 after the l2 norm) they are
+            assert float(((got.float() - ref.float()).abs() / torch.maximum(ulp, torch.tensor(2.0 ** -10))).max()) <= 1.0, name
 
 
 def test_lr_prologue_matches_reference_outputs():
