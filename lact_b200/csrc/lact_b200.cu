@@ -594,11 +594,17 @@ int run_ns_iterations(const NsGroup* grp, int ngroups, int steps, int const_coef
 
 // Fused path: all iterations in one cooperative launch.  launch_ns_prepare must have run on the same groups
 // just before: it leaves the first iterates in grp[g].xa and clears the completion counters grp[g].done.
-template <int BT_MM, int BT_MN>
+// NITER = 2: iterates ping-pong between grp[g].xa / xb, one Gram / polynomial buffer.  NITER > 2 (steps <= NITER):
+// every iteration has its own buffers, `keep[g]` = {iterates (steps + 1) x [nmat][R][C] starting with the first
+// iterate, shifted Gram matrices steps x [nmat][m][m], polynomials likewise}.
+struct NsKeep {
+  bf16 *X, *A, *P;
+};
+template <int BT_MM, int BT_MN, int NITER>
 int launch_ns_fused(const NsGroup* grp, int ngroups, int steps, int const_coeffs, int32_t* status,
-                    cudaStream_t stream, int unscaled_first) {
-  using Args = NsFusedArgs<BT_MM, BT_MN>;
-  auto kernel = ns_fused_kernel<BT_MM, BT_MN>;
+                    cudaStream_t stream, int unscaled_first, const NsKeep* keep = nullptr, int coef_offset = 0) {
+  using Args = NsFusedArgs<BT_MM, BT_MN, NITER>;
+  auto kernel = ns_fused_kernel<BT_MM, BT_MN, NITER>;
   constexpr uint32_t smem = ns_fused_smem_bytes<BT_MM, BT_MN>();
   static_assert(smem <= 232448, "shared memory budget exceeded");
   static_assert(ns_fused_ring<BT_MM, BT_MN>() >= 2, "ring too shallow");
@@ -613,22 +619,35 @@ int launch_ns_fused(const NsGroup* grp, int ngroups, int steps, int const_coeffs
       if (dev < 64) configured[dev] = true;
     }
   }
-  Args args;
+  if (NITER > 2 && (keep == nullptr || steps > NITER)) return LACT_ERR_CONFIG;
+  // the argument block (a few KB per problem set) lives on the heap: it is copied at launch
+  std::vector<uint8_t> storage(sizeof(Args));
+  Args& args = *reinterpret_cast<Args*>(storage.data());
   std::memset(&args, 0, sizeof(args));
   int64_t max_tiles = 1;
   for (int g = 0; g < ngroups; ++g) {
     const NsGroup& G = grp[g];
-    for (int par = 0; par < 2; ++par) {
-      bf16* cur = par == 0 ? G.xa : G.xb;
-      bf16* nxt = par == 0 ? G.xb : G.xa;
-      LACT_TRY(wire_ns_group(G, cur, nxt, BT_MM, BT_MN, args.gram[par][g], args.poly[g], args.upd[par][g]));
+    const int64_t rc = static_cast<int64_t>(G.nmat) * G.R * G.C, mm = static_cast<int64_t>(G.nmat) * G.m * G.m;
+    for (int par = 0; par < NITER; ++par) {
+      NsGroup Gi = G;
+      bf16 *cur, *nxt;
+      if (NITER == 2) {
+        cur = par == 0 ? G.xa : G.xb;
+        nxt = par == 0 ? G.xb : G.xa;
+      } else {
+        cur = keep[g].X + rc * par;
+        nxt = keep[g].X + rc * (par + 1);
+        Gi.gram = keep[g].A + mm * par;
+        Gi.poly = keep[g].P + mm * par;
+      }
+      LACT_TRY(wire_ns_group(Gi, cur, nxt, BT_MM, BT_MN, args.gram[par][g], args.poly[par][g], args.upd[par][g]));
     }
     args.scale[g] = unscaled_first ? G.scale : nullptr;
     max_tiles = std::max<int64_t>(max_tiles, static_cast<int64_t>(G.nmat) * ceil_div(ns_upd_rows(G), kBM) *
                                                  ceil_div(ns_upd_cols(G), BT_MN) * ngroups);
   }
   for (int it = 0; it < steps; ++it) {
-    const float* co = const_coeffs ? kNsConst : kNsTuned[it];
+    const float* co = const_coeffs ? kNsConst : kNsTuned[it + coef_offset];
     args.coef[it][0] = co[0]; args.coef[it][1] = co[1]; args.coef[it][2] = co[2];
   }
   args.steps = steps;
@@ -662,13 +681,13 @@ int try_ns_fused(const NsGroup* grp, int ngroups, int steps, int const_coeffs, i
   };
   const int64_t want = static_cast<int64_t>(sm_count()) * 3 / 4;
   if (bt_mm == 192 && bt_mn == 192 && gram_tiles(192) >= want)
-    return launch_ns_fused<192, 192>(grp, ngroups, steps, const_coeffs, status, stream, unscaled_first);
+    return launch_ns_fused<192, 192, 2>(grp, ngroups, steps, const_coeffs, status, stream, unscaled_first);
   // (a 256-wide update tile leaves no room for a useful ring next to two staging tiles: 128 is used)
   const bool ok128 = (bt_mm == 192 && bt_mn == 192) || (bt_mm == 128 && (bt_mn == 128 || bt_mn == 256));
   if (ok128 && (gram_tiles(128) >= want || gram_tiles(64) == gram_tiles(128)))
-    return launch_ns_fused<128, 128>(grp, ngroups, steps, const_coeffs, status, stream, unscaled_first);
+    return launch_ns_fused<128, 128, 2>(grp, ngroups, steps, const_coeffs, status, stream, unscaled_first);
   if (ok128 || (bt_mm == 64 && bt_mn == 64))
-    return launch_ns_fused<64, 64>(grp, ngroups, steps, const_coeffs, status, stream, unscaled_first);
+    return launch_ns_fused<64, 64, 2>(grp, ngroups, steps, const_coeffs, status, stream, unscaled_first);
   return LACT_ERR_CONFIG;
 }
 
@@ -1274,14 +1293,31 @@ int lact_ns_trace_fwd(const void* g, int32_t g_dtype, void* x_out, int64_t B, in
   t.grp.xa = t.X;
   const void* srcs[2] = {g, g};
   LACT_TRY(launch_ns_prepare(&t.grp, 1, srcs, g_dtype == LACT_F32, 1, s));  // X[0] = normalised bf16(g)
-  for (int it = 0; it < steps; ++it) {
-    NsGroup gi = t.grp;
-    gi.xa = t.X + rc * it;
-    gi.xb = t.X + rc * (it + 1);
-    gi.gram = t.A + mm * it;
-    gi.poly = t.P + mm * it;
-    const bf16* res = nullptr;
-    LACT_TRY(run_ns_iterations(&gi, 1, 1, const_coeffs, &res, status_word, s, 0, const_coeffs ? 0 : it));
+  // all iterations in one dataflow launch that keeps every iterate (up to five: both coefficient schedules of the
+  // reference's drivers); longer constant-coefficient runs go iteration by iteration
+  int rc_f = LACT_ERR_CONFIG;
+  if (steps <= 5) {
+    const NsKeep keep{t.X, t.A, t.P};
+    int bt_mm = 0, bt_mn = 0;
+    ns_tile_widths(&t.grp, 1, &bt_mm, &bt_mn);
+    const int64_t gram_tiles = static_cast<int64_t>(t.grp.nmat) * ceil_div(t.grp.m, kBM) * ceil_div(t.grp.m, 192);
+    if (bt_mm == 192 && bt_mn == 192 && gram_tiles >= sm_count() * 3 / 4)
+      rc_f = launch_ns_fused<192, 192, 5>(&t.grp, 1, steps, const_coeffs, status_word, s, 0, &keep);
+    else if ((bt_mm == 192 && bt_mn == 192) || (bt_mm == 128 && (bt_mn == 128 || bt_mn == 256)))
+      rc_f = launch_ns_fused<128, 128, 5>(&t.grp, 1, steps, const_coeffs, status_word, s, 0, &keep);
+  }
+  if (rc_f == LACT_ERR_CONFIG) {
+    for (int it = 0; it < steps; ++it) {
+      NsGroup gi = t.grp;
+      gi.xa = t.X + rc * it;
+      gi.xb = t.X + rc * (it + 1);
+      gi.gram = t.A + mm * it;
+      gi.poly = t.P + mm * it;
+      const bf16* res = nullptr;
+      LACT_TRY(run_ns_iterations(&gi, 1, 1, const_coeffs, &res, status_word, s, 0, const_coeffs ? 0 : it));
+    }
+  } else {
+    LACT_TRY(rc_f);
   }
   LACT_CUDA(cudaMemcpyAsync(x_out, t.X + rc * steps, rc * 2, cudaMemcpyDeviceToDevice, s));
   return LACT_OK;

@@ -11,11 +11,14 @@
 
 namespace lact {
 
-template <int BT_MM, int BT_MN>
+// NITER sets of problems are held, iteration `it` uses set it % NITER: two sets for the plain iteration (the iterates
+// ping-pong between two buffers), one set per iteration when every iterate, shifted Gram matrix and polynomial is
+// kept for the backward pass (steps <= NITER then).
+template <int BT_MM, int BT_MN, int NITER = 2>
 struct NsFusedArgs {
-  GemmProblem<OpNs<BT_MM>> gram[2][2];  // [iteration parity][group]
-  GemmProblem<OpNs<BT_MM>> poly[2];     // [group]
-  GemmProblem<OpNs<BT_MN>> upd[2][2];   // [iteration parity][group]
+  GemmProblem<OpNs<BT_MM>> gram[NITER][2];  // [iteration % NITER][group]
+  GemmProblem<OpNs<BT_MM>> poly[NITER][2];
+  GemmProblem<OpNs<BT_MN>> upd[NITER][2];
   const float* scale[2];                // per group: [matrix] 1 / (||G|| + 1e-7) when the first iterate is unscaled
   float coef[16][3];                    // (a, b, c) per iteration
   int32_t steps, ngroups;
@@ -57,9 +60,9 @@ __host__ __device__ constexpr uint32_t ns_fused_smem_bytes() {
          1024 + 256;
 }
 
-template <int BT_MM, int BT_MN>
+template <int BT_MM, int BT_MN, int NITER>
 __global__ void __launch_bounds__(kGemmThreadsFlow, 1)
-ns_fused_kernel(const __grid_constant__ NsFusedArgs<BT_MM, BT_MN> args) {
+ns_fused_kernel(const __grid_constant__ NsFusedArgs<BT_MM, BT_MN, NITER> args) {
   using OpMM = OpNs<BT_MM>;
   using OpMN = OpNs<BT_MN>;
   constexpr int RING = ns_fused_ring<BT_MM, BT_MN>();
@@ -71,7 +74,7 @@ ns_fused_kernel(const __grid_constant__ NsFusedArgs<BT_MM, BT_MN> args) {
   GemmCtx cx;
   gemm_setup(cx, smem_raw, RING, kStride, ns_fused_staging<BT_MM, BT_MN>(), kTmemCols);
   if (threadIdx.x == 32) {
-    for (int par = 0; par < 2; ++par)
+    for (int par = 0; par < (NITER < 2 ? NITER : 2); ++par)
       for (int g = 0; g < args.ngroups; ++g) {
         tma_prefetch_desc(&args.gram[par][g].a[0]);
         tma_prefetch_desc(&args.gram[par][g].b[0]);
@@ -79,12 +82,10 @@ ns_fused_kernel(const __grid_constant__ NsFusedArgs<BT_MM, BT_MN> args) {
         tma_prefetch_desc(&args.upd[par][g].b[0]);
         tma_prefetch_desc(&args.gram[par][g].out[0]);
         tma_prefetch_desc(&args.upd[par][g].out[0]);
+        tma_prefetch_desc(&args.poly[par][g].a[0]);
+        tma_prefetch_desc(&args.poly[par][g].b[0]);
+        tma_prefetch_desc(&args.poly[par][g].out[0]);
       }
-    for (int g = 0; g < args.ngroups; ++g) {
-      tma_prefetch_desc(&args.poly[g].a[0]);
-      tma_prefetch_desc(&args.poly[g].b[0]);
-      tma_prefetch_desc(&args.poly[g].out[0]);
-    }
   }
   bool failed = false;
 
@@ -96,13 +97,13 @@ ns_fused_kernel(const __grid_constant__ NsFusedArgs<BT_MM, BT_MN> args) {
     patch.scale[g] = args.scale[g];
     deps.counter[g] = args.done[g];
     deps.need[g] = 0;
-    const auto& A = args.poly[g];
+    const auto& A = args.poly[0][g];
     const auto& U = args.upd[0][g];
     tiles_mm[g] = ((A.M + kBM - 1) / kBM) * ((A.N + BT_MM - 1) / BT_MM);
     tiles_mn[g] = ((U.M + kBM - 1) / kBM) * ((U.N + BT_MN - 1) / BT_MN);
   }
   for (int it = 0; it < args.steps && !failed; ++it) {
-    const int par = it & 1;
+    const int par = it % NITER;
     const float a = args.coef[it][0], b = args.coef[it][1], c = args.coef[it][2];
     patch.scale_pow = it == 0 ? 2 : 0;
     patch.diag = b / (2.f * c);       // gram: S = X X^T + (b / 2c) I
@@ -113,7 +114,7 @@ ns_fused_kernel(const __grid_constant__ NsFusedArgs<BT_MM, BT_MN> args) {
     patch.diag = a - b * b / (4.f * c);  // poly: P = c S S + (a - b^2 / 4c) I
     patch.acc_scale = c;
     patch.scale_pow = 0;
-    failed = gemm_phase<OpMM, RING>(cx, args.poly, args.ngroups, patch, deps);
+    failed = gemm_phase<OpMM, RING>(cx, args.poly[par], args.ngroups, patch, deps);
     if (failed) break;
     for (int g = 0; g < 2; ++g) deps.need[g] += tiles_mm[g];
     patch.diag = 0.f;                 // update: X' = P X
