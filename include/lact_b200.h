@@ -86,6 +86,10 @@ typedef struct lact_scan_io {
   /* training: per UPDATE step u (in program order), fp32 [w0w2 | w1 | g0g2 | g1] with w = the weights
    * that step computed with ([B,2H,D], [B,D,H]) and g = its gradient after momentum; or NULL */
   void *state_dump;
+  /* training with Muon (ns_steps 1..5): per UPDATE step, the Newton-Schulz iterates of both groups in the layout
+   * lact_ns_trace_bwd reads (lact_scan_ns_trace_bytes per step; 256-byte aligned), so that the backward does not
+   * recompute them; or NULL */
+  void *ns_trace;
 } lact_scan_io;
 
 /* Library version (major * 1000 + minor).  No counterpart in the reference. */
@@ -127,6 +131,11 @@ int lact_debug_wait_timeout(int32_t *status_word, void *stream);
 /* Scratch bytes needed by lact_scan_fwd for this configuration and step list. */
 int lact_scan_workspace_bytes(const lact_scan_config *cfg, int32_t n_steps, const int32_t *kind,
                               const int64_t *start, const int64_t *end, size_t *bytes_out);
+
+/* Bytes of Newton-Schulz trace that lact_scan_fwd keeps per UPDATE step when lact_scan_io.ns_trace is given
+ * ([w0;w2] group first, the w1 group at `second_group_offset`); LACT_ERR_CONFIG if this configuration keeps none
+ * (Muon off, or more than five iterations).  No counterpart in the reference (autograd keeps its own graph). */
+int lact_scan_ns_trace_bytes(const lact_scan_config *cfg, size_t *bytes_per_update, size_t *second_group_offset);
 
 /* The chunk recurrence: executes `n_steps` steps in order; APPLY writes
  * o[:, out_start : out_start + (end - start)] = f_W(q[:, start:end]); UPDATE updates the fast
@@ -276,6 +285,8 @@ int lact_bmm2_strided_bf16(const void *a0, int32_t a0_mn_major, int64_t a0_ld, i
  *   lact_ns_trace_bwd: dx0[B, R, C] (fp32) = gradient w.r.t. the NORMALISED first iterate bf16(g) / (||g|| + 1e-7),
  *     from du[B, R, C] (bf16) = gradient w.r.t. x_out, using the trace of the matching forward call. */
 int lact_ns_trace_bytes(int64_t B, int64_t R, int64_t C, int32_t steps, size_t *bytes_out);
+/* byte offset, inside a trace, of the final iterate x_out (bf16 [B, R, C]) */
+int lact_ns_trace_result_offset(int64_t B, int64_t R, int64_t C, int32_t steps, size_t *offset_out);
 int lact_ns_trace_fwd(const void *g, int32_t g_dtype, void *x_out, int64_t B, int64_t R, int64_t C, int32_t steps,
                       int32_t const_coeffs, int32_t gram_right, void *trace, size_t trace_bytes, int32_t *status_word,
                       void *stream);

@@ -28,7 +28,7 @@ class ScanConfig(C.Structure):
 class ScanIO(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in ("w0", "w1", "w2", "q", "k", "v", "lr0", "lr1", "lr2", "momentum", "m0_in",
                                           "m1_in", "m2_in", "o", "w0_out", "w1_out", "w2_out", "m0_out", "m1_out",
-                                          "m2_out", "state_dump")]
+                                          "m2_out", "state_dump", "ns_trace")]
 
 
 _lib: Optional[C.CDLL] = None
@@ -55,6 +55,10 @@ def _declare(lib: C.CDLL) -> None:
     lib.lact_profile_read.restype = C.c_int
     lib.lact_scan_workspace_bytes.argtypes = [C.POINTER(ScanConfig), i32, C.POINTER(i32), C.POINTER(i64),
                                               C.POINTER(i64), szp]
+    lib.lact_scan_ns_trace_bytes.argtypes = [C.POINTER(ScanConfig), szp, szp]
+    lib.lact_scan_ns_trace_bytes.restype = C.c_int
+    lib.lact_ns_trace_result_offset.argtypes = [i64, i64, i64, i32, szp]
+    lib.lact_ns_trace_result_offset.restype = C.c_int
     lib.lact_scan_fwd.argtypes = [C.POINTER(ScanConfig), C.POINTER(ScanIO), i32, C.POINTER(i32), C.POINTER(i64),
                                   C.POINTER(i64), C.POINTER(i64), vp, C.c_size_t, vp]
     lib.lact_swiglu_ffn_workspace_bytes.argtypes = [i64, i64, i64, i64, szp]

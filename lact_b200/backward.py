@@ -206,14 +206,33 @@ def scan_forward_saving(opts, steps, w0, w1, w2, q, k, v, lr0, lr1, lr2, momentu
     H = w0.shape[1]
     per = 2 * (B * 2 * H * D + B * D * H)
     dump = torch.empty(max(n_upd, 1), per, dtype=torch.float32, device=q.device)
+    # with Muon the forward's own Newton-Schulz iterates are kept too (no recomputation in the backward)
+    stride, _ = ops.ns_trace_layout(B, Ltok, D, H, opts) if q.dtype == BF16 else (0, 0)
+    ns_dump = torch.empty(max(n_upd, 1) * stride if stride else 1, dtype=torch.uint8, device=q.device)
     with torch.no_grad():
         res = ops.scan_eager(w0, w1, w2, q, k, v, lr0, lr1, lr2, steps, momentum=momentum, return_state=True,
-                             _state_dump=dump, **{k_: v_ for k_, v_ in opts.items() if k_ not in ("return_state", "_detach_norms")})
+                             _state_dump=dump, _ns_trace=ns_dump if stride else None,
+                             **{k_: v_ for k_, v_ in opts.items() if k_ not in ("return_state", "_detach_norms")})
     o, wf0, wf1, wf2 = res[:4]
-    return o, wf0, wf1, wf2, dump
+    return o, wf0, wf1, wf2, dump, ns_dump
 
 
-def scan_backward(opts, steps, w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, dump, wf0, wf1, wf2, dO, gwf=None):
+def ns_saved_from_trace(trace: torch.Tensor, G: torch.Tensor, steps, const_coeffs, gram_right):
+    """The `saved` record `ns_backward` expects, built from a trace the training forward kept (no recomputation),
+    and the iteration's result U (a bf16 view into the trace)."""
+    nmat, R, Cc = G.shape
+    off = C.c_size_t(0)
+    L.check(L.lib().lact_ns_trace_result_offset(nmat, R, Cc, int(steps), C.byref(off)), "lact_ns_trace_result_offset")
+    U = trace[off.value:off.value + nmat * R * Cc * 2].view(BF16).view(nmat, R, Cc)
+    Gb = G.to(BF16)
+    nrm = torch.linalg.vector_norm(Gb, dim=(1, 2), keepdim=True, dtype=torch.float32).to(BF16)
+    den = (nrm.float() + 1e-7).to(BF16)
+    return dict(trace=trace, shape=(nmat, R, Cc), steps=int(steps), cc=int(bool(const_coeffs)), gr=int(bool(gram_right)),
+                Gb=Gb, den=den.float(), nrm=nrm.float()), U
+
+
+def scan_backward(opts, steps, w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, dump, wf0, wf1, wf2, dO, gwf=None,
+                  ns_dump=None):
     """Reverse sweep over the step program.  `momentum` may be None.  `gwf` = optional cotangents
     (g_w0, g_w1, g_w2; any may be None) of the final fast weights the forward returned: they seed
     the weight gradient the sweep starts from (in the reference the returned weights carry autograd
@@ -250,6 +269,12 @@ def scan_backward(opts, steps, w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, dum
         base = n02 + n1
         return dump[u, base:base + n02].view(B, 2 * H, D), dump[u, base + n02:base + n02 + n1].view(B, D, H)
 
+    ns_stride = ns_off1 = 0
+    if ns_dump is not None:
+        from . import ops as _ops
+        ns_stride, ns_off1 = _ops.ns_trace_layout(B, Ltok, D, H, opts)
+        if ns_stride == 0:
+            ns_dump = None
     prenorm, muon = bool(opts.get("prenorm")), bool(opts.get("use_muon"))
     overwrite = bool(opts.get("overwrite_quirk")) and muon
     nst, cc, gr = int(opts.get("ns_steps", 5)), bool(opts.get("ns_const_coeffs")), bool(opts.get("ns_gram_right"))
@@ -265,10 +290,22 @@ def scan_backward(opts, steps, w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, dum
                 return ops.zeropower_via_newtonschulz5(g.transpose(1, 2).contiguous(), st).transpose(1, 2)
             return ops.zeropower_via_newtonschulz5(g, st)
 
+        def kept_result(u, group):
+            """Newton-Schulz result of update u as the forward kept it (bf16 view into its trace)."""
+            tr = ns_dump[u * ns_stride:(u + 1) * ns_stride]
+            tr = tr[:ns_off1] if group == 0 else tr[ns_off1:]
+            nmat, R, Cc = ((B, 2 * H, D) if opts.get("ns_concat") else (2 * B, H, D)) if group == 0 else (B, D, H)
+            off = C.c_size_t(0)
+            L.check(L.lib().lact_ns_trace_result_offset(nmat, R, Cc, nst, C.byref(off)), "lact_ns_trace_result_offset")
+            x = tr[off.value:off.value + nmat * R * Cc * 2].view(BF16)
+            return x.view(B, 2 * H, D) if group == 0 else x.view(B, D, H)
+
         masters = [(W0_02, W0_1)]
         for u in range(n_upd - 1):
             g02, g1 = grad_state(u)
-            if muon:
+            if muon and ns_dump is not None:
+                g02, g1 = kept_result(u, 0), kept_result(u, 1)
+            elif muon:
                 g02 = fast_ns(g02) if opts.get("ns_concat") else torch.cat(
                     [fast_ns(g02[:, :H]), fast_ns(g02[:, H:])], dim=1)
                 g1 = fast_ns(g1)
@@ -287,9 +324,20 @@ def scan_backward(opts, steps, w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, dum
     dM02 = dM1 = None
     dn02 = torch.zeros(B, 2 * H, dtype=f32, device=dev)
     dn1 = torch.zeros(B, D, dtype=f32, device=dev)
-    dq = torch.zeros_like(q, dtype=BF16)
-    dk = torch.zeros_like(k, dtype=BF16)
-    dv = torch.zeros_like(v, dtype=BF16)
+    # every token range is written in place by the first step that produces a gradient for it: zero-filling (a full
+    # pass over three [B, L, D] tensors) is needed only where no step does
+    def covered(kind_):
+        end_ = 0
+        for s_, e_ in sorted((st[1], st[2]) for st in steps if st[0] == kind_ and st[2] > st[1]):
+            if s_ > end_:
+                return False
+            end_ = max(end_, e_)
+        return end_ >= Ltok
+    alloc_q = torch.empty_like if covered(P.APPLY) else torch.zeros_like
+    alloc_kv = torch.empty_like if covered(P.UPDATE) else torch.zeros_like
+    dq = alloc_q(q, dtype=BF16)
+    dk = alloc_kv(k, dtype=BF16)
+    dv = alloc_kv(v, dtype=BF16)
     dlr = [torch.zeros(B, Ltok, dtype=f32, device=dev) for _ in range(3)]
     dmom = torch.zeros(B, Ltok, dtype=f32, device=dev) if has_momentum else None
     dO = dO.to(BF16)
@@ -328,8 +376,13 @@ def scan_backward(opts, steps, w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, dum
         U02, U1, sv02, sv1 = G02.contiguous(), G1.contiguous(), None, None
         if muon:
             g02m = G02.contiguous() if opts.get("ns_concat") else G02.contiguous().view(2 * B, H, D)
-            sv02, U02 = ns_forward_saved(g02m, nst, cc, gr)
-            sv1, U1 = ns_forward_saved(G1.contiguous(), nst, cc, gr)
+            if ns_dump is not None:
+                tr = ns_dump[u * ns_stride:(u + 1) * ns_stride]
+                sv02, U02 = ns_saved_from_trace(tr[:ns_off1], g02m, nst, cc, gr)
+                sv1, U1 = ns_saved_from_trace(tr[ns_off1:], G1.contiguous(), nst, cc, gr)
+            else:
+                sv02, U02 = ns_forward_saved(g02m, nst, cc, gr)
+                sv1, U1 = ns_forward_saved(G1.contiguous(), nst, cc, gr)
             U02 = U02.view(B, 2 * H, D)
         # renorm backward: dWn is the gradient w.r.t. (base + update); base is W_u, the master
         # copy (pre-norm), or the gradient itself (bidirectional overwrite)

@@ -665,12 +665,16 @@ int launch_ns_fused(const NsGroup* grp, int ngroups, int steps, int const_coeffs
 // Picks the fused kernel instantiated for the tile widths this problem wants; returns
 // LACT_ERR_CONFIG when there is none (the caller then runs the multi-launch path).
 int try_ns_fused(const NsGroup* grp, int ngroups, int steps, int const_coeffs, int32_t* status,
-                 cudaStream_t stream, const bf16** result, int unscaled_first = 0) {
+                 cudaStream_t stream, const bf16** result, int unscaled_first = 0, const NsKeep* keep = nullptr) {
   if (steps < 1 || steps > kNsFusedMaxSteps) return LACT_ERR_CONFIG;
   if (!const_coeffs && steps != 5) return LACT_ERR_CONFIG;
+  if (keep != nullptr && steps > 5) return LACT_ERR_CONFIG;
   int bt_mm = 0, bt_mn = 0;
   ns_tile_widths(grp, ngroups, &bt_mm, &bt_mn);
-  for (int g = 0; g < ngroups; ++g) result[g] = (steps % 2 == 0) ? grp[g].xa : grp[g].xb;
+  for (int g = 0; g < ngroups; ++g) {
+    if (keep != nullptr) result[g] = keep[g].X + static_cast<int64_t>(grp[g].nmat) * grp[g].R * grp[g].C * steps;
+    else result[g] = (steps % 2 == 0) ? grp[g].xa : grp[g].xb;
+  }
   // Few matrices per launch (a small (batch x head) shard): the kernel is bound by the 15-phase chain of each
   // matrix, not by throughput, so narrower tiles that spread every phase over more SMs (and shorten the serial
   // work per tile) win.  Tiles of the Gram phase at width bt over all groups:
@@ -679,15 +683,17 @@ int try_ns_fused(const NsGroup* grp, int ngroups, int steps, int const_coeffs, i
     for (int g = 0; g < ngroups; ++g) t += static_cast<int64_t>(grp[g].nmat) * ceil_div(grp[g].m, kBM) * ceil_div(grp[g].m, bt);
     return t;
   };
+  // keep == nullptr: iterates ping-pong (two problem sets); else every iteration keeps its buffers (five sets)
+#define LACT_NS_FUSED(BTV)                                                                                          \
+  (keep == nullptr ? launch_ns_fused<BTV, BTV, 2>(grp, ngroups, steps, const_coeffs, status, stream, unscaled_first) \
+                   : launch_ns_fused<BTV, BTV, 5>(grp, ngroups, steps, const_coeffs, status, stream, unscaled_first, keep))
   const int64_t want = static_cast<int64_t>(sm_count()) * 3 / 4;
-  if (bt_mm == 192 && bt_mn == 192 && gram_tiles(192) >= want)
-    return launch_ns_fused<192, 192, 2>(grp, ngroups, steps, const_coeffs, status, stream, unscaled_first);
+  if (bt_mm == 192 && bt_mn == 192 && gram_tiles(192) >= want) return LACT_NS_FUSED(192);
   // (a 256-wide update tile leaves no room for a useful ring next to two staging tiles: 128 is used)
   const bool ok128 = (bt_mm == 192 && bt_mn == 192) || (bt_mm == 128 && (bt_mn == 128 || bt_mn == 256));
-  if (ok128 && (gram_tiles(128) >= want || gram_tiles(64) == gram_tiles(128)))
-    return launch_ns_fused<128, 128, 2>(grp, ngroups, steps, const_coeffs, status, stream, unscaled_first);
-  if (ok128 || (bt_mm == 64 && bt_mn == 64))
-    return launch_ns_fused<64, 64, 2>(grp, ngroups, steps, const_coeffs, status, stream, unscaled_first);
+  if (ok128 && (gram_tiles(128) >= want || gram_tiles(64) == gram_tiles(128))) return LACT_NS_FUSED(128);
+  if (ok128 || (bt_mm == 64 && bt_mn == 64)) return LACT_NS_FUSED(64);
+#undef LACT_NS_FUSED
   return LACT_ERR_CONFIG;
 }
 
@@ -733,6 +739,38 @@ void plan_ns(Carver& c, int64_t B, int64_t D, int64_t H, int concat, int gram_ri
   carve_ns_group(c, plan->grp[0]);
   carve_ns_group(c, plan->grp[1]);
 }
+
+// Trace layout in the caller's buffer (bf16 unless noted): group scratch (norm partials,
+// scale factors); X[0..steps] ([B][R][C] each); shifted Gram matrix A + (b/2c) I and polynomial P per iteration
+// ([B][m][m]); then the backward's temporaries: c A + (b/2) I, Q, S ([B][m][m]) and two [B][R][C] gradient buffers.
+struct NsTrace {
+  NsGroup grp;
+  bf16* X;   // (steps + 1) iterates
+  bf16 *A, *P;  // steps matrices each (A: the shifted Gram matrix)
+  bf16 *CB, *Q, *S, *dXa, *dXb;
+  size_t bytes;
+};
+
+int plan_ns_trace(void* base, int64_t B, int64_t R, int64_t C, int steps, int gram_right, NsTrace* t) {
+  if (B < 1 || B > 65535 || R < 8 || C < 8 || (R % 8) || (C % 8) || steps < 1 || steps > 16) return LACT_ERR_SHAPE;
+  Carver cv(base);
+  ns_group_init(t->grp, B, R, C, gram_right);
+  const size_t rc = static_cast<size_t>(B) * R * C, mm = static_cast<size_t>(B) * t->grp.m * t->grp.m;
+  t->grp.partial = cv.take<float>(static_cast<size_t>(B) * kNsMaxParts);
+  t->grp.scale = cv.take<float>(B);
+  t->grp.done = cv.take<uint32_t>(static_cast<size_t>(B) + 64);
+  t->X = cv.take<bf16>(rc * (steps + 1));
+  t->A = cv.take<bf16>(mm * steps);
+  t->P = cv.take<bf16>(mm * steps);
+  t->CB = cv.take<bf16>(mm);
+  t->Q = cv.take<bf16>(mm);
+  t->S = cv.take<bf16>(mm);
+  t->dXa = cv.take<bf16>(rc);
+  t->dXb = cv.take<bf16>(rc);
+  t->bytes = cv.off + 256;
+  return LACT_OK;
+}
+
 
 struct ScanPlan {
   int32_t* status;
@@ -816,6 +854,23 @@ bool has_later_update(const int32_t* kind, int n_steps, int i) {
   return false;
 }
 
+// Bytes of Newton-Schulz trace one UPDATE step keeps in training (both groups, 256-byte aligned), and the offset of
+// the second group's trace; LACT_ERR_CONFIG if this configuration keeps none (Muon off, more than five steps).
+int scan_ns_trace_layout(const lact_scan_config& c, size_t* stride, size_t* g0_bytes) {
+  if (!c.use_muon || c.ns_steps < 1 || c.ns_steps > 5) return LACT_ERR_CONFIG;
+  NsGroup g0, g1;
+  if (c.ns_concat) ns_group_init(g0, c.B, 2 * c.H, c.D, c.ns_gram_right);
+  else ns_group_init(g0, 2 * c.B, c.H, c.D, c.ns_gram_right);
+  ns_group_init(g1, c.B, c.D, c.H, c.ns_gram_right);
+  NsTrace t0, t1;
+  LACT_TRY(plan_ns_trace(nullptr, g0.nmat, g0.R, g0.C, c.ns_steps, c.ns_gram_right, &t0));
+  LACT_TRY(plan_ns_trace(nullptr, g1.nmat, g1.R, g1.C, c.ns_steps, c.ns_gram_right, &t1));
+  const size_t a = (t0.bytes + 255) & ~static_cast<size_t>(255), b = (t1.bytes + 255) & ~static_cast<size_t>(255);
+  *g0_bytes = a;
+  *stride = a + b;
+  return LACT_OK;
+}
+
 int scan_fwd(const lact_scan_config& c, const lact_scan_io& io, int32_t n_steps, const int32_t* kind,
              const int64_t* start, const int64_t* end, const int64_t* out_start, void* workspace, size_t ws_bytes,
              cudaStream_t stream) {
@@ -882,6 +937,12 @@ int scan_fwd(const lact_scan_config& c, const lact_scan_io& io, int32_t n_steps,
     LACT_TRY(flush(first_u));
   }
 
+  // training with Muon: per-update Newton-Schulz traces in the caller's buffer (see lact_scan_ns_trace_bytes)
+  size_t ns_trace_stride = 0, ns_trace_g0 = 0;
+  const bool ns_keep = io.ns_trace != nullptr && c.use_muon && scan_ns_trace_layout(c, &ns_trace_stride, &ns_trace_g0) == LACT_OK;
+  if (io.ns_trace != nullptr && !ns_keep) return LACT_ERR_CONFIG;
+  if (ns_keep && (reinterpret_cast<uintptr_t>(io.ns_trace) & 255) != 0) return LACT_ERR_WORKSPACE;
+
   int update_idx = 0;
   for (int i = 0; i < n_steps; ++i) {
     if (kind[i] == LACT_STEP_APPLY) {
@@ -913,7 +974,7 @@ int scan_fwd(const lact_scan_config& c, const lact_scan_io& io, int32_t n_steps,
       if (fused_parts[0] <= kNsMaxParts && fused_parts[1] <= kNsMaxParts) {
         g.partial02 = p.ns.grp[0].partial;
         g.partial1 = p.ns.grp[1].partial;
-        if (c.ns_steps > 0) {  // the iteration starts from bf16(G) itself, normalisation folded in
+        if (c.ns_steps > 0 && !ns_keep) {  // the iteration starts from bf16(G) itself, normalisation folded in
           g.gb02 = p.ns.grp[0].xa;
           g.gb1 = p.ns.grp[1].xa;
         }
@@ -946,7 +1007,28 @@ int scan_fwd(const lact_scan_config& c, const lact_scan_io& io, int32_t n_steps,
       r.B = static_cast<int>(B); r.R = R; r.C = C;
       r.mode = c.renorm; r.prenorm = c.prenorm; r.prenorm_bf16 = c.prenorm_bf16; r.quirk = c.overwrite_quirk;
     }
-    if (c.use_muon) {
+    if (c.use_muon && ns_keep) {
+      // training: every iterate, shifted Gram matrix and polynomial of this update stays in the caller's trace
+      // buffers (the layout lact_ns_trace_bwd reads); the first iterate is the explicitly normalised gradient
+      NsPlan& ns = p.ns;
+      const bf16* xres[2] = {nullptr, nullptr};
+      const void* srcs[2] = {p.G02, p.G1};
+      NsGroup tg[2];
+      NsKeep keep[2];
+      uint8_t* tb = static_cast<uint8_t*>(io.ns_trace) + static_cast<size_t>(update_idx - 1) * ns_trace_stride;
+      for (int gi = 0; gi < 2; ++gi) {
+        NsTrace t;
+        LACT_TRY(plan_ns_trace(tb + (gi == 0 ? 0 : ns_trace_g0), ns.grp[gi].nmat, ns.grp[gi].R, ns.grp[gi].C, c.ns_steps,
+                               c.ns_gram_right, &t));
+        tg[gi] = ns.grp[gi];
+        tg[gi].xa = t.X;
+        keep[gi] = NsKeep{t.X, t.A, t.P};
+      }
+      LACT_TRY(launch_ns_prepare(tg, 2, srcs, 1, 1, stream, fused_parts[0] > 0 ? fused_parts : nullptr));
+      LACT_TRY(try_ns_fused(tg, 2, c.ns_steps, c.ns_const_coeffs, p.status, stream, xres, 0, keep));
+      rn[0].x = xres[0];
+      rn[1].x = xres[1];
+    } else if (c.use_muon) {
       NsPlan& ns = p.ns;
       const bf16* xres[2] = {nullptr, nullptr};
       const void* srcs[2] = {p.G02, p.G1};
@@ -1087,6 +1169,12 @@ int lact_scan_workspace_bytes(const lact_scan_config* cfg, int32_t n_steps, cons
   LACT_TRY(plan_scan(*cfg, n_steps, kind, start, end, nullptr, &p));
   *bytes_out = p.bytes;
   return LACT_OK;
+}
+
+int lact_scan_ns_trace_bytes(const lact_scan_config* cfg, size_t* bytes_per_update, size_t* second_group_offset) {
+  if (!cfg || !bytes_per_update || !second_group_offset) return LACT_ERR_NULL;
+  LACT_TRY(validate_scan_config(*cfg));
+  return scan_ns_trace_layout(*cfg, bytes_per_update, second_group_offset);
 }
 
 int lact_scan_fwd(const lact_scan_config* cfg, const lact_scan_io* io, int32_t n_steps, const int32_t* kind,
@@ -1239,42 +1327,20 @@ int lact_newton_schulz(const void* g, int32_t g_dtype, void* x, int64_t B, int64
 }
 
 // ---------------------------------------------------------------- Newton-Schulz with saved iterates, and its backward
-// Trace layout in the caller's buffer (bf16 unless noted): group scratch (norm partials,
-// scale factors); X[0..steps] ([B][R][C] each); shifted Gram matrix A + (b/2c) I and polynomial P per iteration
-// ([B][m][m]); then the backward's temporaries: c A + (b/2) I, Q, S ([B][m][m]) and two [B][R][C] gradient buffers.
-struct NsTrace {
-  NsGroup grp;
-  bf16* X;   // (steps + 1) iterates
-  bf16 *A, *P;  // steps matrices each (A: the shifted Gram matrix)
-  bf16 *CB, *Q, *S, *dXa, *dXb;
-  size_t bytes;
-};
-
-static int plan_ns_trace(void* base, int64_t B, int64_t R, int64_t C, int steps, int gram_right, NsTrace* t) {
-  if (B < 1 || B > 65535 || R < 8 || C < 8 || (R % 8) || (C % 8) || steps < 1 || steps > 16) return LACT_ERR_SHAPE;
-  Carver cv(base);
-  ns_group_init(t->grp, B, R, C, gram_right);
-  const size_t rc = static_cast<size_t>(B) * R * C, mm = static_cast<size_t>(B) * t->grp.m * t->grp.m;
-  t->grp.partial = cv.take<float>(static_cast<size_t>(B) * kNsMaxParts);
-  t->grp.scale = cv.take<float>(B);
-  t->grp.done = cv.take<uint32_t>(static_cast<size_t>(B) + 64);
-  t->X = cv.take<bf16>(rc * (steps + 1));
-  t->A = cv.take<bf16>(mm * steps);
-  t->P = cv.take<bf16>(mm * steps);
-  t->CB = cv.take<bf16>(mm);
-  t->Q = cv.take<bf16>(mm);
-  t->S = cv.take<bf16>(mm);
-  t->dXa = cv.take<bf16>(rc);
-  t->dXb = cv.take<bf16>(rc);
-  t->bytes = cv.off + 256;
-  return LACT_OK;
-}
-
 int lact_ns_trace_bytes(int64_t B, int64_t R, int64_t C, int32_t steps, size_t* bytes_out) {
   if (!bytes_out) return LACT_ERR_NULL;
   NsTrace t;
   LACT_TRY(plan_ns_trace(nullptr, B, R, C, steps, 0, &t));
   *bytes_out = t.bytes;
+  return LACT_OK;
+}
+
+int lact_ns_trace_result_offset(int64_t B, int64_t R, int64_t C, int32_t steps, size_t* offset_out) {
+  if (!offset_out) return LACT_ERR_NULL;
+  NsTrace t;
+  LACT_TRY(plan_ns_trace(nullptr, B, R, C, steps, 0, &t));
+  // with a null base the carved pointers ARE the byte offsets
+  *offset_out = reinterpret_cast<size_t>(t.X) + static_cast<size_t>(B) * R * C * steps * sizeof(bf16);
   return LACT_OK;
 }
 
@@ -1298,13 +1364,8 @@ int lact_ns_trace_fwd(const void* g, int32_t g_dtype, void* x_out, int64_t B, in
   int rc_f = LACT_ERR_CONFIG;
   if (steps <= 5) {
     const NsKeep keep{t.X, t.A, t.P};
-    int bt_mm = 0, bt_mn = 0;
-    ns_tile_widths(&t.grp, 1, &bt_mm, &bt_mn);
-    const int64_t gram_tiles = static_cast<int64_t>(t.grp.nmat) * ceil_div(t.grp.m, kBM) * ceil_div(t.grp.m, 192);
-    if (bt_mm == 192 && bt_mn == 192 && gram_tiles >= sm_count() * 3 / 4)
-      rc_f = launch_ns_fused<192, 192, 5>(&t.grp, 1, steps, const_coeffs, status_word, s, 0, &keep);
-    else if ((bt_mm == 192 && bt_mn == 192) || (bt_mm == 128 && (bt_mn == 128 || bt_mn == 256)))
-      rc_f = launch_ns_fused<128, 128, 5>(&t.grp, 1, steps, const_coeffs, status_word, s, 0, &keep);
+    const bf16* res = nullptr;
+    rc_f = try_ns_fused(&t.grp, 1, steps, const_coeffs, status_word, s, &res, 0, &keep);
   }
   if (rc_f == LACT_ERR_CONFIG) {
     for (int it = 0; it < steps; ++it) {

@@ -73,7 +73,8 @@ def _weight(t: torch.Tensor, shape: tuple, name: str) -> torch.Tensor:
 def scan_eager(w0, w1, w2, q, k, v, lr0, lr1, lr2, steps: Sequence[P.Step], *, out_len: Optional[int] = None,
                momentum=None, m_init=None, use_muon=False, ns_steps=5, ns_const_coeffs=False, ns_concat=False,
                ns_gram_right=False, renorm=L.RENORM_EPS_OUTSIDE, prenorm=False, prenorm_bf16=False,
-               overwrite_quirk=False, w_scale=1.0, return_state=False, return_momentum=False, _state_dump=None):
+               overwrite_quirk=False, w_scale=1.0, return_state=False, return_momentum=False, _state_dump=None,
+               _ns_trace=None):
     """Forward of the general chunk recurrence, straight through the C ABI (`lact_scan_fwd`), no
     autograd.  `scan` is the public, differentiable and compilable entry point."""
     dev = _need_cuda(w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum)
@@ -152,6 +153,8 @@ def scan_eager(w0, w1, w2, q, k, v, lr0, lr1, lr2, steps: Sequence[P.Step], *, o
     io.o = o.data_ptr()
     if _state_dump is not None:
         io.state_dump = _state_dump.data_ptr()
+    if _ns_trace is not None:
+        io.ns_trace = _ns_trace.data_ptr()
     state = mom = None
     if return_state:
         state = (torch.empty(B, H, D, dtype=torch.float32, device=dev),
@@ -173,6 +176,24 @@ def scan_eager(w0, w1, w2, q, k, v, lr0, lr1, lr2, steps: Sequence[P.Step], *, o
     if return_momentum:
         res.extend(mom)
     return res[0] if len(res) == 1 else tuple(res)
+
+
+def ns_trace_layout(B, Ltok, D, H, opts) -> Tuple[int, int]:
+    """(bytes of Newton-Schulz trace the training forward keeps per update, offset of the w1 group's trace), or
+    (0, 0) when this configuration keeps none (Muon off, more than five iterations)."""
+    if not opts.get("use_muon"):
+        return 0, 0
+    cfg = L.ScanConfig()
+    cfg.B, cfg.L, cfg.D, cfg.H, cfg.out_len = B, Ltok, D, H, Ltok
+    cfg.act_dtype = L.LACT_BF16
+    cfg.use_muon, cfg.ns_steps = 1, int(opts.get("ns_steps", 5))
+    cfg.ns_const_coeffs, cfg.ns_concat = int(bool(opts.get("ns_const_coeffs"))), int(bool(opts.get("ns_concat")))
+    cfg.ns_gram_right, cfg.renorm = int(bool(opts.get("ns_gram_right"))), int(opts.get("renorm", L.RENORM_EPS_OUTSIDE))
+    stride, off = C.c_size_t(0), C.c_size_t(0)
+    rc = L.lib().lact_scan_ns_trace_bytes(C.byref(cfg), C.byref(stride), C.byref(off))
+    if rc != 0:
+        return 0, 0
+    return int(stride.value), int(off.value)
 
 
 def _scan_f32(dev, w0, w1, w2, q, k, v, lr0, lr1, lr2, steps, out_len, momentum, m_init, opts, state_dump):
@@ -230,8 +251,8 @@ def _scan_fwd_op(w0: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, q: torch.
     if cfg[12]:
         from .backward import scan_forward_saving
         opts["out_len"] = out_len
-        o, a, b, c, dump = scan_forward_saving(opts, st, w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum)
-        return [o, a, b, c, dump]
+        o, a, b, c, dump, ns_dump = scan_forward_saving(opts, st, w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum)
+        return [o, a, b, c, dump, ns_dump]
     m_init = (m0, m1, m2) if m0 is not None else None
     res = scan_eager(w0, w1, w2, q, k, v, lr0, lr1, lr2, st, out_len=out_len, momentum=momentum, m_init=m_init,
                      return_state=True, return_momentum=bool(cfg[11]), **opts)
@@ -251,15 +272,17 @@ def _scan_fwd_fake(w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, m0, m1, m2, ste
     if cfg[12]:
         n_upd = sum(1 for i in range(0, len(steps), 4) if steps[i] == P.UPDATE)
         outs.append(q.new_empty((max(n_upd, 1), 2 * (B * 2 * H * D + B * D * H)), dtype=f32))
+        stride, _ = ns_trace_layout(B, Ltok, D, H, _opts_of(cfg, w_scale))
+        outs.append(q.new_empty((max(n_upd, 1) * stride if stride else 1,), dtype=torch.uint8))
     return outs
 
 
 @torch.library.custom_op("lact_b200::scan_bwd", mutates_args=(), device_types="cuda")
 def _scan_bwd_op(w0: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, q: torch.Tensor, k: torch.Tensor,
                  v: torch.Tensor, lr0: torch.Tensor, lr1: torch.Tensor, lr2: torch.Tensor,
-                 momentum: Optional[torch.Tensor], dump: torch.Tensor, wf0: torch.Tensor, wf1: torch.Tensor,
-                 wf2: torch.Tensor, dO: torch.Tensor, gw0: Optional[torch.Tensor], gw1: Optional[torch.Tensor],
-                 gw2: Optional[torch.Tensor], steps: List[int], cfg: List[int],
+                 momentum: Optional[torch.Tensor], dump: torch.Tensor, ns_dump: torch.Tensor, wf0: torch.Tensor,
+                 wf1: torch.Tensor, wf2: torch.Tensor, dO: torch.Tensor, gw0: Optional[torch.Tensor],
+                 gw1: Optional[torch.Tensor], gw2: Optional[torch.Tensor], steps: List[int], cfg: List[int],
                  w_scale: float) -> List[torch.Tensor]:
     """Gradients of (w0, w1, w2, q, k, v, lr0, lr1, lr2[, momentum]) from the cotangents of o (dO) and,
     optionally, of the returned final fast weights (gw0, gw1, gw2)."""
@@ -268,14 +291,17 @@ def _scan_bwd_op(w0: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, q: torch.
     opts["_detach_norms"] = bool(cfg[9])
     gwf = (gw0, gw1, gw2) if (gw0 is not None or gw1 is not None or gw2 is not None) else None
     g = scan_backward(opts, _steps_of(steps), w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, dump, wf0, wf1, wf2,
-                      dO.contiguous(), gwf)
-    # fresh, non-overlapping tensors (the w0 / w2 gradients are two halves of one buffer)
-    return [t.clone(memory_format=torch.contiguous_format) for t in g if t is not None]
+                      dO.contiguous(), gwf, ns_dump if ns_dump.numel() > 1 else None)
+    # operator outputs must not alias each other: the w0 / w2 gradients are two halves of one buffer (copied); the
+    # others are fresh tensors of the sweep
+    g = [t for t in g if t is not None]
+    return [g[0].clone(memory_format=torch.contiguous_format), g[1], g[2].clone(memory_format=torch.contiguous_format)] + \
+           [t if t.is_contiguous() else t.contiguous() for t in g[3:]]
 
 
 @_scan_bwd_op.register_fake
-def _scan_bwd_fake(w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, dump, wf0, wf1, wf2, dO, gw0, gw1, gw2, steps, cfg,
-                   w_scale):
+def _scan_bwd_fake(w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, dump, ns_dump, wf0, wf1, wf2, dO, gw0, gw1, gw2,
+                   steps, cfg, w_scale):
     outs = [torch.empty_like(t) for t in (w0, w1, w2, q, k, v, lr0, lr1, lr2)]
     if momentum is not None:
         outs.append(torch.empty_like(momentum))
@@ -290,7 +316,7 @@ def _scan_setup_context(ctx, inputs, output):
     ctx.set_materialize_grads(False)
     if cfg[12]:
         keep = [w0, w1, w2, q, k, v, lr0, lr1, lr2] + ([momentum] if momentum is not None else []) + \
-               [output[4], output[1], output[2], output[3]]
+               [output[4], output[5], output[1], output[2], output[3]]
         ctx.save_for_backward(*keep)
 
 
@@ -300,15 +326,15 @@ def _scan_autograd(ctx, grads):
     t = list(ctx.saved_tensors)
     ins, rest = t[:9], t[9:]
     momentum = rest.pop(0) if ctx.has_momentum else None
-    dump, wf0, wf1, wf2 = rest
+    dump, ns_dump, wf0, wf1, wf2 = rest
     dO = grads[0]
     if dO is None:
         q, k = ins[3], ins[4]
         dO = q.new_zeros((q.shape[0], ctx.cfg[10] if ctx.cfg[10] >= 0 else k.shape[1], q.shape[2]))
     # cotangents of the returned final weights (None when the caller did not use them)
     gw = [g_.float().contiguous() if g_ is not None else None for g_ in grads[1:4]]
-    g = torch.ops.lact_b200.scan_bwd(*ins, momentum, dump, wf0, wf1, wf2, dO, gw[0], gw[1], gw[2], ctx.steps, ctx.cfg,
-                                     ctx.w_scale)
+    g = torch.ops.lact_b200.scan_bwd(*ins, momentum, dump, ns_dump, wf0, wf1, wf2, dO, gw[0], gw[1], gw[2], ctx.steps,
+                                     ctx.cfg, ctx.w_scale)
     dmom = g[9] if ctx.has_momentum else None
     return (*g[:9], dmom, None, None, None, None, None, None)
 
