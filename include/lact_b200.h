@@ -300,7 +300,19 @@ int lact_fw_grad_bwd_pointwise(const void *y02, const void *dh, const void *g_dy
                                void *g_y02, void *g_dh, void *dy02, void *hid, void *g_lr0, void *g_lr1, void *g_lr2,
                                int64_t rows, int64_t H, void *stream);
 int lact_renorm_bwd(const void *base, const void *upd, int32_t upd_dtype, const void *n0, const void *dy, void *dw,
-                    void *dn0, int64_t rows, int64_t C, int32_t mode, void *stream);
+                    void *dw_bf16 /* optional bf16 copy of dw, or NULL */, void *dn0, int64_t rows, int64_t C,
+                    int32_t mode, void *stream);
+/* Two more stages of the reverse sweep that the reference leaves to autograd through its eager lines:
+ *   lact_ns_norm_bwd: backward of the Frobenius normalisation in front of Newton-Schulz (ttt_operation.py:45-52):
+ *     dx0 [nmat][n] (fp32, in/out) <- dx0 / den - bf16(g) <dx0, bf16(g)> / (den^2 nrm), nrm = bf16(||bf16(g)||),
+ *     den = bf16(nrm + 1e-7), g [nmat][n] fp32;
+ *   lact_momentum_bwd: momentum step (ttt_operation.py:170-179) for both gradient arrays (n0, n1 fp32 elements per
+ *     batch entry): dg += carry (if add_carry); dbeta[b] = <dg, mprev> (mprev NULL at the first update);
+ *     carry <- dg * beta[b]; dgb = bf16(dg).  carry / beta NULL: no momentum (bf16 copy only). */
+int lact_ns_norm_bwd(const void *g, void *dx0, int64_t nmat, int64_t elems_per_matrix, void *stream);
+int lact_momentum_bwd(void *dg0, void *dg1, void *carry0, void *carry1, const void *mprev0, const void *mprev1,
+                      void *dgb0, void *dgb1, const void *beta, void *dbeta, int64_t B, int64_t n0, int64_t n1,
+                      int32_t add_carry, void *stream);
 
 /* fp32 mode (fp32 activations; the reference's CPU configuration, e.g. bidirectional_lact_layer.py with fp32 inputs):
  * plain FFMA kernels for accuracy, no tensor cores.  The Python package runs the step program with them.

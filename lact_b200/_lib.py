@@ -85,7 +85,11 @@ def _declare(lib: C.CDLL) -> None:
     lib.lact_swiglu_bwd_planes.argtypes = [vp, vp, vp, vp, vp, i32, f32, vp, vp, i64, i64, vp]
     lib.lact_fw_grad_bwd_pointwise.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, f32, vp, vp, vp, vp, vp, vp, vp, i64,
                                                i64, vp]
-    lib.lact_renorm_bwd.argtypes = [vp, vp, i32, vp, vp, vp, vp, i64, i64, i32, vp]
+    lib.lact_renorm_bwd.argtypes = [vp, vp, i32, vp, vp, vp, vp, vp, i64, i64, i32, vp]
+    lib.lact_ns_norm_bwd.argtypes = [vp, vp, i64, i64, vp]
+    lib.lact_ns_norm_bwd.restype = C.c_int
+    lib.lact_momentum_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i32, vp]
+    lib.lact_momentum_bwd.restype = C.c_int
     lib.lact_ns_trace_bytes.argtypes = [i64, i64, i64, i32, C.POINTER(C.c_size_t)]
     lib.lact_ns_trace_fwd.argtypes = [vp, i32, vp, i64, i64, i64, i32, i32, i32, vp, C.c_size_t, vp, vp]
     lib.lact_ns_trace_bwd.argtypes = [vp, vp, i64, i64, i64, i32, i32, i32, vp, C.c_size_t, vp, vp]

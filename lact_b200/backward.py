@@ -108,14 +108,16 @@ def apply_backward(w02b, w1b, q, dO, dW02, dW1, dq_out=None):
     return gemm(dy02, w02b, b_mn=True, out=dq_out, out_dtype=BF16)   # dq = dy02 w02
 
 
-def fw_grad_backward(w02b, w1b, k, v, lr0, lr1, lr2, w_scale, gG02, gG1, dW02, dW1, dk_out=None, dv_out=None):
+def fw_grad_backward(w02b, w1b, k, v, lr0, lr1, lr2, w_scale, gG02, gG1, dW02, dW1, dk_out=None, dv_out=None,
+                     g02b=None, g1b=None):
     """Backward of the lr-weighted fast-weight gradient on one token range, given the gradients gG02
     ([B,2H,D]) / gG1 ([B,D,H]) of its outputs.  Accumulates into dW02 / dW1; returns
     (dk, dv [bf16; written into the views `dk_out` / `dv_out` if given], dlr0, dlr1, dlr2 [fp32, B x n]).
     lact_fw_grad.py:61-156."""
     B, n, D = k.shape
     H = w1b.shape[2]
-    g02b, g1b = gG02.to(BF16), gG1.to(BF16)
+    if g02b is None:
+        g02b, g1b = gG02.to(BF16), gG1.to(BF16)
     y02 = gemm(k, w02b, out_dtype=BF16)
     dh = gemm(v, w1b, b_mn=True, out_dtype=BF16)
     g_dy02 = gemm(k, g02b, out_dtype=BF16)                   # [B, n, 2H]
@@ -136,16 +138,18 @@ def fw_grad_backward(w02b, w1b, k, v, lr0, lr1, lr2, w_scale, gG02, gG1, dW02, d
     return dk, dv, glr[0], glr[1], glr[2]
 
 
-def renorm_backward(base, upd, n0, dy, dn0, mode):
-    """dw for y = renorm(base + upd); adds the n0 gradient into dn0.  Rows = all leading dims."""
+def renorm_backward(base, upd, n0, dy, dn0, mode, want_bf16=False):
+    """dw for y = renorm(base + upd); adds the n0 gradient into dn0.  Rows = all leading dims.  With `want_bf16`
+    returns (dw, bf16 copy of dw)."""
     C_ = base.shape[-1]
     rows = base.numel() // C_
     dw = torch.empty_like(base)
+    dwb = torch.empty_like(base, dtype=BF16) if want_bf16 else None
     upd = upd.contiguous()
     L.check(L.lib().lact_renorm_bwd(base.data_ptr(), upd.data_ptr(), L.dtype_code(upd), n0.data_ptr(), dy.data_ptr(),
-                                    dw.data_ptr(), _vecptr(dn0), rows, C_, int(mode), L.stream_ptr()),
+                                    dw.data_ptr(), _vecptr(dwb), _vecptr(dn0), rows, C_, int(mode), L.stream_ptr()),
             "lact_renorm_bwd")
-    return dw
+    return (dw, dwb) if want_bf16 else dw
 
 
 NS_TUNED5 = ((4.0848, -6.8946, 2.9270), (3.9505, -6.3029, 2.6377), (3.7418, -5.5913, 2.3037),
@@ -169,11 +173,8 @@ def ns_forward_saved(G, steps, const_coeffs, gram_right):
         L.check(L.lib().lact_ns_trace_fwd(G.data_ptr(), L.dtype_code(G), U.data_ptr(), nmat, R, Cc, int(steps),
                                           int(bool(const_coeffs)), int(bool(gram_right)), trace.data_ptr(), trace.numel(),
                                           _status_word(G.device).data_ptr(), L.stream_ptr()), "lact_ns_trace_fwd")
-    Gb = G.to(BF16)
-    nrm = torch.linalg.vector_norm(Gb, dim=(1, 2), keepdim=True, dtype=torch.float32).to(BF16)
-    den = (nrm.float() + 1e-7).to(BF16)
     return dict(trace=trace, shape=(nmat, R, Cc), steps=int(steps), cc=int(bool(const_coeffs)), gr=int(bool(gram_right)),
-                Gb=Gb, den=den.float(), nrm=nrm.float()), U
+                G=G), U
 
 
 def ns_backward(saved, dU):
@@ -182,17 +183,18 @@ def ns_backward(saved, dU):
     as identities, bf16 operands as in the reference's autograd), then the Frobenius
     normalisation X0 = bf16(G) / (||G|| + 1e-7) is differentiated here."""
     nmat, R, Cc = saved["shape"]
-    du = dU.to(BF16).contiguous()
+    du = (dU if dU.dtype == BF16 else dU.to(BF16)).contiguous()
     dX0 = torch.empty(nmat, R, Cc, dtype=torch.float32, device=du.device)
     trace = saved["trace"]
     with torch.cuda.device(du.device):
         L.check(L.lib().lact_ns_trace_bwd(du.data_ptr(), dX0.data_ptr(), nmat, R, Cc, saved["steps"], saved["cc"],
                                           saved["gr"], trace.data_ptr(), trace.numel(),
                                           _status_word(du.device).data_ptr(), L.stream_ptr()), "lact_ns_trace_bwd")
-    Gf, den, nrm = saved["Gb"].float(), saved["den"], saved["nrm"]
-    dot = (dX0 * Gf).sum(dim=(1, 2), keepdim=True)
-    # dX0 / den - G <dX0, G> / (den^2 ||G||), in place in dX0
-    return dX0.mul_(1.0 / den).addcmul_(Gf, dot / (den * den * nrm.clamp_min(1e-30)), value=-1.0)
+    # dX0 / den - bf16(G) <dX0, bf16(G)> / (den^2 ||bf16(G)||), in place in dX0
+    G = saved["G"]
+    G = G if (G.dtype == torch.float32 and G.is_contiguous()) else G.float().contiguous()
+    L.check(L.lib().lact_ns_norm_bwd(G.data_ptr(), dX0.data_ptr(), nmat, R * Cc, L.stream_ptr()), "lact_ns_norm_bwd")
+    return dX0
 
 
 def scan_forward_saving(opts, steps, w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum):
@@ -224,11 +226,8 @@ def ns_saved_from_trace(trace: torch.Tensor, G: torch.Tensor, steps, const_coeff
     off = C.c_size_t(0)
     L.check(L.lib().lact_ns_trace_result_offset(nmat, R, Cc, int(steps), C.byref(off)), "lact_ns_trace_result_offset")
     U = trace[off.value:off.value + nmat * R * Cc * 2].view(BF16).view(nmat, R, Cc)
-    Gb = G.to(BF16)
-    nrm = torch.linalg.vector_norm(Gb, dim=(1, 2), keepdim=True, dtype=torch.float32).to(BF16)
-    den = (nrm.float() + 1e-7).to(BF16)
     return dict(trace=trace, shape=(nmat, R, Cc), steps=int(steps), cc=int(bool(const_coeffs)), gr=int(bool(gram_right)),
-                Gb=Gb, den=den.float(), nrm=nrm.float()), U
+                G=G), U
 
 
 def scan_backward(opts, steps, w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, dump, wf0, wf1, wf2, dO, gwf=None,
@@ -392,22 +391,22 @@ def scan_backward(opts, steps, w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, dum
             b02, b1 = G02, G1
         else:
             b02, b1 = Wp02, Wp1
-        dWn02 = renorm_backward(b02.contiguous(), U02, n0_02, dW02, dn02, mode)
-        dWn1 = renorm_backward(b1.contiguous(), U1, n0_1, dW1, dn1, mode)
-        if prenorm and dWm02 is not None:
+        carry_in = prenorm and dWm02 is not None
+        want_b = sv02 is not None and not carry_in
+        r02 = renorm_backward(b02.contiguous(), U02, n0_02, dW02, dn02, mode, want_bf16=want_b)
+        r1 = renorm_backward(b1.contiguous(), U1, n0_1, dW1, dn1, mode, want_bf16=want_b)
+        (dWn02, dWn02b), (dWn1, dWn1b) = (r02, r1) if want_b else ((r02, None), (r1, None))
+        if carry_in:
             dWn02 += dWm02
             dWn1 += dWm1
         if sv02 is not None:
-            dG02 = ns_backward(sv02, dWn02.view(sv02["Gb"].shape)).view(B, 2 * H, D)
-            dG1 = ns_backward(sv1, dWn1)
+            dG02 = ns_backward(sv02, (dWn02b if dWn02b is not None else dWn02).view(sv02["shape"])).view(B, 2 * H, D)
+            dG1 = ns_backward(sv1, dWn1b if dWn1b is not None else dWn1)
             if overwrite:
-                dG02 = dG02 + dWn02
-                dG1 = dG1 + dWn1
+                dG02 += dWn02
+                dG1 += dWn1
         else:
             dG02, dG1 = dWn02.clone(), dWn1.clone()
-        if dM02 is not None:
-            dG02 += dM02
-            dG1 += dM1
         if prenorm:        # the weights update u computed with receive gradient only from its own steps
             dWm02, dWm1 = dWn02, dWn1
             dW02, dW1 = torch.zeros_like(dWn02), torch.zeros_like(dWn1)
@@ -415,21 +414,34 @@ def scan_backward(opts, steps, w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, dum
             dW02, dW1 = torch.zeros_like(dWn02), torch.zeros_like(dWn1)
         else:
             dW02, dW1 = dWn02, dWn1
+        # momentum step (one kernel): dG += what arrives from the next update's momentum state, dbeta, the share
+        # that goes on to the previous update, and the bf16 copies the contractions below read
+        g02b, g1b = torch.empty_like(dG02, dtype=BF16), torch.empty_like(dG1, dtype=BF16)
+        beta = dbeta = None
+        mp02 = mp1 = None
         if has_momentum:
-            beta = momv[:, s:e].mean(dim=1)  # [B]
+            beta = momv[:, s:e].mean(dim=1).contiguous()  # [B]
             if u > 0:
-                Mp02, Mp1 = grad_state(u - 1)
-                dbeta = (dG02 * Mp02).sum(dim=(1, 2)) + (dG1 * Mp1).sum(dim=(1, 2))
-                dmom[:, s:e] += (dbeta / float(e - s)).unsqueeze(1)
-            dM02, dM1 = dG02 * beta.view(B, 1, 1), dG1 * beta.view(B, 1, 1)
+                mp02, mp1 = grad_state(u - 1)
+                dbeta = torch.empty(B, dtype=f32, device=dev)
+            if dM02 is None:
+                dM02, dM1, add_carry = torch.empty_like(dG02), torch.empty_like(dG1), 0
+            else:
+                add_carry = 1
+        L.check(L.lib().lact_momentum_bwd(dG02.data_ptr(), dG1.data_ptr(), _vecptr(dM02 if has_momentum else None),
+                                          _vecptr(dM1 if has_momentum else None), _vecptr(mp02), _vecptr(mp1),
+                                          g02b.data_ptr(), g1b.data_ptr(), _vecptr(beta), _vecptr(dbeta), B, 2 * H * D,
+                                          D * H, add_carry if has_momentum else 0, L.stream_ptr()), "lact_momentum_bwd")
+        if dbeta is not None:
+            dmom[:, s:e] += (dbeta / float(e - s)).unsqueeze(1)
         w02b, w1b = shadow(u)
         if fresh(kv_done, s, e):
             _, _, g0, g1, g2 = fw_grad_backward(w02b, w1b, k[:, s:e], v[:, s:e], lr0v[:, s:e], lr1v[:, s:e],
                                                 lr2v[:, s:e], w_scale, dG02, dG1, dW02, dW1, dk_out=dk[:, s:e],
-                                                dv_out=dv[:, s:e])
+                                                dv_out=dv[:, s:e], g02b=g02b, g1b=g1b)
         else:
             gk, gv, g0, g1, g2 = fw_grad_backward(w02b, w1b, k[:, s:e], v[:, s:e], lr0v[:, s:e], lr1v[:, s:e],
-                                                  lr2v[:, s:e], w_scale, dG02, dG1, dW02, dW1)
+                                                  lr2v[:, s:e], w_scale, dG02, dG1, dW02, dW1, g02b=g02b, g1b=g1b)
             dk[:, s:e] += gk
             dv[:, s:e] += gv
         dlr[0][:, s:e] += g0

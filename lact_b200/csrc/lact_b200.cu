@@ -1707,14 +1707,47 @@ int lact_fw_grad_bwd_pointwise(const void* y02, const void* dh, const void* g_dy
 }
 
 int lact_renorm_bwd(const void* base, const void* upd, int32_t upd_dtype, const void* n0, const void* dy, void* dw,
-                    void* dn0, int64_t rows, int64_t C, int32_t mode, void* stream) {
+                    void* dw_bf16, void* dn0, int64_t rows, int64_t C, int32_t mode, void* stream) {
   if (!base || !upd || !n0 || !dy || !dw) return LACT_ERR_NULL;
   if (rows < 1 || C < 1 || mode < 0 || mode > 2) return LACT_ERR_SHAPE;
   RenormBwdArgs a{static_cast<const float*>(base), upd, upd_dtype == LACT_F32, static_cast<const float*>(n0),
-                  static_cast<const float*>(dy), static_cast<float*>(dw), static_cast<float*>(dn0), rows,
-                  static_cast<int32_t>(C), mode};
+                  static_cast<const float*>(dy), static_cast<float*>(dw), static_cast<bf16*>(dw_bf16),
+                  static_cast<float*>(dn0), rows, static_cast<int32_t>(C), mode};
   KernelScope scope(kClsOther, static_cast<cudaStream_t>(stream));
   renorm_bwd_kernel<<<ceil_div(rows, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  LACT_CUDA(cudaGetLastError());
+  return LACT_OK;
+}
+
+int lact_ns_norm_bwd(const void* g, void* dx0, int64_t nmat, int64_t elems_per_matrix, void* stream) {
+  if (!g || !dx0) return LACT_ERR_NULL;
+  if (nmat < 1 || nmat > 65535 * 16 || elems_per_matrix < 4 || (elems_per_matrix % 4) != 0) return LACT_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(g) & 15) != 0 || (reinterpret_cast<uintptr_t>(dx0) & 15) != 0) return LACT_ERR_SHAPE;
+  KernelScope scope(kClsOther, static_cast<cudaStream_t>(stream));
+  ns_norm_bwd_kernel<<<static_cast<unsigned>(nmat), 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const float*>(g), static_cast<float*>(dx0), elems_per_matrix);
+  LACT_CUDA(cudaGetLastError());
+  return LACT_OK;
+}
+
+int lact_momentum_bwd(void* dg0, void* dg1, void* carry0, void* carry1, const void* mprev0, const void* mprev1,
+                      void* dgb0, void* dgb1, const void* beta, void* dbeta, int64_t B, int64_t n0, int64_t n1,
+                      int32_t add_carry, void* stream) {
+  if (!dg0 || !dg1 || !dgb0 || !dgb1) return LACT_ERR_NULL;
+  if ((carry0 == nullptr) != (carry1 == nullptr) || (mprev0 == nullptr) != (mprev1 == nullptr)) return LACT_ERR_NULL;
+  if (B < 1 || B > 65535 * 16 || n0 < 4 || n1 < 4 || (n0 % 4) != 0 || (n1 % 4) != 0) return LACT_ERR_SHAPE;
+  MomentumBwdArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.dg[0] = static_cast<float*>(dg0); a.dg[1] = static_cast<float*>(dg1);
+  a.carry[0] = static_cast<float*>(carry0); a.carry[1] = static_cast<float*>(carry1);
+  a.mprev[0] = static_cast<const float*>(mprev0); a.mprev[1] = static_cast<const float*>(mprev1);
+  a.dgb[0] = static_cast<bf16*>(dgb0); a.dgb[1] = static_cast<bf16*>(dgb1);
+  a.beta = static_cast<const float*>(beta);
+  a.dbeta = static_cast<float*>(dbeta);
+  a.n[0] = n0; a.n[1] = n1;
+  a.add_carry = add_carry;
+  KernelScope scope(kClsOther, static_cast<cudaStream_t>(stream));
+  momentum_bwd_kernel<<<static_cast<unsigned>(B), 1024, 0, static_cast<cudaStream_t>(stream)>>>(a);
   LACT_CUDA(cudaGetLastError());
   return LACT_OK;
 }

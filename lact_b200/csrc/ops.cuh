@@ -843,6 +843,7 @@ struct RenormBwdArgs {
   const float* n0;    // [rows]
   const float* dy;    // [rows][C]
   float* dw;          // [rows][C] out
+  bf16* dw_b;         // optional bf16 copy of dw (operand of the Newton-Schulz backward), or nullptr
   float* dn0;         // [rows] accumulated
   int64_t rows;
   int32_t C, mode;
@@ -878,9 +879,101 @@ __global__ void __launch_bounds__(256) renorm_bwd_kernel(const RenormBwdArgs a) 
   }
   for (int c = lane; c < a.C; c += 32) {
     const float w = a.base[off + c] + load_scalar(a.upd, a.upd_f32, off + c);
-    a.dw[off + c] = s * a.dy[off + c] - k * w;
+    const float d = s * a.dy[off + c] - k * w;
+    a.dw[off + c] = d;
+    if (a.dw_b != nullptr) a.dw_b[off + c] = __float2bfloat16_rn(d);
   }
   if (lane == 0 && a.dn0 != nullptr) a.dn0[row] += dot * t;
+}
+
+// block-wide sum of two values (blockDim.x a multiple of 32, at most 1024); every thread gets the totals
+__device__ __forceinline__ void block_sum2(float& a, float& b, float* scratch /* [66] */) {
+  a = warp_sum(a);
+  b = warp_sum(b);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (l == 0) { scratch[w] = a; scratch[32 + w] = b; }
+  __syncthreads();
+  if (w == 0) {
+    float x = l < nw ? scratch[l] : 0.f, y = l < nw ? scratch[32 + l] : 0.f;
+    x = warp_sum(x);
+    y = warp_sum(y);
+    if (l == 0) { scratch[64] = x; scratch[65] = y; }
+  }
+  __syncthreads();
+  a = scratch[64];
+  b = scratch[65];
+}
+
+// Backward of the Frobenius normalisation in front of Newton-Schulz, X0 = bf16(G) / den with nrm = bf16(||bf16(G)||),
+// den = bf16(nrm + 1e-7):  dG = dX0 / den - bf16(G) <dX0, bf16(G)> / (den^2 nrm), written in place over dX0.
+// One block per matrix (`n` elements each).
+__global__ void __launch_bounds__(1024) ns_norm_bwd_kernel(const float* g, float* dx0, int64_t n) {
+  __shared__ float scratch[66];
+  const float* G = g + static_cast<int64_t>(blockIdx.x) * n;
+  float* D = dx0 + static_cast<int64_t>(blockIdx.x) * n;
+  float ss = 0.f, dot = 0.f;
+  for (int64_t i = threadIdx.x * 4; i < n; i += blockDim.x * 4) {
+    const float4 gv = *reinterpret_cast<const float4*>(G + i), dv = *reinterpret_cast<const float4*>(D + i);
+    const float a = bf16_round(gv.x), b = bf16_round(gv.y), c = bf16_round(gv.z), d = bf16_round(gv.w);
+    ss += a * a + b * b + c * c + d * d;
+    dot += a * dv.x + b * dv.y + c * dv.z + d * dv.w;
+  }
+  block_sum2(ss, dot, scratch);
+  const float nrm = bf16_round(sqrtf(ss)), den = bf16_round(nrm + 1e-7f);
+  const float inv = 1.0f / den, coef = dot / (den * den * fmaxf(nrm, 1e-30f));
+  for (int64_t i = threadIdx.x * 4; i < n; i += blockDim.x * 4) {
+    const float4 gv = *reinterpret_cast<const float4*>(G + i);
+    float4 dv = *reinterpret_cast<const float4*>(D + i);
+    dv.x = dv.x * inv - bf16_round(gv.x) * coef;
+    dv.y = dv.y * inv - bf16_round(gv.y) * coef;
+    dv.z = dv.z * inv - bf16_round(gv.z) * coef;
+    dv.w = dv.w * inv - bf16_round(gv.w) * coef;
+    *reinterpret_cast<float4*>(D + i) = dv;
+  }
+}
+
+// Momentum step of the reverse sweep for one batch entry per block, over the two gradient arrays (n0 and n1 elements
+// per entry):  dG += carry (the gradient that reaches this update's momentum state from the NEXT update, if any);
+// dbeta[b] = <dG, Mprev> (Mprev: momentum state before this update, or nullptr at the first update);
+// carry <- dG * beta[b] (what reaches the previous update's state); and a bf16 copy of dG for the contractions of
+// the fast-weight-gradient backward.  beta == nullptr: no momentum (only dG += 0 and the bf16 copy).
+struct MomentumBwdArgs {
+  float* dg[2];          // in/out
+  float* carry[2];       // in/out, or nullptr when there is no momentum
+  const float* mprev[2]; // or nullptr
+  bf16* dgb[2];          // out
+  const float* beta;     // [B] or nullptr
+  float* dbeta;          // [B] out (written, not accumulated), or nullptr
+  int64_t n[2];
+  int32_t add_carry;     // 0 at the last update of the program (nothing arrives from a later one)
+};
+__global__ void __launch_bounds__(1024) momentum_bwd_kernel(const MomentumBwdArgs a) {
+  __shared__ float scratch[66];
+  const int b = blockIdx.x;
+  const float bt = a.beta != nullptr ? a.beta[b] : 0.f;
+  float dot = 0.f, unused = 0.f;
+#pragma unroll
+  for (int w = 0; w < 2; ++w) {
+    const int64_t off = static_cast<int64_t>(b) * a.n[w];
+    for (int64_t i = threadIdx.x * 4; i < a.n[w]; i += blockDim.x * 4) {
+      float4 d = *reinterpret_cast<const float4*>(a.dg[w] + off + i);
+      if (a.carry[w] != nullptr && a.add_carry) {
+        const float4 c = *reinterpret_cast<const float4*>(a.carry[w] + off + i);
+        d.x += c.x; d.y += c.y; d.z += c.z; d.w += c.w;
+        *reinterpret_cast<float4*>(a.dg[w] + off + i) = d;
+      }
+      if (a.mprev[w] != nullptr) {
+        const float4 m = *reinterpret_cast<const float4*>(a.mprev[w] + off + i);
+        dot += d.x * m.x + d.y * m.y + d.z * m.z + d.w * m.w;
+      }
+      if (a.carry[w] != nullptr)
+        *reinterpret_cast<float4*>(a.carry[w] + off + i) = make_float4(d.x * bt, d.y * bt, d.z * bt, d.w * bt);
+      *reinterpret_cast<uint2*>(a.dgb[w] + off + i) = make_uint2(pack_bf16x2(d.x, d.y), pack_bf16x2(d.z, d.w));
+    }
+  }
+  block_sum2(dot, unused, scratch);
+  if (threadIdx.x == 0 && a.dbeta != nullptr) a.dbeta[b] = dot;
 }
 
 // ------------------------------------------------------------------------------------------
