@@ -271,6 +271,27 @@ int lact_bmm2_bf16(const void *a0, int32_t a0_mn_major, const void *b0, int32_t 
                    int32_t a1_mn_major, const void *b1, int32_t b1_mn_major, void *c, int32_t c_dtype,
                    int32_t accumulate, int64_t batch, int64_t M, int64_t N, int64_t K, int32_t *status_word,
                    void *stream);
+/* One or two independent batched products c (+)= a0 b0^T [+ a1 b1^T] in ONE persistent launch (the training backward
+ * pairs products that share a shape class, halving its launches).  Fields as the arguments of
+ * lact_bmm2_strided_bf16; both problems single-product or both two-product.  No counterpart in the reference. */
+typedef struct lact_bmm_desc {
+  const void *a0, *b0, *a1, *b1; /* a1 = b1 = NULL: single product */
+  void *c;
+  int64_t a0_ld, a0_bs, b0_ld, b0_bs, a1_ld, a1_bs, b1_ld, b1_bs, c_ld, c_bs;
+  int64_t batch, M, N, K;
+  int32_t a0_mn, b0_mn, a1_mn, b1_mn, c_dtype, accumulate;
+} lact_bmm_desc;
+int lact_bmm_group_bf16(const lact_bmm_desc *problems, int32_t n, int32_t *status_word, void *stream);
+
+/* The pointwise stage of lact_fw_grad alone: dy02[B, N, 2H] = [dy0 * lr0 | dy2 * lr2], hid[B, N, H] = hidden * lr1
+ * (bf16) from k, v [B, N, D] (bf16; token / batch strides in elements) -- lact_fw_grad.py:25-58.  A NULL learning
+ * rate stands for 1 (lr: [B, *] with batch stride lr_bs): with (k, v) = (q, dO) this is the backward of apply's
+ * pre-activations, lact_swiglu_ffn.py:46-76. */
+int lact_fw_grad_pointwise(const void *w0w2, const void *w1, const void *k, int64_t k_ts, int64_t k_bs, const void *v,
+                           int64_t v_ts, int64_t v_bs, const void *lr0, const void *lr1, const void *lr2,
+                           int32_t lr_dtype, int64_t lr_bs, float w_scale, void *dy02, void *hid, int64_t B, int64_t N,
+                           int64_t D, int64_t H, int32_t *status_word, void *stream);
+
 /* The same product on strided operands and result (views of larger tensors, e.g. a token range of [B, L, D]):
  * *_ld = row stride, *_bs = batch stride, in elements (multiples of 8; base pointers 16-byte aligned). */
 int lact_bmm2_strided_bf16(const void *a0, int32_t a0_mn_major, int64_t a0_ld, int64_t a0_bs, const void *b0,
@@ -307,9 +328,26 @@ int lact_renorm_bwd(const void *base, const void *upd, int32_t upd_dtype, const 
  *     dx0 [nmat][n] (fp32, in/out) <- dx0 / den - bf16(g) <dx0, bf16(g)> / (den^2 nrm), nrm = bf16(||bf16(g)||),
  *     den = bf16(nrm + 1e-7), g [nmat][n] fp32;
  *   lact_momentum_bwd: momentum step (ttt_operation.py:170-179) for both gradient arrays (n0, n1 fp32 elements per
- *     batch entry): dg += carry (if add_carry); dbeta[b] = <dg, mprev> (mprev NULL at the first update);
+ *     batch entry): dg += carry (if add_carry); sum over s of dbeta[b][s] = <dg, mprev> (mprev NULL at the first update);
  *     carry <- dg * beta[b]; dgb = bf16(dg).  carry / beta NULL: no momentum (bf16 copy only). */
-int lact_ns_norm_bwd(const void *g, void *dx0, int64_t nmat, int64_t elems_per_matrix, void *stream);
+/* The same backward for one or two groups of matrices (e.g. the [w0; w2] and the w1 gradients of one update) in ONE
+ * cooperative launch, followed by the normalisation backward: dg = d loss / d G (fp32, written).  Needs the trace of
+ * lact_ns_trace_fwd / the training scan (steps <= 5).  LACT_ERR_CONFIG when no fused instantiation covers the shapes:
+ * call lact_ns_trace_bwd + lact_ns_norm_bwd per group instead. */
+typedef struct lact_ns_bwd_group {
+  const void *du;    /* bf16 [nmat][rows][cols]: gradient w.r.t. the iteration's result */
+  const void *g;     /* fp32 [nmat][rows][cols]: the matrix the iteration started from (before normalisation) */
+  void *dg;          /* fp32 [nmat][rows][cols], written */
+  void *trace;       /* the group's trace */
+  size_t trace_bytes;
+  void *partials;    /* fp32 scratch, nmat * 2 * lact_momentum_bwd_slices() */
+  int64_t nmat, rows, cols;
+} lact_ns_bwd_group;
+int lact_ns_trace_bwd_fused(const lact_ns_bwd_group *groups, int32_t ngroups, int32_t steps, int32_t const_coeffs,
+                            int32_t gram_right, int32_t *status_word, void *stream);
+int lact_ns_norm_bwd(const void *g, void *dx0, void *partials /* fp32 scratch, nmat * 2 * lact_momentum_bwd_slices() */,
+                     int64_t nmat, int64_t elems_per_matrix, void *stream);
+int lact_momentum_bwd_slices(void); /* slices per batch entry: dbeta of lact_momentum_bwd is [B][slices] partial sums */
 int lact_momentum_bwd(void *dg0, void *dg1, void *carry0, void *carry1, const void *mprev0, const void *mprev1,
                       void *dgb0, void *dgb1, const void *beta, void *dbeta, int64_t B, int64_t n0, int64_t n1,
                       int32_t add_carry, void *stream);

@@ -31,6 +31,24 @@ class ScanIO(C.Structure):
                                           "m2_out", "state_dump", "ns_trace")]
 
 
+ERR_CONFIG = -5  # LACT_ERR_CONFIG
+
+
+class BmmDesc(C.Structure):
+    """lact_bmm_desc of the C header."""
+    _fields_ = ([(n, C.c_void_p) for n in ("a0", "b0", "a1", "b1", "c")] +
+                [(n, C.c_int64) for n in ("a0_ld", "a0_bs", "b0_ld", "b0_bs", "a1_ld", "a1_bs", "b1_ld", "b1_bs",
+                                          "c_ld", "c_bs", "batch", "M", "N", "K")] +
+                [(n, C.c_int32) for n in ("a0_mn", "b0_mn", "a1_mn", "b1_mn", "c_dtype", "accumulate")])
+
+
+class NsBwdGroup(C.Structure):
+    """lact_ns_bwd_group of the C header."""
+    _fields_ = [("du", C.c_void_p), ("g", C.c_void_p), ("dg", C.c_void_p), ("trace", C.c_void_p),
+                ("trace_bytes", C.c_size_t), ("partials", C.c_void_p), ("nmat", C.c_int64), ("rows", C.c_int64),
+                ("cols", C.c_int64)]
+
+
 _lib: Optional[C.CDLL] = None
 
 
@@ -86,7 +104,12 @@ def _declare(lib: C.CDLL) -> None:
     lib.lact_fw_grad_bwd_pointwise.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, f32, vp, vp, vp, vp, vp, vp, vp, i64,
                                                i64, vp]
     lib.lact_renorm_bwd.argtypes = [vp, vp, i32, vp, vp, vp, vp, vp, i64, i64, i32, vp]
-    lib.lact_ns_norm_bwd.argtypes = [vp, vp, i64, i64, vp]
+    lib.lact_ns_norm_bwd.argtypes = [vp, vp, vp, i64, i64, vp]
+    lib.lact_momentum_bwd_slices.restype = C.c_int
+    lib.lact_bmm_group_bf16.argtypes = [C.POINTER(BmmDesc), i32, vp, vp]
+    lib.lact_fw_grad_pointwise.argtypes = [vp, vp, vp, i64, i64, vp, i64, i64, vp, vp, vp, i32, i64, f32, vp, vp, i64, i64,
+                                           i64, i64, vp, vp]
+    lib.lact_ns_trace_bwd_fused.argtypes = [C.POINTER(NsBwdGroup), i32, i32, i32, i32, vp, vp]
     lib.lact_ns_norm_bwd.restype = C.c_int
     lib.lact_momentum_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i32, vp]
     lib.lact_momentum_bwd.restype = C.c_int

@@ -60,10 +60,9 @@ def _strided(t):
     return t, t.stride(1), t.stride(0)
 
 
-def gemm(a, b, a_mn=False, b_mn=False, a1=None, b1=None, a1_mn=False, b1_mn=False, out=None,
-         out_dtype=torch.float32, accumulate=False):
-    """c[batch, M, N] (+)= a b^T (+ a1 b1^T).  Operands bf16, [batch, rows, K] or (``*_mn``) [batch, K, rows];
-    operands and `out` may be views into larger tensors (token ranges)."""
+def _desc(a, b, a_mn=False, b_mn=False, a1=None, b1=None, a1_mn=False, b1_mn=False, out=None,
+          out_dtype=torch.float32, accumulate=False):
+    """(lact_bmm_desc, output tensor, tensors to keep alive) for c[batch, M, N] (+)= a b^T (+ a1 b1^T)."""
     a, a_ld, a_bs = _strided(a)
     b, b_ld, b_bs = _strided(b)
     batch = a.shape[0]
@@ -76,36 +75,63 @@ def gemm(a, b, a_mn=False, b_mn=False, a1=None, b1=None, a1_mn=False, b1_mn=Fals
     if a1 is not None:
         a1, a1_ld, a1_bs = _strided(a1)
         b1, b1_ld, b1_bs = _strided(b1)
-    st = _status_word(a.device)
-    rc = L.lib().lact_bmm2_strided_bf16(a.data_ptr(), int(a_mn), a_ld, a_bs, b.data_ptr(), int(b_mn), b_ld, b_bs,
-                                        a1.data_ptr() if a1 is not None else None, int(a1_mn), a1_ld, a1_bs,
-                                        b1.data_ptr() if b1 is not None else None, int(b1_mn), b1_ld, b1_bs,
-                                        out.data_ptr(), L.dtype_code(out), out.stride(1), out.stride(0), int(accumulate),
-                                        batch, M, N, K, st.data_ptr(), L.stream_ptr())
-    L.check(rc, "lact_bmm2_strided_bf16")
+    d = L.BmmDesc(a.data_ptr(), b.data_ptr(), a1.data_ptr() if a1 is not None else None,
+                  b1.data_ptr() if b1 is not None else None, out.data_ptr(), a_ld, a_bs, b_ld, b_bs, a1_ld, a1_bs,
+                  b1_ld, b1_bs, out.stride(1), out.stride(0), batch, M, N, K, int(a_mn), int(b_mn), int(a1_mn),
+                  int(b1_mn), L.dtype_code(out), int(accumulate))
+    return d, out, (a, b, a1, b1)
+
+
+def gemm(a, b, **kw):
+    """c[batch, M, N] (+)= a b^T (+ a1 b1^T).  Operands bf16, [batch, rows, K] or (``*_mn``) [batch, K, rows];
+    operands and `out` may be views into larger tensors (token ranges).  Keywords: a_mn, b_mn, a1, b1, a1_mn, b1_mn,
+    out, out_dtype (fp32), accumulate."""
+    d, out, _keep = _desc(a, b, **kw)
+    rc = L.lib().lact_bmm_group_bf16(C.byref(d), 1, _status_word(out.device).data_ptr(), L.stream_ptr())
+    L.check(rc, "lact_bmm_group_bf16")
     return out
+
+
+def gemm_pair(spec0, spec1):
+    """Two independent products (each spec = (a, b, keywords of `gemm`)) in one launch; returns their outputs."""
+    d0, out0, _k0 = _desc(spec0[0], spec0[1], **spec0[2])
+    d1, out1, _k1 = _desc(spec1[0], spec1[1], **spec1[2])
+    pair = (L.BmmDesc * 2)(d0, d1)
+    rc = L.lib().lact_bmm_group_bf16(pair, 2, _status_word(out0.device).data_ptr(), L.stream_ptr())
+    L.check(rc, "lact_bmm_group_bf16")
+    return out0, out1
 
 
 def _vecptr(t: Optional[torch.Tensor]):
     return t.data_ptr() if t is not None else None
 
 
+def _tok_strides(t):
+    """A [B, n, D] bf16 activation view as (tensor, token stride, batch stride) for entry points that take strides."""
+    if t.stride(2) != 1 or t.stride(1) % 8 or t.stride(0) % 8 or t.data_ptr() % 16 or t.stride(1) < t.shape[2]:
+        t = t.contiguous()
+    return t, t.stride(1), t.stride(0)
+
+
 def apply_backward(w02b, w1b, q, dO, dW02, dW1, dq_out=None):
     """Backward of o = w1 (silu(w0 q) * (w2 q)) on one token range.  Accumulates the weight gradients
     (fp32) into dW02 / dW1 and returns dq (bf16; written into the view `dq_out` if given).
-    lact_swiglu_ffn.py:46-76."""
+    lact_swiglu_ffn.py:46-76.  Three launches: the pre-activations y0, y2 = q w0^T, q w2^T and dh = dO w1 with the
+    pointwise stage in their epilogue (the fast-weight gradient's own kernel with unit learning rates), both weight
+    gradients, dq."""
     B, n, D = q.shape
     H = w1b.shape[2]
-    y02 = gemm(q, w02b, out_dtype=BF16)                      # [B, n, 2H]
-    dh = gemm(dO, w1b, b_mn=True, out_dtype=BF16)            # [B, n, H]   dO w1
-    dy02 = torch.empty_like(y02)
-    hid = torch.empty_like(dh)
-    L.check(L.lib().lact_swiglu_bwd_planes(y02.data_ptr(), dh.data_ptr(), None, None, None, L.LACT_F32, 1.0,
-                                           dy02.data_ptr(), hid.data_ptr(), B * n, H, L.stream_ptr()),
-            "lact_swiglu_bwd_planes")
-    gemm(dy02, q, a_mn=True, b_mn=True, out=dW02, accumulate=True)   # [2H, D] += dy02^T q
-    gemm(dO, hid, a_mn=True, b_mn=True, out=dW1, accumulate=True)    # [D, H]  += dO^T hidden
-    return gemm(dy02, w02b, b_mn=True, out=dq_out, out_dtype=BF16)   # dq = dy02 w02
+    dy02 = torch.empty(B, n, 2 * H, dtype=BF16, device=q.device)
+    hid = torch.empty(B, n, H, dtype=BF16, device=q.device)
+    qs, q_ts, q_bs = _tok_strides(q)
+    ds, d_ts, d_bs = _tok_strides(dO)
+    L.check(L.lib().lact_fw_grad_pointwise(w02b.data_ptr(), w1b.data_ptr(), qs.data_ptr(), q_ts, q_bs, ds.data_ptr(), d_ts,
+                                           d_bs, None, None, None, L.LACT_F32, 0, 1.0, dy02.data_ptr(), hid.data_ptr(),
+                                           B, n, D, H, _status_word(q.device).data_ptr(), L.stream_ptr()),
+            "lact_fw_grad_pointwise")
+    gemm_pair((dy02, q, dict(a_mn=True, b_mn=True, out=dW02, accumulate=True)),     # [2H, D] += dy02^T q
+              (dO, hid, dict(a_mn=True, b_mn=True, out=dW1, accumulate=True)))      # [D, H]  += dO^T hidden
+    return gemm(dy02, w02b, b_mn=True, out=dq_out, out_dtype=BF16)                  # dq = dy02 w02
 
 
 def fw_grad_backward(w02b, w1b, k, v, lr0, lr1, lr2, w_scale, gG02, gG1, dW02, dW1, dk_out=None, dv_out=None,
@@ -113,15 +139,14 @@ def fw_grad_backward(w02b, w1b, k, v, lr0, lr1, lr2, w_scale, gG02, gG1, dW02, d
     """Backward of the lr-weighted fast-weight gradient on one token range, given the gradients gG02
     ([B,2H,D]) / gG1 ([B,D,H]) of its outputs.  Accumulates into dW02 / dW1; returns
     (dk, dv [bf16; written into the views `dk_out` / `dv_out` if given], dlr0, dlr1, dlr2 [fp32, B x n]).
-    lact_fw_grad.py:61-156."""
+    lact_fw_grad.py:61-156.  Products that share a shape class run two per launch."""
     B, n, D = k.shape
     H = w1b.shape[2]
     if g02b is None:
         g02b, g1b = gG02.to(BF16), gG1.to(BF16)
-    y02 = gemm(k, w02b, out_dtype=BF16)
-    dh = gemm(v, w1b, b_mn=True, out_dtype=BF16)
-    g_dy02 = gemm(k, g02b, out_dtype=BF16)                   # [B, n, 2H]
-    g_hid = gemm(v, g1b, b_mn=True, out_dtype=BF16)          # [B, n, H]
+    bf = dict(out_dtype=BF16)
+    y02, g_dy02 = gemm_pair((k, w02b, bf), (k, g02b, bf))                                  # [B, n, 2H] each
+    dh, g_hid = gemm_pair((v, w1b, dict(b_mn=True, out_dtype=BF16)), (v, g1b, dict(b_mn=True, out_dtype=BF16)))
     g_y02, dy02l = torch.empty_like(y02), torch.empty_like(y02)
     g_dh, hidl = torch.empty_like(dh), torch.empty_like(dh)
     glr = [torch.empty(B, n, dtype=torch.float32, device=k.device) for _ in range(3)]
@@ -131,10 +156,10 @@ def fw_grad_backward(w02b, w1b, k, v, lr0, lr1, lr2, w_scale, gG02, gG1, dW02, d
         lr2.data_ptr(), L.dtype_code(lr0), float(w_scale), g_y02.data_ptr(), g_dh.data_ptr(), dy02l.data_ptr(),
         hidl.data_ptr(), glr[0].data_ptr(), glr[1].data_ptr(), glr[2].data_ptr(), B * n, H, L.stream_ptr()),
         "lact_fw_grad_bwd_pointwise")
-    dk = gemm(g_y02, w02b, b_mn=True, a1=dy02l, b1=g02b, b1_mn=True, out=dk_out, out_dtype=BF16)
-    dv = gemm(g_dh, w1b, a1=hidl, b1=g1b, out=dv_out, out_dtype=BF16)
-    gemm(g_y02, k, a_mn=True, b_mn=True, out=dW02, accumulate=True)
-    gemm(v, g_dh, a_mn=True, b_mn=True, out=dW1, accumulate=True)
+    dk, dv = gemm_pair((g_y02, w02b, dict(b_mn=True, a1=dy02l, b1=g02b, b1_mn=True, out=dk_out, out_dtype=BF16)),
+                       (g_dh, w1b, dict(a1=hidl, b1=g1b, out=dv_out, out_dtype=BF16)))
+    gemm_pair((g_y02, k, dict(a_mn=True, b_mn=True, out=dW02, accumulate=True)),
+              (v, g_dh, dict(a_mn=True, b_mn=True, out=dW1, accumulate=True)))
     return dk, dv, glr[0], glr[1], glr[2]
 
 
@@ -193,8 +218,41 @@ def ns_backward(saved, dU):
     # dX0 / den - bf16(G) <dX0, bf16(G)> / (den^2 ||bf16(G)||), in place in dX0
     G = saved["G"]
     G = G if (G.dtype == torch.float32 and G.is_contiguous()) else G.float().contiguous()
-    L.check(L.lib().lact_ns_norm_bwd(G.data_ptr(), dX0.data_ptr(), nmat, R * Cc, L.stream_ptr()), "lact_ns_norm_bwd")
+    part = torch.empty(nmat * 2 * L.lib().lact_momentum_bwd_slices(), dtype=torch.float32, device=du.device)
+    L.check(L.lib().lact_ns_norm_bwd(G.data_ptr(), dX0.data_ptr(), part.data_ptr(), nmat, R * Cc, L.stream_ptr()),
+            "lact_ns_norm_bwd")
     return dX0
+
+
+def ns_backward_groups(saved, dUs):
+    """`ns_backward` for one or two groups of matrices at once: all iterations of all groups in one cooperative
+    launch (`lact_ns_trace_bwd_fused`) when an instantiation covers the shapes, else one group after the other."""
+    same = all(sv["steps"] == saved[0]["steps"] and sv["cc"] == saved[0]["cc"] and sv["gr"] == saved[0]["gr"]
+               for sv in saved)
+    if same and saved[0]["steps"] <= 5 and len(saved) <= 2:
+        dev = dUs[0].device
+        slices = L.lib().lact_momentum_bwd_slices()
+        groups = (L.NsBwdGroup * len(saved))()
+        keep, outs = [], []
+        for i, (sv, dU) in enumerate(zip(saved, dUs)):
+            nmat, R, Cc = sv["shape"]
+            du = (dU if dU.dtype == BF16 else dU.to(BF16)).contiguous()
+            G = sv["G"]
+            G = G if (G.dtype == torch.float32 and G.is_contiguous()) else G.float().contiguous()
+            dg = torch.empty(nmat, R, Cc, dtype=torch.float32, device=dev)
+            part = torch.empty(nmat * 2 * slices, dtype=torch.float32, device=dev)
+            keep += [du, G, part]
+            outs.append(dg)
+            groups[i] = L.NsBwdGroup(du.data_ptr(), G.data_ptr(), dg.data_ptr(), sv["trace"].data_ptr(),
+                                     sv["trace"].numel(), part.data_ptr(), nmat, R, Cc)
+        with torch.cuda.device(dev):
+            rc = L.lib().lact_ns_trace_bwd_fused(groups, len(saved), saved[0]["steps"], saved[0]["cc"], saved[0]["gr"],
+                                                 _status_word(dev).data_ptr(), L.stream_ptr())
+        if rc == 0:
+            return outs
+        if rc != L.ERR_CONFIG:
+            L.check(rc, "lact_ns_trace_bwd_fused")
+    return [ns_backward(sv, dU) for sv, dU in zip(saved, dUs)]
 
 
 def scan_forward_saving(opts, steps, w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum):
@@ -323,20 +381,23 @@ def scan_backward(opts, steps, w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, dum
     dM02 = dM1 = None
     dn02 = torch.zeros(B, 2 * H, dtype=f32, device=dev)
     dn1 = torch.zeros(B, D, dtype=f32, device=dev)
-    # every token range is written in place by the first step that produces a gradient for it: zero-filling (a full
-    # pass over three [B, L, D] tensors) is needed only where no step does
-    def covered(kind_):
-        end_ = 0
+    # every token range is written in place by the first step that produces a gradient for it: only the gaps no
+    # step covers are zero-filled
+    def gaps(kind_):
+        out_, end_ = [], 0
         for s_, e_ in sorted((st[1], st[2]) for st in steps if st[0] == kind_ and st[2] > st[1]):
             if s_ > end_:
-                return False
+                out_.append((end_, s_))
             end_ = max(end_, e_)
-        return end_ >= Ltok
-    alloc_q = torch.empty_like if covered(P.APPLY) else torch.zeros_like
-    alloc_kv = torch.empty_like if covered(P.UPDATE) else torch.zeros_like
-    dq = alloc_q(q, dtype=BF16)
-    dk = alloc_kv(k, dtype=BF16)
-    dv = alloc_kv(v, dtype=BF16)
+        if end_ < Ltok:
+            out_.append((end_, Ltok))
+        return out_
+    dq, dk, dv = torch.empty_like(q, dtype=BF16), torch.empty_like(k, dtype=BF16), torch.empty_like(v, dtype=BF16)
+    for a_, b_ in gaps(P.APPLY):
+        dq[:, a_:b_].zero_()
+    for a_, b_ in gaps(P.UPDATE):
+        dk[:, a_:b_].zero_()
+        dv[:, a_:b_].zero_()
     dlr = [torch.zeros(B, Ltok, dtype=f32, device=dev) for _ in range(3)]
     dmom = torch.zeros(B, Ltok, dtype=f32, device=dev) if has_momentum else None
     dO = dO.to(BF16)
@@ -400,8 +461,9 @@ def scan_backward(opts, steps, w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, dum
             dWn02 += dWm02
             dWn1 += dWm1
         if sv02 is not None:
-            dG02 = ns_backward(sv02, (dWn02b if dWn02b is not None else dWn02).view(sv02["shape"])).view(B, 2 * H, D)
-            dG1 = ns_backward(sv1, dWn1b if dWn1b is not None else dWn1)
+            dG02, dG1 = ns_backward_groups([sv02, sv1], [(dWn02b if dWn02b is not None else dWn02).view(sv02["shape"]),
+                                                         dWn1b if dWn1b is not None else dWn1])
+            dG02 = dG02.view(B, 2 * H, D)
             if overwrite:
                 dG02 += dWn02
                 dG1 += dWn1
@@ -423,7 +485,7 @@ def scan_backward(opts, steps, w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, dum
             beta = momv[:, s:e].mean(dim=1).contiguous()  # [B]
             if u > 0:
                 mp02, mp1 = grad_state(u - 1)
-                dbeta = torch.empty(B, dtype=f32, device=dev)
+                dbeta = torch.empty(B, L.lib().lact_momentum_bwd_slices(), dtype=f32, device=dev)
             if dM02 is None:
                 dM02, dM1, add_carry = torch.empty_like(dG02), torch.empty_like(dG1), 0
             else:
@@ -433,7 +495,7 @@ def scan_backward(opts, steps, w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, dum
                                           g02b.data_ptr(), g1b.data_ptr(), _vecptr(beta), _vecptr(dbeta), B, 2 * H * D,
                                           D * H, add_carry if has_momentum else 0, L.stream_ptr()), "lact_momentum_bwd")
         if dbeta is not None:
-            dmom[:, s:e] += (dbeta / float(e - s)).unsqueeze(1)
+            dmom[:, s:e] += (dbeta.sum(dim=1) / float(e - s)).unsqueeze(1)
         w02b, w1b = shadow(u)
         if fresh(kv_done, s, e):
             _, _, g0, g1, g2 = fw_grad_backward(w02b, w1b, k[:, s:e], v[:, s:e], lr0v[:, s:e], lr1v[:, s:e],

@@ -13,7 +13,7 @@
 #include <vector>
 
 #include "../../include/lact_b200.h"
-#include "ns_fused.cuh"
+#include "ns_bwd_fused.cuh"
 
 namespace lact {
 namespace {
@@ -378,38 +378,45 @@ struct GradArgs {
 
 inline int contract_bt(int64_t D, int64_t H) { return choose_bt({{D, 2 * H}, {H, D}}); }
 
-int run_grad(const GradArgs& a, int32_t* status, cudaStream_t stream) {
+// Pointwise stage: dy02 = [dy0 | dy2] ([B][len][2H]) and hid = hidden * lr1 ([B][len][H]) for tokens [start, end).
+int run_grad_pointwise(const GradArgs& a, int32_t* status, cudaStream_t stream) {
   const int64_t len = a.end - a.start;
   if (len <= 0) return LACT_ERR_STEPS;
   const Mat w02{a.w02b, 2 * a.H, a.D, a.D, a.B, 2 * a.H * a.D};
   const Mat w1{a.w1b, a.D, a.H, a.H, a.B, a.D * a.H};
   const Mat km{a.k, a.end, a.D, a.k_ts, a.B, a.k_bs};
   const Mat vm{a.v, a.end, a.D, a.v_ts, a.B, a.v_bs};
+  const Mat hid{a.hid, len, a.H, a.H, a.B, len * a.H};
+  GemmArgs<OpFwGradPointwise, 1> g;
+  std::memset(&g, 0, sizeof(g));
+  auto& P = g.prob[0];
+  constexpr int BT = OpFwGradPointwise::BT;
+  LACT_TRY(make_operand(kb_of(P), &P.a[0], &P.ai[0], km, 0, kBM, static_cast<int>(a.start), 0));
+  LACT_TRY(make_operand(kb_of(P), &P.a[1], &P.ai[1], vm, 0, kBM, static_cast<int>(a.start), 0));
+  LACT_TRY(make_operand(kb_of(P), &P.b[0], &P.bi[0], w02, 0, BT, 0, 0));
+  LACT_TRY(make_operand(kb_of(P), &P.b[1], &P.bi[1], w02, 0, BT, static_cast<int>(a.H), 0));
+  // dh = v w1: w1 is [D][H], i.e. k (= D) rows with the n (= H) axis contiguous
+  LACT_TRY(make_operand(kb_of(P), &P.b[2], &P.bi[2], w1, 1, BT, 0, 0));
+  P.M = static_cast<int>(len); P.N = static_cast<int>(a.H); P.K = static_cast<int>(a.D);
+  P.batch = static_cast<int>(a.B);
+  P.ep = EpiFwGrad{a.lr0, a.lr1, a.lr2, a.lr_f32, static_cast<int32_t>(a.start), a.lr_bs, a.w_scale};
+  // dy0 and dy2 share the [len][2H] plane: two maps of H columns each, so neither can spill
+  const Mat dy0m{a.dy02, len, a.H, 2 * a.H, a.B, len * 2 * a.H};
+  const Mat dy2m{a.dy02 + a.H, len, a.H, 2 * a.H, a.B, len * 2 * a.H};
+  LACT_TRY(make_output(&P.out[0], &P.oi[0], dy0m, 0, 0));
+  LACT_TRY(make_output(&P.out[1], &P.oi[1], dy2m, 0, 0));
+  LACT_TRY(make_output(&P.out[2], &P.oi[2], hid, 0, 0));
+  g.status = status;
+  return launch_gemm(g, stream, kClsGradPointwise);
+}
+
+int run_grad(const GradArgs& a, int32_t* status, cudaStream_t stream) {
+  const int64_t len = a.end - a.start;
+  LACT_TRY(run_grad_pointwise(a, status, stream));
+  const Mat km{a.k, a.end, a.D, a.k_ts, a.B, a.k_bs};
+  const Mat vm{a.v, a.end, a.D, a.v_ts, a.B, a.v_bs};
   const Mat dy{a.dy02, len, 2 * a.H, 2 * a.H, a.B, len * 2 * a.H};
   const Mat hid{a.hid, len, a.H, a.H, a.B, len * a.H};
-  {
-    GemmArgs<OpFwGradPointwise, 1> g;
-    std::memset(&g, 0, sizeof(g));
-    auto& P = g.prob[0];
-    constexpr int BT = OpFwGradPointwise::BT;
-    LACT_TRY(make_operand(kb_of(P), &P.a[0], &P.ai[0], km, 0, kBM, static_cast<int>(a.start), 0));
-    LACT_TRY(make_operand(kb_of(P), &P.a[1], &P.ai[1], vm, 0, kBM, static_cast<int>(a.start), 0));
-    LACT_TRY(make_operand(kb_of(P), &P.b[0], &P.bi[0], w02, 0, BT, 0, 0));
-    LACT_TRY(make_operand(kb_of(P), &P.b[1], &P.bi[1], w02, 0, BT, static_cast<int>(a.H), 0));
-    // dh = v w1: w1 is [D][H], i.e. k (= D) rows with the n (= H) axis contiguous
-    LACT_TRY(make_operand(kb_of(P), &P.b[2], &P.bi[2], w1, 1, BT, 0, 0));
-    P.M = static_cast<int>(len); P.N = static_cast<int>(a.H); P.K = static_cast<int>(a.D);
-    P.batch = static_cast<int>(a.B);
-    P.ep = EpiFwGrad{a.lr0, a.lr1, a.lr2, a.lr_f32, static_cast<int32_t>(a.start), a.lr_bs, a.w_scale};
-    // dy0 and dy2 share the [len][2H] plane: two maps of H columns each, so neither can spill
-    const Mat dy0m{a.dy02, len, a.H, 2 * a.H, a.B, len * 2 * a.H};
-    const Mat dy2m{a.dy02 + a.H, len, a.H, 2 * a.H, a.B, len * 2 * a.H};
-    LACT_TRY(make_output(&P.out[0], &P.oi[0], dy0m, 0, 0));
-    LACT_TRY(make_output(&P.out[1], &P.oi[1], dy2m, 0, 0));
-    LACT_TRY(make_output(&P.out[2], &P.oi[2], hid, 0, 0));
-    g.status = status;
-    LACT_TRY(launch_gemm(g, stream, kClsGradPointwise));
-  }
   // token contraction: [dw0; dw2] = dy02^T k  and  dw1 = v^T hidden
   const int bt = contract_bt(a.D, a.H);
   auto fill = [&](auto& g, int btv) -> int {
@@ -768,6 +775,116 @@ int plan_ns_trace(void* base, int64_t B, int64_t R, int64_t C, int steps, int gr
   t->dXa = cv.take<bf16>(rc);
   t->dXb = cv.take<bf16>(rc);
   t->bytes = cv.off + 256;
+  return LACT_OK;
+}
+
+
+static int ns_norm_bwd_launch(const float* g, const void* dx0, int dx_bf16, float* dg, float* partials, int64_t nmat,
+                              int64_t elems, cudaStream_t s) {
+  if (nmat < 1 || nmat > 65535 * 16 || elems < 4 || (elems % 4) != 0) return LACT_ERR_SHAPE;
+  if (((reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(dx0) | reinterpret_cast<uintptr_t>(dg)) & 15) != 0)
+    return LACT_ERR_SHAPE;
+  const dim3 grid(static_cast<unsigned>(nmat), kNormBwdSlices);
+  {
+    KernelScope scope(kClsOther, s);
+    ns_norm_bwd_partial_kernel<<<grid, 512, 0, s>>>(g, dx0, dx_bf16, partials, elems);
+    LACT_CUDA(cudaGetLastError());
+  }
+  KernelScope scope(kClsOther, s);
+  ns_norm_bwd_apply_kernel<<<grid, 512, 0, s>>>(g, dx0, dx_bf16, dg, partials, elems);
+  LACT_CUDA(cudaGetLastError());
+  return LACT_OK;
+}
+
+// ---- all iterations of the Newton-Schulz backward of one or two groups in one cooperative launch
+template <int BT>
+static int launch_ns_bwd_fused(const NsTrace* tr, const bf16* const* du, int ngroups, int steps, int const_coeffs,
+                               int32_t* status, cudaStream_t stream) {
+  constexpr int NITER = 5;
+  using Args = NsBwdFusedArgs<BT, NITER>;
+  auto kernel = ns_bwd_fused_kernel<BT, NITER>;
+  constexpr uint32_t smem = ns_bwd_smem_bytes<BT>();
+  static_assert(smem <= 232448, "shared memory budget exceeded");
+  static_assert(ns_bwd_ring<BT>() >= 2, "ring too shallow");
+  static_assert(sizeof(Args) <= 32000, "kernel parameter block too large");
+  static std::mutex mu;
+  static bool configured[64] = {false};
+  int dev = 0;
+  LACT_CUDA(cudaGetDevice(&dev));
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev >= 64 || !configured[dev]) {
+      LACT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      if (dev < 64) configured[dev] = true;
+    }
+  }
+  std::vector<uint8_t> storage(sizeof(Args));
+  Args& args = *reinterpret_cast<Args*>(storage.data());
+  std::memset(&args, 0, sizeof(args));
+  int64_t max_tiles = 1;
+  for (int g = 0; g < ngroups; ++g) {
+    const NsTrace& t = tr[g];
+    const NsGroup& G = t.grp;
+    const int64_t rc1 = static_cast<int64_t>(G.R) * G.C, mm1 = static_cast<int64_t>(G.m) * G.m;
+    const int64_t rc = rc1 * G.nmat, mm = mm1 * G.nmat;
+    const int tall = G.transposed;
+    const Mat Q{t.Q, G.m, G.m, G.m, G.nmat, mm1};
+    const Mat T{t.S, G.m, G.m, G.m, G.nmat, mm1};
+    const bf16* dX = du[g];
+    for (int it = steps - 1; it >= 0; --it) {
+      bf16* out = (it & 1) ? t.dXa : t.dXb;
+      const Mat X{t.X + rc * it, G.R, G.C, G.C, G.nmat, rc1};
+      const Mat D{dX, G.R, G.C, G.C, G.nmat, rc1};
+      const Mat O{out, G.R, G.C, G.C, G.nmat, rc1};
+      const Mat S{t.A + mm * it, G.m, G.m, G.m, G.nmat, mm1};
+      const Mat PB{t.P + mm * it, G.m, G.m, G.m, G.nmat, mm1};
+      auto& pq = args.q[it][g];
+      auto& pt = args.t[it][g];
+      auto& px = args.dx[it][g];
+      // Q = dX X^T + X dX^T (wide; the iterate's rows are K-major operands) / dX^T X + X^T dX (tall; MN-major)
+      LACT_TRY(make_operand(1, &pq.a[0], &pq.ai[0], D, tall, kBM, 0, 0));
+      LACT_TRY(make_operand(1, &pq.b[0], &pq.bi[0], X, tall, BT, 0, 0));
+      LACT_TRY(make_operand(1, &pq.a[1], &pq.ai[1], X, tall, kBM, 0, 0));
+      LACT_TRY(make_operand(1, &pq.b[1], &pq.bi[1], D, tall, BT, 0, 0));
+      pq.M = G.m; pq.N = G.m; pq.K = G.n; pq.batch = G.nmat;
+      LACT_TRY(make_output(&pq.out[0], &pq.oi[0], Q, 0, 0));
+      // T = c (S Q + Q S): all three symmetric, rows serve as K-major operands on either side
+      LACT_TRY(make_operand(1, &pt.a[0], &pt.ai[0], S, 0, kBM, 0, 0));
+      LACT_TRY(make_operand(1, &pt.b[0], &pt.bi[0], Q, 0, BT, 0, 0));
+      LACT_TRY(make_operand(1, &pt.a[1], &pt.ai[1], Q, 0, kBM, 0, 0));
+      LACT_TRY(make_operand(1, &pt.b[1], &pt.bi[1], S, 0, BT, 0, 0));
+      pt.M = G.m; pt.N = G.m; pt.K = G.m; pt.batch = G.nmat;
+      LACT_TRY(make_output(&pt.out[0], &pt.oi[0], T, 0, 0));
+      // dX_i = P dX + T X (wide: the [k][n] iterates are MN-major B operands) / dX P + X T (tall)
+      if (!tall) {
+        LACT_TRY(make_operand(1, &px.a[0], &px.ai[0], PB, 0, kBM, 0, 0));
+        LACT_TRY(make_operand(1, &px.b[0], &px.bi[0], D, 1, BT, 0, 0));
+        LACT_TRY(make_operand(1, &px.a[1], &px.ai[1], T, 0, kBM, 0, 0));
+        LACT_TRY(make_operand(1, &px.b[1], &px.bi[1], X, 1, BT, 0, 0));
+      } else {
+        LACT_TRY(make_operand(1, &px.a[0], &px.ai[0], D, 0, kBM, 0, 0));
+        LACT_TRY(make_operand(1, &px.b[0], &px.bi[0], PB, 0, BT, 0, 0));
+        LACT_TRY(make_operand(1, &px.a[1], &px.ai[1], X, 0, kBM, 0, 0));
+        LACT_TRY(make_operand(1, &px.b[1], &px.bi[1], T, 0, BT, 0, 0));
+      }
+      px.M = ns_upd_rows(G); px.N = ns_upd_cols(G); px.K = G.m; px.batch = G.nmat;
+      LACT_TRY(make_output(&px.out[0], &px.oi[0], O, 0, 0));
+      dX = out;
+    }
+    args.done[g] = G.done;
+    LACT_CUDA(cudaMemsetAsync(G.done, 0, sizeof(uint32_t) * G.nmat, stream));
+    max_tiles = std::max<int64_t>(max_tiles, static_cast<int64_t>(G.nmat) * ceil_div(ns_upd_rows(G), kBM) *
+                                                 ceil_div(ns_upd_cols(G), BT) * ngroups);
+  }
+  for (int it = 0; it < steps; ++it) args.coef_c[it] = (const_coeffs ? kNsConst : kNsTuned[it])[2];
+  args.steps = steps;
+  args.ngroups = ngroups;
+  args.status = status;
+  const int grid = static_cast<int>(std::min<int64_t>(sm_count(), std::max<int64_t>(max_tiles, 8)));
+  void* kargs[] = {&args};
+  KernelScope scope(kClsOther, stream);
+  LACT_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kernel), dim3(grid), dim3(kGemmThreadsFlow), kargs, smem,
+                                        stream));
   return LACT_OK;
 }
 
@@ -1384,6 +1501,10 @@ int lact_ns_trace_fwd(const void* g, int32_t g_dtype, void* x_out, int64_t B, in
   return LACT_OK;
 }
 
+static int bmm2_scaled(const void* a0, int32_t a0_mn, const void* b0, int32_t b0_mn, const void* a1, int32_t a1_mn,
+                       const void* b1, int32_t b1_mn, void* c, int32_t c_dtype, int64_t batch, int64_t M, int64_t N,
+                       int64_t K, int32_t* status_word, void* stream, float alpha);
+
 // dx0 (fp32) = gradient w.r.t. the normalised first iterate X[0], given du = bf16 gradient w.r.t. the
 // result X[steps]; roundings are treated as identities and every operand is bf16 (the reference
 // differentiates its bf16 iteration the same way).  With Q = dP + dP^T (dP = dX' X^T) and
@@ -1397,7 +1518,6 @@ int lact_ns_trace_bwd(const void* du, void* dx0, int64_t B, int64_t R, int64_t C
   NsTrace t;
   LACT_TRY(plan_ns_trace(trace, B, R, C, steps, gram_right, &t));
   if (t.bytes > trace_bytes) return LACT_ERR_WORKSPACE;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int64_t m = t.grp.m, n = t.grp.n;
   const size_t rc = static_cast<size_t>(B) * R * C, mm = static_cast<size_t>(B) * m * m;
   const int tall = t.grp.transposed;
@@ -1406,16 +1526,11 @@ int lact_ns_trace_bwd(const void* du, void* dx0, int64_t B, int64_t R, int64_t C
     const float* co = const_coeffs ? kNsConst : kNsTuned[it];
     const bf16* X = t.X + rc * it;
     const bf16* P = t.P + mm * it;
-    {
-      KernelScope scope(kClsOther, s);
-      // c A + (b/2) I = c (A + (b/2c) I)
-      scale_bf16_kernel<<<ceil_div(static_cast<int64_t>(mm), 256 * 8), 256, 0, s>>>(t.A + mm * it, t.CB,
-                                                                                    static_cast<int64_t>(mm), co[2]);
-      LACT_CUDA(cudaGetLastError());
-    }
     // Q [m][m]: contraction over the long side n
     LACT_TRY(lact_bmm2_bf16(dX, tall, X, tall, X, tall, dX, tall, t.Q, LACT_BF16, 0, B, m, m, n, status_word, stream));
-    LACT_TRY(lact_bmm2_bf16(t.CB, 0, t.Q, 0, t.Q, 0, t.CB, 0, t.S, LACT_BF16, 0, B, m, m, m, status_word, stream));
+    // S = CB Q + Q CB with CB = c A + (b/2) I = c (A + (b/2c) I): the kept shifted Gram matrix, scaled in the epilogue
+    const bf16* As = t.A + mm * it;
+    LACT_TRY(bmm2_scaled(As, 0, t.Q, 0, t.Q, 0, As, 0, t.S, LACT_BF16, B, m, m, m, status_word, stream, co[2]));
     void* out = it == 0 ? dx0 : static_cast<void*>((it & 1) ? t.dXa : t.dXb);
     const int out_dt = it == 0 ? LACT_F32 : LACT_BF16;
     if (!tall) LACT_TRY(lact_bmm2_bf16(P, 0, dX, 1, t.S, 0, X, 1, out, out_dt, 0, B, m, n, m, status_word, stream));
@@ -1598,57 +1713,126 @@ int lact_prenorm_momentum_l2norm(const void* x, const void* dx, const void* m, c
   return LACT_OK;
 }
 
+// One or two independent problems c (+)= alpha (a0 b0^T [+ a1 b1^T]) in one persistent launch (both single-product
+// or both two-product; one tile width for the launch).
+static int bmm_group(const lact_bmm_desc* d, int n, int32_t* status_word, void* stream, float alpha) {
+  if (!d || !status_word) return LACT_ERR_NULL;
+  if (n < 1 || n > 2) return LACT_ERR_CONFIG;
+  LACT_TRY(check_device());
+  const bool two = d[0].a1 != nullptr;
+  for (int p = 0; p < n; ++p) {
+    const lact_bmm_desc& q = d[p];
+    if (!q.a0 || !q.b0 || !q.c || ((q.a1 == nullptr) != (q.b1 == nullptr))) return LACT_ERR_NULL;
+    if ((q.a1 != nullptr) != two) return LACT_ERR_CONFIG;
+    if (q.batch < 1 || q.batch > 65535 || q.M < 1 || q.N < 8 || q.K < 1 || (q.N % 8)) return LACT_ERR_SHAPE;
+    // the contiguous axis of every operand must be a multiple of 8 elements (16-byte TMA strides)
+    if (((q.a0_mn || (q.a1 && q.a1_mn)) && (q.M % 8)) ||
+        ((!q.a0_mn || (q.a1 && !q.a1_mn) || !q.b0_mn || (q.b1 && !q.b1_mn)) && (q.K % 8)))
+      return LACT_ERR_SHAPE;
+    if (q.accumulate && q.c_dtype != LACT_F32) return LACT_ERR_DTYPE;
+    // c is written in 16-byte (fp32) / 8-byte (bf16) units
+    if ((reinterpret_cast<uintptr_t>(q.c) & 15) != 0 || q.c_ld < q.N || (q.c_ld % 8) != 0 ||
+        (q.batch > 1 && (q.c_bs % 8) != 0))
+      return LACT_ERR_SHAPE;
+    auto bad = [&](int mn, int64_t rows, int64_t ld) { return ld < (mn ? rows : q.K); };
+    if (bad(q.a0_mn, q.M, q.a0_ld) || bad(q.b0_mn, q.N, q.b0_ld) ||
+        (q.a1 && (bad(q.a1_mn, q.M, q.a1_ld) || bad(q.b1_mn, q.N, q.b1_ld))))
+      return LACT_ERR_SHAPE;
+  }
+  // operand as a matrix of `rows` = M or N: [rows][K] with row stride ld, or (MN-major) [K][rows]
+  auto mat = [](const lact_bmm_desc& q, const void* ptr, int mn, int64_t rows, int64_t ld, int64_t bs) {
+    return mn ? Mat{ptr, q.K, rows, ld, q.batch, bs} : Mat{ptr, rows, q.K, ld, q.batch, bs};
+  };
+  const lact_bmm_desc& l = d[n - 1];
+  int bt = choose_bt({{d[0].N, d[0].M * d[0].batch}, {l.N, n > 1 ? l.M * l.batch : 0}});
+  if (two) bt = std::min(bt, 192);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  auto fill = [&](auto& g, int btv) -> int {
+    for (int p = 0; p < n; ++p) {
+      const lact_bmm_desc& q = d[p];
+      auto& P = g.prob[p];
+      LACT_TRY(make_operand(kb_of(P), &P.a[0], &P.ai[0], mat(q, q.a0, q.a0_mn, q.M, q.a0_ld, q.a0_bs), q.a0_mn, kBM, 0, 0));
+      LACT_TRY(make_operand(kb_of(P), &P.b[0], &P.bi[0], mat(q, q.b0, q.b0_mn, q.N, q.b0_ld, q.b0_bs), q.b0_mn, btv, 0, 0));
+      if constexpr (std::remove_reference_t<decltype(g)>::OpType::NA == 2) {
+        LACT_TRY(make_operand(kb_of(P), &P.a[1], &P.ai[1], mat(q, q.a1, q.a1_mn, q.M, q.a1_ld, q.a1_bs), q.a1_mn, kBM, 0, 0));
+        LACT_TRY(make_operand(kb_of(P), &P.b[1], &P.bi[1], mat(q, q.b1, q.b1_mn, q.N, q.b1_ld, q.b1_bs), q.b1_mn, btv, 0, 0));
+      }
+      P.M = static_cast<int>(q.M); P.N = static_cast<int>(q.N); P.K = static_cast<int>(q.K);
+      P.batch = static_cast<int>(q.batch);
+      P.ep = EpiStore{q.c, q.c_bs, q.c_ld, 0, q.c_dtype == LACT_F32, q.accumulate, alpha};
+    }
+    g.status = status_word;
+    return LACT_OK;
+  };
+  if (n == 1) return two ? launch_op<OpStore2T, 1>(bt, fill, s, kClsOther, 1) : launch_op<OpStoreDirectT, 1>(bt, fill, s, kClsOther, 1);
+  return two ? launch_op<OpStore2T, 2>(bt, fill, s, kClsOther, 2) : launch_op<OpStoreDirectT, 2>(bt, fill, s, kClsOther, 2);
+}
+
+int lact_bmm_group_bf16(const lact_bmm_desc* problems, int32_t n, int32_t* status_word, void* stream) {
+  return bmm_group(problems, n, status_word, stream, 1.0f);
+}
+
+static int bmm2_strided(const void* a0, int32_t a0_mn, int64_t a0_ld, int64_t a0_bs, const void* b0, int32_t b0_mn,
+                        int64_t b0_ld, int64_t b0_bs, const void* a1, int32_t a1_mn, int64_t a1_ld, int64_t a1_bs,
+                        const void* b1, int32_t b1_mn, int64_t b1_ld, int64_t b1_bs, void* c, int32_t c_dtype,
+                        int64_t c_ld, int64_t c_bs, int32_t accumulate, int64_t batch, int64_t M, int64_t N, int64_t K,
+                        int32_t* status_word, void* stream, float alpha) {
+  if (!a0 || !b0 || !c) return LACT_ERR_NULL;
+  lact_bmm_desc q;
+  std::memset(&q, 0, sizeof(q));
+  q.a0 = a0; q.b0 = b0; q.a1 = a1; q.b1 = b1; q.c = c;
+  q.a0_ld = a0_ld; q.a0_bs = a0_bs; q.b0_ld = b0_ld; q.b0_bs = b0_bs;
+  q.a1_ld = a1_ld; q.a1_bs = a1_bs; q.b1_ld = b1_ld; q.b1_bs = b1_bs;
+  q.c_ld = c_ld; q.c_bs = c_bs;
+  q.batch = batch; q.M = M; q.N = N; q.K = K;
+  q.a0_mn = a0_mn; q.b0_mn = b0_mn; q.a1_mn = a1_mn; q.b1_mn = b1_mn;
+  q.c_dtype = c_dtype; q.accumulate = accumulate;
+  return bmm_group(&q, 1, status_word, stream, alpha);
+}
+
+// Pointwise stage of the fast-weight gradient on its own (see lact_fw_grad): also the backward of apply's
+// pre-activations with (k, v) = (q, dO) and unit learning rates.
+int lact_fw_grad_pointwise(const void* w0w2, const void* w1, const void* k, int64_t k_ts, int64_t k_bs, const void* v,
+                           int64_t v_ts, int64_t v_bs, const void* lr0, const void* lr1, const void* lr2, int32_t lr_dtype,
+                           int64_t lr_bs, float w_scale, void* dy02, void* hid, int64_t B, int64_t N, int64_t D, int64_t H,
+                           int32_t* status_word, void* stream) {
+  if (!w0w2 || !w1 || !k || !v || !dy02 || !hid || !status_word) return LACT_ERR_NULL;
+  LACT_TRY(check_device());
+  if (B < 1 || B > 65535 || N < 1 || D < 8 || H < 8 || (D % 8) || (H % 8)) return LACT_ERR_SHAPE;
+  if (k_ts < D || v_ts < D || (k_ts % 8) || (v_ts % 8) || (k_bs % 8) || (v_bs % 8)) return LACT_ERR_SHAPE;
+  if (lr_dtype != LACT_F32 && lr_dtype != LACT_BF16) return LACT_ERR_DTYPE;
+  GradArgs a{};
+  a.w02b = static_cast<const bf16*>(w0w2);
+  a.w1b = static_cast<const bf16*>(w1);
+  a.k = k; a.v = v;
+  a.k_ts = k_ts; a.k_bs = k_bs; a.v_ts = v_ts; a.v_bs = v_bs;
+  a.start = 0; a.end = N;
+  a.lr0 = lr0; a.lr1 = lr1; a.lr2 = lr2;
+  a.lr_f32 = lr_dtype == LACT_F32;
+  a.lr_bs = lr_bs;
+  a.w_scale = w_scale;
+  a.dy02 = static_cast<bf16*>(dy02);
+  a.hid = static_cast<bf16*>(hid);
+  a.B = B; a.D = D; a.H = H;
+  return run_grad_pointwise(a, status_word, static_cast<cudaStream_t>(stream));
+}
+
 int lact_bmm2_strided_bf16(const void* a0, int32_t a0_mn, int64_t a0_ld, int64_t a0_bs, const void* b0, int32_t b0_mn,
                            int64_t b0_ld, int64_t b0_bs, const void* a1, int32_t a1_mn, int64_t a1_ld, int64_t a1_bs,
                            const void* b1, int32_t b1_mn, int64_t b1_ld, int64_t b1_bs, void* c, int32_t c_dtype,
                            int64_t c_ld, int64_t c_bs, int32_t accumulate, int64_t batch, int64_t M, int64_t N, int64_t K,
                            int32_t* status_word, void* stream) {
-  if (!a0 || !b0 || !c || !status_word || ((a1 == nullptr) != (b1 == nullptr))) return LACT_ERR_NULL;
-  LACT_TRY(check_device());
-  if (batch < 1 || batch > 65535 || M < 1 || N < 8 || K < 1 || (N % 8)) return LACT_ERR_SHAPE;
-  // the contiguous axis of every operand must be a multiple of 8 elements (16-byte TMA strides)
-  if (((a0_mn || (a1 && a1_mn)) && (M % 8)) || ((!a0_mn || (a1 && !a1_mn) || !b0_mn || (b1 && !b1_mn)) && (K % 8)))
-    return LACT_ERR_SHAPE;
-  if (accumulate && c_dtype != LACT_F32) return LACT_ERR_DTYPE;
-  // c is written in 16-byte (fp32) / 8-byte (bf16) units
-  if ((reinterpret_cast<uintptr_t>(c) & 15) != 0 || c_ld < N || (c_ld % 8) != 0 || (batch > 1 && (c_bs % 8) != 0))
-    return LACT_ERR_SHAPE;
-  // operand as a matrix of `rows` = M or N: [rows][K] with row stride ld, or (MN-major) [K][rows]
-  auto mat = [&](const void* p, int mn, int64_t rows, int64_t ld, int64_t bs) {
-    return mn ? Mat{p, K, rows, ld, batch, bs} : Mat{p, rows, K, ld, batch, bs};
-  };
-  auto bad = [&](int mn, int64_t rows, int64_t ld) { return ld < (mn ? rows : K); };
-  if (bad(a0_mn, M, a0_ld) || bad(b0_mn, N, b0_ld) || (a1 && (bad(a1_mn, M, a1_ld) || bad(b1_mn, N, b1_ld))))
-    return LACT_ERR_SHAPE;
-  const int bt = choose_bt({{N, 1}});
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const EpiStore ep{c, c_bs, c_ld, 0, c_dtype == LACT_F32, accumulate};
-  if (a1 == nullptr) {
-    auto fill = [&](auto& g, int btv) -> int {
-      auto& P = g.prob[0];
-      LACT_TRY(make_operand(kb_of(P), &P.a[0], &P.ai[0], mat(a0, a0_mn, M, a0_ld, a0_bs), a0_mn, kBM, 0, 0));
-      LACT_TRY(make_operand(kb_of(P), &P.b[0], &P.bi[0], mat(b0, b0_mn, N, b0_ld, b0_bs), b0_mn, btv, 0, 0));
-      P.M = static_cast<int>(M); P.N = static_cast<int>(N); P.K = static_cast<int>(K);
-      P.batch = static_cast<int>(batch);
-      P.ep = ep;
-      g.status = status_word;
-      return LACT_OK;
-    };
-    return launch_op<OpStoreDirectT, 1>(bt, fill, s, kClsOther, 1);
-  }
-  auto fill2 = [&](auto& g, int btv) -> int {
-    auto& P = g.prob[0];
-    LACT_TRY(make_operand(kb_of(P), &P.a[0], &P.ai[0], mat(a0, a0_mn, M, a0_ld, a0_bs), a0_mn, kBM, 0, 0));
-    LACT_TRY(make_operand(kb_of(P), &P.b[0], &P.bi[0], mat(b0, b0_mn, N, b0_ld, b0_bs), b0_mn, btv, 0, 0));
-    LACT_TRY(make_operand(kb_of(P), &P.a[1], &P.ai[1], mat(a1, a1_mn, M, a1_ld, a1_bs), a1_mn, kBM, 0, 0));
-    LACT_TRY(make_operand(kb_of(P), &P.b[1], &P.bi[1], mat(b1, b1_mn, N, b1_ld, b1_bs), b1_mn, btv, 0, 0));
-    P.M = static_cast<int>(M); P.N = static_cast<int>(N); P.K = static_cast<int>(K);
-    P.batch = static_cast<int>(batch);
-    P.ep = ep;
-    g.status = status_word;
-    return LACT_OK;
-  };
-  return launch_op<OpStore2T, 1>(std::min(bt, 192), fill2, s, kClsOther, 1);
+  return bmm2_strided(a0, a0_mn, a0_ld, a0_bs, b0, b0_mn, b0_ld, b0_bs, a1, a1_mn, a1_ld, a1_bs, b1, b1_mn, b1_ld, b1_bs, c,
+                      c_dtype, c_ld, c_bs, accumulate, batch, M, N, K, status_word, stream, 1.0f);
+}
+
+// contiguous two-product with the accumulator scaled by alpha before the store (internal)
+static int bmm2_scaled(const void* a0, int32_t a0_mn, const void* b0, int32_t b0_mn, const void* a1, int32_t a1_mn,
+                       const void* b1, int32_t b1_mn, void* c, int32_t c_dtype, int64_t batch, int64_t M, int64_t N,
+                       int64_t K, int32_t* status_word, void* stream, float alpha) {
+  auto ld = [&](int mn, int64_t rows) { return mn ? rows : K; };
+  return bmm2_strided(a0, a0_mn, ld(a0_mn, M), M * K, b0, b0_mn, ld(b0_mn, N), N * K, a1, a1_mn, ld(a1_mn, M), M * K, b1,
+                      b1_mn, ld(b1_mn, N), N * K, c, c_dtype, N, M * N, 0, batch, M, N, K, status_word, stream, alpha);
 }
 
 int lact_bmm2_bf16(const void* a0, int32_t a0_mn, const void* b0, int32_t b0_mn, const void* a1, int32_t a1_mn,
@@ -1719,16 +1903,66 @@ int lact_renorm_bwd(const void* base, const void* upd, int32_t upd_dtype, const 
   return LACT_OK;
 }
 
-int lact_ns_norm_bwd(const void* g, void* dx0, int64_t nmat, int64_t elems_per_matrix, void* stream) {
-  if (!g || !dx0) return LACT_ERR_NULL;
-  if (nmat < 1 || nmat > 65535 * 16 || elems_per_matrix < 4 || (elems_per_matrix % 4) != 0) return LACT_ERR_SHAPE;
-  if ((reinterpret_cast<uintptr_t>(g) & 15) != 0 || (reinterpret_cast<uintptr_t>(dx0) & 15) != 0) return LACT_ERR_SHAPE;
-  KernelScope scope(kClsOther, static_cast<cudaStream_t>(stream));
-  ns_norm_bwd_kernel<<<static_cast<unsigned>(nmat), 1024, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const float*>(g), static_cast<float*>(dx0), elems_per_matrix);
-  LACT_CUDA(cudaGetLastError());
+int lact_ns_norm_bwd(const void* g, void* dx0, void* partials, int64_t nmat, int64_t elems_per_matrix, void* stream) {
+  if (!g || !dx0 || !partials) return LACT_ERR_NULL;
+  return ns_norm_bwd_launch(static_cast<const float*>(g), dx0, 0, static_cast<float*>(dx0), static_cast<float*>(partials),
+                            nmat, elems_per_matrix, static_cast<cudaStream_t>(stream));
+}
+
+int lact_ns_trace_bwd_fused(const lact_ns_bwd_group* groups, int32_t ngroups, int32_t steps, int32_t const_coeffs,
+                            int32_t gram_right, int32_t* status_word, void* stream) {
+  if (!groups || !status_word) return LACT_ERR_NULL;
+  if (ngroups < 1 || ngroups > 2 || steps < 1 || steps > 5) return LACT_ERR_CONFIG;
+  LACT_TRY(check_device());
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  NsTrace tr[2];
+  NsGroup grp[2];
+  const bf16* du[2] = {nullptr, nullptr};
+  for (int g = 0; g < ngroups; ++g) {
+    const lact_ns_bwd_group& G = groups[g];
+    if (!G.du || !G.g || !G.dg || !G.trace || !G.partials) return LACT_ERR_NULL;
+    LACT_TRY(plan_ns_trace(G.trace, G.nmat, G.rows, G.cols, steps, gram_right, &tr[g]));
+    if (tr[g].bytes > G.trace_bytes) return LACT_ERR_WORKSPACE;
+    grp[g] = tr[g].grp;
+    du[g] = static_cast<const bf16*>(G.du);
+  }
+  // Tile width (one for all phases).  Among the widths that give the m x m phases enough tiles to occupy most SMs,
+  // the one with the least padded work (wider on a tie); with few matrices the kernel is bound by each matrix's
+  // chain of phases, so the width with the most tiles (again wider on a tie).
+  auto mm_tiles = [&](int bt) {
+    int64_t t = 0;
+    for (int g = 0; g < ngroups; ++g) t += static_cast<int64_t>(grp[g].nmat) * ceil_div(grp[g].m, kBM) * ceil_div(grp[g].m, bt);
+    return t;
+  };
+  auto padded_work = [&](int bt) {
+    int64_t w = 0;
+    for (int g = 0; g < ngroups; ++g)
+      w += static_cast<int64_t>(grp[g].nmat) * bt *
+           (2 * ceil_div(grp[g].m, kBM) * ceil_div(grp[g].m, bt) * static_cast<int64_t>(grp[g].m + grp[g].n) / 2 +
+            ceil_div(ns_upd_rows(grp[g]), kBM) * ceil_div(ns_upd_cols(grp[g]), bt) * static_cast<int64_t>(grp[g].m));
+    return w;
+  };
+  const int64_t want = static_cast<int64_t>(sm_count()) * 3 / 4;
+  int bt = 0;
+  for (int cand : {192, 128, 64})
+    if (mm_tiles(cand) >= want && (bt == 0 || padded_work(cand) < padded_work(bt))) bt = cand;
+  if (bt == 0) bt = mm_tiles(64) > mm_tiles(128) ? 64 : (mm_tiles(128) > mm_tiles(192) ? 128 : 192);
+  int rc = LACT_ERR_CONFIG;
+  if (bt == 192) rc = launch_ns_bwd_fused<192>(tr, du, ngroups, steps, const_coeffs, status_word, s);
+  else if (bt == 128) rc = launch_ns_bwd_fused<128>(tr, du, ngroups, steps, const_coeffs, status_word, s);
+  else rc = launch_ns_bwd_fused<64>(tr, du, ngroups, steps, const_coeffs, status_word, s);
+  if (rc != LACT_OK) return rc;
+  // the gradient w.r.t. the first iterate is the bf16 buffer the last phase wrote; the Frobenius normalisation
+  // X0 = bf16(G) / (||G|| + 1e-7) is differentiated into the caller's fp32 dG
+  for (int g = 0; g < ngroups; ++g) {
+    const lact_ns_bwd_group& G = groups[g];
+    LACT_TRY(ns_norm_bwd_launch(static_cast<const float*>(G.g), tr[g].dXb, 1, static_cast<float*>(G.dg),
+                                static_cast<float*>(G.partials), G.nmat, G.rows * G.cols, s));
+  }
   return LACT_OK;
 }
+
+int lact_momentum_bwd_slices(void) { return kNormBwdSlices; }
 
 int lact_momentum_bwd(void* dg0, void* dg1, void* carry0, void* carry1, const void* mprev0, const void* mprev1,
                       void* dgb0, void* dgb1, const void* beta, void* dbeta, int64_t B, int64_t n0, int64_t n1,
@@ -1747,7 +1981,7 @@ int lact_momentum_bwd(void* dg0, void* dg1, void* carry0, void* carry1, const vo
   a.n[0] = n0; a.n[1] = n1;
   a.add_carry = add_carry;
   KernelScope scope(kClsOther, static_cast<cudaStream_t>(stream));
-  momentum_bwd_kernel<<<static_cast<unsigned>(B), 1024, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  momentum_bwd_kernel<<<dim3(static_cast<unsigned>(B), kNormBwdSlices), 512, 0, static_cast<cudaStream_t>(stream)>>>(a);
   LACT_CUDA(cudaGetLastError());
   return LACT_OK;
 }

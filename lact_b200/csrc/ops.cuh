@@ -23,6 +23,7 @@ struct EpiStore {
   int32_t row_off;
   int32_t f32;
   int32_t accumulate;  // fp32 only: out += acc (each element is owned by exactly one lane)
+  float alpha = 1.0f;  // the accumulator is multiplied by alpha before it is stored / added
   static constexpr uint32_t kScratch = kEpiWarps * 32 * 144;
   // One warp's 32 x 32 block of results, thread `lane` holding row `row0 + lane` in v[0..31]: the block goes through
   // `scratch` (this warp's 32 x 144 bytes of shared memory) so that eight lanes cover a 128-byte row segment and every
@@ -31,8 +32,8 @@ struct EpiStore {
                                              int lane) const {
 #pragma unroll
     for (int gq = 0; gq < 8; ++gq)
-      asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(scratch + lane * 144 + gq * 16), "f"(v[gq * 4]),
-                   "f"(v[gq * 4 + 1]), "f"(v[gq * 4 + 2]), "f"(v[gq * 4 + 3])
+      asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(scratch + lane * 144 + gq * 16), "f"(v[gq * 4] * alpha),
+                   "f"(v[gq * 4 + 1] * alpha), "f"(v[gq * 4 + 2] * alpha), "f"(v[gq * 4 + 3] * alpha)
                    : "memory");
     __syncwarp();
     const int u = lane & 7, rsub = lane >> 3;
@@ -327,6 +328,36 @@ struct OpNs {
   }
 };
 
+// Two-product Newton-Schulz GEMM for the backward pass: out = bf16(acc_scale * (a0 b0^T + a1 b1^T)), both products
+// into one accumulator (equal K), one k-block of both products per ring stage, staged (TMA-stored) output.
+template <int BT_>
+struct OpNs2 {
+  static constexpr int NA = 2, NB = 2, NACC = 1, BT = BT_, NTERMS = 2, NOUT = 1;
+  static constexpr bool kTileReduce = false;
+  static constexpr bool kWarpTranspose = false, kReverseBatch = false;
+  static constexpr uint32_t kEpiScratch = 0;
+  static constexpr int KB = 1;
+  static constexpr int STAGES = ring_depth(2 * (kATileBytes + BT_ * kBK * 2), kBM * BT_ * 2);
+  using Epi = EpiNs;
+  __host__ __device__ static constexpr int term_a(int t) { return t; }
+  __host__ __device__ static constexpr int term_b(int t) { return t; }
+  __host__ __device__ static constexpr int term_col(int) { return 0; }
+  __host__ __device__ static constexpr int term_n(int) { return BT_; }
+  __host__ __device__ static constexpr bool term_first(int t) { return t == 0; }
+  __device__ static __forceinline__ bool skip_store(const Epi&, int) { return false; }
+  struct Prefetch {
+    float sc;
+  };
+  __device__ static __forceinline__ void prefetch(const Epi& ep, int, int, int, int, int, int, Prefetch& pf) {
+    pf.sc = ep.acc_scale;
+  }
+  __device__ static __forceinline__ void epilogue_staged(const Epi&, int, int, int, int, int, const float (&v)[1][32],
+                                                         float (&o)[1][32], Prefetch& pf) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) o[0][j] = v[0][j] * pf.sc;
+  }
+};
+
 // [y0 | y2] = x [w0 slice ; w2 slice]^T; epilogue = SwiGLU gate, staged.  With one k-block per stage
 // the two weight tiles are adjacent in shared memory and one 128 x 2BT MMA covers both; with two
 // k-blocks per stage each tile holds its k-blocks back to back, so the product is two 128 x BT MMAs
@@ -382,9 +413,10 @@ struct OpFwGradPointwise {
     pf.l0 = pf.l1 = pf.l2 = 0.f;
     if (row < M) {
       const int64_t li = batch * ep.lr_bs + ep.tok_off + row;
-      pf.l0 = load_scalar(ep.lr0, ep.lr_f32, li) * ep.w_scale;
-      pf.l1 = load_scalar(ep.lr1, ep.lr_f32, li) * ep.w_scale;
-      pf.l2 = load_scalar(ep.lr2, ep.lr_f32, li) * ep.w_scale;
+      // (a null learning rate stands for 1: the backward of apply is this same pointwise stage on (q, dO))
+      pf.l0 = (ep.lr0 ? load_scalar(ep.lr0, ep.lr_f32, li) : 1.f) * ep.w_scale;
+      pf.l1 = (ep.lr1 ? load_scalar(ep.lr1, ep.lr_f32, li) : 1.f) * ep.w_scale;
+      pf.l2 = (ep.lr2 ? load_scalar(ep.lr2, ep.lr_f32, li) : 1.f) * ep.w_scale;
     }
   }
   __device__ static __forceinline__ bool skip_store(const Epi&, int) { return false; }
@@ -622,18 +654,6 @@ __global__ void __launch_bounds__(256) ns_scale_kernel(const NsPrepArgs args) {
       xo[off] = __float2bfloat16_rn(bf16_round(load_scalar(G.src, G.src_f32, base + off)) / den);
     }
   }
-}
-
-// dst = bf16(factor * src), 8 elements per thread.
-__global__ void __launch_bounds__(256) scale_bf16_kernel(const bf16* src, bf16* dst, int64_t total, float factor) {
-  const int64_t i0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 8;
-  if (i0 >= total) return;
-  uint4 u = *reinterpret_cast<const uint4*>(src + i0);
-  uint32_t* w = reinterpret_cast<uint32_t*>(&u);
-#pragma unroll
-  for (int i = 0; i < 4; ++i)
-    w[i] = pack_bf16x2(factor * __uint_as_float(w[i] << 16), factor * __uint_as_float(w[i] & 0xFFFF0000u));
-  *reinterpret_cast<uint4*>(dst + i0) = u;
 }
 
 struct RenormArgs {
@@ -907,29 +927,59 @@ __device__ __forceinline__ void block_sum2(float& a, float& b, float* scratch /*
 
 // Backward of the Frobenius normalisation in front of Newton-Schulz, X0 = bf16(G) / den with nrm = bf16(||bf16(G)||),
 // den = bf16(nrm + 1e-7):  dG = dX0 / den - bf16(G) <dX0, bf16(G)> / (den^2 nrm), written in place over dX0.
-// One block per matrix (`n` elements each).
-__global__ void __launch_bounds__(1024) ns_norm_bwd_kernel(const float* g, float* dx0, int64_t n) {
+// Two launches over (matrices x slices) blocks: partial sums, then the rewrite (`n` elements per matrix).
+constexpr int kNormBwdSlices = 16;
+// four consecutive gradient values, fp32 or bf16 storage
+__device__ __forceinline__ float4 load4_f32_or_bf16(const void* p, int is_bf16, int64_t i) {
+  if (!is_bf16) return *reinterpret_cast<const float4*>(static_cast<const float*>(p) + i);
+  const uint2 u = *reinterpret_cast<const uint2*>(static_cast<const bf16*>(p) + i);
+  return make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xFFFF0000u), __uint_as_float(u.y << 16),
+                     __uint_as_float(u.y & 0xFFFF0000u));
+}
+// part 1: per (matrix, slice) partial sums of bf16(G)^2 and dX0 * bf16(G) into part[(mat * slices + s) * 2 + {0, 1}]
+__global__ void __launch_bounds__(512) ns_norm_bwd_partial_kernel(const float* g, const void* dx0, int dx_bf16, float* part,
+                                                                  int64_t n) {
   __shared__ float scratch[66];
   const float* G = g + static_cast<int64_t>(blockIdx.x) * n;
-  float* D = dx0 + static_cast<int64_t>(blockIdx.x) * n;
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * n;
+  const int64_t per = ((n / 4 + gridDim.y - 1) / gridDim.y) * 4;
+  const int64_t lo = static_cast<int64_t>(blockIdx.y) * per, hi = lo + per < n ? lo + per : n;
   float ss = 0.f, dot = 0.f;
-  for (int64_t i = threadIdx.x * 4; i < n; i += blockDim.x * 4) {
-    const float4 gv = *reinterpret_cast<const float4*>(G + i), dv = *reinterpret_cast<const float4*>(D + i);
+  for (int64_t i = lo + threadIdx.x * 4; i < hi; i += blockDim.x * 4) {
+    const float4 gv = *reinterpret_cast<const float4*>(G + i), dv = load4_f32_or_bf16(dx0, dx_bf16, base + i);
     const float a = bf16_round(gv.x), b = bf16_round(gv.y), c = bf16_round(gv.z), d = bf16_round(gv.w);
     ss += a * a + b * b + c * c + d * d;
     dot += a * dv.x + b * dv.y + c * dv.z + d * dv.w;
   }
   block_sum2(ss, dot, scratch);
+  if (threadIdx.x == 0) {
+    part[(static_cast<int64_t>(blockIdx.x) * gridDim.y + blockIdx.y) * 2] = ss;
+    part[(static_cast<int64_t>(blockIdx.x) * gridDim.y + blockIdx.y) * 2 + 1] = dot;
+  }
+}
+// part 2: the partials are added in slice order (same result in every block), then the slice of dG is written
+// (`dg` may be `dx0` itself when that is fp32)
+__global__ void __launch_bounds__(512) ns_norm_bwd_apply_kernel(const float* g, const void* dx0, int dx_bf16, float* dg,
+                                                                const float* part, int64_t n) {
+  const float* G = g + static_cast<int64_t>(blockIdx.x) * n;
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * n;
+  float ss = 0.f, dot = 0.f;
+  for (int s = 0; s < static_cast<int>(gridDim.y); ++s) {
+    ss += part[(static_cast<int64_t>(blockIdx.x) * gridDim.y + s) * 2];
+    dot += part[(static_cast<int64_t>(blockIdx.x) * gridDim.y + s) * 2 + 1];
+  }
   const float nrm = bf16_round(sqrtf(ss)), den = bf16_round(nrm + 1e-7f);
   const float inv = 1.0f / den, coef = dot / (den * den * fmaxf(nrm, 1e-30f));
-  for (int64_t i = threadIdx.x * 4; i < n; i += blockDim.x * 4) {
+  const int64_t per = ((n / 4 + gridDim.y - 1) / gridDim.y) * 4;
+  const int64_t lo = static_cast<int64_t>(blockIdx.y) * per, hi = lo + per < n ? lo + per : n;
+  for (int64_t i = lo + threadIdx.x * 4; i < hi; i += blockDim.x * 4) {
     const float4 gv = *reinterpret_cast<const float4*>(G + i);
-    float4 dv = *reinterpret_cast<const float4*>(D + i);
+    float4 dv = load4_f32_or_bf16(dx0, dx_bf16, base + i);
     dv.x = dv.x * inv - bf16_round(gv.x) * coef;
     dv.y = dv.y * inv - bf16_round(gv.y) * coef;
     dv.z = dv.z * inv - bf16_round(gv.z) * coef;
     dv.w = dv.w * inv - bf16_round(gv.w) * coef;
-    *reinterpret_cast<float4*>(D + i) = dv;
+    *reinterpret_cast<float4*>(dg + base + i) = dv;
   }
 }
 
@@ -949,6 +999,8 @@ struct MomentumBwdArgs {
   int32_t add_carry;     // 0 at the last update of the program (nothing arrives from a later one)
 };
 __global__ void __launch_bounds__(1024) momentum_bwd_kernel(const MomentumBwdArgs a) {
+  // grid (batch entries, slices): block (b, s) owns the s-th of gridDim.y equal slices of both arrays of entry b and
+  // leaves its share of <dG, Mprev> in dbeta[b * gridDim.y + s] (the host adds the slices)
   __shared__ float scratch[66];
   const int b = blockIdx.x;
   const float bt = a.beta != nullptr ? a.beta[b] : 0.f;
@@ -956,7 +1008,9 @@ __global__ void __launch_bounds__(1024) momentum_bwd_kernel(const MomentumBwdArg
 #pragma unroll
   for (int w = 0; w < 2; ++w) {
     const int64_t off = static_cast<int64_t>(b) * a.n[w];
-    for (int64_t i = threadIdx.x * 4; i < a.n[w]; i += blockDim.x * 4) {
+    const int64_t per = ((a.n[w] / 4 + gridDim.y - 1) / gridDim.y) * 4;
+    const int64_t lo = static_cast<int64_t>(blockIdx.y) * per, hi = lo + per < a.n[w] ? lo + per : a.n[w];
+    for (int64_t i = lo + threadIdx.x * 4; i < hi; i += blockDim.x * 4) {
       float4 d = *reinterpret_cast<const float4*>(a.dg[w] + off + i);
       if (a.carry[w] != nullptr && a.add_carry) {
         const float4 c = *reinterpret_cast<const float4*>(a.carry[w] + off + i);
@@ -973,7 +1027,7 @@ __global__ void __launch_bounds__(1024) momentum_bwd_kernel(const MomentumBwdArg
     }
   }
   block_sum2(dot, unused, scratch);
-  if (threadIdx.x == 0 && a.dbeta != nullptr) a.dbeta[b] = dot;
+  if (threadIdx.x == 0 && a.dbeta != nullptr) a.dbeta[b * gridDim.y + blockIdx.y] = dot;
 }
 
 // ------------------------------------------------------------------------------------------

@@ -223,6 +223,41 @@ def test_newton_schulz_backward(lb, shape, steps):
     assert orc.cosine(got, ref64) >= 0.98
 
 
+@pytest.mark.parametrize("shapes,steps", [
+    ([(3, 64, 64), (2, 64, 128)], None),          # 64-wide tiles; square + wide
+    ([(4, 256, 128), (4, 128, 128)], None),        # 128-wide tiles; tall + square (the [w0; w2] / w1 pairing)
+    ([(20, 768, 384), (20, 384, 384)], None),      # 192-wide tiles, enough work for them
+    ([(2, 384, 768)], 3),                          # one group, constant coefficients, 3 iterations
+])
+def test_newton_schulz_backward_fused_launch(lb, shapes, steps):
+    """All iterations of one or two groups in one cooperative launch: against the launch-per-product path on the
+    same kept iterates (same operands and roundings except the last gradient, which the fused kernel leaves in bf16
+    before the normalisation backward), and against fp64 autograd."""
+    from oracle import lact_oracle as orc
+    from lact_b200 import backward as bw
+    g = torch.Generator().manual_seed(11)
+    Gs = [torch.randn(*sh, generator=g) for sh in shapes]
+    dUs = [torch.randn(*sh, generator=g) for sh in shapes]
+    saved = [bw.ns_forward_saved(G.cuda(), 5 if steps is None else steps, steps is not None, False)[0] for G in Gs]
+    from lact_b200 import _lib as LL
+    before = LL.launch_count()
+    fused = bw.ns_backward_groups(saved, [d.cuda() for d in dUs])
+    launches = LL.launch_count() - before
+    bw.check_status(torch.device("cuda", 0))
+    # one cooperative launch + two small normalisation kernels per group (the launch-per-product path needs
+    # three launches per iteration and group)
+    assert launches == 1 + 2 * len(shapes), launches
+    for sv, G, dU, got in zip(saved, Gs, dUs, fused):
+        plain = bw.ns_backward(sv, dU.cuda())
+        assert torch.isfinite(got).all()
+        assert orc.rel_fro(got.double().cpu(), plain.double().cpu()) <= 1e-2
+        if G.shape[1] * G.shape[2] <= 256 * 128:
+            Gl = G.to(BF16).double().clone().requires_grad_(True)
+            (orc.newton_schulz_f64(Gl, steps) * dU.double()).sum().backward()
+            assert orc.cosine(got.double().cpu(), Gl.grad) >= 0.98
+    bw.check_status(torch.device("cuda", 0))
+
+
 def test_llm_backward_with_muon_first_chunks(lb):
     """Muon on: gradients of the tokens that see at most one Newton-Schulz step are compared with
     autograd through the oracle (loose band: the iteration's own bf16 noise, see the forward tests)."""
