@@ -42,6 +42,12 @@ def reset_status(dev: torch.device) -> None:
     _status_word(dev).zero_()
 
 
+def post_status(dev: torch.device) -> None:
+    """After a sweep has been enqueued: its status word travels to the host without waiting for the device and is
+    examined at a later library call or in `synchronize_and_check` (see `_lib._StatusRing`)."""
+    L.mark_pending(_status_word(dev).view(torch.uint8))
+
+
 def check_status(dev: torch.device) -> None:
     """Raises if a bounded wait ran out during the sweep; the word is cleared first, so the next
     backward call starts clean."""
@@ -402,6 +408,24 @@ def scan_backward(opts, steps, w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, dum
     dmom = torch.zeros(B, Ltok, dtype=f32, device=dev) if has_momentum else None
     dO = dO.to(BF16)
 
+    # learning rates of the update steps as contiguous [B, n] blocks: one copy per sweep when the steps tile a token
+    # range back to back with one length (the usual chunking), else one small copy per step
+    upd_steps = [(st[1], st[2]) for st in steps if st[0] == P.UPDATE and st[2] > st[1]]
+    lr_blocks = None
+    if upd_steps:
+        n_ = upd_steps[0][1] - upd_steps[0][0]
+        if all(e_ - s_ == n_ for s_, e_ in upd_steps) and all(upd_steps[i + 1][0] == upd_steps[i][1]
+                                                              for i in range(len(upd_steps) - 1)):
+            s0_, e1_ = upd_steps[0][0], upd_steps[-1][1]
+            blk = lambda t: t[:, s0_:e1_].reshape(B, len(upd_steps), n_).transpose(0, 1).contiguous()
+            lr_blocks = (s0_, n_, blk(lr0v), blk(lr1v), blk(lr2v))
+
+    def lr_slices(s_, e_):
+        if lr_blocks is not None:
+            i_ = (s_ - lr_blocks[0]) // lr_blocks[1]
+            return lr_blocks[2][i_], lr_blocks[3][i_], lr_blocks[4][i_]
+        return lr0v[:, s_:e_], lr1v[:, s_:e_], lr2v[:, s_:e_]
+
     cnt = n_upd
     shadows = {}
     q_done, kv_done = [], []  # token ranges whose dq / dk, dv have been written
@@ -497,20 +521,20 @@ def scan_backward(opts, steps, w0, w1, w2, q, k, v, lr0, lr1, lr2, momentum, dum
         if dbeta is not None:
             dmom[:, s:e] += (dbeta.sum(dim=1) / float(e - s)).unsqueeze(1)
         w02b, w1b = shadow(u)
+        l0_, l1_, l2_ = lr_slices(s, e)
         if fresh(kv_done, s, e):
-            _, _, g0, g1, g2 = fw_grad_backward(w02b, w1b, k[:, s:e], v[:, s:e], lr0v[:, s:e], lr1v[:, s:e],
-                                                lr2v[:, s:e], w_scale, dG02, dG1, dW02, dW1, dk_out=dk[:, s:e],
-                                                dv_out=dv[:, s:e], g02b=g02b, g1b=g1b)
+            _, _, g0, g1, g2 = fw_grad_backward(w02b, w1b, k[:, s:e], v[:, s:e], l0_, l1_, l2_, w_scale, dG02, dG1,
+                                                dW02, dW1, dk_out=dk[:, s:e], dv_out=dv[:, s:e], g02b=g02b, g1b=g1b)
         else:
-            gk, gv, g0, g1, g2 = fw_grad_backward(w02b, w1b, k[:, s:e], v[:, s:e], lr0v[:, s:e], lr1v[:, s:e],
-                                                  lr2v[:, s:e], w_scale, dG02, dG1, dW02, dW1, g02b=g02b, g1b=g1b)
+            gk, gv, g0, g1, g2 = fw_grad_backward(w02b, w1b, k[:, s:e], v[:, s:e], l0_, l1_, l2_, w_scale, dG02, dG1,
+                                                  dW02, dW1, g02b=g02b, g1b=g1b)
             dk[:, s:e] += gk
             dv[:, s:e] += gv
         dlr[0][:, s:e] += g0
         dlr[1][:, s:e] += g1
         dlr[2][:, s:e] += g2
         cnt = u
-    check_status(dev)
+    post_status(dev)
     if dWm02 is not None:  # W_0 is both the first master and the first compute copy
         dW02, dW1 = dW02 + dWm02, dW1 + dWm1
     # the target row norms are functions of the initial weights (not detached in the LLM / AR paths)

@@ -534,11 +534,12 @@ def _swiglu_ffn_fwd_fake(W0_W2, W1, X):
 def _swiglu_ffn_bwd_op(W0_W2: torch.Tensor, W1: torch.Tensor, X: torch.Tensor,
                        grad_out: torch.Tensor) -> List[torch.Tensor]:
     """(grad_W0_W2, grad_W1, grad_X), bf16: lact_swiglu_ffn.py:46-76 (pre-activations recomputed)."""
-    from .backward import apply_backward, check_status, reset_status
+    from .backward import apply_backward, post_status, reset_status
     reset_status(X.device)
     dW02 = torch.zeros(W0_W2.shape, dtype=torch.float32, device=X.device)
     dW1 = torch.zeros(W1.shape, dtype=torch.float32, device=X.device)
     dX = apply_backward(W0_W2.contiguous(), W1.contiguous(), X.contiguous(), grad_out.to(BF16).contiguous(), dW02, dW1)
+    post_status(X.device)
     return [dW02.to(BF16), dW1.to(BF16), dX]
 
 
@@ -599,11 +600,12 @@ def _fw_grads_bwd_op(W0_W2: torch.Tensor, W1: torch.Tensor, K: torch.Tensor, V: 
                      lr1: torch.Tensor, lr2: torch.Tensor, g02: torch.Tensor, g1: torch.Tensor) -> List[torch.Tensor]:
     """Gradients of (W0_W2, W1, K, V, lr0, lr1, lr2) given those of (DW0_DW2, DW1): the hand-written second-order
     backward of lact_fw_grad.py:61-156 (bf16 for weights and activations, fp32 row sums for the learning rates)."""
-    from .backward import fw_grad_backward, reset_status
+    from .backward import fw_grad_backward, post_status, reset_status
     reset_status(K.device)
     dW02 = torch.zeros(W0_W2.shape, dtype=torch.float32, device=K.device)
     dW1 = torch.zeros(W1.shape, dtype=torch.float32, device=K.device)
     dk, dv, g0, g1_, g2 = fw_grad_backward(W0_W2, W1, K, V, lr0, lr1, lr2, 1.0, g02, g1, dW02, dW1)
+    post_status(K.device)
     return [dW02.to(BF16), dW1.to(BF16), dk, dv, g0.to(lr0.dtype), g1_.to(lr1.dtype), g2.to(lr2.dtype)]
 
 

@@ -56,6 +56,34 @@ def test_back_to_back_calls_never_synchronise(lb, orc):
     assert all(torch.equal(outs[0], o) for o in outs[2::2])
 
 
+def test_training_step_never_synchronises(lb, orc):
+    """Forward + backward of a driver with PyTorch's synchronisation detector armed: any blocking call on the
+    host path (an .item(), a blocking copy, a stream wait) raises."""
+    from lact_b200 import _lib as LL
+    i = _inputs(orc, 2, 512, 64, 64, seed=6)
+    dO = torch.randn(2, 512, 64).to(BF16).cuda()
+
+    def step():
+        leaves = {n: i[n].cuda().requires_grad_(True) for n in NAMES}
+        mom = i["momentum"].cuda().requires_grad_(True)
+        o = lb.block_causal_lact_swiglu(*[leaves[n] for n in NAMES], chunk_size=128, use_muon=True, momentum=mom)
+        o.backward(dO)
+        return leaves["k"].grad
+
+    g_ref = step()  # warm-up: allocations, pinned ring
+    lb.synchronize_and_check()
+    i = {k_: v_.cuda() for k_, v_ in i.items()}
+    before = LL.stream_sync_count()
+    torch.cuda.set_sync_debug_mode("error")
+    try:
+        g = step()
+    finally:
+        torch.cuda.set_sync_debug_mode("default")
+    assert LL.stream_sync_count() == before
+    lb.synchronize_and_check()
+    assert torch.equal(g, g_ref)
+
+
 def test_bounded_wait_runs_out_is_reported_and_the_next_call_is_clean(lb, orc):
     """A wait that nothing satisfies gives up after the configured limit and leaves status 101 in the
     workspace; the shim turns it into LactError; the workspace is usable again afterwards."""
