@@ -398,6 +398,54 @@ def engine_probe():
                       "148 tiles per round, launches back to back in one stream"}))
 
 
+def token_sharded_bench(lb, dev, rank, world, warmup, steps):
+    """A shape whose (batch x head) axis cannot fill several GPUs but whose chunks can: 4 units, head dim 384,
+    chunks of 32 768 tokens, 4 chunks (Muon and momentum on).  Every rank holds 1 / N of each chunk's tokens; the
+    time is the device time of the whole recurrence, max over ranks."""
+    import torch.distributed as dist
+    from lact_b200 import token_sharded as ts
+    B, D, H, C, n_chunks = 4, 384, 384, 32768, 4
+    L = C * n_chunks
+    g = torch.Generator().manual_seed(0)
+    rn = lambda *sh: torch.randn(*sh, generator=g)
+    w0, w1, w2 = rn(B, H, D) / D ** 0.5, rn(B, D, H) / H ** 0.5, rn(B, H, D) / D ** 0.5
+    full = {}
+    for n in ("q", "k", "v"):
+        x = rn(B, L, D)
+        full[n] = (x / x.norm(dim=-1, keepdim=True) if n != "v" else x).to(torch.bfloat16)
+    for n in ("lr0", "lr1", "lr2"):
+        full[n] = torch.nn.functional.softplus(rn(B, L, 1) - 2.0)
+    full["momentum"] = torch.sigmoid(rn(B, L, 1))
+    mine = {n: ts.shard_tokens(x, C, world, rank).to(dev) for n, x in full.items()}
+    w = [t.to(dev) for t in (w0, w1, w2)]
+    run = lambda: ts.token_sharded_block_causal_lact_swiglu(*w, mine["q"], mine["k"], mine["v"], mine["lr0"],
+                                                            mine["lr1"], mine["lr2"], chunk_size=C, use_muon=True,
+                                                            momentum=mine["momentum"])
+    for _ in range(max(3, warmup)):
+        run()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    lb.synchronize_and_check()
+    if rank == 0:
+        print(json.dumps({"metric": "ttt_token_sharded_tokens_per_s", "value": L / (ms.item() * 1e-3), "unit": "tokens/s",
+                          "n_gpus": world, "steps": steps, "ms_per_step": ms.item(), "higher_is_better": True,
+                          "scaling": "strong", "dtype": "bf16", "data": "synthetic",
+                          "config": {"workload": "token-sharded causal recurrence", "units": B, "head_dim": D,
+                                     "hidden": H, "chunk": C, "seq_len": L, "use_muon": True, "momentum": True,
+                                     "collective": "one NCCL all-reduce of B (3 D H + 1) fp32 per chunk",
+                                     "l2": "inputs (%.0f MB per rank) exceed L2" % (3 * B * L * D * 2 / world / 1e6)}}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -415,6 +463,10 @@ def main():
     ap.add_argument("--engine-probe", action="store_true",
                     help="micro-benchmark of the GEMM engine alone (time per output tile by tile width and "
                          "contraction length); prints its own JSON line and exits")
+    ap.add_argument("--token-sharded", action="store_true",
+                    help="time the token-sharded recurrence (every chunk's tokens spread over the N ranks, one "
+                         "all-reduce of the partial fast-weight gradients per chunk) on a few-unit, large-chunk shape; "
+                         "prints its own JSON line and exits (not the headline metric)")
     ap.add_argument("--batch", type=int, default=None,
                     help="override the batch size (profiler captures on a small case; not a headline number)")
     ap.add_argument("--seq-len", type=int, default=None, help="override the sequence length (same caveat)")
@@ -451,6 +503,12 @@ def main():
     import lact_b200
     from lact_b200 import _lib as LL
     from lact_b200 import parallel
+
+    if args.token_sharded:
+        token_sharded_bench(lact_b200, dev, rank, world, warmup, steps)
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     units, L, D, H, C = CFG["batch"] * CFG["heads"], CFG["L"], CFG["D"], CFG["H"], CFG["chunk"]
     global_tokens = CFG["batch"] * L

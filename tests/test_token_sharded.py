@@ -1,0 +1,119 @@
+"""Token-sharded recurrence, host logic on CPU: two gloo ranks, each with half of every chunk's
+tokens and the oracle's sub-ops standing in for the CUDA ones, against the oracle's fused
+post-norm driver on the whole sequence."""
+import os
+import socket
+from types import SimpleNamespace
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from lact_b200 import token_sharded as ts
+
+NAMES = ("q", "k", "v", "lr0", "lr1", "lr2", "momentum")
+
+
+def oracle_sub_ops():
+    from oracle import lact_oracle as orc
+    return SimpleNamespace(apply=orc.apply_fused, grads=orc.grads_fused, newton_schulz=orc.newton_schulz,
+                           l2_norm_add=lambda x, dx, n, eps=1e-5: orc.l2_norm_add(x, dx, n, eps=eps))
+
+
+def test_shard_and_unshard_are_inverse():
+    x = torch.arange(2 * 24 * 3).reshape(2, 24, 3)
+    for chunk, world in ((8, 2), (12, 4), (24, 3)):
+        parts = [ts.shard_tokens(x, chunk, world, r) for r in range(world)]
+        assert all(p.shape == (2, 24 // world, 3) for p in parts)
+        assert torch.equal(ts.unshard_tokens(parts, chunk), x)
+    # rank r holds the r-th slice of every chunk
+    assert ts.shard_tokens(x, 8, 2, 1)[0, :, 0].tolist() == [3 * t for t in (4, 5, 6, 7, 12, 13, 14, 15, 20, 21, 22, 23)]
+    with pytest.raises(ValueError):
+        ts.shard_tokens(x, 9, 2, 0)
+    with pytest.raises(ValueError):
+        ts.shard_tokens(x, 8, 3, 0)
+
+
+def _inputs(B, L, D, H, seed):
+    from oracle import lact_oracle as orc
+    i = orc.make_inputs(B, L, D, H, seed=seed)
+    for n in ("q", "k", "v"):
+        i[n] = i[n].to(torch.bfloat16)
+    return i
+
+
+def _worker(rank, world, port, use_muon, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(1)
+    i = _inputs(2, 256, 32, 32, seed=3)
+    mine = {n: ts.shard_tokens(i[n], 64, world, rank) for n in NAMES}
+    o = ts.token_sharded_block_causal_lact_swiglu(i["w0"], i["w1"], i["w2"], mine["q"], mine["k"], mine["v"],
+                                                  mine["lr0"], mine["lr1"], mine["lr2"], chunk_size=64,
+                                                  use_muon=use_muon, momentum=mine["momentum"],
+                                                  sub_ops=oracle_sub_ops())
+    torch.save(o, os.path.join(out_dir, f"o{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("use_muon", [False, True])
+def test_two_ranks_reproduce_the_unsharded_recurrence(tmp_path, use_muon):
+    from oracle import lact_oracle as orc
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_worker, args=(2, port, use_muon, str(tmp_path)), nprocs=2, join=True)
+    torch.set_num_threads(1)
+    i = _inputs(2, 256, 32, 32, seed=3)
+    got = ts.unshard_tokens([torch.load(str(tmp_path / f"o{r}.pt")) for r in range(2)], 64).float()
+    ref = orc.block_causal_lact_swiglu_fused(i["w0"], i["w1"], i["w2"], i["q"], i["k"], i["v"], i["lr0"], i["lr1"],
+                                             i["lr2"], chunk_size=64, use_muon=use_muon,
+                                             momentum=i["momentum"]).float()
+    assert got.shape == ref.shape
+    # chunk 0 uses the initial weights on both sides: identical
+    assert torch.equal(got[:, :64], ref[:, :64])
+    # later chunks: the per-rank partial gradients are rounded to bf16 before they are added, the unsharded
+    # gradient once after; without Newton-Schulz that is a 2^-9 relative perturbation of the update
+    if not use_muon:
+        assert orc.rel_max(got, ref) <= 2e-2
+        assert orc.cosine(got, ref) >= 0.9995
+    else:  # the iteration amplifies the perturbation (the reference's own one-ulp response is of this size)
+        assert orc.rel_max(got[:, 64:128], ref[:, 64:128]) <= 8e-2
+        assert orc.cosine(got, ref) >= 0.99
+
+
+def test_lock_step_instances_equal_the_process_group_path():
+    """Two TokenShardedScan instances driven in lock step with a plain sum in place of the all-reduce give what the
+    single-rank call on the whole sequence gives up to the rounding of the partial gradients."""
+    from oracle import lact_oracle as orc
+    torch.set_num_threads(1)
+    i = _inputs(1, 192, 32, 32, seed=4)
+    W, C = 2, 64
+    scans = []
+    for r in range(W):
+        mine = {n: ts.shard_tokens(i[n], C, W, r) for n in NAMES}
+        scans.append(ts.TokenShardedScan(i["w0"], i["w1"], i["w2"], mine["q"], mine["k"], mine["v"], mine["lr0"],
+                                         mine["lr1"], mine["lr2"], C, W, use_muon=False, momentum=mine["momentum"],
+                                         sub_ops=oracle_sub_ops()))
+    for c in range(scans[0].n_chunks - 1):
+        flats = []
+        for s in scans:
+            s.apply(c)
+            flats.append(s.local_gradient(c))
+        total = flats[0] + flats[1]
+        for s in scans:
+            s.update(total.clone())
+    for s in scans:
+        s.apply(s.n_chunks - 1)
+    assert torch.equal(scans[0].w02, scans[1].w02) and torch.equal(scans[0].w1, scans[1].w1)
+    got = ts.unshard_tokens([s.out for s in scans], C).float()
+    one = ts.token_sharded_block_causal_lact_swiglu(i["w0"], i["w1"], i["w2"], i["q"], i["k"], i["v"], i["lr0"],
+                                                    i["lr1"], i["lr2"], chunk_size=C, use_muon=False,
+                                                    momentum=i["momentum"], sub_ops=oracle_sub_ops()).float()
+    ref = orc.block_causal_lact_swiglu_fused(i["w0"], i["w1"], i["w2"], i["q"], i["k"], i["v"], i["lr0"], i["lr1"],
+                                             i["lr2"], chunk_size=C, use_muon=False, momentum=i["momentum"]).float()
+    assert torch.equal(one, ref)  # one rank: the same arithmetic as the unsharded driver, bit for bit
+    assert orc.rel_max(got, ref) <= 2e-2
