@@ -352,8 +352,9 @@ def train_step_timing(lb, t, dev, B, L, D, H, C, global_tokens, world, barrier, 
     return {"ms_per_step": ms_step, "tokens_per_s": global_tokens / (ms_step * 1e-3), "steps": steps,
             "algorithmic_flops_per_step_per_gpu": fwd + bwd, "tflops_per_gpu": tf,
             "frac_of_bf16_peak_burst": tf / peaks["bf16_burst"],
-            "note": "forward on the fused kernels with the per-update state kept; backward = per-chunk reverse "
-                    "sweep driven from the host (recomputes pre-activations and the Newton-Schulz iterates)"}
+            "config": {"seq_len": L, "chunk": C, "units_per_gpu": B},
+            "note": "forward on the fused kernels keeping the per-update state and every Newton-Schulz iterate; "
+                    "backward = per-chunk reverse sweep driven from the host (pre-activations recomputed)"}
 
 
 # ------------------------------------------------------------------------------------------ main arm
@@ -635,6 +636,20 @@ def main():
     train = None
     if not args.no_train:
         train = train_step_timing(lact_b200, t, dev, B, L, D, H, C, global_tokens, world, barrier, peaks)
+        if world == 1 and not reduced:
+            # the training configuration's second shape: 65536 tokens in chunks of 4096 (same units)
+            del t
+            torch.cuda.empty_cache()
+            CFG["L"] = 2 * L
+            try:
+                t2 = make_inputs(dev, 0, first, B)
+            finally:
+                CFG["L"] = L
+            train["seq65536_chunk4096"] = train_step_timing(lact_b200, t2, dev, B, 2 * L, D, H, 2 * C,
+                                                            CFG["batch"] * 2 * L, world, barrier, peaks, steps=2)
+            del t2
+            torch.cuda.empty_cache()
+            t = make_inputs(dev, 0, first, B)
 
     # weak scaling for comparison: every rank runs the WHOLE problem on its own data
     replicas = None
