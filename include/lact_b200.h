@@ -246,6 +246,18 @@ int lact_lr_prologue(const void *lr_proj, int32_t proj_dtype, int64_t proj_ld, f
                      int32_t logits_dtype, int64_t logits_ld, void *lr0, void *lr1, void *lr2, void *momentum, int64_t b,
                      int64_t s, int64_t n_heads, void *stream);
 
+/* Causal sliding-window attention forward, the other half of each hybrid layer, on the same q / k / v layout as
+ * the layer's projections: o[b, l, h, d] = softmax over keys (i - window, i] of q_i . k_j * softmax_scale, times v.
+ * Replaces flash_attn_func(q, k, v, causal=True, window_size=(window - 1, 0)) at
+ * lact_llm/lact_model/layer_lact_swiglu.py:386-394 and
+ * minimal_implementations/causal_lact_with_sliding_window_attn.py:380-384.  bf16; d = 64 or 128; heads adjacent within
+ * a token (head stride d), token / batch strides in elements (views of a fused projection are fine);
+ * window <= 0 or >= l: plain causal attention.  status_word: device word, 0 before the call (101 = a bounded wait
+ * ran out). */
+int lact_swa_fwd(const void *q, const void *k, const void *v, void *o, int64_t b, int64_t l, int64_t n_heads, int64_t d,
+                 int64_t q_ts, int64_t q_bs, int64_t k_ts, int64_t k_bs, int64_t v_ts, int64_t v_bs, int64_t o_ts,
+                 int64_t o_bs, int64_t window, float softmax_scale, int32_t *status_word, void *stream);
+
 /* Output side of the LLM layer in one pass (layer_lact_swiglu.py:556-568): per-head RMSNorm of the recurrence's
  * output (fp32 arithmetic x * rsqrt(mean(x^2) + eps) * weight, rounded to bf16: the arithmetic of the
  * fla.modules.RMSNorm kernel the reference calls), times bf16(silu(gate_proj)), heads merged back, plus `resid`.

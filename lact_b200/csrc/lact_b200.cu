@@ -14,6 +14,7 @@
 
 #include "../../include/lact_b200.h"
 #include "ns_bwd_fused.cuh"
+#include "swa.cuh"
 
 namespace lact {
 namespace {
@@ -889,6 +890,47 @@ static int launch_ns_bwd_fused(const NsTrace* tr, const bf16* const* du, int ngr
 }
 
 
+// 4-D map (feature, token, head, batch) of a [b][l][h][d] bf16 activation whose token / batch strides are free
+// (views of a fused projection) and whose heads are adjacent; box {64, 128, 1, 1}, 128-byte swizzle.
+int encode_map_heads(CUtensorMap* map, const void* ptr, int64_t b, int64_t l, int64_t h, int64_t d, int64_t ts,
+                     int64_t bs) {
+  EncodeFn fn = get_encode_fn();
+  if (fn == nullptr) return LACT_ERR_CUDA;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0 || (ts % 8) != 0 || (bs % 8) != 0 || ts < h * d) return LACT_ERR_SHAPE;
+  cuuint64_t dims[4] = {static_cast<cuuint64_t>(d), static_cast<cuuint64_t>(l), static_cast<cuuint64_t>(h),
+                        static_cast<cuuint64_t>(b)};
+  cuuint64_t strides[3] = {static_cast<cuuint64_t>(ts) * 2, static_cast<cuuint64_t>(d) * 2,
+                           static_cast<cuuint64_t>(b > 1 ? bs : ts * l) * 2};
+  cuuint32_t box[4] = {64, 128, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? LACT_OK : LACT_ERR_CUDA;
+}
+
+template <int HD>
+int launch_swa(const SwaArgs& a, int64_t ctas, cudaStream_t stream) {
+  auto kernel = swa_fwd_kernel<HD>;
+  constexpr uint32_t smem = SwaSmem<HD>::kBytes;
+  static_assert(smem <= 232448, "shared memory budget exceeded");
+  static std::mutex mu;
+  static bool configured[64] = {false};
+  int dev = 0;
+  LACT_CUDA(cudaGetDevice(&dev));
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev >= 64 || !configured[dev]) {
+      LACT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      if (dev < 64) configured[dev] = true;
+    }
+  }
+  KernelScope scope(kClsOther, stream);
+  kernel<<<static_cast<unsigned>(ctas), 192, smem, stream>>>(a);
+  LACT_CUDA(cudaGetLastError());
+  return LACT_OK;
+}
+
 struct ScanPlan {
   int32_t* status;
   float *W02, *W1, *W02c, *W1c, *n02, *n1, *G02, *G1, *beta;
@@ -1683,6 +1725,35 @@ int lact_out_epilogue(const void* fw_x, const void* weight, const void* gate_pro
   }
   LACT_CUDA(cudaGetLastError());
   return LACT_OK;
+}
+
+int lact_swa_fwd(const void* q, const void* k, const void* v, void* o, int64_t b, int64_t l, int64_t n_heads, int64_t d,
+                 int64_t q_ts, int64_t q_bs, int64_t k_ts, int64_t k_bs, int64_t v_ts, int64_t v_bs, int64_t o_ts,
+                 int64_t o_bs, int64_t window, float softmax_scale, int32_t* status_word, void* stream) {
+  if (!q || !k || !v || !o || !status_word) return LACT_ERR_NULL;
+  LACT_TRY(check_device());
+  if (d != 64 && d != 128) return LACT_ERR_SHAPE;
+  if (b < 1 || l < 1 || n_heads < 1 || b > 65535 || n_heads > 65535 || l > (1ll << 30)) return LACT_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(o) & 15) != 0 || o_ts < n_heads * d || (o_ts % 8) != 0 || (o_bs % 8) != 0)
+    return LACT_ERR_SHAPE;
+  if (!(softmax_scale > 0.f)) return LACT_ERR_CONFIG;
+  SwaArgs a;
+  std::memset(&a, 0, sizeof(a));
+  LACT_TRY(encode_map_heads(&a.q, q, b, l, n_heads, d, q_ts, q_bs));
+  LACT_TRY(encode_map_heads(&a.k, k, b, l, n_heads, d, k_ts, k_bs));
+  LACT_TRY(encode_map_heads(&a.v, v, b, l, n_heads, d, v_ts, v_bs));
+  a.o = static_cast<bf16*>(o);
+  a.o_bs = o_bs; a.o_ts = o_ts; a.o_hs = d;
+  a.L = static_cast<int32_t>(l);
+  a.window = window > 0 && window < l ? static_cast<int32_t>(window) : 0;
+  a.heads = static_cast<int32_t>(n_heads);
+  a.q_tiles = ceil_div(l, 128);
+  a.scale_log2 = softmax_scale * 1.4426950408889634f;
+  a.status = status_word;
+  const int64_t ctas = b * n_heads * a.q_tiles;
+  if (ctas > 0x7FFFFFFFll) return LACT_ERR_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return d == 64 ? launch_swa<64>(a, ctas, st) : launch_swa<128>(a, ctas, st);
 }
 
 int lact_l2_norm_add(const void* x, int32_t x_dtype, const void* x_add, int32_t add_dtype, const void* scale, void* y,

@@ -269,3 +269,51 @@ def _out_epilogue_fwd(fw_x: torch.Tensor, norm_weight: torch.Tensor, num_heads: 
                                           num_heads, d, float(eps), L.stream_ptr()), "lact_out_epilogue")
     return out
 
+
+
+# ------------------------------------------------------------------------------------------ sliding-window attention
+@torch.library.custom_op("lact_b200::swa_fwd", mutates_args=(), device_types="cuda")
+def _swa_fwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: int, softmax_scale: float) -> torch.Tensor:
+    from .backward import _status_word, post_status, reset_status
+    b, l, h, d = q.shape
+
+    def view(t, name):
+        # heads adjacent within a token, 16-byte aligned token / batch strides: the layout of a slice of a fused
+        # projection reshaped to heads; anything else is copied
+        if (t.stride(3) != 1 or t.stride(2) != d or t.stride(1) % 8 or t.stride(0) % 8 or t.data_ptr() % 16
+                or t.stride(1) < h * d):
+            t = t.contiguous()
+        return t
+
+    q, k, v = view(q, "q"), view(k, "k"), view(v, "v")
+    o = torch.empty(b, l, h, d, dtype=BF16, device=q.device)
+    reset_status(q.device)
+    with torch.cuda.device(q.device):
+        L.check(L.lib().lact_swa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), b, l, h, d, q.stride(1),
+                                     q.stride(0), k.stride(1), k.stride(0), v.stride(1), v.stride(0), o.stride(1),
+                                     o.stride(0), int(window), float(softmax_scale), _status_word(q.device).data_ptr(),
+                                     L.stream_ptr()), "lact_swa_fwd")
+    post_status(q.device)
+    return o
+
+
+@_swa_fwd_op.register_fake
+def _swa_fwd_fake(q, k, v, window, softmax_scale):
+    return q.new_empty(q.shape)
+
+
+def sliding_window_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window_size: Optional[int] = None,
+                             softmax_scale: Optional[float] = None) -> torch.Tensor:
+    """Causal attention over the last `window_size` keys (the query's own position included), q, k, v and the
+    result [b, l, n_heads, head_dim] bf16: what `flash_attn_func(q, k, v, causal=True, window_size=(window_size - 1,
+    0))` computes at lact_llm/lact_model/layer_lact_swiglu.py:386-394 and
+    minimal_implementations/causal_lact_with_sliding_window_attn.py:380-384 (`window_size=None`: all earlier keys).
+    head_dim 64 or 128.  Forward only."""
+    if not (q.is_cuda and k.is_cuda and v.is_cuda):
+        raise ValueError("sliding_window_attention needs CUDA tensors (there is no CPU implementation)")
+    assert q.dim() == 4 and q.shape == k.shape == v.shape, "q, k, v: [b, l, n_heads, head_dim], equal head counts"
+    assert q.dtype == k.dtype == v.dtype == BF16, "bf16 activations"
+    if q.shape[3] not in (64, 128):
+        raise ValueError("head_dim must be 64 or 128")
+    scale = float(softmax_scale) if softmax_scale is not None else q.shape[3] ** -0.5
+    return torch.ops.lact_b200.swa_fwd(q, k, v, int(window_size) if window_size else 0, scale)

@@ -774,3 +774,26 @@ def out_epilogue(fw_x: torch.Tensor, weight: torch.Tensor, n_heads: int, scale_p
     y = y.reshape(b, n_heads, s, d).permute(0, 2, 1, 3).reshape(b, s, n_heads * d)
     return (o_attn + y) if o_attn is not None else y.contiguous()
 
+
+
+def sliding_window_attention(q, k, v, window_size=None, softmax_scale=None, block: int = 1024):
+    """Causal attention over the keys (i - window_size, i] in fp32: the published semantics of
+    `flash_attn_func(q, k, v, causal=True, window_size=(window_size - 1, 0))` (flash-attn 2.x: a query attends keys
+    [i - left, i + right]), the call the reference makes at lact_llm/lact_model/layer_lact_swiglu.py:386-394 and
+    minimal_implementations/causal_lact_with_sliding_window_attn.py:380-384.  flash-attn has no CPU implementation,
+    so this restatement is checked against `torch.nn.functional.scaled_dot_product_attention` with the same band
+    mask (tests/test_oracle_golden.py).  q, k, v: [b, l, h, d]; returns fp32 [b, l, h, d]."""
+    b, l, h, d = q.shape
+    scale = d ** -0.5 if softmax_scale is None else softmax_scale
+    w = l if not window_size else int(window_size)
+    qf, kf, vf = (t.float().permute(0, 2, 1, 3) for t in (q, k, v))  # [b, h, l, d]
+    out = torch.empty(b, h, l, d)
+    for s0 in range(0, l, block):
+        s1 = min(l, s0 + block)
+        k0 = max(0, s0 - (w - 1))
+        sc = torch.matmul(qf[:, :, s0:s1], kf[:, :, k0:s1].transpose(-1, -2)) * scale
+        i = torch.arange(s0, s1).view(-1, 1)
+        j = torch.arange(k0, s1).view(1, -1)
+        sc = sc.masked_fill(~((j <= i) & (j > i - w)), float("-inf"))
+        out[:, :, s0:s1] = torch.matmul(torch.softmax(sc, dim=-1), vf[:, :, k0:s1])
+    return out.permute(0, 2, 1, 3).contiguous()

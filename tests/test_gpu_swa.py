@@ -1,0 +1,79 @@
+"""Causal sliding-window attention kernel against the CPU oracle (fp32 softmax attention over the band):
+head dimensions 64 and 128, windows smaller / larger than the sequence and not multiples of the tile,
+ragged sequence lengths, strided views of a fused projection, a window of one key."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+BF16 = torch.bfloat16
+
+
+@pytest.fixture(scope="module")
+def lo():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from lact_b200 import build
+    build.build()
+    from lact_b200 import layer_ops
+    return layer_ops
+
+
+def _check(lo, q, k, v, window):
+    import lact_b200
+    from oracle import lact_oracle as orc
+    got = lo.sliding_window_attention(q.cuda(), k.cuda(), v.cuda(), window)
+    lact_b200.synchronize_and_check()
+    ref = orc.sliding_window_attention(q, k, v, window)
+    got = got.float().cpu()
+    assert torch.isfinite(got).all()
+    # bf16 probabilities and bf16 output: a few 2^-9 of the row's largest value
+    err = (got - ref).abs().max() / ref.abs().max()
+    assert err <= 1.5e-2, float(err)
+    assert orc.cosine(got, ref) >= 0.9999
+
+
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("l,window", [(1024, 256), (1000, 300), (777, None), (128, 64), (65, 1), (2500, 2048), (640, 129)])
+def test_swa_matches_oracle(lo, d, l, window):
+    g = torch.Generator().manual_seed(l + d)
+    q, k, v = (torch.randn(2, l, 3, d, generator=g).to(BF16) for _ in range(3))
+    _check(lo, q, k, v, window)
+
+
+def test_swa_on_views_of_a_fused_projection(lo):
+    """q, k, v as the three slices of one [b, l, 3 * h * d] projection (token stride 3 h d), no copies."""
+    import lact_b200
+    from oracle import lact_oracle as orc
+    b, l, h, d = 2, 512, 4, 128
+    g = torch.Generator().manual_seed(3)
+    qkv = torch.randn(b, l, 3 * h * d, generator=g).to(BF16)
+    dev = qkv.cuda()
+    qv, kv, vv = (t.reshape(b, l, h, d) for t in dev.chunk(3, dim=-1))
+    assert not qv.is_contiguous()
+    got = lo.sliding_window_attention(qv, kv, vv, 200)
+    lact_b200.synchronize_and_check()
+    q, k, v = (t.reshape(b, l, h, d) for t in qkv.chunk(3, dim=-1))
+    ref = orc.sliding_window_attention(q, k, v, 200)
+    assert (got.float().cpu() - ref).abs().max() / ref.abs().max() <= 1.5e-2
+
+
+def test_swa_large_scores_and_scale(lo):
+    """Scores far from zero (the running maximum changes from tile to tile) and a caller-given scale."""
+    import lact_b200
+    from oracle import lact_oracle as orc
+    g = torch.Generator().manual_seed(5)
+    b, l, h, d = 1, 900, 2, 64
+    q = (torch.randn(b, l, h, d, generator=g) * 3).to(BF16)
+    k = (torch.randn(b, l, h, d, generator=g) * 3).to(BF16)
+    v = torch.randn(b, l, h, d, generator=g).to(BF16)
+    got = lo.sliding_window_attention(q.cuda(), k.cuda(), v.cuda(), 400, softmax_scale=0.2)
+    lact_b200.synchronize_and_check()
+    ref = orc.sliding_window_attention(q, k, v, 400, softmax_scale=0.2)
+    assert torch.isfinite(got.float()).all()
+    assert (got.float().cpu() - ref).abs().max() / ref.abs().max() <= 2e-2
+
+
+def test_swa_rejects_unsupported_head_dim(lo):
+    q = torch.randn(1, 64, 2, 96).to(BF16).cuda()
+    with pytest.raises(ValueError):
+        lo.sliding_window_attention(q, q, q, 16)

@@ -190,3 +190,20 @@ def test_out_epilogue_matches_reference_outputs():
         assert torch.equal(orc.out_epilogue(fw_x, weight, n_h, sproj, o_attn), case["out"]), name
         seen += 1
     assert seen == 2
+
+
+@pytest.mark.parametrize("l,window", [(300, 64), (257, None), (130, 1), (96, 200)])
+def test_sliding_window_attention_restatement_against_sdpa(l, window):
+    """The oracle's banded attention against PyTorch's own scaled_dot_product_attention with the band as an
+    explicit mask (an independent implementation of the same published semantics)."""
+    from oracle import lact_oracle as orc
+    g = torch.Generator().manual_seed(l)
+    q, k, v = (torch.randn(2, l, 3, 32, generator=g) for _ in range(3))
+    got = orc.sliding_window_attention(q, k, v, window, block=100)
+    i = torch.arange(l).view(-1, 1)
+    j = torch.arange(l).view(1, -1)
+    w = l if window is None else window
+    mask = (j <= i) & (j > i - w)
+    ref = torch.nn.functional.scaled_dot_product_attention(q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3),
+                                                           v.permute(0, 2, 1, 3), attn_mask=mask).permute(0, 2, 1, 3)
+    assert torch.allclose(got, ref, atol=2e-6, rtol=1e-5)
