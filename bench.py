@@ -399,6 +399,36 @@ def engine_probe():
                       "148 tiles per round, launches back to back in one stream"}))
 
 
+def swa_bench(lb, dev, warmup, steps, batch=None, seq_len=None):
+    """Causal sliding-window attention at the benchmark model's layer shape: batch 8, 32768 tokens, 12 heads of 128,
+    window 2048, bf16.  FLOPs counted over the band only (4 d per (query, visible key) pair)."""
+    from lact_b200 import layer_ops
+    b, l, h, d, w = batch or 8, seq_len or 32768, 12, 128, 2048
+    g = torch.Generator(device=dev).manual_seed(0)
+    q, k, v = (torch.randn(b, l, h, d, device=dev, generator=g).to(BF16) for _ in range(3))
+    for _ in range(warmup):
+        layer_ops.sliding_window_attention(q, k, v, w)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        layer_ops.sliding_window_attention(q, k, v, w)
+    e1.record()
+    torch.cuda.synchronize()
+    lb.synchronize_and_check()
+    ms = e0.elapsed_time(e1) / steps
+    pairs = sum(min(i + 1, w) for i in range(l))
+    flops = 4.0 * pairs * d * h * b
+    peaks = measured_peaks()
+    print(json.dumps({"metric": "swa_fwd_tokens_per_s", "value": b * l / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+                      "steps": steps, "ms_per_step": ms, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+                      "tflops": flops / (ms * 1e-3) / 1e12,
+                      "frac_of_bf16_peak_burst": flops / (ms * 1e-3) / 1e12 / peaks["bf16_burst"],
+                      "config": {"workload": "causal sliding-window attention forward", "batch": b, "seq_len": l,
+                                 "heads": h, "head_dim": d, "window": w,
+                                 "l2": "q, k, v, o (%.0f MB) exceed L2" % (4 * b * l * h * d * 2 / 1e6)}}))
+
+
 def token_sharded_bench(lb, dev, rank, world, warmup, steps):
     """A shape whose (batch x head) axis cannot fill several GPUs but whose chunks can: 4 units, head dim 384,
     chunks of 32 768 tokens, 4 chunks (Muon and momentum on).  Every rank holds 1 / N of each chunk's tokens; the
@@ -468,6 +498,9 @@ def main():
                     help="time the token-sharded recurrence (every chunk's tokens spread over the N ranks, one "
                          "all-reduce of the partial fast-weight gradients per chunk) on a few-unit, large-chunk shape; "
                          "prints its own JSON line and exits (not the headline metric)")
+    ap.add_argument("--swa", action="store_true",
+                    help="time the sliding-window attention kernel (the other half of a hybrid layer) at the layer "
+                         "shape of the benchmark model; prints its own JSON line and exits (not the headline metric)")
     ap.add_argument("--batch", type=int, default=None,
                     help="override the batch size (profiler captures on a small case; not a headline number)")
     ap.add_argument("--seq-len", type=int, default=None, help="override the sequence length (same caveat)")
@@ -505,6 +538,10 @@ def main():
     from lact_b200 import _lib as LL
     from lact_b200 import parallel
 
+    if args.swa:
+        if rank == 0:
+            swa_bench(lact_b200, dev, max(3, warmup), steps, args.batch, args.seq_len)
+        return
     if args.token_sharded:
         token_sharded_bench(lact_b200, dev, rank, world, warmup, steps)
         if world > 1:
