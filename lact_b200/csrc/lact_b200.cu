@@ -375,6 +375,8 @@ struct GradArgs {
   float* partial1 = nullptr;
   bf16* gb02 = nullptr;        // optional bf16 copies of the two outputs (Newton-Schulz input)
   bf16* gb1 = nullptr;
+  const float* g02_prev = nullptr;  // optional: momentum state read from here instead of g02 / g1 (fp32)
+  const float* g1_prev = nullptr;
 };
 
 inline int contract_bt(int64_t D, int64_t H) { return choose_bt({{D, 2 * H}, {H, D}}); }
@@ -427,14 +429,14 @@ int run_grad(const GradArgs& a, int32_t* status, cudaStream_t stream) {
     P0.M = static_cast<int>(2 * a.H); P0.N = static_cast<int>(a.D); P0.K = static_cast<int>(len);
     P0.batch = static_cast<int>(a.B);
     P0.ep = EpiDW{a.g02, 2 * a.H * a.D, a.D, a.beta, 1, a.g_f32, a.partial02, ceil_div(2 * a.H, kBM),
-                  ceil_div(a.D, btv), a.gb02};
+                  ceil_div(a.D, btv), a.gb02, a.g02_prev};
     auto& P1 = g.prob[1];
     LACT_TRY(make_operand(kb_of(P1), &P1.a[0], &P1.ai[0], vm, 1, kBM, 0, static_cast<int>(a.start)));
     LACT_TRY(make_operand(kb_of(P1), &P1.b[0], &P1.bi[0], hid, 1, btv, 0, 0));
     P1.M = static_cast<int>(a.D); P1.N = static_cast<int>(a.H); P1.K = static_cast<int>(len);
     P1.batch = static_cast<int>(a.B);
     P1.ep = EpiDW{a.g1, a.D * a.H, a.H, a.beta, 1, a.g_f32, a.partial1, ceil_div(a.D, kBM), ceil_div(a.H, btv),
-                  a.gb1};
+                  a.gb1, a.g1_prev};
     g.status = status;
     return LACT_OK;
   };
@@ -1049,12 +1051,24 @@ int scan_fwd(const lact_scan_config& c, const lact_scan_io& io, int32_t n_steps,
 
   const int64_t B = c.B, D = c.D, H = c.H;
   LACT_CUDA(cudaMemsetAsync(p.status, 0, 256, stream));
+  // Training (post-norm): the per-update state the backward needs is not copied out, it LIVES in the caller's dump:
+  // update u reads its master weights from slot u and writes the new ones into slot u + 1 (the last update into the
+  // workspace), and the gradient / momentum state of update u is written into slot u while slot u - 1 is read.
+  const size_t n02 = static_cast<size_t>(B) * 2 * H * D, n1 = static_cast<size_t>(B) * D * H;
+  int n_updates = 0;
+  for (int i = 0; i < n_steps; ++i) n_updates += kind[i] == LACT_STEP_UPDATE;
+  const bool dump_in_place = io.state_dump != nullptr && !c.prenorm && n_updates > 0;
+  auto slot = [&](int u) { return static_cast<float*>(io.state_dump) + static_cast<size_t>(u) * 2 * (n02 + n1); };
+  float* W02cur = dump_in_place ? slot(0) : p.W02;   // master weights in force
+  float* W1cur = dump_in_place ? slot(0) + n02 : p.W1;
+  float* G02cur = p.G02;                              // gradient / momentum state after the latest update
+  float* G1cur = p.G1;
   {
     const int64_t rows = B * (2 * H + D);
     KernelScope scope(kClsPrepare, stream);
     prepare_weights_kernel<<<ceil_div(rows, 8), 256, 0, stream>>>(io.w0, io.w1, io.w2, c.w_dtype == LACT_F32,
                                                                   static_cast<int>(B), static_cast<int>(H),
-                                                                  static_cast<int>(D), p.W02, p.W1, p.W02c, p.W1c,
+                                                                  static_cast<int>(D), W02cur, W1cur, p.W02c, p.W1c,
                                                                   p.n02, p.n1, p.W02b, p.W1b);
     LACT_CUDA(cudaGetLastError());
   }
@@ -1112,16 +1126,25 @@ int scan_fwd(const lact_scan_config& c, const lact_scan_io& io, int32_t n_steps,
     }
     const float* beta = c.use_momentum ? p.beta + static_cast<int64_t>(update_idx) * B : nullptr;
     float* dump = nullptr;
-    if (io.state_dump != nullptr) {
-      // training: weights used by this update and (below) its gradient after momentum
-      const size_t n02 = static_cast<size_t>(B) * 2 * H * D, n1 = static_cast<size_t>(B) * D * H;
-      dump = static_cast<float*>(io.state_dump) + static_cast<size_t>(update_idx) * 2 * (n02 + n1);
+    if (io.state_dump != nullptr && !dump_in_place) {
+      // training (pre-norm): the weights this update computed with and (below) its gradient after momentum are copied
+      dump = slot(update_idx);
       LACT_CUDA(cudaMemcpyAsync(dump, c.prenorm ? p.W02c : p.W02, n02 * 4, cudaMemcpyDeviceToDevice, stream));
       LACT_CUDA(cudaMemcpyAsync(dump + n02, c.prenorm ? p.W1c : p.W1, n1 * 4, cudaMemcpyDeviceToDevice, stream));
     }
+    const float* G02prev = nullptr;
+    const float* G1prev = nullptr;
+    if (dump_in_place) {
+      G02prev = G02cur;
+      G1prev = G1cur;
+      G02cur = slot(update_idx) + n02 + n1;
+      G1cur = slot(update_idx) + 2 * n02 + n1;
+    }
     ++update_idx;
     GradArgs g{p.W02b, p.W1b, io.k, io.v, c.k_bs, c.k_ts, c.v_bs, c.v_ts, start[i], end[i], io.lr0, io.lr1, io.lr2,
-               c.lr_dtype == LACT_F32, c.L, c.w_scale, p.dy02, p.hid, p.G02, p.G1, 1, beta, B, D, H};
+               c.lr_dtype == LACT_F32, c.L, c.w_scale, p.dy02, p.hid, G02cur, G1cur, 1, beta, B, D, H};
+    g.g02_prev = G02prev;
+    g.g1_prev = G1prev;
     // The Frobenius norms Newton-Schulz needs are gathered per output tile by the contraction when a
     // tile never straddles two matrices (concatenated [2H, D], or H a multiple of the 128-row tile).
     int fused_parts[2] = {0, 0};
@@ -1143,7 +1166,6 @@ int scan_fwd(const lact_scan_config& c, const lact_scan_io& io, int32_t n_steps,
     }
     LACT_TRY(run_grad(g, p.status, stream));
     if (dump != nullptr) {
-      const size_t n02 = static_cast<size_t>(B) * 2 * H * D, n1 = static_cast<size_t>(B) * D * H;
       LACT_CUDA(cudaMemcpyAsync(dump + n02 + n1, p.G02, n02 * 4, cudaMemcpyDeviceToDevice, stream));
       LACT_CUDA(cudaMemcpyAsync(dump + 2 * n02 + n1, p.G1, n1 * 4, cudaMemcpyDeviceToDevice, stream));
     }
@@ -1157,10 +1179,14 @@ int scan_fwd(const lact_scan_config& c, const lact_scan_io& io, int32_t n_steps,
       const int R = static_cast<int>(w == 0 ? 2 * H : D), C = static_cast<int>(w == 0 ? D : H);
       if (C > kRenormMaxCols) return LACT_ERR_SHAPE;
       r.master = w == 0 ? p.W02 : p.W1;
+      if (dump_in_place) {  // read slot u, write slot u + 1 (the last update writes the workspace copy)
+        r.master_in = w == 0 ? W02cur : W1cur;
+        if (update_idx < n_updates) r.master = w == 0 ? slot(update_idx) : slot(update_idx) + n02;
+      }
       r.compute = want_compute ? (w == 0 ? p.W02c : p.W1c) : nullptr;
       r.shadow = w == 0 ? p.W02b : p.W1b;
       r.n0 = w == 0 ? p.n02 : p.n1;
-      r.g = w == 0 ? p.G02 : p.G1;
+      r.g = w == 0 ? G02cur : G1cur;
       r.x = nullptr;
       r.x_bs = static_cast<int64_t>(R) * C;
       r.B = static_cast<int>(B); r.R = R; r.C = C;
@@ -1171,7 +1197,7 @@ int scan_fwd(const lact_scan_config& c, const lact_scan_io& io, int32_t n_steps,
       // buffers (the layout lact_ns_trace_bwd reads); the first iterate is the explicitly normalised gradient
       NsPlan& ns = p.ns;
       const bf16* xres[2] = {nullptr, nullptr};
-      const void* srcs[2] = {p.G02, p.G1};
+      const void* srcs[2] = {G02cur, G1cur};
       NsGroup tg[2];
       NsKeep keep[2];
       uint8_t* tb = static_cast<uint8_t*>(io.ns_trace) + static_cast<size_t>(update_idx - 1) * ns_trace_stride;
@@ -1190,7 +1216,7 @@ int scan_fwd(const lact_scan_config& c, const lact_scan_io& io, int32_t n_steps,
     } else if (c.use_muon) {
       NsPlan& ns = p.ns;
       const bf16* xres[2] = {nullptr, nullptr};
-      const void* srcs[2] = {p.G02, p.G1};
+      const void* srcs[2] = {G02cur, G1cur};
       const int unscaled = g.gb02 != nullptr ? 1 : 0;
       LACT_TRY(launch_ns_prepare(ns.grp, ns.ngroups, srcs, 1, !unscaled, stream,
                                  fused_parts[0] > 0 ? fused_parts : nullptr));
@@ -1202,6 +1228,10 @@ int scan_fwd(const lact_scan_config& c, const lact_scan_io& io, int32_t n_steps,
       rn[1].x = xres[1];
     }
     LACT_TRY(launch_add_renorm(rn[0], rn[1], stream));
+    if (dump_in_place) {
+      W02cur = rn[0].master;
+      W1cur = rn[1].master;
+    }
   }
   // final state out
   if (io.w0_out) LACT_CUDA(cudaMemcpy2DAsync(io.w0_out, H * D * 4, p.W02c, 2 * H * D * 4, H * D * 4, B,
@@ -1209,11 +1239,11 @@ int scan_fwd(const lact_scan_config& c, const lact_scan_io& io, int32_t n_steps,
   if (io.w2_out) LACT_CUDA(cudaMemcpy2DAsync(io.w2_out, H * D * 4, p.W02c + H * D, 2 * H * D * 4, H * D * 4, B,
                                              cudaMemcpyDeviceToDevice, stream));
   if (io.w1_out) LACT_CUDA(cudaMemcpyAsync(io.w1_out, p.W1c, B * D * H * 4, cudaMemcpyDeviceToDevice, stream));
-  if (io.m0_out) LACT_CUDA(cudaMemcpy2DAsync(io.m0_out, H * D * 4, p.G02, 2 * H * D * 4, H * D * 4, B,
+  if (io.m0_out) LACT_CUDA(cudaMemcpy2DAsync(io.m0_out, H * D * 4, G02cur, 2 * H * D * 4, H * D * 4, B,
                                              cudaMemcpyDeviceToDevice, stream));
-  if (io.m2_out) LACT_CUDA(cudaMemcpy2DAsync(io.m2_out, H * D * 4, p.G02 + H * D, 2 * H * D * 4, H * D * 4, B,
+  if (io.m2_out) LACT_CUDA(cudaMemcpy2DAsync(io.m2_out, H * D * 4, G02cur + H * D, 2 * H * D * 4, H * D * 4, B,
                                              cudaMemcpyDeviceToDevice, stream));
-  if (io.m1_out) LACT_CUDA(cudaMemcpyAsync(io.m1_out, p.G1, B * D * H * 4, cudaMemcpyDeviceToDevice, stream));
+  if (io.m1_out) LACT_CUDA(cudaMemcpyAsync(io.m1_out, G1cur, B * D * H * 4, cudaMemcpyDeviceToDevice, stream));
   return LACT_OK;
 }
 

@@ -82,6 +82,9 @@ struct EpiDW {
   int32_t tiles_m, tiles_n;
   // optional: bf16 copy of g with the same strides (the first Newton-Schulz iterate before scaling)
   bf16* gb;
+  // optional: the momentum state is read from here instead of `g` (same layout, fp32): training keeps every update's
+  // state in its own slot, so the previous one is read and the next one written without a copy in between
+  const float* g_prev = nullptr;
   // One warp's 32 x 32 block of results, thread `lane` holding row `row0 + lane` in v[0..31].  The block goes
   // through `scratch` (this warp's 32 x 144 bytes of shared memory) so that the read-modify-write of the fp32
   // state is issued with eight lanes per 128-byte row segment (four full lines per instruction) instead of one
@@ -109,7 +112,8 @@ struct EpiDW {
       const int row = row0 + i * 4 + rsub;
       old[i] = make_float4(0.f, 0.f, 0.f, 0.f);
       if (rmw && col_ok && row < M)
-        old[i] = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(g) + base + static_cast<int64_t>(row) * ld);
+        old[i] = *reinterpret_cast<const float4*>((g_prev != nullptr ? g_prev : reinterpret_cast<const float*>(g)) + base +
+                                                  static_cast<int64_t>(row) * ld);
     }
     float ss = 0.f;
 #pragma unroll
@@ -658,6 +662,7 @@ __global__ void __launch_bounds__(256) ns_scale_kernel(const NsPrepArgs args) {
 
 struct RenormArgs {
   float* master;     // [B][R][C] fp32, in/out
+  const float* master_in;  // nullptr, or where the current master is read from (`master` is then written only)
   float* compute;    // [B][R][C] fp32 out (may be nullptr): the weights the next step computes with
   bf16* shadow;      // [B][R][C] bf16 out
   const float* n0;   // [B][R]
@@ -697,7 +702,7 @@ __device__ __forceinline__ void renorm_row(const RenormArgs& a, int64_t row, int
         upd = *reinterpret_cast<const float4*>(a.g + off + c);
       }
       const float4 base = use_g_base ? *reinterpret_cast<const float4*>(a.g + off + c)
-                                     : *reinterpret_cast<const float4*>(a.master + off + c);
+                                     : *reinterpret_cast<const float4*>((a.master_in != nullptr ? a.master_in : a.master) + off + c);
       w[i] = make_float4(base.x + upd.x, base.y + upd.y, base.z + upd.z, base.w + upd.w);
       ss += w[i].x * w[i].x + w[i].y * w[i].y + w[i].z * w[i].z + w[i].w * w[i].w;
     }
