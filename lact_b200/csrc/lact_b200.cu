@@ -610,14 +610,14 @@ int run_ns_iterations(const NsGroup* grp, int ngroups, int steps, int const_coef
 struct NsKeep {
   bf16 *X, *A, *P;
 };
-template <int BT_MM, int BT_MN, int NITER>
+template <int BT_MM, int BT_MN, int NITER, bool SYM = false>
 int launch_ns_fused(const NsGroup* grp, int ngroups, int steps, int const_coeffs, int32_t* status,
                     cudaStream_t stream, int unscaled_first, const NsKeep* keep = nullptr, int coef_offset = 0) {
-  using Args = NsFusedArgs<BT_MM, BT_MN, NITER>;
-  auto kernel = ns_fused_kernel<BT_MM, BT_MN, NITER>;
-  constexpr uint32_t smem = ns_fused_smem_bytes<BT_MM, BT_MN>();
+  using Args = NsFusedArgs<BT_MM, BT_MN, NITER, SYM>;
+  auto kernel = ns_fused_kernel<BT_MM, BT_MN, NITER, SYM>;
+  constexpr uint32_t smem = ns_fused_smem_bytes<BT_MM, BT_MN, SYM>();
   static_assert(smem <= 232448, "shared memory budget exceeded");
-  static_assert(ns_fused_ring<BT_MM, BT_MN>() >= 2, "ring too shallow");
+  static_assert(ns_fused_ring<BT_MM, BT_MN, SYM>() >= 2, "ring too shallow");
   static std::mutex mu;
   static bool configured[64] = {false};
   int dev = 0;
@@ -698,6 +698,17 @@ int try_ns_fused(const NsGroup* grp, int ngroups, int steps, int const_coeffs, i
   (keep == nullptr ? launch_ns_fused<BTV, BTV, 2>(grp, ngroups, steps, const_coeffs, status, stream, unscaled_first) \
                    : launch_ns_fused<BTV, BTV, 5>(grp, ngroups, steps, const_coeffs, status, stream, unscaled_first, keep))
   const int64_t want = static_cast<int64_t>(sm_count()) * 3 / 4;
+  // Gram side a multiple of 128 in every group and plenty of matrices: the symmetric phases (Gram matrix, polynomial)
+  // run on 128 x 128 tiles on and above the diagonal only, the update keeps its 192-wide tiles
+  bool sym_ok = bt_mm == 192 && bt_mn == 192 && gram_tiles(192) >= want;
+#ifdef LACT_NO_SYM
+  sym_ok = false;
+#endif
+  for (int g = 0; g < ngroups; ++g) sym_ok = sym_ok && grp[g].m % kBM == 0 && grp[g].m >= 2 * kBM;
+  if (sym_ok)
+    return keep == nullptr
+               ? launch_ns_fused<128, 192, 2, true>(grp, ngroups, steps, const_coeffs, status, stream, unscaled_first)
+               : launch_ns_fused<128, 192, 5, true>(grp, ngroups, steps, const_coeffs, status, stream, unscaled_first, keep);
   if (bt_mm == 192 && bt_mn == 192 && gram_tiles(192) >= want) return LACT_NS_FUSED(192);
   // (a 256-wide update tile leaves no room for a useful ring next to two staging tiles: 128 is used)
   const bool ok128 = (bt_mm == 192 && bt_mn == 192) || (bt_mm == 128 && (bt_mn == 128 || bt_mn == 256));
@@ -800,15 +811,15 @@ static int ns_norm_bwd_launch(const float* g, const void* dx0, int dx_bf16, floa
 }
 
 // ---- all iterations of the Newton-Schulz backward of one or two groups in one cooperative launch
-template <int BT>
+template <int BT_MM, int BT, bool SYM>
 static int launch_ns_bwd_fused(const NsTrace* tr, const bf16* const* du, int ngroups, int steps, int const_coeffs,
                                int32_t* status, cudaStream_t stream) {
   constexpr int NITER = 5;
-  using Args = NsBwdFusedArgs<BT, NITER>;
-  auto kernel = ns_bwd_fused_kernel<BT, NITER>;
-  constexpr uint32_t smem = ns_bwd_smem_bytes<BT>();
+  using Args = NsBwdFusedArgs<BT_MM, BT, NITER, SYM>;
+  auto kernel = ns_bwd_fused_kernel<BT_MM, BT, NITER, SYM>;
+  constexpr uint32_t smem = ns_bwd_smem_bytes<BT_MM, BT, SYM>();
   static_assert(smem <= 232448, "shared memory budget exceeded");
-  static_assert(ns_bwd_ring<BT>() >= 2, "ring too shallow");
+  static_assert(ns_bwd_ring<BT_MM, BT, SYM>() >= 2, "ring too shallow");
   static_assert(sizeof(Args) <= 32000, "kernel parameter block too large");
   static std::mutex mu;
   static bool configured[64] = {false};
@@ -846,16 +857,16 @@ static int launch_ns_bwd_fused(const NsTrace* tr, const bf16* const* du, int ngr
       auto& px = args.dx[it][g];
       // Q = dX X^T + X dX^T (wide; the iterate's rows are K-major operands) / dX^T X + X^T dX (tall; MN-major)
       LACT_TRY(make_operand(1, &pq.a[0], &pq.ai[0], D, tall, kBM, 0, 0));
-      LACT_TRY(make_operand(1, &pq.b[0], &pq.bi[0], X, tall, BT, 0, 0));
+      LACT_TRY(make_operand(1, &pq.b[0], &pq.bi[0], X, tall, BT_MM, 0, 0));
       LACT_TRY(make_operand(1, &pq.a[1], &pq.ai[1], X, tall, kBM, 0, 0));
-      LACT_TRY(make_operand(1, &pq.b[1], &pq.bi[1], D, tall, BT, 0, 0));
+      LACT_TRY(make_operand(1, &pq.b[1], &pq.bi[1], D, tall, BT_MM, 0, 0));
       pq.M = G.m; pq.N = G.m; pq.K = G.n; pq.batch = G.nmat;
       LACT_TRY(make_output(&pq.out[0], &pq.oi[0], Q, 0, 0));
       // T = c (S Q + Q S): all three symmetric, rows serve as K-major operands on either side
       LACT_TRY(make_operand(1, &pt.a[0], &pt.ai[0], S, 0, kBM, 0, 0));
-      LACT_TRY(make_operand(1, &pt.b[0], &pt.bi[0], Q, 0, BT, 0, 0));
+      LACT_TRY(make_operand(1, &pt.b[0], &pt.bi[0], Q, 0, BT_MM, 0, 0));
       LACT_TRY(make_operand(1, &pt.a[1], &pt.ai[1], Q, 0, kBM, 0, 0));
-      LACT_TRY(make_operand(1, &pt.b[1], &pt.bi[1], S, 0, BT, 0, 0));
+      LACT_TRY(make_operand(1, &pt.b[1], &pt.bi[1], S, 0, BT_MM, 0, 0));
       pt.M = G.m; pt.N = G.m; pt.K = G.m; pt.batch = G.nmat;
       LACT_TRY(make_output(&pt.out[0], &pt.oi[0], T, 0, 0));
       // dX_i = P dX + T X (wide: the [k][n] iterates are MN-major B operands) / dX P + X T (tall)
@@ -2048,10 +2059,15 @@ int lact_ns_trace_bwd_fused(const lact_ns_bwd_group* groups, int32_t ngroups, in
   for (int cand : {192, 128, 64})
     if (mm_tiles(cand) >= want && (bt == 0 || padded_work(cand) < padded_work(bt))) bt = cand;
   if (bt == 0) bt = mm_tiles(64) > mm_tiles(128) ? 64 : (mm_tiles(128) > mm_tiles(192) ? 128 : 192);
+  // Q and T are symmetric: with Gram sides that are multiples of 128 their phases run on the 128 x 128 tiles on and
+  // above the diagonal only
+  bool sym_ok = bt == 192;
+  for (int g = 0; g < ngroups; ++g) sym_ok = sym_ok && grp[g].m % kBM == 0 && grp[g].m >= 2 * kBM;
   int rc = LACT_ERR_CONFIG;
-  if (bt == 192) rc = launch_ns_bwd_fused<192>(tr, du, ngroups, steps, const_coeffs, status_word, s);
-  else if (bt == 128) rc = launch_ns_bwd_fused<128>(tr, du, ngroups, steps, const_coeffs, status_word, s);
-  else rc = launch_ns_bwd_fused<64>(tr, du, ngroups, steps, const_coeffs, status_word, s);
+  if (sym_ok) rc = launch_ns_bwd_fused<128, 192, true>(tr, du, ngroups, steps, const_coeffs, status_word, s);
+  else if (bt == 192) rc = launch_ns_bwd_fused<192, 192, false>(tr, du, ngroups, steps, const_coeffs, status_word, s);
+  else if (bt == 128) rc = launch_ns_bwd_fused<128, 128, false>(tr, du, ngroups, steps, const_coeffs, status_word, s);
+  else rc = launch_ns_bwd_fused<64, 64, false>(tr, du, ngroups, steps, const_coeffs, status_word, s);
   if (rc != LACT_OK) return rc;
   // the gradient w.r.t. the first iterate is the bf16 buffer the last phase wrote; the Frobenius normalisation
   // X0 = bf16(G) / (||G|| + 1e-7) is differentiated into the caller's fp32 dG

@@ -12,10 +12,11 @@
 
 namespace lact {
 
-template <int BT, int NITER>
+// SYM: Q and T (both symmetric) are computed on and above the diagonal only, in 128 x 128 tiles (BT_MM = 128).
+template <int BT_MM, int BT, int NITER, bool SYM>
 struct NsBwdFusedArgs {
-  GemmProblem<OpNs2<BT>> q[NITER][2];    // [iteration][group]
-  GemmProblem<OpNs2<BT>> t[NITER][2];
+  GemmProblem<OpNs2T<BT_MM, SYM>> q[NITER][2];    // [iteration][group]
+  GemmProblem<OpNs2T<BT_MM, SYM>> t[NITER][2];
   GemmProblem<OpNs2<BT>> dx[NITER][2];
   float coef_c[NITER];                   // c of (a, b, c) per iteration
   int32_t steps, ngroups;
@@ -23,26 +24,38 @@ struct NsBwdFusedArgs {
   uint32_t* done[2];  // per group: [matrix] completion counters, zero at launch
 };
 
-template <int BT>
-__host__ __device__ constexpr int ns_bwd_ring() {
-  return static_cast<int>((232448u - 1024u - 256u - kBM * BT * 2) / gemm_stage_bytes<OpNs2<BT>>());
+template <int BT_MM, int BT, bool SYM>
+__host__ __device__ constexpr uint32_t ns_bwd_stride() {
+  return gemm_stage_bytes<OpNs2T<BT_MM, SYM>>() > gemm_stage_bytes<OpNs2<BT>>() ? gemm_stage_bytes<OpNs2T<BT_MM, SYM>>()
+                                                                               : gemm_stage_bytes<OpNs2<BT>>();
 }
-template <int BT>
+template <int BT_MM, int BT, bool SYM>
+__host__ __device__ constexpr uint32_t ns_bwd_staging() {
+  return gemm_staging_bytes<OpNs2T<BT_MM, SYM>>() > gemm_staging_bytes<OpNs2<BT>>() ? gemm_staging_bytes<OpNs2T<BT_MM, SYM>>()
+                                                                                   : gemm_staging_bytes<OpNs2<BT>>();
+}
+template <int BT_MM, int BT, bool SYM>
+__host__ __device__ constexpr int ns_bwd_ring() {
+  return static_cast<int>((232448u - 1024u - 256u - ns_bwd_staging<BT_MM, BT, SYM>()) / ns_bwd_stride<BT_MM, BT, SYM>());
+}
+template <int BT_MM, int BT, bool SYM>
 __host__ __device__ constexpr uint32_t ns_bwd_smem_bytes() {
-  return ns_bwd_ring<BT>() * gemm_stage_bytes<OpNs2<BT>>() + kBM * BT * 2 + 1024 + 256;
+  return ns_bwd_ring<BT_MM, BT, SYM>() * ns_bwd_stride<BT_MM, BT, SYM>() + ns_bwd_staging<BT_MM, BT, SYM>() + 1024 + 256;
 }
 
-template <int BT, int NITER>
+template <int BT_MM, int BT, int NITER, bool SYM>
 __global__ void __launch_bounds__(kGemmThreadsFlow, 1)
-ns_bwd_fused_kernel(const __grid_constant__ NsBwdFusedArgs<BT, NITER> args) {
+ns_bwd_fused_kernel(const __grid_constant__ NsBwdFusedArgs<BT_MM, BT, NITER, SYM> args) {
+  static_assert(!SYM || BT_MM == kBM, "symmetric phases use square 128 x 128 tiles");
+  using OpMM = OpNs2T<BT_MM, SYM>;
   using Op = OpNs2<BT>;
-  constexpr int RING = ns_bwd_ring<BT>();
+  constexpr int RING = ns_bwd_ring<BT_MM, BT, SYM>();
   constexpr uint32_t kTmemCols = 512;
   griddep_launch_dependents();
   if (*reinterpret_cast<volatile int32_t*>(args.status) != kStatusOk) return;  // uniform over the grid
   extern __shared__ uint8_t smem_raw[];
   GemmCtx cx;
-  gemm_setup(cx, smem_raw, RING, gemm_stage_bytes<Op>(), kBM * BT * 2, kTmemCols);
+  gemm_setup(cx, smem_raw, RING, ns_bwd_stride<BT_MM, BT, SYM>(), ns_bwd_staging<BT_MM, BT, SYM>(), kTmemCols);
   bool failed = false;
   NsPatch patch;
   FlowDeps deps;
@@ -53,18 +66,19 @@ ns_bwd_fused_kernel(const __grid_constant__ NsBwdFusedArgs<BT, NITER> args) {
     deps.need[g] = 0;
     const auto& A = args.q[0][g];
     const auto& U = args.dx[0][g];
-    tiles_mm[g] = ((A.M + kBM - 1) / kBM) * ((A.N + BT - 1) / BT);
+    const uint32_t tm = (A.M + kBM - 1) / kBM;
+    tiles_mm[g] = SYM ? tm * (tm + 1) / 2 : tm * ((A.N + BT_MM - 1) / BT_MM);
     tiles_mn[g] = ((U.M + kBM - 1) / kBM) * ((U.N + BT - 1) / BT);
   }
   patch.diag = 0.f;
   patch.scale_pow = 0;
   for (int it = args.steps - 1; it >= 0 && !failed; --it) {
     patch.acc_scale = 1.f;
-    failed = gemm_phase<Op, RING>(cx, args.q[it], args.ngroups, patch, deps);
+    failed = gemm_phase<OpMM, RING>(cx, args.q[it], args.ngroups, patch, deps);
     if (failed) break;
     for (int g = 0; g < 2; ++g) deps.need[g] += tiles_mm[g];
     patch.acc_scale = args.coef_c[it];
-    failed = gemm_phase<Op, RING>(cx, args.t[it], args.ngroups, patch, deps);
+    failed = gemm_phase<OpMM, RING>(cx, args.t[it], args.ngroups, patch, deps);
     if (failed) break;
     for (int g = 0; g < 2; ++g) deps.need[g] += tiles_mm[g];
     patch.acc_scale = 1.f;

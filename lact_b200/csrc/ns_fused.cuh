@@ -14,10 +14,11 @@ namespace lact {
 // NITER sets of problems are held, iteration `it` uses set it % NITER: two sets for the plain iteration (the iterates
 // ping-pong between two buffers), one set per iteration when every iterate, shifted Gram matrix and polynomial is
 // kept for the backward pass (steps <= NITER then).
-template <int BT_MM, int BT_MN, int NITER = 2>
+// SYM: the Gram and polynomial phases compute only the tiles on and above the diagonal (BT_MM = 128).
+template <int BT_MM, int BT_MN, int NITER = 2, bool SYM = false>
 struct NsFusedArgs {
-  GemmProblem<OpNs<BT_MM>> gram[NITER][2];  // [iteration % NITER][group]
-  GemmProblem<OpNs<BT_MM>> poly[NITER][2];
+  GemmProblem<OpNsT<BT_MM, SYM>> gram[NITER][2];  // [iteration % NITER][group]
+  GemmProblem<OpNsT<BT_MM, SYM>> poly[NITER][2];
   GemmProblem<OpNs<BT_MN>> upd[NITER][2];
   const float* scale[2];                // per group: [matrix] 1 / (||G|| + 1e-7) when the first iterate is unscaled
   float coef[16][3];                    // (a, b, c) per iteration
@@ -40,39 +41,41 @@ struct NsPatch {
   }
 };
 
-template <int BT_MM, int BT_MN>
+template <int BT_MM, int BT_MN, bool SYM = false>
 __host__ __device__ constexpr uint32_t ns_fused_stage_stride() {
-  return gemm_stage_bytes<OpNs<BT_MM>>() > gemm_stage_bytes<OpNs<BT_MN>>() ? gemm_stage_bytes<OpNs<BT_MM>>()
-                                                                         : gemm_stage_bytes<OpNs<BT_MN>>();
+  return gemm_stage_bytes<OpNsT<BT_MM, SYM>>() > gemm_stage_bytes<OpNs<BT_MN>>() ? gemm_stage_bytes<OpNsT<BT_MM, SYM>>()
+                                                                                : gemm_stage_bytes<OpNs<BT_MN>>();
 }
-template <int BT_MM, int BT_MN>
+template <int BT_MM, int BT_MN, bool SYM = false>
 __host__ __device__ constexpr uint32_t ns_fused_staging() {
-  return kBM * (BT_MM > BT_MN ? BT_MM : BT_MN) * 2;
+  return gemm_staging_bytes<OpNsT<BT_MM, SYM>>() > gemm_staging_bytes<OpNs<BT_MN>>() ? gemm_staging_bytes<OpNsT<BT_MM, SYM>>()
+                                                                                    : gemm_staging_bytes<OpNs<BT_MN>>();
 }
-template <int BT_MM, int BT_MN>
+template <int BT_MM, int BT_MN, bool SYM = false>
 __host__ __device__ constexpr int ns_fused_ring() {
-  return static_cast<int>((232448u - 1024u - 256u - ns_fused_staging<BT_MM, BT_MN>()) /
-                          ns_fused_stage_stride<BT_MM, BT_MN>());
+  return static_cast<int>((232448u - 1024u - 256u - ns_fused_staging<BT_MM, BT_MN, SYM>()) /
+                          ns_fused_stage_stride<BT_MM, BT_MN, SYM>());
 }
-template <int BT_MM, int BT_MN>
+template <int BT_MM, int BT_MN, bool SYM = false>
 __host__ __device__ constexpr uint32_t ns_fused_smem_bytes() {
-  return ns_fused_ring<BT_MM, BT_MN>() * ns_fused_stage_stride<BT_MM, BT_MN>() + ns_fused_staging<BT_MM, BT_MN>() +
-         1024 + 256;
+  return ns_fused_ring<BT_MM, BT_MN, SYM>() * ns_fused_stage_stride<BT_MM, BT_MN, SYM>() +
+         ns_fused_staging<BT_MM, BT_MN, SYM>() + 1024 + 256;
 }
 
-template <int BT_MM, int BT_MN, int NITER>
+template <int BT_MM, int BT_MN, int NITER, bool SYM = false>
 __global__ void __launch_bounds__(kGemmThreadsFlow, 1)
-ns_fused_kernel(const __grid_constant__ NsFusedArgs<BT_MM, BT_MN, NITER> args) {
-  using OpMM = OpNs<BT_MM>;
+ns_fused_kernel(const __grid_constant__ NsFusedArgs<BT_MM, BT_MN, NITER, SYM> args) {
+  static_assert(!SYM || BT_MM == kBM, "symmetric phases use square 128 x 128 tiles");
+  using OpMM = OpNsT<BT_MM, SYM>;
   using OpMN = OpNs<BT_MN>;
-  constexpr int RING = ns_fused_ring<BT_MM, BT_MN>();
-  constexpr uint32_t kStride = ns_fused_stage_stride<BT_MM, BT_MN>();
+  constexpr int RING = ns_fused_ring<BT_MM, BT_MN, SYM>();
+  constexpr uint32_t kStride = ns_fused_stage_stride<BT_MM, BT_MN, SYM>();
   constexpr uint32_t kTmemCols = 512;
   griddep_launch_dependents();  // the next kernel may run its prologue while this one works
   if (*reinterpret_cast<volatile int32_t*>(args.status) != kStatusOk) return;  // uniform over the grid
   extern __shared__ uint8_t smem_raw[];
   GemmCtx cx;
-  gemm_setup(cx, smem_raw, RING, kStride, ns_fused_staging<BT_MM, BT_MN>(), kTmemCols);
+  gemm_setup(cx, smem_raw, RING, kStride, ns_fused_staging<BT_MM, BT_MN, SYM>(), kTmemCols);
   if (threadIdx.x == 32) {
     for (int par = 0; par < (NITER < 2 ? NITER : 2); ++par)
       for (int g = 0; g < args.ngroups; ++g) {
@@ -99,7 +102,8 @@ ns_fused_kernel(const __grid_constant__ NsFusedArgs<BT_MM, BT_MN, NITER> args) {
     deps.need[g] = 0;
     const auto& A = args.poly[0][g];
     const auto& U = args.upd[0][g];
-    tiles_mm[g] = ((A.M + kBM - 1) / kBM) * ((A.N + BT_MM - 1) / BT_MM);
+    const uint32_t tm = (A.M + kBM - 1) / kBM;
+    tiles_mm[g] = SYM ? tm * (tm + 1) / 2 : tm * ((A.N + BT_MM - 1) / BT_MM);
     tiles_mn[g] = ((U.M + kBM - 1) / kBM) * ((U.N + BT_MN - 1) / BT_MN);
   }
   for (int it = 0; it < args.steps && !failed; ++it) {

@@ -300,14 +300,18 @@ struct OpBmm2 {
 // The Frobenius normalisation X0 = G / (||G|| + 1e-7) can be folded in as well: the first iteration then runs
 // on bf16(G) itself and its gram / update epilogues multiply the fp32 accumulator by s^2 / s,
 // s = 1 / (||G|| + 1e-7) (per matrix, `scale`).
-template <int BT_>
-struct OpNs {
+// SYM_: the output is symmetric (Gram matrix, polynomial): only tiles on and above the diagonal are computed and the
+// others are stored as transposes (see op_symmetric in the engine); identical values, a third fewer products at m = 384.
+template <int BT_, bool SYM_>
+struct OpNsT {
   static constexpr int NA = 1, NB = 1, NACC = 1, BT = BT_, NTERMS = 1, NOUT = 1;
   static constexpr bool kTileReduce = false;
   static constexpr bool kWarpTranspose = false, kReverseBatch = false;
+  static constexpr bool kSymmetric = SYM_;
   static constexpr uint32_t kEpiScratch = 0;
-  static constexpr int KB = kb_per_stage(kATileBytes + BT_ * kBK * 2, kBM * BT_ * 2);
-  static constexpr int STAGES = ring_depth(KB * (kATileBytes + BT_ * kBK * 2), kBM * BT_ * 2);
+  static constexpr uint32_t kStagingTiles = (SYM_ ? 2 : 1) * kBM * BT_ * 2;
+  static constexpr int KB = kb_per_stage(kATileBytes + BT_ * kBK * 2, kStagingTiles);
+  static constexpr int STAGES = ring_depth(KB * (kATileBytes + BT_ * kBK * 2), kStagingTiles);
   using Epi = EpiNs;
   __host__ __device__ static constexpr int term_a(int) { return 0; }
   __host__ __device__ static constexpr int term_b(int) { return 0; }
@@ -332,16 +336,20 @@ struct OpNs {
   }
 };
 
+template <int BT_>
+using OpNs = OpNsT<BT_, false>;
+
 // Two-product Newton-Schulz GEMM for the backward pass: out = bf16(acc_scale * (a0 b0^T + a1 b1^T)), both products
 // into one accumulator (equal K), one k-block of both products per ring stage, staged (TMA-stored) output.
-template <int BT_>
-struct OpNs2 {
+template <int BT_, bool SYM_>
+struct OpNs2T {
   static constexpr int NA = 2, NB = 2, NACC = 1, BT = BT_, NTERMS = 2, NOUT = 1;
   static constexpr bool kTileReduce = false;
   static constexpr bool kWarpTranspose = false, kReverseBatch = false;
+  static constexpr bool kSymmetric = SYM_;
   static constexpr uint32_t kEpiScratch = 0;
   static constexpr int KB = 1;
-  static constexpr int STAGES = ring_depth(2 * (kATileBytes + BT_ * kBK * 2), kBM * BT_ * 2);
+  static constexpr int STAGES = ring_depth(2 * (kATileBytes + BT_ * kBK * 2), (SYM_ ? 2 : 1) * kBM * BT_ * 2);
   using Epi = EpiNs;
   __host__ __device__ static constexpr int term_a(int t) { return t; }
   __host__ __device__ static constexpr int term_b(int t) { return t; }
@@ -361,6 +369,9 @@ struct OpNs2 {
     for (int j = 0; j < 32; ++j) o[0][j] = v[0][j] * pf.sc;
   }
 };
+
+template <int BT_>
+using OpNs2 = OpNs2T<BT_, false>;
 
 // [y0 | y2] = x [w0 slice ; w2 slice]^T; epilogue = SwiGLU gate, staged.  With one k-block per stage
 // the two weight tiles are adjacent in shared memory and one 128 x 2BT MMA covers both; with two

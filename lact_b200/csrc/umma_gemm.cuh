@@ -72,9 +72,7 @@ __host__ __device__ constexpr uint32_t gemm_stage_bytes() {
 // bf16 staging tiles for TMA-stored outputs: NOUT x [128 rows][BT columns], 128-byte swizzled in
 // 64-column panels (the layout the output tensor maps expect)
 template <class Op>
-__host__ __device__ constexpr uint32_t gemm_staging_bytes() {
-  return Op::NOUT * kBM * Op::BT * 2 + Op::kEpiScratch;
-}
+__host__ __device__ constexpr uint32_t gemm_staging_bytes();
 template <class Op>
 __host__ __device__ constexpr uint32_t gemm_smem_bytes() {
   return Op::STAGES * gemm_stage_bytes<Op>() + gemm_staging_bytes<Op>() + 1024 /*alignment slack*/ + 256 /*barriers*/;
@@ -121,6 +119,19 @@ __device__ __forceinline__ uint64_t operand_desc(uint32_t tile, int mn_major, ui
 struct TileCoord {
   int prob, batch, m0, n0;
 };
+
+// Ops whose output is a symmetric M x M matrix (both operands the same rows) may declare `kSymmetric`: only the
+// 128 x 128 tiles on and above the diagonal are computed, and every off-diagonal tile is stored twice, as it is and
+// transposed (from a second staging tile the epilogue fills).  Needs BT = 128, one staged output, dataflow mode.
+template <class Op, class = void>
+struct op_symmetric { static constexpr bool value = false; };
+template <class Op>
+struct op_symmetric<Op, decltype(void(Op::kSymmetric))> { static constexpr bool value = Op::kSymmetric; };
+
+template <class Op>
+__host__ __device__ constexpr uint32_t gemm_staging_bytes() {
+  return (Op::NOUT + (op_symmetric<Op>::value ? 1 : 0)) * kBM * Op::BT * 2 + Op::kEpiScratch;
+}
 
 // Per-thread view of the CTA's pipeline resources and of this thread's progress counters.  The
 // producer thread advances `it`, the MMA thread `it` and `tcount`, epilogue threads `tcount`;
@@ -225,18 +236,25 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
   constexpr uint32_t kAccCols = NACC * BT;
   constexpr int kMaxProb = 2;
   static_assert(2 * kAccCols <= 512, "double-buffered accumulators exceed tensor memory");
+  // Multi-phase (dataflow) kernels run ops of different tile widths back to back without draining the pipeline: the two
+  // accumulator buffers sit at fixed halves of the 512 allocated columns there, so that buffer 0 of one op can never
+  // overlap buffer 1 of the previous op while its epilogue is still reading it.
+  constexpr uint32_t kAccStride = Deps::kOn ? 256u : kAccCols;
   static_assert(BT % 64 == 0 && BT <= 256, "BT must be 64, 128, 192 or 256");
 
-  int tiles_of[kMaxProb], tn_of[kMaxProb], tm_of[kMaxProb];
+  constexpr bool SYM = op_symmetric<Op>::value;
+  static_assert(!SYM || (BT == kBM && Op::NOUT == 1 && Deps::kOn), "symmetric ops: 128-wide tiles, one staged output, dataflow");
+  int tiles_of[kMaxProb], tn_of[kMaxProb], tm_of[kMaxProb], per_batch_of[kMaxProb];
   int total_tiles = 0;
 #pragma unroll
   for (int p = 0; p < kMaxProb; ++p) {
     if (p < nprob) {
       tn_of[p] = (probs[p].N + BT - 1) / BT;
       tm_of[p] = (probs[p].M + kBM - 1) / kBM;
-      tiles_of[p] = tn_of[p] * tm_of[p] * probs[p].batch;
+      per_batch_of[p] = SYM ? tm_of[p] * (tm_of[p] + 1) / 2 : tn_of[p] * tm_of[p];
+      tiles_of[p] = per_batch_of[p] * probs[p].batch;
     } else {
-      tn_of[p] = tm_of[p] = 1;
+      tn_of[p] = tm_of[p] = per_batch_of[p] = 1;
       tiles_of[p] = 0;
     }
     total_tiles += tiles_of[p];
@@ -245,14 +263,22 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
     TileCoord c;
     c.prob = 0;
     if (tile >= tiles_of[0]) { tile -= tiles_of[0]; c.prob = 1; }
-    const int per_batch = tn_of[c.prob] * tm_of[c.prob];
+    const int per_batch = per_batch_of[c.prob];
     c.batch = tile / per_batch;
-    const int r = tile - c.batch * per_batch;
+    int r = tile - c.batch * per_batch;
     // a consumer of large intermediates walks the batch entries backwards: the entries its producer wrote last
     // are the ones still in L2
     if constexpr (Op::kReverseBatch) c.batch = probs[c.prob].batch - 1 - c.batch;
-    c.m0 = (r / tn_of[c.prob]) * kBM;
-    c.n0 = (r % tn_of[c.prob]) * BT;
+    if constexpr (SYM) {
+      // tiles on and above the diagonal, row by row: row i holds the tiles (i, i) .. (i, T - 1)
+      int i = 0, len = tm_of[c.prob];
+      while (r >= len) { r -= len; ++i; --len; }
+      c.m0 = i * kBM;
+      c.n0 = (i + r) * BT;
+    } else {
+      c.m0 = (r / tn_of[c.prob]) * kBM;
+      c.n0 = (r % tn_of[c.prob]) * BT;
+    }
     return c;
   };
 
@@ -309,7 +335,7 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
         const uint32_t as = cx.tcount & 1, aph = (cx.tcount >> 1) & 1;
         if (!mbar_wait(&cx.acc_empty_bar[as], aph ^ 1, cx.abort_flag)) { failed = true; break; }
         tc_fence_after();
-        const uint32_t acc_base = cx.tmem_base + as * kAccCols;
+        const uint32_t acc_base = cx.tmem_base + as * kAccStride;
         const int num_sb = (num_kb + KB - 1) / KB;
         for (int sb = 0; sb < num_sb; ++sb, ++cx.it) {
           const int s = cx.it % RING;
@@ -380,6 +406,16 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
                            P.oi[o].row_off + tc.m0, P.oi[o].batch_off + tc.batch);
             }
           }
+          if constexpr (SYM) {
+            // the transposed tile (second staging tile) goes below the diagonal
+            if (tc.m0 != tc.n0) {
+              for (int pnl = 0; pnl < BT / 64; ++pnl) {
+                if (tc.m0 + pnl * 64 >= P.N) break;
+                tma_store_3d(&P.out[0], stg + kBM * BT * 2 + pnl * (kBM * 128), P.oi[0].col_off + tc.m0 + pnl * 64,
+                             P.oi[0].row_off + tc.n0, P.oi[0].batch_off + tc.batch);
+              }
+            }
+          }
           bulk_commit_group();
           bulk_wait_read_all();
           mbar_arrive(&cx.stg_empty_bar[0]);
@@ -420,7 +456,7 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
       Op::prefetch(ep, tc.batch, row, tc.n0, half, P.M, P.N, pf);
       bool got = mbar_wait(&cx.acc_full_bar[as], aph, cx.abort_flag);
       tc_fence_after();
-      const uint32_t acc_base = cx.tmem_base + as * kAccCols + (static_cast<uint32_t>(quarter * 32) << 16);
+      const uint32_t acc_base = cx.tmem_base + as * kAccStride + (static_cast<uint32_t>(quarter * 32) << 16);
       if constexpr (NOUT > 0) {
         // A warp whose wait ran out must not leave the others stuck at a named barrier: it raises
         // a flag that only epilogue warps write, and every warp decides after the barrier.
@@ -469,6 +505,21 @@ __device__ __forceinline__ bool gemm_phase(GemmCtx& cx, const GemmProblem<Op>* p
                            "r"(pack_bf16x2(ov[o][g * 8 + 4], ov[o][g * 8 + 5])),
                            "r"(pack_bf16x2(ov[o][g * 8 + 6], ov[o][g * 8 + 7]))
                            : "memory");
+            }
+          }
+          if constexpr (SYM) {
+            if (tc.m0 != tc.n0) {
+              // element (row_local, c + j) lands at (c + j, row_local) of the second staging tile: the 32 lanes of a
+              // warp write 32 consecutive columns of one row (64 contiguous bytes)
+              const uint32_t tbase = stg + kBM * BT * 2 + (row_local >> 6) * (kBM * 128) + (row_local & 7) * 2;
+              const uint32_t tunit = (row_local & 63) >> 3;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const uint32_t rt = c + j;
+                const uint32_t addr = tbase + rt * 128 + ((tunit ^ (rt & 7)) << 4);
+                const __nv_bfloat16 hv = __float2bfloat16_rn(ov[0][j]);
+                asm volatile("st.shared.b16 [%0], %1;" ::"r"(addr), "h"(*reinterpret_cast<const uint16_t*>(&hv)) : "memory");
+              }
             }
           }
         } else {
