@@ -501,6 +501,9 @@ def main():
     ap.add_argument("--swa", action="store_true",
                     help="time the sliding-window attention kernel (the other half of a hybrid layer) at the layer "
                          "shape of the benchmark model; prints its own JSON line and exits (not the headline metric)")
+    ap.add_argument("--slabs", type=int, default=None,
+                    help="slabs of (batch x head) units the end-to-end arm streams through the device (default: 8 when "
+                         "the units divide)")
     ap.add_argument("--batch", type=int, default=None,
                     help="override the batch size (profiler captures on a small case; not a headline number)")
     ap.add_argument("--seq-len", type=int, default=None, help="override the sequence length (same caveat)")
@@ -645,7 +648,9 @@ def main():
         n_e2e = max(2, min(steps, 4))
         # the public call, fed from pinned host memory in slabs of (batch x head) entries so that the
         # copies of one slab overlap the kernels of another (every entry is an independent recurrence)
-        n_slabs = 4 if B % 4 == 0 and B >= 16 else (2 if B % 2 == 0 and B >= 8 else 1)
+        n_slabs = 8 if B % 8 == 0 and B >= 32 else (4 if B % 4 == 0 and B >= 16 else (2 if B % 2 == 0 and B >= 8 else 1))
+        if args.slabs is not None and args.slabs >= 1 and B % args.slabs == 0:
+            n_slabs = args.slabs
         pipe = HostPipeline(lambda **kw: run_step(lact_b200, kw), host, out_host, n_slabs=n_slabs, device=dev)
         e2e_step = pipe.run
 

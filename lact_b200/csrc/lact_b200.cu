@@ -701,9 +701,6 @@ int try_ns_fused(const NsGroup* grp, int ngroups, int steps, int const_coeffs, i
   // Gram side a multiple of 128 in every group and plenty of matrices: the symmetric phases (Gram matrix, polynomial)
   // run on 128 x 128 tiles on and above the diagonal only, the update keeps its 192-wide tiles
   bool sym_ok = bt_mm == 192 && bt_mn == 192 && gram_tiles(192) >= want;
-#ifdef LACT_NO_SYM
-  sym_ok = false;
-#endif
   for (int g = 0; g < ngroups; ++g) sym_ok = sym_ok && grp[g].m % kBM == 0 && grp[g].m >= 2 * kBM;
   if (sym_ok)
     return keep == nullptr
