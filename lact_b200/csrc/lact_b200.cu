@@ -1535,9 +1535,11 @@ int lact_ns_trace_bytes(int64_t B, int64_t R, int64_t C, int32_t steps, size_t* 
 int lact_ns_trace_result_offset(int64_t B, int64_t R, int64_t C, int32_t steps, size_t* offset_out) {
   if (!offset_out) return LACT_ERR_NULL;
   NsTrace t;
-  LACT_TRY(plan_ns_trace(nullptr, B, R, C, steps, 0, &t));
-  // with a null base the carved pointers ARE the byte offsets
-  *offset_out = reinterpret_cast<size_t>(t.X) + static_cast<size_t>(B) * R * C * steps * sizeof(bf16);
+  // carve from a fake, never dereferenced base (a null base yields null pointers) and subtract it again
+  uint8_t* const fake = reinterpret_cast<uint8_t*>(static_cast<uintptr_t>(1) << 40);
+  LACT_TRY(plan_ns_trace(fake, B, R, C, steps, 0, &t));
+  *offset_out = static_cast<size_t>(reinterpret_cast<uint8_t*>(t.X) - fake) +
+                static_cast<size_t>(B) * R * C * steps * sizeof(bf16);
   return LACT_OK;
 }
 

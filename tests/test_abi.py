@@ -78,6 +78,22 @@ def test_workspace_queries_and_shape_checks(lib):
     assert lib.lact_scan_workspace_bytes(C.byref(cfg), 3, kind, start, end, C.byref(n)) == -3
 
 
+def test_newton_schulz_trace_layout_queries(lib):
+    """Host-only layout arithmetic of the Newton-Schulz trace: the result (iterate number `steps`) sits behind the
+    norm partials, scale factors and completion counters and `steps` earlier iterates, inside the buffer."""
+    for B, R, Cc, steps in ((2, 64, 128, 1), (4, 128, 64, 5), (3, 384, 384, 3)):
+        off, need = C.c_size_t(0), C.c_size_t(0)
+        assert lib.lact_ns_trace_result_offset(B, R, Cc, steps, C.byref(off)) == 0
+        assert lib.lact_ns_trace_bytes(B, R, Cc, steps, C.byref(need)) == 0
+
+        def up(x):
+            return (x + 255) & ~255
+        x0 = up(up(up(0) + B * 512 * 4) + B * 4)       # partial sums [B][512] fp32, then scale [B] fp32 ...
+        x0 = up(x0 + (B + 64) * 4)                       # ... then completion counters [B + 64] u32, then the iterates
+        assert off.value == x0 + B * R * Cc * steps * 2
+        assert off.value % 16 == 0 and off.value + B * R * Cc * 2 <= need.value
+
+
 def test_python_shim_rejects_cpu_tensors():
     import torch
     import lact_b200

@@ -280,6 +280,33 @@ def test_llm_backward_with_muon_first_chunks(lb):
         assert orc.rel_fro(a, b) <= 0.25, (n, orc.rel_fro(a, b))
 
 
+@pytest.mark.parametrize("iters", [1, 2])
+def test_muon_backward_pins_every_weight_path(lb, iters):
+    """Muon on with ONE or TWO Newton-Schulz iterations (the AR driver's `num_moun_iters`, constant coefficients):
+    the iteration then amplifies bf16 noise little, so each of the nine gradients -- in particular dW0, dW1 and dW2,
+    which reach the loss through three separate Newton-Schulz / renorm paths -- is held to a tight band against
+    autograd through the oracle run with the kernels' rounding model of the iteration."""
+    from oracle import lact_oracle as orc
+    B, L, D, H, mb = 2, 384, 64, 128, 128
+    inp = orc.make_inputs(B, L, D, H, seed=31)
+    for n in ("q", "k", "v"):
+        inp[n] = inp[n].to(BF16)
+    dO = torch.randn(B, L, D, generator=torch.Generator().manual_seed(6)).to(BF16)
+    kw = dict(mini_batch_size=mb, update_every=mb, use_moun=True, num_moun_iters=iters)
+    ref_fn = lambda w0, w1, w2, q, k, v, l0, l1, l2, m: orc.ar_mini_batch(
+        w0, w1, w2, q, k, v, l0, l1, l2, 1.0, ns=orc.newton_schulz_folded, **kw)[0]
+    cu_fn = lambda w0, w1, w2, q, k, v, l0, l1, l2, m: lb.ar_fast_weight_swish_glu_weight_norm_mini_batch(
+        w0, w1, w2, q, k, v, l0, l1, l2, 1.0, **kw)[0]
+    o_ref, g_ref = _grads_oracle(orc, inp, ref_fn, False, dO)
+    o, g = _grads_cuda(inp, cu_fn, False, dO)
+    assert orc.rel_max(o.float().cpu(), o_ref.float()) <= 3e-2
+    for n in NAMES:
+        a, b = g[n].float().cpu(), g_ref[n].float()
+        assert torch.isfinite(a).all(), n
+        rm, cs = orc.rel_max(a, b), orc.cosine(a, b)
+        assert cs >= 0.998 and rm <= 5e-2, f"grad {n} ({iters} iterations): rel_max={rm:.3e} cos={cs:.6f}"
+
+
 def test_compiled_caller_sees_one_operator(lb):
     """A caller wrapped in torch.compile (as the reference's layers are) traces through the public
     function without a graph break (fullgraph=True) and gets the eager results, forward and backward."""
