@@ -162,6 +162,16 @@ def test_prenorm_fused_signature_backward_runs_with_muon(lb):
         w0, w1, w2, q, k, v, l0, l1, l2, chunk_size=C, use_muon=False, momentum=m)
     _, g0 = _grads_cuda(inp, fn0, True, dO)
     assert torch.equal(g["q"][:, :C], g0["q"][:, :C])
+    # and against autograd through the oracle's pre-norm fused recurrence run with the kernels' rounding model of the
+    # iteration (three chunks, two updates: the un-normalised masters are rebuilt from the kept results)
+    ref_fn = lambda w0, w1, w2, q, k, v, l0, l1, l2, m: orc.block_causal_lact_swiglu_fused(
+        w0, w1, w2, q, k, v, l0, l1, l2, chunk_size=C, use_muon=True, momentum=m, prenorm=True,
+        ns=orc.newton_schulz_folded)
+    _, g_ref = _grads_oracle(orc, inp, ref_fn, True, dO)
+    for n in NAMES:
+        a, b = g[n].float().cpu(), g_ref[n].float()
+        assert orc.cosine(a, b) >= 0.99, (n, orc.cosine(a, b))
+        assert orc.rel_fro(a, b) <= 0.15, (n, orc.rel_fro(a, b))
 
 
 @pytest.mark.parametrize("muon", [False, True])
@@ -184,14 +194,11 @@ def test_bidirectional_backward(lb, muon):
     if not muon:
         _check(orc, g, g_ref, list(NAMES))
         return
-    for n in NAMES:  # one bf16 Newton-Schulz pass between inputs and output: loose band
-        a, b = g[n].float().cpu(), g_ref[n].float()
+    for n in NAMES:  # one bf16 Newton-Schulz pass (5 iterations) between inputs and output; measured: cosine
+        a, b = g[n].float().cpu(), g_ref[n].float()   # >= 0.9984, rel_fro <= 0.057 against the eager-rounding oracle
         assert torch.isfinite(a).all(), n
-        if n == "q":  # dq depends on the updated weights only through the forward values
-            assert orc.cosine(a, b) >= 0.995, (n, orc.cosine(a, b))
-        else:
-            assert orc.cosine(a, b) >= 0.95, (n, orc.cosine(a, b))
-            assert orc.rel_fro(a, b) <= 0.35, (n, orc.rel_fro(a, b))
+        assert orc.cosine(a, b) >= 0.995, (n, orc.cosine(a, b))
+        assert orc.rel_fro(a, b) <= 0.12, (n, orc.rel_fro(a, b))
 
 
 @pytest.mark.parametrize("shape,steps", [((3, 64, 64), None), ((2, 64, 128), 5), ((2, 128, 64), 3), ((2, 192, 192), None)])
@@ -273,11 +280,23 @@ def test_llm_backward_with_muon_first_chunks(lb):
         w0, w1, w2, q, k, v, l0, l1, l2, chunk_size=C, use_muon=True, momentum=m)
     o_ref, g_ref = _grads_oracle(orc, inp, ref_fn, True, dO)
     o, g = _grads_cuda(inp, cu_fn, True, dO)
-    for n in ("q", "k", "v", "w0", "w1", "w2", "lr0", "lr1", "lr2"):
+    for n in ("q", "k", "v", "w0", "w1", "w2", "lr0", "lr1", "lr2"):   # measured: cosine >= 0.9975, rel_fro <= 0.072
         a, b = g[n].float().cpu(), g_ref[n].float()
         assert torch.isfinite(a).all(), n
-        assert orc.cosine(a, b) >= 0.97, (n, orc.cosine(a, b))
-        assert orc.rel_fro(a, b) <= 0.25, (n, orc.rel_fro(a, b))
+        assert orc.cosine(a, b) >= 0.995, (n, orc.cosine(a, b))
+        assert orc.rel_fro(a, b) <= 0.14, (n, orc.rel_fro(a, b))
+    # the fused signature against the oracle with the kernels' own rounding model of the iteration: tighter
+    # (measured: cosine >= 0.9994, rel_fro <= 0.035)
+    ref_fn = lambda w0, w1, w2, q, k, v, l0, l1, l2, m: orc.block_causal_lact_swiglu_fused(
+        w0, w1, w2, q, k, v, l0, l1, l2, chunk_size=C, use_muon=True, momentum=m, ns=orc.newton_schulz_folded)
+    cu_fn = lambda w0, w1, w2, q, k, v, l0, l1, l2, m: lb.postnorm_block_causal_lact_swiglu_fused_kernel_triton(
+        w0, w1, w2, q, k, v, l0, l1, l2, chunk_size=C, use_muon=True, momentum=m)
+    o_ref, g_ref = _grads_oracle(orc, inp, ref_fn, True, dO)
+    o, g = _grads_cuda(inp, cu_fn, True, dO)
+    for n in ("q", "k", "v", "w0", "w1", "w2", "lr0", "lr1", "lr2"):
+        a, b = g[n].float().cpu(), g_ref[n].float()
+        assert orc.cosine(a, b) >= 0.998, (n, orc.cosine(a, b))
+        assert orc.rel_fro(a, b) <= 0.07, (n, orc.rel_fro(a, b))
 
 
 @pytest.mark.parametrize("iters", [1, 2])

@@ -275,3 +275,27 @@ def test_cfg3_backward_at_benchmark_head_shape(lb, orc):
     _, g = _grads_cuda(inp, cu_fn, True, dO)
     lb.synchronize_and_check()
     _check(orc, g, g_ref, list(NAMES) + ["momentum"])
+
+
+@pytest.mark.parametrize("B", [2, 12])   # 12 units: enough matrices for the wide / symmetric tile variants
+def test_cfg3_backward_with_muon_at_benchmark_head_shape(lb, orc, B):
+    """The same with Muon on (two chunks, one update: the kept Newton-Schulz iterates of the [768 x 384] and
+    [384 x 384] groups, the one-launch backward of the iteration with its symmetric phases, the renorm backward that
+    reads the kept result): against autograd through the oracle's fused recurrence run with the kernels' rounding
+    model of the iteration.  One update amplifies bf16 noise through five iterations: cosine >= 0.995."""
+    from test_gpu_backward import _grads_cuda, _grads_oracle
+    L, D, H, C = 4096, 384, 384, 2048
+    inp = bf(orc.make_inputs(B, L, D, H, seed=35))
+    dO = torch.randn(B, L, D, generator=torch.Generator().manual_seed(6)).to(BF16)
+    ref_fn = lambda w0, w1, w2, q, k, v, l0, l1, l2, m: orc.block_causal_lact_swiglu_fused(
+        w0, w1, w2, q, k, v, l0, l1, l2, chunk_size=C, use_muon=True, momentum=m, ns=orc.newton_schulz_folded)
+    cu_fn = lambda w0, w1, w2, q, k, v, l0, l1, l2, m: lb.postnorm_block_causal_lact_swiglu_fused_kernel_triton(
+        w0, w1, w2, q, k, v, l0, l1, l2, chunk_size=C, use_muon=True, momentum=m)
+    _, g_ref = _grads_oracle(orc, inp, ref_fn, True, dO)
+    _, g = _grads_cuda(inp, cu_fn, True, dO)
+    lb.synchronize_and_check()
+    for n in NAMES:
+        a, b = g[n].float().cpu(), g_ref[n].float()
+        assert torch.isfinite(a).all(), n
+        assert orc.cosine(a, b) >= 0.995, (n, orc.cosine(a, b))
+        assert orc.rel_fro(a, b) <= 0.12, (n, orc.rel_fro(a, b))
