@@ -326,6 +326,31 @@ def test_muon_backward_pins_every_weight_path(lb, iters):
         assert cs >= 0.998 and rm <= 5e-2, f"grad {n} ({iters} iterations): rel_max={rm:.3e} cos={cs:.6f}"
 
 
+def test_muon_and_momentum_backward_tight(lb):
+    """Three updates with momentum AND one Newton-Schulz iteration each (the AR driver with momentum): the momentum
+    chain's gradient (dbeta through the carried state, the share passed to the previous update) next to the iteration's
+    backward, every gradient including the momentum gate's against the oracle with the kernels' rounding model."""
+    from oracle import lact_oracle as orc
+    B, L, D, H, mb = 2, 512, 64, 128, 128
+    inp = orc.make_inputs(B, L, D, H, seed=37)
+    for n in ("q", "k", "v"):
+        inp[n] = inp[n].to(BF16)
+    dO = torch.randn(B, L, D, generator=torch.Generator().manual_seed(9)).to(BF16)
+    kw = dict(mini_batch_size=mb, update_every=mb, use_moun=True, num_moun_iters=1, use_momentum=True)
+    ref_fn = lambda w0, w1, w2, q, k, v, l0, l1, l2, m: orc.ar_mini_batch(
+        w0, w1, w2, q, k, v, l0, l1, l2, 1.0, fw_momentum=m, ns=orc.newton_schulz_folded, **kw)[0]
+    cu_fn = lambda w0, w1, w2, q, k, v, l0, l1, l2, m: lb.ar_fast_weight_swish_glu_weight_norm_mini_batch_with_momentum(
+        w0, w1, w2, q, k, v, l0, l1, l2, 1.0, fw_momentum=m, **kw)[0]
+    o_ref, g_ref = _grads_oracle(orc, inp, ref_fn, True, dO)
+    o, g = _grads_cuda(inp, cu_fn, True, dO)
+    assert orc.rel_max(o.float().cpu(), o_ref.float()) <= 3e-2
+    for n in list(NAMES) + ["momentum"]:
+        a, b = g[n].float().cpu(), g_ref[n].float()
+        assert torch.isfinite(a).all(), n
+        rm, cs = orc.rel_max(a, b), orc.cosine(a, b)
+        assert cs >= 0.995 and rm <= (0.12 if n == "momentum" else 6e-2), f"grad {n}: rel_max={rm:.3e} cos={cs:.6f}"
+
+
 def test_compiled_caller_sees_one_operator(lb):
     """A caller wrapped in torch.compile (as the reference's layers are) traces through the public
     function without a graph break (fullgraph=True) and gets the eager results, forward and backward."""
