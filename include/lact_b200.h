@@ -107,6 +107,9 @@ int64_t lact_launch_count(void);
  * for the recorded events, writes the summed milliseconds and launch counts of each class into
  * arrays of lact_profile_num_classes() entries, and clears the records. */
 int lact_profile_enable(int enable);
+/* While enabled, every kernel launch sits inside an NVTX range named after its kernel class (gemm_swiglu_gate,
+ * ns_fused, add_renorm, ...), for timeline tools.  Off by default.  No counterpart in the reference. */
+int lact_nvtx_enable(int enable);
 int lact_profile_num_classes(void);
 const char *lact_profile_class_name(int cls);
 int lact_profile_read(double *ms, int64_t *launches);

@@ -283,6 +283,11 @@ def stream_sync_count() -> int:
     return int(lib().lact_stream_sync_count())
 
 
+def nvtx_enable(on: bool = True) -> None:
+    """NVTX ranges around every kernel launch of the library (named after the kernel class) on / off."""
+    check(lib().lact_nvtx_enable(1 if on else 0), "lact_nvtx_enable")
+
+
 def launch_count() -> int:
     """Kernels launched by the library in this process so far."""
     return int(lib().lact_launch_count())

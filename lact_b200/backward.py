@@ -196,6 +196,10 @@ def ns_forward_saved(G, steps, const_coeffs, gram_right):
     nmat, R, Cc = G.shape
     if G.dtype not in (torch.float32, BF16):
         G = G.float()
+    if int(steps) == 0:   # no iteration (lact_nvs/lact_ttt.py with muon_update_steps = 0): the normalisation alone
+        from . import ops
+        U = ops.zeropower_via_newtonschulz5(G, 0)
+        return dict(trace=None, shape=(nmat, R, Cc), steps=0, cc=1, gr=int(bool(gram_right)), G=G), U
     need = C.c_size_t(0)
     L.check(L.lib().lact_ns_trace_bytes(nmat, R, Cc, int(steps), C.byref(need)), "lact_ns_trace_bytes")
     trace = torch.empty(need.value, dtype=torch.uint8, device=G.device)
@@ -217,10 +221,13 @@ def ns_backward(saved, dU):
     du = (dU if dU.dtype == BF16 else dU.to(BF16)).contiguous()
     dX0 = torch.empty(nmat, R, Cc, dtype=torch.float32, device=du.device)
     trace = saved["trace"]
+    if saved["steps"] == 0:
+        dX0.copy_(du)
     with torch.cuda.device(du.device):
-        L.check(L.lib().lact_ns_trace_bwd(du.data_ptr(), dX0.data_ptr(), nmat, R, Cc, saved["steps"], saved["cc"],
-                                          saved["gr"], trace.data_ptr(), trace.numel(),
-                                          _status_word(du.device).data_ptr(), L.stream_ptr()), "lact_ns_trace_bwd")
+        if saved["steps"] > 0:
+            L.check(L.lib().lact_ns_trace_bwd(du.data_ptr(), dX0.data_ptr(), nmat, R, Cc, saved["steps"], saved["cc"],
+                                              saved["gr"], trace.data_ptr(), trace.numel(),
+                                              _status_word(du.device).data_ptr(), L.stream_ptr()), "lact_ns_trace_bwd")
     # dX0 / den - bf16(G) <dX0, bf16(G)> / (den^2 ||bf16(G)||), in place in dX0
     G = saved["G"]
     G = G if (G.dtype == torch.float32 and G.is_contiguous()) else G.float().contiguous()
@@ -235,7 +242,7 @@ def ns_backward_groups(saved, dUs):
     launch (`lact_ns_trace_bwd_fused`) when an instantiation covers the shapes, else one group after the other."""
     same = all(sv["steps"] == saved[0]["steps"] and sv["cc"] == saved[0]["cc"] and sv["gr"] == saved[0]["gr"]
                for sv in saved)
-    if same and saved[0]["steps"] <= 5 and len(saved) <= 2:
+    if same and 1 <= saved[0]["steps"] <= 5 and len(saved) <= 2:
         dev = dUs[0].device
         slices = L.lib().lact_momentum_bwd_slices()
         groups = (L.NsBwdGroup * len(saved))()

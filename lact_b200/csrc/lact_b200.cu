@@ -3,6 +3,7 @@
 // include/lact_b200.h.  No device memory is allocated here: all scratch is carved out of the
 // caller's workspace.
 #include <cuda_runtime.h>
+#include <nvtx3/nvToolsExt.h>
 
 #include <algorithm>
 #include <atomic>
@@ -145,12 +146,19 @@ Profiler g_prof;
 std::atomic<int64_t> g_stream_syncs{0};  // cudaStreamSynchronize calls made by the library
 
 // Counts one kernel launch; when timing is enabled, brackets it with two events on its stream.
+std::atomic<bool> g_nvtx{false};  // NVTX range around every launch, named after its kernel class
+
 struct KernelScope {
   int cls;
   cudaStream_t stream;
   cudaEvent_t a = nullptr, b = nullptr;
+  bool range = false;
   KernelScope(int cls_, cudaStream_t s) : cls(cls_), stream(s) {
     g_prof.launches.fetch_add(1, std::memory_order_relaxed);
+    if (g_nvtx.load(std::memory_order_relaxed)) {
+      nvtxRangePushA(kClassNames[cls]);
+      range = true;
+    }
     if (g_prof.enabled.load(std::memory_order_relaxed)) {
       a = g_prof.get();
       b = g_prof.get();
@@ -163,6 +171,7 @@ struct KernelScope {
       std::lock_guard<std::mutex> lock(g_prof.mu);
       g_prof.recs.push_back({a, b, cls});
     }
+    if (range) nvtxRangePop();
   }
 };
 
@@ -936,7 +945,7 @@ int launch_swa(const SwaArgs& a, int64_t ctas, cudaStream_t stream) {
     }
   }
   KernelScope scope(kClsOther, stream);
-  kernel<<<static_cast<unsigned>(ctas), 192, smem, stream>>>(a);
+  kernel<<<static_cast<unsigned>(ctas), 320, smem, stream>>>(a);
   LACT_CUDA(cudaGetLastError());
   return LACT_OK;
 }
@@ -1290,6 +1299,11 @@ int64_t lact_launch_count(void) { return g_prof.launches.load(); }
 
 int lact_profile_enable(int enable) {
   g_prof.enabled.store(enable != 0);
+  return LACT_OK;
+}
+
+int lact_nvtx_enable(int enable) {
+  g_nvtx.store(enable != 0);
   return LACT_OK;
 }
 

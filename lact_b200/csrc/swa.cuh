@@ -3,11 +3,14 @@
 //   warp 0     TMA producer: the query tile once, then key and value tiles of 128 rows through two-stage rings;
 //   warp 1     MMA issuer:   S = Q K^T (128 x 128, fp32, tensor memory, double-buffered) and O_t = P V per key tile
 //                            (128 x d, tensor memory, double-buffered; NOT accumulated across tiles);
-//   warps 2-5  softmax:      one thread per query row (a row is a tensor-memory lane, so row max and row sum need no
-//                            shuffles): two passes over S (max, then exp2 / sum), the bf16 probabilities go to shared
-//                            memory in the swizzled K-major layout the second product reads as its A operand, and
-//                            the running output row lives in registers: O <- O * exp2(m_old - m_new) + O_t, folded
-//                            one tile behind so that the products of tile t + 1 overlap the softmax of tile t.
+//   warps 2-9  softmax:      two threads per query row (a row is a tensor-memory lane; the two warps that may read a
+//                            lane quarter split the row: 64 keys of S and half of the output features each, and
+//                            agree on the row maximum through shared memory): two passes over S (max, then
+//                            exp2 / sum), the bf16 probabilities go to shared memory in the swizzled K-major layout
+//                            the second product reads as its A operand, and the running output row lives in
+//                            registers: O <- O * exp2(m_old - m_new) + O_t, folded one tile behind so that the
+//                            products of tile t + 1 overlap the softmax of tile t.  Two warps per scheduler hide the
+//                            fixed latencies one warp alone sits out.
 // Key and value tiles share one shared-memory layout ([128 rows][64 features] boxes, 128-byte swizzle): the first
 // product reads it K-major (features = k), the second MN-major (keys = k).  Every wait is bounded.
 #pragma once
@@ -37,11 +40,11 @@ struct SwaSmem {
   static constexpr uint32_t kTile = 128 * HD * 2;          // one Q / K / V tile
   static constexpr uint32_t kPTile = 128 * 128 * 2;        // probabilities of one key tile
   static constexpr uint32_t kQ = 0, kK = kTile, kV = 3 * kTile, kP = 5 * kTile, kBars = 5 * kTile + 2 * kPTile;
-  static constexpr uint32_t kBytes = kBars + 256 + 1024;   // + barriers + alignment slack
+  static constexpr uint32_t kBytes = kBars + 256 + 1024 + 1024;   // + barriers + row-pair exchange + alignment slack
 };
 
 template <int HD>
-__global__ void __launch_bounds__(192, 1) swa_fwd_kernel(const __grid_constant__ SwaArgs a) {
+__global__ void __launch_bounds__(320, 1) swa_fwd_kernel(const __grid_constant__ SwaArgs a) {
   static_assert(HD == 64 || HD == 128, "head dimensions 64 and 128");
   using SM = SwaSmem<HD>;
   constexpr int KBD = HD / 64;                // 64-feature blocks of a tile
@@ -56,12 +59,15 @@ __global__ void __launch_bounds__(192, 1) swa_fwd_kernel(const __grid_constant__
   uint64_t* k_empty = bars + 3;       // [2]
   uint64_t* v_full = bars + 5;        // [2]
   uint64_t* s_full = bars + 7;        // [2]
-  uint64_t* s_empty = bars + 9;       // [2]  4 arrivals (one per softmax warp)
-  uint64_t* p_full = bars + 11;       // [2]  4 arrivals
+  uint64_t* s_empty = bars + 9;       // [2]  8 arrivals (one per softmax warp)
+  uint64_t* p_full = bars + 11;       // [2]  8 arrivals
   uint64_t* pv_done = bars + 13;      // [2]  frees the value stage and the probability buffer, publishes O_t
-  uint64_t* o_empty = bars + 15;      // [2]  4 arrivals
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+  uint64_t* o_empty = bars + 15;      // [2]  8 arrivals
+  uint64_t* x_written = bars + 17;    // [4]  per lane quarter: both warps of the quarter have written their value
+  uint64_t* x_read = bars + 21;       // [4]  ... and read the partner's
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 25);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  float* xch = reinterpret_cast<float*>(aligned + SM::kBars + 256);   // [2 halves][128 rows]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -71,10 +77,14 @@ __global__ void __launch_bounds__(192, 1) swa_fwd_kernel(const __grid_constant__
       mbar_init(&k_empty[s], 1);
       mbar_init(&v_full[s], 1);
       mbar_init(&s_full[s], 1);
-      mbar_init(&s_empty[s], 4);
-      mbar_init(&p_full[s], 4);
+      mbar_init(&s_empty[s], 8);
+      mbar_init(&p_full[s], 8);
       mbar_init(&pv_done[s], 1);
-      mbar_init(&o_empty[s], 4);
+      mbar_init(&o_empty[s], 8);
+    }
+    for (int qd = 0; qd < 4; ++qd) {
+      mbar_init(&x_written[qd], 2);
+      mbar_init(&x_read[qd], 2);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -160,40 +170,51 @@ __global__ void __launch_bounds__(192, 1) swa_fwd_kernel(const __grid_constant__
       }
     }
   } else {
-    // ---------------- softmax: thread = query row
+    // ---------------- softmax: two threads per query row (warps w and w + 4 share a tensor-memory lane quarter):
+    // thread `half` owns keys [64 half, 64 half + 64) of every S tile and output features [HD/2 half, HD/2 (half + 1))
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;
     const int qi = q0 + r;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    constexpr int OC = HD / 2;   // output features per thread
     float m = -INFINITY, l = 0.f, a_prev = 1.f;
-    float O[HD];
+    float O[OC];
 #pragma unroll
-    for (int j = 0; j < HD; ++j) O[j] = 0.f;
-    auto fold = [&](int u, float alpha) -> bool {   // O <- O * alpha + O_u
+    for (int j = 0; j < OC; ++j) O[j] = 0.f;
+    uint32_t xphase = 0;   // exchanges done so far (two barrier phases each)
+    // the two threads of a row agree on a value through shared memory (bounded mbarrier waits, no bar.sync: a thread
+    // that gave up must not leave its partner waiting for ever)
+    auto exchange = [&](float mine, float& other) -> bool {
+      xch[half * 128 + r] = mine;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&x_written[quarter]);
+      if (!mbar_wait(&x_written[quarter], xphase & 1, abort_flag)) return false;
+      other = xch[(half ^ 1) * 128 + r];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&x_read[quarter]);
+      if (!mbar_wait(&x_read[quarter], xphase & 1, abort_flag)) return false;
+      ++xphase;
+      return true;
+    };
+    auto fold = [&](int u, float alpha) -> bool {   // O <- O * alpha + O_u (this thread's features)
       const int ob = u & 1;
       if (!mbar_wait(&pv_done[ob], (u >> 1) & 1, abort_flag)) return false;
       tc_fence_after();
-      const uint32_t o_addr = tmem + lane_off + 256 + ob * HD;
-      uint32_t ba[32], bb[32];
-      tmem_ld32(o_addr, ba);
+      const uint32_t o_addr = tmem + lane_off + 256 + ob * HD + half * OC;
+      uint32_t ba[32];
 #pragma unroll
-      for (int c = 0; c < HD; c += 64) {
+      for (int c = 0; c < OC; c += 32) {
+        tmem_ld32(o_addr + c, ba);
         tmem_ld_wait();
-        tmem_ld32(o_addr + c + 32, bb);
 #pragma unroll
         for (int j = 0; j < 32; ++j) O[c + j] = fmaf(O[c + j], alpha, __uint_as_float(ba[j]));
-        tmem_ld_wait();
-        if (c + 64 < HD) tmem_ld32(o_addr + c + 64, ba);
-#pragma unroll
-        for (int j = 0; j < 32; ++j) O[c + 32 + j] = fmaf(O[c + 32 + j], alpha, __uint_as_float(bb[j]));
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&o_empty[ob]);
       return true;
     };
-    // Tensor-memory loads are asynchronous: chunk c + 1 is requested before chunk c is processed (two register
-    // buffers), so that the single softmax warp of each scheduler does not sit out every load's latency.
     for (int t = 0; t < T && !failed; ++t) {
       const int sb = t & 1;
       const int kv0 = kv_lo + t * 128;
@@ -201,9 +222,10 @@ __global__ void __launch_bounds__(192, 1) swa_fwd_kernel(const __grid_constant__
       tc_fence_after();
       // every (row, key) pair of the tile inside the band and the sequence: no masks
       const bool interior = kv0 + 127 <= q0 && kv0 >= q0 + 127 - (window - 1) && kv0 + 127 < a.L;
+      const int c0 = half * 64;                                // this thread's first key column of the tile
       const int j_hi = (qi < a.L - 1 ? qi : a.L - 1) - kv0;   // last / first column of the tile this row may see
       const int j_lo = qi - (window - 1) - kv0;
-      const uint32_t s_addr = tmem + lane_off + sb * 128;
+      const uint32_t s_addr = tmem + lane_off + sb * 128 + c0;
       uint32_t ba[32], bb[32];
       float mx = -INFINITY;
       auto max_chunk = [&](const uint32_t (&bits)[32], int c) {
@@ -216,24 +238,22 @@ __global__ void __launch_bounds__(192, 1) swa_fwd_kernel(const __grid_constant__
             if (c + j >= j_lo && c + j <= j_hi) mx = fmaxf(mx, __uint_as_float(bits[j]));
         }
       };
+      // chunk c + 1 is requested before chunk c is processed (tensor-memory loads are asynchronous)
       tmem_ld32(s_addr, ba);
       tmem_ld_wait();
       tmem_ld32(s_addr + 32, bb);
-      max_chunk(ba, 0);
-      tmem_ld_wait();
-      tmem_ld32(s_addr + 64, ba);
-      max_chunk(bb, 32);
-      tmem_ld_wait();
-      tmem_ld32(s_addr + 96, bb);
-      max_chunk(ba, 64);
+      max_chunk(ba, c0);
       tmem_ld_wait();
       tmem_ld32(s_addr, ba);   // first chunk of the second pass
-      max_chunk(bb, 96);
+      max_chunk(bb, c0 + 32);
+      float mx_other;
+      if (!exchange(mx, mx_other)) { failed = true; break; }
+      mx = fmaxf(mx, mx_other);
       const float m_new = fmaxf(m, mx * a.scale_log2);
       const float alpha = m_new == -INFINITY ? 1.f : fast_exp2(m - m_new);
       const float shift = m_new == -INFINITY ? 0.f : m_new;
       float sum = 0.f;
-      const uint32_t p_row = base + SM::kP + sb * SM::kPTile + r * 128;
+      const uint32_t p_row = base + SM::kP + sb * SM::kPTile + half * kBox + r * 128;   // this thread's 64-key panel
       auto exp_chunk = [&](const uint32_t (&bits)[32], int c) {
         float p[32];
         if (interior) {
@@ -246,11 +266,10 @@ __global__ void __launch_bounds__(192, 1) swa_fwd_kernel(const __grid_constant__
         }
 #pragma unroll
         for (int j = 0; j < 32; ++j) sum += p[j];
-        const uint32_t panel = p_row + (c >> 6) * kBox;
         const uint32_t unit0 = (c & 63) >> 3;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-          const uint32_t addr = panel + (((unit0 + g) ^ (r & 7)) << 4);
+          const uint32_t addr = p_row + (((unit0 + g) ^ (r & 7)) << 4);
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pack_bf16x2(p[g * 8 + 0], p[g * 8 + 1])),
                        "r"(pack_bf16x2(p[g * 8 + 2], p[g * 8 + 3])), "r"(pack_bf16x2(p[g * 8 + 4], p[g * 8 + 5])),
                        "r"(pack_bf16x2(p[g * 8 + 6], p[g * 8 + 7]))
@@ -259,15 +278,9 @@ __global__ void __launch_bounds__(192, 1) swa_fwd_kernel(const __grid_constant__
       };
       tmem_ld_wait();
       tmem_ld32(s_addr + 32, bb);
-      exp_chunk(ba, 0);
+      exp_chunk(ba, c0);
       tmem_ld_wait();
-      tmem_ld32(s_addr + 64, ba);
-      exp_chunk(bb, 32);
-      tmem_ld_wait();
-      tmem_ld32(s_addr + 96, bb);
-      exp_chunk(ba, 64);
-      tmem_ld_wait();
-      exp_chunk(bb, 96);
+      exp_chunk(bb, c0 + 32);
       // S has been read twice and is free; the probabilities are visible to the tensor core
       tc_fence_before();
       fence_async_proxy();
@@ -276,17 +289,20 @@ __global__ void __launch_bounds__(192, 1) swa_fwd_kernel(const __grid_constant__
         mbar_arrive(&s_empty[sb]);
         mbar_arrive(&p_full[sb]);
       }
-      l = l * alpha + sum;
+      l = l * alpha + sum;   // this thread's share of the row sum (both shares see the same alphas)
       m = m_new;
       if (t >= 1 && !fold(t - 1, a_prev)) { failed = true; break; }
       a_prev = alpha;
     }
     if (!failed && T > 0 && !fold(T - 1, a_prev)) failed = true;
+    float l_other = 0.f;
+    if (!failed && !exchange(l, l_other)) failed = true;
     if (!failed && qi < a.L) {
-      const float inv = l > 0.f ? 1.0f / l : 0.f;
-      bf16* dst = a.o + batch * a.o_bs + static_cast<int64_t>(qi) * a.o_ts + head * a.o_hs;
+      const float tot = l + l_other;
+      const float inv = tot > 0.f ? 1.0f / tot : 0.f;
+      bf16* dst = a.o + batch * a.o_bs + static_cast<int64_t>(qi) * a.o_ts + head * a.o_hs + half * OC;
 #pragma unroll
-      for (int c = 0; c < HD; c += 8) {
+      for (int c = 0; c < OC; c += 8) {
         uint4 u;
         u.x = pack_bf16x2(O[c] * inv, O[c + 1] * inv);
         u.y = pack_bf16x2(O[c + 2] * inv, O[c + 3] * inv);

@@ -351,6 +351,34 @@ def test_muon_and_momentum_backward_tight(lb):
         assert cs >= 0.995 and rm <= (0.12 if n == "momentum" else 6e-2), f"grad {n}: rel_max={rm:.3e} cos={cs:.6f}"
 
 
+@pytest.mark.parametrize("steps", [0, 2])
+def test_nvs_operator_list_backward(lb, steps):
+    """The NVS driver (transposed weight layout, Gram matrix on the other side for square matrices, constant
+    coefficients, target norms detached, one update on the input tokens and one apply on all tokens): gradients against
+    autograd through the oracle's restatement of lact_nvs/lact_ttt.py:70-147.  `steps = 0` still divides the gradient
+    by its Frobenius norm (the normalisation backward alone); two iterations add the iteration's backward."""
+    from oracle import lact_oracle as orc
+    B, L, D, H = 2, 384, 64, 64
+    inp = orc.make_inputs(B, L, D, H, seed=41)
+    for n in ("q", "k", "v"):
+        inp[n] = inp[n].to(BF16)
+    dO = torch.randn(B, L, D, generator=torch.Generator().manual_seed(3)).to(BF16)
+    order = [(0, 256, True, False), (0, 384, False, True)]
+    t = lambda w: w.transpose(1, 2)
+    ref_fn = lambda w0, w1, w2, q, k, v, l0, l1, l2, m: orc.nvs_mini_batch_apply(
+        t(w0), t(w1), t(w2), q, k, v, l0, l1, l2, order, muon_update_steps=steps)[0]
+    cu_fn = lambda w0, w1, w2, q, k, v, l0, l1, l2, m: lb.fast_weight_swish_glu_weight_norm_mini_batch_apply(
+        t(w0), t(w1), t(w2), q, k, v, l0, l1, l2, [lb.TTTOperator(*op) for op in order], muon_update_steps=steps)[0]
+    o_ref, g_ref = _grads_oracle(orc, inp, ref_fn, False, dO)
+    o, g = _grads_cuda(inp, cu_fn, False, dO)
+    assert orc.rel_max(o.float().cpu(), o_ref.float()) <= 3e-2
+    for n in NAMES:
+        a, b = g[n].float().cpu(), g_ref[n].float()
+        assert torch.isfinite(a).all(), n
+        rm, cs = orc.rel_max(a, b), orc.cosine(a, b)
+        assert cs >= 0.997 and rm <= 6e-2, f"grad {n} ({steps} iterations): rel_max={rm:.3e} cos={cs:.6f}"
+
+
 def test_compiled_caller_sees_one_operator(lb):
     """A caller wrapped in torch.compile (as the reference's layers are) traces through the public
     function without a graph break (fullgraph=True) and gets the eager results, forward and backward."""
