@@ -261,6 +261,25 @@ int lact_swa_fwd(const void *q, const void *k, const void *v, void *o, int64_t b
                  int64_t q_ts, int64_t q_bs, int64_t k_ts, int64_t k_bs, int64_t v_ts, int64_t v_bs, int64_t o_ts,
                  int64_t o_bs, int64_t window, float softmax_scale, int32_t *status_word, void *stream);
 
+/* Backward of lact_qkv_prologue / lact_qkv_prologue_rope on the saved projections (same strides): dq, dk, dv are the
+ * gradients of the head-major outputs ([(b n_heads), s, d] bf16, NULL = none), dxq, dxk, dxv the gradients of the
+ * projections ([b, s, n_heads * d] bf16, contiguous, written).  The forward's bf16 roundings are treated as identities.
+ * rope_head_dim = 0: no rotation.  Autograd of layer_lact_swiglu.py:399-446. */
+int lact_qkv_prologue_bwd(const void *xq, const void *xk, const void *xv, int64_t ld_q, int64_t ld_k, int64_t ld_v,
+                          int64_t bs_q, int64_t bs_k, int64_t bs_v, const void *dq, const void *dk, const void *dv,
+                          void *dxq, void *dxk, void *dxv, int64_t b, int64_t s, int64_t n_heads, int64_t d,
+                          int32_t qkv_silu, int32_t v_silu, const void *cos, const void *sin, int64_t rope_head_dim,
+                          int64_t n_positions, int64_t seqlen_offset, void *stream);
+
+/* Backward of lact_out_epilogue: dx [(b n_heads), s, d] and dgate [b, s, n_heads * d] (bf16, written; dgate NULL iff
+ * gate_proj NULL), and per-block partial sums of the norm weight's gradient, dw_partial [lact_out_epilogue_bwd_blocks()][d]
+ * fp32 (the caller adds the rows; fixed order, deterministic).  The gradient of the residual input is dout itself.
+ * Autograd of layer_lact_swiglu.py:556-568. */
+int lact_out_epilogue_bwd_blocks(void);
+int lact_out_epilogue_bwd(const void *fw_x, const void *weight, const void *gate_proj, int64_t gate_ld, const void *dout,
+                          int64_t dout_ld, void *dx, void *dgate, void *dw_partial, int64_t b, int64_t s, int64_t n_heads,
+                          int64_t d, float eps, void *stream);
+
 /* Output side of the LLM layer in one pass (layer_lact_swiglu.py:556-568): per-head RMSNorm of the recurrence's
  * output (fp32 arithmetic x * rsqrt(mean(x^2) + eps) * weight, rounded to bf16: the arithmetic of the
  * fla.modules.RMSNorm kernel the reference calls), times bf16(silu(gate_proj)), heads merged back, plus `resid`.

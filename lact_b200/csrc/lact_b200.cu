@@ -1701,6 +1701,114 @@ static int qkv_prologue_impl(const void* xq, const void* xk, const void* xv, int
   return LACT_OK;
 }
 
+int lact_qkv_prologue_bwd(const void* xq, const void* xk, const void* xv, int64_t ld_q, int64_t ld_k, int64_t ld_v,
+                          int64_t bs_q, int64_t bs_k, int64_t bs_v, const void* dq, const void* dk, const void* dv,
+                          void* dxq, void* dxk, void* dxv, int64_t b, int64_t s, int64_t n_heads, int64_t d,
+                          int32_t qkv_silu, int32_t v_silu, const void* cos, const void* sin, int64_t rope_head_dim,
+                          int64_t n_positions, int64_t seqlen_offset, void* stream) {
+  if (!xq || !xk || !xv || !dxq || !dxk || !dxv) return LACT_ERR_NULL;
+  LACT_TRY(check_device());
+  if (b < 1 || s < 1 || n_heads < 1 || d < 8 || d > 1024 || (d % 8) != 0) return LACT_ERR_SHAPE;
+  if (b * s * n_heads > (1ll << 40) || b > 65535 || s > (1ll << 30)) return LACT_ERR_SHAPE;
+  const void* xs[3] = {xq, xk, xv};
+  const void* dzs[3] = {dq, dk, dv};
+  void* outs[3] = {dxq, dxk, dxv};
+  const int64_t lds[3] = {ld_q, ld_k, ld_v}, bss[3] = {bs_q, bs_k, bs_v};
+  PrologueBwdArgs a;
+  std::memset(&a, 0, sizeof(a));
+  for (int t = 0; t < 3; ++t) {
+    if ((reinterpret_cast<uintptr_t>(xs[t]) & 15) != 0 || (reinterpret_cast<uintptr_t>(outs[t]) & 15) != 0 ||
+        (reinterpret_cast<uintptr_t>(dzs[t]) & 15) != 0 || lds[t] < n_heads * d || (lds[t] % 8) != 0 || (bss[t] % 8) != 0)
+      return LACT_ERR_SHAPE;
+    a.x[t] = static_cast<const bf16*>(xs[t]);
+    a.dz[t] = static_cast<const bf16*>(dzs[t]);
+    a.dx[t] = static_cast<bf16*>(outs[t]);
+    a.ld[t] = lds[t];
+    a.bs[t] = bss[t];
+  }
+  a.b = static_cast<int32_t>(b); a.s = static_cast<int32_t>(s);
+  a.n_h = static_cast<int32_t>(n_heads); a.d = static_cast<int32_t>(d);
+  a.silu[0] = a.silu[1] = qkv_silu ? 1 : 0;
+  a.silu[2] = (qkv_silu && v_silu) ? 1 : 0;
+  a.l2norm[0] = a.l2norm[1] = 1;
+  a.l2norm[2] = 0;
+  if (rope_head_dim != 0) {
+    if (!cos || !sin) return LACT_ERR_NULL;
+    if (rope_head_dim < 32 || rope_head_dim > 1024 || (rope_head_dim & (rope_head_dim - 1)) != 0 ||
+        (d % rope_head_dim) != 0 || seqlen_offset < 0 || seqlen_offset + s > n_positions)
+      return LACT_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(cos) & 15) != 0 || (reinterpret_cast<uintptr_t>(sin) & 15) != 0) return LACT_ERR_SHAPE;
+    a.cos = static_cast<const bf16*>(cos);
+    a.sin = static_cast<const bf16*>(sin);
+    a.rope_hd = static_cast<int32_t>(rope_head_dim);
+    a.pos0 = static_cast<int32_t>(seqlen_offset);
+  }
+  const int64_t rows = b * s * n_heads;
+  KernelScope scope(kClsOther, static_cast<cudaStream_t>(stream));
+  const unsigned grid = static_cast<unsigned>(ceil_div(rows, 8));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (a.rope_hd != 0) {
+    switch (ceil_div(d, 256)) {
+      case 1: qkv_prologue_bwd_kernel<1, true><<<grid, 256, 0, st>>>(a); break;
+      case 2: qkv_prologue_bwd_kernel<2, true><<<grid, 256, 0, st>>>(a); break;
+      case 3: qkv_prologue_bwd_kernel<3, true><<<grid, 256, 0, st>>>(a); break;
+      default: qkv_prologue_bwd_kernel<4, true><<<grid, 256, 0, st>>>(a); break;
+    }
+  } else {
+    switch (ceil_div(d, 256)) {
+      case 1: qkv_prologue_bwd_kernel<1, false><<<grid, 256, 0, st>>>(a); break;
+      case 2: qkv_prologue_bwd_kernel<2, false><<<grid, 256, 0, st>>>(a); break;
+      case 3: qkv_prologue_bwd_kernel<3, false><<<grid, 256, 0, st>>>(a); break;
+      default: qkv_prologue_bwd_kernel<4, false><<<grid, 256, 0, st>>>(a); break;
+    }
+  }
+  LACT_CUDA(cudaGetLastError());
+  return LACT_OK;
+}
+
+int lact_out_epilogue_bwd_blocks(void) { return sm_count() * 4; }
+
+int lact_out_epilogue_bwd(const void* fw_x, const void* weight, const void* gate_proj, int64_t gate_ld, const void* dout,
+                          int64_t dout_ld, void* dx, void* dgate, void* dw_partial, int64_t b, int64_t s, int64_t n_heads,
+                          int64_t d, float eps, void* stream) {
+  if (!fw_x || !weight || !dout || !dx || !dw_partial) return LACT_ERR_NULL;
+  if ((gate_proj == nullptr) != (dgate == nullptr)) return LACT_ERR_NULL;
+  LACT_TRY(check_device());
+  if (b < 1 || s < 1 || n_heads < 1 || d < 8 || d > 1024 || (d % 8) != 0 || b > 65535 || s > (1ll << 30))
+    return LACT_ERR_SHAPE;
+  auto bad = [&](const void* p, int64_t ld) {
+    return p != nullptr && ((reinterpret_cast<uintptr_t>(p) & 15) != 0 || ld < n_heads * d || (ld % 8) != 0);
+  };
+  if ((reinterpret_cast<uintptr_t>(fw_x) & 15) != 0 || (reinterpret_cast<uintptr_t>(weight) & 15) != 0 ||
+      (reinterpret_cast<uintptr_t>(dx) & 15) != 0 || (reinterpret_cast<uintptr_t>(dgate) & 15) != 0 ||
+      bad(gate_proj, gate_ld) || bad(dout, dout_ld))
+    return LACT_ERR_SHAPE;
+  EpilogueBwdArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.x = static_cast<const bf16*>(fw_x);
+  a.weight = static_cast<const float*>(weight);
+  a.gate = static_cast<const bf16*>(gate_proj);
+  a.dout = static_cast<const bf16*>(dout);
+  a.gate_ld = gate_ld; a.dout_ld = dout_ld;
+  a.dx = static_cast<bf16*>(dx);
+  a.dgate = static_cast<bf16*>(dgate);
+  a.dw_partial = static_cast<float*>(dw_partial);
+  a.b = static_cast<int32_t>(b); a.s = static_cast<int32_t>(s);
+  a.n_h = static_cast<int32_t>(n_heads); a.d = static_cast<int32_t>(d);
+  a.eps = eps;
+  KernelScope scope(kClsOther, static_cast<cudaStream_t>(stream));
+  const unsigned grid = static_cast<unsigned>(lact_out_epilogue_bwd_blocks());
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (ceil_div(d, 256)) {
+    case 1: out_epilogue_bwd_kernel<1><<<grid, 256, 0, st>>>(a); break;
+    case 2: out_epilogue_bwd_kernel<2><<<grid, 256, 0, st>>>(a); break;
+    case 3: out_epilogue_bwd_kernel<3><<<grid, 256, 0, st>>>(a); break;
+    default: out_epilogue_bwd_kernel<4><<<grid, 256, 0, st>>>(a); break;
+  }
+  LACT_CUDA(cudaGetLastError());
+  return LACT_OK;
+}
+
 int lact_qkv_prologue(const void* xq, const void* xk, const void* xv, int64_t ld_q, int64_t ld_k, int64_t ld_v,
                       int64_t bs_q, int64_t bs_k, int64_t bs_v, void* q, void* k, void* v, int64_t b, int64_t s,
                       int64_t n_heads, int64_t d, int32_t qkv_silu, int32_t v_silu, void* stream) {

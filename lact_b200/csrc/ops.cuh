@@ -1395,4 +1395,216 @@ __global__ void __launch_bounds__(256, NCH <= 2 ? 8 : 4) out_epilogue_kernel(con
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// backward of the layer passes (roundings of the forward treated as identities, fp32 arithmetic on the saved inputs)
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ float silu_grad(float x) {
+  const float sg = sigmoidf_fast(x);
+  return sg * (1.f + x * (1.f - sg));
+}
+
+// Backward of qkv_prologue_kernel: one warp per (batch, token, head) and tensor.  Given dz (gradient of the head-major
+// output) it undoes the rotation (dy = R^T dz), the per-head l2 norm (y = u / (||u|| + 1e-5)) and the SiLU, and writes
+// dx [b][s][n_h * d] (contiguous).
+struct PrologueBwdArgs {
+  const bf16* x[3];      // saved projections, strides as in the forward
+  int64_t ld[3], bs[3];
+  const bf16* dz[3];     // [(b n_h)][s][d] contiguous, or nullptr (no gradient for that tensor: zeros are written)
+  bf16* dx[3];           // [b][s][n_h * d] contiguous
+  int32_t b, s, n_h, d;
+  int32_t silu[3], l2norm[3];
+  const bf16 *cos, *sin;
+  int32_t rope_hd, pos0;
+};
+template <int NCH, bool ROPE>
+__global__ void __launch_bounds__(256, (ROPE || NCH > 1) ? 2 : 4) qkv_prologue_bwd_kernel(const PrologueBwdArgs a) {
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t rows = static_cast<int64_t>(a.b) * a.s * a.n_h;
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const int h = static_cast<int>(row % a.n_h);
+  const int64_t bs_idx = row / a.n_h;
+  const int tok = static_cast<int>(bs_idx % a.s), bi = static_cast<int>(bs_idx / a.s);
+  const int64_t z_off = ((static_cast<int64_t>(bi) * a.n_h + h) * a.s + tok) * a.d;
+  const int64_t x_out = bs_idx * (static_cast<int64_t>(a.n_h) * a.d) + static_cast<int64_t>(h) * a.d;
+#pragma unroll
+  for (int t = 0; t < 3; ++t) {
+    const bf16* src = a.x[t] + bi * a.bs[t] + tok * a.ld[t] + static_cast<int64_t>(h) * a.d;
+    float xv[NCH][8], u[NCH][8], g[NCH][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int col = (c * 32 + lane) * 8;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { xv[c][i] = 0.f; u[c][i] = 0.f; g[c][i] = 0.f; }
+      if (col < a.d) {
+        load8_bf16(src + col, xv[c]);
+        if (a.dz[t] != nullptr) load8_bf16(a.dz[t] + z_off + col, g[c]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          u[c][i] = a.silu[t] ? bf16_round(__fdividef(xv[c][i], 1.f + __expf(-xv[c][i]))) : xv[c][i];
+          ss += u[c][i] * u[c][i];
+        }
+      }
+    }
+    if (ROPE && t < 2) {
+      // dy = R^T dz: first half dz cos + partner sin, second half dz cos - partner sin (partner as in the forward)
+      const int half = a.rope_hd >> 1;
+      const int64_t trow = static_cast<int64_t>(a.pos0 + tok) * half;
+      float other[NCH][8];
+#pragma unroll
+      for (int c = 0; c < NCH; ++c)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          if (half < 256) other[c][i] = __shfl_xor_sync(0xFFFFFFFFu, g[c][i], half >> 3);
+          else other[c][i] = g[(c ^ (half >> 8)) < NCH ? (c ^ (half >> 8)) : c][i];
+        }
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        const int col = (c * 32 + lane) * 8;
+        if (col < a.d) {
+          const int j = (static_cast<int>(h) * a.d + col) % a.rope_hd;
+          const bool first = j < half;
+          float cs[8], sn[8];
+          load8_bf16(a.cos + trow + (first ? j : j - half), cs);
+          load8_bf16(a.sin + trow + (first ? j : j - half), sn);
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            g[c][i] = first ? g[c][i] * cs[i] + other[c][i] * sn[i] : g[c][i] * cs[i] - other[c][i] * sn[i];
+        }
+      }
+    }
+    if (a.l2norm[t]) {
+      float dot = 0.f;
+#pragma unroll
+      for (int c = 0; c < NCH; ++c)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) dot += g[c][i] * u[c][i];
+      ss = warp_sum(ss);
+      dot = warp_sum(dot);
+      const float nrm = sqrtf(ss), den = nrm + 1e-5f;
+      const float inv = 1.f / den, coef = dot / (den * den * fmaxf(nrm, 1e-30f));
+#pragma unroll
+      for (int c = 0; c < NCH; ++c)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) g[c][i] = g[c][i] * inv - u[c][i] * coef;
+    }
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int col = (c * 32 + lane) * 8;
+      if (col < a.d) {
+        if (a.silu[t]) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) g[c][i] *= silu_grad(xv[c][i]);
+        }
+        store8_bf16(a.dx[t] + x_out + col, g[c]);
+      }
+    }
+  }
+}
+
+// Backward of out_epilogue_kernel.  Persistent grid: warp w of the grid walks rows w, w + W, ... (a fixed order), writes
+// dx and dgate per row and keeps its share of the norm weight's gradient in registers; the block's eight shares are
+// added in shared memory and stored as one partial row [gridDim.x][d] (the caller adds the partials: deterministic).
+struct EpilogueBwdArgs {
+  const bf16* x;        // [(b n_h)][s][d]
+  const float* weight;  // [d]
+  const bf16* gate;     // [b][s][n_h * d] or nullptr
+  const bf16* dout;     // [b][s][n_h * d]
+  int64_t gate_ld, dout_ld;
+  bf16* dx;             // [(b n_h)][s][d]
+  bf16* dgate;          // [b][s][n_h * d] contiguous, or nullptr
+  float* dw_partial;    // [gridDim.x][d]
+  int32_t b, s, n_h, d;
+  float eps;
+};
+template <int NCH>
+__global__ void __launch_bounds__(256, 2) out_epilogue_bwd_kernel(const EpilogueBwdArgs a) {
+  __shared__ float red[8][32 * 8 + 1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t rows = static_cast<int64_t>(a.b) * a.s * a.n_h;
+  const int64_t nwarps = static_cast<int64_t>(gridDim.x) * 8;
+  float dw[NCH][8];
+  float w[NCH][8];
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int col = (c * 32 + lane) * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { dw[c][j] = 0.f; w[c][j] = col + j < a.d ? a.weight[col + j] : 0.f; }
+  }
+  for (int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + warp; row < rows; row += nwarps) {
+    const int h = static_cast<int>(row % a.n_h);
+    const int64_t bs_idx = row / a.n_h;
+    const int tok = static_cast<int>(bs_idx % a.s), bi = static_cast<int>(bs_idx / a.s);
+    const int64_t x_off = ((static_cast<int64_t>(bi) * a.n_h + h) * a.s + tok) * a.d;
+    const int64_t off = static_cast<int64_t>(h) * a.d;
+    float v[NCH][8], dn[NCH][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int col = (c * 32 + lane) * 8;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { v[c][j] = 0.f; dn[c][j] = 0.f; }
+      if (col < a.d) {
+        load8_bf16(a.x + x_off + col, v[c]);
+        load8_bf16(a.dout + bs_idx * a.dout_ld + off + col, dn[c]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += v[c][j] * v[c][j];
+      }
+    }
+    ss = warp_sum(ss);
+    const float rstd = 1.f / sqrtf(ss / static_cast<float>(a.d) + a.eps);
+    float dot = 0.f;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int col = (c * 32 + lane) * 8;
+      if (col >= a.d) continue;
+      if (a.gate != nullptr) {
+        float gt[8], dg[8];
+        load8_bf16(a.gate + bs_idx * a.gate_ld + off + col, gt);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float n = v[c][j] * rstd * w[c][j];
+          dg[j] = dn[c][j] * n * silu_grad(gt[j]);
+          dn[c][j] *= __fdividef(gt[j], 1.f + __expf(-gt[j]));
+        }
+        if (a.dgate != nullptr) store8_bf16(a.dgate + bs_idx * (static_cast<int64_t>(a.n_h) * a.d) + off + col, dg);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        dw[c][j] += dn[c][j] * v[c][j] * rstd;
+        dot += dn[c][j] * w[c][j] * v[c][j];
+      }
+    }
+    dot = warp_sum(dot);
+    const float k3 = rstd * rstd * rstd * dot / static_cast<float>(a.d);
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int col = (c * 32 + lane) * 8;
+      if (col >= a.d) continue;
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = rstd * w[c][j] * dn[c][j] - v[c][j] * k3;
+      store8_bf16(a.dx + x_off + col, o);
+    }
+  }
+  // block partial of the weight gradient: warp shares added in a fixed order
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 8; ++j) red[warp][lane * 8 + j] = dw[c][j];
+    __syncthreads();
+    if (warp == 0) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int col = (c * 32 + lane) * 8 + j;
+        float tot = 0.f;
+        for (int ww = 0; ww < 8; ++ww) tot += red[ww][lane * 8 + j];
+        if (col < a.d) a.dw_partial[static_cast<int64_t>(blockIdx.x) * a.d + col] = tot;
+      }
+    }
+  }
+}
+
 }  // namespace lact

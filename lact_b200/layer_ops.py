@@ -2,9 +2,10 @@
 lact_llm/lact_model/layer_lact_swiglu.py, is outside this package; these are the passes over
 [b, s, n_h * d] that sit directly on the recurrence's inputs and output).
 
-Forward: one fused CUDA pass each.  Backward (training): each pass is an autograd Function whose backward
-re-evaluates the same formula with plain PyTorch operations in fp32 on the saved inputs and differentiates that
-(several elementwise passes instead of one; the forward values the rest of the graph sees are the fused kernel's)."""
+Forward: one fused CUDA pass each.  Backward (training): each pass is an autograd Function; the two passes over
+[b, s, n_h * d] (`qkv_prologue`, `out_epilogue`) have fused backward kernels that recompute from the saved inputs
+(the forward's bf16 roundings are treated as identities); the small learning-rate pass differentiates a plain
+PyTorch restatement."""
 from __future__ import annotations
 
 import math
@@ -28,31 +29,9 @@ def _unheads(t: torch.Tensor, n_h: int) -> torch.Tensor:
     return t.reshape(B // n_h, n_h, s, d).permute(0, 2, 1, 3).reshape(B // n_h, s, n_h * d)
 
 
-def _eager_qkv(xq, xk, xv, n_h, qkv_silu, v_silu, rope):
-    """fp32 restatement of the pass (layer_lact_swiglu.py:399-446), differentiable."""
-    def one(x, silu, norm, rot):
-        y = _heads(x.float(), n_h)
-        if silu:
-            y = F.silu(y)
-        if norm:
-            y = y / (y.norm(dim=-1, keepdim=True) + 1e-5)
-        if rot and rope is not None:
-            cos, sin, hd, off = rope
-            s = y.shape[1]
-            m = _unheads(y, n_h)
-            b, _, nd = m.shape
-            m = m.reshape(b, s, nd // hd, hd)
-            c = cos[off:off + s].float()[:, None, :]
-            sn = sin[off:off + s].float()[:, None, :]
-            x1, x2 = m[..., :hd // 2], m[..., hd // 2:]
-            m = torch.cat([x1 * c - x2 * sn, x1 * sn + x2 * c], dim=-1).reshape(b, s, nd)
-            y = _heads(m, n_h)
-        return y
-    return one(xq, qkv_silu, True, True), one(xk, qkv_silu, True, True), one(xv, qkv_silu and v_silu, False, False)
-
-
 class _QkvPrologue(torch.autograd.Function):
-    """Forward: the fused kernel.  Backward: autograd through `_eager_qkv` on the saved projections."""
+    """Forward: the fused kernel.  Backward: `lact_qkv_prologue_bwd` on the saved projections (rotation transposed,
+    l2-norm and SiLU differentiated in one pass per row)."""
     @staticmethod
     def forward(ctx, xq, xk, xv, num_heads, qkv_silu, v_silu, cos, sin, rope_hd, offset):
         ctx.save_for_backward(xq, xk, xv, *((cos, sin) if cos is not None else ()))
@@ -62,14 +41,22 @@ class _QkvPrologue(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dq, dk, dv):
         saved = ctx.saved_tensors
-        xq, xk, xv = saved[:3]
         n_h, qkv_silu, v_silu, rope_hd, offset = ctx.cfg
-        rope = (saved[3], saved[4], rope_hd, offset) if len(saved) == 5 else None
-        with torch.enable_grad():
-            leaves = [t.detach().float().requires_grad_(True) for t in (xq, xk, xv)]
-            outs = _eager_qkv(*leaves, n_h, qkv_silu, v_silu, rope)
-            g = torch.autograd.grad(outs, leaves, [t.float() for t in (dq, dk, dv)])
-        return (*[gi.to(x.dtype) for gi, x in zip(g, (xq, xk, xv))], None, None, None, None, None, None, None)
+        xs = [_rows(t, "projection") for t in saved[:3]]
+        b, s, nd = xs[0].shape
+        d = nd // n_h
+        cos, sin = (saved[3], saved[4]) if len(saved) == 5 else (None, None)
+        dzs = [None if g is None else g.to(BF16).contiguous() for g in (dq, dk, dv)]
+        outs = [torch.empty(b, s, nd, dtype=BF16, device=xs[0].device) for _ in range(3)]
+        with torch.cuda.device(xs[0].device):
+            L.check(L.lib().lact_qkv_prologue_bwd(
+                xs[0].data_ptr(), xs[1].data_ptr(), xs[2].data_ptr(), xs[0].stride(1), xs[1].stride(1), xs[2].stride(1),
+                xs[0].stride(0), xs[1].stride(0), xs[2].stride(0), *[None if g is None else g.data_ptr() for g in dzs],
+                outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(), b, s, n_h, d, int(qkv_silu), int(v_silu),
+                cos.data_ptr() if cos is not None else None, sin.data_ptr() if sin is not None else None,
+                int(rope_hd) if cos is not None else 0, cos.shape[0] if cos is not None else 0, int(offset),
+                L.stream_ptr()), "lact_qkv_prologue_bwd")
+        return (*[o.to(x.dtype) for o, x in zip(outs, saved[:3])], None, None, None, None, None, None, None)
 
 
 def _rows(t: torch.Tensor, name: str) -> torch.Tensor:
@@ -199,16 +186,9 @@ def _lr_prologue_fwd(lr_proj: torch.Tensor, num_heads: int, base_lr: float, mome
     return outs[0], outs[1], outs[2], mom
 
 
-def _eager_out(fw_x, w, n_h, scale_proj, o, eps):
-    x = fw_x.float()
-    y = x * torch.rsqrt(x.square().mean(dim=-1, keepdim=True) + eps) * w.float()
-    if scale_proj is not None:
-        y = y * _heads(F.silu(scale_proj.float()), n_h)
-    y = _unheads(y, n_h)
-    return y + o.float() if o is not None else y
-
-
 class _OutEpilogue(torch.autograd.Function):
+    """Forward: the fused kernel.  Backward: `lact_out_epilogue_bwd` (RMSNorm, gate and head merge differentiated in
+    one pass per row; the norm weight's gradient as per-block partial sums added here)."""
     @staticmethod
     def forward(ctx, fw_x, norm_weight, scale_proj, o, num_heads, eps):
         ctx.save_for_backward(fw_x, norm_weight, *((scale_proj,) if scale_proj is not None else ()))
@@ -219,14 +199,28 @@ class _OutEpilogue(torch.autograd.Function):
     def backward(ctx, dout):
         saved = ctx.saved_tensors
         n_h, eps, has_gate, has_o = ctx.cfg
-        with torch.enable_grad():
-            x = saved[0].detach().float().requires_grad_(True)
-            w = saved[1].detach().float().requires_grad_(True)
-            gate = saved[2].detach().float().requires_grad_(True) if has_gate else None
-            leaves = [x, w] + ([gate] if has_gate else [])
-            g = torch.autograd.grad(_eager_out(x, w, n_h, gate, None, eps), leaves, dout.float())
-        return (g[0].to(saved[0].dtype), g[1].to(saved[1].dtype), g[2].to(saved[2].dtype) if has_gate else None,
-                dout if has_o else None, None, None)
+        x = saved[0].contiguous()
+        B, s, d = x.shape
+        b = B // n_h
+        w = saved[1].detach().float().contiguous()
+        gate = None
+        if has_gate:
+            gate = _rows(saved[2], "scale_proj")
+            gate = gate if gate.stride(0) == s * gate.stride(1) else gate.contiguous()
+        dy = _rows(dout.to(BF16), "grad")
+        dy = dy if dy.stride(0) == s * dy.stride(1) else dy.contiguous()
+        dx = torch.empty_like(x)
+        dgate = torch.empty(b, s, n_h * d, dtype=BF16, device=x.device) if has_gate else None
+        blocks = L.lib().lact_out_epilogue_bwd_blocks()
+        part = torch.empty(blocks, d, dtype=torch.float32, device=x.device)
+        with torch.cuda.device(x.device):
+            L.check(L.lib().lact_out_epilogue_bwd(x.data_ptr(), w.data_ptr(), gate.data_ptr() if has_gate else None,
+                                                  gate.stride(1) if has_gate else 0, dy.data_ptr(), dy.stride(1),
+                                                  dx.data_ptr(), dgate.data_ptr() if has_gate else None, part.data_ptr(),
+                                                  b, s, n_h, d, float(eps), L.stream_ptr()), "lact_out_epilogue_bwd")
+        dw = part.sum(dim=0).to(saved[1].dtype)
+        return (dx.to(saved[0].dtype), dw, dgate.to(saved[2].dtype) if has_gate else None, dout if has_o else None,
+                None, None)
 
 
 def out_epilogue(fw_x: torch.Tensor, norm_weight: torch.Tensor, num_heads: int, scale_proj: torch.Tensor = None,
