@@ -24,7 +24,9 @@ os.environ.setdefault("TORCHDYNAMO_DISABLE", "1")
 import torch  # noqa: E402
 import torch.nn.functional as F  # noqa: E402
 
-REF_ROOT = os.environ.get("LACT_REFERENCE_ROOT", "/root/reference")
+# where the reference tree lives: LACT_REFERENCE_ROOT, else a `reference` directory beside this repository
+REF_ROOT = os.environ.get("LACT_REFERENCE_ROOT") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
 
 
 def available() -> bool:

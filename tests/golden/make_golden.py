@@ -1,7 +1,7 @@
 """Generates tests/golden/ref_outputs.pt by RUNNING THE REFERENCE's own functions on CPU.
 
-Run in a container that holds the reference tree (default /root/reference, or
-LACT_REFERENCE_ROOT):
+Run where the reference tree is available (LACT_REFERENCE_ROOT, default: a `reference` directory beside this
+repository):
 
     python tests/golden/make_golden.py              # chunk drivers and sub-ops -> ref_outputs.pt
     python tests/golden/make_golden.py --prologue   # layer prologue             -> layer_prologue.pt
