@@ -420,10 +420,31 @@ def swa_bench(lb, dev, warmup, steps, batch=None, seq_len=None):
     pairs = sum(min(i + 1, w) for i in range(l))
     flops = 4.0 * pairs * d * h * b
     peaks = measured_peaks()
+    # forward + backward (dq, dk, dv): algorithmic FLOPs of the backward = 2.5 x the forward's (five products for two)
+    leaves = [t.clone().requires_grad_(True) for t in (q, k, v)]
+    dO = torch.randn(b, l, h, d, device=dev, generator=g).to(BF16)
+
+    def train():
+        for t in leaves:
+            t.grad = None
+        layer_ops.sliding_window_attention(*leaves, w).backward(dO)
+    for _ in range(2):
+        train()
+    torch.cuda.synchronize()
+    n_tr = max(2, steps // 2)
+    e0.record()
+    for _ in range(n_tr):
+        train()
+    e1.record()
+    torch.cuda.synchronize()
+    lb.synchronize_and_check()
+    ms_tr = e0.elapsed_time(e1) / n_tr
     print(json.dumps({"metric": "swa_fwd_tokens_per_s", "value": b * l / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
                       "steps": steps, "ms_per_step": ms, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
                       "tflops": flops / (ms * 1e-3) / 1e12,
                       "frac_of_bf16_peak_burst": flops / (ms * 1e-3) / 1e12 / peaks["bf16_burst"],
+                      "train": {"ms_per_step": ms_tr, "steps": n_tr, "tflops": 3.5 * flops / (ms_tr * 1e-3) / 1e12,
+                                "frac_of_bf16_peak_burst": 3.5 * flops / (ms_tr * 1e-3) / 1e12 / peaks["bf16_burst"]},
                       "config": {"workload": "causal sliding-window attention forward", "batch": b, "seq_len": l,
                                  "heads": h, "head_dim": d, "window": w,
                                  "l2": "q, k, v, o (%.0f MB) exceed L2" % (4 * b * l * h * d * 2 / 1e6)}}))

@@ -15,7 +15,7 @@
 
 #include "../../include/lact_b200.h"
 #include "ns_bwd_fused.cuh"
-#include "swa.cuh"
+#include "swa_bwd.cuh"
 
 namespace lact {
 namespace {
@@ -932,6 +932,28 @@ template <int HD>
 int launch_swa(const SwaArgs& a, int64_t ctas, cudaStream_t stream) {
   auto kernel = swa_fwd_kernel<HD>;
   constexpr uint32_t smem = SwaSmem<HD>::kBytes;
+  static_assert(smem <= 232448, "shared memory budget exceeded");
+  static std::mutex mu;
+  static bool configured[64] = {false};
+  int dev = 0;
+  LACT_CUDA(cudaGetDevice(&dev));
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev >= 64 || !configured[dev]) {
+      LACT_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      if (dev < 64) configured[dev] = true;
+    }
+  }
+  KernelScope scope(kClsOther, stream);
+  kernel<<<static_cast<unsigned>(ctas), 320, smem, stream>>>(a);
+  LACT_CUDA(cudaGetLastError());
+  return LACT_OK;
+}
+
+template <int HD, int MODE>
+int launch_swa_bwd(const SwaBwdArgs& a, int64_t ctas, cudaStream_t stream) {
+  auto kernel = swa_bwd_kernel<HD, MODE>;
+  constexpr uint32_t smem = SwaBwdSmem<HD>::kBytes;
   static_assert(smem <= 232448, "shared memory budget exceeded");
   static std::mutex mu;
   static bool configured[64] = {false};
@@ -1891,7 +1913,7 @@ int lact_out_epilogue(const void* fw_x, const void* weight, const void* gate_pro
 
 int lact_swa_fwd(const void* q, const void* k, const void* v, void* o, int64_t b, int64_t l, int64_t n_heads, int64_t d,
                  int64_t q_ts, int64_t q_bs, int64_t k_ts, int64_t k_bs, int64_t v_ts, int64_t v_bs, int64_t o_ts,
-                 int64_t o_bs, int64_t window, float softmax_scale, int32_t* status_word, void* stream) {
+                 int64_t o_bs, int64_t window, float softmax_scale, void* lse, int32_t* status_word, void* stream) {
   if (!q || !k || !v || !o || !status_word) return LACT_ERR_NULL;
   LACT_TRY(check_device());
   if (d != 64 && d != 128) return LACT_ERR_SHAPE;
@@ -1911,11 +1933,66 @@ int lact_swa_fwd(const void* q, const void* k, const void* v, void* o, int64_t b
   a.heads = static_cast<int32_t>(n_heads);
   a.q_tiles = ceil_div(l, 128);
   a.scale_log2 = softmax_scale * 1.4426950408889634f;
+  a.lse = static_cast<float*>(lse);
   a.status = status_word;
   const int64_t ctas = b * n_heads * a.q_tiles;
   if (ctas > 0x7FFFFFFFll) return LACT_ERR_SHAPE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   return d == 64 ? launch_swa<64>(a, ctas, st) : launch_swa<128>(a, ctas, st);
+}
+
+int lact_swa_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout, const void* lse, void* dq,
+                 void* dk, void* dv, void* delta, int64_t b, int64_t l, int64_t n_heads, int64_t d, int64_t q_ts,
+                 int64_t q_bs, int64_t k_ts, int64_t k_bs, int64_t v_ts, int64_t v_bs, int64_t o_ts, int64_t o_bs,
+                 int64_t do_ts, int64_t do_bs, int64_t window, float softmax_scale, int32_t* status_word, void* stream) {
+  if (!q || !k || !v || !o || !dout || !lse || !dq || !dk || !dv || !delta || !status_word) return LACT_ERR_NULL;
+  LACT_TRY(check_device());
+  if (d != 64 && d != 128) return LACT_ERR_SHAPE;
+  if (b < 1 || l < 1 || n_heads < 1 || b > 65535 || n_heads > 65535 || l > (1ll << 30)) return LACT_ERR_SHAPE;
+  if (!(softmax_scale > 0.f)) return LACT_ERR_CONFIG;
+  for (const void* p : {static_cast<const void*>(dq), static_cast<const void*>(dk), static_cast<const void*>(dv), o, dout})
+    if ((reinterpret_cast<uintptr_t>(p) & 15) != 0) return LACT_ERR_SHAPE;
+  if (o_ts < n_heads * d || do_ts < n_heads * d || (o_ts % 8) || (o_bs % 8) || (do_ts % 8) || (do_bs % 8)) return LACT_ERR_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  {
+    SwaDeltaArgs da;
+    std::memset(&da, 0, sizeof(da));
+    da.o = static_cast<const bf16*>(o);
+    da.dout = static_cast<const bf16*>(dout);
+    da.o_ts = o_ts; da.o_bs = o_bs; da.d_ts = do_ts; da.d_bs = do_bs;
+    da.delta = static_cast<float*>(delta);
+    da.b = static_cast<int32_t>(b); da.L = static_cast<int32_t>(l);
+    da.heads = static_cast<int32_t>(n_heads); da.d = static_cast<int32_t>(d);
+    const int64_t rows = b * l * n_heads;
+    KernelScope scope(kClsOther, st);
+    swa_delta_kernel<<<static_cast<unsigned>(ceil_div(rows, 8)), 256, 0, st>>>(da);
+    LACT_CUDA(cudaGetLastError());
+  }
+  SwaBwdArgs a;
+  std::memset(&a, 0, sizeof(a));
+  LACT_TRY(encode_map_heads(&a.q, q, b, l, n_heads, d, q_ts, q_bs));
+  LACT_TRY(encode_map_heads(&a.k, k, b, l, n_heads, d, k_ts, k_bs));
+  LACT_TRY(encode_map_heads(&a.v, v, b, l, n_heads, d, v_ts, v_bs));
+  LACT_TRY(encode_map_heads(&a.dout, dout, b, l, n_heads, d, do_ts, do_bs));
+  a.lse = static_cast<const float*>(lse);
+  a.delta = static_cast<const float*>(delta);
+  a.o_ts = n_heads * d; a.o_bs = l * n_heads * d; a.o_hs = d;   // gradients are written contiguous [b][l][h][d]
+  a.L = static_cast<int32_t>(l);
+  a.window = window > 0 && window < l ? static_cast<int32_t>(window) : 0;
+  a.heads = static_cast<int32_t>(n_heads);
+  a.tiles = ceil_div(l, 128);
+  a.scale_log2 = softmax_scale * 1.4426950408889634f;
+  a.scale = softmax_scale;
+  a.status = status_word;
+  const int64_t ctas = b * n_heads * a.tiles;
+  if (ctas > 0x7FFFFFFFll) return LACT_ERR_SHAPE;
+  // keys' side (dK, dV), then queries' side (dQ)
+  a.out0 = static_cast<bf16*>(dk);
+  a.out1 = static_cast<bf16*>(dv);
+  LACT_TRY((d == 64 ? launch_swa_bwd<64, 0>(a, ctas, st) : launch_swa_bwd<128, 0>(a, ctas, st)));
+  a.out0 = static_cast<bf16*>(dq);
+  a.out1 = nullptr;
+  return d == 64 ? launch_swa_bwd<64, 1>(a, ctas, st) : launch_swa_bwd<128, 1>(a, ctas, st);
 }
 
 int lact_l2_norm_add(const void* x, int32_t x_dtype, const void* x_add, int32_t add_dtype, const void* scale, void* y,

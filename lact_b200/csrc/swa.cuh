@@ -25,6 +25,7 @@ struct SwaArgs {
   int32_t L, window;     // window <= 0: unbounded (plain causal attention)
   int32_t heads, q_tiles;
   float scale_log2;      // log2(e) / sqrt(d)
+  float* lse;            // optional [b][h][l]: log2-domain log-sum-exp of every row (the backward's input), or nullptr
   int32_t* status;
 };
 
@@ -300,6 +301,7 @@ __global__ void __launch_bounds__(320, 1) swa_fwd_kernel(const __grid_constant__
     if (!failed && qi < a.L) {
       const float tot = l + l_other;
       const float inv = tot > 0.f ? 1.0f / tot : 0.f;
+      if (a.lse != nullptr && half == 0) a.lse[(static_cast<int64_t>(batch) * a.heads + head) * a.L + qi] = m + log2f(tot);
       bf16* dst = a.o + batch * a.o_bs + static_cast<int64_t>(qi) * a.o_ts + head * a.o_hs + half * OC;
 #pragma unroll
       for (int c = 0; c < OC; c += 8) {

@@ -9,7 +9,7 @@ PyTorch restatement."""
 from __future__ import annotations
 
 import math
-from typing import Optional, Tuple
+from typing import List, Optional, Tuple
 
 import torch
 import torch.nn.functional as F
@@ -266,34 +266,83 @@ def _out_epilogue_fwd(fw_x: torch.Tensor, norm_weight: torch.Tensor, num_heads: 
 
 
 # ------------------------------------------------------------------------------------------ sliding-window attention
+def _head_view(t: torch.Tensor, h: int, d: int) -> torch.Tensor:
+    """[b, l, h, d] with heads adjacent within a token and 16-byte aligned token / batch strides (the layout of a slice
+    of a fused projection reshaped to heads); anything else is copied."""
+    if (t.stride(3) != 1 or t.stride(2) != d or t.stride(1) % 8 or t.stride(0) % 8 or t.data_ptr() % 16
+            or t.stride(1) < h * d):
+        t = t.contiguous()
+    return t
+
+
 @torch.library.custom_op("lact_b200::swa_fwd", mutates_args=(), device_types="cuda")
-def _swa_fwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: int, softmax_scale: float) -> torch.Tensor:
+def _swa_fwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: int, softmax_scale: float) -> List[torch.Tensor]:
+    """[o, lse]: the attention output and every row's log-sum-exp (log2 domain, fp32 [b, h, l]) for the backward."""
     from .backward import _status_word, post_status, reset_status
     b, l, h, d = q.shape
-
-    def view(t, name):
-        # heads adjacent within a token, 16-byte aligned token / batch strides: the layout of a slice of a fused
-        # projection reshaped to heads; anything else is copied
-        if (t.stride(3) != 1 or t.stride(2) != d or t.stride(1) % 8 or t.stride(0) % 8 or t.data_ptr() % 16
-                or t.stride(1) < h * d):
-            t = t.contiguous()
-        return t
-
-    q, k, v = view(q, "q"), view(k, "k"), view(v, "v")
+    q, k, v = _head_view(q, h, d), _head_view(k, h, d), _head_view(v, h, d)
     o = torch.empty(b, l, h, d, dtype=BF16, device=q.device)
+    lse = torch.empty(b, h, l, dtype=torch.float32, device=q.device)
     reset_status(q.device)
     with torch.cuda.device(q.device):
         L.check(L.lib().lact_swa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), b, l, h, d, q.stride(1),
                                      q.stride(0), k.stride(1), k.stride(0), v.stride(1), v.stride(0), o.stride(1),
-                                     o.stride(0), int(window), float(softmax_scale), _status_word(q.device).data_ptr(),
-                                     L.stream_ptr()), "lact_swa_fwd")
+                                     o.stride(0), int(window), float(softmax_scale), lse.data_ptr(),
+                                     _status_word(q.device).data_ptr(), L.stream_ptr()), "lact_swa_fwd")
     post_status(q.device)
-    return o
+    return [o, lse]
 
 
 @_swa_fwd_op.register_fake
 def _swa_fwd_fake(q, k, v, window, softmax_scale):
-    return q.new_empty(q.shape)
+    b, l, h, d = q.shape
+    return [q.new_empty(q.shape), q.new_empty((b, h, l), dtype=torch.float32)]
+
+
+@torch.library.custom_op("lact_b200::swa_bwd", mutates_args=(), device_types="cuda")
+def _swa_bwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tensor, lse: torch.Tensor,
+                dout: torch.Tensor, window: int, softmax_scale: float) -> List[torch.Tensor]:
+    """[dq, dk, dv] (bf16, contiguous): probabilities recomputed from lse, five products per (query tile, key tile)."""
+    from .backward import _status_word, post_status, reset_status
+    b, l, h, d = q.shape
+    q, k, v = _head_view(q, h, d), _head_view(k, h, d), _head_view(v, h, d)
+    o, dout = _head_view(o, h, d), _head_view(dout.to(BF16), h, d)
+    dq, dk, dv = (torch.empty(b, l, h, d, dtype=BF16, device=q.device) for _ in range(3))
+    delta = torch.empty(b, h, l, dtype=torch.float32, device=q.device)
+    reset_status(q.device)
+    with torch.cuda.device(q.device):
+        L.check(L.lib().lact_swa_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), dout.data_ptr(),
+                                     lse.contiguous().data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                     delta.data_ptr(), b, l, h, d, q.stride(1), q.stride(0), k.stride(1), k.stride(0),
+                                     v.stride(1), v.stride(0), o.stride(1), o.stride(0), dout.stride(1), dout.stride(0),
+                                     int(window), float(softmax_scale), _status_word(q.device).data_ptr(),
+                                     L.stream_ptr()), "lact_swa_bwd")
+    post_status(q.device)
+    return [dq, dk, dv]
+
+
+@_swa_bwd_op.register_fake
+def _swa_bwd_fake(q, k, v, o, lse, dout, window, softmax_scale):
+    return [q.new_empty(q.shape), q.new_empty(q.shape), q.new_empty(q.shape)]
+
+
+def _swa_setup(ctx, inputs, output):
+    q, k, v, window, scale = inputs
+    ctx.save_for_backward(q, k, v, output[0], output[1])
+    ctx.cfg = (int(window), float(scale))
+    ctx.set_materialize_grads(False)
+
+
+def _swa_autograd(ctx, grads):
+    q, k, v, o, lse = ctx.saved_tensors
+    dout = grads[0]
+    if dout is None:
+        return None, None, None, None, None
+    dq, dk, dv = torch.ops.lact_b200.swa_bwd(q, k, v, o, lse, dout.contiguous(), ctx.cfg[0], ctx.cfg[1])
+    return dq, dk, dv, None, None
+
+
+_swa_fwd_op.register_autograd(_swa_autograd, setup_context=_swa_setup)
 
 
 def sliding_window_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window_size: Optional[int] = None,
@@ -302,7 +351,7 @@ def sliding_window_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, 
     result [b, l, n_heads, head_dim] bf16: what `flash_attn_func(q, k, v, causal=True, window_size=(window_size - 1,
     0))` computes at lact_llm/lact_model/layer_lact_swiglu.py:386-394 and
     minimal_implementations/causal_lact_with_sliding_window_attn.py:380-384 (`window_size=None`: all earlier keys).
-    head_dim 64 or 128.  Forward only."""
+    head_dim 64 or 128.  Differentiable (dq, dk, dv by `lact_swa_bwd`)."""
     if not (q.is_cuda and k.is_cuda and v.is_cuda):
         raise ValueError("sliding_window_attention needs CUDA tensors (there is no CPU implementation)")
     assert q.dim() == 4 and q.shape == k.shape == v.shape, "q, k, v: [b, l, n_heads, head_dim], equal head counts"
@@ -310,4 +359,4 @@ def sliding_window_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, 
     if q.shape[3] not in (64, 128):
         raise ValueError("head_dim must be 64 or 128")
     scale = float(softmax_scale) if softmax_scale is not None else q.shape[3] ** -0.5
-    return torch.ops.lact_b200.swa_fwd(q, k, v, int(window_size) if window_size else 0, scale)
+    return torch.ops.lact_b200.swa_fwd(q, k, v, int(window_size) if window_size else 0, scale)[0]
