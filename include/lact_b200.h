@@ -255,12 +255,15 @@ int lact_lr_prologue(const void *lr_proj, int32_t proj_dtype, int64_t proj_ld, f
  * lact_llm/lact_model/layer_lact_swiglu.py:386-394 and
  * minimal_implementations/causal_lact_with_sliding_window_attn.py:380-384.  bf16; d = 64 or 128; heads adjacent within
  * a token (head stride d), token / batch strides in elements (views of a fused projection are fine);
- * window <= 0 or >= l: plain causal attention.  lse: optional fp32 [b, n_heads, l], receives every row's log-sum-exp
+ * window <= 0 or >= l: plain causal attention.  seq_start: NULL, or for b = 1 an int32 [l] device array giving, for every
+ * token, the first token of the packed sequence it belongs to (nondecreasing; what cu_seqlens describes in
+ * flash_attn_varlen_func, layer_lact_swiglu.py:371-385): earlier keys are invisible.  lse: optional fp32 [b, n_heads, l], receives every row's log-sum-exp
  * in the log2 domain (what lact_swa_bwd needs), or NULL.  status_word: device word, 0 before the call (101 = a bounded
  * wait ran out). */
 int lact_swa_fwd(const void *q, const void *k, const void *v, void *o, int64_t b, int64_t l, int64_t n_heads, int64_t d,
                  int64_t q_ts, int64_t q_bs, int64_t k_ts, int64_t k_bs, int64_t v_ts, int64_t v_bs, int64_t o_ts,
-                 int64_t o_bs, int64_t window, float softmax_scale, void *lse, int32_t *status_word, void *stream);
+                 int64_t o_bs, int64_t window, float softmax_scale, const int32_t *seq_start, void *lse,
+                 int32_t *status_word, void *stream);
 
 /* Backward of lact_swa_fwd: dq, dk, dv (bf16, contiguous [b, l, n_heads, d], written) from the forward's inputs, its
  * output o, its lse and the output gradient dout (bf16, token / batch strides in elements).  delta: fp32 scratch
@@ -269,7 +272,8 @@ int lact_swa_fwd(const void *q, const void *k, const void *v, void *o, int64_t b
 int lact_swa_bwd(const void *q, const void *k, const void *v, const void *o, const void *dout, const void *lse, void *dq,
                  void *dk, void *dv, void *delta, int64_t b, int64_t l, int64_t n_heads, int64_t d, int64_t q_ts,
                  int64_t q_bs, int64_t k_ts, int64_t k_bs, int64_t v_ts, int64_t v_bs, int64_t o_ts, int64_t o_bs,
-                 int64_t do_ts, int64_t do_bs, int64_t window, float softmax_scale, int32_t *status_word, void *stream);
+                 int64_t do_ts, int64_t do_bs, int64_t window, float softmax_scale, const int32_t *seq_start,
+                 int32_t *status_word, void *stream);
 
 /* Backward of lact_qkv_prologue / lact_qkv_prologue_rope on the saved projections (same strides): dq, dk, dv are the
  * gradients of the head-major outputs ([(b n_heads), s, d] bf16, NULL = none), dxq, dxk, dxv the gradients of the

@@ -1913,8 +1913,10 @@ int lact_out_epilogue(const void* fw_x, const void* weight, const void* gate_pro
 
 int lact_swa_fwd(const void* q, const void* k, const void* v, void* o, int64_t b, int64_t l, int64_t n_heads, int64_t d,
                  int64_t q_ts, int64_t q_bs, int64_t k_ts, int64_t k_bs, int64_t v_ts, int64_t v_bs, int64_t o_ts,
-                 int64_t o_bs, int64_t window, float softmax_scale, void* lse, int32_t* status_word, void* stream) {
+                 int64_t o_bs, int64_t window, float softmax_scale, const int32_t* seq_start, void* lse, int32_t* status_word,
+                 void* stream) {
   if (!q || !k || !v || !o || !status_word) return LACT_ERR_NULL;
+  if (seq_start != nullptr && b != 1) return LACT_ERR_CONFIG;   // packed sequences live in one batch entry
   LACT_TRY(check_device());
   if (d != 64 && d != 128) return LACT_ERR_SHAPE;
   if (b < 1 || l < 1 || n_heads < 1 || b > 65535 || n_heads > 65535 || l > (1ll << 30)) return LACT_ERR_SHAPE;
@@ -1934,6 +1936,7 @@ int lact_swa_fwd(const void* q, const void* k, const void* v, void* o, int64_t b
   a.q_tiles = ceil_div(l, 128);
   a.scale_log2 = softmax_scale * 1.4426950408889634f;
   a.lse = static_cast<float*>(lse);
+  a.seq_start = seq_start;
   a.status = status_word;
   const int64_t ctas = b * n_heads * a.q_tiles;
   if (ctas > 0x7FFFFFFFll) return LACT_ERR_SHAPE;
@@ -1944,8 +1947,10 @@ int lact_swa_fwd(const void* q, const void* k, const void* v, void* o, int64_t b
 int lact_swa_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout, const void* lse, void* dq,
                  void* dk, void* dv, void* delta, int64_t b, int64_t l, int64_t n_heads, int64_t d, int64_t q_ts,
                  int64_t q_bs, int64_t k_ts, int64_t k_bs, int64_t v_ts, int64_t v_bs, int64_t o_ts, int64_t o_bs,
-                 int64_t do_ts, int64_t do_bs, int64_t window, float softmax_scale, int32_t* status_word, void* stream) {
+                 int64_t do_ts, int64_t do_bs, int64_t window, float softmax_scale, const int32_t* seq_start,
+                 int32_t* status_word, void* stream) {
   if (!q || !k || !v || !o || !dout || !lse || !dq || !dk || !dv || !delta || !status_word) return LACT_ERR_NULL;
+  if (seq_start != nullptr && b != 1) return LACT_ERR_CONFIG;
   LACT_TRY(check_device());
   if (d != 64 && d != 128) return LACT_ERR_SHAPE;
   if (b < 1 || l < 1 || n_heads < 1 || b > 65535 || n_heads > 65535 || l > (1ll << 30)) return LACT_ERR_SHAPE;
@@ -1976,6 +1981,7 @@ int lact_swa_bwd(const void* q, const void* k, const void* v, const void* o, con
   LACT_TRY(encode_map_heads(&a.dout, dout, b, l, n_heads, d, do_ts, do_bs));
   a.lse = static_cast<const float*>(lse);
   a.delta = static_cast<const float*>(delta);
+  a.seq_start = seq_start;
   a.o_ts = n_heads * d; a.o_bs = l * n_heads * d; a.o_hs = d;   // gradients are written contiguous [b][l][h][d]
   a.L = static_cast<int32_t>(l);
   a.window = window > 0 && window < l ? static_cast<int32_t>(window) : 0;

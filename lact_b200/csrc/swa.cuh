@@ -25,6 +25,8 @@ struct SwaArgs {
   int32_t L, window;     // window <= 0: unbounded (plain causal attention)
   int32_t heads, q_tiles;
   float scale_log2;      // log2(e) / sqrt(d)
+  const int32_t* seq_start;  // optional [l]: first token of the packed sequence every token belongs to (nondecreasing;
+                             // keys before it are invisible), or nullptr: one sequence per batch entry
   float* lse;            // optional [b][h][l]: log2-domain log-sum-exp of every row (the backward's input), or nullptr
   int32_t* status;
 };
@@ -107,6 +109,9 @@ __global__ void __launch_bounds__(320, 1) swa_fwd_kernel(const __grid_constant__
   const int window = a.window > 0 ? a.window : a.L;
   int kv_lo = q0 - (window - 1);
   kv_lo = kv_lo < 0 ? 0 : (kv_lo / 128) * 128;
+  // packed sequences: no row of this tile sees a key before the first row's sequence start
+  if (a.seq_start != nullptr && a.seq_start[q0] > kv_lo) kv_lo = (a.seq_start[q0] / 128) * 128;
+  const int tile_start = a.seq_start != nullptr ? a.seq_start[q0 + 127 < a.L ? q0 + 127 : a.L - 1] : 0;  // last row's
   const int kv_hi = q0 + 128 < a.L ? q0 + 128 : a.L;
   const int T = (kv_hi - kv_lo + 127) / 128;
   bool failed = *reinterpret_cast<volatile int32_t*>(a.status) != kStatusOk;
@@ -177,6 +182,7 @@ __global__ void __launch_bounds__(320, 1) swa_fwd_kernel(const __grid_constant__
     const int half = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;
     const int qi = q0 + r;
+    const int row_start = (a.seq_start != nullptr && qi < a.L) ? a.seq_start[qi] : 0;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     constexpr int OC = HD / 2;   // output features per thread
     float m = -INFINITY, l = 0.f, a_prev = 1.f;
@@ -222,10 +228,10 @@ __global__ void __launch_bounds__(320, 1) swa_fwd_kernel(const __grid_constant__
       if (!mbar_wait(&s_full[sb], (t >> 1) & 1, abort_flag)) { failed = true; break; }
       tc_fence_after();
       // every (row, key) pair of the tile inside the band and the sequence: no masks
-      const bool interior = kv0 + 127 <= q0 && kv0 >= q0 + 127 - (window - 1) && kv0 + 127 < a.L;
+      const bool interior = kv0 + 127 <= q0 && kv0 >= q0 + 127 - (window - 1) && kv0 + 127 < a.L && kv0 >= tile_start;
       const int c0 = half * 64;                                // this thread's first key column of the tile
       const int j_hi = (qi < a.L - 1 ? qi : a.L - 1) - kv0;   // last / first column of the tile this row may see
-      const int j_lo = qi - (window - 1) - kv0;
+      const int j_lo = (qi - (window - 1) > row_start ? qi - (window - 1) : row_start) - kv0;
       const uint32_t s_addr = tmem + lane_off + sb * 128 + c0;
       uint32_t ba[32], bb[32];
       float mx = -INFINITY;

@@ -20,6 +20,7 @@ struct SwaBwdArgs {
   CUtensorMap q, k, v, dout;   // 4-D maps (feature, token, head, batch), box {64, 128, 1, 1}
   const float* lse;            // [b][h][l]: log2-domain log-sum-exp of the forward (m + log2(l))
   const float* delta;          // [b][h][l]: sum_d dO O
+  const int32_t* seq_start;    // optional [l], as in the forward
   bf16* out0;                  // MODE 0: dK, MODE 1: dQ   ([b][l][h][d], strides below)
   bf16* out1;                  // MODE 0: dV
   int64_t o_bs, o_ts, o_hs;
@@ -192,10 +193,14 @@ __global__ void __launch_bounds__(320, 1) swa_bwd_kernel(const __grid_constant__
       }
       if (!mbar_wait(sdp_full, t & 1, abort_flag)) { failed = true; break; }
       tc_fence_after();
-      const bool interior = kv0 + 127 <= q0 && kv0 >= q0 + 127 - (window - 1) && kv0 + 127 < a.L && q0 + 127 < a.L;
+      // (packed sequences: the last query row of the tile has the latest sequence start)
+      const int tile_start = a.seq_start != nullptr ? a.seq_start[q0 + 127 < a.L ? q0 + 127 : a.L - 1] : 0;
+      const int row_start = (a.seq_start != nullptr && qi < a.L) ? a.seq_start[qi] : 0;
+      const bool interior = kv0 + 127 <= q0 && kv0 >= q0 + 127 - (window - 1) && kv0 + 127 < a.L && q0 + 127 < a.L &&
+                            kv0 >= tile_start;
       const int c0 = half * 64;
       const int j_hi = (qi < a.L ? qi : -1) - kv0;   // last / first key column of the tile this query may see
-      const int j_lo = qi - (window - 1) - kv0;
+      const int j_lo = (qi - (window - 1) > row_start ? qi - (window - 1) : row_start) - kv0;
       const int j_end = a.L - kv0;                     // keys beyond the sequence
       const uint32_t s_addr = tmem + lane_off + c0, dp_addr = tmem + lane_off + 128 + c0;
       const uint32_t p_row = base + SM::kP + half * kBox + r * 128, ds_row = base + SM::kDS + half * kBox + r * 128;

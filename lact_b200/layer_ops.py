@@ -276,7 +276,8 @@ def _head_view(t: torch.Tensor, h: int, d: int) -> torch.Tensor:
 
 
 @torch.library.custom_op("lact_b200::swa_fwd", mutates_args=(), device_types="cuda")
-def _swa_fwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: int, softmax_scale: float) -> List[torch.Tensor]:
+def _swa_fwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: int, softmax_scale: float,
+                seq_start: Optional[torch.Tensor] = None) -> List[torch.Tensor]:
     """[o, lse]: the attention output and every row's log-sum-exp (log2 domain, fp32 [b, h, l]) for the backward."""
     from .backward import _status_word, post_status, reset_status
     b, l, h, d = q.shape
@@ -287,21 +288,23 @@ def _swa_fwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: int, 
     with torch.cuda.device(q.device):
         L.check(L.lib().lact_swa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), b, l, h, d, q.stride(1),
                                      q.stride(0), k.stride(1), k.stride(0), v.stride(1), v.stride(0), o.stride(1),
-                                     o.stride(0), int(window), float(softmax_scale), lse.data_ptr(),
+                                     o.stride(0), int(window), float(softmax_scale),
+                                     seq_start.data_ptr() if seq_start is not None else None, lse.data_ptr(),
                                      _status_word(q.device).data_ptr(), L.stream_ptr()), "lact_swa_fwd")
     post_status(q.device)
     return [o, lse]
 
 
 @_swa_fwd_op.register_fake
-def _swa_fwd_fake(q, k, v, window, softmax_scale):
+def _swa_fwd_fake(q, k, v, window, softmax_scale, seq_start=None):
     b, l, h, d = q.shape
     return [q.new_empty(q.shape), q.new_empty((b, h, l), dtype=torch.float32)]
 
 
 @torch.library.custom_op("lact_b200::swa_bwd", mutates_args=(), device_types="cuda")
 def _swa_bwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tensor, lse: torch.Tensor,
-                dout: torch.Tensor, window: int, softmax_scale: float) -> List[torch.Tensor]:
+                dout: torch.Tensor, window: int, softmax_scale: float,
+                seq_start: Optional[torch.Tensor] = None) -> List[torch.Tensor]:
     """[dq, dk, dv] (bf16, contiguous): probabilities recomputed from lse, five products per (query tile, key tile)."""
     from .backward import _status_word, post_status, reset_status
     b, l, h, d = q.shape
@@ -315,43 +318,50 @@ def _swa_bwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tens
                                      lse.contiguous().data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
                                      delta.data_ptr(), b, l, h, d, q.stride(1), q.stride(0), k.stride(1), k.stride(0),
                                      v.stride(1), v.stride(0), o.stride(1), o.stride(0), dout.stride(1), dout.stride(0),
-                                     int(window), float(softmax_scale), _status_word(q.device).data_ptr(),
-                                     L.stream_ptr()), "lact_swa_bwd")
+                                     int(window), float(softmax_scale),
+                                     seq_start.data_ptr() if seq_start is not None else None,
+                                     _status_word(q.device).data_ptr(), L.stream_ptr()), "lact_swa_bwd")
     post_status(q.device)
     return [dq, dk, dv]
 
 
 @_swa_bwd_op.register_fake
-def _swa_bwd_fake(q, k, v, o, lse, dout, window, softmax_scale):
+def _swa_bwd_fake(q, k, v, o, lse, dout, window, softmax_scale, seq_start=None):
     return [q.new_empty(q.shape), q.new_empty(q.shape), q.new_empty(q.shape)]
 
 
 def _swa_setup(ctx, inputs, output):
-    q, k, v, window, scale = inputs
-    ctx.save_for_backward(q, k, v, output[0], output[1])
+    q, k, v, window, scale, seq_start = inputs
+    ctx.save_for_backward(q, k, v, output[0], output[1], *((seq_start,) if seq_start is not None else ()))
     ctx.cfg = (int(window), float(scale))
     ctx.set_materialize_grads(False)
 
 
 def _swa_autograd(ctx, grads):
-    q, k, v, o, lse = ctx.saved_tensors
+    q, k, v, o, lse = ctx.saved_tensors[:5]
+    seq_start = ctx.saved_tensors[5] if len(ctx.saved_tensors) == 6 else None
     dout = grads[0]
+    # one entry per input the caller passed: an omitted (None) seq_start is not an input of the autograd node
+    tail = (None, None, None) if seq_start is not None else (None, None)
     if dout is None:
-        return None, None, None, None, None
-    dq, dk, dv = torch.ops.lact_b200.swa_bwd(q, k, v, o, lse, dout.contiguous(), ctx.cfg[0], ctx.cfg[1])
-    return dq, dk, dv, None, None
+        return (None, None, None) + tail
+    dq, dk, dv = torch.ops.lact_b200.swa_bwd(q, k, v, o, lse, dout.contiguous(), ctx.cfg[0], ctx.cfg[1], seq_start)
+    return (dq, dk, dv) + tail
 
 
 _swa_fwd_op.register_autograd(_swa_autograd, setup_context=_swa_setup)
 
 
 def sliding_window_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window_size: Optional[int] = None,
-                             softmax_scale: Optional[float] = None) -> torch.Tensor:
+                             softmax_scale: Optional[float] = None,
+                             cu_seqlens: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention over the last `window_size` keys (the query's own position included), q, k, v and the
     result [b, l, n_heads, head_dim] bf16: what `flash_attn_func(q, k, v, causal=True, window_size=(window_size - 1,
     0))` computes at lact_llm/lact_model/layer_lact_swiglu.py:386-394 and
     minimal_implementations/causal_lact_with_sliding_window_attn.py:380-384 (`window_size=None`: all earlier keys).
-    head_dim 64 or 128.  Differentiable (dq, dk, dv by `lact_swa_bwd`)."""
+    head_dim 64 or 128.  Differentiable (dq, dk, dv by `lact_swa_bwd`).  `cu_seqlens` (int32 [n + 1], device): the batch
+    entry (b must be 1) is n sequences packed back to back, as for `flash_attn_varlen_func` (:371-385): no query sees
+    a key of an earlier sequence."""
     if not (q.is_cuda and k.is_cuda and v.is_cuda):
         raise ValueError("sliding_window_attention needs CUDA tensors (there is no CPU implementation)")
     assert q.dim() == 4 and q.shape == k.shape == v.shape, "q, k, v: [b, l, n_heads, head_dim], equal head counts"
@@ -359,4 +369,11 @@ def sliding_window_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, 
     if q.shape[3] not in (64, 128):
         raise ValueError("head_dim must be 64 or 128")
     scale = float(softmax_scale) if softmax_scale is not None else q.shape[3] ** -0.5
-    return torch.ops.lact_b200.swa_fwd(q, k, v, int(window_size) if window_size else 0, scale)[0]
+    seq_start = None
+    if cu_seqlens is not None:
+        if q.shape[0] != 1:
+            raise ValueError("packed sequences (cu_seqlens) need a batch of one")
+        cu = cu_seqlens.to(device=q.device, dtype=torch.int64)
+        # first token of its sequence, for every token (no host synchronisation: the output size is known)
+        seq_start = torch.repeat_interleave(cu[:-1], cu[1:] - cu[:-1], output_size=q.shape[1]).to(torch.int32).contiguous()
+    return torch.ops.lact_b200.swa_fwd(q, k, v, int(window_size) if window_size else 0, scale, seq_start)[0]

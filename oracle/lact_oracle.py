@@ -776,13 +776,17 @@ def out_epilogue(fw_x: torch.Tensor, weight: torch.Tensor, n_heads: int, scale_p
 
 
 
-def sliding_window_attention(q, k, v, window_size=None, softmax_scale=None, block: int = 1024):
+def sliding_window_attention(q, k, v, window_size=None, softmax_scale=None, block: int = 1024, cu_seqlens=None):
     """Causal attention over the keys (i - window_size, i] in fp32: the published semantics of
     `flash_attn_func(q, k, v, causal=True, window_size=(window_size - 1, 0))` (flash-attn 2.x: a query attends keys
     [i - left, i + right]), the call the reference makes at lact_llm/lact_model/layer_lact_swiglu.py:386-394 and
     minimal_implementations/causal_lact_with_sliding_window_attn.py:380-384.  flash-attn has no CPU implementation,
     so this restatement is checked against `torch.nn.functional.scaled_dot_product_attention` with the same band
     mask (tests/test_oracle_golden.py).  q, k, v: [b, l, h, d]; returns fp32 [b, l, h, d]."""
+    if cu_seqlens is not None:   # sequences packed into one batch entry (flash_attn_varlen_func): one by one
+        cu = [int(c) for c in cu_seqlens]
+        return torch.cat([sliding_window_attention(q[:, s0:s1], k[:, s0:s1], v[:, s0:s1], window_size, softmax_scale, block)
+                          for s0, s1 in zip(cu[:-1], cu[1:])], dim=1)
     b, l, h, d = q.shape
     scale = d ** -0.5 if softmax_scale is None else softmax_scale
     w = l if not window_size else int(window_size)

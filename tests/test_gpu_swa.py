@@ -120,3 +120,29 @@ def test_swa_backward_on_views_and_partial_graph(lo):
     (orc.sliding_window_attention(rq, rk, rv, 100) * dO.float()).sum().backward()
     assert orc.rel_max(dev.grad.float().cpu(), ref.grad) <= 3e-2
     assert orc.cosine(dev.grad.float().cpu(), ref.grad) >= 0.9995
+
+
+@pytest.mark.parametrize("window", [None, 150])
+def test_swa_packed_sequences_forward_and_backward(lo, window):
+    """cu_seqlens: sequences packed into one batch entry; boundaries inside and on tile edges, a one-token sequence."""
+    import lact_b200
+    from oracle import lact_oracle as orc
+    cu = torch.tensor([0, 100, 101, 384, 700, 1000], dtype=torch.int32)
+    l, h, d = 1000, 2, 128
+    g = torch.Generator().manual_seed(13)
+    q, k, v = (torch.randn(1, l, h, d, generator=g).to(BF16) for _ in range(3))
+    dO = torch.randn(1, l, h, d, generator=g).to(BF16)
+    leaves = [t.float().clone().requires_grad_(True) for t in (q, k, v)]
+    ref = orc.sliding_window_attention(*leaves, window, cu_seqlens=cu)
+    (ref * dO.float()).sum().backward()
+    cl = [t.cuda().clone().requires_grad_(True) for t in (q, k, v)]
+    o = lo.sliding_window_attention(*cl, window, cu_seqlens=cu.cuda())
+    o.backward(dO.cuda())
+    lact_b200.synchronize_and_check()
+    assert (o.detach().float().cpu() - ref.detach()).abs().max() / ref.detach().abs().max() <= 1.5e-2
+    for name, got, want in zip("qkv", cl, leaves):
+        a, b_ = got.grad.float().cpu(), want.grad
+        assert orc.rel_max(a, b_) <= 3e-2 and orc.cosine(a, b_) >= 0.9995, (name, orc.rel_max(a, b_), orc.cosine(a, b_))
+    with pytest.raises(ValueError):
+        lo.sliding_window_attention(torch.cat([cl[0]] * 2).detach(), torch.cat([cl[1]] * 2).detach(),
+                                    torch.cat([cl[2]] * 2).detach(), window, cu_seqlens=cu.cuda())
