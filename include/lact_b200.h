@@ -235,11 +235,14 @@ int lact_qkv_prologue(const void *xq, const void *xk, const void *xv, int64_t ld
  * (layer_lact_swiglu.py:417-446: heads merged back, re-split into attention heads of rope_head_dim features, rotated by
  * fla.modules.RotaryEmbedding in its non-interleaved layout, split into fast-weight heads again).  cos, sin: bf16
  * [n_positions][rope_head_dim / 2] (the module's cached tables, in the activations' dtype); token t of every sequence
- * uses row seqlen_offset + t.  rope_head_dim: a power of two in [32, 1024] that divides d.  v is not rotated. */
+ * uses row seqlen_offset + t.  rope_head_dim: a power of two in [32, 1024] that divides d.  v is not rotated.
+ * seq_start: NULL, or for b = 1 an int32 [s] device array with the first token of the packed sequence every token belongs
+ * to (the layer's cu_seqlens, :434): token t then uses row seqlen_offset + t - seq_start[t]. */
 int lact_qkv_prologue_rope(const void *xq, const void *xk, const void *xv, int64_t ld_q, int64_t ld_k, int64_t ld_v,
                            int64_t bs_q, int64_t bs_k, int64_t bs_v, void *q, void *k, void *v, int64_t b, int64_t s,
                            int64_t n_heads, int64_t d, int32_t qkv_silu, int32_t v_silu, const void *cos, const void *sin,
-                           int64_t rope_head_dim, int64_t n_positions, int64_t seqlen_offset, void *stream);
+                           int64_t rope_head_dim, int64_t n_positions, int64_t seqlen_offset, const int32_t *seq_start,
+                           void *stream);
 
 /* Per-token learning rates and momentum of the LLM layer (layer_lact_swiglu.py:463-480, 245-249):
  * lr = softplus(float(lr_proj) + base_lr_inv), lr_proj [b][s][n_heads * 3] (row stride proj_ld) -> lr0, lr1, lr2
@@ -283,7 +286,7 @@ int lact_qkv_prologue_bwd(const void *xq, const void *xk, const void *xv, int64_
                           int64_t bs_q, int64_t bs_k, int64_t bs_v, const void *dq, const void *dk, const void *dv,
                           void *dxq, void *dxk, void *dxv, int64_t b, int64_t s, int64_t n_heads, int64_t d,
                           int32_t qkv_silu, int32_t v_silu, const void *cos, const void *sin, int64_t rope_head_dim,
-                          int64_t n_positions, int64_t seqlen_offset, void *stream);
+                          int64_t n_positions, int64_t seqlen_offset, const int32_t *seq_start, void *stream);
 
 /* Backward of lact_out_epilogue: dx [(b n_heads), s, d] and dgate [b, s, n_heads * d] (bf16, written; dgate NULL iff
  * gate_proj NULL), and per-block partial sums of the norm weight's gradient, dw_partial [lact_out_epilogue_bwd_blocks()][d]

@@ -96,7 +96,7 @@ def _declare(lib: C.CDLL) -> None:
                                            i32, i64, i64, i32, i64, i64, i64, i64, vp, vp]
     lib.lact_qkv_prologue.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, vp, vp, vp, i64, i64, i64, i64, i32, i32, vp]
     lib.lact_qkv_prologue_rope.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, vp, vp, vp, i64, i64, i64, i64, i32, i32,
-                                           vp, vp, i64, i64, i64, vp]
+                                           vp, vp, i64, i64, i64, vp, vp]
     lib.lact_qkv_prologue_rope.restype = C.c_int
     lib.lact_lr_prologue.argtypes = [vp, i32, i64, f32, vp, i32, i64, vp, vp, vp, vp, i64, i64, i64, vp]
     lib.lact_out_epilogue.argtypes = [vp, vp, vp, i64, vp, i64, vp, i64, i64, i64, i64, i64, f32, vp]
@@ -106,7 +106,7 @@ def _declare(lib: C.CDLL) -> None:
     lib.lact_renorm_bwd.argtypes = [vp, vp, i32, vp, vp, vp, vp, vp, i64, i64, i32, vp]
     lib.lact_ns_norm_bwd.argtypes = [vp, vp, vp, i64, i64, vp]
     lib.lact_momentum_bwd_slices.restype = C.c_int
-    lib.lact_qkv_prologue_bwd.argtypes = [vp] * 3 + [i64] * 6 + [vp] * 6 + [i64] * 4 + [i32, i32, vp, vp, i64, i64, i64, vp]
+    lib.lact_qkv_prologue_bwd.argtypes = [vp] * 3 + [i64] * 6 + [vp] * 6 + [i64] * 4 + [i32, i32, vp, vp, i64, i64, i64, vp, vp]
     lib.lact_out_epilogue_bwd_blocks.restype = C.c_int
     lib.lact_out_epilogue_bwd.argtypes = [vp, vp, vp, i64, vp, i64, vp, vp, vp, i64, i64, i64, i64, f32, vp]
     lib.lact_swa_fwd.argtypes = [vp, vp, vp, vp] + [i64] * 13 + [f32, vp, vp, vp, vp]

@@ -1662,8 +1662,9 @@ static int qkv_prologue_impl(const void* xq, const void* xk, const void* xv, int
                              int64_t bs_q, int64_t bs_k, int64_t bs_v, void* q, void* k, void* v, int64_t b, int64_t s,
                              int64_t n_heads, int64_t d, int32_t qkv_silu, int32_t v_silu, const void* cos,
                              const void* sin, int64_t rope_head_dim, int64_t n_positions, int64_t seqlen_offset,
-                             void* stream) {
+                             const int32_t* seq_start, void* stream) {
   if (!xq || !xk || !xv || !q || !k || !v) return LACT_ERR_NULL;
+  if (seq_start != nullptr && (b != 1 || rope_head_dim == 0)) return LACT_ERR_CONFIG;
   LACT_TRY(check_device());
   if (b < 1 || s < 1 || n_heads < 1 || d < 8 || d > 1024 || (d % 8) != 0) return LACT_ERR_SHAPE;
   if (b * s * n_heads > (1ll << 40) || b > 65535 || s > (1ll << 30)) return LACT_ERR_SHAPE;
@@ -1699,6 +1700,7 @@ static int qkv_prologue_impl(const void* xq, const void* xk, const void* xv, int
     a.sin = static_cast<const bf16*>(sin);
     a.rope_hd = static_cast<int32_t>(rope_head_dim);
     a.pos0 = static_cast<int32_t>(seqlen_offset);
+    a.seq_start = seq_start;
   }
   const int64_t rows = b * s * n_heads;
   KernelScope scope(kClsOther, static_cast<cudaStream_t>(stream));
@@ -1727,8 +1729,9 @@ int lact_qkv_prologue_bwd(const void* xq, const void* xk, const void* xv, int64_
                           int64_t bs_q, int64_t bs_k, int64_t bs_v, const void* dq, const void* dk, const void* dv,
                           void* dxq, void* dxk, void* dxv, int64_t b, int64_t s, int64_t n_heads, int64_t d,
                           int32_t qkv_silu, int32_t v_silu, const void* cos, const void* sin, int64_t rope_head_dim,
-                          int64_t n_positions, int64_t seqlen_offset, void* stream) {
+                          int64_t n_positions, int64_t seqlen_offset, const int32_t* seq_start, void* stream) {
   if (!xq || !xk || !xv || !dxq || !dxk || !dxv) return LACT_ERR_NULL;
+  if (seq_start != nullptr && (b != 1 || rope_head_dim == 0)) return LACT_ERR_CONFIG;
   LACT_TRY(check_device());
   if (b < 1 || s < 1 || n_heads < 1 || d < 8 || d > 1024 || (d % 8) != 0) return LACT_ERR_SHAPE;
   if (b * s * n_heads > (1ll << 40) || b > 65535 || s > (1ll << 30)) return LACT_ERR_SHAPE;
@@ -1764,6 +1767,7 @@ int lact_qkv_prologue_bwd(const void* xq, const void* xk, const void* xv, int64_
     a.sin = static_cast<const bf16*>(sin);
     a.rope_hd = static_cast<int32_t>(rope_head_dim);
     a.pos0 = static_cast<int32_t>(seqlen_offset);
+    a.seq_start = seq_start;
   }
   const int64_t rows = b * s * n_heads;
   KernelScope scope(kClsOther, static_cast<cudaStream_t>(stream));
@@ -1835,16 +1839,17 @@ int lact_qkv_prologue(const void* xq, const void* xk, const void* xv, int64_t ld
                       int64_t bs_q, int64_t bs_k, int64_t bs_v, void* q, void* k, void* v, int64_t b, int64_t s,
                       int64_t n_heads, int64_t d, int32_t qkv_silu, int32_t v_silu, void* stream) {
   return qkv_prologue_impl(xq, xk, xv, ld_q, ld_k, ld_v, bs_q, bs_k, bs_v, q, k, v, b, s, n_heads, d, qkv_silu, v_silu,
-                           nullptr, nullptr, 0, 0, 0, stream);
+                           nullptr, nullptr, 0, 0, 0, nullptr, stream);
 }
 
 int lact_qkv_prologue_rope(const void* xq, const void* xk, const void* xv, int64_t ld_q, int64_t ld_k, int64_t ld_v,
                            int64_t bs_q, int64_t bs_k, int64_t bs_v, void* q, void* k, void* v, int64_t b, int64_t s,
                            int64_t n_heads, int64_t d, int32_t qkv_silu, int32_t v_silu, const void* cos, const void* sin,
-                           int64_t rope_head_dim, int64_t n_positions, int64_t seqlen_offset, void* stream) {
+                           int64_t rope_head_dim, int64_t n_positions, int64_t seqlen_offset, const int32_t* seq_start,
+                           void* stream) {
   if (rope_head_dim == 0) return LACT_ERR_SHAPE;
   return qkv_prologue_impl(xq, xk, xv, ld_q, ld_k, ld_v, bs_q, bs_k, bs_v, q, k, v, b, s, n_heads, d, qkv_silu, v_silu,
-                           cos, sin, rope_head_dim, n_positions, seqlen_offset, stream);
+                           cos, sin, rope_head_dim, n_positions, seqlen_offset, seq_start, stream);
 }
 
 int lact_lr_prologue(const void* lr_proj, int32_t proj_dtype, int64_t proj_ld, float base_lr_inv, const void* mom_logits,

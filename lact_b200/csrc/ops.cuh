@@ -1188,6 +1188,7 @@ struct PrologueArgs {
   // in fp32 from the bf16 inputs, rounded once (the arithmetic of the rotary kernel the reference calls).
   const bf16 *cos, *sin;  // [positions][rope_hd / 2], bf16 (the reference caches them in the activations' dtype)
   int32_t rope_hd, pos0;  // position of token 0
+  const int32_t* seq_start;  // optional [s] (b = 1): packed sequences, token t sits at position pos0 + t - seq_start[t]
 };
 
 // One warp per (batch, token, head): y = silu(x) rounded to bf16, then y / (bf16(||y||) + 1e-5) with the norm, the
@@ -1244,7 +1245,7 @@ __global__ void __launch_bounds__(256, ROPE ? (NCH <= 2 ? 4 : 2) : (NCH <= 2 ? 8
       // partner of a feature sits rope_hd / 2 columns away, i.e. rope_hd / 16 lanes away (same 16-byte chunk index)
       // or, from rope_hd = 512 up, rope_hd / 512 chunks away in the same lane
       const int half = a.rope_hd >> 1;
-      const int64_t trow = static_cast<int64_t>(a.pos0 + tok) * half;
+      const int64_t trow = static_cast<int64_t>(a.pos0 + tok - (a.seq_start != nullptr ? a.seq_start[tok] : 0)) * half;
 #pragma unroll
       for (int c = 0; c < NCH; ++c)
 #pragma unroll
@@ -1415,6 +1416,7 @@ struct PrologueBwdArgs {
   int32_t silu[3], l2norm[3];
   const bf16 *cos, *sin;
   int32_t rope_hd, pos0;
+  const int32_t* seq_start;  // as in the forward
 };
 template <int NCH, bool ROPE>
 __global__ void __launch_bounds__(256, (ROPE || NCH > 1) ? 2 : 4) qkv_prologue_bwd_kernel(const PrologueBwdArgs a) {
@@ -1450,7 +1452,7 @@ __global__ void __launch_bounds__(256, (ROPE || NCH > 1) ? 2 : 4) qkv_prologue_b
     if (ROPE && t < 2) {
       // dy = R^T dz: first half dz cos + partner sin, second half dz cos - partner sin (partner as in the forward)
       const int half = a.rope_hd >> 1;
-      const int64_t trow = static_cast<int64_t>(a.pos0 + tok) * half;
+      const int64_t trow = static_cast<int64_t>(a.pos0 + tok - (a.seq_start != nullptr ? a.seq_start[tok] : 0)) * half;
       float other[NCH][8];
 #pragma unroll
       for (int c = 0; c < NCH; ++c)

@@ -33,10 +33,11 @@ class _QkvPrologue(torch.autograd.Function):
     """Forward: the fused kernel.  Backward: `lact_qkv_prologue_bwd` on the saved projections (rotation transposed,
     l2-norm and SiLU differentiated in one pass per row)."""
     @staticmethod
-    def forward(ctx, xq, xk, xv, num_heads, qkv_silu, v_silu, cos, sin, rope_hd, offset):
+    def forward(ctx, xq, xk, xv, num_heads, qkv_silu, v_silu, cos, sin, rope_hd, offset, seq_start=None):
         ctx.save_for_backward(xq, xk, xv, *((cos, sin) if cos is not None else ()))
         ctx.cfg = (num_heads, qkv_silu, v_silu, rope_hd, offset)
-        return _qkv_prologue_fwd(xq, xk, xv, num_heads, qkv_silu, v_silu, cos, sin, rope_hd, offset)
+        ctx.seq_start = seq_start   # int32 index tensor, no gradient
+        return _qkv_prologue_fwd(xq, xk, xv, num_heads, qkv_silu, v_silu, cos, sin, rope_hd, offset, seq_start)
 
     @staticmethod
     def backward(ctx, dq, dk, dv):
@@ -55,8 +56,15 @@ class _QkvPrologue(torch.autograd.Function):
                 outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(), b, s, n_h, d, int(qkv_silu), int(v_silu),
                 cos.data_ptr() if cos is not None else None, sin.data_ptr() if sin is not None else None,
                 int(rope_hd) if cos is not None else 0, cos.shape[0] if cos is not None else 0, int(offset),
-                L.stream_ptr()), "lact_qkv_prologue_bwd")
-        return (*[o.to(x.dtype) for o, x in zip(outs, saved[:3])], None, None, None, None, None, None, None)
+                ctx.seq_start.data_ptr() if ctx.seq_start is not None else None, L.stream_ptr()), "lact_qkv_prologue_bwd")
+        return (*[o.to(x.dtype) for o, x in zip(outs, saved[:3])], None, None, None, None, None, None, None, None)
+
+
+def _seq_start(cu_seqlens: torch.Tensor, n_tokens: int, device) -> torch.Tensor:
+    """int32 [n_tokens]: for every token of a packed batch entry, the first token of its sequence (no host
+    synchronisation: the output size is known)."""
+    cu = cu_seqlens.to(device=device, dtype=torch.int64)
+    return torch.repeat_interleave(cu[:-1], cu[1:] - cu[:-1], output_size=n_tokens).to(torch.int32).contiguous()
 
 
 def _rows(t: torch.Tensor, name: str) -> torch.Tensor:
@@ -75,7 +83,7 @@ def rotary_tables(head_dim: int, n_positions: int, base: float = 500000.0, devic
     return torch.cos(freqs).to(dtype), torch.sin(freqs).to(dtype)
 
 
-def _qkv_prologue_fwd(xq, xk, xv, num_heads, qkv_silu, v_silu, cos, sin, rope_hd, offset):
+def _qkv_prologue_fwd(xq, xk, xv, num_heads, qkv_silu, v_silu, cos, sin, rope_hd, offset, seq_start=None):
     xq, xk, xv = _rows(xq, "xq"), _rows(xk, "xk"), _rows(xv, "xv")
     b, s, nd = xq.shape
     d = nd // num_heads
@@ -92,18 +100,21 @@ def _qkv_prologue_fwd(xq, xk, xv, num_heads, qkv_silu, v_silu, cos, sin, rope_hd
                                                xv.stride(1), xq.stride(0), xk.stride(0), xv.stride(0), q.data_ptr(),
                                                k.data_ptr(), v.data_ptr(), b, s, num_heads, d, int(bool(qkv_silu)),
                                                int(bool(v_silu)), cos.data_ptr(), sin.data_ptr(), int(rope_hd),
-                                               cos.shape[0], int(offset), L.stream_ptr()), "lact_qkv_prologue_rope")
+                                               cos.shape[0], int(offset),
+                                               seq_start.data_ptr() if seq_start is not None else None,
+                                               L.stream_ptr()), "lact_qkv_prologue_rope")
     return q, k, v
 
 
 def qkv_prologue(xq: torch.Tensor, xk: torch.Tensor, xv: torch.Tensor, num_heads: int, qkv_silu: bool = True,
                  no_v_silu: bool = False, rotary: Optional[Tuple[torch.Tensor, torch.Tensor, int]] = None,
-                 seqlen_offset: int = 0):
+                 seqlen_offset: int = 0, cu_seqlens: Optional[torch.Tensor] = None):
     """fast_q, fast_k, fast_v of layer_lact_swiglu.py:399-446 in one pass: `[b, s, (n_h d)] -> [(b n_h), s, d]`, SiLU
     on q, k (and v unless `no_v_silu`), per-head l2_norm of q and k (ttt_operation.py:19-26) and, when `rotary` =
     (cos, sin, attention_head_dim) is given (`ttt_nope` off), the rotary embedding of q and k over attention heads of
     that size (tables as `rotary_tables` / fla.modules.RotaryEmbedding build them, bf16 [positions, head_dim / 2]).
-    Inputs may be views of a fused projection.  Differentiable (see the module docstring)."""
+    Inputs may be views of a fused projection.  Differentiable (see the module docstring).  `cu_seqlens` (with
+    `rotary`, batch of one): sequences packed back to back, positions restart at every sequence start (:434)."""
     if not (xq.is_cuda and xk.is_cuda and xv.is_cuda):
         raise ValueError("qkv_prologue needs CUDA tensors (there is no CPU implementation)")
     assert xq.shape == xk.shape == xv.shape and xq.dim() == 3 and xq.shape[2] % num_heads == 0
@@ -113,10 +124,16 @@ def qkv_prologue(xq: torch.Tensor, xk: torch.Tensor, xv: torch.Tensor, num_heads
         cos, sin, rope_hd = rotary
         assert cos.dtype == BF16 and sin.dtype == BF16 and cos.shape == sin.shape and cos.shape[1] * 2 == rope_hd
         cos, sin = cos.contiguous(), sin.contiguous()
+    seq_start = None
+    if cu_seqlens is not None and rotary is not None:
+        if xq.shape[0] != 1:
+            raise ValueError("packed sequences (cu_seqlens) need a batch of one")
+        seq_start = _seq_start(cu_seqlens, xq.shape[1], xq.device)
     if torch.is_grad_enabled() and any(t.requires_grad for t in (xq, xk, xv)):
         return _QkvPrologue.apply(xq, xk, xv, num_heads, bool(qkv_silu), not no_v_silu, cos, sin, int(rope_hd),
-                                  int(seqlen_offset))
-    return _qkv_prologue_fwd(xq, xk, xv, num_heads, bool(qkv_silu), not no_v_silu, cos, sin, int(rope_hd), int(seqlen_offset))
+                                  int(seqlen_offset), seq_start)
+    return _qkv_prologue_fwd(xq, xk, xv, num_heads, bool(qkv_silu), not no_v_silu, cos, sin, int(rope_hd),
+                             int(seqlen_offset), seq_start)
 
 
 class _LrPrologue(torch.autograd.Function):
@@ -373,7 +390,5 @@ def sliding_window_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, 
     if cu_seqlens is not None:
         if q.shape[0] != 1:
             raise ValueError("packed sequences (cu_seqlens) need a batch of one")
-        cu = cu_seqlens.to(device=q.device, dtype=torch.int64)
-        # first token of its sequence, for every token (no host synchronisation: the output size is known)
-        seq_start = torch.repeat_interleave(cu[:-1], cu[1:] - cu[:-1], output_size=q.shape[1]).to(torch.int32).contiguous()
+        seq_start = _seq_start(cu_seqlens, q.shape[1], q.device)
     return torch.ops.lact_b200.swa_fwd(q, k, v, int(window_size) if window_size else 0, scale, seq_start)[0]

@@ -723,10 +723,15 @@ def rotary(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, seqlen_offset:
 
 
 def qkv_prologue_rope(xq, xk, xv, n_heads: int, rope_head_dim: int, cos, sin, seqlen_offset: int = 0,
-                      qkv_silu: bool = True, v_silu: bool = True, policy: str = "ref"):
+                      qkv_silu: bool = True, v_silu: bool = True, policy: str = "ref", cu_seqlens=None):
     """`qkv_prologue` followed by the rotary embedding of fast q and k as the layer applies it when `ttt_nope` is off
     (lact_llm/lact_model/layer_lact_swiglu.py:417-446): fast-weight heads merged back to [b, s, n_h * d], re-split
     into attention heads of `rope_head_dim` features, rotated, and split into fast-weight heads again."""
+    if cu_seqlens is not None:   # packed sequences (batch of one): positions restart at every sequence start
+        cu = [int(c) for c in cu_seqlens]
+        parts = [qkv_prologue_rope(xq[:, a:e], xk[:, a:e], xv[:, a:e], n_heads, rope_head_dim, cos, sin, seqlen_offset,
+                                   qkv_silu, v_silu, policy) for a, e in zip(cu[:-1], cu[1:])]
+        return tuple(torch.cat([p[i] for p in parts], dim=1) for i in range(3))
     q, k, v = qkv_prologue(xq, xk, xv, n_heads, qkv_silu, v_silu)
     b, s, nd = xq.shape
     d = nd // n_heads

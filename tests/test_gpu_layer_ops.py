@@ -226,3 +226,28 @@ def test_layer_passes_are_differentiable(lb, orc):
     for got, want, what in zip(C4, ref, ("d fw_x", "d weight", "d scale_proj", "d o")):
         assert got.grad is not None, what
         assert orc.rel_max(got.grad.float().cpu(), want) <= 2e-2 and orc.cosine(got.grad.float().cpu(), want) >= 0.999, what
+
+
+def test_rotary_prologue_with_packed_sequences(lb, orc):
+    """cu_seqlens: positions restart at every sequence start (layer_lact_swiglu.py:434), forward and gradients."""
+    from lact_b200 import layer_ops as lo
+    b, s, n_h, d, hd = 1, 300, 2, 128, 64
+    cu = torch.tensor([0, 70, 71, 200, 300], dtype=torch.int32)
+    g = torch.Generator().manual_seed(21)
+    xs = [torch.randn(b, s, n_h * d, generator=g).to(BF16) for _ in range(3)]
+    dz = [torch.randn(b * n_h, s, d, generator=g).to(BF16) for _ in range(3)]
+    cos, sin = orc.rotary_tables(hd, s)
+    leaves = [x.float().clone().requires_grad_(True) for x in xs]
+    ref = orc.qkv_prologue_rope(*leaves, n_h, hd, cos, sin, policy="fused", cu_seqlens=cu)
+    sum((r.float() * z.float()).sum() for r, z in zip(ref, dz)).backward()
+    cl = [x.cuda().clone().requires_grad_(True) for x in xs]
+    got = lo.qkv_prologue(*cl, n_h, rotary=(cos.cuda(), sin.cuda(), hd), cu_seqlens=cu.cuda())
+    torch.autograd.backward(got, [z.cuda() for z in dz])
+    for a, r in zip(got, ref):
+        assert orc.rel_max(a.detach().float().cpu(), r.detach().float()) <= 2e-2
+    for a, r in zip(cl, leaves):
+        assert orc.rel_max(a.grad.float().cpu(), r.grad) <= 3e-2 and orc.cosine(a.grad.float().cpu(), r.grad) >= 0.999
+    # without cu_seqlens the later sequences get different positions: the outputs must differ there
+    plain = lo.qkv_prologue(*[c.detach() for c in cl], n_h, rotary=(cos.cuda(), sin.cuda(), hd))
+    assert not torch.equal(plain[0][:, 100:], got[0][:, 100:].detach())
+    assert torch.equal(plain[0][:, :70], got[0][:, :70].detach())
