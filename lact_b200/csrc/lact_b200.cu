@@ -912,7 +912,7 @@ static int launch_ns_bwd_fused(const NsTrace* tr, const bf16* const* du, int ngr
 // 4-D map (feature, token, head, batch) of a [b][l][h][d] bf16 activation whose token / batch strides are free
 // (views of a fused projection) and whose heads are adjacent; box {64, 128, 1, 1}, 128-byte swizzle.
 int encode_map_heads(CUtensorMap* map, const void* ptr, int64_t b, int64_t l, int64_t h, int64_t d, int64_t ts,
-                     int64_t bs) {
+                     int64_t bs, uint32_t box_rows = 128) {
   EncodeFn fn = get_encode_fn();
   if (fn == nullptr) return LACT_ERR_CUDA;
   if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0 || (ts % 8) != 0 || (bs % 8) != 0 || ts < h * d) return LACT_ERR_SHAPE;
@@ -920,7 +920,7 @@ int encode_map_heads(CUtensorMap* map, const void* ptr, int64_t b, int64_t l, in
                         static_cast<cuuint64_t>(b)};
   cuuint64_t strides[3] = {static_cast<cuuint64_t>(ts) * 2, static_cast<cuuint64_t>(d) * 2,
                            static_cast<cuuint64_t>(b > 1 ? bs : ts * l) * 2};
-  cuuint32_t box[4] = {64, 128, 1, 1};
+  cuuint32_t box[4] = {64, box_rows, 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -1984,6 +1984,10 @@ int lact_swa_bwd(const void* q, const void* k, const void* v, const void* o, con
   LACT_TRY(encode_map_heads(&a.k, k, b, l, n_heads, d, k_ts, k_bs));
   LACT_TRY(encode_map_heads(&a.v, v, b, l, n_heads, d, v_ts, v_bs));
   LACT_TRY(encode_map_heads(&a.dout, dout, b, l, n_heads, d, do_ts, do_bs));
+  LACT_TRY(encode_map_heads(&a.q64, q, b, l, n_heads, d, q_ts, q_bs, 64));
+  LACT_TRY(encode_map_heads(&a.k64, k, b, l, n_heads, d, k_ts, k_bs, 64));
+  LACT_TRY(encode_map_heads(&a.v64, v, b, l, n_heads, d, v_ts, v_bs, 64));
+  LACT_TRY(encode_map_heads(&a.dout64, dout, b, l, n_heads, d, do_ts, do_bs, 64));
   a.lse = static_cast<const float*>(lse);
   a.delta = static_cast<const float*>(delta);
   a.seq_start = seq_start;
