@@ -5,14 +5,15 @@
 //                            (128 x d, tensor memory, double-buffered; NOT accumulated across tiles);
 //   warps 2-9  softmax:      two threads per query row (a row is a tensor-memory lane; the two warps that may read a
 //                            lane quarter split the row: 64 keys of S and half of the output features each, and
-//                            agree on the row maximum through shared memory): two passes over S (max, then
-//                            exp2 / sum), the bf16 probabilities go to shared memory in the swizzled K-major layout
+//                            swap their row maxima through shared memory at a named barrier): the 64 scores are read
+//                            once into registers (max, then exp2 / sum), the bf16 probabilities go to shared memory in the swizzled K-major layout
 //                            the second product reads as its A operand, and the running output row lives in
 //                            registers: O <- O * exp2(m_old - m_new) + O_t, folded one tile behind so that the
 //                            products of tile t + 1 overlap the softmax of tile t.  Two warps per scheduler hide the
 //                            fixed latencies one warp alone sits out.
 // Key and value tiles share one shared-memory layout ([128 rows][64 features] boxes, 128-byte swizzle): the first
-// product reads it K-major (features = k), the second MN-major (keys = k).  Every wait is bounded.
+// product reads it K-major (features = k), the second MN-major (keys = k).  Every mbarrier wait is bounded; the named
+// barriers of the row pairs are reached by every softmax thread in every iteration, whatever its waits returned.
 #pragma once
 #include "umma_gemm.cuh"
 
@@ -66,9 +67,7 @@ __global__ void __launch_bounds__(320, 1) swa_fwd_kernel(const __grid_constant__
   uint64_t* p_full = bars + 11;       // [2]  8 arrivals
   uint64_t* pv_done = bars + 13;      // [2]  frees the value stage and the probability buffer, publishes O_t
   uint64_t* o_empty = bars + 15;      // [2]  8 arrivals
-  uint64_t* x_written = bars + 17;    // [4]  per lane quarter: both warps of the quarter have written their value
-  uint64_t* x_read = bars + 21;       // [4]  ... and read the partner's
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 25);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   float* xch = reinterpret_cast<float*>(aligned + SM::kBars + 256);   // [2 halves][128 rows]
 
@@ -84,10 +83,6 @@ __global__ void __launch_bounds__(320, 1) swa_fwd_kernel(const __grid_constant__
       mbar_init(&p_full[s], 8);
       mbar_init(&pv_done[s], 1);
       mbar_init(&o_empty[s], 8);
-    }
-    for (int qd = 0; qd < 4; ++qd) {
-      mbar_init(&x_written[qd], 2);
-      mbar_init(&x_read[qd], 2);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -189,20 +184,15 @@ __global__ void __launch_bounds__(320, 1) swa_fwd_kernel(const __grid_constant__
     float O[OC];
 #pragma unroll
     for (int j = 0; j < OC; ++j) O[j] = 0.f;
-    uint32_t xphase = 0;   // exchanges done so far (two barrier phases each)
-    // the two threads of a row agree on a value through shared memory (bounded mbarrier waits, no bar.sync: a thread
-    // that gave up must not leave its partner waiting for ever)
-    auto exchange = [&](float mine, float& other) -> bool {
+    // the two threads of a row swap a value through shared memory; the two warps of a lane quarter meet at a named
+    // barrier of their own.  A named barrier has no time limit, so EVERY softmax thread runs every exchange of every
+    // iteration, also after one of its bounded waits has run out (it then skips the work, never the barriers).
+    auto exchange = [&](float mine) -> float {
       xch[half * 128 + r] = mine;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&x_written[quarter]);
-      if (!mbar_wait(&x_written[quarter], xphase & 1, abort_flag)) return false;
-      other = xch[(half ^ 1) * 128 + r];
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&x_read[quarter]);
-      if (!mbar_wait(&x_read[quarter], xphase & 1, abort_flag)) return false;
-      ++xphase;
-      return true;
+      named_barrier_sync(1 + quarter, 64);
+      const float other = xch[(half ^ 1) * 128 + r];
+      named_barrier_sync(1 + quarter, 64);
+      return other;
     };
     auto fold = [&](int u, float alpha) -> bool {   // O <- O * alpha + O_u (this thread's features)
       const int ob = u & 1;
@@ -222,73 +212,70 @@ __global__ void __launch_bounds__(320, 1) swa_fwd_kernel(const __grid_constant__
       if (lane == 0) mbar_arrive(&o_empty[ob]);
       return true;
     };
-    for (int t = 0; t < T && !failed; ++t) {
+    for (int t = 0; t < T; ++t) {
       const int sb = t & 1;
       const int kv0 = kv_lo + t * 128;
-      if (!mbar_wait(&s_full[sb], (t >> 1) & 1, abort_flag)) { failed = true; break; }
-      tc_fence_after();
+      if (!failed && !mbar_wait(&s_full[sb], (t >> 1) & 1, abort_flag)) {
+        failed = true;
+        *abort_flag = 1;
+      }
       // every (row, key) pair of the tile inside the band and the sequence: no masks
       const bool interior = kv0 + 127 <= q0 && kv0 >= q0 + 127 - (window - 1) && kv0 + 127 < a.L && kv0 >= tile_start;
       const int c0 = half * 64;                                // this thread's first key column of the tile
       const int j_hi = (qi < a.L - 1 ? qi : a.L - 1) - kv0;   // last / first column of the tile this row may see
       const int j_lo = (qi - (window - 1) > row_start ? qi - (window - 1) : row_start) - kv0;
       const uint32_t s_addr = tmem + lane_off + sb * 128 + c0;
-      uint32_t ba[32], bb[32];
+      uint32_t ba[32], bb[32];   // this thread's 64 scores: read once, kept across the exchange of the row maximum
       float mx = -INFINITY;
-      auto max_chunk = [&](const uint32_t (&bits)[32], int c) {
+      if (!failed) {
+        tc_fence_after();
+        tmem_ld32(s_addr, ba);
+        tmem_ld32(s_addr + 32, bb);
+        tmem_ld_wait();
         if (interior) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(bits[j]));
+          for (int j = 0; j < 32; ++j) mx = fmaxf(mx, fmaxf(__uint_as_float(ba[j]), __uint_as_float(bb[j])));
         } else {
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (c + j >= j_lo && c + j <= j_hi) mx = fmaxf(mx, __uint_as_float(bits[j]));
+          for (int j = 0; j < 32; ++j) {
+            if (c0 + j >= j_lo && c0 + j <= j_hi) mx = fmaxf(mx, __uint_as_float(ba[j]));
+            if (c0 + 32 + j >= j_lo && c0 + 32 + j <= j_hi) mx = fmaxf(mx, __uint_as_float(bb[j]));
+          }
         }
-      };
-      // chunk c + 1 is requested before chunk c is processed (tensor-memory loads are asynchronous)
-      tmem_ld32(s_addr, ba);
-      tmem_ld_wait();
-      tmem_ld32(s_addr + 32, bb);
-      max_chunk(ba, c0);
-      tmem_ld_wait();
-      tmem_ld32(s_addr, ba);   // first chunk of the second pass
-      max_chunk(bb, c0 + 32);
-      float mx_other;
-      if (!exchange(mx, mx_other)) { failed = true; break; }
-      mx = fmaxf(mx, mx_other);
+      }
+      mx = fmaxf(mx, exchange(mx));
+      if (failed) continue;
       const float m_new = fmaxf(m, mx * a.scale_log2);
       const float alpha = m_new == -INFINITY ? 1.f : fast_exp2(m - m_new);
       const float shift = m_new == -INFINITY ? 0.f : m_new;
       float sum = 0.f;
       const uint32_t p_row = base + SM::kP + sb * SM::kPTile + half * kBox + r * 128;   // this thread's 64-key panel
-      auto exp_chunk = [&](const uint32_t (&bits)[32], int c) {
-        float p[32];
-        if (interior) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) p[j] = fast_exp2(fmaf(__uint_as_float(bits[j]), a.scale_log2, -shift));
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            p[j] = (c + j >= j_lo && c + j <= j_hi) ? fast_exp2(fmaf(__uint_as_float(bits[j]), a.scale_log2, -shift)) : 0.f;
-        }
-#pragma unroll
-        for (int j = 0; j < 32; ++j) sum += p[j];
+      auto exp_chunk = [&](const uint32_t (&bits)[32], int c, const bool masked) {
         const uint32_t unit0 = (c & 63) >> 3;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
+          float p[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int j = g * 8 + e;
+            const float x = fast_exp2(fmaf(__uint_as_float(bits[j]), a.scale_log2, -shift));
+            p[e] = (!masked || (c + j >= j_lo && c + j <= j_hi)) ? x : 0.f;
+            sum += p[e];
+          }
           const uint32_t addr = p_row + (((unit0 + g) ^ (r & 7)) << 4);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pack_bf16x2(p[g * 8 + 0], p[g * 8 + 1])),
-                       "r"(pack_bf16x2(p[g * 8 + 2], p[g * 8 + 3])), "r"(pack_bf16x2(p[g * 8 + 4], p[g * 8 + 5])),
-                       "r"(pack_bf16x2(p[g * 8 + 6], p[g * 8 + 7]))
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pack_bf16x2(p[0], p[1])),
+                       "r"(pack_bf16x2(p[2], p[3])), "r"(pack_bf16x2(p[4], p[5])), "r"(pack_bf16x2(p[6], p[7]))
                        : "memory");
         }
       };
-      tmem_ld_wait();
-      tmem_ld32(s_addr + 32, bb);
-      exp_chunk(ba, c0);
-      tmem_ld_wait();
-      exp_chunk(bb, c0 + 32);
-      // S has been read twice and is free; the probabilities are visible to the tensor core
+      if (interior) {   // (two copies of the loop: the mask tests vanish from this one)
+        exp_chunk(ba, c0, false);
+        exp_chunk(bb, c0 + 32, false);
+      } else {
+        exp_chunk(ba, c0, true);
+        exp_chunk(bb, c0 + 32, true);
+      }
+      // S has been read and is free; the probabilities are visible to the tensor core
       tc_fence_before();
       fence_async_proxy();
       __syncwarp();
@@ -298,12 +285,14 @@ __global__ void __launch_bounds__(320, 1) swa_fwd_kernel(const __grid_constant__
       }
       l = l * alpha + sum;   // this thread's share of the row sum (both shares see the same alphas)
       m = m_new;
-      if (t >= 1 && !fold(t - 1, a_prev)) { failed = true; break; }
+      if (t >= 1 && !fold(t - 1, a_prev)) {
+        failed = true;
+        *abort_flag = 1;
+      }
       a_prev = alpha;
     }
     if (!failed && T > 0 && !fold(T - 1, a_prev)) failed = true;
-    float l_other = 0.f;
-    if (!failed && !exchange(l, l_other)) failed = true;
+    const float l_other = exchange(l);
     if (!failed && qi < a.L) {
       const float tot = l + l_other;
       const float inv = tot > 0.f ? 1.0f / tot : 0.f;
