@@ -371,14 +371,18 @@ _swa_fwd_op.register_autograd(_swa_autograd, setup_context=_swa_setup)
 
 def sliding_window_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window_size: Optional[int] = None,
                              softmax_scale: Optional[float] = None,
-                             cu_seqlens: Optional[torch.Tensor] = None) -> torch.Tensor:
+                             cu_seqlens: Optional[torch.Tensor] = None,
+                             attention_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention over the last `window_size` keys (the query's own position included), q, k, v and the
     result [b, l, n_heads, head_dim] bf16: what `flash_attn_func(q, k, v, causal=True, window_size=(window_size - 1,
     0))` computes at lact_llm/lact_model/layer_lact_swiglu.py:386-394 and
     minimal_implementations/causal_lact_with_sliding_window_attn.py:380-384 (`window_size=None`: all earlier keys).
     head_dim 64 or 128.  Differentiable (dq, dk, dv by `lact_swa_bwd`).  `cu_seqlens` (int32 [n + 1], device): the batch
     entry (b must be 1) is n sequences packed back to back, as for `flash_attn_varlen_func` (:371-385): no query sees
-    a key of an earlier sequence."""
+    a key of an earlier sequence.  `attention_mask` ([b, l], nonzero = token, zero = padding, any padding side): the
+    padded-batch branch (:351-370): the real tokens of all entries are gathered into one packed entry, attended per
+    sequence and scattered back, padding positions of the result are zero (`unpad_input` / `pad_input`).  Like the
+    reference's, this branch reads the number of real tokens on the host."""
     if not (q.is_cuda and k.is_cuda and v.is_cuda):
         raise ValueError("sliding_window_attention needs CUDA tensors (there is no CPU implementation)")
     assert q.dim() == 4 and q.shape == k.shape == v.shape, "q, k, v: [b, l, n_heads, head_dim], equal head counts"
@@ -386,9 +390,23 @@ def sliding_window_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, 
     if q.shape[3] not in (64, 128):
         raise ValueError("head_dim must be 64 or 128")
     scale = float(softmax_scale) if softmax_scale is not None else q.shape[3] ** -0.5
+    window = int(window_size) if window_size else 0
+    if attention_mask is not None:
+        if cu_seqlens is not None:
+            raise ValueError("give attention_mask or cu_seqlens, not both")
+        b, l, h, d = q.shape
+        assert attention_mask.shape == (b, l), "attention_mask: [b, l]"
+        mask = attention_mask.to(device=q.device) != 0
+        idx = torch.nonzero(mask.reshape(-1)).reshape(-1)   # (host synchronisation: data-dependent size)
+        if idx.numel() == 0:
+            return torch.zeros_like(q)
+        cu = torch.nn.functional.pad(torch.cumsum(mask.sum(dim=1), 0), (1, 0)).to(torch.int32)
+        packed = [t.reshape(b * l, h, d).index_select(0, idx).unsqueeze(0) for t in (q, k, v)]
+        o = torch.ops.lact_b200.swa_fwd(*packed, window, scale, _seq_start(cu, idx.numel(), q.device))[0]
+        return torch.zeros(b * l, h, d, dtype=q.dtype, device=q.device).index_copy(0, idx, o[0]).reshape(b, l, h, d)
     seq_start = None
     if cu_seqlens is not None:
         if q.shape[0] != 1:
             raise ValueError("packed sequences (cu_seqlens) need a batch of one")
         seq_start = _seq_start(cu_seqlens, q.shape[1], q.device)
-    return torch.ops.lact_b200.swa_fwd(q, k, v, int(window_size) if window_size else 0, scale, seq_start)[0]
+    return torch.ops.lact_b200.swa_fwd(q, k, v, window, scale, seq_start)[0]

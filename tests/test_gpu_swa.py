@@ -146,3 +146,43 @@ def test_swa_packed_sequences_forward_and_backward(lo, window):
     with pytest.raises(ValueError):
         lo.sliding_window_attention(torch.cat([cl[0]] * 2).detach(), torch.cat([cl[1]] * 2).detach(),
                                     torch.cat([cl[2]] * 2).detach(), window, cu_seqlens=cu.cuda())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("side", ["left", "right"])
+def test_swa_padded_batch_forward_and_backward(lo, side):
+    """attention_mask: every batch entry attends over its own real tokens only, padding rows come back zero and
+    receive no gradient (the reference's unpad -> varlen attention -> pad branch)."""
+    import lact_b200
+    from oracle import lact_oracle as orc
+    b, l, h, d, window = 3, 300, 2, 64, 96
+    lens = [300, 1, 170]
+    mask = torch.zeros(b, l, dtype=torch.int64)
+    for i, n in enumerate(lens):
+        if side == "right":
+            mask[i, :n] = 1
+        else:
+            mask[i, l - n:] = 1
+    g = torch.Generator().manual_seed(29)
+    q, k, v = (torch.randn(b, l, h, d, generator=g).to(BF16) for _ in range(3))
+    dO = torch.randn(b, l, h, d, generator=g).to(BF16)
+    leaves = [t.float().clone().requires_grad_(True) for t in (q, k, v)]
+    ref = torch.zeros(b, l, h, d)
+    for i in range(b):
+        sel = mask[i].bool()
+        ref[i, sel] = orc.sliding_window_attention(*(t[i:i + 1, sel] for t in leaves), window)[0]
+    (ref * dO.float()).sum().backward()
+    cl = [t.cuda().clone().requires_grad_(True) for t in (q, k, v)]
+    o = lo.sliding_window_attention(*cl, window, attention_mask=mask.cuda())
+    o.backward(dO.cuda())
+    lact_b200.synchronize_and_check()
+    got = o.detach().float().cpu()
+    assert float(got[mask == 0].abs().max()) == 0.0
+    assert (got - ref.detach()).abs().max() / ref.detach().abs().max() <= 1.5e-2
+    for name, x, want in zip("qkv", cl, leaves):
+        a, b_ = x.grad.float().cpu(), want.grad
+        assert float(a[mask == 0].abs().max()) == 0.0, name
+        assert orc.rel_max(a, b_) <= 3e-2 and orc.cosine(a, b_) >= 0.9995, (name, orc.rel_max(a, b_), orc.cosine(a, b_))
+    with pytest.raises(ValueError):
+        lo.sliding_window_attention(*[t.detach() for t in cl], window, attention_mask=mask.cuda(),
+                                    cu_seqlens=torch.tensor([0, 900], dtype=torch.int32).cuda())
