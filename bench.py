@@ -22,6 +22,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import tempfile
 import subprocess
 import sys
 import threading
@@ -552,9 +553,9 @@ def main():
     dev = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        # NCCL_DEBUG=VERSION makes NCCL print its version on stdout, next to the one JSON line this script owes
-        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"
+        # with NCCL_DEBUG set (VERSION, WARN, ...) NCCL prints its version banner and its messages on stdout, next to
+        # the one JSON line this script owes: send them to a per-process log file instead
+        os.environ.setdefault("NCCL_DEBUG_FILE", os.path.join(tempfile.gettempdir(), "lact_b200_bench_nccl.%h.%p.log"))
         dist.init_process_group("nccl", device_id=dev)
     from lact_b200 import build
     if rank == 0:
