@@ -299,3 +299,23 @@ def test_cfg3_backward_with_muon_at_benchmark_head_shape(lb, orc, B):
         assert torch.isfinite(a).all(), n
         assert orc.cosine(a, b) >= 0.995, (n, orc.cosine(a, b))
         assert orc.rel_fro(a, b) <= 0.12, (n, orc.rel_fro(a, b))
+
+
+def test_cfg3b_chunk_4096_forward_and_backward(lb, orc):
+    """The second training configuration's chunk size (4096 tokens) at D = H = 384, fused signature, momentum, Muon
+    off, a sequence that is not a multiple of the chunk (9192 tokens: zero-padded to three chunks, two updates):
+    output chunk by chunk at the stated tolerance and every gradient against autograd through the CPU oracle."""
+    from test_gpu_backward import _check, _grads_cuda, _grads_oracle
+    B, L, D, H, C = 2, 9192, 384, 384, 4096
+    inp = bf(orc.make_inputs(B, L, D, H, seed=36))
+    dO = torch.randn(B, L, D, generator=torch.Generator().manual_seed(7)).to(BF16)
+    ref_fn = lambda w0, w1, w2, q, k, v, l0, l1, l2, m: orc.block_causal_lact_swiglu_fused(
+        w0, w1, w2, q, k, v, l0, l1, l2, chunk_size=C, use_muon=False, momentum=m)
+    cu_fn = lambda w0, w1, w2, q, k, v, l0, l1, l2, m: lb.postnorm_block_causal_lact_swiglu_fused_kernel_triton(
+        w0, w1, w2, q, k, v, l0, l1, l2, chunk_size=C, use_muon=False, momentum=m)
+    o_ref, g_ref = _grads_oracle(orc, inp, ref_fn, True, dO)
+    o, g = _grads_cuda(inp, cu_fn, True, dO)
+    lb.synchronize_and_check()
+    for s in range(0, L, C):
+        close(orc, o[:, s:s + C], o_ref[:, s:s + C], what=f"cfg3b chunk at {s}")
+    _check(orc, g, g_ref, list(NAMES) + ["momentum"])
