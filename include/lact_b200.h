@@ -258,22 +258,26 @@ int lact_lr_prologue(const void *lr_proj, int32_t proj_dtype, int64_t proj_ld, f
  * lact_llm/lact_model/layer_lact_swiglu.py:386-394 and
  * minimal_implementations/causal_lact_with_sliding_window_attn.py:380-384.  bf16; d = 64 or 128; heads adjacent within
  * a token (head stride d), token / batch strides in elements (views of a fused projection are fine);
- * window <= 0 or >= l: plain causal attention.  seq_start: NULL, or for b = 1 an int32 [l] device array giving, for every
+ * window = 0 or >= l: plain causal attention.  window < 0: BLOCK attention, not causal: every query of a batch entry sees
+ * all lk keys of that entry (q, o: [b, l, h, d]; k, v: [b, lk, h, d]; lk <= 0 stands for l; with window >= 0, lk must
+ * equal l) - the full attention over a frame block that the autoregressive-video layer runs through
+ * flash_attention(q, k, v, k_lens, window_size=(-1, -1)) at
+ * lact_ar_video/minVid/models/blocks/ar_lact_swa_repeat.py:299-463.  seq_start (causal only): NULL, or for b = 1 an int32 [l] device array giving, for every
  * token, the first token of the packed sequence it belongs to (nondecreasing; what cu_seqlens describes in
  * flash_attn_varlen_func, layer_lact_swiglu.py:371-385): earlier keys are invisible.  lse: optional fp32 [b, n_heads, l], receives every row's log-sum-exp
  * in the log2 domain (what lact_swa_bwd needs), or NULL.  status_word: device word, 0 before the call (101 = a bounded
  * wait ran out). */
-int lact_swa_fwd(const void *q, const void *k, const void *v, void *o, int64_t b, int64_t l, int64_t n_heads, int64_t d,
-                 int64_t q_ts, int64_t q_bs, int64_t k_ts, int64_t k_bs, int64_t v_ts, int64_t v_bs, int64_t o_ts,
+int lact_swa_fwd(const void *q, const void *k, const void *v, void *o, int64_t b, int64_t l, int64_t lk, int64_t n_heads,
+                 int64_t d, int64_t q_ts, int64_t q_bs, int64_t k_ts, int64_t k_bs, int64_t v_ts, int64_t v_bs, int64_t o_ts,
                  int64_t o_bs, int64_t window, float softmax_scale, const int32_t *seq_start, void *lse,
                  int32_t *status_word, void *stream);
 
-/* Backward of lact_swa_fwd: dq, dk, dv (bf16, contiguous [b, l, n_heads, d], written) from the forward's inputs, its
+/* Backward of lact_swa_fwd: dq (bf16, contiguous [b, l, n_heads, d]) and dk, dv ([b, lk, n_heads, d]), written, from the forward's inputs, its
  * output o, its lse and the output gradient dout (bf16, token / batch strides in elements).  delta: fp32 scratch
  * [b, n_heads, l].  Three launches: row sums of dout * o, the keys' side (dK, dV), the queries' side (dQ); the
  * probabilities are recomputed from lse.  What autograd of flash_attn_func computes for the reference layer. */
 int lact_swa_bwd(const void *q, const void *k, const void *v, const void *o, const void *dout, const void *lse, void *dq,
-                 void *dk, void *dv, void *delta, int64_t b, int64_t l, int64_t n_heads, int64_t d, int64_t q_ts,
+                 void *dk, void *dv, void *delta, int64_t b, int64_t l, int64_t lk, int64_t n_heads, int64_t d, int64_t q_ts,
                  int64_t q_bs, int64_t k_ts, int64_t k_bs, int64_t v_ts, int64_t v_bs, int64_t o_ts, int64_t o_bs,
                  int64_t do_ts, int64_t do_bs, int64_t window, float softmax_scale, const int32_t *seq_start,
                  int32_t *status_word, void *stream);

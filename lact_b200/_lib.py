@@ -109,8 +109,8 @@ def _declare(lib: C.CDLL) -> None:
     lib.lact_qkv_prologue_bwd.argtypes = [vp] * 3 + [i64] * 6 + [vp] * 6 + [i64] * 4 + [i32, i32, vp, vp, i64, i64, i64, vp, vp]
     lib.lact_out_epilogue_bwd_blocks.restype = C.c_int
     lib.lact_out_epilogue_bwd.argtypes = [vp, vp, vp, i64, vp, i64, vp, vp, vp, i64, i64, i64, i64, f32, vp]
-    lib.lact_swa_fwd.argtypes = [vp, vp, vp, vp] + [i64] * 13 + [f32, vp, vp, vp, vp]
-    lib.lact_swa_bwd.argtypes = [vp] * 10 + [i64] * 15 + [f32, vp, vp, vp]
+    lib.lact_swa_fwd.argtypes = [vp, vp, vp, vp] + [i64] * 14 + [f32, vp, vp, vp, vp]
+    lib.lact_swa_bwd.argtypes = [vp] * 10 + [i64] * 16 + [f32, vp, vp, vp]
     lib.lact_bmm_group_bf16.argtypes = [C.POINTER(BmmDesc), i32, vp, vp]
     lib.lact_fw_grad_pointwise.argtypes = [vp, vp, vp, i64, i64, vp, i64, i64, vp, vp, vp, i32, i64, f32, vp, vp, i64, i64,
                                            i64, i64, vp, vp]

@@ -1916,23 +1916,28 @@ int lact_out_epilogue(const void* fw_x, const void* weight, const void* gate_pro
   return LACT_OK;
 }
 
-int lact_swa_fwd(const void* q, const void* k, const void* v, void* o, int64_t b, int64_t l, int64_t n_heads, int64_t d,
-                 int64_t q_ts, int64_t q_bs, int64_t k_ts, int64_t k_bs, int64_t v_ts, int64_t v_bs, int64_t o_ts,
+int lact_swa_fwd(const void* q, const void* k, const void* v, void* o, int64_t b, int64_t l, int64_t lk, int64_t n_heads,
+                 int64_t d, int64_t q_ts, int64_t q_bs, int64_t k_ts, int64_t k_bs, int64_t v_ts, int64_t v_bs, int64_t o_ts,
                  int64_t o_bs, int64_t window, float softmax_scale, const int32_t* seq_start, void* lse, int32_t* status_word,
                  void* stream) {
   if (!q || !k || !v || !o || !status_word) return LACT_ERR_NULL;
   if (seq_start != nullptr && b != 1) return LACT_ERR_CONFIG;   // packed sequences live in one batch entry
+  const bool causal = window >= 0;
+  if (lk <= 0) lk = l;
+  if (causal ? lk != l : seq_start != nullptr) return LACT_ERR_CONFIG;   // causal: keys = queries; block: no packing
   LACT_TRY(check_device());
   if (d != 64 && d != 128) return LACT_ERR_SHAPE;
-  if (b < 1 || l < 1 || n_heads < 1 || b > 65535 || n_heads > 65535 || l > (1ll << 30)) return LACT_ERR_SHAPE;
+  if (b < 1 || l < 1 || n_heads < 1 || b > 65535 || n_heads > 65535 || l > (1ll << 30) || lk > (1ll << 30)) return LACT_ERR_SHAPE;
   if ((reinterpret_cast<uintptr_t>(o) & 15) != 0 || o_ts < n_heads * d || (o_ts % 8) != 0 || (o_bs % 8) != 0)
     return LACT_ERR_SHAPE;
   if (!(softmax_scale > 0.f)) return LACT_ERR_CONFIG;
   SwaArgs a;
   std::memset(&a, 0, sizeof(a));
   LACT_TRY(encode_map_heads(&a.q, q, b, l, n_heads, d, q_ts, q_bs));
-  LACT_TRY(encode_map_heads(&a.k, k, b, l, n_heads, d, k_ts, k_bs));
-  LACT_TRY(encode_map_heads(&a.v, v, b, l, n_heads, d, v_ts, v_bs));
+  LACT_TRY(encode_map_heads(&a.k, k, b, lk, n_heads, d, k_ts, k_bs));
+  LACT_TRY(encode_map_heads(&a.v, v, b, lk, n_heads, d, v_ts, v_bs));
+  a.Lk = static_cast<int32_t>(lk);
+  a.causal = causal ? 1 : 0;
   a.o = static_cast<bf16*>(o);
   a.o_bs = o_bs; a.o_ts = o_ts; a.o_hs = d;
   a.L = static_cast<int32_t>(l);
@@ -1950,15 +1955,18 @@ int lact_swa_fwd(const void* q, const void* k, const void* v, void* o, int64_t b
 }
 
 int lact_swa_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout, const void* lse, void* dq,
-                 void* dk, void* dv, void* delta, int64_t b, int64_t l, int64_t n_heads, int64_t d, int64_t q_ts,
+                 void* dk, void* dv, void* delta, int64_t b, int64_t l, int64_t lk, int64_t n_heads, int64_t d, int64_t q_ts,
                  int64_t q_bs, int64_t k_ts, int64_t k_bs, int64_t v_ts, int64_t v_bs, int64_t o_ts, int64_t o_bs,
                  int64_t do_ts, int64_t do_bs, int64_t window, float softmax_scale, const int32_t* seq_start,
                  int32_t* status_word, void* stream) {
   if (!q || !k || !v || !o || !dout || !lse || !dq || !dk || !dv || !delta || !status_word) return LACT_ERR_NULL;
   if (seq_start != nullptr && b != 1) return LACT_ERR_CONFIG;
+  const bool causal = window >= 0;
+  if (lk <= 0) lk = l;
+  if (causal ? lk != l : seq_start != nullptr) return LACT_ERR_CONFIG;
   LACT_TRY(check_device());
   if (d != 64 && d != 128) return LACT_ERR_SHAPE;
-  if (b < 1 || l < 1 || n_heads < 1 || b > 65535 || n_heads > 65535 || l > (1ll << 30)) return LACT_ERR_SHAPE;
+  if (b < 1 || l < 1 || n_heads < 1 || b > 65535 || n_heads > 65535 || l > (1ll << 30) || lk > (1ll << 30)) return LACT_ERR_SHAPE;
   if (!(softmax_scale > 0.f)) return LACT_ERR_CONFIG;
   for (const void* p : {static_cast<const void*>(dq), static_cast<const void*>(dk), static_cast<const void*>(dv), o, dout})
     if ((reinterpret_cast<uintptr_t>(p) & 15) != 0) return LACT_ERR_SHAPE;
@@ -1981,32 +1989,38 @@ int lact_swa_bwd(const void* q, const void* k, const void* v, const void* o, con
   SwaBwdArgs a;
   std::memset(&a, 0, sizeof(a));
   LACT_TRY(encode_map_heads(&a.q, q, b, l, n_heads, d, q_ts, q_bs));
-  LACT_TRY(encode_map_heads(&a.k, k, b, l, n_heads, d, k_ts, k_bs));
-  LACT_TRY(encode_map_heads(&a.v, v, b, l, n_heads, d, v_ts, v_bs));
+  LACT_TRY(encode_map_heads(&a.k, k, b, lk, n_heads, d, k_ts, k_bs));
+  LACT_TRY(encode_map_heads(&a.v, v, b, lk, n_heads, d, v_ts, v_bs));
   LACT_TRY(encode_map_heads(&a.dout, dout, b, l, n_heads, d, do_ts, do_bs));
   LACT_TRY(encode_map_heads(&a.q64, q, b, l, n_heads, d, q_ts, q_bs, 64));
-  LACT_TRY(encode_map_heads(&a.k64, k, b, l, n_heads, d, k_ts, k_bs, 64));
-  LACT_TRY(encode_map_heads(&a.v64, v, b, l, n_heads, d, v_ts, v_bs, 64));
+  LACT_TRY(encode_map_heads(&a.k64, k, b, lk, n_heads, d, k_ts, k_bs, 64));
+  LACT_TRY(encode_map_heads(&a.v64, v, b, lk, n_heads, d, v_ts, v_bs, 64));
   LACT_TRY(encode_map_heads(&a.dout64, dout, b, l, n_heads, d, do_ts, do_bs, 64));
   a.lse = static_cast<const float*>(lse);
   a.delta = static_cast<const float*>(delta);
   a.seq_start = seq_start;
-  a.o_ts = n_heads * d; a.o_bs = l * n_heads * d; a.o_hs = d;   // gradients are written contiguous [b][l][h][d]
+  a.o_ts = n_heads * d; a.o_hs = d;   // gradients are written contiguous [b][l or lk][h][d]
   a.L = static_cast<int32_t>(l);
+  a.Lk = static_cast<int32_t>(lk);
+  a.causal = causal ? 1 : 0;
   a.window = window > 0 && window < l ? static_cast<int32_t>(window) : 0;
   a.heads = static_cast<int32_t>(n_heads);
-  a.tiles = ceil_div(l, 128);
   a.scale_log2 = softmax_scale * 1.4426950408889634f;
   a.scale = softmax_scale;
   a.status = status_word;
-  const int64_t ctas = b * n_heads * a.tiles;
-  if (ctas > 0x7FFFFFFFll) return LACT_ERR_SHAPE;
-  // keys' side (dK, dV), then queries' side (dQ)
+  const int64_t k_tiles = ceil_div(lk, 128), q_tiles = ceil_div(l, 128);
+  if (b * n_heads * std::max(k_tiles, q_tiles) > 0x7FFFFFFFll) return LACT_ERR_SHAPE;
+  // keys' side (dK, dV): one CTA per key tile; then queries' side (dQ): one CTA per query tile
   a.out0 = static_cast<bf16*>(dk);
   a.out1 = static_cast<bf16*>(dv);
-  LACT_TRY((d == 64 ? launch_swa_bwd<64, 0>(a, ctas, st) : launch_swa_bwd<128, 0>(a, ctas, st)));
+  a.tiles = static_cast<int32_t>(k_tiles);
+  a.o_bs = lk * n_heads * d;
+  LACT_TRY((d == 64 ? launch_swa_bwd<64, 0>(a, b * n_heads * k_tiles, st) : launch_swa_bwd<128, 0>(a, b * n_heads * k_tiles, st)));
   a.out0 = static_cast<bf16*>(dq);
   a.out1 = nullptr;
+  a.tiles = static_cast<int32_t>(q_tiles);
+  a.o_bs = l * n_heads * d;
+  const int64_t ctas = b * n_heads * q_tiles;
   return d == 64 ? launch_swa_bwd<64, 1>(a, ctas, st) : launch_swa_bwd<128, 1>(a, ctas, st);
 }
 

@@ -23,7 +23,8 @@ struct SwaArgs {
   CUtensorMap q, k, v;   // 4-D maps (feature, token, head, batch), box {64, 128, 1, 1}
   bf16* o;               // [b][l][h][d], strides below (elements); feature stride 1
   int64_t o_bs, o_ts, o_hs;
-  int32_t L, window;     // window <= 0: unbounded (plain causal attention)
+  int32_t L, window;     // queries per batch entry; window <= 0: unbounded (plain causal attention)
+  int32_t Lk, causal;    // keys per batch entry (= L when causal); causal = 0: every query sees every key of its entry
   int32_t heads, q_tiles;
   float scale_log2;      // log2(e) / sqrt(d)
   const int32_t* seq_start;  // optional [l]: first token of the packed sequence every token belongs to (nondecreasing;
@@ -107,7 +108,11 @@ __global__ void __launch_bounds__(320, 1) swa_fwd_kernel(const __grid_constant__
   // packed sequences: no row of this tile sees a key before the first row's sequence start
   if (a.seq_start != nullptr && a.seq_start[q0] > kv_lo) kv_lo = (a.seq_start[q0] / 128) * 128;
   const int tile_start = a.seq_start != nullptr ? a.seq_start[q0 + 127 < a.L ? q0 + 127 : a.L - 1] : 0;  // last row's
-  const int kv_hi = q0 + 128 < a.L ? q0 + 128 : a.L;
+  int kv_hi = q0 + 128 < a.L ? q0 + 128 : a.L;
+  if (!a.causal) {   // block attention: all keys of the entry
+    kv_lo = 0;
+    kv_hi = a.Lk;
+  }
   const int T = (kv_hi - kv_lo + 127) / 128;
   bool failed = *reinterpret_cast<volatile int32_t*>(a.status) != kStatusOk;
 
@@ -220,10 +225,12 @@ __global__ void __launch_bounds__(320, 1) swa_fwd_kernel(const __grid_constant__
         *abort_flag = 1;
       }
       // every (row, key) pair of the tile inside the band and the sequence: no masks
-      const bool interior = kv0 + 127 <= q0 && kv0 >= q0 + 127 - (window - 1) && kv0 + 127 < a.L && kv0 >= tile_start;
+      const bool interior = a.causal ? (kv0 + 127 <= q0 && kv0 >= q0 + 127 - (window - 1) && kv0 + 127 < a.L && kv0 >= tile_start)
+                                     : kv0 + 127 < a.Lk;
       const int c0 = half * 64;                                // this thread's first key column of the tile
-      const int j_hi = (qi < a.L - 1 ? qi : a.L - 1) - kv0;   // last / first column of the tile this row may see
-      const int j_lo = (qi - (window - 1) > row_start ? qi - (window - 1) : row_start) - kv0;
+      // last / first column of the tile this row may see
+      const int j_hi = (a.causal ? (qi < a.L - 1 ? qi : a.L - 1) : a.Lk - 1) - kv0;
+      const int j_lo = (a.causal ? (qi - (window - 1) > row_start ? qi - (window - 1) : row_start) : 0) - kv0;
       const uint32_t s_addr = tmem + lane_off + sb * 128 + c0;
       uint32_t ba[32], bb[32];   // this thread's 64 scores: read once, kept across the exchange of the row maximum
       float mx = -INFINITY;

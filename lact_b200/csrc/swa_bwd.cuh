@@ -28,7 +28,8 @@ struct SwaBwdArgs {
   bf16* out0;                  // MODE 0: dK, MODE 1: dQ   ([b][l][h][d], strides below)
   bf16* out1;                  // MODE 0: dV
   int64_t o_bs, o_ts, o_hs;
-  int32_t L, window, heads, tiles;
+  int32_t L, window, heads, tiles;   // L: queries per batch entry; tiles: outer tiles per (batch, head) of this launch
+  int32_t Lk, causal;                // keys per batch entry (= L when causal); causal = 0: every query sees every key
   float scale_log2, scale;
   int32_t* status;
 };
@@ -104,12 +105,14 @@ __global__ void __launch_bounds__(320, 1) swa_bwd_kernel(const __grid_constant__
     t_lo = o0 / 64;
     const int q_max = o0 + 127 + window - 1;
     t_hi = (q_max < a.L - 1 ? q_max : a.L - 1) / 64;
+    if (!a.causal) t_lo = 0, t_hi = (a.L - 1) / 64;   // block attention: every query tile
   } else {           // keys this query tile sees: not before the window of its first query, nor before that query's sequence
     int lo = o0 - (window - 1);
     if (lo < 0) lo = 0;
     if (a.seq_start != nullptr && a.seq_start[o0] > lo) lo = a.seq_start[o0];
     t_lo = lo / 64;
     t_hi = (o0 + 127 < a.L - 1 ? o0 + 127 : a.L - 1) / 64;
+    if (!a.causal) t_lo = 0, t_hi = (a.Lk - 1) / 64;  // every key tile
   }
   const int T = t_hi - t_lo + 1;
   bool failed = *reinterpret_cast<volatile int32_t*>(a.status) != kStatusOk;
@@ -243,7 +246,8 @@ __global__ void __launch_bounds__(320, 1) swa_bwd_kernel(const __grid_constant__
             // rows = keys, columns = queries i0 + c
             const int last_q = i0 + 63 < a.L ? i0 + 63 : a.L - 1;
             const int tile_start = a.seq_start != nullptr ? a.seq_start[last_q] : 0;
-            const bool interior = o0 + 127 <= i0 && o0 >= i0 + 63 - (window - 1) && i0 + 63 < a.L && o0 >= tile_start;
+            const bool interior = a.causal ? (o0 + 127 <= i0 && o0 >= i0 + 63 - (window - 1) && i0 + 63 < a.L && o0 >= tile_start)
+                                           : (i0 + 63 < a.L && o0 + 127 < a.Lk);
             const float* st = stats + s * 192 + c0;
             if (interior) {
 #pragma unroll
@@ -269,7 +273,7 @@ __global__ void __launch_bounds__(320, 1) swa_bwd_kernel(const __grid_constant__
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                   const int j = g * 4 + e, qi = i0 + c0 + j;
-                  const bool ok = row <= qi && row >= qi - (window - 1) && row >= sv[e] && qi < a.L && row < a.L;
+                  const bool ok = (!a.causal || (row <= qi && row >= qi - (window - 1) && row >= sv[e])) && qi < a.L && row < a.Lk;
                   p[j] = ok ? fast_exp2(fmaf(__uint_as_float(sb[j]), a.scale_log2, -lv[e])) : 0.f;
                   ds[j] = p[j] * fmaf(__uint_as_float(db[j]), a.scale, -dv[e]);
                 }
@@ -279,7 +283,8 @@ __global__ void __launch_bounds__(320, 1) swa_bwd_kernel(const __grid_constant__
             // rows = queries, columns = keys i0 + c
             const int last_q = o0 + 127 < a.L ? o0 + 127 : a.L - 1;
             const int tile_start = a.seq_start != nullptr ? a.seq_start[last_q] : 0;
-            const bool interior = i0 + 63 <= o0 && i0 >= o0 + 127 - (window - 1) && o0 + 127 < a.L && i0 >= tile_start;
+            const bool interior = a.causal ? (i0 + 63 <= o0 && i0 >= o0 + 127 - (window - 1) && o0 + 127 < a.L && i0 >= tile_start)
+                                           : (i0 + 63 < a.Lk && o0 + 127 < a.L);
             if (interior) {
 #pragma unroll
               for (int j = 0; j < 32; ++j) {
@@ -287,8 +292,8 @@ __global__ void __launch_bounds__(320, 1) swa_bwd_kernel(const __grid_constant__
                 ds[j] = p[j] * fmaf(__uint_as_float(db[j]), a.scale, -delta_r);
               }
             } else {
-              const int k_hi = row < a.L ? row : -1;   // last / first key this query may see
-              const int k_lo = row - (window - 1) > row_start ? row - (window - 1) : row_start;
+              const int k_hi = row < a.L ? (a.causal ? row : a.Lk - 1) : -1;   // last / first key this query may see
+              const int k_lo = a.causal ? (row - (window - 1) > row_start ? row - (window - 1) : row_start) : 0;
 #pragma unroll
               for (int j = 0; j < 32; ++j) {
                 const int kv = i0 + c0 + j;
@@ -335,7 +340,7 @@ __global__ void __launch_bounds__(320, 1) swa_bwd_kernel(const __grid_constant__
           uint32_t bits[32];
           tmem_ld32(tmem + lane_off + 256 + acc * HD + half * OC + c, bits);
           tmem_ld_wait();
-          if (row < a.L) {
+          if (row < (MODE == 0 ? a.Lk : a.L)) {
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
               uint4 u;

@@ -295,15 +295,18 @@ def _head_view(t: torch.Tensor, h: int, d: int) -> torch.Tensor:
 @torch.library.custom_op("lact_b200::swa_fwd", mutates_args=(), device_types="cuda")
 def _swa_fwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: int, softmax_scale: float,
                 seq_start: Optional[torch.Tensor] = None) -> List[torch.Tensor]:
-    """[o, lse]: the attention output and every row's log-sum-exp (log2 domain, fp32 [b, h, l]) for the backward."""
+    """[o, lse]: the attention output and every row's log-sum-exp (log2 domain, fp32 [b, h, l]) for the backward.
+    window > 0: causal, the last `window` keys; 0: causal, all earlier keys; < 0: block attention (not causal: every
+    query sees all keys of its batch entry; k and v may then hold another number of tokens than q)."""
     from .backward import _status_word, post_status, reset_status
     b, l, h, d = q.shape
+    lk = k.shape[1]
     q, k, v = _head_view(q, h, d), _head_view(k, h, d), _head_view(v, h, d)
     o = torch.empty(b, l, h, d, dtype=BF16, device=q.device)
     lse = torch.empty(b, h, l, dtype=torch.float32, device=q.device)
     reset_status(q.device)
     with torch.cuda.device(q.device):
-        L.check(L.lib().lact_swa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), b, l, h, d, q.stride(1),
+        L.check(L.lib().lact_swa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), b, l, lk, h, d, q.stride(1),
                                      q.stride(0), k.stride(1), k.stride(0), v.stride(1), v.stride(0), o.stride(1),
                                      o.stride(0), int(window), float(softmax_scale),
                                      seq_start.data_ptr() if seq_start is not None else None, lse.data_ptr(),
@@ -325,15 +328,17 @@ def _swa_bwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tens
     """[dq, dk, dv] (bf16, contiguous): probabilities recomputed from lse, five products per (query tile, key tile)."""
     from .backward import _status_word, post_status, reset_status
     b, l, h, d = q.shape
+    lk = k.shape[1]
     q, k, v = _head_view(q, h, d), _head_view(k, h, d), _head_view(v, h, d)
     o, dout = _head_view(o, h, d), _head_view(dout.to(BF16), h, d)
-    dq, dk, dv = (torch.empty(b, l, h, d, dtype=BF16, device=q.device) for _ in range(3))
+    dq = torch.empty(b, l, h, d, dtype=BF16, device=q.device)
+    dk, dv = (torch.empty(b, lk, h, d, dtype=BF16, device=q.device) for _ in range(2))
     delta = torch.empty(b, h, l, dtype=torch.float32, device=q.device)
     reset_status(q.device)
     with torch.cuda.device(q.device):
         L.check(L.lib().lact_swa_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), dout.data_ptr(),
                                      lse.contiguous().data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
-                                     delta.data_ptr(), b, l, h, d, q.stride(1), q.stride(0), k.stride(1), k.stride(0),
+                                     delta.data_ptr(), b, l, lk, h, d, q.stride(1), q.stride(0), k.stride(1), k.stride(0),
                                      v.stride(1), v.stride(0), o.stride(1), o.stride(0), dout.stride(1), dout.stride(0),
                                      int(window), float(softmax_scale),
                                      seq_start.data_ptr() if seq_start is not None else None,
@@ -344,7 +349,7 @@ def _swa_bwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tens
 
 @_swa_bwd_op.register_fake
 def _swa_bwd_fake(q, k, v, o, lse, dout, window, softmax_scale, seq_start=None):
-    return [q.new_empty(q.shape), q.new_empty(q.shape), q.new_empty(q.shape)]
+    return [q.new_empty(q.shape), q.new_empty(k.shape), q.new_empty(k.shape)]
 
 
 def _swa_setup(ctx, inputs, output):
@@ -410,3 +415,71 @@ def sliding_window_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, 
             raise ValueError("packed sequences (cu_seqlens) need a batch of one")
         seq_start = _seq_start(cu_seqlens, q.shape[1], q.device)
     return torch.ops.lact_b200.swa_fwd(q, k, v, window, scale, seq_start)[0]
+
+
+def block_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                    softmax_scale: Optional[float] = None) -> torch.Tensor:
+    """Full (not causal) attention of every query of a batch entry over all keys of that entry: q [b, lq, h, d],
+    k, v [b, lk, h, d] bf16, result [b, lq, h, d].  What `flash_attention(q, k, v, k_lens=<all keys>, window_size=(-1,
+    -1))` computes for the frame blocks of the autoregressive-video layer
+    (lact_ar_video/minVid/models/blocks/ar_lact_swa_repeat.py:313-318, 344-364).  The same tcgen05 kernels as
+    `sliding_window_attention`, band and sequence masks off.  head_dim 64 or 128.  Differentiable."""
+    if not (q.is_cuda and k.is_cuda and v.is_cuda):
+        raise ValueError("block_attention needs CUDA tensors (there is no CPU implementation)")
+    assert q.dim() == 4 and k.shape == v.shape and k.dim() == 4, "q [b, lq, h, d]; k, v [b, lk, h, d]"
+    assert q.shape[0] == k.shape[0] and q.shape[2:] == k.shape[2:], "q and k, v differ in the token count only"
+    assert q.dtype == k.dtype == v.dtype == BF16, "bf16 activations"
+    if q.shape[3] not in (64, 128):
+        raise ValueError("head_dim must be 64 or 128")
+    if q.shape[1] == 0 or k.shape[1] == 0:
+        return torch.zeros_like(q)
+    scale = float(softmax_scale) if softmax_scale is not None else q.shape[3] ** -0.5
+    return torch.ops.lact_b200.swa_fwd(q, k, v, -1, scale, None)[0]
+
+
+def batched_sliding_window_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mini_batch_size: int,
+                                     update_every: int, num_chunks: int, kv_cache_size: int) -> torch.Tensor:
+    """The block attention of the autoregressive-video layer, same name and arguments as
+    ar_lact_swa_repeat.py:299-365.  q, k, v: [b, l, h, d] with l = update_every - mini_batch_size + update_every *
+    (num_chunks - 1).  The first update_every - mini_batch_size tokens attend among themselves; every later block of
+    update_every tokens is a clean part (the first mini_batch_size tokens, attending among themselves) followed by a
+    noisy part that attends over the last kv_cache_size clean keys and the keys after them (mini_batch_size +
+    kv_cache_size keys, as the reference's k_lens says)."""
+    b, l = q.shape[:2]
+    first, n_c, mb = update_every - mini_batch_size, num_chunks - 1, mini_batch_size
+    assert l == first + update_every * n_c, "l = update_every - mini_batch_size + update_every * (num_chunks - 1)"
+    assert 0 <= kv_cache_size <= mb
+    parts = [block_attention(q[:, :first], k[:, :first], v[:, :first])] if first > 0 else []
+    if n_c > 0:
+        q_r, k_r, v_r = (t[:, first:].reshape(b * n_c, update_every, *t.shape[2:]) for t in (q, k, v))
+        o_clean = block_attention(q_r[:, :mb], k_r[:, :mb], v_r[:, :mb])
+        k_end = min(update_every, 2 * mb)   # keys [mb - kv_cache_size, mb - kv_cache_size + (mb + kv_cache_size))
+        o_noise = block_attention(q_r[:, mb:], k_r[:, mb - kv_cache_size:k_end], v_r[:, mb - kv_cache_size:k_end])
+        parts.append(torch.cat([o_clean, o_noise], dim=1).reshape(b, n_c * update_every, *q.shape[2:]))
+    return torch.cat(parts, dim=1) if len(parts) > 1 else parts[0]
+
+
+def batched_sliding_window_attention_with_repeated_chunks(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                                                          mini_batch_size: int, update_every: int, num_chunks: int,
+                                                          kv_cache_size: int) -> torch.Tensor:
+    """ar_lact_swa_repeat.py:368-463, same name and arguments: update_every = (num_repeat + 1) * mini_batch_size.  The
+    first update_every - mini_batch_size tokens are num_repeat blocks of mini_batch_size tokens, each attending within
+    itself; every later block of update_every tokens is a clean part (mini_batch_size tokens, attending within itself)
+    and num_repeat noisy parts, each attending over the last kv_cache_size clean keys and its own keys."""
+    b, l = q.shape[:2]
+    first, n_c, mb = update_every - mini_batch_size, num_chunks - 1, mini_batch_size
+    nr = update_every // mb - 1
+    assert update_every == (nr + 1) * mb and nr >= 1, "update_every must be a multiple (>= 2) of mini_batch_size"
+    assert l == first + update_every * n_c and 0 <= kv_cache_size <= mb
+    tail = q.shape[2:]
+    blocks = lambda t: t[:, :first].reshape(b * nr, mb, *tail)
+    parts = [block_attention(blocks(q), blocks(k), blocks(v)).reshape(b, first, *tail)]
+    if n_c > 0:
+        q_r, k_r, v_r = (t[:, first:].reshape(b * n_c, update_every, *tail) for t in (q, k, v))
+        o_clean = block_attention(q_r[:, :mb], k_r[:, :mb], v_r[:, :mb])
+        noisy = lambda t: t[:, mb:].reshape(b * n_c * nr, mb, *tail)
+        cached = lambda t: t[:, mb - kv_cache_size:mb].repeat_interleave(nr, dim=0)
+        o_noise = block_attention(noisy(q_r), torch.cat([cached(k_r), noisy(k_r)], dim=1),
+                                  torch.cat([cached(v_r), noisy(v_r)], dim=1)).reshape(b * n_c, nr * mb, *tail)
+        parts.append(torch.cat([o_clean, o_noise], dim=1).reshape(b, n_c * update_every, *tail))
+    return torch.cat(parts, dim=1) if len(parts) > 1 else parts[0]

@@ -806,3 +806,44 @@ def sliding_window_attention(q, k, v, window_size=None, softmax_scale=None, bloc
         sc = sc.masked_fill(~((j <= i) & (j > i - w)), float("-inf"))
         out[:, :, s0:s1] = torch.matmul(torch.softmax(sc, dim=-1), vf[:, :, k0:s1])
     return out.permute(0, 2, 1, 3).contiguous()
+
+
+def masked_attention(q, k, v, visible, softmax_scale=None):
+    """fp32 softmax attention with an explicit boolean visibility matrix `visible` [lq, lk] (True = the query may
+    attend the key), q [b, lq, h, d], k, v [b, lk, h, d] -> fp32 [b, lq, h, d].  The definition the block-attention
+    restatements below are written against."""
+    d = q.shape[-1]
+    scale = d ** -0.5 if softmax_scale is None else softmax_scale
+    qf, kf, vf = (t.float().permute(0, 2, 1, 3) for t in (q, k, v))
+    sc = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    sc = sc.masked_fill(~visible.view(1, 1, *visible.shape), float("-inf"))
+    return torch.matmul(torch.softmax(sc, dim=-1), vf).permute(0, 2, 1, 3).contiguous()
+
+
+def ar_block_visibility(l, mini_batch_size, update_every, num_chunks, kv_cache_size, repeated):
+    """Which key every query of the autoregressive-video layer's attention sees, as ONE [l, l] matrix, from the
+    structure of lact_ar_video/minVid/models/blocks/ar_lact_swa_repeat.py:299-365 (`repeated` False) and :368-463
+    (True): the leading update_every - mini_batch_size tokens attend among themselves (as num_repeat separate blocks
+    when repeated); in every later block of update_every tokens the first mini_batch_size (clean) tokens attend among
+    themselves and the noisy tokens attend over the last kv_cache_size clean keys plus - not repeated - the
+    mini_batch_size keys after them, or - repeated - the keys of their own mini_batch_size block."""
+    mb, ue = mini_batch_size, update_every
+    first = ue - mb
+    assert l == first + ue * (num_chunks - 1)
+    vis = torch.zeros(l, l, dtype=torch.bool)
+    if repeated:
+        for s in range(0, first, mb):
+            vis[s:s + mb, s:s + mb] = True
+    else:
+        vis[:first, :first] = True
+    for c in range(num_chunks - 1):
+        s = first + c * ue
+        vis[s:s + mb, s:s + mb] = True
+        if repeated:
+            for r in range(ue // mb - 1):
+                n0 = s + mb + r * mb
+                vis[n0:n0 + mb, s + mb - kv_cache_size:s + mb] = True
+                vis[n0:n0 + mb, n0:n0 + mb] = True
+        else:
+            vis[s + mb:s + ue, s + mb - kv_cache_size:min(s + ue, s + 2 * mb)] = True
+    return vis

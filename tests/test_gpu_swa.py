@@ -186,3 +186,61 @@ def test_swa_padded_batch_forward_and_backward(lo, side):
     with pytest.raises(ValueError):
         lo.sliding_window_attention(*[t.detach() for t in cl], window, attention_mask=mask.cuda(),
                                     cu_seqlens=torch.tensor([0, 900], dtype=torch.int32).cuda())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("d,lq,lk", [(128, 300, 300), (128, 200, 457), (64, 390, 130), (128, 1560, 1750), (64, 64, 1)])
+def test_block_attention_forward_and_backward(lo, d, lq, lk):
+    """Not causal, other key count than query count (the autoregressive-video layer's frame blocks): output and
+    gradients against fp32 attention with every key visible."""
+    import lact_b200
+    from oracle import lact_oracle as orc
+    b, h = 2, 2
+    g = torch.Generator().manual_seed(31)
+    q = torch.randn(b, lq, h, d, generator=g).to(BF16)
+    k, v = (torch.randn(b, lk, h, d, generator=g).to(BF16) for _ in range(2))
+    dO = torch.randn(b, lq, h, d, generator=g).to(BF16)
+    leaves = [t.float().clone().requires_grad_(True) for t in (q, k, v)]
+    ref = orc.masked_attention(*leaves, torch.ones(lq, lk, dtype=torch.bool))
+    (ref * dO.float()).sum().backward()
+    cl = [t.cuda().clone().requires_grad_(True) for t in (q, k, v)]
+    o = lo.block_attention(*cl)
+    o.backward(dO.cuda())
+    lact_b200.synchronize_and_check()
+    assert (o.detach().float().cpu() - ref.detach()).abs().max() / ref.detach().abs().max() <= 1.5e-2
+    for name, x, want in zip("qkv", cl, leaves):
+        a, b_ = x.grad.float().cpu(), want.grad
+        assert a.shape == b_.shape
+        if float(b_.abs().max()) == 0.0:   # one key: the probabilities are constant, dq and dk vanish
+            assert float(a.abs().max()) <= 1e-2, name
+        else:
+            assert orc.rel_max(a, b_) <= 3e-2 and orc.cosine(a, b_) >= 0.9995, (name, orc.rel_max(a, b_), orc.cosine(a, b_))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("repeated", [False, True])
+def test_ar_video_block_attention_matches_the_visibility_matrix(lo, repeated):
+    """batched_sliding_window_attention[_with_repeated_chunks]: the reshaped block calls against ONE masked attention
+    over the whole sequence with the visibility matrix restated from the reference's structure; forward and backward."""
+    import lact_b200
+    from oracle import lact_oracle as orc
+    mb, kvc, num_chunks = 150, 70, 3
+    ue = 3 * mb if repeated else 2 * mb
+    l = ue - mb + ue * (num_chunks - 1)
+    b, h, d = 2, 2, 128
+    g = torch.Generator().manual_seed(37)
+    q, k, v = (torch.randn(b, l, h, d, generator=g).to(BF16) for _ in range(3))
+    dO = torch.randn(b, l, h, d, generator=g).to(BF16)
+    leaves = [t.float().clone().requires_grad_(True) for t in (q, k, v)]
+    ref = orc.masked_attention(*leaves, orc.ar_block_visibility(l, mb, ue, num_chunks, kvc, repeated))
+    (ref * dO.float()).sum().backward()
+    cl = [t.cuda().clone().requires_grad_(True) for t in (q, k, v)]
+    fn = lo.batched_sliding_window_attention_with_repeated_chunks if repeated else lo.batched_sliding_window_attention
+    o = fn(*cl, mb, ue, num_chunks, kvc)
+    o.backward(dO.cuda())
+    lact_b200.synchronize_and_check()
+    assert o.shape == q.shape
+    assert (o.detach().float().cpu() - ref.detach()).abs().max() / ref.detach().abs().max() <= 1.5e-2
+    for name, x, want in zip("qkv", cl, leaves):
+        a, b_ = x.grad.float().cpu(), want.grad
+        assert orc.rel_max(a, b_) <= 3e-2 and orc.cosine(a, b_) >= 0.9995, (name, orc.rel_max(a, b_), orc.cosine(a, b_))

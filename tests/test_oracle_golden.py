@@ -207,3 +207,39 @@ def test_sliding_window_attention_restatement_against_sdpa(l, window):
     ref = torch.nn.functional.scaled_dot_product_attention(q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3),
                                                            v.permute(0, 2, 1, 3), attn_mask=mask).permute(0, 2, 1, 3)
     assert torch.allclose(got, ref, atol=2e-6, rtol=1e-5)
+
+
+@pytest.mark.parametrize("repeated", [False, True])
+def test_ar_block_visibility_equals_the_block_by_block_calls(repeated):
+    """The one-matrix restatement of the autoregressive-video layer's attention against a literal replay of the
+    reference's structure (ar_lact_swa_repeat.py:299-463: reshape into blocks, one full attention per block group)
+    with PyTorch's scaled_dot_product_attention standing in for the flash-attn call."""
+    import torch.nn.functional as F
+    from einops import rearrange, repeat
+    mb, kvc, num_chunks = 6, 4, 3
+    ue = 3 * mb if repeated else 2 * mb
+    first = ue - mb
+    l = first + ue * (num_chunks - 1)
+    b, h, d = 2, 2, 8
+    g = torch.Generator().manual_seed(3)
+    q, k, v = (torch.randn(b, l, h, d, generator=g) for _ in range(3))
+    full = lambda q_, k_, v_: F.scaled_dot_product_attention(q_.transpose(1, 2), k_.transpose(1, 2), v_.transpose(1, 2)).transpose(1, 2)
+    o = torch.zeros_like(q)
+    nr = ue // mb - 1
+    if repeated:
+        blk = lambda t: rearrange(t[:, :first], "b (nr fw) h d -> (b nr) fw h d", nr=nr)
+        o[:, :first] = rearrange(full(blk(q), blk(k), blk(v)), "(b nr) fw h d -> b (nr fw) h d", nr=nr)
+    else:
+        o[:, :first] = full(q[:, :first], k[:, :first], v[:, :first])
+    q_r, k_r, v_r = (rearrange(t[:, first:], "b (n_c sw) h d -> (b n_c) sw h d", sw=ue) for t in (q, k, v))
+    o_clean = full(q_r[:, :mb], k_r[:, :mb], v_r[:, :mb])
+    if repeated:
+        nz = lambda t: rearrange(t[:, mb:], "b (n_repeat sw) h d -> (b n_repeat) sw h d", n_repeat=nr)
+        rp = lambda t: repeat(t[:, :mb][:, -kvc:], "b sw h d -> (b n_repeat) sw h d", n_repeat=nr)
+        o_noise = full(nz(q_r), torch.cat([rp(k_r), nz(k_r)], 1), torch.cat([rp(v_r), nz(v_r)], 1))
+        o_noise = rearrange(o_noise, "(b n_repeat) sw h d -> b (n_repeat sw) h d", n_repeat=nr)
+    else:
+        o_noise = full(q_r[:, mb:], k_r[:, mb - kvc:], v_r[:, mb - kvc:])
+    o[:, first:] = rearrange(torch.cat([o_clean, o_noise], 1), "(b n_c) sw h d -> b (n_c sw) h d", n_c=num_chunks - 1)
+    got = orc.masked_attention(q, k, v, orc.ar_block_visibility(l, mb, ue, num_chunks, kvc, repeated))
+    assert torch.allclose(got, o, atol=1e-5, rtol=1e-5)
