@@ -483,3 +483,21 @@ def batched_sliding_window_attention_with_repeated_chunks(q: torch.Tensor, k: to
                                   torch.cat([cached(v_r), noisy(v_r)], dim=1)).reshape(b * n_c, nr * mb, *tail)
         parts.append(torch.cat([o_clean, o_noise], dim=1).reshape(b, n_c * update_every, *tail))
     return torch.cat(parts, dim=1) if len(parts) > 1 else parts[0]
+
+
+def sliding_window_attention_inference(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mini_batch_size: int,
+                                       kv_cache: Optional[torch.Tensor] = None, interleave: bool = False,
+                                       kv_cache_size: int = 1560) -> torch.Tensor:
+    """ar_lact_swa_repeat.py:464-531, same name and arguments: the attention of one generation step of the
+    autoregressive-video layer.  (1) no cache, not interleaved: full attention; (2) interleaved: the first
+    mini_batch_size (clean) tokens attend among themselves, the rest over the last kv_cache_size clean keys and their
+    own; (3) with a cache ([2 b, l_c, h, d]: keys of all entries, then values): full attention over cache + k."""
+    if kv_cache is None and not interleave:
+        return block_attention(q, k, v)
+    if interleave:
+        mb = mini_batch_size
+        o_clean = block_attention(q[:, :mb], k[:, :mb], v[:, :mb])
+        o_rest = block_attention(q[:, mb:], k[:, mb - kv_cache_size:], v[:, mb - kv_cache_size:])
+        return torch.cat([o_clean, o_rest], dim=1)
+    k_cache, v_cache = kv_cache.chunk(2, dim=0)
+    return block_attention(q, torch.cat([k_cache, k], dim=1), torch.cat([v_cache, v], dim=1))

@@ -244,3 +244,31 @@ def test_ar_video_block_attention_matches_the_visibility_matrix(lo, repeated):
     for name, x, want in zip("qkv", cl, leaves):
         a, b_ = x.grad.float().cpu(), want.grad
         assert orc.rel_max(a, b_) <= 3e-2 and orc.cosine(a, b_) >= 0.9995, (name, orc.rel_max(a, b_), orc.cosine(a, b_))
+
+
+@pytest.mark.gpu
+def test_ar_video_inference_attention_three_cases(lo):
+    """sliding_window_attention_inference: plain, interleaved (clean + noisy part) and with a key / value cache."""
+    import lact_b200
+    from oracle import lact_oracle as orc
+    b, h, d, mb, kvc = 2, 2, 128, 140, 60
+    g = torch.Generator().manual_seed(41)
+    q, k, v = (torch.randn(b, 2 * mb, h, d, generator=g).to(BF16) for _ in range(3))
+    cache = torch.randn(2 * b, kvc, h, d, generator=g).to(BF16)
+    cu = lambda *ts: [t.cuda() for t in ts]
+    close = lambda got, ref: float((got.float().cpu() - ref).abs().max() / ref.abs().max()) <= 1.5e-2
+    # (1) plain
+    got = lo.sliding_window_attention_inference(*cu(q, k, v), mb)
+    assert close(got, orc.masked_attention(q, k, v, torch.ones(2 * mb, 2 * mb, dtype=torch.bool)))
+    # (2) interleaved: clean block, then the noisy block over the last kvc clean keys and itself
+    vis = torch.zeros(2 * mb, 2 * mb, dtype=torch.bool)
+    vis[:mb, :mb] = True
+    vis[mb:, mb - kvc:] = True
+    got = lo.sliding_window_attention_inference(*cu(q, k, v), mb, interleave=True, kv_cache_size=kvc)
+    assert close(got, orc.masked_attention(q, k, v, vis))
+    # (3) cache of all entries' keys, then values
+    got = lo.sliding_window_attention_inference(*cu(q, k, v), mb, kv_cache=cache.cuda())
+    kc, vc = cache[:b], cache[b:]
+    ref = orc.masked_attention(q, torch.cat([kc, k], 1), torch.cat([vc, v], 1), torch.ones(2 * mb, kvc + 2 * mb, dtype=torch.bool))
+    assert close(got, ref)
+    lact_b200.synchronize_and_check()
