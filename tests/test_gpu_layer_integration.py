@@ -130,3 +130,44 @@ def test_two_stacked_layers_train_step_with_muon(mods):
         assert torch.isfinite(t.float()).all()
     for a, b_ in zip(outs[0], outs[1]):
         assert torch.equal(a, b_)
+
+
+def test_nvs_layer_chain(mods):
+    """The novel-view-synthesis block (lact_nvs/lact_ttt.py:204-245): SiLU of the fused q / k / v projection, l2 norm of
+    q and k, softplus learning rates (the reference orders the lr projection (lrs, head); the kernel wants (head, lrs):
+    the rows of the Linear are permuted once), the operator-list recurrence in the transposed weight layout with
+    Muon, RMSNorm of the result and the head merge -- this package's operators against the oracle's, forward."""
+    lb, lo, orc = mods
+    b, l, hidden, n_h = 2, 640, 256, 2
+    d = hidden // n_h
+    g = torch.Generator().manual_seed(21)
+    rn = lambda *s, scale=1.0: torch.randn(*s, generator=g) * scale
+    p = dict(wqkv=rn(3 * hidden, hidden, scale=hidden ** -0.5).to(BF16), wlr=rn(3 * n_h, hidden, scale=hidden ** -0.5),
+             norm=1.0 + 0.1 * rn(d), w0=rn(n_h, d, d, scale=d ** -0.5), w1=rn(n_h, d, d, scale=d ** -0.5),
+             w2=rn(n_h, d, d, scale=d ** -0.5))
+    x = (rn(b, l, hidden) * 0.5).to(BF16)
+    order = [(0, 128, False, True), (0, 384, True, False), (384, 512, True, True), (512, 640, False, True)]
+    base_lr, steps = 0.01, 5
+    # (lrs, head) -> (head, lrs)
+    perm = torch.tensor([lrs * n_h + h for h in range(n_h) for lrs in range(3)])
+
+    def chain(x, p, ops, dev):
+        xq, xk, xv = F.linear(x, p["wqkv"]).chunk(3, dim=-1)
+        fq, fk, fv = ops["qkv"](xq, xk, xv, n_h)
+        lr0, lr1, lr2, _ = ops["lr"](F.linear(x.float(), p["wlr"][perm.to(dev)]), n_h, base_lr, None)
+        rep = lambda w: w.repeat(b, 1, 1)
+        out, *_ = ops["ttt"](rep(p["w0"]), rep(p["w1"]), rep(p["w2"]), fq, fk, fv, lr0, lr1, lr2, order, steps)
+        return ops["out"](out, p["norm"], n_h, None, None)
+
+    ref = chain(x, p, dict(qkv=orc.qkv_prologue, lr=orc.lr_prologue,
+                           ttt=lambda *a: orc.nvs_mini_batch_apply(*a, nm=orc.Numerics("ref", autocast=True)),
+                           out=lambda fw, w, n, gate, o: orc.out_epilogue(fw, w, n, gate, o)), "cpu")
+    pc = {k: v.cuda() for k, v in p.items()}
+    got = chain(x.cuda(), pc, dict(qkv=lo.qkv_prologue, lr=lo.lr_prologue,
+                                   ttt=lb.fast_weight_swish_glu_weight_norm_mini_batch_apply, out=lo.out_epilogue), "cuda")
+    lb.synchronize_and_check()
+    assert got.shape == (b, 384, hidden) and got.dtype == BF16   # the three apply operators' tokens, in list order
+    # the first apply uses the initial weights (exact band); the others carry one or two Newton-Schulz passes
+    assert orc.rel_max(got[:, :128].float().cpu(), ref[:, :128].float()) <= 3e-2
+    cs, rm = orc.cosine(got.float().cpu(), ref.float()), orc.rel_max(got.float().cpu(), ref.float())
+    assert cs >= 0.995 and rm <= 1e-1, (cs, rm)
