@@ -555,6 +555,9 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         # with NCCL_DEBUG set (VERSION, WARN, ...) NCCL prints its version banner and its messages on stdout, next to
         # the one JSON line this script owes: send them to a per-process log file instead
+        # (NCCL honours the file only above the VERSION level)
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"
         os.environ.setdefault("NCCL_DEBUG_FILE", os.path.join(tempfile.gettempdir(), "lact_b200_bench_nccl.%h.%p.log"))
         dist.init_process_group("nccl", device_id=dev)
     from lact_b200 import build
