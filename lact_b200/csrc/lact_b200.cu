@@ -708,14 +708,18 @@ int try_ns_fused(const NsGroup* grp, int ngroups, int steps, int const_coeffs, i
                    : launch_ns_fused<BTV, BTV, 5>(grp, ngroups, steps, const_coeffs, status, stream, unscaled_first, keep))
   const int64_t want = static_cast<int64_t>(sm_count()) * 3 / 4;
   // Gram side a multiple of 128 in every group and plenty of matrices: the symmetric phases (Gram matrix, polynomial)
-  // run on 128 x 128 tiles on and above the diagonal only, the update keeps its 192-wide tiles
-  bool sym_ok = bt_mm == 192 && bt_mn == 192 && gram_tiles(192) >= want;
-  for (int g = 0; g < ngroups; ++g) sym_ok = sym_ok && grp[g].m % kBM == 0 && grp[g].m >= 2 * kBM;
-  if (sym_ok)
+  // run on 128 x 128 tiles on and above the diagonal only, the update keeps its 192-wide tiles.  With fewer matrices
+  // (measured at D = H = 384: 16 and 12 units, i.e. under 1.5 Gram tiles of width 192 per SM) the symmetric phases
+  // leave a second, nearly empty round of tiles and plain 128-wide tiles are 4-5 % faster; from 20 units up the
+  // symmetric variant wins.
+  const bool wide = bt_mm == 192 && bt_mn == 192;
+  bool symmable = wide;
+  for (int g = 0; g < ngroups; ++g) symmable = symmable && grp[g].m % kBM == 0 && grp[g].m >= 2 * kBM;
+  if (symmable && gram_tiles(192) >= static_cast<int64_t>(sm_count()) * 3 / 2)
     return keep == nullptr
                ? launch_ns_fused<128, 192, 2, true>(grp, ngroups, steps, const_coeffs, status, stream, unscaled_first)
                : launch_ns_fused<128, 192, 5, true>(grp, ngroups, steps, const_coeffs, status, stream, unscaled_first, keep);
-  if (bt_mm == 192 && bt_mn == 192 && gram_tiles(192) >= want) return LACT_NS_FUSED(192);
+  if (wide && !symmable && gram_tiles(192) >= want) return LACT_NS_FUSED(192);
   // (a 256-wide update tile leaves no room for a useful ring next to two staging tiles: 128 is used)
   const bool ok128 = (bt_mm == 192 && bt_mn == 192) || (bt_mm == 128 && (bt_mn == 128 || bt_mn == 256));
   if (ok128 && (gram_tiles(128) >= want || gram_tiles(64) == gram_tiles(128))) return LACT_NS_FUSED(128);

@@ -277,7 +277,7 @@ def test_cfg3_backward_at_benchmark_head_shape(lb, orc):
     _check(orc, g, g_ref, list(NAMES) + ["momentum"])
 
 
-@pytest.mark.parametrize("B", [2, 12])   # 12 units: enough matrices for the wide / symmetric tile variants
+@pytest.mark.parametrize("B", [2, 12, 20])   # 2 / 12 / 20 units: the 64-wide, 128-wide and symmetric tile variants
 def test_cfg3_backward_with_muon_at_benchmark_head_shape(lb, orc, B):
     """The same with Muon on (two chunks, one update: the kept Newton-Schulz iterates of the [768 x 384] and
     [384 x 384] groups, the one-launch backward of the iteration with its symmetric phases, the renorm backward that

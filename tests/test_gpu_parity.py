@@ -165,9 +165,12 @@ def _flip_one_ulp(G):
                                    (2, 128, 256), (2, 192, 192),
                                    # contraction lengths that are not whole 64-wide k-blocks, odd k-block counts
                                    (2, 72, 200), (1, 200, 72), (1, 136, 328),
-                                   # enough matrices per launch for the wide-tile variants of the fused kernel (few
-                                   # matrices select narrower tiles: the cases above)
-                                   (24, 384, 384), (20, 768, 384), (16, 192, 192)])
+                                   # enough matrices per launch for the 128-wide tiles of the fused kernel (few
+                                   # matrices select 64-wide tiles: the cases above) ...
+                                   (24, 384, 384), (16, 192, 192),
+                                   # ... and for its symmetric variant (Gram and polynomial phases on the tiles on and
+                                   # above the diagonal, 192-wide update tiles: 1.5 Gram tiles per SM and more)
+                                   (40, 384, 384), (38, 768, 384)])
 @pytest.mark.parametrize("steps", [None, 0, 3, 5])
 def test_newton_schulz(lb, orc, shape, steps):
     g = torch.Generator().manual_seed(2)
@@ -182,9 +185,12 @@ def test_newton_schulz(lb, orc, shape, steps):
     # the kernels fold the residual terms into the contractions (fewer roundings than the reference's
     # eager arithmetic): against the CPU model with the same rounding points the result must stay
     # within twice that model's own sensitivity to a single bf16 ulp of its input ...
+    # (the flipped element sits in matrix 0: the sensitivity is measured there and every matrix is held to it, so
+    # the band does not depend on how many matrices share the tensor)
     model = orc.newton_schulz_folded(G, steps)
-    noise = orc.rel_fro(orc.newton_schulz_folded(_flip_one_ulp(G), steps), model)
-    assert orc.rel_fro(x, model) <= 2.0 * noise + 4e-3, (orc.rel_fro(x, model), noise)
+    noise = orc.rel_fro(orc.newton_schulz_folded(_flip_one_ulp(G), steps)[:1], model[:1])
+    worst = max(orc.rel_fro(x[i:i + 1], model[i:i + 1]) for i in range(shape[0]))
+    assert worst <= 2.0 * noise + 4e-3, (worst, noise)
     # ... and its distance to the reference's eager result is no more than the two implementations'
     # distances to the exact iteration added up
     assert orc.rel_fro(x, ref) <= err_k + err_r + 2e-3, (orc.rel_fro(x, ref), err_k, err_r)
