@@ -272,3 +272,43 @@ def test_ar_video_inference_attention_three_cases(lo):
     ref = orc.masked_attention(q, torch.cat([kc, k], 1), torch.cat([vc, v], 1), torch.ones(2 * mb, kvc + 2 * mb, dtype=torch.bool))
     assert close(got, ref)
     lact_b200.synchronize_and_check()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("mode", ["window", "causal", "block", "packed"])
+def test_swa_against_the_flash_attn_library_when_installed(lo, mode):
+    """The calls the reference layer makes (flash_attn_func / flash_attn_varlen_func, flash-attn as installed on the
+    test machine) on the same bf16 inputs: outputs and gradients of the two bf16 implementations agree to bf16
+    accuracy.  Skipped where the library is not importable."""
+    fa = pytest.importorskip("flash_attn")
+    import lact_b200
+    b, l, h, d, w = 2, 3000, 4, 128, 700
+    g = torch.Generator().manual_seed(43)
+    q, k, v = (torch.randn(b, l, h, d, generator=g).to(BF16).cuda() for _ in range(3))
+    dO = torch.randn(b, l, h, d, generator=g).to(BF16).cuda()
+    cu = torch.tensor([0, 500, 1777, 3000], dtype=torch.int32).cuda()
+    if mode == "packed":
+        q, k, v, dO = (t[:1].contiguous() for t in (q, k, v, dO))
+    mine = [t.clone().requires_grad_(True) for t in (q, k, v)]
+    ref = [t.clone().requires_grad_(True) for t in (q, k, v)]
+    if mode == "window":
+        o = lo.sliding_window_attention(*mine, w)
+        o_ref = fa.flash_attn_func(*ref, causal=True, window_size=(w - 1, 0))
+    elif mode == "causal":
+        o = lo.sliding_window_attention(*mine, None)
+        o_ref = fa.flash_attn_func(*ref, causal=True)
+    elif mode == "block":
+        o = lo.block_attention(*mine)
+        o_ref = fa.flash_attn_func(*ref, causal=False)
+    else:
+        o = lo.sliding_window_attention(*mine, w, cu_seqlens=cu)
+        o_ref = fa.flash_attn_varlen_func(*(t[0] for t in ref), cu_seqlens_q=cu, cu_seqlens_k=cu, max_seqlen_q=1277,
+                                          max_seqlen_k=1277, causal=True, window_size=(w - 1, 0)).unsqueeze(0)
+    o.backward(dO)
+    o_ref.backward(dO)
+    lact_b200.synchronize_and_check()
+    rel = lambda a, b_: float((a.float() - b_.float()).abs().max() / b_.float().abs().max())
+    cos = lambda a, b_: float(torch.nn.functional.cosine_similarity(a.float().flatten(), b_.float().flatten(), dim=0))
+    assert rel(o.detach(), o_ref.detach()) <= 1.5e-2, rel(o.detach(), o_ref.detach())
+    for name, a, b_ in zip("qkv", mine, ref):
+        assert rel(a.grad, b_.grad) <= 3e-2 and cos(a.grad, b_.grad) >= 0.9995, (name, rel(a.grad, b_.grad), cos(a.grad, b_.grad))
