@@ -251,3 +251,45 @@ def test_rotary_prologue_with_packed_sequences(lb, orc):
     plain = lo.qkv_prologue(*[c.detach() for c in cl], n_h, rotary=(cos.cuda(), sin.cuda(), hd))
     assert not torch.equal(plain[0][:, 100:], got[0][:, 100:].detach())
     assert torch.equal(plain[0][:, :70], got[0][:, :70].detach())
+
+
+def test_layer_passes_against_the_fla_kernels_when_they_run(lb, orc):
+    """The library kernels the reference layer itself calls (flash-linear-attention's Triton RotaryEmbedding and
+    RMSNorm, lact_llm/lact_model/layer_lact_swiglu.py:170, 242, 429, 557), run on this GPU on the same inputs: the
+    rotary prologue after the reference's own SiLU / l2_norm arithmetic, and the per-head RMSNorm of the output
+    epilogue.  Skipped where the package or its Triton backend is not usable."""
+    fla_modules = pytest.importorskip("fla.modules")
+    import torch.nn.functional as F
+    from lact_b200 import layer_ops as lo
+    b, s, n_h, d, hd = 2, 300, 2, 384, 128
+    g = torch.Generator().manual_seed(51)
+    xq, xk, xv = ((torch.randn(b, s, n_h * d, generator=g) * 0.8).to(BF16).cuda() for _ in range(3))
+    try:
+        rot = fla_modules.RotaryEmbedding(dim=hd, base=500000.0).cuda()
+        heads = lambda t: t.reshape(b, s, n_h, d).permute(0, 2, 1, 3).reshape(b * n_h, s, d)
+        l2n = lambda x: (x / (x.norm(dim=-1, keepdim=True) + 1e-5)).type(x.dtype)   # ttt_operation.py:19-26
+        fq, fk = l2n(heads(F.silu(xq))), l2n(heads(F.silu(xk)))
+        merge = lambda t: t.reshape(b, n_h, s, d).permute(0, 2, 1, 3).reshape(b, s, (n_h * d) // hd, hd)
+        rq, rk = rot(merge(fq), merge(fk), seqlen_offset=0, max_seqlen=s)
+        back = lambda t: heads(t.reshape(b, s, n_h * d))
+        want_q, want_k = back(rq), back(rk)
+        norm = fla_modules.RMSNorm(d, elementwise_affine=True, eps=1e-5).cuda()
+        with torch.no_grad():
+            norm.weight.copy_(1.0 + 0.1 * torch.randn(d, generator=g).cuda())
+        fw = (torch.randn(b * n_h, s, d, generator=g) * 0.5).to(BF16).cuda()
+        want_n = norm(fw).detach()
+        torch.cuda.synchronize()
+    except Exception as e:   # no usable Triton backend for this GPU in the installed package
+        pytest.skip(f"fla kernels did not run here: {type(e).__name__}: {str(e)[:120]}")
+    cos, sin = lo.rotary_tables(hd, s, device="cuda")
+    got_q, got_k, _ = lo.qkv_prologue(xq, xk, xv, n_h, rotary=(cos, sin, hd))
+    got_n = lo.out_epilogue(fw, norm.weight.detach(), n_h)
+    lb.synchronize_and_check()
+    # fla's rotary kernel contracts x cos - y sin differently from its own PyTorch restatement (which the oracle and
+    # this package follow bit for bit): where the two products cancel, the results differ by several ulps OF THE TINY
+    # RESULT, so the rotation is held to one bf16 ulp at the scale of the operands instead (2^-8 of the largest value)
+    for name, got, want in (("q", got_q, want_q), ("k", got_k, want_k)):
+        frac, _ = _ulp_report(got, want)
+        worst = float((got.float() - want.float()).abs().max() / want.float().abs().max())
+        assert frac <= 0.02 and worst <= 2.0 ** -8, f"rotary {name} vs fla: {frac:.4%} differ, worst {worst:.2e} of the maximum"
+    _check(got_n, want_n.reshape(b, n_h, s, d).permute(0, 2, 1, 3).reshape(b, s, n_h * d), "RMSNorm vs fla")
