@@ -5,7 +5,13 @@ lact_llm/lact_model/layer_lact_swiglu.py, is outside this package; these are the
 Forward: one fused CUDA pass each.  Backward (training): each pass is an autograd Function; the two passes over
 [b, s, n_h * d] (`qkv_prologue`, `out_epilogue`) have fused backward kernels that recompute from the saved inputs
 (the forward's bf16 roundings are treated as identities); the small learning-rate pass differentiates a plain
-PyTorch restatement."""
+PyTorch restatement.
+
+Attention half of the hybrid layers (tcgen05 kernels, forward and backward, head dimension 64 or 128):
+`sliding_window_attention` (causal band; packed sequences by `cu_seqlens`, padded batches by `attention_mask`),
+`block_attention` (not causal, own key count) and, under the reference's names, the autoregressive-video layer's
+`batched_sliding_window_attention`, `batched_sliding_window_attention_with_repeated_chunks` and
+`sliding_window_attention_inference`."""
 from __future__ import annotations
 
 import math
