@@ -102,3 +102,29 @@ def test_python_shim_rejects_cpu_tensors():
     lr = torch.zeros(1, 16, 1)
     with pytest.raises(RuntimeError):
         lact_b200.block_causal_lact_swiglu(w, w, w, x, x, x, lr, lr, lr, chunk_size=8)
+
+
+def header_prototypes():
+    """{name: number of parameters} for every function include/lact_b200.h declares."""
+    text = open(os.path.join(ROOT, "include", "lact_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    protos = {}
+    for m in re.finditer(r"\b(lact_[a-z0-9_]+)\s*\(([^;{}]*?)\)\s*;", text, flags=re.S):
+        params = m.group(2).strip()
+        protos[m.group(1)] = 0 if params in ("", "void") else len(params.split(","))
+    return protos
+
+
+def test_ctypes_prototypes_match_the_header(lib):
+    """Every entry point whose ctypes argument list the shim sets must list as many arguments as the header's
+    prototype has parameters (a missing or extra argument would shift every later one silently)."""
+    protos = header_prototypes()
+    assert len(protos) >= 30
+    checked = 0
+    for name, n_params in protos.items():
+        argtypes = getattr(getattr(lib, name), "argtypes", None)
+        if argtypes is None:
+            continue
+        assert len(argtypes) == n_params, f"{name}: header has {n_params} parameters, the shim passes {len(argtypes)}"
+        checked += 1
+    assert checked >= 20
