@@ -189,7 +189,8 @@ def test_swa_padded_batch_forward_and_backward(lo, side):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("d,lq,lk", [(128, 300, 300), (128, 200, 457), (64, 390, 130), (128, 1560, 1750), (64, 64, 1)])
+@pytest.mark.parametrize("d,lq,lk", [(128, 300, 300), (128, 200, 457), (64, 390, 130), (128, 1560, 1750), (64, 64, 1),
+                                     (128, 1, 700)])   # (one query over a cache of keys: a decoding step)
 def test_block_attention_forward_and_backward(lo, d, lq, lk):
     """Not causal, other key count than query count (the autoregressive-video layer's frame blocks): output and
     gradients against fp32 attention with every key visible."""
