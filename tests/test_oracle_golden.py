@@ -243,3 +243,23 @@ def test_ar_block_visibility_equals_the_block_by_block_calls(repeated):
     o[:, first:] = rearrange(torch.cat([o_clean, o_noise], 1), "(b n_c) sw h d -> b (n_c sw) h d", n_c=num_chunks - 1)
     got = orc.masked_attention(q, k, v, orc.ar_block_visibility(l, mb, ue, num_chunks, kvc, repeated))
     assert torch.allclose(got, o, atol=1e-5, rtol=1e-5)
+
+
+@pytest.mark.parametrize("l,w", [(37, 5), (64, 64), (50, None)])
+def test_banded_attention_equals_masked_attention(l, w):
+    """Two restatements of the same semantics: the blocked banded attention and one masked attention with the band
+    written out as a visibility matrix (the form the block-attention checks use)."""
+    g = torch.Generator().manual_seed(5)
+    q, k, v = (torch.randn(2, l, 2, 16, generator=g) for _ in range(3))
+    i, j = torch.arange(l).view(-1, 1), torch.arange(l).view(1, -1)
+    vis = (j <= i) & (j > i - (w if w else l))
+    assert torch.allclose(orc.sliding_window_attention(q, k, v, w, block=16), orc.masked_attention(q, k, v, vis),
+                          atol=1e-5, rtol=1e-5)
+
+
+def test_sequence_start_index_of_packed_sequences():
+    """The per-token sequence-start array the attention and rotary kernels take, from cu_seqlens (host-side helper)."""
+    from lact_b200.layer_ops import _seq_start
+    cu = torch.tensor([0, 3, 4, 9], dtype=torch.int32)
+    assert _seq_start(cu, 9, "cpu").tolist() == [0, 0, 0, 3, 4, 4, 4, 4, 4]
+    assert _seq_start(cu, 9, "cpu").dtype == torch.int32
