@@ -1,5 +1,6 @@
 // Causal sliding-window attention forward for sm_100a: o_i = softmax_j(q_i . k_j / sqrt(d)) v_j over the keys
-// i - window < j <= i of the same (batch, head).  One CTA per (batch, head, 128-query tile):
+// i - window < j <= i of the same (batch, head); with causal = 0, over all Lk keys of the batch entry (block
+// attention).  One CTA per (batch, head, 128-query tile):
 //   warp 0     TMA producer: the query tile once, then key and value tiles of 128 rows through two-stage rings;
 //   warp 1     MMA issuer:   S = Q K^T (128 x 128, fp32, tensor memory, double-buffered) and O_t = P V per key tile
 //                            (128 x d, tensor memory, double-buffered; NOT accumulated across tiles);

@@ -1,5 +1,6 @@
-// Backward of the causal sliding-window attention (swa.cuh) for sm_100a.  With P = softmax(q k^T * scale) restricted
-// to the band, recomputed from the forward's log-sum-exp L, and Delta_i = sum_d dO_i O_i:
+// Backward of the attention kernel of swa.cuh (causal sliding window, or - causal = 0 - every key of the batch entry
+// visible to every query) for sm_100a.  With P = softmax(q k^T * scale) restricted to the visible keys, recomputed from
+// the forward's log-sum-exp L, and Delta_i = sum_d dO_i O_i:
 //   dV_j = sum_i P_ij dO_i,   dS_ij = P_ij (dO_i . v_j - Delta_i) * scale,   dK_j = sum_i dS_ij q_i,   dQ_i = sum_j dS_ij k_j.
 // One kernel, two modes (a CTA owns a 128-row OUTER tile and walks 64-row INNER tiles of its band):
 //   MODE 0  outer = key tile j, inner = query tiles i:  dV_j += P^T dO_i,  dK_j += dS^T Q_i   (two accumulators)
@@ -12,8 +13,9 @@
 // Pipeline over the inner tiles: the inner tiles go through a three-stage ring (a stage is held from its load to the end
 // of its second products, so two stages would put the load latency on the critical path), S / dP columns and the
 // P / dS tiles are double-buffered; the issuing thread queues the first products of tile t + 1 BEFORE the second
-// products of tile t, so the tensor pipe works on one tile while the softmax threads work on the other.  Every wait
-// is bounded.
+// products of tile t, so the tensor pipe works on one tile while the softmax threads work on the other.  Every
+// mbarrier wait is bounded; the one named barrier (mode 0, per-query values staged a tile ahead) is reached by every
+// softmax thread in every iteration, whatever its waits returned.
 #pragma once
 #include "swa.cuh"
 
