@@ -699,7 +699,9 @@ def _l2_norm_add_bwd_op(x: torch.Tensor, x_add: torch.Tensor, tgt_scale: torch.T
     sc = tgt_scale.reshape(B, T).float().contiguous()
     dsc = torch.zeros(B, T, dtype=torch.float32, device=x.device)
     dw = renorm_backward(x.float().contiguous(), x_add, sc, dy.float().contiguous(), dsc, L.RENORM_EPS_INSIDE)
-    return [dw.to(x.dtype), dw.to(x_add.dtype), dsc.reshape(tgt_scale.shape).to(tgt_scale.dtype)]
+    # (two distinct tensors even where both inputs have dw's dtype: an operator's outputs may not alias one another)
+    dxa = dw.to(x_add.dtype) if x_add.dtype != dw.dtype else dw.clone()
+    return [dw.to(x.dtype), dxa, dsc.reshape(tgt_scale.shape).to(tgt_scale.dtype)]
 
 
 @_l2_norm_add_bwd_op.register_fake

@@ -11,7 +11,13 @@ reference has no such driver; the recurrence is that of its fused post-norm func
 sequence-parallel helpers (lact_ar_video/minVid/models/wan/wan_base/distributed/sp_support.py:65-144).
 
 Token layout: with chunk size C and W ranks, rank r holds tokens [r * C/W, (r+1) * C/W) of every
-chunk, chunks concatenated in order (`shard_tokens` / `unshard_tokens`).  Forward only.
+chunk, chunks concatenated in order (`shard_tokens` / `unshard_tokens`).
+
+Training (Muon off): the recurrence is built from the differentiable fused sub-ops, and the all-reduce is an autograd
+node whose backward all-reduces the incoming gradient (every rank's loss depends on the summed gradient).  Each rank
+gets the gradients of its own token shards (q, k, v, learning rates, momentum) in full; the gradients of the REPLICATED
+initial weights come out as per-rank shares that the caller sums over the ranks, as a data-parallel wrapper does for
+any replicated parameter.  With Muon the Newton-Schulz sub-op has no autograd formula here: forward only.
 """
 from __future__ import annotations
 
@@ -43,6 +49,22 @@ def unshard_tokens(parts: List[torch.Tensor], chunk_size: int) -> torch.Tensor:
     n_chunks = Lloc // per
     st = torch.stack([p.reshape(B, n_chunks, per, *p.shape[2:]) for p in parts], dim=2)
     return st.reshape(B, n_chunks * chunk_size, *parts[0].shape[2:])
+
+
+class _AllReduceSum(torch.autograd.Function):
+    """y = sum over ranks of x (every rank receives y); dL/dx = sum over ranks of dL/dy."""
+    @staticmethod
+    def forward(ctx, x, all_reduce):
+        ctx.all_reduce = all_reduce
+        y = x.detach().clone()
+        all_reduce(y)
+        return y
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous().clone()
+        ctx.all_reduce(g)
+        return g, None
 
 
 def _cuda_ops() -> SimpleNamespace:
@@ -113,6 +135,8 @@ class TokenShardedScan:
             dw1 = dw1 + self.m1 * beta
             self.m02, self.m1 = dw02, dw1
         if self.use_muon:
+            if torch.is_grad_enabled() and (dw1.requires_grad or dw02.requires_grad):
+                raise NotImplementedError("token-sharded training with Muon: the Newton-Schulz sub-op has no gradient here")
             dw1 = self.ops.newton_schulz(dw1)
             dw02 = self.ops.newton_schulz(dw02)
         self.w02 = self.ops.l2_norm_add(self.w02, dw02.contiguous(), self.n02, eps=1e-5)
@@ -123,7 +147,10 @@ class TokenShardedScan:
         for c in range(self.n_chunks - 1):
             self.apply(c)
             flat = self.local_gradient(c)
-            all_reduce(flat)
+            if flat.requires_grad:
+                flat = _AllReduceSum.apply(flat, all_reduce)
+            else:
+                all_reduce(flat)
             self.update(flat)
         self.apply(self.n_chunks - 1)
         return self.out
@@ -137,7 +164,8 @@ def token_sharded_block_causal_lact_swiglu(w0, w1, w2, q, k, v, lr0, lr1, lr2, c
     `group`.  q, k, v, lr*, momentum are this rank's token shards (`shard_tokens` layout), the weights are the full
     (replicated) initial fast weights; returns this rank's shard of the output.  `chunk_size` is the GLOBAL chunk
     size.  One all-reduce of [B (2HD + DH) + B] fp32 values per update; without an initialised process group the
-    call degenerates to the single-rank recurrence."""
+    call degenerates to the single-rank recurrence.  Differentiable with Muon off (module docstring: the weights'
+    gradients are per-rank shares to be summed over the ranks)."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     scan = TokenShardedScan(w0, w1, w2, q, k, v, lr0, lr1, lr2, chunk_size, world, use_muon=use_muon,
                             momentum=momentum, sub_ops=sub_ops)

@@ -90,7 +90,9 @@ def test_fast_weight_grads_are_differentiable(lb, orc, B, N, D, H):
 
 
 @pytest.mark.parametrize("x_dtype,add_dtype,tgt", [(torch.float32, BF16, None), (torch.float32, BF16, BF16),
-                                                  (BF16, BF16, None)])
+                                                  (BF16, BF16, None),
+                                                  # both fp32: the two gradients are the same values, yet two tensors
+                                                  (torch.float32, torch.float32, None)])
 def test_l2_norm_add_fused_is_differentiable(lb, orc, x_dtype, add_dtype, tgt):
     B, T, D = 3, 200, 384
     g = torch.Generator().manual_seed(43)

@@ -115,3 +115,47 @@ def test_two_nccl_ranks(lb, tmp_path):
         momentum=i["momentum"])
     got = ts.unshard_tokens([torch.load(str(tmp_path / f"o{r}.pt")) for r in range(2)], C)
     _check(orc, got, ref, C, False)
+
+
+def test_lock_step_training_on_one_device(lb):
+    """Muon off, two lock-step instances on the CUDA sub-ops (with their autograd formulas) sharing the weight leaves:
+    gradients of every input against the fused driver's own backward on the unsharded sequence."""
+    from oracle import lact_oracle as orc
+    from lact_b200 import token_sharded as ts
+    B, L, D, H, C, W = 2, 1024, 64, 128, 256, 2
+    base = {k: v.cuda() for k, v in _inputs(B, L, D, H, seed=11).items()}
+    dO = torch.randn(B, L, D, generator=torch.Generator().manual_seed(12)).to(BF16).cuda()
+    names = ("w0", "w1", "w2") + NAMES
+
+    def leaves():
+        return {n: base[n].clone().requires_grad_(True) for n in names}
+
+    a = leaves()
+    ref = lb.postnorm_block_causal_lact_swiglu_fused_kernel_triton(
+        *[a[n] for n in ("w0", "w1", "w2", "q", "k", "v", "lr0", "lr1", "lr2")], chunk_size=C, use_muon=False,
+        momentum=a["momentum"])
+    (ref.float() * dO.float()).sum().backward()
+    b = leaves()
+    scans = []
+    for r in range(W):
+        mine = {n: ts.shard_tokens(b[n], C, W, r) for n in NAMES}
+        scans.append(ts.TokenShardedScan(b["w0"], b["w1"], b["w2"], mine["q"], mine["k"], mine["v"], mine["lr0"],
+                                         mine["lr1"], mine["lr2"], C, W, use_muon=False, momentum=mine["momentum"]))
+    for c in range(scans[0].n_chunks - 1):
+        flats = []
+        for s in scans:
+            s.apply(c)
+            flats.append(s.local_gradient(c))
+        total = flats[0] + flats[1]
+        for s in scans:
+            s.update(total)
+    for s in scans:
+        s.apply(s.n_chunks - 1)
+    out = ts.unshard_tokens([s.out for s in scans], C)
+    (out.float() * dO.float()).sum().backward()
+    lb.synchronize_and_check()
+    for n in names:
+        g, g_ref = b[n].grad, a[n].grad
+        assert g is not None and torch.isfinite(g.float()).all(), n
+        cs = orc.cosine(g.float().cpu(), g_ref.float().cpu())
+        assert cs >= 0.995, (n, cs)

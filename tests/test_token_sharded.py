@@ -117,3 +117,107 @@ def test_lock_step_instances_equal_the_process_group_path():
                                              i["lr2"], chunk_size=C, use_muon=False, momentum=i["momentum"]).float()
     assert torch.equal(one, ref)  # one rank: the same arithmetic as the unsharded driver, bit for bit
     assert orc.rel_max(got, ref) <= 2e-2
+
+
+def _loss_grads(fn, i, dO, names):
+    leaves = {n: i[n].float().clone().requires_grad_(True) for n in names}
+    o = fn(leaves)
+    (o.float() * dO.float()).sum().backward()
+    return o.detach(), {n: leaves[n].grad for n in names}
+
+
+GRAD_NAMES = ("w0", "w1", "w2") + NAMES
+
+
+def test_lock_step_training_gradients_match_the_unsharded_recurrence():
+    """Muon off, two lock-step instances sharing the weight leaves (a plain differentiable sum in place of the
+    all-reduce): the gradients of every input against autograd through the unsharded oracle driver."""
+    from oracle import lact_oracle as orc
+    torch.set_num_threads(1)
+    i = _inputs(1, 192, 32, 32, seed=6)
+    W, C = 2, 64
+    dO = torch.randn(1, 192, 32, generator=torch.Generator().manual_seed(8))
+
+    def sharded(leaves):
+        scans = []
+        for r in range(W):
+            mine = {n: ts.shard_tokens(leaves[n], C, W, r) for n in NAMES}
+            scans.append(ts.TokenShardedScan(leaves["w0"], leaves["w1"], leaves["w2"], mine["q"], mine["k"], mine["v"],
+                                             mine["lr0"], mine["lr1"], mine["lr2"], C, W, use_muon=False,
+                                             momentum=mine["momentum"], sub_ops=oracle_sub_ops()))
+        for c in range(scans[0].n_chunks - 1):
+            flats = []
+            for s in scans:
+                s.apply(c)
+                flats.append(s.local_gradient(c))
+            total = flats[0] + flats[1]
+            for s in scans:
+                s.update(total)
+        for s in scans:
+            s.apply(s.n_chunks - 1)
+        return ts.unshard_tokens([s.out for s in scans], C)
+
+    def whole(leaves):
+        return orc.block_causal_lact_swiglu_fused(leaves["w0"], leaves["w1"], leaves["w2"], leaves["q"], leaves["k"],
+                                                  leaves["v"], leaves["lr0"], leaves["lr1"], leaves["lr2"], chunk_size=C,
+                                                  use_muon=False, momentum=leaves["momentum"])
+
+    _, g = _loss_grads(sharded, i, dO, GRAD_NAMES)
+    _, g_ref = _loss_grads(whole, i, dO, GRAD_NAMES)
+    for n in GRAD_NAMES:
+        assert g[n] is not None and torch.isfinite(g[n]).all(), n
+        assert orc.cosine(g[n], g_ref[n]) >= 0.999, (n, orc.cosine(g[n], g_ref[n]))
+        assert orc.rel_max(g[n], g_ref[n]) <= 5e-2, (n, orc.rel_max(g[n], g_ref[n]))
+
+
+def _train_worker(rank, world, port, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(1)
+    i = _inputs(2, 256, 32, 32, seed=3)
+    dO = ts.shard_tokens(torch.randn(2, 256, 32, generator=torch.Generator().manual_seed(9)), 64, world, rank)
+    w = {n: i[n].clone().requires_grad_(True) for n in ("w0", "w1", "w2")}
+    mine = {n: ts.shard_tokens(i[n].float(), 64, world, rank).requires_grad_(True) for n in NAMES}
+    o = ts.token_sharded_block_causal_lact_swiglu(w["w0"], w["w1"], w["w2"], mine["q"], mine["k"], mine["v"],
+                                                  mine["lr0"], mine["lr1"], mine["lr2"], chunk_size=64, use_muon=False,
+                                                  momentum=mine["momentum"], sub_ops=oracle_sub_ops())
+    (o.float() * dO).sum().backward()
+    for t in w.values():   # replicated parameters: the per-rank shares are summed, as a data-parallel wrapper would
+        dist.all_reduce(t.grad)
+    torch.save({**{n: w[n].grad for n in w}, **{n: mine[n].grad for n in NAMES}}, os.path.join(out_dir, f"g{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_ranks_training_gradients(tmp_path):
+    """The process-group path with its differentiable all-reduce: two gloo ranks, gradients of the token shards
+    gathered and of the replicated weights summed, against autograd through the unsharded oracle driver."""
+    from oracle import lact_oracle as orc
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_train_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    torch.set_num_threads(1)
+    i = _inputs(2, 256, 32, 32, seed=3)
+    dO = torch.randn(2, 256, 32, generator=torch.Generator().manual_seed(9))
+    parts = [torch.load(str(tmp_path / f"g{r}.pt")) for r in range(2)]
+    whole = lambda leaves: orc.block_causal_lact_swiglu_fused(
+        leaves["w0"], leaves["w1"], leaves["w2"], leaves["q"], leaves["k"], leaves["v"], leaves["lr0"], leaves["lr1"],
+        leaves["lr2"], chunk_size=64, use_muon=False, momentum=leaves["momentum"])
+    _, g_ref = _loss_grads(whole, i, dO, GRAD_NAMES)
+    for n in ("w0", "w1", "w2"):
+        assert torch.equal(parts[0][n], parts[1][n])   # after the sum every rank holds the same weight gradient
+        assert orc.cosine(parts[0][n], g_ref[n]) >= 0.999 and orc.rel_max(parts[0][n], g_ref[n]) <= 5e-2, n
+    for n in NAMES:
+        got = ts.unshard_tokens([p[n] for p in parts], 64)
+        assert orc.cosine(got, g_ref[n]) >= 0.999 and orc.rel_max(got, g_ref[n]) <= 5e-2, (n, orc.cosine(got, g_ref[n]))
+
+
+def test_training_with_muon_is_refused():
+    i = _inputs(1, 128, 32, 32, seed=5)
+    w0 = i["w0"].clone().requires_grad_(True)
+    with pytest.raises(NotImplementedError):
+        ts.token_sharded_block_causal_lact_swiglu(w0, i["w1"], i["w2"], i["q"], i["k"], i["v"], i["lr0"], i["lr1"], i["lr2"],
+                                                  chunk_size=64, use_muon=True, momentum=i["momentum"],
+                                                  sub_ops=oracle_sub_ops())
