@@ -643,6 +643,25 @@ def fused_lact_swiglu_ffn_fast_weight_grads(W0_W2, W1, K, V, lr0, lr1, lr2):
     return dw02, dw1
 
 
+class _NewtonSchulz(torch.autograd.Function):
+    """U = NS(G) with every iterate kept (`lact_ns_trace_fwd`); dG from `lact_ns_trace_bwd` (bf16 operands, roundings
+    treated as identities, as autograd through the reference's bf16 iteration does) and the Frobenius normalisation."""
+    @staticmethod
+    def forward(ctx, G, steps):
+        from .backward import ns_forward_saved
+        Gd = G.detach()
+        ctx.saved, U = ns_forward_saved(Gd, 5 if steps is None else int(steps), steps is not None, False)
+        ctx.in_dtype = G.dtype
+        return U
+
+    @staticmethod
+    def backward(ctx, dU):
+        from .backward import ns_backward, post_status
+        dG = ns_backward(ctx.saved, dU.contiguous())
+        post_status(dG.device)
+        return dG.to(ctx.in_dtype), None
+
+
 @_no_trace
 def zeropower_via_newtonschulz5(G: torch.Tensor, steps: Optional[int] = None) -> torch.Tensor:
     """Newton-Schulz orthogonalisation in bf16.  `steps=None`: the tuned 5-step schedule of
@@ -650,6 +669,10 @@ def zeropower_via_newtonschulz5(G: torch.Tensor, steps: Optional[int] = None) ->
     lact_nvs/lact_ttt.py:32-67.  G: [b, r, c], any float dtype -> bf16 [b, r, c]."""
     assert len(G.shape) == 3
     dev = _need_cuda(G)
+    if torch.is_grad_enabled() and G.requires_grad:
+        # the reference's function is plain PyTorch and so differentiable: here the iterates are kept and walked
+        # backwards by the recurrence's own Newton-Schulz backward kernels
+        return _NewtonSchulz.apply(G, steps)
     if G.dtype not in (torch.float32, BF16):
         G = G.float()
     G = G.contiguous()

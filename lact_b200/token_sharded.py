@@ -13,11 +13,11 @@ sequence-parallel helpers (lact_ar_video/minVid/models/wan/wan_base/distributed/
 Token layout: with chunk size C and W ranks, rank r holds tokens [r * C/W, (r+1) * C/W) of every
 chunk, chunks concatenated in order (`shard_tokens` / `unshard_tokens`).
 
-Training (Muon off): the recurrence is built from the differentiable fused sub-ops, and the all-reduce is an autograd
-node whose backward all-reduces the incoming gradient (every rank's loss depends on the summed gradient).  Each rank
-gets the gradients of its own token shards (q, k, v, learning rates, momentum) in full; the gradients of the REPLICATED
-initial weights come out as per-rank shares that the caller sums over the ranks, as a data-parallel wrapper does for
-any replicated parameter.  With Muon the Newton-Schulz sub-op has no autograd formula here: forward only.
+Training: the recurrence is built from the differentiable sub-ops (the Newton-Schulz one included), and the all-reduce
+is an autograd node whose backward all-reduces the incoming gradient (every rank's loss depends on the summed
+gradient).  Each rank gets the gradients of its own token shards (q, k, v, learning rates, momentum) in full; the
+gradients of the REPLICATED initial weights come out as per-rank shares that the caller sums over the ranks, as a
+data-parallel wrapper does for any replicated parameter.
 """
 from __future__ import annotations
 
@@ -135,8 +135,6 @@ class TokenShardedScan:
             dw1 = dw1 + self.m1 * beta
             self.m02, self.m1 = dw02, dw1
         if self.use_muon:
-            if torch.is_grad_enabled() and (dw1.requires_grad or dw02.requires_grad):
-                raise NotImplementedError("token-sharded training with Muon: the Newton-Schulz sub-op has no gradient here")
             dw1 = self.ops.newton_schulz(dw1)
             dw02 = self.ops.newton_schulz(dw02)
         self.w02 = self.ops.l2_norm_add(self.w02, dw02.contiguous(), self.n02, eps=1e-5)
@@ -164,8 +162,8 @@ def token_sharded_block_causal_lact_swiglu(w0, w1, w2, q, k, v, lr0, lr1, lr2, c
     `group`.  q, k, v, lr*, momentum are this rank's token shards (`shard_tokens` layout), the weights are the full
     (replicated) initial fast weights; returns this rank's shard of the output.  `chunk_size` is the GLOBAL chunk
     size.  One all-reduce of [B (2HD + DH) + B] fp32 values per update; without an initialised process group the
-    call degenerates to the single-rank recurrence.  Differentiable with Muon off (module docstring: the weights'
-    gradients are per-rank shares to be summed over the ranks)."""
+    call degenerates to the single-rank recurrence.  Differentiable (module docstring: the weights' gradients are
+    per-rank shares to be summed over the ranks)."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     scan = TokenShardedScan(w0, w1, w2, q, k, v, lr0, lr1, lr2, chunk_size, world, use_muon=use_muon,
                             momentum=momentum, sub_ops=sub_ops)

@@ -230,6 +230,27 @@ def test_newton_schulz_backward(lb, shape, steps):
     assert orc.cosine(got, ref64) >= 0.98
 
 
+@pytest.mark.parametrize("shape,steps,dtype", [((3, 64, 64), None, torch.float32), ((2, 128, 64), 3, BF16),
+                                               ((2, 192, 384), 0, torch.float32)])
+def test_newton_schulz_sub_op_is_differentiable(lb, shape, steps, dtype):
+    """`zeropower_via_newtonschulz5` under autograd (the reference's function is plain PyTorch, hence differentiable):
+    the value equals the plain call's bit for bit and the gradient is the backward helper's."""
+    from lact_b200 import backward as bw
+    g = torch.Generator().manual_seed(17)
+    G = torch.randn(*shape, generator=g).to(dtype).cuda()
+    dU = torch.randn(*shape, generator=g).cuda()
+    plain = lb.zeropower_via_newtonschulz5(G, steps)
+    Gl = G.clone().requires_grad_(True)
+    U = lb.zeropower_via_newtonschulz5(Gl, steps)
+    assert U.dtype == BF16 and torch.equal(U, plain)
+    (U.float() * dU).sum().backward()
+    saved, _ = bw.ns_forward_saved(G, 5 if steps is None else steps, steps is not None, False)
+    want = bw.ns_backward(saved, dU.to(BF16).float())
+    lb.synchronize_and_check()
+    assert Gl.grad is not None and Gl.grad.dtype == dtype and torch.isfinite(Gl.grad.float()).all()
+    assert torch.equal(Gl.grad.float(), want.to(dtype).float())
+
+
 @pytest.mark.parametrize("shapes,steps", [
     ([(3, 64, 64), (2, 64, 128)], None),          # 64-wide tiles; square + wide
     ([(4, 256, 128), (4, 128, 128)], None),        # 128-wide tiles; tall + square (the [w0; w2] / w1 pairing)

@@ -117,9 +117,11 @@ def test_two_nccl_ranks(lb, tmp_path):
     _check(orc, got, ref, C, False)
 
 
-def test_lock_step_training_on_one_device(lb):
-    """Muon off, two lock-step instances on the CUDA sub-ops (with their autograd formulas) sharing the weight leaves:
-    gradients of every input against the fused driver's own backward on the unsharded sequence."""
+@pytest.mark.parametrize("use_muon", [False, True])
+def test_lock_step_training_on_one_device(lb, use_muon):
+    """Two lock-step instances on the CUDA sub-ops (with their autograd formulas, the Newton-Schulz one included)
+    sharing the weight leaves: gradients of every input against the fused driver's own backward on the unsharded
+    sequence (with Muon the per-rank rounding of the partial gradients is amplified by the iteration: looser band)."""
     from oracle import lact_oracle as orc
     from lact_b200 import token_sharded as ts
     B, L, D, H, C, W = 2, 1024, 64, 128, 256, 2
@@ -132,7 +134,7 @@ def test_lock_step_training_on_one_device(lb):
 
     a = leaves()
     ref = lb.postnorm_block_causal_lact_swiglu_fused_kernel_triton(
-        *[a[n] for n in ("w0", "w1", "w2", "q", "k", "v", "lr0", "lr1", "lr2")], chunk_size=C, use_muon=False,
+        *[a[n] for n in ("w0", "w1", "w2", "q", "k", "v", "lr0", "lr1", "lr2")], chunk_size=C, use_muon=use_muon,
         momentum=a["momentum"])
     (ref.float() * dO.float()).sum().backward()
     b = leaves()
@@ -140,7 +142,7 @@ def test_lock_step_training_on_one_device(lb):
     for r in range(W):
         mine = {n: ts.shard_tokens(b[n], C, W, r) for n in NAMES}
         scans.append(ts.TokenShardedScan(b["w0"], b["w1"], b["w2"], mine["q"], mine["k"], mine["v"], mine["lr0"],
-                                         mine["lr1"], mine["lr2"], C, W, use_muon=False, momentum=mine["momentum"]))
+                                         mine["lr1"], mine["lr2"], C, W, use_muon=use_muon, momentum=mine["momentum"]))
     for c in range(scans[0].n_chunks - 1):
         flats = []
         for s in scans:
@@ -158,4 +160,4 @@ def test_lock_step_training_on_one_device(lb):
         g, g_ref = b[n].grad, a[n].grad
         assert g is not None and torch.isfinite(g.float()).all(), n
         cs = orc.cosine(g.float().cpu(), g_ref.float().cpu())
-        assert cs >= 0.995, (n, cs)
+        assert cs >= (0.97 if use_muon else 0.995), (n, cs)
