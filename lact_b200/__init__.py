@@ -13,6 +13,7 @@ from .ops import (  # noqa: F401
     fused_lact_swiglu_ffn_fast_weight_grads,
     fused_prenorm_update_with_momentum_and_l2_norm,
     fused_swiglu_ffn_fwd,
+    l2_norm,
     l2_norm_add_fused,
     minimal_block_causal_lact_swiglu,
     postnorm_block_causal_lact_swiglu_fused_kernel_triton,

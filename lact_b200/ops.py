@@ -643,6 +643,15 @@ def fused_lact_swiglu_ffn_fast_weight_grads(W0_W2, W1, K, V, lr0, lr1, lr2):
     return dw02, dw1
 
 
+def l2_norm(x: torch.Tensor) -> torch.Tensor:
+    """x scaled to unit l2 norm along its last axis, `x / (||x|| + 1e-5)` with the norm, the sum and the quotient each
+    in x's dtype (lact_llm/lact_model/ttt_operation.py:19-26; the layer imports it next to the chunk drivers,
+    layer_lact_swiglu.py:20-24).  Plain tensor arithmetic, exported so that the layer's import line keeps working; the
+    fused pass over q, k, v (`layer_ops.qkv_prologue`: head split, SiLU and this normalisation in one kernel) is what
+    a layer on this package calls instead."""
+    return (x / (x.norm(dim=-1, keepdim=True) + 1e-5)).type(x.dtype)
+
+
 class _NewtonSchulz(torch.autograd.Function):
     """U = NS(G) with every iterate kept (`lact_ns_trace_fwd`); dG from `lact_ns_trace_bwd` (bf16 operands, roundings
     treated as identities, as autograd through the reference's bf16 iteration does) and the Frobenius normalisation."""

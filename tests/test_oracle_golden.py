@@ -263,3 +263,19 @@ def test_sequence_start_index_of_packed_sequences():
     cu = torch.tensor([0, 3, 4, 9], dtype=torch.int32)
     assert _seq_start(cu, 9, "cpu").tolist() == [0, 0, 0, 3, 4, 4, 4, 4, 4]
     assert _seq_start(cu, 9, "cpu").dtype == torch.int32
+
+
+def test_exported_l2_norm_reproduces_the_reference_outputs():
+    """`lact_b200.l2_norm` (the helper the reference layer imports beside the chunk drivers) on SiLU'd, head-split
+    projections: bit-exact against the fixture written by the reference's own `l2_norm`."""
+    import os
+    import torch.nn.functional as F
+    import lact_b200
+    blob = torch.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "layer_prologue.pt"),
+                      map_location="cpu", weights_only=False)
+    case = blob["a"]
+    sp = case["spec"]
+    g = torch.Generator().manual_seed(sp["seed"])
+    xq = torch.randn(sp["b"], sp["s"], sp["n_h"] * sp["d"], generator=g).to(torch.bfloat16) * 1.5
+    heads = xq.reshape(sp["b"], sp["s"], sp["n_h"], sp["d"]).permute(0, 2, 1, 3).reshape(sp["b"] * sp["n_h"], sp["s"], sp["d"])
+    assert torch.equal(lact_b200.l2_norm(F.silu(heads)), case["q"])
